@@ -1,0 +1,305 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-contraction hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode_gemv] [--impl ours|reference]
+
+One JSON line on stdout (rank 0).  Workloads (synthetic, seeded; shapes from the decode /
+prefill configurations of the Gemma-4 12B-like model):
+
+  decode_gemv   48 "layers" x {gate/up 3840->30720, down 15360->3840, QKV 3840->8192,
+                O 4096->3840}: FP8 E4M3 weights with bf16 per-row scales, bf16 activations
+                quantised per token to E4M3 inside each GEMV launch; 48 distinct weight sets
+                (10.76 GB, far larger than L2).  Metric: GB/s of algorithmic bytes.
+
+A step is one pass over all 48 layers, replayed as one CUDA graph.  `value` is measured with
+inputs resident in HBM; `e2e` copies the step's activations from pinned host memory and the
+results back inside the timed region.  With N > 1 every rank runs an independent replica
+(the path does not shard at batch 1) and `value` is the sum over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+DECODE_SHAPES = [("gate_up", 30720, 3840), ("down", 3840, 15360), ("qkv", 8192, 3840), ("o", 3840, 4096)]
+LAYERS = 48
+SEED = 20261125
+
+
+def decode_bytes_per_layer() -> int:
+    """Algorithmic bytes of one layer: weights + fp32-equivalent scales + bf16 x + bf16 y."""
+    total = 0
+    for _, rows, k in DECODE_SHAPES:
+        total += rows * k + rows * 4 + k * 2 + rows * 2
+    return total
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[list[str]] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        reasons = set()
+        for s in self.samples:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:]):
+                if v == "Active":
+                    reasons.add(name)
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's own CPU numeric path on a bounded sample
+# --------------------------------------------------------------------------------------------
+def cpu_decode_sample(steps: int, warmup: int, use_ref: bool):
+    """Times one decode layer (all four GEMVs incl. the per-token FP8 quantisation) on the host
+    cores with the reference's src/numeric/fp8.cpp functions (or the oracle port when the
+    compiled reference is absent).  Returns (GB/s, seconds per sample, cores, kind)."""
+    import numpy as np
+    from oracle import Oracle, default_threads, ref_available
+    kind = "reference" if use_ref and ref_available() else "port"
+    o = Oracle(ref=(kind == "reference"))
+    port = Oracle()
+    threads = default_threads()
+    rng = np.random.default_rng(SEED)
+    layer = []
+    for _, rows, k in DECODE_SHAPES:
+        w = rng.integers(0, 256, size=(rows, k), dtype=np.uint8)
+        w[(w & 0x7F) == 0x7F] = 0x38
+        ws = port.to_bf16(rng.uniform(1e-4, 2e-4, size=rows).astype(np.float32))
+        x = port.from_bf16(port.to_bf16(rng.standard_normal((1, k)).astype(np.float32)))
+        layer.append((x, w, ws))
+
+    def one_pass():
+        for x, w, ws in layer:
+            q, s = o.fp8_quantize(x, threads=threads)
+            o.fp8_matmul(q, s, w, ws, threads=threads)
+
+    for _ in range(warmup):
+        one_pass()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_pass()
+    dt = (time.perf_counter() - t0) / steps
+    return decode_bytes_per_layer() / dt / 1e9, dt, threads, kind
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    gbs, dt, cores, kind = cpu_decode_sample(args.steps, min(args.warmup, 1), use_ref=True)
+    sample = "one decode layer (4 FP8 GEMVs + per-token quantisation, 224 MB) per step, all host cores"
+    line = {
+        "impl": "reference", "metric": "decode GEMV GB/s", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": {"workload": "decode_gemv", "layers": LAYERS, "shapes": DECODE_SHAPES},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------------------------
+def run_decode_gemv(args):
+    import torch
+    import torch.distributed as dist
+    from gem16_b200 import load
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = load()
+    lib.gemb_device_check()
+
+    # ---- synthetic model state: 48 distinct FP8 weight sets quantised with our own quantizer --
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + 1000 * 1 + rank)
+    weights = []
+    for layer in range(LAYERS):
+        mats = []
+        for _, rows, k in DECODE_SHAPES:
+            w = torch.randn((rows, k), device=dev, dtype=torch.float32, generator=gen) * 0.02
+            wq = torch.empty((rows, k), device=dev, dtype=torch.uint8)
+            wsc = torch.empty((rows,), device=dev, dtype=torch.float32)
+            lib.gemb_fp8_quantize(w, 0, wq, wsc, rows, k, None)
+            mats.append((wq, wsc.to(torch.bfloat16).view(torch.int16)))
+            del w
+        weights.append(mats)
+    # activations: one bf16 vector per op, in one contiguous buffer (device + pinned host copy)
+    x_elems = sum(k for _, _, k in DECODE_SHAPES) * LAYERS
+    y_elems = sum(r for _, r, _ in DECODE_SHAPES) * LAYERS
+    x_host = torch.randn((x_elems,), dtype=torch.float32).to(torch.bfloat16).pin_memory()
+    y_host = torch.empty((y_elems,), dtype=torch.bfloat16).pin_memory()
+    x_dev = x_host.to(dev)
+    y_dev = torch.zeros((y_elems,), device=dev, dtype=torch.bfloat16)
+
+    def enqueue_pass():
+        xo = yo = 0
+        n = 0
+        for mats in weights:
+            for (wq, ws), (_, rows, k) in zip(mats, DECODE_SHAPES):
+                lib.gemb_fp8_gemv_bf16in(x_dev[xo:xo + k], wq, ws, y_dev[yo:yo + rows], 1, rows, k,
+                                         torch.cuda.current_stream())
+                xo += k
+                yo += rows
+                n += 1
+        return n
+
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        launches_per_step = enqueue_pass()  # also warms lazily initialised state before capture
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            enqueue_pass()
+
+        def barrier():
+            torch.cuda.synchronize(dev)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(dev)
+
+        def timed(fn, steps):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            start.record(stream)
+            for _ in range(steps):
+                fn()
+            end.record(stream)
+            barrier()
+            ms = start.elapsed_time(end)
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms / 1e3
+
+        def step_resident():
+            graph.replay()
+
+        def step_e2e():
+            x_dev.copy_(x_host, non_blocking=True)
+            graph.replay()
+            y_host.copy_(y_dev, non_blocking=True)
+            stream.synchronize()
+
+        for _ in range(max(args.warmup, 3)):
+            step_resident()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        secs = timed(step_resident, args.steps)
+        clocks = sampler.stop() if rank == 0 else None
+        for _ in range(2):
+            step_e2e()
+        secs_e2e = timed(step_e2e, args.steps)
+
+    bytes_step = decode_bytes_per_layer() * LAYERS
+    value = world * bytes_step * args.steps / secs / 1e9
+    e2e = world * bytes_step * args.steps / secs_e2e / 1e9
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks = measured_peaks()
+    launch_s = secs / (args.steps * launches_per_step)
+    achieved = bytes_step / launches_per_step / launch_s / 1e9
+    line = {
+        "metric": "decode GEMV GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": "decode_gemv", "layers": LAYERS, "shapes": DECODE_SHAPES,
+                   "l2": "48 distinct weight sets, 10.76 GB per pass >> 126 MB L2", "multi_gpu": "replicas only"},
+        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": x_elems * 2, "d2h_bytes_per_step": y_elems * 2},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "fp8_gemv_kernel (bf16-in fused quantisation)",
+                     "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                     "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": None,
+                     "avg_launch_us": launch_s * 1e6},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        gbs, dt, cores, kind = cpu_decode_sample(1, 0, use_ref=True)
+        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
+                                "sample": f"one decode layer of 48 (224 MB), {dt:.2f} s on {cores} host threads"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode_gemv", choices=["decode_gemv"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    run_decode_gemv(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,100 @@
+// Shared host/device helpers for the gemb200 operator library.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+
+#include "gemb200.h"
+
+namespace gemb {
+
+// Records `message` (printf style) as the calling thread's last error and returns `code`.
+int32_t fail(int32_t code, const char* fmt, ...);
+// cudaGetLastError() after a launch: GEMB_OK, or GEMB_INTERNAL with "op: cudaErrorName: string"
+// (the format of CudaFailure at src/cuda/nvfp4/reference.cu:27-31).
+int32_t check_launch(const char* op);
+// GEMB_OK when the current device is sm_100-class; cached per device.
+int32_t require_sm100(const char* op);
+// Number of SMs of the current device (cached).
+int sm_count();
+
+inline bool positive_finite(float v) { return std::isfinite(v) && v > 0.0f; }
+
+#define GEMB_REQUIRE(cond, ...)                                           \
+  do {                                                                    \
+    if (!(cond)) return ::gemb::fail(GEMB_INVALID_ARGUMENT, __VA_ARGS__); \
+  } while (0)
+
+#define GEMB_TRY(expr)                   \
+  do {                                   \
+    int32_t gemb_rc_ = (expr);           \
+    if (gemb_rc_ != GEMB_OK) return gemb_rc_; \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// Device-side codecs.  E2M1/E4M3 conversions use the hardware cvt instructions, which round to
+// nearest with ties to the even code and saturate to the largest finite value: the same rule
+// as ChooseNearestE2M1 / ChooseNearestPositiveE4M3Fn in src/numeric/nvfp4.cpp:26-56.
+// ---------------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t bits) {
+  return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+}
+__device__ __forceinline__ uint16_t float_to_bf16_bits(float v) {
+  return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ float bf16_round(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+__device__ __forceinline__ uint8_t e4m3_encode(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+__device__ __forceinline__ float e4m3_decode(uint8_t bits) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(bits, __NV_E4M3);
+  return __half2float(__half(h));
+}
+// Two floats -> one byte, `lo` in the low nibble.
+__device__ __forceinline__ uint8_t e2m1x2_encode(float lo, float hi) {
+  return static_cast<uint8_t>(
+      __nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest));
+}
+// One byte -> half2, low nibble in .x.
+__device__ __forceinline__ __half2 e2m1x2_decode(uint8_t byte) {
+  __half2_raw r = __nv_cvt_fp4x2_to_halfraw2(byte, __NV_E2M1);
+  return __half2(r);
+}
+__device__ __forceinline__ float rcp_approx_ftz(float v) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+
+// Byte offset of block scale (row r, scale column c) in the 128x4 interleaved layout with
+// `c_pad` = K/16 rounded up to 4  (src/cuda/nvfp4/cutlass_sm120.cu:160-172).
+__host__ __device__ __forceinline__ uint64_t interleaved_scale_offset(uint64_t r, uint64_t c,
+                                                                       uint64_t c_pad) {
+  return ((r / 128) * (c_pad / 4) + c / 4) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + c % 4;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace gemb

@@ -1,0 +1,519 @@
+// Batch-1 decode projections: HBM-streaming, warp-reduced GEMV kernels for FP8 (W8A8) and NVFP4
+// (W4A4) weights in the checkpoint's row-major source layout.
+//
+// Shape of every kernel: a CTA of 8 warps stages the activation vector once in shared memory
+// (decoded to fp16, which holds every E4M3 and E2M1 value exactly), then each warp streams
+// kRows weight rows with coalesced 128-bit loads (lane l reads bytes [16 l, 16 l + 16) of each
+// 512-byte row segment, `no_allocate` so the stream does not evict the activation from L1),
+// accumulates in fp32 and folds the 32 lanes with an xor butterfly.  Weights are read exactly
+// once: algorithmic bytes per output row are K (FP8) or K/2 + K/16 (NVFP4) plus the scale and
+// the 4-byte result; the activation (K bytes or less) is re-read per CTA from L2.
+#include "common.cuh"
+
+namespace gemb {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// Two E4M3 bytes (low half of `pair`) -> two fp16 values.
+__device__ __forceinline__ uint32_t e4m3x2_to_half2(uint16_t pair) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(pair));
+  return r;
+}
+// acc += a * b with fp16 inputs and an fp32 accumulator, one rounding (sm_100 mixed fma).
+__device__ __forceinline__ void fma_f16(float& acc, uint16_t a, uint16_t b) {
+  asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc) : "h"(a), "h"(b));
+}
+__device__ __forceinline__ void dot16_fp8(float& acc, const uint4& w, const uint4& xa, const uint4& xb) {
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+  const uint32_t xx[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t h0 = e4m3x2_to_half2(static_cast<uint16_t>(ww[i] & 0xFFFFu));
+    const uint32_t h1 = e4m3x2_to_half2(static_cast<uint16_t>(ww[i] >> 16));
+    fma_f16(acc, static_cast<uint16_t>(h0 & 0xFFFFu), static_cast<uint16_t>(xx[2 * i] & 0xFFFFu));
+    fma_f16(acc, static_cast<uint16_t>(h0 >> 16), static_cast<uint16_t>(xx[2 * i] >> 16));
+    fma_f16(acc, static_cast<uint16_t>(h1 & 0xFFFFu), static_cast<uint16_t>(xx[2 * i + 1] & 0xFFFFu));
+    fma_f16(acc, static_cast<uint16_t>(h1 >> 16), static_cast<uint16_t>(xx[2 * i + 1] >> 16));
+  }
+}
+
+struct Fp8Problem {
+  const uint8_t* w;
+  const uint16_t* w_scales;
+  void* out;
+  uint64_t rows;
+};
+struct Fp8Group {
+  Fp8Problem p[3];
+  unsigned first_block[4];  // CTA index at which each problem starts; [n] = total
+  int n;
+};
+
+// Shared-memory layout of the staged activation: per 512-element segment, lane l's sixteen
+// values are split into two 8-value halves stored at [l*8, l*8+8) and [256 + l*8, 256 + l*8 + 8)
+// so that each 128-bit shared load of a warp touches 512 contiguous bytes (no bank conflicts).
+//
+// Stages an already quantized activation (E4M3 bytes) as fp16 in shared memory.
+__device__ __forceinline__ void stage_fp8_activation(const uint8_t* act, uint64_t k, __half* xs) {
+  for (uint64_t c = threadIdx.x; c < k / 16; c += kThreads) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(act) + c);
+    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+    uint32_t h[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      h[2 * i] = e4m3x2_to_half2(static_cast<uint16_t>(ww[i] & 0xFFFFu));
+      h[2 * i + 1] = e4m3x2_to_half2(static_cast<uint16_t>(ww[i] >> 16));
+    }
+    __half* dst = xs + (c / 32) * 512 + (c % 32) * 8;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<uint4*>(dst + 256) = make_uint4(h[4], h[5], h[6], h[7]);
+  }
+}
+
+// Quantizes a bf16 activation per token inside the CTA (same arithmetic as the standalone FP8
+// quantizer: scale = amax/448, q = E4M3(x/scale), src/numeric/fp8.cpp:41-58) and stages the
+// decoded bytes as fp16.  Returns the token scale.
+__device__ __forceinline__ float stage_bf16_activation(const uint16_t* x, uint64_t k, __half* xs,
+                                                       float* red) {
+  float amax = 0.0f;
+  for (uint64_t c = threadIdx.x; c < k / 8; c += kThreads) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x) + c);
+    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      amax = fmaxf(amax, fabsf(__uint_as_float(ww[i] << 16)));
+      amax = fmaxf(amax, fabsf(__uint_as_float(ww[i] & 0xFFFF0000u)));
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < kWarps; ++i) amax = fmaxf(amax, red[i]);
+  const float scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 448.0f);
+  for (uint64_t c = threadIdx.x; c < k / 8; c += kThreads) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x) + c);
+    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+    uint32_t h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float lo = __fdiv_rn(__uint_as_float(ww[i] << 16), scale);
+      const float hi = __fdiv_rn(__uint_as_float(ww[i] & 0xFFFF0000u), scale);
+      const uint16_t q = static_cast<uint16_t>(
+          __nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+      h[i] = e4m3x2_to_half2(q);
+    }
+    const uint64_t c16 = c / 2;
+    *reinterpret_cast<uint4*>(xs + (c16 / 32) * 512 + (c % 2) * 256 + (c16 % 32) * 8) =
+        make_uint4(h[0], h[1], h[2], h[3]);
+  }
+  return scale;
+}
+
+template <int kRows, bool kFusedQuant, bool kBf16Out>
+__global__ void __launch_bounds__(kThreads)
+fp8_gemv_kernel(const void* __restrict__ act, const float* __restrict__ act_scale, Fp8Group grp,
+                uint64_t k) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __half* xs = reinterpret_cast<__half*>(smem_raw);
+  __shared__ float red[kWarps];
+
+  float a_scale;
+  if constexpr (kFusedQuant) {
+    a_scale = stage_bf16_activation(static_cast<const uint16_t*>(act), k, xs, red);
+  } else {
+    stage_fp8_activation(static_cast<const uint8_t*>(act), k, xs);
+    a_scale = __ldg(act_scale);
+  }
+  __syncthreads();
+
+  int pi = 0;
+  while (pi + 1 < grp.n && blockIdx.x >= grp.first_block[pi + 1]) ++pi;
+  const Fp8Problem prob = grp.p[pi];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t row0 = (static_cast<uint64_t>(blockIdx.x - grp.first_block[pi]) * kWarps + warp) * kRows;
+  if (row0 >= prob.rows) return;
+
+  const uint8_t* wrow[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    const uint64_t row = row0 + r < prob.rows ? row0 + r : prob.rows - 1;
+    wrow[r] = prob.w + row * k;
+  }
+  float acc[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) acc[r] = 0.0f;
+
+  constexpr int kUnroll = kRows >= 4 ? 2 : (kRows == 2 ? 4 : 8);
+  const uint64_t step = 512ull * kUnroll;
+  uint64_t kb = 0;
+  for (; kb + step <= k; kb += step) {
+    uint4 wv[kUnroll][kRows];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) wv[u][r] = ldg_stream(wrow[r] + kb + u * 512 + lane * 16);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const __half* xp = xs + kb + u * 512 + lane * 8;
+      const uint4 xa = *reinterpret_cast<const uint4*>(xp), xb = *reinterpret_cast<const uint4*>(xp + 256);
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) dot16_fp8(acc[r], wv[u][r], xa, xb);
+    }
+  }
+  for (uint64_t kk = kb + lane * 16; kk < k; kk += 512) {
+    const __half* xp = xs + (kk / 512) * 512 + lane * 8;
+    const uint4 xa = *reinterpret_cast<const uint4*>(xp), xb = *reinterpret_cast<const uint4*>(xp + 256);
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) dot16_fp8(acc[r], ldg_stream(wrow[r] + kk), xa, xb);
+  }
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) acc[r] = warp_sum(acc[r]);
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      if (row0 + r < prob.rows) {
+        // (acc * a_scale) * w_scale, in that order: src/cuda/fp8/sm120.cu:234-239.
+        const float ws = bf16_bits_to_float(__ldg(prob.w_scales + row0 + r));
+        const float y = __fmul_rn(__fmul_rn(acc[r], a_scale), ws);
+        if constexpr (kBf16Out) static_cast<uint16_t*>(prob.out)[row0 + r] = float_to_bf16_bits(y);
+        else static_cast<float*>(prob.out)[row0 + r] = y;
+      }
+    }
+  }
+}
+
+// Rows per warp: enough CTAs to put at least two on every SM, otherwise as many rows per warp
+// as possible so the staged activation is amortised.
+int pick_rows_per_warp(uint64_t total_rows) {
+  const uint64_t want = 2ull * sm_count();
+  if (total_rows / (kWarps * 4) >= want) return 4;
+  if (total_rows / (kWarps * 2) >= want) return 2;
+  return 1;
+}
+
+template <bool kFusedQuant, bool kBf16Out>
+int32_t launch_fp8_gemv(const char* op, const void* act, const float* act_scale, Fp8Group grp,
+                        uint64_t k, cudaStream_t stream) {
+  uint64_t total_rows = 0;
+  for (int i = 0; i < grp.n; ++i) total_rows += grp.p[i].rows;
+  const int rpw = pick_rows_per_warp(total_rows);
+  unsigned blocks = 0;
+  for (int i = 0; i < grp.n; ++i) {
+    grp.first_block[i] = blocks;
+    blocks += static_cast<unsigned>((grp.p[i].rows + kWarps * rpw - 1) / (kWarps * rpw));
+  }
+  grp.first_block[grp.n] = blocks;
+  const size_t smem = (k + 511) / 512 * 512 * sizeof(__half);
+#define GEMB_LAUNCH_FP8_GEMV(R)                                                                   \
+  do {                                                                                            \
+    auto kern = fp8_gemv_kernel<R, kFusedQuant, kBf16Out>;                                        \
+    if (smem > 48 * 1024) {                                                                       \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                           static_cast<int>(smem));                               \
+      if (e != cudaSuccess)                                                                       \
+        return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e)); \
+    }                                                                                             \
+    kern<<<blocks, kThreads, smem, stream>>>(act, act_scale, grp, k);                             \
+  } while (0)
+  if (rpw == 4) GEMB_LAUNCH_FP8_GEMV(4);
+  else if (rpw == 2) GEMB_LAUNCH_FP8_GEMV(2);
+  else GEMB_LAUNCH_FP8_GEMV(1);
+#undef GEMB_LAUNCH_FP8_GEMV
+  return check_launch(op);
+}
+
+int32_t validate_fp8_gemv(const char* op, const void* act, const void* w, const void* ws,
+                          const void* out, uint64_t rows, uint64_t k) {
+  GEMB_REQUIRE(act && w && ws && out, "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(rows > 0 && k > 0, "%s: geometry must be nonzero", op);
+  GEMB_REQUIRE(k % 16 == 0, "%s: contracting extent must be a multiple of 16", op);
+  GEMB_REQUIRE(k <= 110 * 1024, "%s: contracting extent exceeds the shared-memory staging limit (112640)", op);
+  GEMB_REQUIRE(rows < (1ull << 31), "%s: too many rows", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0,
+               "%s: activation and weight must be 16-byte aligned", op);
+  return GEMB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// NVFP4 GEMV.  Activation staged as fp16 values (decoded E2M1) plus fp32 decoded block scales.
+// A lane's 16-byte weight chunk is two 16-element blocks; within a block the sixteen E2M1
+// products are summed in fp16 (exact: each product is a multiple of 1/4 no larger than 36, a
+// half2 lane sums eight of them, at most 288), then the block sum is scaled by sa*sw in fp32.
+// ---------------------------------------------------------------------------------------------
+// All four bytes of a word -> four half2.
+__device__ __forceinline__ void e2m1x8_to_half2(uint32_t word, uint32_t (&h)[4]) {
+  asm("{ .reg .b8 t0, t1, t2, t3;\n"
+      "  mov.b32 {t0, t1, t2, t3}, %4;\n"
+      "  cvt.rn.f16x2.e2m1x2 %0, t0;\n"
+      "  cvt.rn.f16x2.e2m1x2 %1, t1;\n"
+      "  cvt.rn.f16x2.e2m1x2 %2, t2;\n"
+      "  cvt.rn.f16x2.e2m1x2 %3, t3; }"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(word));
+}
+__device__ __forceinline__ uint32_t hfma2_bits(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ float half2_sum(uint32_t h) {
+  const __half2 v = *reinterpret_cast<const __half2*>(&h);
+  return __low2float(v) + __high2float(v);
+}
+// One 16-element block: w bytes (lo, hi words) against 16 staged fp16 activations.
+__device__ __forceinline__ float block_dot_fp4(uint32_t w_lo, uint32_t w_hi, const uint4& xa, const uint4& xb) {
+  uint32_t h[4];
+  uint32_t acc = 0;
+  e2m1x8_to_half2(w_lo, h);
+  acc = hfma2_bits(h[0], xa.x, acc);
+  acc = hfma2_bits(h[1], xa.y, acc);
+  acc = hfma2_bits(h[2], xa.z, acc);
+  acc = hfma2_bits(h[3], xa.w, acc);
+  e2m1x8_to_half2(w_hi, h);
+  acc = hfma2_bits(h[0], xb.x, acc);
+  acc = hfma2_bits(h[1], xb.y, acc);
+  acc = hfma2_bits(h[2], xb.z, acc);
+  acc = hfma2_bits(h[3], xb.w, acc);
+  return half2_sum(acc);
+}
+
+template <int kRows, bool kGateUp>
+__global__ void __launch_bounds__(kThreads)
+nvfp4_gemv_kernel(const uint8_t* __restrict__ act, const uint8_t* __restrict__ act_scales,
+                  const uint8_t* __restrict__ w0, const uint8_t* __restrict__ ws0,
+                  const uint8_t* __restrict__ w1, const uint8_t* __restrict__ ws1,
+                  float* __restrict__ out0, float* __restrict__ out1, float* __restrict__ product,
+                  uint64_t rows, uint64_t k, float div0, float div1) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  // Staged activation: per 1024-element segment (512 weight bytes), lane l's 32 values are
+  // stored as four 8-value parts at [p*256 + l*8, +8), p = 0..3 (conflict-free 128-bit loads).
+  const uint64_t k_pad = (k + 1023) / 1024 * 1024;
+  __half* xs = reinterpret_cast<__half*>(smem_raw);              // k_pad halves
+  float* sa = reinterpret_cast<float*>(smem_raw + k_pad * 2);    // k/16 decoded scales
+  for (uint64_t c = threadIdx.x; c < k / 32; c += kThreads) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(act) + c);  // 32 elements
+    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+    uint32_t h[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t t[4];
+      e2m1x8_to_half2(ww[i], t);
+      h[4 * i] = t[0]; h[4 * i + 1] = t[1]; h[4 * i + 2] = t[2]; h[4 * i + 3] = t[3];
+    }
+    __half* dst = xs + (c / 32) * 1024 + (c % 32) * 8;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      *reinterpret_cast<uint4*>(dst + i * 256) = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+  }
+  for (uint64_t c = threadIdx.x; c < k / 16; c += kThreads) sa[c] = e4m3_decode(__ldg(act_scales + c));
+  __syncthreads();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t row0 = (static_cast<uint64_t>(blockIdx.x) * kWarps + warp) * kRows;
+  if (row0 >= rows) return;
+  constexpr int kMats = kGateUp ? 2 : 1;
+  const uint64_t row_bytes = k / 2, srow_bytes = k / 16;
+  float acc[kMats][kRows];
+#pragma unroll
+  for (int m = 0; m < kMats; ++m)
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) acc[m][r] = 0.0f;
+
+  // A lane owns 16 weight bytes = 32 elements = 2 blocks per 512-byte row segment.
+  for (uint64_t kb = lane * 16ull; kb < row_bytes; kb += 512) {
+    uint4 wv[kMats][kRows];
+    uint16_t sv[kMats][kRows];
+#pragma unroll
+    for (int m = 0; m < kMats; ++m)
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        const uint64_t row = row0 + r < rows ? row0 + r : rows - 1;
+        const uint8_t* wp = (m == 0 ? w0 : w1) + row * row_bytes + kb;
+        const uint8_t* sp = (m == 0 ? ws0 : ws1) + row * srow_bytes + kb / 8;
+        wv[m][r] = ldg_stream(wp);
+        sv[m][r] = __ldg(reinterpret_cast<const uint16_t*>(sp));
+      }
+    const __half* xp = xs + (kb / 512) * 1024 + lane * 8;
+    const uint4 x0 = *reinterpret_cast<const uint4*>(xp), x1 = *reinterpret_cast<const uint4*>(xp + 256),
+                x2 = *reinterpret_cast<const uint4*>(xp + 512), x3 = *reinterpret_cast<const uint4*>(xp + 768);
+    const float sa0 = sa[kb / 8], sa1 = sa[kb / 8 + 1];
+#pragma unroll
+    for (int m = 0; m < kMats; ++m)
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        const float d0 = block_dot_fp4(wv[m][r].x, wv[m][r].y, x0, x1);
+        const float d1 = block_dot_fp4(wv[m][r].z, wv[m][r].w, x2, x3);
+        const float sw0 = e4m3_decode(static_cast<uint8_t>(sv[m][r] & 0xFF));
+        const float sw1 = e4m3_decode(static_cast<uint8_t>(sv[m][r] >> 8));
+        acc[m][r] = fmaf(d0, sa0 * sw0, acc[m][r]);
+        acc[m][r] = fmaf(d1, sa1 * sw1, acc[m][r]);
+      }
+  }
+#pragma unroll
+  for (int m = 0; m < kMats; ++m)
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) acc[m][r] = warp_sum(acc[m][r]);
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      if (row0 + r >= rows) continue;
+      // Single final division by ga*gw: src/cuda/nvfp4/sm120.cu:243.
+      const float y0 = __fdiv_rn(acc[0][r], div0);
+      if constexpr (kGateUp) {
+        const float y1 = __fdiv_rn(acc[1][r], div1);
+        if (out0) out0[row0 + r] = y0;
+        if (out1) out1[row0 + r] = y1;
+        // bf16 boundaries and GELU-tanh product: src/cuda/nvfp4/sm120.cu:375-386.
+        const float g = bf16_round(y0), u = bf16_round(y1);
+        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        const float gelu = bf16_round(0.5f * g * (1.0f + tanhf(inner)));
+        product[row0 + r] = bf16_round(gelu * u);
+      } else {
+        out0[row0 + r] = y0;
+      }
+    }
+  }
+}
+
+template <bool kGateUp>
+int32_t launch_nvfp4_gemv(const char* op, const uint8_t* act, const uint8_t* act_scales,
+                          const uint8_t* w0, const uint8_t* ws0, const uint8_t* w1,
+                          const uint8_t* ws1, float* out0, float* out1, float* product,
+                          uint64_t rows, uint64_t k, float div0, float div1, cudaStream_t stream) {
+  const int rpw = kGateUp ? (rows / (kWarps * 2) >= 2ull * sm_count() ? 2 : 1)
+                          : pick_rows_per_warp(rows);
+  const unsigned blocks = static_cast<unsigned>((rows + kWarps * rpw - 1) / (kWarps * rpw));
+  const size_t smem = (k + 1023) / 1024 * 1024 * 2 + (k / 16) * 4;
+#define GEMB_LAUNCH_FP4_GEMV(R)                                                                   \
+  do {                                                                                            \
+    auto kern = nvfp4_gemv_kernel<R, kGateUp>;                                                    \
+    if (smem > 48 * 1024) {                                                                       \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                           static_cast<int>(smem));                               \
+      if (e != cudaSuccess)                                                                       \
+        return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e)); \
+    }                                                                                             \
+    kern<<<blocks, kThreads, smem, stream>>>(act, act_scales, w0, ws0, w1, ws1, out0, out1,       \
+                                             product, rows, k, div0, div1);             \
+  } while (0)
+  if (rpw == 4) { if constexpr (!kGateUp) GEMB_LAUNCH_FP4_GEMV(4); }
+  else if (rpw == 2) GEMB_LAUNCH_FP4_GEMV(2);
+  else GEMB_LAUNCH_FP4_GEMV(1);
+#undef GEMB_LAUNCH_FP4_GEMV
+  return check_launch(op);
+}
+
+int32_t validate_nvfp4_gemv(const char* op, uint64_t rows, uint64_t k, float ga, float gw) {
+  GEMB_REQUIRE(rows > 0 && k > 0, "%s: geometry must be nonzero", op);
+  GEMB_REQUIRE(k % 64 == 0 && rows % 8 == 0,
+               "%s: requires K divisible by 64 and rows divisible by 8", op);
+  GEMB_REQUIRE(k <= 96 * 1024, "%s: contracting extent exceeds the shared-memory staging limit (98304)", op);
+  GEMB_REQUIRE(rows < (1ull << 31), "%s: too many rows", op);
+  GEMB_REQUIRE(positive_finite(ga) && positive_finite(gw), "%s: global divisors must be positive and finite", op);
+  GEMB_REQUIRE(std::isfinite(ga * gw), "%s: combined global divisor overflowed", op);
+  return GEMB_OK;
+}
+
+}  // namespace
+}  // namespace gemb
+
+using namespace gemb;
+
+extern "C" {
+
+int32_t gemb_fp8_gemv(const uint8_t* act, const float* act_scale, const uint8_t* w,
+                      const uint16_t* w_scales, float* out, uint64_t rows, uint64_t k,
+                      gemb_stream_t stream) {
+  const char* op = "gemb_fp8_gemv";
+  GEMB_REQUIRE(act_scale != nullptr, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_fp8_gemv(op, act, w, w_scales, out, rows, k));
+  GEMB_TRY(require_sm100(op));
+  Fp8Group grp{};
+  grp.n = 1;
+  grp.p[0] = {w, w_scales, out, rows};
+  return launch_fp8_gemv<false, false>(op, act, act_scale, grp, k, stream);
+}
+
+int32_t gemb_fp8_gemv_qkv(const uint8_t* act, const float* act_scale, const uint8_t* q_w,
+                          const uint16_t* q_s, float* q_out, uint64_t q_rows, const uint8_t* k_w,
+                          const uint16_t* k_s, float* k_out, uint64_t k_rows, const uint8_t* v_w,
+                          const uint16_t* v_s, float* v_out, uint64_t v_rows, uint64_t k,
+                          gemb_stream_t stream) {
+  const char* op = "gemb_fp8_gemv_qkv";
+  GEMB_REQUIRE(act_scale != nullptr, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_fp8_gemv(op, act, q_w, q_s, q_out, q_rows, k));
+  GEMB_TRY(validate_fp8_gemv(op, act, k_w, k_s, k_out, k_rows, k));
+  const bool has_v = v_w != nullptr || v_rows != 0;
+  if (has_v) GEMB_TRY(validate_fp8_gemv(op, act, v_w, v_s, v_out, v_rows, k));
+  GEMB_TRY(require_sm100(op));
+  Fp8Group grp{};
+  grp.n = has_v ? 3 : 2;
+  grp.p[0] = {q_w, q_s, q_out, q_rows};
+  grp.p[1] = {k_w, k_s, k_out, k_rows};
+  if (has_v) grp.p[2] = {v_w, v_s, v_out, v_rows};
+  return launch_fp8_gemv<false, false>(op, act, act_scale, grp, k, stream);
+}
+
+int32_t gemb_fp8_gemv_bf16in(const uint16_t* act_bf16, const uint8_t* w, const uint16_t* w_scales,
+                             void* out, int32_t out_dtype, uint64_t rows, uint64_t k,
+                             gemb_stream_t stream) {
+  const char* op = "gemb_fp8_gemv_bf16in";
+  GEMB_TRY(validate_fp8_gemv(op, act_bf16, w, w_scales, out, rows, k));
+  GEMB_REQUIRE(out_dtype == GEMB_F32 || out_dtype == GEMB_BF16, "%s: output dtype must be GEMB_F32 or GEMB_BF16", op);
+  GEMB_TRY(require_sm100(op));
+  Fp8Group grp{};
+  grp.n = 1;
+  grp.p[0] = {w, w_scales, out, rows};
+  if (out_dtype == GEMB_BF16) return launch_fp8_gemv<true, true>(op, act_bf16, nullptr, grp, k, stream);
+  return launch_fp8_gemv<true, false>(op, act_bf16, nullptr, grp, k, stream);
+}
+
+int32_t gemb_nvfp4_gemv(const uint8_t* act, const uint8_t* act_scales, const uint8_t* w,
+                        const uint8_t* w_scales, float* out, uint64_t rows, uint64_t k, float ga,
+                        float gw, gemb_stream_t stream) {
+  const char* op = "gemb_nvfp4_gemv";
+  GEMB_REQUIRE(act && act_scales && w && w_scales && out, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_nvfp4_gemv(op, rows, k, ga, gw));
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(w_scales) % 2 == 0,
+               "%s: activation and weight must be 16-byte aligned, weight scales 2-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  return launch_nvfp4_gemv<false>(op, act, act_scales, w, w_scales, nullptr, nullptr, out, nullptr,
+                                  nullptr, rows, k, ga * gw, 1.0f, stream);
+}
+
+int32_t gemb_nvfp4_gemv_gate_up(const uint8_t* act, const uint8_t* act_scales, const uint8_t* gate_w,
+                                const uint8_t* gate_s, const uint8_t* up_w, const uint8_t* up_s,
+                                float* gate_out, float* up_out, float* product, uint64_t rows,
+                                uint64_t k, float gate_ga, float gate_gw, float up_ga, float up_gw,
+                                gemb_stream_t stream) {
+  const char* op = "gemb_nvfp4_gemv_gate_up";
+  GEMB_REQUIRE(act && act_scales && gate_w && gate_s && up_w && up_s && product,
+               "%s: required pointers must be nonnull", op);
+  GEMB_REQUIRE((gate_out == nullptr) == (up_out == nullptr),
+               "%s: gate and up outputs must both be present or both null", op);
+  GEMB_TRY(validate_nvfp4_gemv(op, rows, k, gate_ga, gate_gw));
+  GEMB_TRY(validate_nvfp4_gemv(op, rows, k, up_ga, up_gw));
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(gate_w) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(up_w) % 16 == 0 && reinterpret_cast<uintptr_t>(gate_s) % 2 == 0 &&
+                   reinterpret_cast<uintptr_t>(up_s) % 2 == 0,
+               "%s: activation and weights must be 16-byte aligned, weight scales 2-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  return launch_nvfp4_gemv<true>(op, act, act_scales, gate_w, gate_s, up_w, up_s, gate_out, up_out,
+                                 product, rows, k, gate_ga * gate_gw, up_ga * up_gw, stream);
+}
+
+}  // extern "C"

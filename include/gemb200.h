@@ -1,0 +1,207 @@
+/* gemb200 -- B200 (sm_100a) implementation of gem16's quantized-weight contraction path.
+ *
+ * C ABI.  Every entry point mirrors one operator launcher of `namespace gem16::internal`
+ * (cited per function as file:line inside the gem16 tree) or, for the MoE path where gem16
+ * holds only specifications, the record layouts those specifications define.
+ *
+ * Conventions (same as the reference launchers):
+ *   - every pointer is a DEVICE pointer owned by the caller unless its name ends in `_host`;
+ *   - operators allocate nothing, never synchronise, and are ordered on `stream`;
+ *   - the return value is a gemb_status; on failure gemb_last_error() holds the message
+ *     (thread local), formatted like the reference's "op: cudaErrorName: string";
+ *   - null pointers, bad geometry and non-finite / non-positive divisors are rejected with
+ *     GEMB_INVALID_ARGUMENT before anything is launched (src/cuda/nvfp4/reference.cu:270-284).
+ *   - there is no CPU fallback: without an sm_100 device every launch fails with
+ *     GEMB_UNSUPPORTED.
+ *
+ * Data formats (src/numeric/nvfp4.cpp:13-15,58-70; docs/CHECKPOINT_FORMAT.md:62-95):
+ *   NVFP4  packed E2M1, element 2i in the low nibble of byte i; one E4M3FN scale byte per 16
+ *          contiguous K elements; one fp32 "global divisor" per tensor.
+ *   FP8    E4M3FN bytes; activations carry one fp32 scale per token, weights one bf16 scale per
+ *          output row.
+ *   bf16   raw uint16 bit patterns.
+ */
+#ifndef GEMB200_H_
+#define GEMB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* gemb_stream_t; /* identical to cudaStream_t */
+
+/* Mirrors gem16::StatusCode, include/gem16/status.h:9-19, value for value. */
+typedef enum gemb_status {
+  GEMB_OK = 0,
+  GEMB_INVALID_ARGUMENT = 1,
+  GEMB_NOT_FOUND = 2,
+  GEMB_IO_ERROR = 3,
+  GEMB_DATA_LOSS = 4,
+  GEMB_UNSUPPORTED = 5,
+  GEMB_RESOURCE_EXHAUSTED = 6,
+  GEMB_CANCELLED = 7,
+  GEMB_INTERNAL = 8
+} gemb_status;
+
+/* Element type of an activation input. */
+enum { GEMB_F32 = 0, GEMB_BF16 = 1 };
+/* Where an NVFP4 quantizer writes its block scales.
+ *   COMPACT      row-major [tokens, K/16]                     (src/cuda/nvfp4/reference.cu:99-101)
+ *   INTERLEAVED  rows padded to 128, K/16 padded to 4, byte offset
+ *                ((r/128)*(C/4)+c/4)*512 + (r%32)*16 + ((r%128)/32)*4 + c%4, padding zero
+ *                                                             (src/cuda/nvfp4/cutlass_sm120.cu:160-194)
+ */
+enum { GEMB_SCALES_COMPACT = 0, GEMB_SCALES_INTERLEAVED = 1 };
+/* Which of the reference's two quantizer contracts to follow.
+ *   EXACT       q = E2M1((x*g) / decode(scale)), scale = E4M3((amax*(1/6))*g)   -- the host
+ *               oracle, src/numeric/nvfp4.cpp:134-150.  Default; what parity is checked against.
+ *   RCP_APPROX  q = E2M1(x * rcp(decode(scale) * rcp(g))), scale = E4M3((amax*rcp(6))*g) with
+ *               rcp.approx.ftz.f32 -- the reference's device kernels,
+ *               src/cuda/nvfp4/reference.cu:39-43,60-78.
+ */
+enum { GEMB_QUANT_EXACT = 0, GEMB_QUANT_RCP_APPROX = 1 };
+
+const char* gemb_last_error(void);
+const char* gemb_status_name(int32_t status);
+/* ABI version of this header; bumped on any signature change. */
+int32_t gemb_abi_version(void);
+/* GEMB_OK when the current CUDA device is compute capability 10.x, else GEMB_UNSUPPORTED.
+ * Counterpart of the device gate at src/cuda/engine/inference_engine_initialize.cuh:14-19. */
+int32_t gemb_device_check(void);
+/* Bytes of an INTERLEAVED scale buffer for `rows` rows of K elements. */
+uint64_t gemb_interleaved_scale_bytes(uint64_t rows, uint64_t contracting_elements);
+
+/* ------------------------------------------------------------------------------------------
+ * Activation quantizers
+ * ---------------------------------------------------------------------------------------- */
+
+/* NVFP4 block quantizer over [tokens, K], K % 16 == 0.
+ * Replaces LaunchNvfp4ReferenceActivationQuantization, src/cuda/nvfp4/reference.h:13-19
+ * (call with tokens = 1, K = elements for the flattened form). */
+int32_t gemb_nvfp4_quantize(const void* input, int32_t input_dtype, uint8_t* packed_e2m1,
+                            uint8_t* block_scales_e4m3fn, uint64_t tokens,
+                            uint64_t elements_per_token, float global_divisor,
+                            int32_t scale_layout, int32_t quant_mode, gemb_stream_t stream);
+
+/* RMSNorm -> bf16 state rounding -> NVFP4 quantizer, one pass per token.
+ * Replaces LaunchRmsNormNvfp4ActivationQuantizationBatch / ...Bf16Batch,
+ * src/cuda/nvfp4/reference.h:23-47.  weight_bf16 may be null (no learned weight). */
+int32_t gemb_nvfp4_rmsnorm_quantize(const void* input, int32_t input_dtype,
+                                    const uint16_t* weight_bf16, uint8_t* packed_e2m1,
+                                    uint8_t* block_scales_e4m3fn, uint64_t tokens,
+                                    uint64_t elements_per_token, float epsilon,
+                                    float global_divisor, int32_t scale_layout,
+                                    int32_t quant_mode, gemb_stream_t stream);
+
+/* bf16(gate), bf16(up) -> bf16 gelu_tanh(gate) -> bf16 product -> NVFP4 quantizer.
+ * Replaces LaunchGatedGeluNvfp4ActivationQuantization / ...Bf16,
+ * src/cuda/nvfp4/reference.h:52-70. */
+int32_t gemb_nvfp4_gated_gelu_quantize(const void* gate, const void* up, int32_t input_dtype,
+                                       uint8_t* packed_e2m1, uint8_t* block_scales_e4m3fn,
+                                       uint64_t tokens, uint64_t elements_per_token,
+                                       float global_divisor, int32_t scale_layout,
+                                       int32_t quant_mode, gemb_stream_t stream);
+
+/* Compact -> interleaved block scales (padding written as zero).
+ * Replaces LaunchNvfp4CutlassInterleaveActivationScales, src/cuda/nvfp4/cutlass_sm120.h:11-16. */
+int32_t gemb_nvfp4_interleave_scales(const uint8_t* compact_scales, uint8_t* interleaved_scales,
+                                     uint64_t rows, uint64_t contracting_elements,
+                                     gemb_stream_t stream);
+
+/* FP8 dynamic per-token quantizer: scale = amax/448 (1 for an all-zero token), q = E4M3(x/scale).
+ * Replaces LaunchFp8ReferenceTokenQuantization{,Batch,Bf16Batch},
+ * src/cuda/fp8/reference.h:11-33. */
+int32_t gemb_fp8_quantize(const void* input, int32_t input_dtype, uint8_t* output_e4m3fn,
+                          float* output_scales, uint64_t tokens, uint64_t elements_per_token,
+                          gemb_stream_t stream);
+
+/* RMSNorm -> bf16 -> FP8 per-token quantizer.
+ * Replaces LaunchRmsNormFp8TokenQuantizationBatch / ...Bf16Batch,
+ * src/cuda/fp8/reference.h:37-58. */
+int32_t gemb_fp8_rmsnorm_quantize(const void* input, int32_t input_dtype,
+                                  const uint16_t* weight_bf16, uint8_t* output_e4m3fn,
+                                  float* output_scales, uint64_t tokens,
+                                  uint64_t elements_per_token, float epsilon,
+                                  gemb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Batch-1 decode projections (HBM-streaming GEMV).  Weights are row-major [rows, K] in the
+ * checkpoint's source layout; NVFP4 block scales are COMPACT [rows, K/16].
+ * ---------------------------------------------------------------------------------------- */
+
+/* y[row] = (sum_k qa qw) * a_scale * bf16(w_scale[row]), fp32 out.  K % 16 == 0.
+ * Replaces LaunchFp8Sm120DirectProjection, src/cuda/fp8/sm120.h:14-22. */
+int32_t gemb_fp8_gemv(const uint8_t* activation_e4m3fn, const float* activation_scale,
+                      const uint8_t* weight_e4m3fn, const uint16_t* weight_scales_bf16,
+                      float* output, uint64_t rows, uint64_t contracting_elements,
+                      gemb_stream_t stream);
+
+/* One launch for Q, K and V (V may be null with v_rows = 0).
+ * Replaces LaunchFp8Sm120GroupedQkvProjection, src/cuda/fp8/sm120.h:27-43. */
+int32_t gemb_fp8_gemv_qkv(const uint8_t* activation_e4m3fn, const float* activation_scale,
+                          const uint8_t* q_weight, const uint16_t* q_scales_bf16, float* q_output,
+                          uint64_t q_rows, const uint8_t* k_weight, const uint16_t* k_scales_bf16,
+                          float* k_output, uint64_t k_rows, const uint8_t* v_weight,
+                          const uint16_t* v_scales_bf16, float* v_output, uint64_t v_rows,
+                          uint64_t contracting_elements, gemb_stream_t stream);
+
+/* Per-token FP8 quantization of a bf16 vector fused into the GEMV (each CTA re-derives the
+ * token scale and bytes; results are bit-identical to gemb_fp8_quantize + gemb_fp8_gemv).
+ * Fuses the decode pair at src/cuda/engine/inference_engine_decode_graphs.cuh:287-290.
+ * output_dtype: GEMB_F32 or GEMB_BF16 (round-to-nearest-even). */
+int32_t gemb_fp8_gemv_bf16in(const uint16_t* activation_bf16, const uint8_t* weight_e4m3fn,
+                             const uint16_t* weight_scales_bf16, void* output,
+                             int32_t output_dtype, uint64_t rows, uint64_t contracting_elements,
+                             gemb_stream_t stream);
+
+/* y[row] = (sum_k qa sa qw sw) / (ga * gw), fp32 out.  K % 64 == 0, rows % 8 == 0
+ * (the reference's native geometry rule, src/cuda/nvfp4/sm120.cu:708-711).
+ * Replaces LaunchNvfp4Sm120DirectProjection, src/cuda/nvfp4/sm120.h:14-24. */
+int32_t gemb_nvfp4_gemv(const uint8_t* packed_activation_e2m1, const uint8_t* activation_scales,
+                        const uint8_t* packed_weight_e2m1, const uint8_t* weight_scales,
+                        float* output, uint64_t rows, uint64_t contracting_elements,
+                        float activation_global_divisor, float weight_global_divisor,
+                        gemb_stream_t stream);
+
+/* Gate and Up in one launch with the bf16 boundaries and the GELU-tanh product in the epilogue;
+ * gate_output / up_output may be null.
+ * Replaces LaunchNvfp4Sm120FusedGateUp, src/cuda/nvfp4/sm120.h:58-74. */
+int32_t gemb_nvfp4_gemv_gate_up(const uint8_t* packed_activation_e2m1,
+                                const uint8_t* activation_scales,
+                                const uint8_t* packed_gate_weight, const uint8_t* gate_weight_scales,
+                                const uint8_t* packed_up_weight, const uint8_t* up_weight_scales,
+                                float* gate_output, float* up_output, float* product_output,
+                                uint64_t rows, uint64_t contracting_elements,
+                                float gate_activation_global_divisor,
+                                float gate_weight_global_divisor,
+                                float up_activation_global_divisor,
+                                float up_weight_global_divisor, gemb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Scalar cross-check projections (one thread per output, fp32 fma in k order).  Slow on
+ * purpose; they exist so large shapes can be checked on the GPU.
+ * Replace LaunchNvfp4ReferenceProjectionBatch (src/cuda/nvfp4/reference.h:83-94) and
+ * LaunchFp8ReferenceProjectionBatch (src/cuda/fp8/reference.h:69-78).
+ * ---------------------------------------------------------------------------------------- */
+int32_t gemb_nvfp4_reference_projection(const uint8_t* packed_activation_e2m1,
+                                        const uint8_t* activation_scales,
+                                        const uint8_t* packed_weight_e2m1,
+                                        const uint8_t* weight_scales, float* output,
+                                        uint64_t tokens, uint64_t rows,
+                                        uint64_t contracting_elements,
+                                        float activation_global_divisor,
+                                        float weight_global_divisor, gemb_stream_t stream);
+int32_t gemb_fp8_reference_projection(const uint8_t* activation_e4m3fn,
+                                      const float* activation_scales,
+                                      const uint8_t* weight_e4m3fn,
+                                      const uint16_t* weight_scales_bf16, float* output,
+                                      uint64_t tokens, uint64_t rows,
+                                      uint64_t contracting_elements, gemb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEMB200_H_ */

@@ -1,0 +1,67 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every symbol the header declares,
+validates arguments like the reference launchers do, and refuses to compute without a B200."""
+import ctypes
+
+import pytest
+
+from gem16_b200.lib import GembError, parse_header
+
+
+def test_exports_every_declared_symbol(lib):
+    protos = parse_header()
+    assert len(protos) >= 18
+    for name in protos:
+        assert hasattr(lib.cdll, name), name
+
+
+def test_status_names_mirror_reference(lib):
+    # include/gem16/status.h:9-19
+    names = ["kOk", "kInvalidArgument", "kNotFound", "kIoError", "kDataLoss", "kUnsupported",
+             "kResourceExhausted", "kCancelled", "kInternal"]
+    for code, name in enumerate(names):
+        assert lib.cdll.gemb_status_name(code).decode() == name
+
+
+def test_interleaved_bytes(lib):
+    assert lib.cdll.gemb_interleaved_scale_bytes(129, 3840) == 256 * 240
+    assert lib.cdll.gemb_interleaved_scale_bytes(128, 704) == 128 * 44
+    assert lib.cdll.gemb_interleaved_scale_bytes(1, 16) == 128 * 4
+
+
+def test_invalid_arguments_are_rejected_before_any_launch(lib):
+    p = 0x1000  # never dereferenced: validation fails first
+    cases = [
+        ("gemb_nvfp4_quantize", (None, 0, p, p, 1, 16, 1.0, 0, 0, None)),        # null input
+        ("gemb_nvfp4_quantize", (p, 0, p, p, 1, 15, 1.0, 0, 0, None)),           # K % 16
+        ("gemb_nvfp4_quantize", (p, 0, p, p, 1, 16, 0.0, 0, 0, None)),           # divisor 0
+        ("gemb_nvfp4_quantize", (p, 0, p, p, 1, 16, float("inf"), 0, 0, None)),  # divisor inf
+        ("gemb_nvfp4_quantize", (p, 7, p, p, 1, 16, 1.0, 0, 0, None)),           # dtype
+        ("gemb_fp8_quantize", (p, 0, p, p, 0, 16, None)),                         # empty
+        ("gemb_fp8_gemv", (p, p, p, p, p, 8, 24, None)),                          # K % 16
+        ("gemb_nvfp4_gemv", (p, p, p, p, p, 12, 64, 1.0, 1.0, None)),             # rows % 8
+        ("gemb_nvfp4_gemv", (p, p, p, p, p, 8, 48, 1.0, 1.0, None)),              # K % 64
+        ("gemb_nvfp4_gemv", (p, p, p, p, p, 8, 64, -1.0, 1.0, None)),             # divisor
+        ("gemb_nvfp4_reference_projection", (p, p, p, p, p, 1, 8, 8, 1.0, 1.0, None)),
+    ]
+    for name, args in cases:
+        assert lib.raw(name, *args) == 1, name
+        assert name in lib.last_error()
+    with pytest.raises(GembError) as e:
+        lib.gemb_nvfp4_quantize(None, 0, p, p, 1, 16, 1.0, 0, 0, None)
+    assert e.value.status_name == "kInvalidArgument"
+
+
+def test_no_cpu_fallback(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    p = 0x1000
+    assert lib.raw("gemb_device_check") == 5
+    assert lib.raw("gemb_nvfp4_quantize", p, 0, p, p, 1, 16, 1.0, 0, 0, None) == 5
+    assert lib.raw("gemb_fp8_gemv", p, p, p, p, p, 8, 32, None) == 5
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    from gem16_b200.lib import Lib
+    with pytest.raises(RuntimeError):
+        Lib(str(tmp_path / "libgemb200.so"))
