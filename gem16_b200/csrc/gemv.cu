@@ -8,6 +8,8 @@
 // accumulates in fp32 and folds the 32 lanes with an xor butterfly.  Weights are read exactly
 // once: algorithmic bytes per output row are K (FP8) or K/2 + K/16 (NVFP4) plus the scale and
 // the 4-byte result; the activation (K bytes or less) is re-read per CTA from L2.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace gemb {
@@ -54,9 +56,11 @@ struct Fp8Problem {
   void* out;
   uint64_t rows;
 };
+// Up to three projections that share one activation (grouped Q/K/V).  Their rows form one
+// virtual row space; row_start[i] is the first virtual row of problem i, row_start[n] the total.
 struct Fp8Group {
   Fp8Problem p[3];
-  unsigned first_block[4];  // CTA index at which each problem starts; [n] = total
+  uint64_t row_start[4];
   int n;
 };
 
@@ -64,6 +68,17 @@ struct Fp8Group {
 // values are split into two 8-value halves stored at [l*8, l*8+8) and [256 + l*8, 256 + l*8 + 8)
 // so that each 128-bit shared load of a warp touches 512 contiguous bytes (no bank conflicts).
 //
+// The staging buffer is padded to a whole 512-element segment; lanes past K multiply zero
+// weights with whatever the padding holds, so it must hold finite values: zero it.
+__device__ __forceinline__ void zero_fp8_staging_tail(uint64_t k, __half* xs) {
+  const uint64_t chunks = k / 16, chunks_pad = (k + 511) / 512 * 32;
+  for (uint64_t c = chunks + threadIdx.x; c < chunks_pad; c += kThreads) {
+    __half* dst = xs + (c / 32) * 512 + (c % 32) * 8;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(dst + 256) = make_uint4(0, 0, 0, 0);
+  }
+}
+
 // Stages an already quantized activation (E4M3 bytes) as fp16 in shared memory.
 __device__ __forceinline__ void stage_fp8_activation(const uint8_t* act, uint64_t k, __half* xs) {
   for (uint64_t c = threadIdx.x; c < k / 16; c += kThreads) {
@@ -79,22 +94,70 @@ __device__ __forceinline__ void stage_fp8_activation(const uint8_t* act, uint64_
     *reinterpret_cast<uint4*>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
     *reinterpret_cast<uint4*>(dst + 256) = make_uint4(h[4], h[5], h[6], h[7]);
   }
+  zero_fp8_staging_tail(k, xs);
+}
+
+// A value y with E4M3(y) == E4M3(x / scale) for the IEEE quotient x / scale.  x * (1/scale) is
+// within two ulp of the quotient, so both round to the same E4M3 code unless y sits within a
+// few ulp of a rounding boundary of the 3-bit mantissa (fraction bits 0x80000) or in E4M3's
+// subnormal range (below 2^-6), where the true division is used.
+__device__ __forceinline__ float quotient_for_e4m3(float x, float scale, float inv_scale) {
+  const float y = __fmul_rn(x, inv_scale);
+  const uint32_t bits = __float_as_uint(y);
+  const uint32_t mag = bits & 0x7FFFFFFFu;
+  const bool near_boundary = ((bits & 0xFFFFFu) - 0x7FFFCu) <= 8u;
+  const bool tiny = mag < 0x3C800000u && mag != 0u;  // |y| < 2^-6 (and not an exact zero)
+  if (near_boundary || tiny) return __fdiv_rn(x, scale);
+  return y;
+}
+
+// Quantizes eight bf16 values (one 16-byte chunk) and stages them as fp16.
+__device__ __forceinline__ void stage_bf16_chunk(const uint4& v, uint64_t c, float scale,
+                                                 float inv_scale, __half* xs) {
+  const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+  uint32_t h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float lo = quotient_for_e4m3(__uint_as_float(ww[i] << 16), scale, inv_scale);
+    const float hi = quotient_for_e4m3(__uint_as_float(ww[i] & 0xFFFF0000u), scale, inv_scale);
+    const uint16_t q = static_cast<uint16_t>(
+        __nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+    h[i] = e4m3x2_to_half2(q);
+  }
+  const uint64_t c16 = c / 2;
+  *reinterpret_cast<uint4*>(xs + (c16 / 32) * 512 + (c % 2) * 256 + (c16 % 32) * 8) =
+      make_uint4(h[0], h[1], h[2], h[3]);
+}
+__device__ __forceinline__ float chunk_amax(const uint4& v) {
+  const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    amax = fmaxf(amax, fabsf(__uint_as_float(ww[i] << 16)));
+    amax = fmaxf(amax, fabsf(__uint_as_float(ww[i] & 0xFFFF0000u)));
+  }
+  return amax;
 }
 
 // Quantizes a bf16 activation per token inside the CTA (same arithmetic as the standalone FP8
 // quantizer: scale = amax/448, q = E4M3(x/scale), src/numeric/fp8.cpp:41-58) and stages the
-// decoded bytes as fp16.  Returns the token scale.
+// decoded bytes as fp16.  Returns the token scale.  The first pass keeps up to 16,384 elements
+// of loads in flight at once; the second pass re-reads the token from L1.
 __device__ __forceinline__ float stage_bf16_activation(const uint16_t* x, uint64_t k, __half* xs,
                                                        float* red) {
+  constexpr int kBatch = 8;  // 8 chunks x 256 threads x 8 elements = 16,384 per batch
+  const uint64_t chunks = k / 8;
+  const uint4* xp = reinterpret_cast<const uint4*>(x);
   float amax = 0.0f;
-  for (uint64_t c = threadIdx.x; c < k / 8; c += kThreads) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x) + c);
-    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+  for (uint64_t base = threadIdx.x; base < chunks; base += static_cast<uint64_t>(kBatch) * kThreads) {
+    uint4 v[kBatch];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      amax = fmaxf(amax, fabsf(__uint_as_float(ww[i] << 16)));
-      amax = fmaxf(amax, fabsf(__uint_as_float(ww[i] & 0xFFFF0000u)));
+    for (int i = 0; i < kBatch; ++i) {
+      const uint64_t c = base + static_cast<uint64_t>(i) * kThreads;
+      v[i] = c < chunks ? __ldg(xp + c) : make_uint4(0, 0, 0, 0);
     }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) amax = fmaxf(amax, chunk_amax(v[i]));
   }
   amax = warp_max(amax);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
@@ -103,32 +166,74 @@ __device__ __forceinline__ float stage_bf16_activation(const uint16_t* x, uint64
 #pragma unroll
   for (int i = 1; i < kWarps; ++i) amax = fmaxf(amax, red[i]);
   const float scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 448.0f);
-  for (uint64_t c = threadIdx.x; c < k / 8; c += kThreads) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x) + c);
-    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
-    uint32_t h[4];
+  const float inv_scale = __frcp_rn(scale);
+  // Second pass: the token was just read by this CTA, so these loads hit L1.
+  for (uint64_t base = threadIdx.x; base < chunks; base += 4ull * kThreads) {
+    uint4 v[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float lo = __fdiv_rn(__uint_as_float(ww[i] << 16), scale);
-      const float hi = __fdiv_rn(__uint_as_float(ww[i] & 0xFFFF0000u), scale);
-      const uint16_t q = static_cast<uint16_t>(
-          __nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
-      h[i] = e4m3x2_to_half2(q);
+      const uint64_t c = base + static_cast<uint64_t>(i) * kThreads;
+      v[i] = c < chunks ? __ldg(xp + c) : make_uint4(0, 0, 0, 0);
     }
-    const uint64_t c16 = c / 2;
-    *reinterpret_cast<uint4*>(xs + (c16 / 32) * 512 + (c % 2) * 256 + (c16 % 32) * 8) =
-        make_uint4(h[0], h[1], h[2], h[3]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint64_t c = base + static_cast<uint64_t>(i) * kThreads;
+      if (c < chunks) stage_bf16_chunk(v[i], c, scale, inv_scale, xs);
+    }
   }
+  zero_fp8_staging_tail(k, xs);
   return scale;
 }
 
-template <int kRows, bool kFusedQuant, bool kBf16Out>
-__global__ void __launch_bounds__(kThreads)
-fp8_gemv_kernel(const void* __restrict__ act, const float* __restrict__ act_scale, Fp8Group grp,
-                uint64_t k) {
+// Persistent FP8 GEMV.  The grid is one wave of CTAs (SM count x resident CTAs per SM); warp
+// (cta, w) owns tasks cta*8 + w, + gridDim*8, ...; task t covers virtual rows [t*kRows,
+// (t+1)*kRows).  Per task the warp walks K in steps of kUnroll 512-byte segments, issuing all
+// kRows*kUnroll 128-bit loads of a step (predicated at the K tail) before it consumes them.
+// The first step of the first task is issued before the activation is staged, so the HBM
+// pipeline fills while the CTA quantizes / decodes the activation.
+template <int kRows, int kUnroll, bool kFusedQuant, bool kBf16Out>
+__global__ void __launch_bounds__(kThreads, kFusedQuant ? 3 : 4)
+fp8_gemv_kernel(const void* __restrict__ act, const float* __restrict__ act_scale,
+                const __grid_constant__ Fp8Group grp, uint64_t k) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __half* xs = reinterpret_cast<__half*>(smem_raw);
   __shared__ float red[kWarps];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t total_rows = grp.row_start[grp.n];
+  const uint64_t num_tasks = (total_rows + kRows - 1) / kRows;
+  const uint64_t task_stride = static_cast<uint64_t>(gridDim.x) * kWarps;
+  const uint64_t step = 512ull * kUnroll;
+
+  auto row_pointer = [&](uint64_t vrow) -> const uint8_t* {
+    if (vrow >= total_rows) vrow = total_rows - 1;
+    int pi = 0;
+    while (pi + 1 < grp.n && vrow >= grp.row_start[pi + 1]) ++pi;
+    return grp.p[pi].w + (vrow - grp.row_start[pi]) * k;
+  };
+  uint4 wv[kUnroll][kRows];
+  auto load_step = [&](uint64_t task, uint64_t kb) {
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      const uint8_t* wp = row_pointer(task * kRows + r) + kb + lane * 16;
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (kb + u * 512 + lane * 16 < k) wv[u][r] = ldg_stream(wp + u * 512);
+        else wv[u][r] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+
+  // Programmatic dependent launch: let the next kernel in the stream start its own weight
+  // prefetch as soon as SM slots free up; weights are immutable so they may be read before the
+  // previous kernel has finished, everything else waits for it.
+  asm volatile("griddepcontrol.launch_dependents;");
+  uint64_t task = static_cast<uint64_t>(blockIdx.x) * kWarps + warp;
+  bool prefetched = false;
+  if (task < num_tasks) {
+    load_step(task, 0);
+    prefetched = true;
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   float a_scale;
   if constexpr (kFusedQuant) {
@@ -139,100 +244,114 @@ fp8_gemv_kernel(const void* __restrict__ act, const float* __restrict__ act_scal
   }
   __syncthreads();
 
-  int pi = 0;
-  while (pi + 1 < grp.n && blockIdx.x >= grp.first_block[pi + 1]) ++pi;
-  const Fp8Problem prob = grp.p[pi];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint64_t row0 = (static_cast<uint64_t>(blockIdx.x - grp.first_block[pi]) * kWarps + warp) * kRows;
-  if (row0 >= prob.rows) return;
-
-  const uint8_t* wrow[kRows];
+  for (; task < num_tasks; task += task_stride) {
+    float acc[kRows];
 #pragma unroll
-  for (int r = 0; r < kRows; ++r) {
-    const uint64_t row = row0 + r < prob.rows ? row0 + r : prob.rows - 1;
-    wrow[r] = prob.w + row * k;
-  }
-  float acc[kRows];
+    for (int r = 0; r < kRows; ++r) acc[r] = 0.0f;
+    for (uint64_t kb = 0; kb < k; kb += step) {
+      if (!prefetched) load_step(task, kb);
+      prefetched = false;
 #pragma unroll
-  for (int r = 0; r < kRows; ++r) acc[r] = 0.0f;
-
-  constexpr int kUnroll = kRows >= 4 ? 2 : (kRows == 2 ? 4 : 8);
-  const uint64_t step = 512ull * kUnroll;
-  uint64_t kb = 0;
-  for (; kb + step <= k; kb += step) {
-    uint4 wv[kUnroll][kRows];
+      for (int u = 0; u < kUnroll; ++u) {
+        if (kb + u * 512 < k) {  // warp-uniform; lanes past K hold zero weights
+          const __half* xp = xs + kb + u * 512 + lane * 8;
+          const uint4 xa = *reinterpret_cast<const uint4*>(xp), xb = *reinterpret_cast<const uint4*>(xp + 256);
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) wv[u][r] = ldg_stream(wrow[r] + kb + u * 512 + lane * 16);
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const __half* xp = xs + kb + u * 512 + lane * 8;
-      const uint4 xa = *reinterpret_cast<const uint4*>(xp), xb = *reinterpret_cast<const uint4*>(xp + 256);
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) dot16_fp8(acc[r], wv[u][r], xa, xb);
+          for (int r = 0; r < kRows; ++r) dot16_fp8(acc[r], wv[u][r], xa, xb);
+        }
+      }
     }
-  }
-  for (uint64_t kk = kb + lane * 16; kk < k; kk += 512) {
-    const __half* xp = xs + (kk / 512) * 512 + lane * 8;
-    const uint4 xa = *reinterpret_cast<const uint4*>(xp), xb = *reinterpret_cast<const uint4*>(xp + 256);
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) dot16_fp8(acc[r], ldg_stream(wrow[r] + kk), xa, xb);
-  }
+    for (int r = 0; r < kRows; ++r) acc[r] = warp_sum(acc[r]);
+    if (lane == 0) {
 #pragma unroll
-  for (int r = 0; r < kRows; ++r) acc[r] = warp_sum(acc[r]);
-  if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-      if (row0 + r < prob.rows) {
-        // (acc * a_scale) * w_scale, in that order: src/cuda/fp8/sm120.cu:234-239.
-        const float ws = bf16_bits_to_float(__ldg(prob.w_scales + row0 + r));
-        const float y = __fmul_rn(__fmul_rn(acc[r], a_scale), ws);
-        if constexpr (kBf16Out) static_cast<uint16_t*>(prob.out)[row0 + r] = float_to_bf16_bits(y);
-        else static_cast<float*>(prob.out)[row0 + r] = y;
+      for (int r = 0; r < kRows; ++r) {
+        const uint64_t vrow = task * kRows + r;
+        if (vrow < total_rows) {
+          int pi = 0;
+          while (pi + 1 < grp.n && vrow >= grp.row_start[pi + 1]) ++pi;
+          const uint64_t row = vrow - grp.row_start[pi];
+          // (acc * a_scale) * w_scale, in that order: src/cuda/fp8/sm120.cu:234-239.
+          const float ws = bf16_bits_to_float(__ldg(grp.p[pi].w_scales + row));
+          const float y = __fmul_rn(__fmul_rn(acc[r], a_scale), ws);
+          if constexpr (kBf16Out) static_cast<uint16_t*>(grp.p[pi].out)[row] = float_to_bf16_bits(y);
+          else static_cast<float*>(grp.p[pi].out)[row] = y;
+        }
       }
     }
   }
 }
 
-// Rows per warp: enough CTAs to put at least two on every SM, otherwise as many rows per warp
-// as possible so the staged activation is amortised.
-int pick_rows_per_warp(uint64_t total_rows) {
-  const uint64_t want = 2ull * sm_count();
-  if (total_rows / (kWarps * 4) >= want) return 4;
-  if (total_rows / (kWarps * 2) >= want) return 2;
+int g_rows_override = 0;  // 0 = automatic; set through gemb_set_tuning(GEMB_TUNE_GEMV_ROWS, n)
+int g_pdl = 1;            // programmatic dependent launch; gemb_set_tuning(GEMB_TUNE_GEMV_PDL, 0/1)
+
+// Rows per warp task.  One row per task keeps tasks fine-grained (best balance over the
+// persistent grid) and measured fastest on every decode shape; 2 and 4 remain selectable.
+int pick_rows_per_warp(uint64_t total_rows, uint64_t k) {
+  if (g_rows_override == 1 || g_rows_override == 2 || g_rows_override == 4) return g_rows_override;
+  (void)total_rows;
+  (void)k;
   return 1;
+}
+
+template <int kRows, int kUnroll, bool kFusedQuant, bool kBf16Out>
+int32_t launch_fp8_gemv_variant(const char* op, const void* act, const float* act_scale,
+                                const Fp8Group& grp, uint64_t k, cudaStream_t stream) {
+  auto kern = fp8_gemv_kernel<kRows, kUnroll, kFusedQuant, kBf16Out>;
+  const size_t smem = (k + 511) / 512 * 512 * sizeof(__half);
+  static int resident[64] = {0};      // CTAs per SM, per device, for the smem size last seen
+  static size_t resident_smem[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (resident[dev] == 0 || smem != resident_smem[dev]) {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem));
+      if (e != cudaSuccess)
+        return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+    }
+    int occ = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kThreads, smem);
+    if (e != cudaSuccess || occ < 1)
+      return fail(GEMB_INTERNAL, "%s: occupancy query failed: %s", op, cudaGetErrorName(e));
+    resident[dev] = occ;
+    resident_smem[dev] = smem;
+  }
+  const uint64_t tasks = (grp.row_start[grp.n] + kRows - 1) / kRows;
+  const uint64_t wave = static_cast<uint64_t>(sm_count()) * resident[dev];
+  const unsigned blocks = static_cast<unsigned>(std::min<uint64_t>((tasks + kWarps - 1) / kWarps, wave));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, kern, act, act_scale, grp, k);
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(le), cudaGetErrorString(le));
+  }
+  return check_launch(op);
 }
 
 template <bool kFusedQuant, bool kBf16Out>
 int32_t launch_fp8_gemv(const char* op, const void* act, const float* act_scale, Fp8Group grp,
                         uint64_t k, cudaStream_t stream) {
   uint64_t total_rows = 0;
-  for (int i = 0; i < grp.n; ++i) total_rows += grp.p[i].rows;
-  const int rpw = pick_rows_per_warp(total_rows);
-  unsigned blocks = 0;
   for (int i = 0; i < grp.n; ++i) {
-    grp.first_block[i] = blocks;
-    blocks += static_cast<unsigned>((grp.p[i].rows + kWarps * rpw - 1) / (kWarps * rpw));
+    grp.row_start[i] = total_rows;
+    total_rows += grp.p[i].rows;
   }
-  grp.first_block[grp.n] = blocks;
-  const size_t smem = (k + 511) / 512 * 512 * sizeof(__half);
-#define GEMB_LAUNCH_FP8_GEMV(R)                                                                   \
-  do {                                                                                            \
-    auto kern = fp8_gemv_kernel<R, kFusedQuant, kBf16Out>;                                        \
-    if (smem > 48 * 1024) {                                                                       \
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
-                                           static_cast<int>(smem));                               \
-      if (e != cudaSuccess)                                                                       \
-        return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e)); \
-    }                                                                                             \
-    kern<<<blocks, kThreads, smem, stream>>>(act, act_scale, grp, k);                             \
-  } while (0)
-  if (rpw == 4) GEMB_LAUNCH_FP8_GEMV(4);
-  else if (rpw == 2) GEMB_LAUNCH_FP8_GEMV(2);
-  else GEMB_LAUNCH_FP8_GEMV(1);
-#undef GEMB_LAUNCH_FP8_GEMV
-  return check_launch(op);
+  grp.row_start[grp.n] = total_rows;
+  const int rpw = pick_rows_per_warp(total_rows, k);
+  if (rpw == 4) return launch_fp8_gemv_variant<4, 2, kFusedQuant, kBf16Out>(op, act, act_scale, grp, k, stream);
+  if (rpw == 2) return launch_fp8_gemv_variant<2, 4, kFusedQuant, kBf16Out>(op, act, act_scale, grp, k, stream);
+  return launch_fp8_gemv_variant<1, 8, kFusedQuant, kBf16Out>(op, act, act_scale, grp, k, stream);
 }
 
 int32_t validate_fp8_gemv(const char* op, const void* act, const void* w, const void* ws,
@@ -394,7 +513,7 @@ int32_t launch_nvfp4_gemv(const char* op, const uint8_t* act, const uint8_t* act
                           const uint8_t* ws1, float* out0, float* out1, float* product,
                           uint64_t rows, uint64_t k, float div0, float div1, cudaStream_t stream) {
   const int rpw = kGateUp ? (rows / (kWarps * 2) >= 2ull * sm_count() ? 2 : 1)
-                          : pick_rows_per_warp(rows);
+                          : (rows / (kWarps * 4) >= 2ull * sm_count() ? 4 : rows / (kWarps * 2) >= 2ull * sm_count() ? 2 : 1);
   const unsigned blocks = static_cast<unsigned>((rows + kWarps * rpw - 1) / (kWarps * rpw));
   const size_t smem = (k + 1023) / 1024 * 1024 * 2 + (k / 16) * 4;
 #define GEMB_LAUNCH_FP4_GEMV(R)                                                                   \
@@ -433,6 +552,20 @@ int32_t validate_nvfp4_gemv(const char* op, uint64_t rows, uint64_t k, float ga,
 using namespace gemb;
 
 extern "C" {
+
+int32_t gemb_set_tuning(int32_t knob, int32_t value) {
+  if (knob == GEMB_TUNE_GEMV_ROWS) {
+    GEMB_REQUIRE(value == 0 || value == 1 || value == 2 || value == 4,
+                 "gemb_set_tuning: rows per warp must be 0 (auto), 1, 2 or 4");
+    g_rows_override = value;
+    return GEMB_OK;
+  }
+  if (knob == GEMB_TUNE_GEMV_PDL) {
+    g_pdl = value != 0;
+    return GEMB_OK;
+  }
+  return fail(GEMB_INVALID_ARGUMENT, "gemb_set_tuning: unknown knob %d", knob);
+}
 
 int32_t gemb_fp8_gemv(const uint8_t* act, const float* act_scale, const uint8_t* w,
                       const uint16_t* w_scales, float* out, uint64_t rows, uint64_t k,

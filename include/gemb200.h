@@ -71,6 +71,14 @@ int32_t gemb_abi_version(void);
 /* GEMB_OK when the current CUDA device is compute capability 10.x, else GEMB_UNSUPPORTED.
  * Counterpart of the device gate at src/cuda/engine/inference_engine_initialize.cuh:14-19. */
 int32_t gemb_device_check(void);
+/* Benchmark hook: overrides an automatic launch heuristic process-wide (not thread safe; meant
+ * for sweeps).  No counterpart in the reference, which has no runtime kernel selectors
+ * (docs/ARCHITECTURE.md:289).  Knobs: GEMB_TUNE_GEMV_ROWS = weight rows per warp in the decode
+ * GEMVs, value 0 (automatic), 1, 2 or 4; GEMB_TUNE_GEMV_PDL = launch the decode GEMVs with
+ * programmatic stream serialization so a GEMV's weight prefetch overlaps the tail of the kernel
+ * before it (1, default) or not (0). */
+enum { GEMB_TUNE_GEMV_ROWS = 1, GEMB_TUNE_GEMV_PDL = 2 };
+int32_t gemb_set_tuning(int32_t knob, int32_t value);
 /* Bytes of an INTERLEAVED scale buffer for `rows` rows of K elements. */
 uint64_t gemb_interleaved_scale_bytes(uint64_t rows, uint64_t contracting_elements);
 

@@ -124,3 +124,33 @@ def test_decode_set_round_trip_property(lib, dev):
     lib.gemb_fp8_gemv_bf16in(x.view(torch.int16), w, ws, y1, 0, rows, k, None)
     lib.gemb_fp8_gemv_bf16in((x * 2).view(torch.int16), w, ws, y2, 0, rows, k, None)
     assert torch.equal(y1 * 2, y2)
+
+
+def test_fused_quantisation_at_rounding_boundaries(lib, dev, orc):
+    # The fused GEMV replaces x/scale by x*(1/scale) away from E4M3 rounding boundaries; feed it
+    # values whose quotients sit exactly on (and next to) midpoints and in the subnormal range.
+    rows, k = 64, 2048
+    tab = np.array([orc.e4m3_decode(i) for i in range(127)], np.float32)
+    mids = (tab[:-1] + tab[1:]) / 2
+    vals = np.concatenate([mids * 3, -mids * 3, tab * 3, np.nextafter(mids * 3, np.float32(1e9)),
+                           mids * 3 * (1 + 2.0 ** -8), mids * 3 * (1 - 2.0 ** -8)]).astype(np.float32)
+    rng = np.random.default_rng(0)
+    x = bf16_round(np.resize(vals, k)).reshape(1, k)
+    x[0, 0] = 448.0 * 3  # amax -> scale exactly 3
+    xq, xsc = orc.fp8_quantize(x)
+    assert xsc[0] == 3.0
+    w = (rng.standard_normal((rows, k)) * 0.02).astype(np.float32)
+    wq, wsc = orc.fp8_quantize(w)
+    wsb = bf16_bits(wsc)
+    y_plain, y_fused = torch.zeros((rows,), device=dev), torch.zeros((rows,), device=dev)
+    lib.gemb_fp8_gemv(to_dev(xq, dev), to_dev(xsc, dev), to_dev(wq, dev), to_dev(wsb, dev), y_plain, rows, k, None)
+    lib.gemb_fp8_gemv_bf16in(to_dev(bf16_bits(x), dev), to_dev(wq, dev), to_dev(wsb, dev), y_fused, 0, rows, k, None)
+    assert torch.equal(y_plain, y_fused)
+    # a scale that is not a power-of-two multiple: amax 5.0 -> scale 5/448
+    x2 = bf16_round(rng.standard_normal((1, k)).astype(np.float32))
+    x2[0, 1] = 5.0
+    x2 = np.clip(x2, -5, 5)
+    xq2, xsc2 = orc.fp8_quantize(x2)
+    lib.gemb_fp8_gemv(to_dev(xq2, dev), to_dev(xsc2, dev), to_dev(wq, dev), to_dev(wsb, dev), y_plain, rows, k, None)
+    lib.gemb_fp8_gemv_bf16in(to_dev(bf16_bits(x2), dev), to_dev(wq, dev), to_dev(wsb, dev), y_fused, 0, rows, k, None)
+    assert torch.equal(y_plain, y_fused)
