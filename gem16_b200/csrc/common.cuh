@@ -23,6 +23,8 @@ int32_t check_launch(const char* op);
 int32_t require_sm100(const char* op);
 // Number of SMs of the current device (cached).
 int sm_count();
+// Tuning knobs owned by the GEMM translation unit (see gemb_set_tuning).
+int32_t gemm_set_tuning(int32_t knob, int32_t value);
 
 inline bool positive_finite(float v) { return std::isfinite(v) && v > 0.0f; }
 

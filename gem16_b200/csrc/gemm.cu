@@ -1,0 +1,430 @@
+// Prefill projections: tcgen05 GEMMs with TMEM accumulators and TMA-staged operand tiles.
+//
+//   NVFP4  D[M,N] = alpha * sum_k (A e2m1 * SFA ue4m3)(B e2m1 * SFB ue4m3)   kind::mxf4nvf4.block16
+//   FP8    D[M,N] = (sum_k A e4m3 * B e4m3) * a_scale[m] * w_scale[n]          kind::f8f6f4
+//
+// A is the activation [M, K] (tokens), B the weight [N, K] (output rows), both K-major, so
+// D = A * B^T lands with one token per TMEM lane and one output feature per TMEM column.
+//
+// One persistent CTA per SM, six warps:
+//   warp 0   producer: one elected lane issues TMA tile loads (128-byte swizzle, no multicast)
+//            for A and B and 1-D bulk copies for the interleaved block scales into a ring of
+//            kStages shared-memory stages, each guarded by a full/empty mbarrier pair;
+//   warp 1   MMA issuer: owns the 512 TMEM columns; per stage copies the scales shared->TMEM
+//            (tcgen05.cp 32x128b.warpx4), issues one tcgen05.mma per 32 bytes of K and commits
+//            the stage's empty barrier; after the last K step commits the accumulator barrier;
+//   warps 2-5 epilogue: tcgen05.ld 32 lanes x 32 columns at a time, scale, round to bf16 and
+//            store 64 contiguous bytes per thread; accumulators are double buffered in TMEM
+//            (kAccStages) so the epilogue of tile i overlaps the main loop of tile i+1.
+// Tiles are walked with the token-tile index fastest so CTAs running at the same time share the
+// same weight tile through L2.
+//
+// Per stage a tile needs 128 B of K per row: 256 E2M1 or 128 E4M3 elements.  K only has to be
+// a multiple of 64 (NVFP4) / 32 (FP8): the last stage issues fewer MMAs, TMA zero-fills the
+// rest of its box.
+//
+// Every mbarrier wait is bounded; on expiry the kernel records a code in g_gemm_error, stops
+// issuing work, and still releases its TMEM before returning.
+#include <cuda.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace gemb {
+
+__device__ int g_gemm_error = 0;
+
+namespace {
+
+constexpr int kGemmThreads = 192;
+constexpr int BM = 128;
+
+struct GemmParams {
+  const uint8_t* sfa;            // NVFP4: interleaved activation scales
+  const uint8_t* sfb;            // NVFP4: interleaved weight scales
+  const float* a_scales;         // FP8: per-token scales
+  const uint16_t* w_scales;      // FP8: per-row bf16 scales
+  uint16_t* out;                 // bf16 [M, N]
+  uint32_t m, n, k;              // k in elements
+  float alpha;                   // NVFP4: 1 / (ga * gw)
+};
+
+template <bool kFp4, int BN, int kStages, int kAccStages>
+struct Cfg {
+  static constexpr int kKPerStage = kFp4 ? 256 : 128;      // elements covered by 128 bytes
+  static constexpr int kKPerMma = kFp4 ? 64 : 32;          // elements per tcgen05.mma
+  static constexpr int kABytes = BM * 128;
+  static constexpr int kBBytes = BN * 128;
+  static constexpr int kSfaBytes = kFp4 ? 2048 : 0;        // 4 chunks of 512 B
+  static constexpr int kSfbBytes = kFp4 ? (BN / 128) * 2048 : 0;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  // TMEM columns: accumulators first, then per-stage scale regions.
+  static constexpr int kAccCols = kAccStages * BN;
+  static constexpr int kSfaCols = 16;                      // 4 MMAs x 4 columns
+  static constexpr int kSfbCols = (BN / 32) * 4;           // 4 MMAs x BN/32 columns
+  static constexpr int kSfColsPerStage = kFp4 ? kSfaCols + kSfbCols : 0;
+  static_assert(kAccCols + kStages * kSfColsPerStage <= 512, "TMEM budget exceeded");
+  static_assert(BN % 128 == 0 && BN <= 256, "BN must be 128 or 256");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget exceeded");
+};
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+template <bool kFp4, int BN, int kStages, int kAccStages>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const GemmParams p) {
+  using C = Cfg<kFp4, BN, kStages, kAccStages>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_a = smem;
+  uint8_t* stage_b = stage_a + kStages * C::kABytes;
+  uint8_t* stage_sfa = stage_b + kStages * C::kBBytes;
+  uint8_t* stage_sfb = stage_sfa + kStages * C::kSfaBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_sfb + kStages * C::kSfbBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = full + kStages;
+  uint64_t* acc_full = empty + kStages;
+  uint64_t* acc_empty = acc_full + kAccStages;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + kAccStages);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&full[s], 1);
+      ptx::mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < kAccStages; ++s) {
+      ptx::mbar_init(&acc_full[s], 1);
+      ptx::mbar_init(&acc_empty[s], 4);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) ptx::tmem_alloc(tmem_holder, 512);
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const uint32_t m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
+  const uint32_t num_tiles = m_tiles * n_tiles;
+  const uint32_t k_stages = (p.k + C::kKPerStage - 1) / C::kKPerStage;
+  const uint32_t k_groups_pad = (p.k / 16 + 3) / 4;  // 512-byte scale chunks per 128-row group
+
+  auto fail_wait = [&](int code) {
+    atomicCAS(&g_gemm_error, 0, code);
+    *abort_flag = 1;
+  };
+
+  if (warp == 0) {
+    // ------------------------------- producer -------------------------------------------------
+    if (ptx::elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      for (uint32_t tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+        const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
+        for (uint32_t ks = 0; ks < k_stages; ++ks) {
+          if (!ptx::mbar_wait(&empty[stage], phase ^ 1)) { fail_wait(1); break; }
+          const uint32_t k0 = ks * C::kKPerStage;
+          const uint32_t n_mma = min(4u, (p.k - k0) / C::kKPerMma);
+          uint32_t bytes = C::kABytes + C::kBBytes;
+          if constexpr (kFp4) {
+            const uint32_t n_groups = min(static_cast<uint32_t>(BN / 128), (p.n - nt * BN + 127) / 128);
+            bytes += n_mma * 512 * (1 + n_groups);
+            ptx::mbar_expect_tx(&full[stage], bytes);
+            ptx::bulk_load_1d(stage_sfa + stage * C::kSfaBytes,
+                              p.sfa + (static_cast<uint64_t>(mt) * k_groups_pad + ks * 4) * 512, n_mma * 512,
+                              &full[stage]);
+            for (uint32_t g = 0; g < n_groups; ++g)
+              ptx::bulk_load_1d(stage_sfb + stage * C::kSfbBytes + g * 2048,
+                                p.sfb + (static_cast<uint64_t>(nt * (BN / 128) + g) * k_groups_pad + ks * 4) * 512,
+                                n_mma * 512, &full[stage]);
+          } else {
+            ptx::mbar_expect_tx(&full[stage], bytes);
+          }
+          ptx::tma_load_2d(stage_a + stage * C::kABytes, &map_a, &full[stage], static_cast<int32_t>(ks * 128),
+                           static_cast<int32_t>(mt * BM));
+          ptx::tma_load_2d(stage_b + stage * C::kBBytes, &map_b, &full[stage], static_cast<int32_t>(ks * 128),
+                           static_cast<int32_t>(nt * BN));
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -----------------------------------------------
+    if (ptx::elect_one()) {
+      constexpr uint32_t idesc = kFp4 ? ptx::idesc_nvfp4(BM, BN) : ptx::idesc_e4m3(BM, BN);
+      uint32_t stage = 0, phase = 0, as = 0, aphase = 0;
+      for (uint32_t tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+        if (!ptx::mbar_wait(&acc_empty[as], aphase ^ 1)) { fail_wait(2); break; }
+        ptx::tc_fence_after();
+        const uint32_t tmem_acc = tmem_base + as * BN;
+        bool ok = true;
+        for (uint32_t ks = 0; ks < k_stages; ++ks) {
+          if (!ptx::mbar_wait(&full[stage], phase)) { fail_wait(3); ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t k0 = ks * C::kKPerStage;
+          const uint32_t n_mma = min(4u, (p.k - k0) / C::kKPerMma);
+          const uint64_t a_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_a + stage * C::kABytes));
+          const uint64_t b_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_b + stage * C::kBBytes));
+          if constexpr (kFp4) {
+            const uint32_t tsfa = tmem_base + C::kAccCols + stage * C::kSfColsPerStage;
+            const uint32_t tsfb = tsfa + C::kSfaCols;
+            const uint32_t sfa_s = ptx::smem_addr(stage_sfa + stage * C::kSfaBytes);
+            const uint32_t sfb_s = ptx::smem_addr(stage_sfb + stage * C::kSfbBytes);
+            for (uint32_t j = 0; j < n_mma; ++j) {
+              ptx::tc_cp_32x128b_warpx4(tsfa + j * 4, ptx::smem_desc_scale_block(sfa_s + j * 512));
+#pragma unroll
+              for (uint32_t g = 0; g < BN / 128; ++g)
+                ptx::tc_cp_32x128b_warpx4(tsfb + j * (BN / 32) + g * 4,
+                                          ptx::smem_desc_scale_block(sfb_s + g * 2048 + j * 512));
+            }
+            for (uint32_t j = 0; j < n_mma; ++j)
+              ptx::tc_mma_nvfp4(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, tsfa + j * 4,
+                                tsfb + j * (BN / 32), (ks | j) != 0 ? 1u : 0u);
+          } else {
+            for (uint32_t j = 0; j < n_mma; ++j)
+              ptx::tc_mma_f8(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, (ks | j) != 0 ? 1u : 0u);
+          }
+          ptx::tc_commit(&empty[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        ptx::tc_commit(&acc_full[as]);
+        if (++as == kAccStages) { as = 0; aphase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue -------------------------------------------------
+    const uint32_t quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    uint32_t as = 0, aphase = 0;
+    for (uint32_t tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+      const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
+      if (!ptx::mbar_wait(&acc_full[as], aphase)) { fail_wait(4); break; }
+      ptx::tc_fence_after();
+      const uint32_t row = mt * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.m;
+      float row_scale = p.alpha;
+      if constexpr (!kFp4) row_scale = row_ok ? __ldg(p.a_scales + row) : 0.0f;
+      uint16_t* out_row = p.out + static_cast<uint64_t>(row) * p.n;
+      const uint32_t tmem_acc = tmem_base + as * BN + ((quarter * 32) << 16);
+#pragma unroll 1
+      for (uint32_t c = 0; c < BN / 32; ++c) {
+        const uint32_t col0 = nt * BN + c * 32;
+        if (col0 >= p.n) break;  // warp-uniform
+        uint32_t v[32];
+        ptx::tc_ld_32x32b_x32(tmem_acc + c * 32, v);
+        ptx::tc_wait_ld();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float lo = __uint_as_float(v[2 * i]), hi = __uint_as_float(v[2 * i + 1]);
+          if constexpr (kFp4) {
+            lo = __fmul_rn(lo, row_scale);
+            hi = __fmul_rn(hi, row_scale);
+          } else {
+            // (acc * a_scale) * w_scale, in that order: src/cuda/fp8/cutlass_sm120.cu:49-63.
+            const uint32_t c0 = min(col0 + 2 * i, p.n - 1), c1 = min(col0 + 2 * i + 1, p.n - 1);
+            lo = __fmul_rn(__fmul_rn(lo, row_scale), bf16_bits_to_float(__ldg(p.w_scales + c0)));
+            hi = __fmul_rn(__fmul_rn(hi, row_scale), bf16_bits_to_float(__ldg(p.w_scales + c1)));
+          }
+          packed[i] = pack_bf16x2(lo, hi);
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (col0 + q * 8 + 8 <= p.n) {
+              *reinterpret_cast<uint4*>(out_row + col0 + q * 8) =
+                  make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
+      if (++as == kAccStages) { as = 0; aphase ^= 1; }
+    }
+  }
+
+  // ------------------------------- teardown ---------------------------------------------------
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // Give copies that are still in flight a bounded time to land before the CTA exits.
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+// Byte matrix [rows, row_bytes] row-major -> tiles of 128 bytes x box_rows rows, 128-byte swizzle.
+int32_t make_byte_map(const char* op, CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                      uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(GEMB_UNSUPPORTED, "%s: cuTensorMapEncodeTiled is not available from the driver", op);
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(GEMB_INTERNAL, "%s: cuTensorMapEncodeTiled failed with CUresult %d", op, int(r));
+  return GEMB_OK;
+}
+
+int g_gemm_bn = 0;  // 0 = automatic; gemb_set_tuning(GEMB_TUNE_GEMM_BN, 128 | 256)
+
+template <bool kFp4, int BN, int kStages, int kAccStages>
+int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmParams& p, cudaStream_t stream) {
+  using C = Cfg<kFp4, BN, kStages, kAccStages>;
+  auto kern = gemm_kernel<kFp4, BN, kStages, kAccStages>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  const uint64_t row_bytes = kFp4 ? p.k / 2 : p.k;
+  CUtensorMap map_a, map_b;
+  GEMB_TRY(make_byte_map(op, &map_a, a, p.m, row_bytes, BM));
+  GEMB_TRY(make_byte_map(op, &map_b, b, p.n, row_bytes, BN));
+  const uint32_t tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
+  const unsigned grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(sm_count()));
+  kern<<<grid, kGemmThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
+  return check_launch(op);
+}
+
+int32_t validate_gemm(const char* op, uint64_t tokens, uint64_t rows, uint64_t k, uint64_t k_multiple) {
+  GEMB_REQUIRE(tokens > 0 && rows > 0 && k > 0, "%s: geometry must be nonzero", op);
+  GEMB_REQUIRE(k % k_multiple == 0, "%s: contracting extent must be a multiple of %llu", op,
+               static_cast<unsigned long long>(k_multiple));
+  GEMB_REQUIRE(rows % 8 == 0, "%s: rows must be a multiple of 8", op);
+  GEMB_REQUIRE(tokens < (1ull << 31) && rows < (1ull << 31) && k < (1ull << 31), "%s: extent too large", op);
+  return GEMB_OK;
+}
+
+}  // namespace
+
+int32_t gemm_set_tuning(int32_t knob, int32_t value) {
+  if (knob == GEMB_TUNE_GEMM_BN) {
+    GEMB_REQUIRE(value == 0 || value == 128 || value == 256,
+                 "gemb_set_tuning: GEMM tile width must be 0 (auto), 128 or 256");
+    g_gemm_bn = value;
+    return GEMB_OK;
+  }
+  return fail(GEMB_INVALID_ARGUMENT, "gemb_set_tuning: unknown knob %d", knob);
+}
+
+}  // namespace gemb
+
+using namespace gemb;
+
+extern "C" {
+
+int32_t gemb_nvfp4_gemm_bf16(const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* w,
+                             const uint8_t* w_scales_interleaved, uint16_t* out, uint64_t tokens,
+                             uint64_t rows, uint64_t k, float ga, float gw, gemb_stream_t stream) {
+  const char* op = "gemb_nvfp4_gemm_bf16";
+  GEMB_REQUIRE(act && act_scales_interleaved && w && w_scales_interleaved && out, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_gemm(op, tokens, rows, k, 64));
+  GEMB_REQUIRE(positive_finite(ga) && positive_finite(gw) && std::isfinite(ga * gw) && ga * gw > 0.0f,
+               "%s: global divisors must be positive and finite", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(act_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(w_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % 16 == 0,
+               "%s: all buffers must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  GemmParams p{};
+  p.sfa = act_scales_interleaved;
+  p.sfb = w_scales_interleaved;
+  p.out = out;
+  p.m = static_cast<uint32_t>(tokens);
+  p.n = static_cast<uint32_t>(rows);
+  p.k = static_cast<uint32_t>(k);
+  p.alpha = 1.0f / (ga * gw);  // one multiply in the epilogue, as src/cuda/nvfp4/cutlass_sm120.cu:551-552
+  const int bn = g_gemm_bn ? g_gemm_bn : 256;
+  if (bn == 128) return launch_gemm<true, 128, 6, 2>(op, act, w, p, stream);
+  return launch_gemm<true, 256, 4, 1>(op, act, w, p, stream);
+}
+
+int32_t gemb_fp8_gemm_bf16(const uint8_t* act, const float* act_scales, const uint8_t* w,
+                           const uint16_t* w_scales_bf16, uint16_t* out, uint64_t tokens, uint64_t rows,
+                           uint64_t k, gemb_stream_t stream) {
+  const char* op = "gemb_fp8_gemm_bf16";
+  GEMB_REQUIRE(act && act_scales && w && w_scales_bf16 && out, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_gemm(op, tokens, rows, k, 32));
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % 16 == 0,
+               "%s: activation, weight and output must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  GemmParams p{};
+  p.a_scales = act_scales;
+  p.w_scales = w_scales_bf16;
+  p.out = out;
+  p.m = static_cast<uint32_t>(tokens);
+  p.n = static_cast<uint32_t>(rows);
+  p.k = static_cast<uint32_t>(k);
+  p.alpha = 1.0f;
+  const int bn = g_gemm_bn ? g_gemm_bn : 256;
+  if (bn == 128) return launch_gemm<false, 128, 6, 2>(op, act, w, p, stream);
+  return launch_gemm<false, 256, 4, 2>(op, act, w, p, stream);
+}
+
+int32_t gemb_check_device_status(void) {
+  const char* op = "gemb_check_device_status";
+  int code = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&code, g_gemm_error, sizeof code);
+  if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+  if (code != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof zero);
+    return fail(GEMB_INTERNAL, "%s: a GEMM kernel gave up waiting on a pipeline barrier (role %d)", op, code);
+  }
+  return GEMB_OK;
+}
+
+}  // extern "C"

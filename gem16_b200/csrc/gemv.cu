@@ -564,7 +564,7 @@ int32_t gemb_set_tuning(int32_t knob, int32_t value) {
     g_pdl = value != 0;
     return GEMB_OK;
   }
-  return fail(GEMB_INVALID_ARGUMENT, "gemb_set_tuning: unknown knob %d", knob);
+  return gemm_set_tuning(knob, value);
 }
 
 int32_t gemb_fp8_gemv(const uint8_t* act, const float* act_scale, const uint8_t* w,

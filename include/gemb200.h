@@ -76,8 +76,9 @@ int32_t gemb_device_check(void);
  * (docs/ARCHITECTURE.md:289).  Knobs: GEMB_TUNE_GEMV_ROWS = weight rows per warp in the decode
  * GEMVs, value 0 (automatic), 1, 2 or 4; GEMB_TUNE_GEMV_PDL = launch the decode GEMVs with
  * programmatic stream serialization so a GEMV's weight prefetch overlaps the tail of the kernel
- * before it (1, default) or not (0). */
-enum { GEMB_TUNE_GEMV_ROWS = 1, GEMB_TUNE_GEMV_PDL = 2 };
+ * before it (1, default) or not (0); GEMB_TUNE_GEMM_BN = output-feature width of a prefill GEMM
+ * tile, 0 (automatic), 128 or 256. */
+enum { GEMB_TUNE_GEMV_ROWS = 1, GEMB_TUNE_GEMV_PDL = 2, GEMB_TUNE_GEMM_BN = 3 };
 int32_t gemb_set_tuning(int32_t knob, int32_t value);
 /* Bytes of an INTERLEAVED scale buffer for `rows` rows of K elements. */
 uint64_t gemb_interleaved_scale_bytes(uint64_t rows, uint64_t contracting_elements);
@@ -187,6 +188,38 @@ int32_t gemb_nvfp4_gemv_gate_up(const uint8_t* packed_activation_e2m1,
                                 float gate_weight_global_divisor,
                                 float up_activation_global_divisor,
                                 float up_weight_global_divisor, gemb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Prefill projections (tcgen05 GEMM, TMEM accumulators, TMA-staged tiles), bf16 output [tokens,
+ * rows].  Operands are row-major and K-major: activation [tokens, K], weight [rows, K].
+ * ---------------------------------------------------------------------------------------- */
+
+/* NVFP4 W4A4: out = bf16( (sum_k qa sa qw sw) * (1 / (ga * gw)) ).  Both scale buffers use the
+ * INTERLEAVED layout (rows padded to 128); K % 64 == 0, rows % 8 == 0; any token count.
+ * Replaces LaunchNvfp4CutlassProjectionBf16Batch, src/cuda/nvfp4/cutlass_sm120.h:24-39.  The
+ * reference re-tiles its Row8/K64 weights into scratch on every call (PrepareWeightKernel,
+ * src/cuda/nvfp4/cutlass_sm120.cu:196-252); here weights are stored once, row-major with
+ * interleaved scales, so the scratch and workspace arguments disappear. */
+int32_t gemb_nvfp4_gemm_bf16(const uint8_t* packed_activation_e2m1,
+                             const uint8_t* interleaved_activation_scales,
+                             const uint8_t* packed_weight_e2m1,
+                             const uint8_t* interleaved_weight_scales, uint16_t* output_bf16,
+                             uint64_t tokens, uint64_t rows, uint64_t contracting_elements,
+                             float activation_global_divisor, float weight_global_divisor,
+                             gemb_stream_t stream);
+
+/* FP8 W8A8: out = bf16( ((sum_k qa qw) * a_scale[token]) * bf16(w_scale[row]) ).  K % 32 == 0,
+ * rows % 8 == 0.  Replaces LaunchFp8CutlassProjectionBatch, src/cuda/fp8/cutlass_sm120.h:17-28
+ * (no workspace needed). */
+int32_t gemb_fp8_gemm_bf16(const uint8_t* activation_e4m3fn, const float* activation_scales,
+                           const uint8_t* weight_e4m3fn, const uint16_t* weight_scales_bf16,
+                           uint16_t* output_bf16, uint64_t tokens, uint64_t rows,
+                           uint64_t contracting_elements, gemb_stream_t stream);
+
+/* Synchronises the device and reports whether a GEMM kernel gave up on a bounded pipeline wait
+ * since the last call (GEMB_INTERNAL, flag cleared) or not (GEMB_OK).  The reference has no
+ * counterpart: its kernels have no device-side waits. */
+int32_t gemb_check_device_status(void);
 
 /* ------------------------------------------------------------------------------------------
  * Scalar cross-check projections (one thread per output, fp32 fma in k order).  Slow on
