@@ -13,9 +13,12 @@
 //   warp 1   MMA issuer: owns the 512 TMEM columns; per stage copies the scales shared->TMEM
 //            (tcgen05.cp 32x128b.warpx4), issues one tcgen05.mma per 32 bytes of K and commits
 //            the stage's empty barrier; after the last K step commits the accumulator barrier;
-//   warps 2-5 epilogue: tcgen05.ld 32 lanes x 32 columns at a time, scale, round to bf16 and
-//            store 64 contiguous bytes per thread; accumulators are double buffered in TMEM
-//            (kAccStages) so the epilogue of tile i overlaps the main loop of tile i+1.
+//   warps 2-5 epilogue: each warp drains its 32 TMEM lanes 64 columns at a time (two
+//            tcgen05.ld in flight), scales, rounds to bf16, writes a 32 x 128-byte block into
+//            its own swizzled staging buffer and issues a TMA store (which also clips the
+//            token / row tails); staging is double buffered per warp.  With kAccStages = 2 the
+//            accumulators are double buffered in TMEM so the epilogue of tile i overlaps the
+//            main loop of tile i+1.
 // Tiles are walked with the token-tile index fastest so CTAs running at the same time share the
 // same weight tile through L2.
 //
@@ -61,8 +64,9 @@ struct Cfg {
   static constexpr int kSfaBytes = kFp4 ? 2048 : 0;        // 4 chunks of 512 B
   static constexpr int kSfbBytes = kFp4 ? (BN / 128) * 2048 : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kEpiBytes = 4 * 2 * 4096;          // 4 warps x 2 buffers x (32 rows x 128 B)
   static constexpr int kBarrierBytes = 1024;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarrierBytes + 1024;  // + alignment slack
   // TMEM columns: accumulators first, then per-stage scale regions.
   static constexpr int kAccCols = kAccStages * BN;
   static constexpr int kSfaCols = 16;                      // 4 MMAs x 4 columns
@@ -82,13 +86,14 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 template <bool kFp4, int BN, int kStages, int kAccStages>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-            const GemmParams p) {
+            const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   using C = Cfg<kFp4, BN, kStages, kAccStages>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_a = smem;
   uint8_t* stage_b = stage_a + kStages * C::kABytes;
-  uint8_t* stage_sfa = stage_b + kStages * C::kBBytes;
+  uint8_t* epi_stage = stage_b + kStages * C::kBBytes;
+  uint8_t* stage_sfa = epi_stage + C::kEpiBytes;
   uint8_t* stage_sfb = stage_sfa + kStages * C::kSfaBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(stage_sfb + kStages * C::kSfbBytes);
   uint64_t* full = bars;
@@ -112,6 +117,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
+    ptx::prefetch_tensormap(&map_out);
   }
   if (warp == 1) ptx::tmem_alloc(tmem_holder, 512);
   ptx::tc_fence_before();
@@ -209,54 +215,75 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   } else {
     // ------------------------------- epilogue -------------------------------------------------
     const uint32_t quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    uint32_t as = 0, aphase = 0;
+    uint8_t* my_stage = epi_stage + quarter * 8192;
+    uint32_t as = 0, aphase = 0, buf = 0;
     for (uint32_t tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
       const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
       if (!ptx::mbar_wait(&acc_full[as], aphase)) { fail_wait(4); break; }
       ptx::tc_fence_after();
-      const uint32_t row = mt * BM + quarter * 32 + lane;
-      const bool row_ok = row < p.m;
+      const uint32_t row0 = mt * BM + quarter * 32;
       float row_scale = p.alpha;
-      if constexpr (!kFp4) row_scale = row_ok ? __ldg(p.a_scales + row) : 0.0f;
-      uint16_t* out_row = p.out + static_cast<uint64_t>(row) * p.n;
+      if constexpr (!kFp4) row_scale = row0 + lane < p.m ? __ldg(p.a_scales + row0 + lane) : 0.0f;
       const uint32_t tmem_acc = tmem_base + as * BN + ((quarter * 32) << 16);
 #pragma unroll 1
-      for (uint32_t c = 0; c < BN / 32; ++c) {
-        const uint32_t col0 = nt * BN + c * 32;
-        if (col0 >= p.n) break;  // warp-uniform
-        uint32_t v[32];
-        ptx::tc_ld_32x32b_x32(tmem_acc + c * 32, v);
-        ptx::tc_wait_ld();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float lo = __uint_as_float(v[2 * i]), hi = __uint_as_float(v[2 * i + 1]);
-          if constexpr (kFp4) {
-            lo = __fmul_rn(lo, row_scale);
-            hi = __fmul_rn(hi, row_scale);
-          } else {
-            // (acc * a_scale) * w_scale, in that order: src/cuda/fp8/cutlass_sm120.cu:49-63.
-            const uint32_t c0 = min(col0 + 2 * i, p.n - 1), c1 = min(col0 + 2 * i + 1, p.n - 1);
-            lo = __fmul_rn(__fmul_rn(lo, row_scale), bf16_bits_to_float(__ldg(p.w_scales + c0)));
-            hi = __fmul_rn(__fmul_rn(hi, row_scale), bf16_bits_to_float(__ldg(p.w_scales + c1)));
-          }
-          packed[i] = pack_bf16x2(lo, hi);
+      for (uint32_t c = 0; c < BN / 64; ++c) {
+        const uint32_t col0 = nt * BN + c * 64;
+        if (col0 >= p.n || row0 >= p.m) break;  // warp-uniform
+        uint32_t v0[32], v1[32];
+        ptx::tc_ld_32x32b_x32(tmem_acc + c * 64, v0);
+        ptx::tc_ld_32x32b_x32(tmem_acc + c * 64 + 32, v1);
+        uint32_t ws_pair = 0;  // FP8: lane l holds the bf16 scales of columns col0 + 2l, col0 + 2l + 1
+        if constexpr (!kFp4) {
+          const uint32_t c0 = min(col0 + 2 * lane, p.n - 2);
+          ws_pair = __ldg(reinterpret_cast<const uint32_t*>(p.w_scales + c0));
         }
-        if (row_ok) {
+        // The staging buffer about to be overwritten was handed to a TMA store two sub-tiles ago.
+        if (lane == 0) ptx::bulk_wait_group_read<1>();
+        __syncwarp();
+        ptx::tc_wait_ld();
+        uint8_t* sbuf = my_stage + buf * 4096;
+        auto convert = [&](const uint32_t (&v)[32], int half) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            if (col0 + q * 8 + 8 <= p.n) {
-              *reinterpret_cast<uint4*>(out_row + col0 + q * 8) =
-                  make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            uint32_t packed[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int e = q * 8 + i * 2;  // column within this 32-column half
+              float lo = __uint_as_float(v[e]), hi = __uint_as_float(v[e + 1]);
+              if constexpr (kFp4) {
+                lo = __fmul_rn(lo, row_scale);
+                hi = __fmul_rn(hi, row_scale);
+              } else {
+                // (acc * a_scale) * w_scale, in that order: src/cuda/fp8/cutlass_sm120.cu:49-63.
+                const uint32_t wp = __shfl_sync(0xFFFFFFFFu, ws_pair, half * 16 + e / 2);
+                lo = __fmul_rn(__fmul_rn(lo, row_scale), __uint_as_float(wp << 16));
+                hi = __fmul_rn(__fmul_rn(hi, row_scale), __uint_as_float(wp & 0xFFFF0000u));
+              }
+              packed[i] = pack_bf16x2(lo, hi);
             }
+            // 16-byte chunk j of row `lane`, stored at chunk j ^ (lane % 8): the 128-byte swizzle
+            // the output tensor map expects, and conflict free for the warp.
+            const int j = half * 4 + q;
+            *reinterpret_cast<uint4*>(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
+        };
+        convert(v0, 0);
+        convert(v1, 1);
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::tma_store_2d(&map_out, sbuf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
+          ptx::bulk_commit_group();
         }
+        buf ^= 1;
       }
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
       if (++as == kAccStages) { as = 0; aphase ^= 1; }
     }
+    if (lane == 0) ptx::bulk_wait_group_all();
   }
 
   // ------------------------------- teardown ---------------------------------------------------
@@ -312,6 +339,21 @@ int32_t make_byte_map(const char* op, CUtensorMap* map, const void* base, uint64
   return GEMB_OK;
 }
 
+// bf16 matrix [rows, cols] row-major -> boxes of 64 columns (128 bytes) x 32 rows, 128-byte swizzle.
+int32_t make_out_map(const char* op, CUtensorMap* map, void* base, uint64_t rows, uint64_t cols) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(GEMB_UNSUPPORTED, "%s: cuTensorMapEncodeTiled is not available from the driver", op);
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(GEMB_INTERNAL, "%s: cuTensorMapEncodeTiled failed with CUresult %d", op, int(r));
+  return GEMB_OK;
+}
+
 int g_gemm_bn = 0;  // 0 = automatic; gemb_set_tuning(GEMB_TUNE_GEMM_BN, 128 | 256)
 
 template <bool kFp4, int BN, int kStages, int kAccStages>
@@ -328,12 +370,13 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
     configured[dev] = true;
   }
   const uint64_t row_bytes = kFp4 ? p.k / 2 : p.k;
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_out;
   GEMB_TRY(make_byte_map(op, &map_a, a, p.m, row_bytes, BM));
   GEMB_TRY(make_byte_map(op, &map_b, b, p.n, row_bytes, BN));
+  GEMB_TRY(make_out_map(op, &map_out, p.out, p.m, p.n));
   const uint32_t tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
   const unsigned grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(sm_count()));
-  kern<<<grid, kGemmThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
+  kern<<<grid, kGemmThreads, C::kSmemBytes, stream>>>(map_a, map_b, map_out, p);
   return check_launch(op);
 }
 
@@ -387,8 +430,8 @@ int32_t gemb_nvfp4_gemm_bf16(const uint8_t* act, const uint8_t* act_scales_inter
   p.k = static_cast<uint32_t>(k);
   p.alpha = 1.0f / (ga * gw);  // one multiply in the epilogue, as src/cuda/nvfp4/cutlass_sm120.cu:551-552
   const int bn = g_gemm_bn ? g_gemm_bn : 256;
-  if (bn == 128) return launch_gemm<true, 128, 6, 2>(op, act, w, p, stream);
-  return launch_gemm<true, 256, 4, 1>(op, act, w, p, stream);
+  if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
+  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
 }
 
 int32_t gemb_fp8_gemm_bf16(const uint8_t* act, const float* act_scales, const uint8_t* w,

@@ -86,6 +86,21 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
       : "memory");
 }
 
+// 2-D tiled store shared -> global (bulk async-group completion).  Out-of-range parts of the box
+// are clipped by the hardware.
+__device__ __forceinline__ void tma_store_2d(const void* map, const void* smem_src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(smem_addr(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most `kPending` of this thread's bulk groups still read their shared source.
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---- tensor memory ---------------------------------------------------------------------------
 // Whole-warp: allocates `cols` (power of two >= 32) TMEM columns, base address written to smem.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
