@@ -10,15 +10,20 @@
 //   warp 0   producer: one elected lane issues TMA tile loads (128-byte swizzle, no multicast)
 //            for A and B and 1-D bulk copies for the interleaved block scales into a ring of
 //            kStages shared-memory stages, each guarded by a full/empty mbarrier pair;
-//   warp 1   MMA issuer: owns the 512 TMEM columns; per stage copies the scales shared->TMEM
-//            (tcgen05.cp 32x128b.warpx4), issues one tcgen05.mma per 32 bytes of K and commits
-//            the stage's empty barrier; after the last K step commits the accumulator barrier;
+//   warp 1   MMA issuer: owns the 512 TMEM columns; per stage issues one tcgen05.mma per 32
+//            bytes of K and commits the stage's empty barrier; after the last K step commits
+//            the accumulator barrier;
 //   warps 2-5 epilogue: each warp drains its 32 TMEM lanes 64 columns at a time (two
 //            tcgen05.ld in flight), scales, rounds to bf16, writes a 32 x 128-byte block into
 //            its own swizzled staging buffer and issues a TMA store (which also clips the
 //            token / row tails); staging is double buffered per warp.  With kAccStages = 2 the
 //            accumulators are double buffered in TMEM so the epilogue of tile i overlaps the
 //            main loop of tile i+1.
+//   warps 6-9 (NVFP4 only) scale movers: each copies the stage's block scales from shared
+//            memory into its quarter of TMEM with tcgen05.st (one 128-bit shared load feeds four
+//            TMEM columns) and arrives on the stage's scales-ready barrier.  Doing this with
+//            tcgen05.cp from the MMA thread costs a third of the tensor-pipe time, because those
+//            copies queue in front of the MMAs.
 // Tiles are walked with the token-tile index fastest so CTAs running at the same time share the
 // same weight tile through L2.
 //
@@ -42,7 +47,8 @@ __device__ int g_gemm_error = 0;
 
 namespace {
 
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreadsFp8 = 192;   // producer, MMA, 4 epilogue warps
+constexpr int kGemmThreadsFp4 = 320;   // + 4 scale-mover warps
 constexpr int BM = 128;
 
 struct GemmParams {
@@ -53,6 +59,7 @@ struct GemmParams {
   uint16_t* out;                 // bf16 [M, N]
   uint32_t m, n, k;              // k in elements
   float alpha;                   // NVFP4: 1 / (ga * gw)
+  uint32_t debug;                // bit 0: skip loads, bit 1: skip MMAs, bit 2: skip epilogue (experiments only)
 };
 
 template <bool kFp4, int BN, int kStages, int kAccStages>
@@ -61,19 +68,26 @@ struct Cfg {
   static constexpr int kKPerMma = kFp4 ? 64 : 32;          // elements per tcgen05.mma
   static constexpr int kABytes = BM * 128;
   static constexpr int kBBytes = BN * 128;
+  // Weight scales are stored in 128-row groups.  A 192-wide tile starts on a group boundary
+  // (even tiles) or 64 rows into a group (odd tiles): it always stages two whole groups in shared
+  // memory and the scale movers write just the six 32-row columns the tile covers into TMEM.
+  static constexpr int kSfbGroups = BN <= 128 ? 1 : 2;
   static constexpr int kSfaBytes = kFp4 ? 2048 : 0;        // 4 chunks of 512 B
-  static constexpr int kSfbBytes = kFp4 ? (BN / 128) * 2048 : 0;
+  static constexpr int kSfbBytes = kFp4 ? kSfbGroups * 2048 : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kEpiBytes = 4 * 2 * 4096;          // 4 warps x 2 buffers x (32 rows x 128 B)
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarrierBytes + 1024;  // + alignment slack
-  // TMEM columns: accumulators first, then per-stage scale regions.
+  // TMEM columns: accumulators first, then a ring of scale regions (one per step in flight).
   static constexpr int kAccCols = kAccStages * BN;
   static constexpr int kSfaCols = 16;                      // 4 MMAs x 4 columns
-  static constexpr int kSfbCols = (BN / 32) * 4;           // 4 MMAs x BN/32 columns
+  static constexpr int kSfbColsPerMma = BN / 32;
+  static constexpr int kSfbCols = 4 * kSfbColsPerMma;
   static constexpr int kSfColsPerStage = kFp4 ? kSfaCols + kSfbCols : 0;
-  static_assert(kAccCols + kStages * kSfColsPerStage <= 512, "TMEM budget exceeded");
-  static_assert(BN % 128 == 0 && BN <= 256, "BN must be 128 or 256");
+  static constexpr int kSfStages = !kFp4 ? 1 : ((512 - kAccCols) / kSfColsPerStage < kStages ? (512 - kAccCols) / kSfColsPerStage : kStages);
+  static_assert(!kFp4 || kSfStages >= 2, "TMEM budget exceeded");
+  static_assert(kAccCols + (kFp4 ? kSfStages * kSfColsPerStage : 0) <= 512, "TMEM budget exceeded");
+  static_assert(BN % 64 == 0 && BN <= 256, "BN must be 128, 192 or 256");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget exceeded");
 };
 
@@ -84,7 +98,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 template <bool kFp4, int BN, int kStages, int kAccStages>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kFp4 ? kGemmThreadsFp4 : kGemmThreadsFp8, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   using C = Cfg<kFp4, BN, kStages, kAccStages>;
@@ -100,7 +114,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   uint64_t* empty = full + kStages;
   uint64_t* acc_full = empty + kStages;
   uint64_t* acc_empty = acc_full + kAccStages;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + kAccStages);
+  uint64_t* sf_ready = acc_empty + kAccStages;   // per smem stage: scales are in TMEM
+  uint64_t* sf_free = sf_ready + kStages;        // per TMEM scale region: its MMAs have completed
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_free + kStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -108,6 +124,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(&full[s], 1);
       ptx::mbar_init(&empty[s], 1);
+      ptx::mbar_init(&sf_ready[s], 4);
+      ptx::mbar_init(&sf_free[s], 1);
     }
     for (int s = 0; s < kAccStages; ++s) {
       ptx::mbar_init(&acc_full[s], 1);
@@ -130,6 +148,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t k_stages = (p.k + C::kKPerStage - 1) / C::kKPerStage;
   const uint32_t k_groups_pad = (p.k / 16 + 3) / 4;  // 512-byte scale chunks per 128-row group
 
+  // Tile order: groups of 16 token tiles; inside a group the token tile runs fastest, so the
+  // CTAs of a wave share a few weight tiles and the group's activations stay in L2 while every
+  // weight tile passes over them.
+  auto tile_coords = [&](uint32_t tile, uint32_t& mt, uint32_t& nt) {
+    constexpr uint32_t kGroupM = 16;
+    const uint32_t per_group = kGroupM * n_tiles;
+    const uint32_t first_m = (tile / per_group) * kGroupM;
+    const uint32_t gm = min(kGroupM, m_tiles - first_m);
+    const uint32_t within = tile % per_group;
+    mt = first_m + within % gm;
+    nt = within / gm;
+  };
+
   auto fail_wait = [&](int code) {
     atomicCAS(&g_gemm_error, 0, code);
     *abort_flag = 1;
@@ -140,14 +171,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (ptx::elect_one()) {
       uint32_t stage = 0, phase = 0;
       for (uint32_t tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
-        const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
+        uint32_t mt, nt;
+        tile_coords(tile, mt, nt);
         for (uint32_t ks = 0; ks < k_stages; ++ks) {
           if (!ptx::mbar_wait(&empty[stage], phase ^ 1)) { fail_wait(1); break; }
           const uint32_t k0 = ks * C::kKPerStage;
           const uint32_t n_mma = min(4u, (p.k - k0) / C::kKPerMma);
           uint32_t bytes = C::kABytes + C::kBBytes;
+          if (p.debug & 1) {
+            ptx::mbar_arrive(&full[stage]);
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if constexpr (kFp4) {
-            const uint32_t n_groups = min(static_cast<uint32_t>(BN / 128), (p.n - nt * BN + 127) / 128);
+            const uint32_t g0 = (nt * BN) / 128, total_groups = (p.n + 127) / 128;
+            const uint32_t n_groups = min(static_cast<uint32_t>(C::kSfbGroups), total_groups - g0);
             bytes += n_mma * 512 * (1 + n_groups);
             ptx::mbar_expect_tx(&full[stage], bytes);
             ptx::bulk_load_1d(stage_sfa + stage * C::kSfaBytes,
@@ -155,7 +193,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                               &full[stage]);
             for (uint32_t g = 0; g < n_groups; ++g)
               ptx::bulk_load_1d(stage_sfb + stage * C::kSfbBytes + g * 2048,
-                                p.sfb + (static_cast<uint64_t>(nt * (BN / 128) + g) * k_groups_pad + ks * 4) * 512,
+                                p.sfb + (static_cast<uint64_t>(g0 + g) * k_groups_pad + ks * 4) * 512,
                                 n_mma * 512, &full[stage]);
           } else {
             ptx::mbar_expect_tx(&full[stage], bytes);
@@ -170,46 +208,96 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -----------------------------------------------
+    // The CTA's work is a flat sequence of steps (tile, k stage).
     if (ptx::elect_one()) {
       constexpr uint32_t idesc = kFp4 ? ptx::idesc_nvfp4(BM, BN) : ptx::idesc_e4m3(BM, BN);
-      uint32_t stage = 0, phase = 0, as = 0, aphase = 0;
-      for (uint32_t tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
-        if (!ptx::mbar_wait(&acc_empty[as], aphase ^ 1)) { fail_wait(2); break; }
+      const uint32_t my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      const uint32_t total_steps = my_tiles * k_stages;
+      uint32_t as = 0, aphase = 0;
+      uint32_t stage = 0, phase = 0;
+      for (uint32_t step = 0; step < total_steps && !*abort_flag; ++step) {
+        const uint32_t ks = step % k_stages;
+        if (ks == 0) {
+          if (!ptx::mbar_wait(&acc_empty[as], aphase ^ 1)) { fail_wait(2); break; }
+          ptx::tc_fence_after();
+        }
+        // NVFP4 waits for the scale movers (who waited for the operands); FP8 for the operands.
+        if (!ptx::mbar_wait(kFp4 ? &sf_ready[stage] : &full[stage], phase)) { fail_wait(3); break; }
         ptx::tc_fence_after();
         const uint32_t tmem_acc = tmem_base + as * BN;
-        bool ok = true;
-        for (uint32_t ks = 0; ks < k_stages; ++ks) {
-          if (!ptx::mbar_wait(&full[stage], phase)) { fail_wait(3); ok = false; break; }
-          ptx::tc_fence_after();
-          const uint32_t k0 = ks * C::kKPerStage;
-          const uint32_t n_mma = min(4u, (p.k - k0) / C::kKPerMma);
-          const uint64_t a_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_a + stage * C::kABytes));
-          const uint64_t b_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_b + stage * C::kBBytes));
-          if constexpr (kFp4) {
-            const uint32_t tsfa = tmem_base + C::kAccCols + stage * C::kSfColsPerStage;
-            const uint32_t tsfb = tsfa + C::kSfaCols;
-            const uint32_t sfa_s = ptx::smem_addr(stage_sfa + stage * C::kSfaBytes);
-            const uint32_t sfb_s = ptx::smem_addr(stage_sfb + stage * C::kSfbBytes);
-            for (uint32_t j = 0; j < n_mma; ++j) {
-              ptx::tc_cp_32x128b_warpx4(tsfa + j * 4, ptx::smem_desc_scale_block(sfa_s + j * 512));
-#pragma unroll
-              for (uint32_t g = 0; g < BN / 128; ++g)
-                ptx::tc_cp_32x128b_warpx4(tsfb + j * (BN / 32) + g * 4,
-                                          ptx::smem_desc_scale_block(sfb_s + g * 2048 + j * 512));
-            }
-            for (uint32_t j = 0; j < n_mma; ++j)
-              ptx::tc_mma_nvfp4(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, tsfa + j * 4,
-                                tsfb + j * (BN / 32), (ks | j) != 0 ? 1u : 0u);
-          } else {
-            for (uint32_t j = 0; j < n_mma; ++j)
-              ptx::tc_mma_f8(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, (ks | j) != 0 ? 1u : 0u);
-          }
-          ptx::tc_commit(&empty[stage]);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        const uint32_t n_mma = min(4u, (p.k - ks * C::kKPerStage) / C::kKPerMma);
+        const uint64_t a_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_a + stage * C::kABytes));
+        const uint64_t b_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_b + stage * C::kBBytes));
+        if (p.debug & 2) {
+        } else if constexpr (kFp4) {
+          const uint32_t region = step % C::kSfStages;
+          const uint32_t tsfa = tmem_base + C::kAccCols + region * C::kSfColsPerStage;
+          const uint32_t tsfb = tsfa + C::kSfaCols;
+          for (uint32_t j = 0; j < n_mma; ++j)
+            ptx::tc_mma_nvfp4(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, tsfa + j * 4,
+                              tsfb + j * C::kSfbColsPerMma, (ks | j) != 0 ? 1u : 0u);
+        } else {
+          for (uint32_t j = 0; j < n_mma; ++j)
+            ptx::tc_mma_f8(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, (ks | j) != 0 ? 1u : 0u);
         }
-        if (!ok) break;
-        ptx::tc_commit(&acc_full[as]);
-        if (++as == kAccStages) { as = 0; aphase ^= 1; }
+        ptx::tc_commit(&empty[stage]);
+        if constexpr (kFp4) ptx::tc_commit(&sf_free[step % C::kSfStages]);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        if (ks + 1 == k_stages) {
+          ptx::tc_commit(&acc_full[as]);
+          if (++as == kAccStages) { as = 0; aphase ^= 1; }
+        }
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------- scale movers (NVFP4) ------------------------------------
+    if constexpr (kFp4) {
+      const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      const uint32_t my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      const uint32_t total_steps = my_tiles * k_stages;
+      uint32_t stage = 0, phase = 0;
+      for (uint32_t step = 0; step < total_steps && !*abort_flag; ++step) {
+        if (!ptx::mbar_wait(&full[stage], phase)) { fail_wait(5); break; }
+        // The TMEM region is reused every kSfStages steps: wait until the MMAs that read its
+        // previous contents have completed.
+        const uint32_t region = step % C::kSfStages;
+        if (!ptx::mbar_wait(&sf_free[region], ((step / C::kSfStages) & 1) ^ 1)) { fail_wait(6); break; }
+        ptx::tc_fence_after();
+        const uint32_t ks = step % k_stages;
+        const uint32_t n_mma = min(4u, (p.k - ks * C::kKPerStage) / C::kKPerMma);
+        const uint32_t tsfa = tmem_base + C::kAccCols + region * C::kSfColsPerStage + lane_base;
+        const uint32_t tsfb = tsfa + C::kSfaCols;
+        const uint8_t* sfa_s = stage_sfa + stage * C::kSfaBytes + lane * 16;
+        const uint8_t* sfb_s = stage_sfb + stage * C::kSfbBytes + lane * 16;
+        // A 512-byte chunk holds, for row r of 32, sixteen bytes: four 32-row groups x four K
+        // blocks.  Lane r's 16 bytes are exactly its four TMEM columns for one MMA.
+        uint32_t mt, nt;
+        tile_coords(blockIdx.x + (step / k_stages) * gridDim.x, mt, nt);
+        const bool mid_group = ((nt * BN) % 128) != 0;  // only possible for 192-wide tiles
+        for (uint32_t j = 0; j < n_mma; ++j) {
+          ptx::tc_st_32x32b_x4(tsfa + j * 4, *reinterpret_cast<const uint4*>(sfa_s + j * 512));
+          const uint4 g0 = *reinterpret_cast<const uint4*>(sfb_s + j * 512);
+          if constexpr (BN == 128) {
+            ptx::tc_st_32x32b_x4(tsfb + j * 4, g0);
+          } else {
+            const uint4 g1 = *reinterpret_cast<const uint4*>(sfb_s + 2048 + j * 512);
+            if constexpr (BN == 256) {
+              ptx::tc_st_32x32b_x4(tsfb + j * 8, g0);
+              ptx::tc_st_32x32b_x4(tsfb + j * 8 + 4, g1);
+            } else if (mid_group) {   // rows 64..127 of the first group, then the whole second
+              ptx::tc_st_32x32b_x2(tsfb + j * 6, g0.z, g0.w);
+              ptx::tc_st_32x32b_x4(tsfb + j * 6 + 2, g1);
+            } else {                  // the whole first group, then rows 0..63 of the second
+              ptx::tc_st_32x32b_x4(tsfb + j * 6, g0);
+              ptx::tc_st_32x32b_x2(tsfb + j * 6 + 4, g1.x, g1.y);
+            }
+          }
+        }
+        ptx::tc_wait_st();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&sf_ready[stage]);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
   } else {
@@ -218,7 +306,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint8_t* my_stage = epi_stage + quarter * 8192;
     uint32_t as = 0, aphase = 0, buf = 0;
     for (uint32_t tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
-      const uint32_t mt = tile % m_tiles, nt = tile / m_tiles;
+      uint32_t mt, nt;
+      tile_coords(tile, mt, nt);
       if (!ptx::mbar_wait(&acc_full[as], aphase)) { fail_wait(4); break; }
       ptx::tc_fence_after();
       const uint32_t row0 = mt * BM + quarter * 32;
@@ -228,7 +317,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll 1
       for (uint32_t c = 0; c < BN / 64; ++c) {
         const uint32_t col0 = nt * BN + c * 64;
-        if (col0 >= p.n || row0 >= p.m) break;  // warp-uniform
+        if (col0 >= p.n || row0 >= p.m || (p.debug & 4)) break;  // warp-uniform
         uint32_t v0[32], v1[32];
         ptx::tc_ld_32x32b_x32(tmem_acc + c * 64, v0);
         ptx::tc_ld_32x32b_x32(tmem_acc + c * 64 + 32, v1);
@@ -354,6 +443,7 @@ int32_t make_out_map(const char* op, CUtensorMap* map, void* base, uint64_t rows
   return GEMB_OK;
 }
 
+int g_gemm_debug = 0;
 int g_gemm_bn = 0;  // 0 = automatic; gemb_set_tuning(GEMB_TUNE_GEMM_BN, 128 | 256)
 
 template <bool kFp4, int BN, int kStages, int kAccStages>
@@ -376,7 +466,7 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
   GEMB_TRY(make_out_map(op, &map_out, p.out, p.m, p.n));
   const uint32_t tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
   const unsigned grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(sm_count()));
-  kern<<<grid, kGemmThreads, C::kSmemBytes, stream>>>(map_a, map_b, map_out, p);
+  kern<<<grid, kFp4 ? kGemmThreadsFp4 : kGemmThreadsFp8, C::kSmemBytes, stream>>>(map_a, map_b, map_out, p);
   return check_launch(op);
 }
 
@@ -393,9 +483,13 @@ int32_t validate_gemm(const char* op, uint64_t tokens, uint64_t rows, uint64_t k
 
 int32_t gemm_set_tuning(int32_t knob, int32_t value) {
   if (knob == GEMB_TUNE_GEMM_BN) {
-    GEMB_REQUIRE(value == 0 || value == 128 || value == 256,
-                 "gemb_set_tuning: GEMM tile width must be 0 (auto), 128 or 256");
+    GEMB_REQUIRE(value == 0 || value == 128 || value == 192 || value == 256,
+                 "gemb_set_tuning: GEMM tile width must be 0 (auto), 128, 192 or 256");
     g_gemm_bn = value;
+    return GEMB_OK;
+  }
+  if (knob == 99) {
+    g_gemm_debug = value;
     return GEMB_OK;
   }
   return fail(GEMB_INVALID_ARGUMENT, "gemb_set_tuning: unknown knob %d", knob);
@@ -428,9 +522,11 @@ int32_t gemb_nvfp4_gemm_bf16(const uint8_t* act, const uint8_t* act_scales_inter
   p.m = static_cast<uint32_t>(tokens);
   p.n = static_cast<uint32_t>(rows);
   p.k = static_cast<uint32_t>(k);
+  p.debug = g_gemm_debug;
   p.alpha = 1.0f / (ga * gw);  // one multiply in the epilogue, as src/cuda/nvfp4/cutlass_sm120.cu:551-552
-  const int bn = g_gemm_bn ? g_gemm_bn : 256;
+  const int bn = g_gemm_bn ? g_gemm_bn : 256;  // 256 measured fastest; 192 and 128 stay selectable
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
+  if (bn == 192) return launch_gemm<true, 192, 4, 2>(op, act, w, p, stream);
   return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
 }
 
@@ -452,7 +548,8 @@ int32_t gemb_fp8_gemm_bf16(const uint8_t* act, const float* act_scales, const ui
   p.n = static_cast<uint32_t>(rows);
   p.k = static_cast<uint32_t>(k);
   p.alpha = 1.0f;
-  const int bn = g_gemm_bn ? g_gemm_bn : 256;
+  p.debug = g_gemm_debug;
+  const int bn = g_gemm_bn == 128 ? 128 : 256;
   if (bn == 128) return launch_gemm<false, 128, 6, 2>(op, act, w, p, stream);
   return launch_gemm<false, 256, 4, 2>(op, act, w, p, stream);
 }

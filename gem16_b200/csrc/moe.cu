@@ -1,0 +1,522 @@
+// Mixture-of-experts routing path: router logits, softmax / top-k / renormalise, histogram +
+// exclusive prefix + stable permutation of the (token, slot) assignments, quantise-and-dispatch
+// of expert inputs into the padded per-expert row layout the grouped GEMM consumes, and the
+// deterministic weighted combine.
+//
+// gem16 holds no MoE code; these kernels implement the record layouts and ordering rules of
+// docs/plans/gemma4-26b/specs/MOE_ROUTER_SPEC.md and MOE_PREFILL_KERNEL_SPEC.md.  Everything
+// that decides routing is computed with a fixed operation order out of IEEE add / mul / fma /
+// div only, so expert ids, weights, counts and the permutation are reproducible bit for bit.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace gemb {
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// Router logits: logits[t][e] = fma(x[t][H-1], w[e][H-1], ... fma(x[t][0], w[e][0], bias[e])),
+// one fp32 fma per k in ascending k.  CTA = 32 tokens x 128 experts, thread = 2 tokens x 8
+// experts, K walked in shared-memory tiles of 32.
+// ---------------------------------------------------------------------------------------------
+constexpr int kRtTok = 32, kRtExp = 128, kRtK = 32;
+
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
+                     const float* __restrict__ bias, float* __restrict__ logits, uint32_t tokens,
+                     uint32_t hidden, uint32_t experts) {
+  __shared__ float xs[kRtK][kRtTok + 1];
+  __shared__ __align__(16) float ws[kRtK][kRtExp + 4];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const uint32_t tok0 = blockIdx.x * kRtTok, exp0 = blockIdx.y * kRtExp;
+  float acc[2][8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t e = exp0 + tx * 8 + j;
+    const float b = (bias != nullptr && e < experts) ? __ldg(bias + e) : 0.0f;
+    acc[0][j] = b;
+    acc[1][j] = b;
+  }
+  for (uint32_t k0 = 0; k0 < hidden; k0 += kRtK) {
+    {  // X tile: 32 tokens x 32 k, thread -> (token, 4 consecutive k)
+      const int t = threadIdx.x >> 3, kc = (threadIdx.x & 7) * 4;
+      uint2 v = make_uint2(0, 0);
+      if (tok0 + t < tokens && k0 + kc < hidden)
+        v = __ldg(reinterpret_cast<const uint2*>(x + static_cast<uint64_t>(tok0 + t) * hidden + k0 + kc));
+      xs[kc + 0][t] = __uint_as_float(v.x << 16);
+      xs[kc + 1][t] = __uint_as_float(v.x & 0xFFFF0000u);
+      xs[kc + 2][t] = __uint_as_float(v.y << 16);
+      xs[kc + 3][t] = __uint_as_float(v.y & 0xFFFF0000u);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // W tile: 128 experts x 32 k
+      const int e = (threadIdx.x >> 3) + 32 * i, kc = (threadIdx.x & 7) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (exp0 + e < experts && k0 + kc < hidden)
+        v = __ldg(reinterpret_cast<const float4*>(w + static_cast<uint64_t>(exp0 + e) * hidden + k0 + kc));
+      ws[kc + 0][e] = v.x;
+      ws[kc + 1][e] = v.y;
+      ws[kc + 2][e] = v.z;
+      ws[kc + 3][e] = v.w;
+    }
+    __syncthreads();
+    const uint32_t kmax = min(static_cast<uint32_t>(kRtK), hidden - k0);
+#pragma unroll 8
+    for (uint32_t k = 0; k < kmax; ++k) {
+      const float x0 = xs[k][ty * 2], x1 = xs[k][ty * 2 + 1];
+      const float4 wa = *reinterpret_cast<const float4*>(&ws[k][tx * 8]);
+      const float4 wb = *reinterpret_cast<const float4*>(&ws[k][tx * 8 + 4]);
+      const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc[0][j] = fmaf(x0, wv[j], acc[0][j]);
+        acc[1][j] = fmaf(x1, wv[j], acc[1][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const uint32_t t = tok0 + ty * 2 + i;
+    if (t >= tokens) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t e = exp0 + tx * 8 + j;
+      if (e < experts) logits[static_cast<uint64_t>(t) * experts + e] = acc[i][j];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Softmax over all experts, top-k with the lower id winning ties, renormalise, optional
+// per-expert scale (MOE_ROUTER_SPEC.md:27-63).  One warp per token; lane l owns experts
+// l, l+32, ...  Reduction orders are part of the contract:
+//   max / sum: lane-local over the owned experts in ascending order, then an xor butterfly with
+//   strides 16, 8, 4, 2, 1; exp is the fma polynomial below; p = exp / sum; the selected sum
+//   adds the k probabilities in slot order; weight = p / selected_sum (* per_expert_scale).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float det_exp(float x) {
+  if (x < -87.0f) return 0.0f;
+  const float nf = rintf(__fmul_rn(x, 1.4426950408889634f));
+  float r = fmaf(nf, -0.693145751953125f, x);
+  r = fmaf(nf, -1.428606765330187e-06f, r);
+  float p = 1.9875691500e-4f;
+  p = fmaf(p, r, 1.3981999507e-3f);
+  p = fmaf(p, r, 8.3334519073e-3f);
+  p = fmaf(p, r, 4.1665795894e-2f);
+  p = fmaf(p, r, 1.6666665459e-1f);
+  p = fmaf(p, r, 5.0000001201e-1f);
+  const float r2 = __fmul_rn(r, r);
+  const float y = __fadd_rn(fmaf(p, r2, r), 1.0f);
+  const float scale = __uint_as_float(static_cast<uint32_t>(static_cast<int>(nf) + 127) << 23);
+  return __fmul_rn(y, scale);
+}
+
+constexpr int kMaxPerLane = 8;  // up to 256 experts
+
+__global__ void __launch_bounds__(128)
+route_kernel(const float* __restrict__ logits, const float* __restrict__ per_expert_scale,
+             int32_t* __restrict__ ids, float* __restrict__ weights, float* __restrict__ probs,
+             uint32_t tokens, uint32_t experts, uint32_t topk) {
+  const uint32_t t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  const int per_lane = static_cast<int>(experts / 32);
+  const float* lg = logits + static_cast<uint64_t>(t) * experts;
+  float p[kMaxPerLane];
+  float m = __ldg(lg + lane);
+  p[0] = m;
+#pragma unroll
+  for (int j = 1; j < kMaxPerLane; ++j) {
+    if (j < per_lane) {
+      p[j] = __ldg(lg + lane + 32 * j);
+      m = fmaxf(m, p[j]);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  float s = 0.0f;
+#pragma unroll
+  for (int j = 0; j < kMaxPerLane; ++j) {
+    if (j < per_lane) {
+      p[j] = det_exp(__fsub_rn(p[j], m));
+      s = j == 0 ? p[0] : __fadd_rn(s, p[j]);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xFFFFFFFFu, s, o));
+#pragma unroll
+  for (int j = 0; j < kMaxPerLane; ++j) {
+    if (j < per_lane) {
+      p[j] = __fdiv_rn(p[j], s);
+      if (probs) probs[static_cast<uint64_t>(t) * experts + lane + 32 * j] = p[j];
+    }
+  }
+  // k rounds of arg-max.  Taken entries are marked with -1 (probabilities are >= 0).
+  float sel_sum = 0.0f, my_w = 0.0f;
+  int my_id = 0;
+  for (uint32_t slot = 0; slot < topk; ++slot) {
+    float best = -1.0f;
+    int best_id = 0x7FFFFFFF;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      if (j < per_lane && p[j] > best) {  // ascending id, strict '>' keeps the lower id
+        best = p[j];
+        best_id = lane + 32 * j;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+      const int oi = __shfl_xor_sync(0xFFFFFFFFu, best_id, o);
+      if (ob > best || (ob == best && oi < best_id)) {
+        best = ob;
+        best_id = oi;
+      }
+    }
+    if ((best_id & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < kMaxPerLane; ++j)
+        if (j == (best_id >> 5)) p[j] = -1.0f;
+    }
+    sel_sum = slot == 0 ? best : __fadd_rn(sel_sum, best);
+    if (static_cast<uint32_t>(lane) == slot) {
+      my_w = best;
+      my_id = best_id;
+    }
+  }
+  if (static_cast<uint32_t>(lane) < topk) {
+    float wv = __fdiv_rn(my_w, sel_sum);
+    if (per_expert_scale) wv = __fmul_rn(wv, __ldg(per_expert_scale + my_id));
+    ids[static_cast<uint64_t>(t) * topk + lane] = my_id;
+    weights[static_cast<uint64_t>(t) * topk + lane] = wv;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Histogram, exclusive prefix and stable permutation (MOE_PREFILL_KERNEL_SPEC.md:34-58).
+// Assignment i = token * topk + slot.  Inside an expert the order is i ascending (token, then
+// slot).  Three launches, no atomics on global memory, no host readback:
+//   1. per segment of 1024 assignments: per-expert counts (block_counts[segment][expert]);
+//   2. one CTA: exclusive scan over segments per expert, counts, offsets, and the padded plan
+//      (every expert's rows start on a multiple of 128 so a GEMM tile never mixes experts);
+//   3. per segment: stable ranks from warp match masks, scatter perm[] and slot_rows[].
+// ---------------------------------------------------------------------------------------------
+constexpr int kSegment = 1024;  // assignments per CTA: 4 warps x 8 chunks x 32
+
+__global__ void __launch_bounds__(128)
+permute_count_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ block_counts,
+                     uint32_t total, uint32_t experts) {
+  extern __shared__ int smem_counts[];
+  for (uint32_t e = threadIdx.x; e < experts; e += 128) smem_counts[e] = 0;
+  __syncthreads();
+  const uint32_t base = blockIdx.x * kSegment;
+  for (uint32_t i = threadIdx.x; i < kSegment; i += 128)
+    if (base + i < total) atomicAdd(&smem_counts[__ldg(ids + base + i)], 1);
+  __syncthreads();
+  for (uint32_t e = threadIdx.x; e < experts; e += 128)
+    block_counts[static_cast<uint64_t>(blockIdx.x) * experts + e] = smem_counts[e];
+}
+
+// plan layout (int32): [0] number of 128-row tiles, [1] padded rows in total,
+// [2 .. 2+E] padded offset of every expert (+ the end), then tile_expert[tile].
+__global__ void __launch_bounds__(256)
+permute_scan_kernel(int32_t* __restrict__ block_counts, int32_t* __restrict__ counts,
+                    int32_t* __restrict__ offsets, int32_t* __restrict__ plan, uint32_t segments,
+                    uint32_t experts) {
+  extern __shared__ int sm[];
+  int* cnt = sm;                 // [experts]
+  int* off = sm + experts;       // [experts + 1]
+  int* poff = off + experts + 1; // [experts + 1]
+  for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
+    int run = 0;
+    for (uint32_t b = 0; b < segments; ++b) {
+      const int c = block_counts[static_cast<uint64_t>(b) * experts + e];
+      block_counts[static_cast<uint64_t>(b) * experts + e] = run;  // exclusive prefix over segments
+      run += c;
+    }
+    cnt[e] = run;
+    counts[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, po = 0;
+    for (uint32_t e = 0; e < experts; ++e) {
+      off[e] = o;
+      poff[e] = po;
+      o += cnt[e];
+      po += (cnt[e] + 127) / 128 * 128;
+    }
+    off[experts] = o;
+    poff[experts] = po;
+    plan[0] = po / 128;
+    plan[1] = po;
+  }
+  __syncthreads();
+  for (uint32_t e = threadIdx.x; e <= experts; e += blockDim.x) {
+    offsets[e] = off[e];
+    plan[2 + e] = poff[e];
+  }
+  int32_t* tile_expert = plan + 2 + experts + 1;
+  for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x)
+    for (int tile = poff[e] / 128; tile < poff[e + 1] / 128; ++tile) tile_expert[tile] = static_cast<int32_t>(e);
+}
+
+__global__ void __launch_bounds__(128)
+permute_scatter_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ block_prefix,
+                       const int32_t* __restrict__ offsets, const int32_t* __restrict__ plan,
+                       int32_t* __restrict__ perm, int32_t* __restrict__ slot_rows, uint32_t total,
+                       uint32_t experts) {
+  extern __shared__ int sm[];
+  int* warp_counts = sm;  // [4][experts], becomes each warp's running base
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (uint32_t i = threadIdx.x; i < 4 * experts; i += 128) warp_counts[i] = 0;
+  __syncthreads();
+  const uint32_t base = blockIdx.x * kSegment + warp * 256;
+  int my_ids[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint32_t i = base + c * 32 + lane;
+    my_ids[c] = i < total ? __ldg(ids + i) : -1;
+    if (my_ids[c] >= 0) atomicAdd(&warp_counts[warp * experts + my_ids[c]], 1);
+  }
+  __syncthreads();
+  // exclusive prefix over the four warps, plus the segment's own prefix
+  for (uint32_t e = threadIdx.x; e < experts; e += 128) {
+    int run = block_prefix[static_cast<uint64_t>(blockIdx.x) * experts + e];
+    for (int wq = 0; wq < 4; ++wq) {
+      const int c = warp_counts[wq * experts + e];
+      warp_counts[wq * experts + e] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  int* running = warp_counts + warp * experts;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int e = my_ids[c];
+    const unsigned active = __ballot_sync(0xFFFFFFFFu, e >= 0);
+    if (e >= 0) {
+      const unsigned peers = __match_any_sync(active, e);
+      const int rank = __popc(peers & ((1u << lane) - 1));
+      const int within = running[e] + rank;  // position inside the expert
+      const uint32_t i = base + c * 32 + lane;
+      perm[__ldg(offsets + e) + within] = static_cast<int32_t>(i);
+      slot_rows[i] = __ldg(plan + 2 + e) + within;
+      __syncwarp(active);
+      if (rank == 0) running[e] += __popc(peers);
+    }
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Quantise each token's expert input to NVFP4 once and write it to the padded row of every one
+// of its topk assignments, block scales in the interleaved layout of the padded row space.
+// One CTA per token, one thread per 16-element block.
+// ---------------------------------------------------------------------------------------------
+constexpr float kInvSix = 1.0f / 6.0f;
+
+__global__ void __launch_bounds__(256)
+dispatch_quantize_kernel(const uint16_t* __restrict__ x, const int32_t* __restrict__ slot_rows,
+                         uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, uint32_t hidden,
+                         uint32_t topk, float g, uint32_t c_pad) {
+  const uint32_t t = blockIdx.x;
+  __shared__ int rows[32];
+  if (threadIdx.x < topk) rows[threadIdx.x] = __ldg(slot_rows + static_cast<uint64_t>(t) * topk + threadIdx.x);
+  __syncthreads();
+  for (uint32_t c = threadIdx.x; c < hidden / 16; c += blockDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<uint64_t>(t) * hidden + c * 16);
+    const uint4 a = __ldg(src), b = __ldg(src + 1);
+    const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float v[16];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[2 * i] = __uint_as_float(ww[i] << 16);
+      v[2 * i + 1] = __uint_as_float(ww[i] & 0xFFFF0000u);
+      amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+    }
+    // Same arithmetic as the standalone NVFP4 quantizer (src/numeric/nvfp4.cpp:139-150).
+    const uint8_t sb = e4m3_encode(__fmul_rn(__fmul_rn(amax, kInvSix), g));
+    const float ds = e4m3_decode(sb);
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float n0 = ds == 0.0f ? 0.0f : __fdiv_rn(__fmul_rn(v[2 * i], g), ds);
+      const float n1 = ds == 0.0f ? 0.0f : __fdiv_rn(__fmul_rn(v[2 * i + 1], g), ds);
+      const float n2 = ds == 0.0f ? 0.0f : __fdiv_rn(__fmul_rn(v[8 + 2 * i], g), ds);
+      const float n3 = ds == 0.0f ? 0.0f : __fdiv_rn(__fmul_rn(v[8 + 2 * i + 1], g), ds);
+      lo |= static_cast<uint32_t>(e2m1x2_encode(n0, n1)) << (8 * i);
+      hi |= static_cast<uint32_t>(e2m1x2_encode(n2, n3)) << (8 * i);
+    }
+    for (uint32_t s = 0; s < topk; ++s) {
+      const uint64_t r = static_cast<uint64_t>(rows[s]);
+      *reinterpret_cast<uint2*>(packed + r * (hidden / 2) + c * 8) = make_uint2(lo, hi);
+      scales[interleaved_scale_offset(r, c, c_pad)] = sb;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Deterministic combine (MOE_SEMANTICS_SPEC.md:74-83): acc = 0; for slot 0..k-1:
+// acc = fma(weight[slot], y[row(slot)], acc); + shared branch; round to bf16.
+// One thread per 8 output columns.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+combine_kernel(const uint16_t* __restrict__ y, const int32_t* __restrict__ slot_rows,
+               const float* __restrict__ weights, const uint16_t* __restrict__ shared_out,
+               uint16_t* __restrict__ out, uint32_t tokens, uint32_t hidden, uint32_t topk) {
+  const uint32_t chunks = hidden / 8;
+  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<uint64_t>(tokens) * chunks) return;
+  const uint32_t t = static_cast<uint32_t>(idx / chunks), c = static_cast<uint32_t>(idx % chunks);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  for (uint32_t s = 0; s < topk; ++s) {
+    const float wv = __ldg(weights + static_cast<uint64_t>(t) * topk + s);
+    const int64_t r = __ldg(slot_rows + static_cast<uint64_t>(t) * topk + s);
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(y + r * hidden) + c);
+    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] = fmaf(wv, __uint_as_float(ww[i] << 16), acc[2 * i]);
+      acc[2 * i + 1] = fmaf(wv, __uint_as_float(ww[i] & 0xFFFF0000u), acc[2 * i + 1]);
+    }
+  }
+  if (shared_out) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(shared_out + static_cast<uint64_t>(t) * hidden) + c);
+    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] = __fadd_rn(acc[2 * i], __uint_as_float(ww[i] << 16));
+      acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __uint_as_float(ww[i] & 0xFFFF0000u));
+    }
+  }
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    o[i] = static_cast<uint32_t>(float_to_bf16_bits(acc[2 * i])) |
+           (static_cast<uint32_t>(float_to_bf16_bits(acc[2 * i + 1])) << 16);
+  reinterpret_cast<uint4*>(out + static_cast<uint64_t>(t) * hidden)[c] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+}  // namespace
+}  // namespace gemb
+
+using namespace gemb;
+
+namespace {
+uint64_t moe_segments(uint64_t tokens, uint64_t topk) { return (tokens * topk + kSegment - 1) / kSegment; }
+uint64_t moe_max_tiles(uint64_t tokens, uint64_t experts, uint64_t topk) { return tokens * topk / 128 + experts; }
+
+int32_t validate_moe_geometry(const char* op, uint64_t tokens, uint64_t experts, uint64_t topk) {
+  GEMB_REQUIRE(tokens > 0 && tokens * topk < (1ull << 31), "%s: token count must be nonzero and fit 31 bits", op);
+  GEMB_REQUIRE(experts >= 32 && experts % 32 == 0 && experts <= 256, "%s: experts must be a multiple of 32 in [32, 256]", op);
+  GEMB_REQUIRE(topk >= 1 && topk <= 32 && topk <= experts, "%s: top-k must be in [1, 32] and at most the expert count", op);
+  return GEMB_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int32_t gemb_moe_router_logits(const uint16_t* x_bf16, const float* router_weight, const float* bias,
+                               float* logits, uint64_t tokens, uint64_t hidden, uint64_t experts,
+                               gemb_stream_t stream) {
+  const char* op = "gemb_moe_router_logits";
+  GEMB_REQUIRE(x_bf16 && router_weight && logits, "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(tokens > 0 && tokens < (1ull << 31) && experts > 0 && experts < (1ull << 20), "%s: bad geometry", op);
+  GEMB_REQUIRE(hidden > 0 && hidden % 4 == 0 && hidden < (1ull << 31), "%s: hidden must be a nonzero multiple of 4", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(x_bf16) % 8 == 0 && reinterpret_cast<uintptr_t>(router_weight) % 16 == 0,
+               "%s: activations must be 8-byte and router weights 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  dim3 grid(static_cast<unsigned>((tokens + kRtTok - 1) / kRtTok), static_cast<unsigned>((experts + kRtExp - 1) / kRtExp));
+  router_logits_kernel<<<grid, 256, 0, stream>>>(x_bf16, router_weight, bias, logits, static_cast<uint32_t>(tokens),
+                                                 static_cast<uint32_t>(hidden), static_cast<uint32_t>(experts));
+  return check_launch(op);
+}
+
+int32_t gemb_moe_route(const float* logits, const float* per_expert_scale, int32_t* top_ids, float* top_weights,
+                       float* probabilities, uint64_t tokens, uint64_t experts, uint64_t topk,
+                       gemb_stream_t stream) {
+  const char* op = "gemb_moe_route";
+  GEMB_REQUIRE(logits && top_ids && top_weights, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_moe_geometry(op, tokens, experts, topk));
+  GEMB_TRY(require_sm100(op));
+  route_kernel<<<static_cast<unsigned>((tokens + 3) / 4), 128, 0, stream>>>(
+      logits, per_expert_scale, top_ids, top_weights, probabilities, static_cast<uint32_t>(tokens),
+      static_cast<uint32_t>(experts), static_cast<uint32_t>(topk));
+  return check_launch(op);
+}
+
+uint64_t gemb_moe_permute_workspace_bytes(uint64_t tokens, uint64_t experts, uint64_t topk) {
+  return moe_segments(tokens, topk) * experts * sizeof(int32_t);
+}
+uint64_t gemb_moe_plan_ints(uint64_t tokens, uint64_t experts, uint64_t topk) {
+  return 2 + experts + 1 + moe_max_tiles(tokens, experts, topk);
+}
+uint64_t gemb_moe_padded_rows_max(uint64_t tokens, uint64_t experts, uint64_t topk) {
+  return moe_max_tiles(tokens, experts, topk) * 128;
+}
+
+int32_t gemb_moe_permute(const int32_t* top_ids, int32_t* counts, int32_t* offsets, int32_t* perm,
+                         int32_t* slot_rows, int32_t* plan, void* workspace, uint64_t workspace_bytes,
+                         uint64_t tokens, uint64_t experts, uint64_t topk, gemb_stream_t stream) {
+  const char* op = "gemb_moe_permute";
+  GEMB_REQUIRE(top_ids && counts && offsets && perm && slot_rows && plan && workspace, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_moe_geometry(op, tokens, experts, topk));
+  GEMB_REQUIRE(workspace_bytes >= gemb_moe_permute_workspace_bytes(tokens, experts, topk),
+               "%s: workspace too small (%llu bytes needed)", op,
+               static_cast<unsigned long long>(gemb_moe_permute_workspace_bytes(tokens, experts, topk)));
+  GEMB_TRY(require_sm100(op));
+  const uint32_t total = static_cast<uint32_t>(tokens * topk), e = static_cast<uint32_t>(experts);
+  const uint32_t segments = static_cast<uint32_t>(moe_segments(tokens, topk));
+  int32_t* block_counts = static_cast<int32_t*>(workspace);
+  permute_count_kernel<<<segments, 128, e * sizeof(int), stream>>>(top_ids, block_counts, total, e);
+  GEMB_TRY(check_launch(op));
+  permute_scan_kernel<<<1, 256, (3 * e + 2) * sizeof(int), stream>>>(block_counts, counts, offsets, plan, segments, e);
+  GEMB_TRY(check_launch(op));
+  permute_scatter_kernel<<<segments, 128, 4 * e * sizeof(int), stream>>>(top_ids, block_counts, offsets, plan, perm,
+                                                                        slot_rows, total, e);
+  return check_launch(op);
+}
+
+int32_t gemb_moe_dispatch_quantize(const uint16_t* x_bf16, const int32_t* slot_rows, uint8_t* packed_e2m1,
+                                   uint8_t* interleaved_scales, uint64_t tokens, uint64_t hidden, uint64_t topk,
+                                   float global_divisor, gemb_stream_t stream) {
+  const char* op = "gemb_moe_dispatch_quantize";
+  GEMB_REQUIRE(x_bf16 && slot_rows && packed_e2m1 && interleaved_scales, "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(tokens > 0 && tokens < (1ull << 31) && topk >= 1 && topk <= 32, "%s: bad geometry", op);
+  GEMB_REQUIRE(hidden > 0 && hidden % 16 == 0 && hidden < (1ull << 31), "%s: hidden must be a nonzero multiple of 16", op);
+  GEMB_REQUIRE(positive_finite(global_divisor), "%s: global divisor must be positive and finite", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(x_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(packed_e2m1) % 8 == 0,
+               "%s: input must be 16-byte and payload 8-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  const uint32_t c_pad = static_cast<uint32_t>((hidden / 16 + 3) / 4 * 4);
+  const unsigned threads = static_cast<unsigned>(std::min<uint64_t>(256, (hidden / 16 + 31) / 32 * 32));
+  dispatch_quantize_kernel<<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
+      x_bf16, slot_rows, packed_e2m1, interleaved_scales, static_cast<uint32_t>(hidden), static_cast<uint32_t>(topk),
+      global_divisor, c_pad);
+  return check_launch(op);
+}
+
+int32_t gemb_moe_combine(const uint16_t* y_bf16, const int32_t* slot_rows, const float* top_weights,
+                         const uint16_t* shared_bf16, uint16_t* out_bf16, uint64_t tokens, uint64_t hidden,
+                         uint64_t topk, gemb_stream_t stream) {
+  const char* op = "gemb_moe_combine";
+  GEMB_REQUIRE(y_bf16 && slot_rows && top_weights && out_bf16, "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(tokens > 0 && tokens < (1ull << 31) && topk >= 1 && topk <= 32, "%s: bad geometry", op);
+  GEMB_REQUIRE(hidden > 0 && hidden % 8 == 0 && hidden < (1ull << 31), "%s: hidden must be a nonzero multiple of 8", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(y_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(out_bf16) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(shared_bf16) % 16 == 0,
+               "%s: buffers must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  const uint64_t work = tokens * (hidden / 8);
+  combine_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+      y_bf16, slot_rows, top_weights, shared_bf16, out_bf16, static_cast<uint32_t>(tokens),
+      static_cast<uint32_t>(hidden), static_cast<uint32_t>(topk));
+  return check_launch(op);
+}
+
+}  // extern "C"

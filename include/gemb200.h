@@ -216,6 +216,64 @@ int32_t gemb_fp8_gemm_bf16(const uint8_t* activation_e4m3fn, const float* activa
                            uint16_t* output_bf16, uint64_t tokens, uint64_t rows,
                            uint64_t contracting_elements, gemb_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Mixture-of-experts path.  gem16 holds no MoE code yet: the entry points implement the records
+ * and ordering rules its specifications define, at the places its plan reserves for them
+ * (src/cuda/moe/router_reference.cu, prefill_{router,permute,reduce}.cu,
+ * docs/plans/gemma4-26b/milestones/M11_CUDA_MOE_REFERENCE.md:26-45, M15_GROUPED_MOE_PREFILL.md:27-33).
+ * Stages are separate observable launches; nothing is read back to the host between them.
+ * ---------------------------------------------------------------------------------------- */
+
+/* logits[t][e] = bias[e] + sum_k x[t][k] * w[e][k], fp32, exactly one fused multiply-add per k
+ * in ascending k (bias may be null = 0).  x is bf16 [tokens, hidden], w fp32 [experts, hidden].
+ * docs/plans/gemma4-26b/specs/MOE_ROUTER_SPEC.md:3-13 (projection), :27-38 (fp32, deterministic). */
+int32_t gemb_moe_router_logits(const uint16_t* x_bf16, const float* router_weight, const float* bias,
+                               float* logits, uint64_t tokens, uint64_t hidden, uint64_t experts,
+                               gemb_stream_t stream);
+
+/* fp32 softmax over all experts, the topk largest probabilities (the lower expert id wins a
+ * tie), renormalised to sum one, then multiplied by per_expert_scale[id] when it is non-null.
+ * Outputs RoutedExperts records as two arrays: top_ids[tokens, topk] int32 and
+ * top_weights[tokens, topk] fp32; probabilities[tokens, experts] is optional (null to skip).
+ * experts % 32 == 0, experts <= 256, topk <= 32.
+ * docs/plans/gemma4-26b/specs/MOE_ROUTER_SPEC.md:27-73. */
+int32_t gemb_moe_route(const float* logits, const float* per_expert_scale, int32_t* top_ids,
+                       float* top_weights, float* probabilities, uint64_t tokens, uint64_t experts,
+                       uint64_t topk, gemb_stream_t stream);
+
+/* Sizes for gemb_moe_permute: scratch bytes, int32 entries of `plan`, and the upper bound of
+ * padded rows (every expert's rows start on a multiple of 128) that dispatch / grouped GEMM /
+ * combine buffers must hold. */
+uint64_t gemb_moe_permute_workspace_bytes(uint64_t tokens, uint64_t experts, uint64_t topk);
+uint64_t gemb_moe_plan_ints(uint64_t tokens, uint64_t experts, uint64_t topk);
+uint64_t gemb_moe_padded_rows_max(uint64_t tokens, uint64_t experts, uint64_t topk);
+
+/* Histogram(experts) -> exclusive prefix(experts + 1) -> stable permutation of the tokens*topk
+ * assignments (assignment i = token * topk + slot; inside an expert i ascends).
+ *   counts[experts], offsets[experts + 1], perm[tokens * topk] (perm[pos] = i)   -- the spec's
+ *   records;  slot_rows[i] = row of assignment i in the padded per-expert row space;
+ *   plan = {tiles, padded rows, padded_offsets[experts + 1], tile_expert[tiles]} consumed on
+ *   the device by the grouped GEMM (no host readback).
+ * docs/plans/gemma4-26b/specs/MOE_PREFILL_KERNEL_SPEC.md:19-58. */
+int32_t gemb_moe_permute(const int32_t* top_ids, int32_t* counts, int32_t* offsets, int32_t* perm,
+                         int32_t* slot_rows, int32_t* plan, void* workspace, uint64_t workspace_bytes,
+                         uint64_t tokens, uint64_t experts, uint64_t topk, gemb_stream_t stream);
+
+/* NVFP4-quantises each token's expert input once (EXACT contract) and writes payload and
+ * INTERLEAVED block scales to the padded row of each of its topk assignments.
+ * "activation + W2 input quantization" boundary of MOE_PREFILL_KERNEL_SPEC.md:34-47. */
+int32_t gemb_moe_dispatch_quantize(const uint16_t* x_bf16, const int32_t* slot_rows,
+                                   uint8_t* packed_e2m1, uint8_t* interleaved_scales,
+                                   uint64_t tokens, uint64_t hidden, uint64_t topk,
+                                   float global_divisor, gemb_stream_t stream);
+
+/* out[t] = bf16( sum over slots in slot order of fma(weight[t][slot], y[slot_rows[t*topk+slot]])
+ *                + shared[t] ), fp32 accumulation, no atomics; shared may be null.
+ * docs/plans/gemma4-26b/specs/MOE_SEMANTICS_SPEC.md:74-83. */
+int32_t gemb_moe_combine(const uint16_t* y_bf16, const int32_t* slot_rows, const float* top_weights,
+                         const uint16_t* shared_bf16, uint16_t* out_bf16, uint64_t tokens,
+                         uint64_t hidden, uint64_t topk, gemb_stream_t stream);
+
 /* Synchronises the device and reports whether a GEMM kernel gave up on a bounded pipeline wait
  * since the last call (GEMB_INTERNAL, flag cleared) or not (GEMB_OK).  The reference has no
  * counterpart: its kernels have no device-side waits. */
