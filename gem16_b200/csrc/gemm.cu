@@ -59,6 +59,12 @@ struct GemmParams {
   uint16_t* out;                 // bf16 [M, N]
   uint32_t m, n, k;              // k in elements
   float alpha;                   // NVFP4: 1 / (ga * gw)
+  // Grouped (mixture-of-experts) mode when plan != null: token tiles come from the device-side
+  // plan (plan[0] tiles, tile_expert at plan + 3 + experts), the weight is [experts, n, K].
+  const int32_t* plan;
+  const float* w_divisors;       // per-expert weight global divisors (null: alpha is used)
+  float ga;                      // activation global divisor (with w_divisors)
+  uint32_t experts;
   uint32_t debug;                // bit 0: skip loads, bit 1: skip MMAs, bit 2: skip epilogue (experiments only)
 };
 
@@ -143,7 +149,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  const uint32_t m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
+  const uint32_t m_tiles = p.plan ? static_cast<uint32_t>(__ldg(p.plan)) : (p.m + BM - 1) / BM;
+  const uint32_t n_tiles = (p.n + BN - 1) / BN;
+  const int32_t* tile_expert = p.plan ? p.plan + 3 + p.experts : nullptr;
   const uint32_t num_tiles = m_tiles * n_tiles;
   const uint32_t k_stages = (p.k + C::kKPerStage - 1) / C::kKPerStage;
   const uint32_t k_groups_pad = (p.k / 16 + 3) / 4;  // 512-byte scale chunks per 128-row group
@@ -173,6 +181,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       for (uint32_t tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
         uint32_t mt, nt;
         tile_coords(tile, mt, nt);
+        const uint32_t expert = tile_expert ? static_cast<uint32_t>(__ldg(tile_expert + mt)) : 0u;
         for (uint32_t ks = 0; ks < k_stages; ++ks) {
           if (!ptx::mbar_wait(&empty[stage], phase ^ 1)) { fail_wait(1); break; }
           const uint32_t k0 = ks * C::kKPerStage;
@@ -184,7 +193,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             continue;
           }
           if constexpr (kFp4) {
-            const uint32_t g0 = (nt * BN) / 128, total_groups = (p.n + 127) / 128;
+            const uint32_t groups_per_matrix = (p.n + 127) / 128;
+            const uint32_t g0 = expert * groups_per_matrix + (nt * BN) / 128;
+            const uint32_t total_groups = groups_per_matrix * (tile_expert ? p.experts : 1u);
             const uint32_t n_groups = min(static_cast<uint32_t>(C::kSfbGroups), total_groups - g0);
             bytes += n_mma * 512 * (1 + n_groups);
             ptx::mbar_expect_tx(&full[stage], bytes);
@@ -201,7 +212,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           ptx::tma_load_2d(stage_a + stage * C::kABytes, &map_a, &full[stage], static_cast<int32_t>(ks * 128),
                            static_cast<int32_t>(mt * BM));
           ptx::tma_load_2d(stage_b + stage * C::kBBytes, &map_b, &full[stage], static_cast<int32_t>(ks * 128),
-                           static_cast<int32_t>(nt * BN));
+                           static_cast<int32_t>(expert * p.n + nt * BN));
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -313,6 +324,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const uint32_t row0 = mt * BM + quarter * 32;
       float row_scale = p.alpha;
       if constexpr (!kFp4) row_scale = row0 + lane < p.m ? __ldg(p.a_scales + row0 + lane) : 0.0f;
+      if (kFp4 && p.w_divisors != nullptr)
+        row_scale = __fdiv_rn(1.0f, __fmul_rn(p.ga, __ldg(p.w_divisors + (tile_expert ? __ldg(tile_expert + mt) : 0))));
       const uint32_t tmem_acc = tmem_base + as * BN + ((quarter * 32) << 16);
 #pragma unroll 1
       for (uint32_t c = 0; c < BN / 64; ++c) {
@@ -462,7 +475,7 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
   const uint64_t row_bytes = kFp4 ? p.k / 2 : p.k;
   CUtensorMap map_a, map_b, map_out;
   GEMB_TRY(make_byte_map(op, &map_a, a, p.m, row_bytes, BM));
-  GEMB_TRY(make_byte_map(op, &map_b, b, p.n, row_bytes, BN));
+  GEMB_TRY(make_byte_map(op, &map_b, b, static_cast<uint64_t>(p.n) * (p.plan ? p.experts : 1u), row_bytes, BN));
   GEMB_TRY(make_out_map(op, &map_out, p.out, p.m, p.n));
   const uint32_t tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
   const unsigned grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(sm_count()));
@@ -525,6 +538,43 @@ int32_t gemb_nvfp4_gemm_bf16(const uint8_t* act, const uint8_t* act_scales_inter
   p.debug = g_gemm_debug;
   p.alpha = 1.0f / (ga * gw);  // one multiply in the epilogue, as src/cuda/nvfp4/cutlass_sm120.cu:551-552
   const int bn = g_gemm_bn ? g_gemm_bn : 256;  // 256 measured fastest; 192 and 128 stay selectable
+  if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
+  if (bn == 192) return launch_gemm<true, 192, 4, 2>(op, act, w, p, stream);
+  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
+}
+
+int32_t gemb_moe_grouped_gemm_bf16(const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* w,
+                                   const uint8_t* w_scales_interleaved, uint16_t* out, const int32_t* plan,
+                                   uint64_t padded_rows_max, uint64_t experts, uint64_t rows_per_expert,
+                                   uint64_t k, float ga, const float* w_divisors, gemb_stream_t stream) {
+  const char* op = "gemb_moe_grouped_gemm_bf16";
+  GEMB_REQUIRE(act && act_scales_interleaved && w && w_scales_interleaved && out && plan && w_divisors,
+               "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_gemm(op, padded_rows_max, rows_per_expert, k, 64));
+  GEMB_REQUIRE(padded_rows_max % 128 == 0, "%s: padded row capacity must be a multiple of 128", op);
+  GEMB_REQUIRE(rows_per_expert % 128 == 0, "%s: rows per expert must be a multiple of 128", op);
+  GEMB_REQUIRE(experts > 0 && experts <= 4096 && experts * rows_per_expert < (1ull << 31), "%s: bad expert count", op);
+  GEMB_REQUIRE(positive_finite(ga), "%s: activation global divisor must be positive and finite", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(act_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(w_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % 16 == 0,
+               "%s: all buffers must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  GemmParams p{};
+  p.sfa = act_scales_interleaved;
+  p.sfb = w_scales_interleaved;
+  p.out = out;
+  p.m = static_cast<uint32_t>(padded_rows_max);
+  p.n = static_cast<uint32_t>(rows_per_expert);
+  p.k = static_cast<uint32_t>(k);
+  p.plan = plan;
+  p.w_divisors = w_divisors;
+  p.ga = ga;
+  p.experts = static_cast<uint32_t>(experts);
+  p.debug = g_gemm_debug;
+  p.alpha = 1.0f;
+  const int bn = g_gemm_bn ? g_gemm_bn : 256;
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
   if (bn == 192) return launch_gemm<true, 192, 4, 2>(op, act, w, p, stream);
   return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);

@@ -315,8 +315,6 @@ permute_scatter_kernel(const int32_t* __restrict__ ids, const int32_t* __restric
 // of its topk assignments, block scales in the interleaved layout of the padded row space.
 // One CTA per token, one thread per 16-element block.
 // ---------------------------------------------------------------------------------------------
-constexpr float kInvSix = 1.0f / 6.0f;
-
 __global__ void __launch_bounds__(256)
 dispatch_quantize_kernel(const uint16_t* __restrict__ x, const int32_t* __restrict__ slot_rows,
                          uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, uint32_t hidden,
@@ -330,32 +328,57 @@ dispatch_quantize_kernel(const uint16_t* __restrict__ x, const int32_t* __restri
     const uint4 a = __ldg(src), b = __ldg(src + 1);
     const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     float v[16];
-    float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       v[2 * i] = __uint_as_float(ww[i] << 16);
       v[2 * i + 1] = __uint_as_float(ww[i] & 0xFFFF0000u);
-      amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
     }
     // Same arithmetic as the standalone NVFP4 quantizer (src/numeric/nvfp4.cpp:139-150).
-    const uint8_t sb = e4m3_encode(__fmul_rn(__fmul_rn(amax, kInvSix), g));
-    const float ds = e4m3_decode(sb);
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float n0 = ds == 0.0f ? 0.0f : __fdiv_rn(__fmul_rn(v[2 * i], g), ds);
-      const float n1 = ds == 0.0f ? 0.0f : __fdiv_rn(__fmul_rn(v[2 * i + 1], g), ds);
-      const float n2 = ds == 0.0f ? 0.0f : __fdiv_rn(__fmul_rn(v[8 + 2 * i], g), ds);
-      const float n3 = ds == 0.0f ? 0.0f : __fdiv_rn(__fmul_rn(v[8 + 2 * i + 1], g), ds);
-      lo |= static_cast<uint32_t>(e2m1x2_encode(n0, n1)) << (8 * i);
-      hi |= static_cast<uint32_t>(e2m1x2_encode(n2, n3)) << (8 * i);
-    }
+    uint32_t lo, hi;
+    uint8_t sb;
+    quantize_block16<false>(v, g, lo, hi, sb);
     for (uint32_t s = 0; s < topk; ++s) {
       const uint64_t r = static_cast<uint64_t>(rows[s]);
       *reinterpret_cast<uint2*>(packed + r * (hidden / 2) + c * 8) = make_uint2(lo, hi);
       scales[interleaved_scale_offset(r, c, c_pad)] = sb;
     }
   }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Expert activation boundary on the padded rows: gate_up is bf16 [rows, 2*inter] with the gate
+// in the first `inter` columns (the fused gate_up projection's chunk(2) order); product =
+// bf16(bf16(gelu_tanh(gate)) * up) is NVFP4-quantised with the down projection's input divisor
+// (boundaries of src/cuda/nvfp4/reference.cu:177-217).  Rows at or past plan[1] are skipped.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+expert_gelu_quantize_kernel(const uint16_t* __restrict__ gate_up, const int32_t* __restrict__ plan,
+                            uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, uint32_t rows_max,
+                            uint32_t inter, float g, uint32_t c_pad) {
+  const uint32_t blocks_per_row = inter / 16;
+  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const uint32_t rows = plan ? min(rows_max, static_cast<uint32_t>(__ldg(plan + 1))) : rows_max;
+  if (idx >= static_cast<uint64_t>(rows) * blocks_per_row) return;
+  const uint32_t r = static_cast<uint32_t>(idx / blocks_per_row), c = static_cast<uint32_t>(idx % blocks_per_row);
+  const uint16_t* gp = gate_up + static_cast<uint64_t>(r) * 2 * inter + c * 16;
+  const uint4 ga = __ldg(reinterpret_cast<const uint4*>(gp)), gb = __ldg(reinterpret_cast<const uint4*>(gp) + 1);
+  const uint4 ua = __ldg(reinterpret_cast<const uint4*>(gp + inter)), ub = __ldg(reinterpret_cast<const uint4*>(gp + inter) + 1);
+  const uint32_t gw[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+  const uint32_t uw[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float gv = __uint_as_float((i & 1) ? (gw[i >> 1] & 0xFFFF0000u) : (gw[i >> 1] << 16));
+    const float uv = __uint_as_float((i & 1) ? (uw[i >> 1] & 0xFFFF0000u) : (uw[i >> 1] << 16));
+    const float inner = 0.7978845608028654f * (gv + 0.044715f * gv * gv * gv);
+    const float gelu = bf16_round(0.5f * gv * (1.0f + tanhf(inner)));
+    v[i] = bf16_round(gelu * uv);
+  }
+  uint32_t lo, hi;
+  uint8_t sb;
+  quantize_block16<false>(v, g, lo, hi, sb);
+  *reinterpret_cast<uint2*>(packed + static_cast<uint64_t>(r) * (inter / 2) + c * 8) = make_uint2(lo, hi);
+  scales[interleaved_scale_offset(r, c, c_pad)] = sb;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -498,6 +521,26 @@ int32_t gemb_moe_dispatch_quantize(const uint16_t* x_bf16, const int32_t* slot_r
   dispatch_quantize_kernel<<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
       x_bf16, slot_rows, packed_e2m1, interleaved_scales, static_cast<uint32_t>(hidden), static_cast<uint32_t>(topk),
       global_divisor, c_pad);
+  return check_launch(op);
+}
+
+int32_t gemb_moe_expert_gelu_quantize(const uint16_t* gate_up_bf16, const int32_t* plan, uint8_t* packed_e2m1,
+                                      uint8_t* interleaved_scales, uint64_t rows_max, uint64_t intermediate,
+                                      float global_divisor, gemb_stream_t stream) {
+  const char* op = "gemb_moe_expert_gelu_quantize";
+  GEMB_REQUIRE(gate_up_bf16 && packed_e2m1 && interleaved_scales, "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(rows_max > 0 && rows_max < (1ull << 31), "%s: bad row count", op);
+  GEMB_REQUIRE(intermediate > 0 && intermediate % 16 == 0 && intermediate < (1ull << 30),
+               "%s: intermediate size must be a nonzero multiple of 16", op);
+  GEMB_REQUIRE(positive_finite(global_divisor), "%s: global divisor must be positive and finite", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(gate_up_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(packed_e2m1) % 8 == 0,
+               "%s: input must be 16-byte and payload 8-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  const uint64_t work = rows_max * (intermediate / 16);
+  const uint32_t c_pad = static_cast<uint32_t>((intermediate / 16 + 3) / 4 * 4);
+  expert_gelu_quantize_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+      gate_up_bf16, plan, packed_e2m1, interleaved_scales, static_cast<uint32_t>(rows_max),
+      static_cast<uint32_t>(intermediate), global_divisor, c_pad);
   return check_launch(op);
 }
 

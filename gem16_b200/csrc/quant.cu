@@ -9,40 +9,8 @@
 namespace gemb {
 namespace {
 
-constexpr float kInvSix = 1.0f / 6.0f;  // kE2M1MaxReciprocal, src/numeric/nvfp4.cpp:16
 constexpr float kSqrtTwoOverPi = 0.7978845608028654f;
 constexpr float kGeluCubic = 0.044715f;
-
-// Quantizes 16 values into 8 packed bytes (returned as two 32-bit words) and one scale byte.
-// EXACT follows src/numeric/nvfp4.cpp:139-150, RCP_APPROX follows
-// src/cuda/nvfp4/reference.cu:60-78.  Explicit _rn intrinsics keep the compiler from fusing
-// the multiplies into fma, which would change the rounding.
-template <bool kRcp>
-__device__ __forceinline__ void quantize_block16(const float (&v)[16], float g, uint32_t& lo,
-                                                 uint32_t& hi, uint8_t& scale_bits) {
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  float n[16];
-  if constexpr (kRcp) {
-    scale_bits = e4m3_encode(__fmul_rn(__fmul_rn(amax, rcp_approx_ftz(6.0f)), g));
-    const float ds = e4m3_decode(scale_bits);
-    const float os = ds == 0.0f ? 0.0f : rcp_approx_ftz(__fmul_rn(ds, rcp_approx_ftz(g)));
-#pragma unroll
-    for (int i = 0; i < 16; ++i) n[i] = __fmul_rn(v[i], os);
-  } else {
-    scale_bits = e4m3_encode(__fmul_rn(__fmul_rn(amax, kInvSix), g));
-    const float ds = e4m3_decode(scale_bits);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) n[i] = ds == 0.0f ? 0.0f : __fdiv_rn(__fmul_rn(v[i], g), ds);
-  }
-  lo = hi = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    lo |= static_cast<uint32_t>(e2m1x2_encode(n[2 * i], n[2 * i + 1])) << (8 * i);
-    hi |= static_cast<uint32_t>(e2m1x2_encode(n[8 + 2 * i], n[8 + 2 * i + 1])) << (8 * i);
-  }
-}
 
 __device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
   const float4* q = reinterpret_cast<const float4*>(p);

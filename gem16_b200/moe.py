@@ -1,0 +1,128 @@
+"""Host-side sequencing of one MoE layer over the C ABI (torch only allocates device buffers).
+
+Mirrors the stage order of docs/plans/gemma4-26b/specs/MOE_PREFILL_KERNEL_SPEC.md:34-47:
+router -> assignments -> histogram -> prefix -> stable permutation -> grouped gate_up ->
+activation + requantisation -> grouped down -> deterministic weighted reduction (+ shared
+branch).  Every stage is a separate observable launch on one stream; nothing is read back.
+"""
+from __future__ import annotations
+
+import torch
+
+from .lib import load
+
+
+class MoeWeights:
+    """Device-resident NVFP4 expert weights in the layout the grouped GEMM consumes."""
+
+    def __init__(self, lib, dev, router_w, router_bias, gu_packed, gu_scales, gu_div, dn_packed, dn_scales, dn_div,
+                 shared=None):
+        self.dev = dev
+        self.experts, self.two_inter, half_h = gu_packed.shape
+        self.hidden, self.inter = half_h * 2, self.two_inter // 2
+        self.router_w = torch.as_tensor(router_w, device=dev).contiguous()
+        self.router_bias = None if router_bias is None else torch.as_tensor(router_bias, device=dev).contiguous()
+        self.gu_packed = torch.as_tensor(gu_packed, device=dev).contiguous()
+        self.dn_packed = torch.as_tensor(dn_packed, device=dev).contiguous()
+        self.gu_div = torch.as_tensor(gu_div, device=dev, dtype=torch.float32).contiguous()
+        self.dn_div = torch.as_tensor(dn_div, device=dev, dtype=torch.float32).contiguous()
+        self.gu_scales = self._interleave(lib, gu_scales, self.two_inter, self.hidden)
+        self.dn_scales = self._interleave(lib, dn_scales, self.hidden, self.inter)
+        self.shared = None
+        if shared is not None:
+            (sg_p, sg_s, sg_d), (sd_p, sd_s, sd_d) = shared
+            self.shared = {
+                "gu_packed": torch.as_tensor(sg_p, device=dev).contiguous(), "gu_div": float(sg_d),
+                "gu_scales": self._interleave(lib, sg_s[None], sg_p.shape[0], self.hidden),
+                "dn_packed": torch.as_tensor(sd_p, device=dev).contiguous(), "dn_div": float(sd_d),
+                "dn_scales": self._interleave(lib, sd_s[None], self.hidden, sd_p.shape[1] * 2),
+                "inter": sg_p.shape[0] // 2,
+            }
+
+    def _interleave(self, lib, compact, rows, k):
+        compact = torch.as_tensor(compact, device=self.dev).contiguous()
+        per = lib.cdll.gemb_interleaved_scale_bytes(rows, k)
+        out = torch.empty((compact.shape[0], per), dtype=torch.uint8, device=self.dev)
+        for e in range(compact.shape[0]):
+            lib.gemb_nvfp4_interleave_scales(compact[e], out[e], rows, k, None)
+        return out
+
+
+class MoeLayer:
+    """Preallocated buffers + the launch sequence for `tokens` tokens."""
+
+    def __init__(self, weights: MoeWeights, tokens: int, topk: int, ga: float, ga_dn: float, ga_sh_dn: float = 1.0):
+        self.lib = load()
+        self.w, self.tokens, self.topk = weights, tokens, topk
+        self.ga, self.ga_dn, self.ga_sh_dn = ga, ga_dn, ga_sh_dn
+        lib, dev, w = self.lib, weights.dev, weights
+        e, h, i = w.experts, w.hidden, w.inter
+        c = lib.cdll
+        self.rows_max = c.gemb_moe_padded_rows_max(tokens, e, topk)
+        i32 = dict(dtype=torch.int32, device=dev)
+        u8 = dict(dtype=torch.uint8, device=dev)
+        self.logits = torch.empty((tokens, e), device=dev)
+        self.ids = torch.empty((tokens, topk), **i32)
+        self.weights = torch.empty((tokens, topk), device=dev)
+        self.counts = torch.empty((e,), **i32)
+        self.offsets = torch.empty((e + 1,), **i32)
+        self.perm = torch.empty((tokens * topk,), **i32)
+        self.slot_rows = torch.empty((tokens * topk,), **i32)
+        self.plan = torch.zeros((c.gemb_moe_plan_ints(tokens, e, topk),), **i32)
+        self.workspace = torch.empty((c.gemb_moe_permute_workspace_bytes(tokens, e, topk),), **u8)
+        self.a_packed = torch.zeros((self.rows_max, h // 2), **u8)
+        self.a_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, h),), **u8)
+        self.gate_up = torch.empty((self.rows_max, 2 * i), dtype=torch.int16, device=dev)
+        self.p_packed = torch.zeros((self.rows_max, i // 2), **u8)
+        self.p_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, i),), **u8)
+        self.y = torch.empty((self.rows_max, h), dtype=torch.int16, device=dev)
+        self.out = torch.empty((tokens, h), dtype=torch.int16, device=dev)
+        if w.shared is not None:
+            si = w.shared["inter"]
+            self.s_packed = torch.empty((tokens, h // 2), **u8)
+            self.s_scales = torch.zeros((c.gemb_interleaved_scale_bytes(tokens, h),), **u8)
+            self.s_gate_up = torch.empty((tokens, 2 * si), dtype=torch.int16, device=dev)
+            self.s_p_packed = torch.empty((tokens, si // 2), **u8)
+            self.s_p_scales = torch.zeros((c.gemb_interleaved_scale_bytes(tokens, si),), **u8)
+            self.s_out = torch.empty((tokens, h), dtype=torch.int16, device=dev)
+
+    def route(self, x_bf16, stream=None):
+        lib, w, t = self.lib, self.w, self.tokens
+        lib.gemb_moe_router_logits(x_bf16, w.router_w, w.router_bias, self.logits, t, w.hidden, w.experts, stream)
+        lib.gemb_moe_route(self.logits, None, self.ids, self.weights, None, t, w.experts, self.topk, stream)
+        lib.gemb_moe_permute(self.ids, self.counts, self.offsets, self.perm, self.slot_rows, self.plan, self.workspace,
+                             self.workspace.numel(), t, w.experts, self.topk, stream)
+
+    def experts(self, x_bf16, stream=None):
+        lib, w, t = self.lib, self.w, self.tokens
+        lib.gemb_moe_dispatch_quantize(x_bf16, self.slot_rows, self.a_packed, self.a_scales, t, w.hidden, self.topk,
+                                       self.ga, stream)
+        lib.gemb_moe_grouped_gemm_bf16(self.a_packed, self.a_scales, w.gu_packed, w.gu_scales, self.gate_up, self.plan,
+                                       self.rows_max, w.experts, 2 * w.inter, w.hidden, self.ga, w.gu_div, stream)
+        lib.gemb_moe_expert_gelu_quantize(self.gate_up, self.plan, self.p_packed, self.p_scales, self.rows_max, w.inter,
+                                          self.ga_dn, stream)
+        lib.gemb_moe_grouped_gemm_bf16(self.p_packed, self.p_scales, w.dn_packed, w.dn_scales, self.y, self.plan,
+                                       self.rows_max, w.experts, w.hidden, w.inter, self.ga_dn, w.dn_div, stream)
+
+    def shared_branch(self, x_bf16, stream=None):
+        lib, w, t, s = self.lib, self.w, self.tokens, self.w.shared
+        lib.gemb_nvfp4_quantize(x_bf16, 1, self.s_packed, self.s_scales, t, w.hidden, self.ga, 1, 0, stream)
+        lib.gemb_nvfp4_gemm_bf16(self.s_packed, self.s_scales, s["gu_packed"], s["gu_scales"], self.s_gate_up, t,
+                                 2 * s["inter"], w.hidden, self.ga, s["gu_div"], stream)
+        lib.gemb_moe_expert_gelu_quantize(self.s_gate_up, None, self.s_p_packed, self.s_p_scales, t, s["inter"],
+                                          self.ga_sh_dn, stream)
+        lib.gemb_nvfp4_gemm_bf16(self.s_p_packed, self.s_p_scales, s["dn_packed"], s["dn_scales"], self.s_out, t,
+                                 w.hidden, s["inter"], self.ga_sh_dn, s["dn_div"], stream)
+
+    def combine(self, stream=None):
+        shared = self.s_out if self.w.shared is not None else None
+        self.lib.gemb_moe_combine(self.y, self.slot_rows, self.weights, shared, self.out, self.tokens, self.w.hidden,
+                                  self.topk, stream)
+
+    def forward(self, x_bf16, stream=None):
+        self.route(x_bf16, stream)
+        self.experts(x_bf16, stream)
+        if self.w.shared is not None:
+            self.shared_branch(x_bf16, stream)
+        self.combine(stream)
+        return self.out

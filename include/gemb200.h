@@ -267,6 +267,33 @@ int32_t gemb_moe_dispatch_quantize(const uint16_t* x_bf16, const int32_t* slot_r
                                    uint64_t tokens, uint64_t hidden, uint64_t topk,
                                    float global_divisor, gemb_stream_t stream);
 
+/* Grouped expert projection over the padded row space: for every 128-row tile t of the plan,
+ * out[rows of t] = bf16( A[rows of t] . W[tile_expert[t]]^T / (ga * w_divisors[expert]) ).
+ * A: NVFP4 payload [padded_rows_max, K/2] + INTERLEAVED scales; W: [experts, rows_per_expert, K/2]
+ * with each expert's scales INTERLEAVED back to back; w_divisors: fp32 [experts] on the device.
+ * Experts with no assignment own no tile and cost nothing; nothing is read back to the host.
+ * rows_per_expert % 128 == 0, K % 64 == 0.  "grouped W13 / grouped W2" of
+ * docs/plans/gemma4-26b/specs/MOE_PREFILL_KERNEL_SPEC.md:34-66. */
+int32_t gemb_moe_grouped_gemm_bf16(const uint8_t* packed_activation_e2m1,
+                                   const uint8_t* interleaved_activation_scales,
+                                   const uint8_t* packed_weight_e2m1,
+                                   const uint8_t* interleaved_weight_scales, uint16_t* output_bf16,
+                                   const int32_t* plan, uint64_t padded_rows_max, uint64_t experts,
+                                   uint64_t rows_per_expert, uint64_t contracting_elements,
+                                   float activation_global_divisor, const float* weight_global_divisors,
+                                   gemb_stream_t stream);
+
+/* Expert activation boundary on the padded rows: gate_up bf16 [rows, 2*intermediate] (gate first),
+ * product = bf16(bf16(gelu_tanh(gate)) * up), NVFP4-quantised (EXACT contract) with the down
+ * projection's input divisor into payload [rows, intermediate/2] + INTERLEAVED scales.  Only
+ * the plan's padded rows are processed (plan may be null: all rows_max rows).
+ * Boundaries of src/cuda/nvfp4/reference.cu:177-217; fused gate_up order of
+ * tools/capture_gemma4_26b_goldens.py:232-240. */
+int32_t gemb_moe_expert_gelu_quantize(const uint16_t* gate_up_bf16, const int32_t* plan,
+                                      uint8_t* packed_e2m1, uint8_t* interleaved_scales,
+                                      uint64_t rows_max, uint64_t intermediate,
+                                      float global_divisor, gemb_stream_t stream);
+
 /* out[t] = bf16( sum over slots in slot order of fma(weight[t][slot], y[slot_rows[t*topk+slot]])
  *                + shared[t] ), fp32 accumulation, no atomics; shared may be null.
  * docs/plans/gemma4-26b/specs/MOE_SEMANTICS_SPEC.md:74-83. */
