@@ -505,6 +505,74 @@ int32_t gemb_moe_permute(const int32_t* top_ids, int32_t* counts, int32_t* offse
   return check_launch(op);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of gemb_moe_permute.
+//
+// gemb_moe_permute needs a few kilobytes of scratch for the per-segment expert counts and asks
+// the caller for it.  Some hosts cannot supply one: an engine that carves a single arena at
+// model load and forbids the allocator afterwards may have no region left for a workspace it
+// did not plan for, and code running inside a latency-critical or capture-only section must not
+// call cudaMalloc (it synchronises the device and is illegal while a stream is capturing).  For
+// them the scratch lives in the file-scope array below, which every GPU that loads the library
+// holds until the process exits.  Its size is fixed, so the problem size is capped.
+// ---------------------------------------------------------------------------------------------
+constexpr uint64_t kStaticMaxSegments = 128;   // 128 segments x 1024 = 131,072 assignments
+constexpr uint64_t kStaticMaxExperts = 256;
+static __device__ __align__(256) int32_t g_permute_scratch[kStaticMaxSegments * kStaticMaxExperts];  // 128 KiB
+
+// The array's name is only a host-side handle; kernels need its device address.  It is looked
+// up once per device, with that device current, and cached.
+static int32_t* g_permute_scratch_ptr[64] = {nullptr};
+
+static int32_t permute_scratch_address(const char* op, int32_t** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return fail(GEMB_UNSUPPORTED, "%s: no usable CUDA device", op);
+  }
+  if (g_permute_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_permute_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return fail(GEMB_INTERNAL, "%s: cudaGetSymbolAddress: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+    }
+    g_permute_scratch_ptr[dev] = static_cast<int32_t*>(ptr);
+  }
+  *out = g_permute_scratch_ptr[dev];
+  return GEMB_OK;
+}
+
+int32_t gemb_moe_permute_static(const int32_t* top_ids, int32_t* counts, int32_t* offsets, int32_t* perm,
+                                int32_t* slot_rows, int32_t* plan, uint64_t tokens, uint64_t experts,
+                                uint64_t topk, gemb_stream_t stream) {
+  const char* op = "gemb_moe_permute_static";
+  GEMB_REQUIRE(top_ids && counts && offsets && perm && slot_rows && plan, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_moe_geometry(op, tokens, experts, topk));
+  const uint64_t segments64 = moe_segments(tokens, topk);
+  GEMB_REQUIRE(segments64 <= kStaticMaxSegments && experts <= kStaticMaxExperts,
+               "%s: %llu assignments over %llu experts exceed the built-in scratch (at most %llu assignments, %llu "
+               "experts); use gemb_moe_permute with a caller workspace",
+               op, static_cast<unsigned long long>(tokens * topk), static_cast<unsigned long long>(experts),
+               static_cast<unsigned long long>(kStaticMaxSegments * kSegment),
+               static_cast<unsigned long long>(kStaticMaxExperts));
+  GEMB_TRY(require_sm100(op));
+  int32_t* block_counts = nullptr;
+  GEMB_TRY(permute_scratch_address(op, &block_counts));
+  const uint32_t total = static_cast<uint32_t>(tokens * topk), e = static_cast<uint32_t>(experts);
+  const uint32_t segments = static_cast<uint32_t>(segments64);
+  // The count kernel overwrites every (segment, expert) cell this call reads, so nothing has to
+  // be cleared even though the array still holds the previous call's values.
+  permute_count_kernel<<<segments, 128, e * sizeof(int), stream>>>(top_ids, block_counts, total, e);
+  GEMB_TRY(check_launch(op));
+  permute_scan_kernel<<<1, 256, (3 * e + 2) * sizeof(int), stream>>>(block_counts, counts, offsets, plan, segments, e);
+  GEMB_TRY(check_launch(op));
+  permute_scatter_kernel<<<segments, 128, 4 * e * sizeof(int), stream>>>(top_ids, block_counts, offsets, plan, perm,
+                                                                        slot_rows, total, e);
+  return check_launch(op);
+}
+
 int32_t gemb_moe_dispatch_quantize(const uint16_t* x_bf16, const int32_t* slot_rows, uint8_t* packed_e2m1,
                                    uint8_t* interleaved_scales, uint64_t tokens, uint64_t hidden, uint64_t topk,
                                    float global_divisor, gemb_stream_t stream) {

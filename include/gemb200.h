@@ -259,6 +259,23 @@ int32_t gemb_moe_permute(const int32_t* top_ids, int32_t* counts, int32_t* offse
                          int32_t* slot_rows, int32_t* plan, void* workspace, uint64_t workspace_bytes,
                          uint64_t tokens, uint64_t experts, uint64_t topk, gemb_stream_t stream);
 
+/* The same operation as gemb_moe_permute for hosts that can neither hand over a workspace nor
+ * allocate one: an engine whose single load-time arena has no region to spare, or code inside a
+ * section where cudaMalloc is off limits because it would synchronise the device or break a
+ * stream capture.  The per-segment counts go to a 128 KiB array that lives inside the library
+ * (every GPU that loads the library keeps it until exit).  Limits: tokens * topk <= 131,072
+ * and experts <= 256; larger problems are rejected with GEMB_INVALID_ARGUMENT and must use
+ * gemb_moe_permute.  The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, that device current): make that first call outside any stream
+ * capture.  No cudaMalloc / cudaFree or allocating library call is made, ever.  All calls
+ * share the one array: two calls whose kernels can overlap on the GPU (different streams,
+ * no dependency) race on it and corrupt each other's result; calls ordered on one stream are
+ * safe, and nothing has to be cleared between them.
+ * This entry point has no counterpart in the reference. */
+int32_t gemb_moe_permute_static(const int32_t* top_ids, int32_t* counts, int32_t* offsets,
+                                int32_t* perm, int32_t* slot_rows, int32_t* plan, uint64_t tokens,
+                                uint64_t experts, uint64_t topk, gemb_stream_t stream);
+
 /* NVFP4-quantises each token's expert input once (EXACT contract) and writes payload and
  * INTERLEAVED block scales to the padded row of each of its topk assignments.
  * "activation + W2 input quantization" boundary of MOE_PREFILL_KERNEL_SPEC.md:34-47. */
