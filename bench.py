@@ -11,6 +11,14 @@ prefill configurations of the Gemma-4 12B-like model):
                 quantised per token to E4M3 inside each GEMV launch; 48 distinct weight sets
                 (10.76 GB, far larger than L2).  Metric: GB/s of algorithmic bytes.
 
+  nvfp4_linear  (reported under "other_workloads") X bf16 [512, 3840] -> NVFP4 quantiser -> tcgen05 GEMM
+                against W NVFP4 [15360, 3840]; eight distinct weight sets (266 MB > L2) in rotation.
+                Metric: TFLOP/s counting the GEMM's 2*M*N*K flops, for the GEMM alone and with the
+                activation quantiser in the timed region.
+  moe_layer     (reported under "other_workloads") one 26B-A4B-like MoE layer on 4096 tokens: router,
+                top-8, stable permutation, dispatch, grouped NVFP4 expert GEMMs, GELU requantisation,
+                shared FFN, slot-ordered combine.  Metric: tokens/s.
+
 A step is one pass over all 48 layers, replayed as one CUDA graph.  `value` is measured with
 inputs resident in HBM; `e2e` copies the step's activations from pinned host memory and the
 results back inside the timed region.  With N > 1 every rank runs an independent replica
@@ -277,6 +285,16 @@ def run_decode_gemv(args):
                      "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": None,
                      "avg_launch_us": launch_s * 1e6},
     }
+    if world == 1 and not args.no_other_workloads:
+        del weights
+        torch.cuda.empty_cache()
+        other = {}
+        for name, fn in (("nvfp4_linear", bench_nvfp4_linear), ("moe_layer", bench_moe_layer)):
+            try:
+                other[name] = fn(lib, dev)
+            except Exception as exc:  # a secondary workload must not take the headline line down
+                other[name] = {"error": f"{type(exc).__name__}: {exc}"}
+        line["other_workloads"] = other
     if world == 1 and not args.no_cpu_baseline:
         gbs, dt, cores, kind = cpu_decode_sample(1, 0, use_ref=True)
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
@@ -284,6 +302,98 @@ def run_decode_gemv(args):
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------------
+# secondary workloads (rank 0 only, N = 1 semantics; reported under "other_workloads")
+# --------------------------------------------------------------------------------------------
+def graph_time(enqueue, launches_per_graph, reps=20):
+    """Seconds per enqueue() pass, replayed as one CUDA graph, timed with CUDA events."""
+    import torch
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        enqueue(st)
+        st.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            enqueue(st)
+        for _ in range(3):
+            g.replay()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st.synchronize()
+        s.record(st)
+        for _ in range(reps):
+            g.replay()
+        e.record(st)
+        st.synchronize()
+    return s.elapsed_time(e) / reps / 1e3
+
+
+def bench_nvfp4_linear(lib, dev):
+    import torch
+    m, n, k, copies = 512, 15360, 3840, 8
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED)
+    x = torch.randn((m, k), device=dev, generator=gen).to(torch.bfloat16)
+    ga = float(2688.0 / x.float().abs().max().item())
+    xq = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
+    xs = torch.zeros((lib.cdll.gemb_interleaved_scale_bytes(m, k),), dtype=torch.uint8, device=dev)
+    ws = []
+    for _ in range(copies):
+        w = torch.randn((n, k), device=dev, generator=gen) * 0.02
+        gw = float(2688.0 / w.abs().max().item())
+        wq = torch.empty((n, k // 2), dtype=torch.uint8, device=dev)
+        wsc = torch.zeros((lib.cdll.gemb_interleaved_scale_bytes(n, k),), dtype=torch.uint8, device=dev)
+        lib.gemb_nvfp4_quantize(w, 0, wq, wsc, n, k, gw, 1, 0, None)
+        ws.append((wq, wsc, gw))
+        del w
+    out = torch.empty((m, n), dtype=torch.int16, device=dev)
+    lib.gemb_nvfp4_quantize(x.view(torch.int16), 1, xq, xs, m, k, ga, 1, 0, None)
+
+    def gemm_only(st):
+        for wq, wsc, gw in ws:
+            lib.gemb_nvfp4_gemm_bf16(xq, xs, wq, wsc, out, m, n, k, ga, gw, st)
+
+    def quant_and_gemm(st):
+        for wq, wsc, gw in ws:
+            lib.gemb_nvfp4_quantize(x.view(torch.int16), 1, xq, xs, m, k, ga, 1, 0, st)
+            lib.gemb_nvfp4_gemm_bf16(xq, xs, wq, wsc, out, m, n, k, ga, gw, st)
+
+    t_gemm = graph_time(gemm_only, copies) / copies
+    t_both = graph_time(quant_and_gemm, 2 * copies) / copies
+    lib.gemb_check_device_status()
+    flops = 2.0 * m * n * k
+    nominal = 9000.0
+    return {"metric": "NVFP4 GEMM TFLOP/s", "workload": "nvfp4_linear 512x15360x3840 (W4A4)",
+            "value": flops / t_gemm / 1e12, "unit": "TFLOP/s", "us_per_linear": t_gemm * 1e6,
+            "with_activation_quantizer": {"value": flops / t_both / 1e12, "us_per_linear": t_both * 1e6},
+            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<nvfp4, 128x256>", "achieved": flops / t_gemm / 1e12,
+                         "peak": nominal, "unit": "TFLOP/s", "frac": flops / t_gemm / 1e12 / nominal,
+                         "peak_source": "nominal dense FP4 (9 PFLOP/s); MEASURED_PEAKS.json has no FP4 figure",
+                         "frac_of_4x_measured_bf16_sustained": flops / t_gemm / 1e12 / (4 * 1391.3)},
+            "l2": f"{copies} distinct weight sets in rotation, {copies * (n * k // 2 + n * k // 16) / 1e6:.0f} MB > 126 MB L2"}
+
+
+def bench_moe_layer(lib, dev, tokens=4096):
+    import torch
+    from gem16_b200.moe import MoeLayer, synthetic_weights
+    w = synthetic_weights(dev, SEED + 3000)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + 3001)
+    x = torch.randn((tokens, 2816), device=dev, generator=gen).to(torch.bfloat16)
+    ga = float(2688.0 / x.float().abs().max().item())
+    layer = MoeLayer(w, tokens, 8, ga, 2688.0 / 8.0, 2688.0 / 8.0)
+    xi = x.view(torch.int16)
+    secs = graph_time(lambda st: layer.forward(xi, st), 14)
+    lib.gemb_check_device_status()
+    flops = 2.0 * tokens * 128 * 2816 + tokens * 8 * 2.0 * 3 * 704 * 2816 + tokens * 2.0 * 3 * 2112 * 2816
+    weight_bytes = 128 * 3 * 704 * 2816 * 0.5625 + 3 * 2112 * 2816 * 0.5625 + 128 * 2816 * 4
+    return {"metric": "MoE layer tokens/s", "workload": f"moe_layer {tokens} tokens, 128 experts top-8, hidden 2816, expert 704, shared 2112",
+            "value": tokens / secs, "unit": "tokens/s", "us_per_layer": secs * 1e6,
+            "flops": flops, "achieved_tflops": flops / secs / 1e12, "weight_bytes": weight_bytes,
+            "bounds_us": {"tensor_at_9PF": flops / 9e15 * 1e6, "hbm_weights_at_measured_peak": weight_bytes / (measured_peaks()["hbm_gbs"] * 1e9) * 1e6},
+            "padded_rows": int(layer.plan[1].item()), "tiles": int(layer.plan[0].item()),
+            "expert_count_max": int(layer.counts.max().item()), "expert_count_min": int(layer.counts.min().item())}
 
 
 def main():
@@ -294,6 +404,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_gemv", choices=["decode_gemv"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-workloads", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

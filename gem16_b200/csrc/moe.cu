@@ -16,73 +16,123 @@ namespace {
 
 // ---------------------------------------------------------------------------------------------
 // Router logits: logits[t][e] = fma(x[t][H-1], w[e][H-1], ... fma(x[t][0], w[e][0], bias[e])),
-// one fp32 fma per k in ascending k.  CTA = 32 tokens x 128 experts, thread = 2 tokens x 8
-// experts, K walked in shared-memory tiles of 32.
+// one fp32 fma per k in ascending k (the order is the contract; it rules out tensor cores and
+// K-splitting).  CTA = 32 tokens x 128 experts, 128 threads, thread = 8 tokens x 4 experts
+// (32 independent fma chains).  K is walked in shared-memory tiles of 32; the next tile's global
+// loads are issued into registers before the current tile is consumed.
 // ---------------------------------------------------------------------------------------------
-constexpr int kRtTok = 32, kRtExp = 128, kRtK = 32;
+constexpr int kRtExp = 128, kRtK = 32, kRtThreads = 128;
 
-__global__ void __launch_bounds__(256)
+// kTok = tokens per CTA (32 for prefill batches, 8 for decode batches so that a few dozen tokens
+// still spread over many SMs).  Shared tiles are stored k-major with an xor swizzle of the column
+// (multiples of 4 / 8 keep each thread's float4 groups intact) so that both the transposing
+// stores and the float4 loads are bank-conflict free.
+template <int kTok>
+__global__ void __launch_bounds__(kRtThreads)
 router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
                      const float* __restrict__ bias, float* __restrict__ logits, uint32_t tokens,
                      uint32_t hidden, uint32_t experts) {
-  __shared__ float xs[kRtK][kRtTok + 1];
-  __shared__ __align__(16) float ws[kRtK][kRtExp + 4];
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  const uint32_t tok0 = blockIdx.x * kRtTok, exp0 = blockIdx.y * kRtExp;
-  float acc[2][8];
+  constexpr int kPerThread = kTok / 4;  // tokens per thread: 8 or 2
+  __shared__ __align__(16) float xs[kRtK][32];
+  __shared__ __align__(16) float ws[kRtK][kRtExp];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // experts tx*4.., tokens ty*kPerThread..
+  const uint32_t tok0 = blockIdx.x * kTok, exp0 = blockIdx.y * kRtExp;
+  float acc[kPerThread][4];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const uint32_t e = exp0 + tx * 8 + j;
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t e = exp0 + tx * 4 + j;
     const float b = (bias != nullptr && e < experts) ? __ldg(bias + e) : 0.0f;
-    acc[0][j] = b;
-    acc[1][j] = b;
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) acc[i][j] = b;
   }
-  for (uint32_t k0 = 0; k0 < hidden; k0 += kRtK) {
-    {  // X tile: 32 tokens x 32 k, thread -> (token, 4 consecutive k)
-      const int t = threadIdx.x >> 3, kc = (threadIdx.x & 7) * 4;
-      uint2 v = make_uint2(0, 0);
-      if (tok0 + t < tokens && k0 + kc < hidden)
-        v = __ldg(reinterpret_cast<const uint2*>(x + static_cast<uint64_t>(tok0 + t) * hidden + k0 + kc));
-      xs[kc + 0][t] = __uint_as_float(v.x << 16);
-      xs[kc + 1][t] = __uint_as_float(v.x & 0xFFFF0000u);
-      xs[kc + 2][t] = __uint_as_float(v.y << 16);
-      xs[kc + 3][t] = __uint_as_float(v.y & 0xFFFF0000u);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {  // W tile: 128 experts x 32 k
-      const int e = (threadIdx.x >> 3) + 32 * i, kc = (threadIdx.x & 7) * 4;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (exp0 + e < experts && k0 + kc < hidden)
-        v = __ldg(reinterpret_cast<const float4*>(w + static_cast<uint64_t>(exp0 + e) * hidden + k0 + kc));
-      ws[kc + 0][e] = v.x;
-      ws[kc + 1][e] = v.y;
-      ws[kc + 2][e] = v.z;
-      ws[kc + 3][e] = v.w;
-    }
-    __syncthreads();
-    const uint32_t kmax = min(static_cast<uint32_t>(kRtK), hidden - k0);
-#pragma unroll 8
-    for (uint32_t k = 0; k < kmax; ++k) {
-      const float x0 = xs[k][ty * 2], x1 = xs[k][ty * 2 + 1];
-      const float4 wa = *reinterpret_cast<const float4*>(&ws[k][tx * 8]);
-      const float4 wb = *reinterpret_cast<const float4*>(&ws[k][tx * 8 + 4]);
-      const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        acc[0][j] = fmaf(x0, wv[j], acc[0][j]);
-        acc[1][j] = fmaf(x1, wv[j], acc[1][j]);
+  // Global -> register staging: X tile kTok tokens x 32 k bf16 = one uint4 per thread (token
+  // tid/4, k chunk (tid%4)*8); W tile 128 experts x 32 k fp32 = eight float4 per thread
+  // (expert tid/8 + 16 i, k chunk (tid%8)*4).
+  const int xt = threadIdx.x >> 2, xq = threadIdx.x & 3, xk = xq * 8;
+  const int we = threadIdx.x >> 3, wm = threadIdx.x & 7, wk = wm * 4;
+  uint4 xr;
+  float4 wr[8];
+  auto load_tile = [&](uint32_t k0) {
+    xr = make_uint4(0, 0, 0, 0);
+    if (xt < kTok && tok0 + xt < tokens) {
+      const uint16_t* src = x + static_cast<uint64_t>(tok0 + xt) * hidden + k0 + xk;
+      if (k0 + xk + 8 <= hidden) {
+        if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+          xr = __ldg(reinterpret_cast<const uint4*>(src));
+        } else {
+          const uint2 a = __ldg(reinterpret_cast<const uint2*>(src)), b2 = __ldg(reinterpret_cast<const uint2*>(src) + 1);
+          xr = make_uint4(a.x, a.y, b2.x, b2.y);
+        }
+      } else if (k0 + xk + 4 <= hidden) {
+        const uint2 a = __ldg(reinterpret_cast<const uint2*>(src));
+        xr = make_uint4(a.x, a.y, 0, 0);
       }
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      wr[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const uint32_t e = exp0 + we + 16 * i;
+      if (e < experts && k0 + wk < hidden)
+        wr[i] = __ldg(reinterpret_cast<const float4*>(w + static_cast<uint64_t>(e) * hidden + k0 + wk));
+    }
+  };
+  auto store_tile = [&]() {
+    const uint32_t xw[4] = {xr.x, xr.y, xr.z, xr.w};
+    const int xcol = xt ^ (8 * xq);  // rows xk..xk+7 all have (k / 8) & 3 == xq
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      xs[xk + 2 * i][xcol] = __uint_as_float(xw[i] << 16);
+      xs[xk + 2 * i + 1][xcol] = __uint_as_float(xw[i] & 0xFFFF0000u);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int col = (we + 16 * i) ^ (4 * wm);  // rows wk..wk+3 all have k / 4 == wm
+      ws[wk + 0][col] = wr[i].x;
+      ws[wk + 1][col] = wr[i].y;
+      ws[wk + 2][col] = wr[i].z;
+      ws[wk + 3][col] = wr[i].w;
+    }
+  };
+  load_tile(0);
+  for (uint32_t k0 = 0; k0 < hidden; k0 += kRtK) {
+    store_tile();
+    __syncthreads();
+    if (k0 + kRtK < hidden) load_tile(k0 + kRtK);
+    const uint32_t kmax = min(static_cast<uint32_t>(kRtK), hidden - k0);
+#pragma unroll 4
+    for (uint32_t k = 0; k < kmax; ++k) {
+      const float4 wv4 = *reinterpret_cast<const float4*>(&ws[k][(tx * 4) ^ (4 * (k >> 2))]);
+      const float wv[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
+      float xv[kPerThread];
+      if constexpr (kPerThread == 8) {
+        const int col = (ty * 8) ^ (8 * ((k >> 3) & 3));
+        const float4 xa = *reinterpret_cast<const float4*>(&xs[k][col]);
+        const float4 xb = *reinterpret_cast<const float4*>(&xs[k][col + 4]);
+        xv[0] = xa.x; xv[1] = xa.y; xv[2] = xa.z; xv[3] = xa.w;
+        xv[4] = xb.x; xv[5] = xb.y; xv[6] = xb.z; xv[7] = xb.w;
+      } else {
+        const int col = (ty * 2) ^ (8 * ((k >> 3) & 3));
+        const float2 xa = *reinterpret_cast<const float2*>(&xs[k][col]);
+        xv[0] = xa.x; xv[1] = xa.y;
+      }
+#pragma unroll
+      for (int i = 0; i < kPerThread; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+    }
     __syncthreads();
   }
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const uint32_t t = tok0 + ty * 2 + i;
+  for (int i = 0; i < kPerThread; ++i) {
+    const uint32_t t = tok0 + ty * kPerThread + i;
     if (t >= tokens) continue;
+    float* dst = logits + static_cast<uint64_t>(t) * experts + exp0 + tx * 4;
+    if (exp0 + tx * 4 + 4 <= experts && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const uint32_t e = exp0 + tx * 8 + j;
-      if (e < experts) logits[static_cast<uint64_t>(t) * experts + e] = acc[i][j];
+      for (int j = 0; j < 4; ++j)
+        if (exp0 + tx * 4 + j < experts) dst[j] = acc[i][j];
     }
   }
 }
@@ -454,9 +504,19 @@ int32_t gemb_moe_router_logits(const uint16_t* x_bf16, const float* router_weigh
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(x_bf16) % 8 == 0 && reinterpret_cast<uintptr_t>(router_weight) % 16 == 0,
                "%s: activations must be 8-byte and router weights 16-byte aligned", op);
   GEMB_TRY(require_sm100(op));
-  dim3 grid(static_cast<unsigned>((tokens + kRtTok - 1) / kRtTok), static_cast<unsigned>((experts + kRtExp - 1) / kRtExp));
-  router_logits_kernel<<<grid, 256, 0, stream>>>(x_bf16, router_weight, bias, logits, static_cast<uint32_t>(tokens),
-                                                 static_cast<uint32_t>(hidden), static_cast<uint32_t>(experts));
+  // 8-token CTAs only while they do not outnumber the SMs (decode-size batches); beyond that the
+  // 32-token tile does four times the arithmetic per shared-memory load.
+  const bool small = (tokens + 7) / 8 * ((experts + kRtExp - 1) / kRtExp) <= static_cast<uint64_t>(sm_count());
+  const unsigned tile = small ? 8 : 32;
+  dim3 grid(static_cast<unsigned>((tokens + tile - 1) / tile), static_cast<unsigned>((experts + kRtExp - 1) / kRtExp));
+  if (small)
+    router_logits_kernel<8><<<grid, kRtThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
+                                                            static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
+                                                            static_cast<uint32_t>(experts));
+  else
+    router_logits_kernel<32><<<grid, kRtThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
+                                                             static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
+                                                             static_cast<uint32_t>(experts));
   return check_launch(op);
 }
 

@@ -126,3 +126,35 @@ class MoeLayer:
             self.shared_branch(x_bf16, stream)
         self.combine(stream)
         return self.out
+
+
+def synthetic_weights(dev, seed, hidden=2816, experts=128, inter=704, shared_inter=2112, zipf=True):
+    """Seeded synthetic 26B-A4B-like layer generated and quantised on the GPU: router fp32 ~ N(0, 0.02)
+    with a Zipf(1.1) bias (-1.1 ln(rank) over a seeded permutation, zero mean), NVFP4 expert and
+    shared weights ~ N(0, 0.02) with per-tensor divisor 6*448/amax."""
+    lib = load()
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+
+    def quant(rows, k):
+        w = torch.randn((rows, k), device=dev, generator=g) * 0.02
+        div = float(2688.0 / w.abs().max().item())
+        packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=dev)
+        scales = torch.empty((rows, k // 16), dtype=torch.uint8, device=dev)
+        lib.gemb_nvfp4_quantize(w, 0, packed, scales, rows, k, div, 0, 0, None)
+        return packed, scales, div
+
+    router_w = torch.randn((experts, hidden), device=dev, generator=g) * 0.02
+    bias = None
+    if zipf:
+        rank = torch.randperm(experts, device=dev, generator=g).double() + 1
+        b = -1.1 * torch.log(rank)
+        bias = (b - b.mean()).float()
+    gu = [quant(2 * inter, hidden) for _ in range(experts)]
+    dn = [quant(hidden, inter) for _ in range(experts)]
+    shared = None
+    if shared_inter:
+        shared = (quant(2 * shared_inter, hidden), quant(hidden, shared_inter))
+    return MoeWeights(lib, dev, router_w, bias, torch.stack([x[0] for x in gu]), torch.stack([x[1] for x in gu]),
+                      [x[2] for x in gu], torch.stack([x[0] for x in dn]), torch.stack([x[1] for x in dn]),
+                      [x[2] for x in dn], shared)
