@@ -432,6 +432,36 @@ expert_gelu_quantize_kernel(const uint16_t* __restrict__ gate_up, const int32_t*
 }
 
 // ---------------------------------------------------------------------------------------------
+// Expert-parallel plumbing: row gather (pack assignments in permutation order for the all-to-all,
+// and expert outputs back into arrival order) and the scatter of already quantised rows into the
+// padded row space with interleaved scales.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const int32_t* __restrict__ index,
+                   uint32_t divisor, uint64_t rows, uint32_t chunks_per_row) {
+  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= rows * chunks_per_row) return;
+  const uint64_t r = idx / chunks_per_row, c = idx % chunks_per_row;
+  const uint64_t s = static_cast<uint64_t>(__ldg(index + r)) / divisor;
+  dst[r * chunks_per_row + c] = __ldg(src + s * chunks_per_row + c);
+}
+
+__global__ void __launch_bounds__(256)
+scatter_quantized_kernel(const uint8_t* __restrict__ payload, const uint8_t* __restrict__ compact_scales,
+                         const int32_t* __restrict__ slot_rows, uint8_t* __restrict__ packed,
+                         uint8_t* __restrict__ scales, uint64_t rows, uint32_t hidden, uint32_t c_pad) {
+  const uint32_t blocks = hidden / 16;
+  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= rows * blocks) return;
+  const uint64_t r = idx / blocks;
+  const uint32_t c = static_cast<uint32_t>(idx % blocks);
+  const uint64_t d = static_cast<uint64_t>(__ldg(slot_rows + r));
+  *reinterpret_cast<uint2*>(packed + d * (hidden / 2) + c * 8) =
+      __ldg(reinterpret_cast<const uint2*>(payload + r * (hidden / 2) + c * 8));
+  scales[interleaved_scale_offset(d, c, c_pad)] = __ldg(compact_scales + r * blocks + c);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Deterministic combine (MOE_SEMANTICS_SPEC.md:74-83): acc = 0; for slot 0..k-1:
 // acc = fma(weight[slot], y[row(slot)], acc); + shared branch; round to bf16.
 // One thread per 8 output columns.
@@ -483,6 +513,15 @@ using namespace gemb;
 namespace {
 uint64_t moe_segments(uint64_t tokens, uint64_t topk) { return (tokens * topk + kSegment - 1) / kSegment; }
 uint64_t moe_max_tiles(uint64_t tokens, uint64_t experts, uint64_t topk) { return tokens * topk / 128 + experts; }
+
+// The permutation itself has no warp-shape constraint on the expert count (the expert-parallel
+// receiver sorts by a handful of local experts).
+int32_t validate_permute_geometry(const char* op, uint64_t tokens, uint64_t experts, uint64_t topk) {
+  GEMB_REQUIRE(tokens > 0 && tokens * topk < (1ull << 31), "%s: token count must be nonzero and fit 31 bits", op);
+  GEMB_REQUIRE(experts >= 1 && experts <= 1024, "%s: experts must be in [1, 1024]", op);
+  GEMB_REQUIRE(topk >= 1 && topk <= 32, "%s: top-k must be in [1, 32]", op);
+  return GEMB_OK;
+}
 
 int32_t validate_moe_geometry(const char* op, uint64_t tokens, uint64_t experts, uint64_t topk) {
   GEMB_REQUIRE(tokens > 0 && tokens * topk < (1ull << 31), "%s: token count must be nonzero and fit 31 bits", op);
@@ -548,7 +587,7 @@ int32_t gemb_moe_permute(const int32_t* top_ids, int32_t* counts, int32_t* offse
                          uint64_t tokens, uint64_t experts, uint64_t topk, gemb_stream_t stream) {
   const char* op = "gemb_moe_permute";
   GEMB_REQUIRE(top_ids && counts && offsets && perm && slot_rows && plan && workspace, "%s: pointers must be nonnull", op);
-  GEMB_TRY(validate_moe_geometry(op, tokens, experts, topk));
+  GEMB_TRY(validate_permute_geometry(op, tokens, experts, topk));
   GEMB_REQUIRE(workspace_bytes >= gemb_moe_permute_workspace_bytes(tokens, experts, topk),
                "%s: workspace too small (%llu bytes needed)", op,
                static_cast<unsigned long long>(gemb_moe_permute_workspace_bytes(tokens, experts, topk)));
@@ -649,6 +688,38 @@ int32_t gemb_moe_dispatch_quantize(const uint16_t* x_bf16, const int32_t* slot_r
   dispatch_quantize_kernel<<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
       x_bf16, slot_rows, packed_e2m1, interleaved_scales, static_cast<uint32_t>(hidden), static_cast<uint32_t>(topk),
       global_divisor, c_pad);
+  return check_launch(op);
+}
+
+int32_t gemb_moe_gather_rows(const void* src, void* dst, const int32_t* index, uint64_t index_divisor,
+                             uint64_t rows, uint64_t row_bytes, gemb_stream_t stream) {
+  const char* op = "gemb_moe_gather_rows";
+  GEMB_REQUIRE(src && dst && index, "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(rows > 0 && rows < (1ull << 31) && index_divisor >= 1 && index_divisor < (1ull << 31), "%s: bad geometry", op);
+  GEMB_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0 && row_bytes < (1ull << 24), "%s: row size must be a nonzero multiple of 16 bytes", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0,
+               "%s: buffers must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  const uint32_t chunks = static_cast<uint32_t>(row_bytes / 16);
+  gather_rows_kernel<<<static_cast<unsigned>((rows * chunks + 255) / 256), 256, 0, stream>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), index, static_cast<uint32_t>(index_divisor), rows, chunks);
+  return check_launch(op);
+}
+
+int32_t gemb_moe_scatter_quantized(const uint8_t* packed_rows, const uint8_t* compact_scales, const int32_t* slot_rows,
+                                   uint8_t* packed_e2m1, uint8_t* interleaved_scales, uint64_t rows, uint64_t hidden,
+                                   gemb_stream_t stream) {
+  const char* op = "gemb_moe_scatter_quantized";
+  GEMB_REQUIRE(packed_rows && compact_scales && slot_rows && packed_e2m1 && interleaved_scales, "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(rows > 0 && rows < (1ull << 31), "%s: bad row count", op);
+  GEMB_REQUIRE(hidden > 0 && hidden % 16 == 0 && hidden < (1ull << 31), "%s: hidden must be a nonzero multiple of 16", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(packed_rows) % 8 == 0 && reinterpret_cast<uintptr_t>(packed_e2m1) % 8 == 0,
+               "%s: payload buffers must be 8-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  const uint32_t c_pad = static_cast<uint32_t>((hidden / 16 + 3) / 4 * 4);
+  const uint64_t work = rows * (hidden / 16);
+  scatter_quantized_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+      packed_rows, compact_scales, slot_rows, packed_e2m1, interleaved_scales, rows, static_cast<uint32_t>(hidden), c_pad);
   return check_launch(op);
 }
 

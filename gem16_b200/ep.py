@@ -1,0 +1,125 @@
+"""Expert-parallel MoE layer: experts split evenly over ranks, tokens data-sharded, NCCL
+all-to-all for dispatch and combine (torch.distributed is the plumbing; every compute step is a
+C-ABI launch).  gem16 has no multi-GPU code; the protocol below is this library's.
+
+Per layer, on every rank (T local tokens, R ranks, E experts, E/R local experts [r*E/R, (r+1)*E/R)):
+  1. route the local tokens over all E experts (router replicated): ids, weights, counts,
+     offsets and the stable permutation -- which orders assignments by expert, hence by owner rank;
+  2. NVFP4-quantise the local tokens once and pack payload + scales + local expert id in
+     permutation order (1,584 B + 4 B per assignment instead of 5,632 B of bf16);
+  3. all-gather the per-expert counts (the only host read-back: the split sizes), all-to-all the
+     packed rows;
+  4. the owner sorts what it received by local expert with the same stable permutation kernel --
+     arrival order is (source rank, expert, token, slot), so the result is (expert, global token,
+     slot), exactly the single-GPU order -- scatters into the padded row space and runs the
+     grouped gate_up GEMM, GELU requantisation and grouped down GEMM;
+  5. expert outputs go back in arrival order through the reverse all-to-all, and each token's
+     owner combines its topk contributions in slot order and adds its shared branch.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .lib import load
+from .moe import MoeLayer, MoeWeights
+
+
+def ep_splits(counts_all, rank: int, experts_per_rank: int):
+    """Split sizes of the dispatch all-to-all from the gathered per-expert counts [R, E]:
+    (rows this rank sends to each rank, rows it receives from each rank)."""
+    ranks = counts_all.shape[0]
+    per_owner = counts_all.reshape(ranks, ranks, experts_per_rank).sum(-1)   # [source, owner]
+    return [int(v) for v in per_owner[rank]], [int(v) for v in per_owner[:, rank]]
+
+
+class EpMoeLayer:
+    """Buffers and launch sequence of one expert-parallel layer for `tokens` local tokens."""
+
+    def __init__(self, weights: MoeWeights, tokens: int, topk: int, ga: float, ga_dn: float, ga_sh_dn: float,
+                 group=None):
+        self.lib = load()
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.w, self.tokens, self.topk = weights, tokens, topk
+        self.ga, self.ga_dn = ga, ga_dn
+        lib, dev, w, c = self.lib, weights.dev, weights, self.lib.cdll
+        self.e_total, self.e_local = w.router_experts, w.experts
+        assert self.e_local * self.world == self.e_total
+        h, i, n = w.hidden, w.inter, tokens * topk
+        # the local half (routing, shared branch, combine) reuses the single-GPU layer's buffers
+        self.local = MoeLayer(weights, tokens, topk, ga, ga_dn, ga_sh_dn, allocate_experts=False)
+        cap = n * self.world                      # worst case: every assignment of every rank lands here
+        self.cap = cap
+        u8 = dict(dtype=torch.uint8, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.xq = torch.empty((tokens, h // 2), **u8)
+        self.xs = torch.empty((tokens, h // 16), **u8)
+        self.send_payload = torch.empty((n, h // 2), **u8)
+        self.send_scales = torch.empty((n, h // 16), **u8)
+        self.recv_payload = torch.empty((cap, h // 2), **u8)
+        self.recv_scales = torch.empty((cap, h // 16), **u8)
+        self.recv_eid = torch.empty((cap,), **i32)
+        self.counts_all = torch.empty((self.world, self.e_total), **i32)
+        self.rows_max = c.gemb_moe_padded_rows_max(cap, self.e_local, 1)
+        self.l_counts = torch.empty((self.e_local,), **i32)
+        self.l_offsets = torch.empty((self.e_local + 1,), **i32)
+        self.l_perm = torch.empty((cap,), **i32)
+        self.l_rows = torch.empty((cap,), **i32)
+        self.l_plan = torch.zeros((c.gemb_moe_plan_ints(cap, self.e_local, 1),), **i32)
+        self.l_ws = torch.empty((c.gemb_moe_permute_workspace_bytes(cap, self.e_local, 1),), **u8)
+        self.a_packed = torch.zeros((self.rows_max, h // 2), **u8)
+        self.a_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, h),), **u8)
+        self.gate_up = torch.empty((self.rows_max, 2 * i), dtype=torch.int16, device=dev)
+        self.p_packed = torch.zeros((self.rows_max, i // 2), **u8)
+        self.p_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, i),), **u8)
+        self.y = torch.empty((self.rows_max, h), dtype=torch.int16, device=dev)
+        self.y_send = torch.empty((cap, h), dtype=torch.int16, device=dev)
+        self.y_sorted = torch.empty((n, h), dtype=torch.int16, device=dev)
+        self.inv_perm = torch.empty((n,), **i32)
+        self.arange = torch.arange(n, **i32)
+        self.last = {}
+
+    def forward(self, x_bf16):
+        lib, w, t, k, loc = self.lib, self.w, self.tokens, self.topk, self.local
+        h, n = w.hidden, self.tokens * self.topk
+        # 1. routing of the local tokens over all experts
+        lib.gemb_moe_router_logits(x_bf16, w.router_w, w.router_bias, loc.logits, t, h, self.e_total, None)
+        lib.gemb_moe_route(loc.logits, None, loc.ids, loc.weights, None, t, self.e_total, k, None)
+        lib.gemb_moe_permute(loc.ids, loc.counts, loc.offsets, loc.perm, loc.slot_rows, loc.plan, loc.workspace,
+                             loc.workspace.numel(), t, self.e_total, k, None)
+        # 2. quantise once, pack in permutation order
+        lib.gemb_nvfp4_quantize(x_bf16, 1, self.xq, self.xs, t, h, self.ga, 0, 0, None)
+        lib.gemb_moe_gather_rows(self.xq, self.send_payload, loc.perm, k, n, h // 2, None)
+        lib.gemb_moe_gather_rows(self.xs, self.send_scales, loc.perm, k, n, h // 16, None)
+        send_eid = (loc.ids.view(-1)[loc.perm.long()] % self.e_local).to(torch.int32)
+        # 3. split sizes (host read-back of E*R integers), then the dispatch all-to-all
+        dist.all_gather_into_tensor(self.counts_all.view(-1), loc.counts, group=self.group)
+        send_splits, recv_splits = ep_splits(self.counts_all.cpu().numpy(), self.rank, self.e_local)
+        n_recv = sum(recv_splits)
+        dist.all_to_all_single(self.recv_payload[:n_recv], self.send_payload, recv_splits, send_splits, group=self.group)
+        dist.all_to_all_single(self.recv_scales[:n_recv], self.send_scales, recv_splits, send_splits, group=self.group)
+        dist.all_to_all_single(self.recv_eid[:n_recv], send_eid, recv_splits, send_splits, group=self.group)
+        # 4. local experts
+        if n_recv > 0:
+            lib.gemb_moe_permute(self.recv_eid, self.l_counts, self.l_offsets, self.l_perm, self.l_rows, self.l_plan,
+                                 self.l_ws, self.l_ws.numel(), n_recv, self.e_local, 1, None)
+            lib.gemb_moe_scatter_quantized(self.recv_payload, self.recv_scales, self.l_rows, self.a_packed,
+                                           self.a_scales, n_recv, h, None)
+            lib.gemb_moe_grouped_gemm_bf16(self.a_packed, self.a_scales, w.gu_packed, w.gu_scales, self.gate_up,
+                                           self.l_plan, self.rows_max, self.e_local, 2 * w.inter, h, self.ga, w.gu_div, None)
+            lib.gemb_moe_expert_gelu_quantize(self.gate_up, self.l_plan, self.p_packed, self.p_scales, self.rows_max,
+                                              w.inter, self.ga_dn, None)
+            lib.gemb_moe_grouped_gemm_bf16(self.p_packed, self.p_scales, w.dn_packed, w.dn_scales, self.y, self.l_plan,
+                                           self.rows_max, self.e_local, h, w.inter, self.ga_dn, w.dn_div, None)
+            lib.gemb_moe_gather_rows(self.y, self.y_send, self.l_rows, 1, n_recv, h * 2, None)
+        # 5. reverse all-to-all, shared branch, slot-ordered combine on the token's owner
+        dist.all_to_all_single(self.y_sorted.view(torch.uint8), self.y_send[:n_recv].view(torch.uint8), send_splits,
+                               recv_splits, group=self.group)   # byte rows: 16-bit integers are not a NCCL type
+        self.inv_perm[loc.perm.long()] = self.arange
+        if w.shared is not None:
+            loc.shared_branch(x_bf16)
+        shared = loc.s_out if w.shared is not None else None
+        lib.gemb_moe_combine(self.y_sorted, self.inv_perm, loc.weights, shared, loc.out, t, h, k, None)
+        self.last = {"n_recv": n_recv, "send_splits": send_splits, "recv_splits": recv_splits}
+        return loc.out

@@ -18,9 +18,10 @@ class MoeWeights:
     def __init__(self, lib, dev, router_w, router_bias, gu_packed, gu_scales, gu_div, dn_packed, dn_scales, dn_div,
                  shared=None):
         self.dev = dev
-        self.experts, self.two_inter, half_h = gu_packed.shape
+        self.experts, self.two_inter, half_h = gu_packed.shape       # experts held on this device
         self.hidden, self.inter = half_h * 2, self.two_inter // 2
         self.router_w = torch.as_tensor(router_w, device=dev).contiguous()
+        self.router_experts = self.router_w.shape[0]                # experts the router scores
         self.router_bias = None if router_bias is None else torch.as_tensor(router_bias, device=dev).contiguous()
         self.gu_packed = torch.as_tensor(gu_packed, device=dev).contiguous()
         self.dn_packed = torch.as_tensor(dn_packed, device=dev).contiguous()
@@ -51,12 +52,13 @@ class MoeWeights:
 class MoeLayer:
     """Preallocated buffers + the launch sequence for `tokens` tokens."""
 
-    def __init__(self, weights: MoeWeights, tokens: int, topk: int, ga: float, ga_dn: float, ga_sh_dn: float = 1.0):
+    def __init__(self, weights: MoeWeights, tokens: int, topk: int, ga: float, ga_dn: float, ga_sh_dn: float = 1.0,
+                 allocate_experts: bool = True):
         self.lib = load()
         self.w, self.tokens, self.topk = weights, tokens, topk
         self.ga, self.ga_dn, self.ga_sh_dn = ga, ga_dn, ga_sh_dn
         lib, dev, w = self.lib, weights.dev, weights
-        e, h, i = w.experts, w.hidden, w.inter
+        e, h, i = w.router_experts, w.hidden, w.inter
         c = lib.cdll
         self.rows_max = c.gemb_moe_padded_rows_max(tokens, e, topk)
         i32 = dict(dtype=torch.int32, device=dev)
@@ -70,12 +72,13 @@ class MoeLayer:
         self.slot_rows = torch.empty((tokens * topk,), **i32)
         self.plan = torch.zeros((c.gemb_moe_plan_ints(tokens, e, topk),), **i32)
         self.workspace = torch.empty((c.gemb_moe_permute_workspace_bytes(tokens, e, topk),), **u8)
-        self.a_packed = torch.zeros((self.rows_max, h // 2), **u8)
-        self.a_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, h),), **u8)
-        self.gate_up = torch.empty((self.rows_max, 2 * i), dtype=torch.int16, device=dev)
-        self.p_packed = torch.zeros((self.rows_max, i // 2), **u8)
-        self.p_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, i),), **u8)
-        self.y = torch.empty((self.rows_max, h), dtype=torch.int16, device=dev)
+        if allocate_experts:   # the expert-parallel layer owns its own (differently sized) expert buffers
+            self.a_packed = torch.zeros((self.rows_max, h // 2), **u8)
+            self.a_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, h),), **u8)
+            self.gate_up = torch.empty((self.rows_max, 2 * i), dtype=torch.int16, device=dev)
+            self.p_packed = torch.zeros((self.rows_max, i // 2), **u8)
+            self.p_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, i),), **u8)
+            self.y = torch.empty((self.rows_max, h), dtype=torch.int16, device=dev)
         self.out = torch.empty((tokens, h), dtype=torch.int16, device=dev)
         if w.shared is not None:
             si = w.shared["inter"]
@@ -128,10 +131,12 @@ class MoeLayer:
         return self.out
 
 
-def synthetic_weights(dev, seed, hidden=2816, experts=128, inter=704, shared_inter=2112, zipf=True):
+def synthetic_weights(dev, seed, hidden=2816, experts=128, inter=704, shared_inter=2112, zipf=True,
+                      expert_range=None):
     """Seeded synthetic 26B-A4B-like layer generated and quantised on the GPU: router fp32 ~ N(0, 0.02)
     with a Zipf(1.1) bias (-1.1 ln(rank) over a seeded permutation, zero mean), NVFP4 expert and
-    shared weights ~ N(0, 0.02) with per-tensor divisor 6*448/amax."""
+    shared weights ~ N(0, 0.02) with per-tensor divisor 6*448/amax.  expert_range=(lo, hi) keeps
+    only those experts' weights (expert parallelism); the router always scores all of them."""
     lib = load()
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
@@ -150,8 +155,14 @@ def synthetic_weights(dev, seed, hidden=2816, experts=128, inter=704, shared_int
         rank = torch.randperm(experts, device=dev, generator=g).double() + 1
         b = -1.1 * torch.log(rank)
         bias = (b - b.mean()).float()
-    gu = [quant(2 * inter, hidden) for _ in range(experts)]
-    dn = [quant(hidden, inter) for _ in range(experts)]
+    # Every rank draws every expert (identical streams) and keeps its own range.
+    lo, hi = expert_range if expert_range is not None else (0, experts)
+    gu, dn = [], []
+    for e in range(experts):
+        a, b = quant(2 * inter, hidden), quant(hidden, inter)
+        if lo <= e < hi:
+            gu.append(a)
+            dn.append(b)
     shared = None
     if shared_inter:
         shared = (quant(2 * shared_inter, hidden), quant(hidden, shared_inter))

@@ -253,7 +253,7 @@ uint64_t gemb_moe_padded_rows_max(uint64_t tokens, uint64_t experts, uint64_t to
  *   counts[experts], offsets[experts + 1], perm[tokens * topk] (perm[pos] = i)   -- the spec's
  *   records;  slot_rows[i] = row of assignment i in the padded per-expert row space;
  *   plan = {tiles, padded rows, padded_offsets[experts + 1], tile_expert[tiles]} consumed on
- *   the device by the grouped GEMM (no host readback).
+ *   the device by the grouped GEMM (no host readback).  1 <= experts <= 1024, topk <= 32.
  * docs/plans/gemma4-26b/specs/MOE_PREFILL_KERNEL_SPEC.md:19-58. */
 int32_t gemb_moe_permute(const int32_t* top_ids, int32_t* counts, int32_t* offsets, int32_t* perm,
                          int32_t* slot_rows, int32_t* plan, void* workspace, uint64_t workspace_bytes,
@@ -283,6 +283,20 @@ int32_t gemb_moe_dispatch_quantize(const uint16_t* x_bf16, const int32_t* slot_r
                                    uint8_t* packed_e2m1, uint8_t* interleaved_scales,
                                    uint64_t tokens, uint64_t hidden, uint64_t topk,
                                    float global_divisor, gemb_stream_t stream);
+
+/* Expert-parallel plumbing (gem16 has no multi-GPU code; docs/GEMMA4_26B.md:114-117 excludes it,
+ * so these have no counterpart there).
+ * gather_rows: dst[i] = src[index[i] / index_divisor], rows of row_bytes (multiple of 16) bytes --
+ * packs quantised tokens in permutation order for the dispatch all-to-all (index = perm, divisor =
+ * topk) and expert outputs back into arrival order for the combine all-to-all (index = slot rows).
+ * scatter_quantized: places already quantised rows (payload + COMPACT scales, as received) at
+ * slot_rows[i] of the padded row space and converts their scales to the INTERLEAVED layout. */
+int32_t gemb_moe_gather_rows(const void* src, void* dst, const int32_t* index, uint64_t index_divisor,
+                             uint64_t rows, uint64_t row_bytes, gemb_stream_t stream);
+int32_t gemb_moe_scatter_quantized(const uint8_t* packed_rows, const uint8_t* compact_scales,
+                                   const int32_t* slot_rows, uint8_t* packed_e2m1,
+                                   uint8_t* interleaved_scales, uint64_t rows, uint64_t hidden,
+                                   gemb_stream_t stream);
 
 /* Grouped expert projection over the padded row space: for every 128-row tile t of the plan,
  * out[rows of t] = bf16( A[rows of t] . W[tile_expert[t]]^T / (ga * w_divisors[expert]) ).

@@ -1,0 +1,52 @@
+"""One NCCL rank of the GPU expert-parallel test (launched by tests/test_ep_gpu.py with torchrun).
+Every rank also runs the single-GPU layer on all tokens and requires its slice of the
+expert-parallel output, ids, weights and global counts to be bit-identical."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from gem16_b200 import load  # noqa: E402
+from gem16_b200.ep import EpMoeLayer  # noqa: E402
+from gem16_b200.moe import MoeLayer, synthetic_weights  # noqa: E402
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    lib = load()
+    hidden, experts, inter, shared_inter, topk = 2816, 128, 704, 2112, 8
+    tokens = int(sys.argv[1]) if len(sys.argv) > 1 else 96        # per rank
+    e_local = experts // world
+    full = synthetic_weights(dev, 7, hidden, experts, inter, shared_inter)
+    mine = synthetic_weights(dev, 7, hidden, experts, inter, shared_inter, expert_range=(rank * e_local, (rank + 1) * e_local))
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    x_all = torch.randn((tokens * world, hidden), device=dev, generator=g).to(torch.bfloat16)
+    ga = float(2688.0 / x_all.float().abs().max().item())
+    ga_dn = ga_sh = 2688.0 / 8.0
+    ref = MoeLayer(full, tokens * world, topk, ga, ga_dn, ga_sh)
+    ref_out = ref.forward(x_all.view(torch.int16)).clone()
+    ep = EpMoeLayer(mine, tokens, topk, ga, ga_dn, ga_sh)
+    sl = slice(rank * tokens, (rank + 1) * tokens)
+    for _ in range(2):     # twice: buffers are reused across layers
+        out = ep.forward(x_all[sl].contiguous().view(torch.int16))
+        torch.cuda.synchronize()
+        lib.gemb_check_device_status()
+        assert torch.equal(ep.local.ids, ref.ids[sl]), "expert ids differ"
+        assert torch.equal(ep.local.weights, ref.weights[sl]), "routing weights differ"
+        assert torch.equal(ep.counts_all.sum(0).to(torch.int32), ref.counts), "global counts differ"
+        assert torch.equal(out, ref_out[sl]), "expert-parallel output differs from the single-GPU layer"
+    dist.barrier()
+    print(f"rank {rank} ok n_recv={ep.last['n_recv']}", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
