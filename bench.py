@@ -263,6 +263,14 @@ def run_decode_gemv(args):
     bytes_step = decode_bytes_per_layer() * LAYERS
     value = world * bytes_step * args.steps / secs / 1e9
     e2e = world * bytes_step * args.steps / secs_e2e / 1e9
+    moe_ep = None
+    if not args.no_other_workloads:
+        del weights, graph
+        torch.cuda.empty_cache()
+        try:   # collective: every rank takes part
+            moe_ep = bench_moe_ep(lib, dev, world, rank)
+        except Exception as exc:
+            moe_ep = {"error": f"{type(exc).__name__}: {exc}"}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -285,16 +293,15 @@ def run_decode_gemv(args):
                      "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": None,
                      "avg_launch_us": launch_s * 1e6},
     }
+    if moe_ep is not None:
+        line["other_workloads"] = {"moe_ep_stack": moe_ep}
     if world == 1 and not args.no_other_workloads:
-        del weights
-        torch.cuda.empty_cache()
-        other = {}
+        other = line["other_workloads"]
         for name, fn in (("nvfp4_linear", bench_nvfp4_linear), ("moe_layer", bench_moe_layer)):
             try:
                 other[name] = fn(lib, dev)
             except Exception as exc:  # a secondary workload must not take the headline line down
                 other[name] = {"error": f"{type(exc).__name__}: {exc}"}
-        line["other_workloads"] = other
     if world == 1 and not args.no_cpu_baseline:
         gbs, dt, cores, kind = cpu_decode_sample(1, 0, use_ref=True)
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
@@ -394,6 +401,69 @@ def bench_moe_layer(lib, dev, tokens=4096):
             "bounds_us": {"tensor_at_9PF": flops / 9e15 * 1e6, "hbm_weights_at_measured_peak": weight_bytes / (measured_peaks()["hbm_gbs"] * 1e9) * 1e6},
             "padded_rows": int(layer.plan[1].item()), "tiles": int(layer.plan[0].item()),
             "expert_count_max": int(layer.counts.max().item()), "expert_count_min": int(layer.counts.min().item())}
+
+
+def bench_moe_ep(lib, dev, world, rank, layers=30, phases=((16384, "prefill"), (64, "decode"))):
+    """Expert-parallel MoE stack: `layers` distinct 26B-A4B-like layers, experts split evenly over
+    the ranks, tokens data-sharded, NCCL all-to-all dispatch/combine.  Collective: every rank calls
+    it; returns the summary on every rank (times are the max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    from gem16_b200.ep import EpMoeLayer
+    from gem16_b200.moe import MoeLayer, synthetic_weights
+    experts = 128
+    e_local = experts // world
+    rng = (rank * e_local, (rank + 1) * e_local)
+    weights = [synthetic_weights(dev, SEED + 4000 + l, expert_range=rng if world > 1 else None) for l in range(layers)]
+    out = {"metric": "MoE stack tokens/s", "layers": layers, "ranks": world, "experts_per_rank": e_local, "phases": {}}
+    for tokens, name in phases:
+        t_local = tokens // world
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(SEED + 4100)
+        x_all = torch.randn((tokens, 2816), device=dev, generator=gen).to(torch.bfloat16)
+        ga = float(2688.0 / x_all.float().abs().max().item())
+        x = x_all[rank * t_local:(rank + 1) * t_local].contiguous().view(torch.int16)
+        if world > 1:
+            stack = [None] * layers
+            shared_bufs = EpMoeLayer(weights[0], t_local, 8, ga, 336.0, 336.0)
+            def run():
+                for w in weights:
+                    shared_bufs.w = w
+                    shared_bufs.local.w = w
+                    shared_bufs.forward(x)
+        else:
+            buf = MoeLayer(weights[0], tokens, 8, ga, 336.0, 336.0)
+            def run():
+                for w in weights:
+                    buf.w = w
+                    buf.forward(x)
+        for _ in range(2):
+            run()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        s.record()
+        for _ in range(reps):
+            run()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / reps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        lib.gemb_check_device_status()
+        out["phases"][name] = {"tokens": tokens, "ms_per_stack": ms, "tokens_per_s": tokens / ms * 1e3,
+                               "us_per_layer": ms * 1e3 / layers}
+        del x_all
+        if world > 1:
+            del shared_bufs
+        else:
+            del buf
+        torch.cuda.empty_cache()
+    return out
 
 
 def main():
