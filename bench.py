@@ -324,7 +324,7 @@ def graph_time(enqueue, launches_per_graph, reps=20):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=st):
             enqueue(st)
-        for _ in range(3):
+        for _ in range(10):
             g.replay()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         st.synchronize()
@@ -414,7 +414,8 @@ def bench_moe_ep(lib, dev, world, rank, layers=30, phases=((16384, "prefill"), (
     experts = 128
     e_local = experts // world
     rng = (rank * e_local, (rank + 1) * e_local)
-    weights = [synthetic_weights(dev, SEED + 4000 + l, expert_range=rng if world > 1 else None) for l in range(layers)]
+    weights = [synthetic_weights(dev, SEED + 4000 + l, expert_range=rng if world > 1 else None, placement_ranks=world)
+               for l in range(layers)]
     out = {"metric": "MoE stack tokens/s", "layers": layers, "ranks": world, "experts_per_rank": e_local, "phases": {}}
     for tokens, name in phases:
         t_local = tokens // world

@@ -78,11 +78,19 @@ class EpMoeLayer:
         self.y_sorted = torch.empty((n, h), dtype=torch.int16, device=dev)
         self.inv_perm = torch.empty((n,), **i32)
         self.arange = torch.arange(n, **i32)
+        self.side = torch.cuda.Stream(device=dev)     # shared branch runs beside the exchange
         self.last = {}
 
     def forward(self, x_bf16):
         lib, w, t, k, loc = self.lib, self.w, self.tokens, self.topk, self.local
         h, n = w.hidden, self.tokens * self.topk
+        main = torch.cuda.current_stream()
+        if w.shared is not None:
+            # The shared dense branch depends only on x: run it on a side stream so it overlaps the
+            # count exchange, both all-to-alls and the host read-back.
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                loc.shared_branch(x_bf16, self.side)
         # 1. routing of the local tokens over all experts
         lib.gemb_moe_router_logits(x_bf16, w.router_w, w.router_bias, loc.logits, t, h, self.e_total, None)
         lib.gemb_moe_route(loc.logits, None, loc.ids, loc.weights, None, t, self.e_total, k, None)
@@ -118,7 +126,7 @@ class EpMoeLayer:
                                recv_splits, group=self.group)   # byte rows: 16-bit integers are not a NCCL type
         self.inv_perm[loc.perm.long()] = self.arange
         if w.shared is not None:
-            loc.shared_branch(x_bf16)
+            main.wait_stream(self.side)
         shared = loc.s_out if w.shared is not None else None
         lib.gemb_moe_combine(self.y_sorted, self.inv_perm, loc.weights, shared, loc.out, t, h, k, None)
         self.last = {"n_recv": n_recv, "send_splits": send_splits, "recv_splits": recv_splits}

@@ -55,6 +55,7 @@ class MoeLayer:
     def __init__(self, weights: MoeWeights, tokens: int, topk: int, ga: float, ga_dn: float, ga_sh_dn: float = 1.0,
                  allocate_experts: bool = True):
         self.lib = load()
+        self.side = None
         self.w, self.tokens, self.topk = weights, tokens, topk
         self.ga, self.ga_dn, self.ga_sh_dn = ga, ga_dn, ga_sh_dn
         lib, dev, w = self.lib, weights.dev, weights
@@ -123,16 +124,25 @@ class MoeLayer:
                                   self.topk, stream)
 
     def forward(self, x_bf16, stream=None):
+        main = stream if stream is not None else torch.cuda.current_stream()
+        if self.w.shared is not None:
+            # The shared dense branch depends only on x: it runs on a side stream beside routing and
+            # the expert GEMMs and joins before the combine (the fork/join is capturable).
+            if self.side is None:
+                self.side = torch.cuda.Stream(device=self.w.dev)
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                self.shared_branch(x_bf16, self.side)
         self.route(x_bf16, stream)
         self.experts(x_bf16, stream)
         if self.w.shared is not None:
-            self.shared_branch(x_bf16, stream)
+            main.wait_stream(self.side)
         self.combine(stream)
         return self.out
 
 
 def synthetic_weights(dev, seed, hidden=2816, experts=128, inter=704, shared_inter=2112, zipf=True,
-                      expert_range=None):
+                      expert_range=None, placement_ranks=1):
     """Seeded synthetic 26B-A4B-like layer generated and quantised on the GPU: router fp32 ~ N(0, 0.02)
     with a Zipf(1.1) bias (-1.1 ln(rank) over a seeded permutation, zero mean), NVFP4 expert and
     shared weights ~ N(0, 0.02) with per-tensor divisor 6*448/amax.  expert_range=(lo, hi) keeps
@@ -155,6 +165,20 @@ def synthetic_weights(dev, seed, hidden=2816, experts=128, inter=704, shared_int
         rank = torch.randperm(experts, device=dev, generator=g).double() + 1
         b = -1.1 * torch.log(rank)
         bias = (b - b.mean()).float()
+        if placement_ranks > 1:
+            # Load-time expert placement: expert ids are labels, so hand the popularity prior out
+            # in serpentine order over the ranks (hot experts spread evenly); rank r owns ids
+            # [r*E/R, (r+1)*E/R).  The prior is all that is known before any token is routed.
+            order = torch.argsort(bias, descending=True)
+            per = experts // placement_ranks
+            new_bias = torch.empty_like(bias)
+            fill = [0] * placement_ranks
+            for p, src in enumerate(order.tolist()):
+                rnd, pos = divmod(p, placement_ranks)
+                r = pos if rnd % 2 == 0 else placement_ranks - 1 - pos
+                new_bias[r * per + fill[r]] = bias[src]
+                fill[r] += 1
+            bias = new_bias
     # Every rank draws every expert (identical streams) and keeps its own range.
     lo, hi = expert_range if expert_range is not None else (0, experts)
     gu, dn = [], []

@@ -24,8 +24,9 @@ def main():
     hidden, experts, inter, shared_inter, topk = 2816, 128, 704, 2112, 8
     tokens = int(sys.argv[1]) if len(sys.argv) > 1 else 96        # per rank
     e_local = experts // world
-    full = synthetic_weights(dev, 7, hidden, experts, inter, shared_inter)
-    mine = synthetic_weights(dev, 7, hidden, experts, inter, shared_inter, expert_range=(rank * e_local, (rank + 1) * e_local))
+    full = synthetic_weights(dev, 7, hidden, experts, inter, shared_inter, placement_ranks=world)
+    mine = synthetic_weights(dev, 7, hidden, experts, inter, shared_inter, expert_range=(rank * e_local, (rank + 1) * e_local),
+                             placement_ranks=world)
     g = torch.Generator(device=dev)
     g.manual_seed(11)
     x_all = torch.randn((tokens * world, hidden), device=dev, generator=g).to(torch.bfloat16)
