@@ -25,6 +25,8 @@ int32_t require_sm100(const char* op);
 int sm_count();
 // Tuning knobs owned by the GEMM translation unit (see gemb_set_tuning).
 int32_t gemm_set_tuning(int32_t knob, int32_t value);
+// Reads and clears the decode GEMV's bounded-wait flag (0 = clean, -1 = could not read).
+int gemv_take_device_error();
 
 inline bool positive_finite(float v) { return std::isfinite(v) && v > 0.0f; }
 

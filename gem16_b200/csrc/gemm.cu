@@ -614,6 +614,9 @@ int32_t gemb_check_device_status(void) {
     cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof zero);
     return fail(GEMB_INTERNAL, "%s: a GEMM kernel gave up waiting on a pipeline barrier (role %d)", op, code);
   }
+  const int gemv_code = gemv_take_device_error();
+  if (gemv_code != 0)
+    return fail(GEMB_INTERNAL, "%s: a GEMV kernel gave up waiting on a pipeline barrier (role %d)", op, gemv_code);
   return GEMB_OK;
 }
 

@@ -11,12 +11,19 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace gemb {
+
+__device__ int g_gemv_error = 0;
+
 namespace {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
+
+int g_rows_override = 0;  // 0 = automatic; set through gemb_set_tuning(GEMB_TUNE_GEMV_ROWS, n)
+int g_pdl = 1;            // programmatic dependent launch; gemb_set_tuning(GEMB_TUNE_GEMV_PDL, 0/1)
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
@@ -70,9 +77,10 @@ struct Fp8Group {
 //
 // The staging buffer is padded to a whole 512-element segment; lanes past K multiply zero
 // weights with whatever the padding holds, so it must hold finite values: zero it.
+template <int kW>
 __device__ __forceinline__ void zero_fp8_staging_tail(uint64_t k, __half* xs) {
   const uint64_t chunks = k / 16, chunks_pad = (k + 511) / 512 * 32;
-  for (uint64_t c = chunks + threadIdx.x; c < chunks_pad; c += kThreads) {
+  for (uint64_t c = chunks + threadIdx.x; c < chunks_pad; c += kW * 32) {
     __half* dst = xs + (c / 32) * 512 + (c % 32) * 8;
     *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     *reinterpret_cast<uint4*>(dst + 256) = make_uint4(0, 0, 0, 0);
@@ -80,8 +88,9 @@ __device__ __forceinline__ void zero_fp8_staging_tail(uint64_t k, __half* xs) {
 }
 
 // Stages an already quantized activation (E4M3 bytes) as fp16 in shared memory.
+template <int kW>
 __device__ __forceinline__ void stage_fp8_activation(const uint8_t* act, uint64_t k, __half* xs) {
-  for (uint64_t c = threadIdx.x; c < k / 16; c += kThreads) {
+  for (uint64_t c = threadIdx.x; c < k / 16; c += kW * 32) {
     const uint4 v = __ldg(reinterpret_cast<const uint4*>(act) + c);
     const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
     uint32_t h[8];
@@ -94,7 +103,7 @@ __device__ __forceinline__ void stage_fp8_activation(const uint8_t* act, uint64_
     *reinterpret_cast<uint4*>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
     *reinterpret_cast<uint4*>(dst + 256) = make_uint4(h[4], h[5], h[6], h[7]);
   }
-  zero_fp8_staging_tail(k, xs);
+  zero_fp8_staging_tail<kW>(k, xs);
 }
 
 // A value y with E4M3(y) == E4M3(x / scale) for the IEEE quotient x / scale.  x * (1/scale) is
@@ -143,17 +152,18 @@ __device__ __forceinline__ float chunk_amax(const uint4& v) {
 // quantizer: scale = amax/448, q = E4M3(x/scale), src/numeric/fp8.cpp:41-58) and stages the
 // decoded bytes as fp16.  Returns the token scale.  The first pass keeps up to 16,384 elements
 // of loads in flight at once; the second pass re-reads the token from L1.
+template <int kW>
 __device__ __forceinline__ float stage_bf16_activation(const uint16_t* x, uint64_t k, __half* xs,
                                                        float* red) {
   constexpr int kBatch = 8;  // 8 chunks x 256 threads x 8 elements = 16,384 per batch
   const uint64_t chunks = k / 8;
   const uint4* xp = reinterpret_cast<const uint4*>(x);
   float amax = 0.0f;
-  for (uint64_t base = threadIdx.x; base < chunks; base += static_cast<uint64_t>(kBatch) * kThreads) {
+  for (uint64_t base = threadIdx.x; base < chunks; base += static_cast<uint64_t>(kBatch) * (kW * 32)) {
     uint4 v[kBatch];
 #pragma unroll
     for (int i = 0; i < kBatch; ++i) {
-      const uint64_t c = base + static_cast<uint64_t>(i) * kThreads;
+      const uint64_t c = base + static_cast<uint64_t>(i) * (kW * 32);
       v[i] = c < chunks ? __ldg(xp + c) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
@@ -164,24 +174,24 @@ __device__ __forceinline__ float stage_bf16_activation(const uint16_t* x, uint64
   __syncthreads();
   amax = red[0];
 #pragma unroll
-  for (int i = 1; i < kWarps; ++i) amax = fmaxf(amax, red[i]);
+  for (int i = 1; i < kW; ++i) amax = fmaxf(amax, red[i]);
   const float scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 448.0f);
   const float inv_scale = __frcp_rn(scale);
   // Second pass: the token was just read by this CTA, so these loads hit L1.
-  for (uint64_t base = threadIdx.x; base < chunks; base += 4ull * kThreads) {
+  for (uint64_t base = threadIdx.x; base < chunks; base += 4ull * (kW * 32)) {
     uint4 v[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint64_t c = base + static_cast<uint64_t>(i) * kThreads;
+      const uint64_t c = base + static_cast<uint64_t>(i) * (kW * 32);
       v[i] = c < chunks ? __ldg(xp + c) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint64_t c = base + static_cast<uint64_t>(i) * kThreads;
+      const uint64_t c = base + static_cast<uint64_t>(i) * (kW * 32);
       if (c < chunks) stage_bf16_chunk(v[i], c, scale, inv_scale, xs);
     }
   }
-  zero_fp8_staging_tail(k, xs);
+  zero_fp8_staging_tail<kW>(k, xs);
   return scale;
 }
 
@@ -191,17 +201,24 @@ __device__ __forceinline__ float stage_bf16_activation(const uint16_t* x, uint64
 // kRows*kUnroll 128-bit loads of a step (predicated at the K tail) before it consumes them.
 // The first step of the first task is issued before the activation is staged, so the HBM
 // pipeline fills while the CTA quantizes / decodes the activation.
+// Warps per CTA.  (One 24-warp CTA per SM for the fused-quantisation variant, so that the
+// activation is quantised once per SM, measured slower than three 8-warp CTAs: the prologue is
+// bound by its dependent global round trips, not by instruction issue.)
+template <bool kFusedQuant>
+__host__ __device__ constexpr int fp8_gemv_warps() { return kWarps; }
+
 template <int kRows, int kUnroll, bool kFusedQuant, bool kBf16Out>
-__global__ void __launch_bounds__(kThreads, kFusedQuant ? 3 : 4)
+__global__ void __launch_bounds__(fp8_gemv_warps<kFusedQuant>() * 32, kFusedQuant ? 3 : 4)
 fp8_gemv_kernel(const void* __restrict__ act, const float* __restrict__ act_scale,
                 const __grid_constant__ Fp8Group grp, uint64_t k) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __half* xs = reinterpret_cast<__half*>(smem_raw);
-  __shared__ float red[kWarps];
+  constexpr int kW = fp8_gemv_warps<kFusedQuant>();
+  __shared__ float red[kW];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t total_rows = grp.row_start[grp.n];
   const uint64_t num_tasks = (total_rows + kRows - 1) / kRows;
-  const uint64_t task_stride = static_cast<uint64_t>(gridDim.x) * kWarps;
+  const uint64_t task_stride = static_cast<uint64_t>(gridDim.x) * kW;
   const uint64_t step = 512ull * kUnroll;
 
   auto row_pointer = [&](uint64_t vrow) -> const uint8_t* {
@@ -227,7 +244,7 @@ fp8_gemv_kernel(const void* __restrict__ act, const float* __restrict__ act_scal
   // prefetch as soon as SM slots free up; weights are immutable so they may be read before the
   // previous kernel has finished, everything else waits for it.
   asm volatile("griddepcontrol.launch_dependents;");
-  uint64_t task = static_cast<uint64_t>(blockIdx.x) * kWarps + warp;
+  uint64_t task = static_cast<uint64_t>(blockIdx.x) * kW + warp;
   bool prefetched = false;
   if (task < num_tasks) {
     load_step(task, 0);
@@ -237,9 +254,9 @@ fp8_gemv_kernel(const void* __restrict__ act, const float* __restrict__ act_scal
 
   float a_scale;
   if constexpr (kFusedQuant) {
-    a_scale = stage_bf16_activation(static_cast<const uint16_t*>(act), k, xs, red);
+    a_scale = stage_bf16_activation<kW>(static_cast<const uint16_t*>(act), k, xs, red);
   } else {
-    stage_fp8_activation(static_cast<const uint8_t*>(act), k, xs);
+    stage_fp8_activation<kW>(static_cast<const uint8_t*>(act), k, xs);
     a_scale = __ldg(act_scale);
   }
   __syncthreads();
@@ -282,8 +299,6 @@ fp8_gemv_kernel(const void* __restrict__ act, const float* __restrict__ act_scal
   }
 }
 
-int g_rows_override = 0;  // 0 = automatic; set through gemb_set_tuning(GEMB_TUNE_GEMV_ROWS, n)
-int g_pdl = 1;            // programmatic dependent launch; gemb_set_tuning(GEMB_TUNE_GEMV_PDL, 0/1)
 
 // Rows per warp task.  One row per task keeps tasks fine-grained (best balance over the
 // persistent grid) and measured fastest on every decode shape; 2 and 4 remain selectable.
@@ -297,6 +312,7 @@ int pick_rows_per_warp(uint64_t total_rows, uint64_t k) {
 template <int kRows, int kUnroll, bool kFusedQuant, bool kBf16Out>
 int32_t launch_fp8_gemv_variant(const char* op, const void* act, const float* act_scale,
                                 const Fp8Group& grp, uint64_t k, cudaStream_t stream) {
+  constexpr int kW = fp8_gemv_warps<kFusedQuant>();
   auto kern = fp8_gemv_kernel<kRows, kUnroll, kFusedQuant, kBf16Out>;
   const size_t smem = (k + 511) / 512 * 512 * sizeof(__half);
   static int resident[64] = {0};      // CTAs per SM, per device, for the smem size last seen
@@ -312,7 +328,7 @@ int32_t launch_fp8_gemv_variant(const char* op, const void* act, const float* ac
         return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
     }
     int occ = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kThreads, smem);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kW * 32, smem);
     if (e != cudaSuccess || occ < 1)
       return fail(GEMB_INTERNAL, "%s: occupancy query failed: %s", op, cudaGetErrorName(e));
     resident[dev] = occ;
@@ -320,10 +336,10 @@ int32_t launch_fp8_gemv_variant(const char* op, const void* act, const float* ac
   }
   const uint64_t tasks = (grp.row_start[grp.n] + kRows - 1) / kRows;
   const uint64_t wave = static_cast<uint64_t>(sm_count()) * resident[dev];
-  const unsigned blocks = static_cast<unsigned>(std::min<uint64_t>((tasks + kWarps - 1) / kWarps, wave));
+  const unsigned blocks = static_cast<unsigned>(std::min<uint64_t>((tasks + kW - 1) / kW, wave));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(blocks);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kW * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -339,6 +355,261 @@ int32_t launch_fp8_gemv_variant(const char* op, const void* act, const float* ac
   return check_launch(op);
 }
 
+// ---------------------------------------------------------------------------------------------
+// FP8 GEMV with a bulk-copy ring.  One persistent CTA per SM: warp 0 is the producer, sixteen
+// consumer warps follow.  The weight matrix is cut into chunks of whole rows (about 16 KB); the
+// producer streams chunk after chunk into a ring of shared-memory stages with 1-D bulk copies
+// (cp.async.bulk, completion on an mbarrier), so the bytes in flight are bounded by shared
+// memory (about 190 KB per SM), not by registers, and keep flowing while the consumers quantise
+// the activation or wait for the previous kernel (weights are immutable, so the producer starts
+// before griddepcontrol.wait).  Consumer warp w owns stage w, i.e. the CTA's chunks w, w+12, ...
+// (an mbarrier parity wait may run at most one phase ahead, so a warp must see every phase of
+// the stages it waits on): it dots every row of the chunk from shared memory and releases the
+// stage.
+// ---------------------------------------------------------------------------------------------
+constexpr int kRingConsumers = 12;   // also the ring depth: consumer w owns stage w
+constexpr int kRingThreads = 32 * (1 + kRingConsumers);
+constexpr uint32_t kRingStageBytes = 16384;
+
+struct RingTask {
+  const uint8_t* src;
+  uint32_t first_vrow, rows;
+};
+
+__device__ __forceinline__ void zero_fp8_staging_tail_n(uint64_t k, __half* xs, int tid, int nthreads) {
+  const uint64_t chunks = k / 16, chunks_pad = (k + 511) / 512 * 32;
+  for (uint64_t c = chunks + tid; c < chunks_pad; c += nthreads) {
+    __half* dst = xs + (c / 32) * 512 + (c % 32) * 8;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(dst + 256) = make_uint4(0, 0, 0, 0);
+  }
+}
+
+template <bool kFusedQuant, bool kBf16Out>
+__global__ void __launch_bounds__(kRingThreads, 1)
+fp8_gemv_ring_kernel(const void* __restrict__ act, const float* __restrict__ act_scale,
+                     const __grid_constant__ Fp8Group grp, uint32_t k, uint32_t rows_per_chunk,
+                     uint32_t stages) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const uint32_t k_pad = (k + 511) / 512 * 512;
+  __half* xs = reinterpret_cast<__half*>(smem_raw);
+  unsigned char* ring = smem_raw + ((k_pad * 2 + 127) / 128) * 128;
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(stages) * kRingStageBytes);
+  uint64_t* empty = full + stages;
+  float* red = reinterpret_cast<float*>(empty + stages);      // [kRingConsumers]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(red + kRingConsumers);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < stages; ++s) {
+      ptx::mbar_init(&full[s], 1);
+      ptx::mbar_init(&empty[s], 1);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  asm volatile("griddepcontrol.launch_dependents;");
+
+  // Chunk j of this CTA is global chunk blockIdx.x + j * gridDim.x.  Chunks never straddle two
+  // problems of a grouped launch: each problem is cut separately.
+  uint32_t chunk_start[4];
+  chunk_start[0] = 0;
+  for (int i = 0; i < grp.n; ++i)
+    chunk_start[i + 1] = chunk_start[i] + static_cast<uint32_t>((grp.p[i].rows + rows_per_chunk - 1) / rows_per_chunk);
+  const uint32_t total_chunks = chunk_start[grp.n];
+  auto task_of = [&](uint32_t chunk) {
+    int pi = 0;
+    while (pi + 1 < grp.n && chunk >= chunk_start[pi + 1]) ++pi;
+    const uint32_t row0 = (chunk - chunk_start[pi]) * rows_per_chunk;
+    RingTask t;
+    t.rows = min(rows_per_chunk, static_cast<uint32_t>(grp.p[pi].rows) - row0);
+    t.src = grp.p[pi].w + static_cast<uint64_t>(row0) * k;
+    t.first_vrow = static_cast<uint32_t>(grp.row_start[pi]) + row0;
+    return t;
+  };
+  const uint32_t my_chunks = blockIdx.x < total_chunks ? (total_chunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (uint32_t j = 0; j < my_chunks && !*abort_flag; ++j) {
+        if (!ptx::mbar_wait(&empty[stage], phase ^ 1, 1u << 18)) {
+          atomicCAS(&g_gemv_error, 0, 1);
+          *abort_flag = 1;
+          break;
+        }
+        const RingTask t = task_of(blockIdx.x + j * gridDim.x);
+        const uint32_t bytes = t.rows * k;
+        ptx::mbar_expect_tx(&full[stage], bytes);
+        ptx::bulk_load_1d(ring + static_cast<size_t>(stage) * kRingStageBytes, t.src, bytes, &full[stage]);
+        if (++stage == stages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // Everything that is not an immutable weight is read only after the previous kernel is done.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int ctid = threadIdx.x - 32, cthreads = kRingConsumers * 32;
+    float a_scale;
+    if constexpr (kFusedQuant) {
+      const uint16_t* x = static_cast<const uint16_t*>(act);
+      const uint4* xp = reinterpret_cast<const uint4*>(x);
+      const uint32_t chunks8 = k / 8;
+      float amax = 0.0f;
+      for (uint32_t base = ctid; base < chunks8; base += 4u * cthreads) {
+        uint4 v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t c = base + i * cthreads;
+          v[i] = c < chunks8 ? __ldg(xp + c) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) amax = fmaxf(amax, chunk_amax(v[i]));
+      }
+      amax = warp_max(amax);
+      if (lane == 0) red[warp - 1] = amax;
+      asm volatile("bar.sync 1, %0;" ::"n"(kRingConsumers * 32));
+      amax = red[0];
+#pragma unroll
+      for (int i = 1; i < kRingConsumers; ++i) amax = fmaxf(amax, red[i]);
+      a_scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 448.0f);
+      const float inv_scale = __frcp_rn(a_scale);
+      for (uint32_t c = ctid; c < chunks8; c += cthreads) stage_bf16_chunk(__ldg(xp + c), c, a_scale, inv_scale, xs);
+    } else {
+      const uint8_t* a8 = static_cast<const uint8_t*>(act);
+      for (uint32_t c = ctid; c < k / 16; c += cthreads) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(a8) + c);
+        const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+        uint32_t h[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          h[2 * i] = e4m3x2_to_half2(static_cast<uint16_t>(ww[i] & 0xFFFFu));
+          h[2 * i + 1] = e4m3x2_to_half2(static_cast<uint16_t>(ww[i] >> 16));
+        }
+        __half* dst = xs + (c / 32) * 512 + (c % 32) * 8;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4*>(dst + 256) = make_uint4(h[4], h[5], h[6], h[7]);
+      }
+      a_scale = __ldg(act_scale);
+    }
+    zero_fp8_staging_tail_n(k, xs, ctid, cthreads);
+    asm volatile("bar.sync 1, %0;" ::"n"(kRingConsumers * 32));
+
+    const uint32_t cw = warp - 1;
+    for (uint32_t j = cw; j < my_chunks && !*abort_flag; j += kRingConsumers) {
+      const uint32_t stage = j % stages, phase = (j / stages) & 1;
+      if (!ptx::mbar_wait(&full[stage], phase, 1u << 18)) {
+        atomicCAS(&g_gemv_error, 0, 2);
+        *abort_flag = 1;
+        break;
+      }
+      const RingTask t = task_of(blockIdx.x + j * gridDim.x);
+      const unsigned char* sw = ring + static_cast<size_t>(stage) * kRingStageBytes;
+      // Two rows at a time, each with two accumulators (even / odd 512-byte segment): four
+      // independent fma chains per lane, and the staged activation is read once per row pair.
+      for (uint32_t r = 0; r < t.rows; r += 2) {
+        const bool two = r + 1 < t.rows;
+        const unsigned char* row0 = sw + static_cast<size_t>(r) * k;
+        const unsigned char* row1 = row0 + k;
+        float acc[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+        uint32_t kk = lane * 16;
+        for (; kk + 512 < k; kk += 1024) {
+          const __half* xp = xs + (kk / 512) * 512 + lane * 8;
+          const uint4 xa0 = *reinterpret_cast<const uint4*>(xp), xb0 = *reinterpret_cast<const uint4*>(xp + 256);
+          const uint4 xa1 = *reinterpret_cast<const uint4*>(xp + 512), xb1 = *reinterpret_cast<const uint4*>(xp + 768);
+          const uint4 w00 = *reinterpret_cast<const uint4*>(row0 + kk), w01 = *reinterpret_cast<const uint4*>(row0 + kk + 512);
+          uint4 w10 = w00, w11 = w01;
+          if (two) {
+            w10 = *reinterpret_cast<const uint4*>(row1 + kk);
+            w11 = *reinterpret_cast<const uint4*>(row1 + kk + 512);
+          }
+          dot16_fp8(acc[0][0], w00, xa0, xb0);
+          dot16_fp8(acc[0][1], w01, xa1, xb1);
+          if (two) {  // warp-uniform
+            dot16_fp8(acc[1][0], w10, xa0, xb0);
+            dot16_fp8(acc[1][1], w11, xa1, xb1);
+          }
+        }
+        if (kk < k) {  // odd number of segments (or a ragged last one): one more for this lane
+          const __half* xp = xs + (kk / 512) * 512 + lane * 8;
+          const uint4 xa0 = *reinterpret_cast<const uint4*>(xp), xb0 = *reinterpret_cast<const uint4*>(xp + 256);
+          dot16_fp8(acc[0][0], *reinterpret_cast<const uint4*>(row0 + kk), xa0, xb0);
+          if (two) dot16_fp8(acc[1][0], *reinterpret_cast<const uint4*>(row1 + kk), xa0, xb0);
+        }
+        float y0 = warp_sum(acc[0][0] + acc[0][1]);
+        float y1 = warp_sum(acc[1][0] + acc[1][1]);
+        if (lane < (two ? 2 : 1)) {
+          const uint32_t vrow = t.first_vrow + r + lane;
+          int pi = 0;
+          while (pi + 1 < grp.n && vrow >= grp.row_start[pi + 1]) ++pi;
+          const uint64_t orow = vrow - grp.row_start[pi];
+          // (acc * a_scale) * w_scale, in that order: src/cuda/fp8/sm120.cu:234-239.
+          const float ws = bf16_bits_to_float(__ldg(grp.p[pi].w_scales + orow));
+          const float y = __fmul_rn(__fmul_rn(lane == 0 ? y0 : y1, a_scale), ws);
+          if constexpr (kBf16Out) static_cast<uint16_t*>(grp.p[pi].out)[orow] = float_to_bf16_bits(y);
+          else static_cast<float*>(grp.p[pi].out)[orow] = y;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&empty[stage]);
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    // give bulk copies still in flight a bounded time to land before the CTA's memory is reused
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+}
+
+int g_gemv_impl = 0;  // 0 = bulk-copy ring when it fits, 1 = direct global loads
+
+template <bool kFusedQuant, bool kBf16Out>
+int32_t launch_fp8_gemv_ring(const char* op, const void* act, const float* act_scale, const Fp8Group& grp,
+                             uint64_t k, cudaStream_t stream, bool* launched) {
+  *launched = false;
+  const uint32_t rows_per_chunk = static_cast<uint32_t>(kRingStageBytes / k);
+  // Measured: the ring hides the fused-quantisation prologue (it wins for K = 15360 in isolation)
+  // but is slower than direct loads on the short-K shapes, and alternating the two in one decode
+  // pass costs more than it gains (their shared-memory footprints differ, so consecutive kernels
+  // cannot overlap).  The direct kernel is therefore the default; the ring runs on request.
+  if (rows_per_chunk == 0 || g_gemv_impl != 2) return GEMB_OK;
+  const size_t x_bytes = ((k + 511) / 512 * 512 * 2 + 127) / 128 * 128;
+  const size_t fixed = x_bytes + 2 * 16 * 8 + kRingConsumers * 4 + 64;
+  const size_t budget = 227 * 1024 - 1024;
+  if (fixed + static_cast<size_t>(kRingConsumers) * kRingStageBytes > budget) return GEMB_OK;
+  const uint32_t stages = kRingConsumers;
+  const size_t smem = x_bytes + static_cast<size_t>(stages) * kRingStageBytes + 2 * stages * 8 + kRingConsumers * 4 + 64;
+  auto kern = fp8_gemv_ring_kernel<kFusedQuant, kBf16Out>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  uint64_t chunks = 0;
+  for (int i = 0; i < grp.n; ++i) chunks += (grp.p[i].rows + rows_per_chunk - 1) / rows_per_chunk;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(std::min<uint64_t>(chunks, static_cast<uint64_t>(sm_count()))));
+  cfg.blockDim = dim3(kRingThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, kern, act, act_scale, grp, static_cast<uint32_t>(k), rows_per_chunk, stages);
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(le), cudaGetErrorString(le));
+  }
+  *launched = true;
+  return check_launch(op);
+}
+
 template <bool kFusedQuant, bool kBf16Out>
 int32_t launch_fp8_gemv(const char* op, const void* act, const float* act_scale, Fp8Group grp,
                         uint64_t k, cudaStream_t stream) {
@@ -348,6 +619,9 @@ int32_t launch_fp8_gemv(const char* op, const void* act, const float* act_scale,
     total_rows += grp.p[i].rows;
   }
   grp.row_start[grp.n] = total_rows;
+  bool launched = false;
+  GEMB_TRY((launch_fp8_gemv_ring<kFusedQuant, kBf16Out>(op, act, act_scale, grp, k, stream, &launched)));
+  if (launched) return GEMB_OK;
   const int rpw = pick_rows_per_warp(total_rows, k);
   if (rpw == 4) return launch_fp8_gemv_variant<4, 2, kFusedQuant, kBf16Out>(op, act, act_scale, grp, k, stream);
   if (rpw == 2) return launch_fp8_gemv_variant<2, 4, kFusedQuant, kBf16Out>(op, act, act_scale, grp, k, stream);
@@ -547,6 +821,18 @@ int32_t validate_nvfp4_gemv(const char* op, uint64_t rows, uint64_t k, float ga,
 }
 
 }  // namespace
+
+// Reads and clears the GEMV ring's bounded-wait flag (0 = clean).
+int gemv_take_device_error() {
+  int code = 0;
+  if (cudaMemcpyFromSymbol(&code, g_gemv_error, sizeof code) != cudaSuccess) return -1;
+  if (code != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_gemv_error, &zero, sizeof zero);
+  }
+  return code;
+}
+
 }  // namespace gemb
 
 using namespace gemb;
@@ -558,6 +844,12 @@ int32_t gemb_set_tuning(int32_t knob, int32_t value) {
     GEMB_REQUIRE(value == 0 || value == 1 || value == 2 || value == 4,
                  "gemb_set_tuning: rows per warp must be 0 (auto), 1, 2 or 4");
     g_rows_override = value;
+    return GEMB_OK;
+  }
+  if (knob == GEMB_TUNE_GEMV_IMPL) {
+    GEMB_REQUIRE(value == 0 || value == 1 || value == 2,
+                 "gemb_set_tuning: GEMV implementation must be 0 (automatic), 1 (direct loads) or 2 (ring)");
+    g_gemv_impl = value;
     return GEMB_OK;
   }
   if (knob == GEMB_TUNE_GEMV_PDL) {

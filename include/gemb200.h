@@ -77,8 +77,9 @@ int32_t gemb_device_check(void);
  * GEMVs, value 0 (automatic), 1, 2 or 4; GEMB_TUNE_GEMV_PDL = launch the decode GEMVs with
  * programmatic stream serialization so a GEMV's weight prefetch overlaps the tail of the kernel
  * before it (1, default) or not (0); GEMB_TUNE_GEMM_BN = output-feature width of a prefill GEMM
- * tile, 0 (automatic), 128 or 256. */
-enum { GEMB_TUNE_GEMV_ROWS = 1, GEMB_TUNE_GEMV_PDL = 2, GEMB_TUNE_GEMM_BN = 3 };
+ * tile, 0 (automatic), 128, 192 or 256; GEMB_TUNE_GEMV_IMPL = FP8 decode GEMV data path, 0 (automatic),
+ * 1 (direct global loads) or 2 (bulk-copy ring through shared memory wherever it fits). */
+enum { GEMB_TUNE_GEMV_ROWS = 1, GEMB_TUNE_GEMV_PDL = 2, GEMB_TUNE_GEMM_BN = 3, GEMB_TUNE_GEMV_IMPL = 4 };
 int32_t gemb_set_tuning(int32_t knob, int32_t value);
 /* Bytes of an INTERLEAVED scale buffer for `rows` rows of K elements. */
 uint64_t gemb_interleaved_scale_bytes(uint64_t rows, uint64_t contracting_elements);
@@ -332,7 +333,7 @@ int32_t gemb_moe_combine(const uint16_t* y_bf16, const int32_t* slot_rows, const
                          const uint16_t* shared_bf16, uint16_t* out_bf16, uint64_t tokens,
                          uint64_t hidden, uint64_t topk, gemb_stream_t stream);
 
-/* Synchronises the device and reports whether a GEMM kernel gave up on a bounded pipeline wait
+/* Synchronises the device and reports whether a GEMM or GEMV kernel gave up on a bounded pipeline wait
  * since the last call (GEMB_INTERNAL, flag cleared) or not (GEMB_OK).  The reference has no
  * counterpart: its kernels have no device-side waits. */
 int32_t gemb_check_device_status(void);
