@@ -181,7 +181,8 @@ def run_decode_gemv(args):
     gen = torch.Generator(device=dev)
     gen.manual_seed(SEED + 1000 * 1 + rank)
     weights = []
-    for layer in range(LAYERS):
+    layers = args.layers
+    for layer in range(layers):
         mats = []
         for _, rows, k in DECODE_SHAPES:
             w = torch.randn((rows, k), device=dev, dtype=torch.float32, generator=gen) * 0.02
@@ -192,8 +193,8 @@ def run_decode_gemv(args):
             del w
         weights.append(mats)
     # activations: one bf16 vector per op, in one contiguous buffer (device + pinned host copy)
-    x_elems = sum(k for _, _, k in DECODE_SHAPES) * LAYERS
-    y_elems = sum(r for _, r, _ in DECODE_SHAPES) * LAYERS
+    x_elems = sum(k for _, _, k in DECODE_SHAPES) * layers
+    y_elems = sum(r for _, r, _ in DECODE_SHAPES) * layers
     x_host = torch.randn((x_elems,), dtype=torch.float32).to(torch.bfloat16).pin_memory()
     y_host = torch.empty((y_elems,), dtype=torch.bfloat16).pin_memory()
     x_dev = x_host.to(dev)
@@ -260,7 +261,7 @@ def run_decode_gemv(args):
             step_e2e()
         secs_e2e = timed(step_e2e, args.steps)
 
-    bytes_step = decode_bytes_per_layer() * LAYERS
+    bytes_step = decode_bytes_per_layer() * layers
     value = world * bytes_step * args.steps / secs / 1e9
     e2e = world * bytes_step * args.steps / secs_e2e / 1e9
     moe_ep = None
@@ -282,8 +283,9 @@ def run_decode_gemv(args):
         "metric": "decode GEMV GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": "decode_gemv", "layers": LAYERS, "shapes": DECODE_SHAPES,
-                   "l2": "48 distinct weight sets, 10.76 GB per pass >> 126 MB L2", "multi_gpu": "replicas only"},
+        "config": {"workload": "decode_gemv", "layers": layers, "shapes": DECODE_SHAPES,
+                   "l2": f"{layers} distinct weight sets, {bytes_step / 1e9:.2f} GB per pass >> 126 MB L2",
+                   "multi_gpu": "replicas only"},
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": x_elems * 2, "d2h_bytes_per_step": y_elems * 2},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
@@ -297,7 +299,8 @@ def run_decode_gemv(args):
         line["other_workloads"] = {"moe_ep_stack": moe_ep}
     if world == 1 and not args.no_other_workloads:
         other = line["other_workloads"]
-        for name, fn in (("nvfp4_linear", bench_nvfp4_linear), ("moe_layer", bench_moe_layer)):
+        for name, fn in (("nvfp4_linear", bench_nvfp4_linear), ("prefill_gemm", bench_prefill_gemm),
+                         ("moe_layer", bench_moe_layer)):
             try:
                 other[name] = fn(lib, dev)
             except Exception as exc:  # a secondary workload must not take the headline line down
@@ -379,6 +382,48 @@ def bench_nvfp4_linear(lib, dev):
                          "peak_source": "nominal dense FP4 (9 PFLOP/s); MEASURED_PEAKS.json has no FP4 figure",
                          "frac_of_4x_measured_bf16_sustained": flops / t_gemm / 1e12 / (4 * 1391.3)},
             "l2": f"{copies} distinct weight sets in rotation, {copies * (n * k // 2 + n * k // 16) / 1e6:.0f} MB > 126 MB L2"}
+
+
+def bench_prefill_gemm(lib, dev):
+    """The 16,384-token prefill projections of one 12B-like layer (shapes of the prefill stack):
+    NVFP4 gate/up/down and FP8 QKV/O GEMMs on pre-quantised operands, each timed alone."""
+    import torch
+    m = 16384
+    out = {"metric": "prefill GEMM TFLOP/s", "tokens": m, "gemms": {}}
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + 2000)
+    for name, n, k, fp4 in (("gate_or_up", 15360, 3840, True), ("down", 3840, 15360, True),
+                            ("qkv", 8192, 3840, False), ("o", 3840, 4096, False)):
+        x = torch.randn((m, k), device=dev, generator=gen).to(torch.bfloat16)
+        w = (torch.randn((n, k), device=dev, generator=gen) * 0.02)
+        y = torch.empty((m, n), dtype=torch.int16, device=dev)
+        if fp4:
+            ga, gw = float(2688.0 / x.float().abs().max().item()), float(2688.0 / w.abs().max().item())
+            xq = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
+            xs = torch.zeros((lib.cdll.gemb_interleaved_scale_bytes(m, k),), dtype=torch.uint8, device=dev)
+            wq = torch.empty((n, k // 2), dtype=torch.uint8, device=dev)
+            ws = torch.zeros((lib.cdll.gemb_interleaved_scale_bytes(n, k),), dtype=torch.uint8, device=dev)
+            lib.gemb_nvfp4_quantize(x.view(torch.int16), 1, xq, xs, m, k, ga, 1, 0, None)
+            lib.gemb_nvfp4_quantize(w, 0, wq, ws, n, k, gw, 1, 0, None)
+            fn = lambda st: lib.gemb_nvfp4_gemm_bf16(xq, xs, wq, ws, y, m, n, k, ga, gw, st)
+            peak = 9000.0
+        else:
+            xq = torch.empty((m, k), dtype=torch.uint8, device=dev)
+            xs = torch.empty((m,), device=dev)
+            wq = torch.empty((n, k), dtype=torch.uint8, device=dev)
+            ws = torch.empty((n,), device=dev)
+            lib.gemb_fp8_quantize(x.view(torch.int16), 1, xq, xs, m, k, None)
+            lib.gemb_fp8_quantize(w, 0, wq, ws, n, k, None)
+            wsb = ws.to(torch.bfloat16).view(torch.int16)
+            fn = lambda st: lib.gemb_fp8_gemm_bf16(xq, xs, wq, wsb, y, m, n, k, st)
+            peak = 4500.0
+        del x, w
+        secs = graph_time(fn, 1, reps=10)
+        tf = 2.0 * m * n * k / secs / 1e12
+        out["gemms"][name] = {"rows": n, "k": k, "format": "nvfp4" if fp4 else "fp8", "us": secs * 1e6, "tflops": tf,
+                              "frac_of_nominal_dense_peak": tf / peak}
+    lib.gemb_check_device_status()
+    return out
 
 
 def bench_moe_layer(lib, dev, tokens=4096):
@@ -476,9 +521,21 @@ def main():
     ap.add_argument("--workload", default="decode_gemv", choices=["decode_gemv"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-workloads", action="store_true")
+    ap.add_argument("--layers", type=int, default=LAYERS,
+                    help="decode layers held on the device (48 = the benchmark; fewer for a small profiler capture)")
+    ap.add_argument("--only", default=None, choices=["nvfp4_linear", "moe_layer", "prefill_gemm"],
+                    help="run just one secondary workload on one GPU and print its JSON (profiling aid)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.only:
+        import torch
+        from gem16_b200 import load
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        fn = {"nvfp4_linear": bench_nvfp4_linear, "moe_layer": bench_moe_layer, "prefill_gemm": bench_prefill_gemm}[args.only]
+        print(json.dumps(fn(load(), dev)), flush=True)
         return
     run_decode_gemv(args)
 
