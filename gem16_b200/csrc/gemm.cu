@@ -65,6 +65,14 @@ struct GemmParams {
   const float* w_divisors;       // per-expert weight global divisors (null: alpha is used)
   float ga;                      // activation global divisor (with w_divisors)
   uint32_t experts;
+  // Gated epilogue (gated != 0): the weight rows interleave gate and up features in runs of 32
+  // (gemb_nvfp4_pack_gate_up), so every 64 accumulator columns hold 32 gate + 32 up values of
+  // the same features; the epilogue writes the NVFP4-quantised GELU product instead of bf16.
+  uint32_t gated;
+  float alpha_up;                // 1 / (ga * gw_up); `alpha` is the gate's
+  float g_product;               // input divisor of the down projection
+  uint8_t* out_packed;           // [M, n/4] payload of the product (n/2 features)
+  uint8_t* out_scales;           // interleaved scales of the product
   uint32_t debug;                // bit 0: skip loads, bit 1: skip MMAs, bit 2: skip epilogue (experiments only)
 };
 
@@ -339,6 +347,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const uint32_t c0 = min(col0 + 2 * lane, p.n - 2);
           ws_pair = __ldg(reinterpret_cast<const uint32_t*>(p.w_scales + c0));
         }
+        if (kFp4 && p.gated) {
+          // v0 = 32 gate values, v1 = 32 up values of features f0 .. f0+31 for this thread's token.
+          ptx::tc_wait_ld();
+          const uint32_t f0 = col0 / 2, inter = p.n / 2;
+          float alpha_g = row_scale, alpha_u = p.w_divisors != nullptr ? row_scale : p.alpha_up;
+          uint32_t words[4];
+          uint8_t sb[2];
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            float prod[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              // bf16 projection boundaries, bf16 GELU, bf16 product: src/cuda/nvfp4/reference.cu:177-190
+              const float gv = bf16_round(__fmul_rn(__uint_as_float(v0[b * 16 + i]), alpha_g));
+              const float uv = bf16_round(__fmul_rn(__uint_as_float(v1[b * 16 + i]), alpha_u));
+              const float inner = 0.7978845608028654f * (gv + 0.044715f * gv * gv * gv);
+              const float gelu = bf16_round(0.5f * gv * (1.0f + tanhf(inner)));
+              prod[i] = bf16_round(gelu * uv);
+            }
+            quantize_block16<false>(prod, p.g_product, words[2 * b], words[2 * b + 1], sb[b]);
+          }
+          const uint32_t row = row0 + lane;
+          if (row < p.m) {
+            *reinterpret_cast<uint4*>(p.out_packed + static_cast<uint64_t>(row) * (inter / 2) + f0 / 2) =
+                make_uint4(words[0], words[1], words[2], words[3]);
+            const uint32_t c_pad = (inter / 16 + 3) / 4 * 4;
+            *reinterpret_cast<uint16_t*>(p.out_scales + interleaved_scale_offset(row, f0 / 16, c_pad)) =
+                static_cast<uint16_t>(sb[0]) | (static_cast<uint16_t>(sb[1]) << 8);
+          }
+          continue;
+        }
         // The staging buffer about to be overwritten was handed to a TMA store two sub-tiles ago.
         if (lane == 0) ptx::bulk_wait_group_read<1>();
         __syncwarp();
@@ -476,7 +515,10 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
   CUtensorMap map_a, map_b, map_out;
   GEMB_TRY(make_byte_map(op, &map_a, a, p.m, row_bytes, BM));
   GEMB_TRY(make_byte_map(op, &map_b, b, static_cast<uint64_t>(p.n) * (p.plan ? p.experts : 1u), row_bytes, BN));
-  GEMB_TRY(make_out_map(op, &map_out, p.out, p.m, p.n));
+  if (p.gated)  // the tensor-map store path is unused; describe the payload buffer so the map is valid
+    GEMB_TRY(make_out_map(op, &map_out, p.out_packed, p.m, p.n / 8));
+  else
+    GEMB_TRY(make_out_map(op, &map_out, p.out, p.m, p.n));
   const uint32_t tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
   const unsigned grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(sm_count()));
   kern<<<grid, kFp4 ? kGemmThreadsFp4 : kGemmThreadsFp8, C::kSmemBytes, stream>>>(map_a, map_b, map_out, p);
@@ -578,6 +620,138 @@ int32_t gemb_moe_grouped_gemm_bf16(const uint8_t* act, const uint8_t* act_scales
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
   if (bn == 192) return launch_gemm<true, 192, 4, 2>(op, act, w, p, stream);
   return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Gate/up weight packing for the gated epilogue: output row (f / 32) * 64 + which * 32 + f % 32
+// holds feature f of the gate (which = 0) or up (which = 1) matrix; scales follow their rows and
+// are written in the interleaved layout.
+// ---------------------------------------------------------------------------------------------
+namespace gemb {
+namespace {
+__global__ void __launch_bounds__(256)
+pack_gate_up_kernel(const uint8_t* __restrict__ gate, const uint8_t* __restrict__ gate_s,
+                    const uint8_t* __restrict__ up, const uint8_t* __restrict__ up_s,
+                    uint8_t* __restrict__ out, uint8_t* __restrict__ out_s, uint32_t inter, uint32_t k) {
+  const uint32_t chunks = k / 32;                 // 16-byte payload chunks per row
+  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<uint64_t>(2) * inter * chunks) return;
+  const uint32_t orow = static_cast<uint32_t>(idx / chunks), c = static_cast<uint32_t>(idx % chunks);
+  const uint32_t which = (orow / 32) & 1, f = (orow / 64) * 32 + orow % 32;
+  const uint8_t* src = (which ? up : gate) + static_cast<uint64_t>(f) * (k / 2) + c * 16;
+  const uint8_t* ssrc = (which ? up_s : gate_s) + static_cast<uint64_t>(f) * (k / 16) + c * 2;
+  *reinterpret_cast<uint4*>(out + static_cast<uint64_t>(orow) * (k / 2) + c * 16) = __ldg(reinterpret_cast<const uint4*>(src));
+  const uint32_t c_pad = (k / 16 + 3) / 4 * 4;
+  *reinterpret_cast<uint16_t*>(out_s + interleaved_scale_offset(orow, c * 2, c_pad)) =
+      __ldg(reinterpret_cast<const uint16_t*>(ssrc));
+}
+}  // namespace
+}  // namespace gemb
+
+extern "C" int32_t gemb_nvfp4_pack_gate_up(const uint8_t* gate_packed, const uint8_t* gate_scales,
+                                           const uint8_t* up_packed, const uint8_t* up_scales,
+                                           uint8_t* fused_packed, uint8_t* fused_interleaved_scales,
+                                           uint64_t intermediate, uint64_t k, gemb_stream_t stream) {
+  const char* op = "gemb_nvfp4_pack_gate_up";
+  GEMB_REQUIRE(gate_packed && gate_scales && up_packed && up_scales && fused_packed && fused_interleaved_scales,
+               "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(intermediate > 0 && intermediate % 32 == 0 && intermediate < (1ull << 30),
+               "%s: intermediate size must be a nonzero multiple of 32", op);
+  GEMB_REQUIRE(k > 0 && k % 64 == 0 && k < (1ull << 31), "%s: contracting extent must be a nonzero multiple of 64", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(gate_packed) % 16 == 0 && reinterpret_cast<uintptr_t>(up_packed) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(fused_packed) % 16 == 0 && reinterpret_cast<uintptr_t>(gate_scales) % 2 == 0 &&
+                   reinterpret_cast<uintptr_t>(up_scales) % 2 == 0 && reinterpret_cast<uintptr_t>(fused_interleaved_scales) % 4 == 0,
+               "%s: payloads must be 16-byte, scales 2-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  cudaError_t e = cudaMemsetAsync(fused_interleaved_scales, 0, gemb_interleaved_scale_bytes(2 * intermediate, k), stream);
+  if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+  const uint64_t work = 2 * intermediate * (k / 32);
+  pack_gate_up_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+      gate_packed, gate_scales, up_packed, up_scales, fused_packed, fused_interleaved_scales,
+      static_cast<uint32_t>(intermediate), static_cast<uint32_t>(k));
+  return check_launch(op);
+}
+
+static int32_t launch_gated(const char* op, const uint8_t* act, const uint8_t* w, GemmParams& p, cudaStream_t stream) {
+  const int bn = g_gemm_bn ? g_gemm_bn : 256;
+  if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
+  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);   // 192 is not a multiple of 64 gate/up runs per tile pair
+}
+
+int32_t gemb_nvfp4_gemm_gated_quant(const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* w_fused,
+                                    const uint8_t* w_scales_interleaved, uint8_t* product_packed,
+                                    uint8_t* product_interleaved_scales, uint64_t tokens, uint64_t intermediate,
+                                    uint64_t k, float ga, float gw_gate, float gw_up, float product_divisor,
+                                    gemb_stream_t stream) {
+  const char* op = "gemb_nvfp4_gemm_gated_quant";
+  GEMB_REQUIRE(act && act_scales_interleaved && w_fused && w_scales_interleaved && product_packed && product_interleaved_scales,
+               "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_gemm(op, tokens, 2 * intermediate, k, 64));
+  GEMB_REQUIRE(intermediate % 32 == 0, "%s: intermediate size must be a multiple of 32", op);
+  GEMB_REQUIRE(positive_finite(ga) && positive_finite(gw_gate) && positive_finite(gw_up) && positive_finite(product_divisor) &&
+                   std::isfinite(ga * gw_gate) && std::isfinite(ga * gw_up),
+               "%s: global divisors must be positive and finite", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w_fused) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(act_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(w_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(product_packed) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(product_interleaved_scales) % 4 == 0,
+               "%s: all buffers must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  GemmParams p{};
+  p.sfa = act_scales_interleaved;
+  p.sfb = w_scales_interleaved;
+  p.m = static_cast<uint32_t>(tokens);
+  p.n = static_cast<uint32_t>(2 * intermediate);
+  p.k = static_cast<uint32_t>(k);
+  p.alpha = 1.0f / (ga * gw_gate);
+  p.alpha_up = 1.0f / (ga * gw_up);
+  p.gated = 1;
+  p.g_product = product_divisor;
+  p.out_packed = product_packed;
+  p.out_scales = product_interleaved_scales;
+  p.debug = g_gemm_debug;
+  return launch_gated(op, act, w_fused, p, stream);
+}
+
+int32_t gemb_moe_grouped_gemm_gated_quant(const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* w_fused,
+                                          const uint8_t* w_scales_interleaved, uint8_t* product_packed,
+                                          uint8_t* product_interleaved_scales, const int32_t* plan,
+                                          uint64_t padded_rows_max, uint64_t experts, uint64_t intermediate, uint64_t k,
+                                          float ga, const float* w_divisors, float product_divisor, gemb_stream_t stream) {
+  const char* op = "gemb_moe_grouped_gemm_gated_quant";
+  GEMB_REQUIRE(act && act_scales_interleaved && w_fused && w_scales_interleaved && product_packed &&
+                   product_interleaved_scales && plan && w_divisors,
+               "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_gemm(op, padded_rows_max, 2 * intermediate, k, 64));
+  GEMB_REQUIRE(padded_rows_max % 128 == 0, "%s: padded row capacity must be a multiple of 128", op);
+  GEMB_REQUIRE((2 * intermediate) % 128 == 0, "%s: intermediate size must be a multiple of 64", op);
+  GEMB_REQUIRE(experts > 0 && experts <= 4096 && experts * 2 * intermediate < (1ull << 31), "%s: bad expert count", op);
+  GEMB_REQUIRE(positive_finite(ga) && positive_finite(product_divisor), "%s: global divisors must be positive and finite", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w_fused) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(act_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(w_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(product_packed) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(product_interleaved_scales) % 4 == 0,
+               "%s: all buffers must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  GemmParams p{};
+  p.sfa = act_scales_interleaved;
+  p.sfb = w_scales_interleaved;
+  p.m = static_cast<uint32_t>(padded_rows_max);
+  p.n = static_cast<uint32_t>(2 * intermediate);
+  p.k = static_cast<uint32_t>(k);
+  p.plan = plan;
+  p.w_divisors = w_divisors;
+  p.ga = ga;
+  p.experts = static_cast<uint32_t>(experts);
+  p.alpha = 1.0f;
+  p.gated = 1;
+  p.g_product = product_divisor;
+  p.out_packed = product_packed;
+  p.out_scales = product_interleaved_scales;
+  p.debug = g_gemm_debug;
+  return launch_gated(op, act, w_fused, p, stream);
 }
 
 int32_t gemb_fp8_gemm_bf16(const uint8_t* act, const float* act_scales, const uint8_t* w,

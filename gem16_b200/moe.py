@@ -29,6 +29,7 @@ class MoeWeights:
         self.dn_div = torch.as_tensor(dn_div, device=dev, dtype=torch.float32).contiguous()
         self.gu_scales = self._interleave(lib, gu_scales, self.two_inter, self.hidden)
         self.dn_scales = self._interleave(lib, dn_scales, self.hidden, self.inter)
+        self.gu_fused, self.gu_fused_scales = self._fuse(lib, self.gu_packed, gu_scales, self.inter, self.hidden)
         self.shared = None
         if shared is not None:
             (sg_p, sg_s, sg_d), (sd_p, sd_s, sd_d) = shared
@@ -39,6 +40,21 @@ class MoeWeights:
                 "dn_scales": self._interleave(lib, sd_s[None], self.hidden, sd_p.shape[1] * 2),
                 "inter": sg_p.shape[0] // 2,
             }
+            f, fs = self._fuse(lib, self.shared["gu_packed"][None], sg_s[None], sg_p.shape[0] // 2, self.hidden)
+            self.shared["gu_fused"], self.shared["gu_fused_scales"] = f[0], fs[0]
+
+    def _fuse(self, lib, packed, compact, inter, k):
+        """Per expert: gate rows [0, inter) and up rows [inter, 2*inter) -> the 32-feature
+        interleaved layout the gated-epilogue GEMM consumes."""
+        compact = torch.as_tensor(compact, device=self.dev).contiguous()
+        n = packed.shape[0]
+        out = torch.empty_like(packed)
+        per = lib.cdll.gemb_interleaved_scale_bytes(2 * inter, k)
+        out_s = torch.empty((n, per), dtype=torch.uint8, device=self.dev)
+        for e in range(n):
+            lib.gemb_nvfp4_pack_gate_up(packed[e, :inter], compact[e, :inter], packed[e, inter:], compact[e, inter:],
+                                        out[e], out_s[e], inter, k, None)
+        return out, out_s
 
     def _interleave(self, lib, compact, rows, k):
         compact = torch.as_tensor(compact, device=self.dev).contiguous()
@@ -56,6 +72,9 @@ class MoeLayer:
                  allocate_experts: bool = True):
         self.lib = load()
         self.side = None
+        # gate/up GEMM + GELU + requantisation in one kernel: byte-identical, but with four epilogue
+        # warps the extra arithmetic is not hidden yet, so the three-launch form is the default.
+        self.fused = False
         self.w, self.tokens, self.topk = weights, tokens, topk
         self.ga, self.ga_dn, self.ga_sh_dn = ga, ga_dn, ga_sh_dn
         lib, dev, w = self.lib, weights.dev, weights
@@ -86,7 +105,7 @@ class MoeLayer:
             self.s_packed = torch.empty((tokens, h // 2), **u8)
             self.s_scales = torch.zeros((c.gemb_interleaved_scale_bytes(tokens, h),), **u8)
             self.s_gate_up = torch.empty((tokens, 2 * si), dtype=torch.int16, device=dev)
-            self.s_p_packed = torch.empty((tokens, si // 2), **u8)
+            self.s_p_packed = torch.zeros((tokens, si // 2), **u8)
             self.s_p_scales = torch.zeros((c.gemb_interleaved_scale_bytes(tokens, si),), **u8)
             self.s_out = torch.empty((tokens, h), dtype=torch.int16, device=dev)
 
@@ -101,6 +120,13 @@ class MoeLayer:
         lib, w, t = self.lib, self.w, self.tokens
         lib.gemb_moe_dispatch_quantize(x_bf16, self.slot_rows, self.a_packed, self.a_scales, t, w.hidden, self.topk,
                                        self.ga, stream)
+        if self.fused:
+            lib.gemb_moe_grouped_gemm_gated_quant(self.a_packed, self.a_scales, w.gu_fused, w.gu_fused_scales,
+                                                  self.p_packed, self.p_scales, self.plan, self.rows_max, w.experts,
+                                                  w.inter, w.hidden, self.ga, w.gu_div, self.ga_dn, stream)
+            lib.gemb_moe_grouped_gemm_bf16(self.p_packed, self.p_scales, w.dn_packed, w.dn_scales, self.y, self.plan,
+                                           self.rows_max, w.experts, w.hidden, w.inter, self.ga_dn, w.dn_div, stream)
+            return
         lib.gemb_moe_grouped_gemm_bf16(self.a_packed, self.a_scales, w.gu_packed, w.gu_scales, self.gate_up, self.plan,
                                        self.rows_max, w.experts, 2 * w.inter, w.hidden, self.ga, w.gu_div, stream)
         lib.gemb_moe_expert_gelu_quantize(self.gate_up, self.plan, self.p_packed, self.p_scales, self.rows_max, w.inter,
@@ -111,6 +137,13 @@ class MoeLayer:
     def shared_branch(self, x_bf16, stream=None):
         lib, w, t, s = self.lib, self.w, self.tokens, self.w.shared
         lib.gemb_nvfp4_quantize(x_bf16, 1, self.s_packed, self.s_scales, t, w.hidden, self.ga, 1, 0, stream)
+        if self.fused:
+            lib.gemb_nvfp4_gemm_gated_quant(self.s_packed, self.s_scales, s["gu_fused"], s["gu_fused_scales"],
+                                            self.s_p_packed, self.s_p_scales, t, s["inter"], w.hidden, self.ga,
+                                            s["gu_div"], s["gu_div"], self.ga_sh_dn, stream)
+            lib.gemb_nvfp4_gemm_bf16(self.s_p_packed, self.s_p_scales, s["dn_packed"], s["dn_scales"], self.s_out, t,
+                                     w.hidden, s["inter"], self.ga_sh_dn, s["dn_div"], stream)
+            return
         lib.gemb_nvfp4_gemm_bf16(self.s_packed, self.s_scales, s["gu_packed"], s["gu_scales"], self.s_gate_up, t,
                                  2 * s["inter"], w.hidden, self.ga, s["gu_div"], stream)
         lib.gemb_moe_expert_gelu_quantize(self.s_gate_up, None, self.s_p_packed, self.s_p_scales, t, s["inter"],

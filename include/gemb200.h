@@ -209,6 +209,36 @@ int32_t gemb_nvfp4_gemm_bf16(const uint8_t* packed_activation_e2m1,
                              float activation_global_divisor, float weight_global_divisor,
                              gemb_stream_t stream);
 
+/* Gate and Up projections, GELU and requantisation in ONE kernel.  The fused weight holds the
+ * gate and up rows interleaved in runs of 32 features (gemb_nvfp4_pack_gate_up), so each token's
+ * accumulator row carries gate and up of the same features side by side and the epilogue emits
+ * product = bf16(bf16(gelu_tanh(bf16(gate))) * bf16(up)) already NVFP4-quantised (EXACT contract)
+ * with the down projection's input divisor: payload [tokens, intermediate/2] + INTERLEAVED
+ * scales, byte-identical to gemb_nvfp4_gemm_bf16 (gate), (up) + gemb_nvfp4_gated_gelu_quantize.
+ * intermediate % 32 == 0, K % 64 == 0.
+ * Replaces LaunchNvfp4CutlassProjectionBf16Batch (gate) + LaunchNvfp4CutlassUpGatedGeluQuantizedBatch,
+ * src/cuda/nvfp4/cutlass_sm120.h:24-66 (the reference fuses only the Up GEMM with the epilogue and
+ * reads a materialised bf16 Gate; here neither projection is written to memory). */
+int32_t gemb_nvfp4_gemm_gated_quant(const uint8_t* packed_activation_e2m1,
+                                    const uint8_t* interleaved_activation_scales,
+                                    const uint8_t* fused_gate_up_weight,
+                                    const uint8_t* fused_interleaved_weight_scales,
+                                    uint8_t* product_packed_e2m1, uint8_t* product_interleaved_scales,
+                                    uint64_t tokens, uint64_t intermediate,
+                                    uint64_t contracting_elements, float activation_global_divisor,
+                                    float gate_weight_global_divisor, float up_weight_global_divisor,
+                                    float product_global_divisor, gemb_stream_t stream);
+
+/* Builds the fused gate/up weight of gemb_nvfp4_gemm_gated_quant from the two row-major NVFP4
+ * matrices [intermediate, K/2] with COMPACT scales: output row (f/32)*64 + which*32 + f%32 holds
+ * feature f of gate (which = 0) or up (which = 1); output scales are INTERLEAVED.  A load-time
+ * step, the counterpart of the reference's host tiler (src/cuda/nvfp4/sm120_layout.cpp:58-145). */
+int32_t gemb_nvfp4_pack_gate_up(const uint8_t* gate_packed, const uint8_t* gate_scales,
+                                const uint8_t* up_packed, const uint8_t* up_scales,
+                                uint8_t* fused_packed, uint8_t* fused_interleaved_scales,
+                                uint64_t intermediate, uint64_t contracting_elements,
+                                gemb_stream_t stream);
+
 /* FP8 W8A8: out = bf16( ((sum_k qa qw) * a_scale[token]) * bf16(w_scale[row]) ).  K % 32 == 0,
  * rows % 8 == 0.  Replaces LaunchFp8CutlassProjectionBatch, src/cuda/fp8/cutlass_sm120.h:17-28
  * (no workspace needed). */
@@ -314,6 +344,23 @@ int32_t gemb_moe_grouped_gemm_bf16(const uint8_t* packed_activation_e2m1,
                                    uint64_t rows_per_expert, uint64_t contracting_elements,
                                    float activation_global_divisor, const float* weight_global_divisors,
                                    gemb_stream_t stream);
+
+/* Grouped form of gemb_nvfp4_gemm_gated_quant: per-expert fused gate/up weights
+ * [experts, 2*intermediate, K/2] (each packed with gemb_nvfp4_pack_gate_up), one weight divisor per
+ * expert; output = quantised product rows [padded_rows_max, intermediate/2] + INTERLEAVED scales,
+ * ready for the grouped down projection.  Fuses "grouped W13 -> activation + W2 input
+ * quantization" of docs/plans/gemma4-26b/specs/MOE_PREFILL_KERNEL_SPEC.md:34-47. */
+int32_t gemb_moe_grouped_gemm_gated_quant(const uint8_t* packed_activation_e2m1,
+                                          const uint8_t* interleaved_activation_scales,
+                                          const uint8_t* fused_gate_up_weights,
+                                          const uint8_t* fused_interleaved_weight_scales,
+                                          uint8_t* product_packed_e2m1,
+                                          uint8_t* product_interleaved_scales, const int32_t* plan,
+                                          uint64_t padded_rows_max, uint64_t experts,
+                                          uint64_t intermediate, uint64_t contracting_elements,
+                                          float activation_global_divisor,
+                                          const float* weight_global_divisors,
+                                          float product_global_divisor, gemb_stream_t stream);
 
 /* Expert activation boundary on the padded rows: gate_up bf16 [rows, 2*intermediate] (gate first),
  * product = bf16(bf16(gelu_tanh(gate)) * up), NVFP4-quantised (EXACT contract) with the down

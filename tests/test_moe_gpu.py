@@ -143,3 +143,32 @@ def test_layer_real_dims(lib, dev, orc):
     for a, b in zip(first, (layer.ids, layer.weights, layer.perm, layer.out)):
         assert torch.equal(a, b)
     assert int(to_np(layer.counts).sum()) == 64 * 8
+
+
+def test_fused_gated_epilogue_is_byte_identical(lib, dev, orc):
+    # One kernel (gate/up GEMM + GELU + requantisation) against the three-launch form, on the
+    # expert path (grouped, K = hidden) and the shared branch (rows not a multiple of 128).
+    rng = np.random.default_rng(21)
+    tokens, hidden, experts, inter, shared_inter, topk = 300, 2816, 128, 704, 2112, 8
+    from gem16_b200.moe import synthetic_weights
+    w = synthetic_weights(dev, 5, hidden, experts, inter, shared_inter)
+    x = to_dev(bf16_bits(rng.standard_normal((tokens, hidden)).astype(np.float32)), dev)
+    layer = MoeLayer(w, tokens, topk, 700.0, 336.0, 336.0)
+    results = []
+    for fused in (False, True):
+        layer.fused = fused
+        for t in (layer.p_packed, layer.p_scales, layer.s_p_packed, layer.s_p_scales):
+            t.zero_()
+        out = layer.forward(x).clone()
+        torch.cuda.synchronize()
+        lib.gemb_check_device_status()
+        rows = layer.slot_rows.long()
+        blocks = torch.arange(inter // 16, device=dev)
+        # scales of the valid rows only (padding rows of the padded space hold garbage by design)
+        c_pad = (inter // 16 + 3) // 4 * 4
+        off = ((rows[:, None] // 128) * (c_pad // 4) + blocks[None, :] // 4) * 512 + (rows[:, None] % 32) * 16 \
+            + ((rows[:, None] % 128) // 32) * 4 + blocks[None, :] % 4
+        results.append((layer.p_packed[rows].clone(), layer.p_scales[off].clone(), layer.s_p_packed.clone(),
+                        layer.s_p_scales.clone(), layer.y[rows].clone(), out))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
