@@ -200,17 +200,30 @@ def run_decode_gemv(args):
     x_dev = x_host.to(dev)
     y_dev = torch.zeros((y_elems,), device=dev, dtype=torch.bfloat16)
 
+    # "fused": one launch per projection, the bf16 activation is quantised inside the GEMV.
+    # "split": the decode-size token quantizer, then the GEMV on E4M3 bytes (fp32 out); with
+    # programmatic dependent launch the GEMV prefetches weights while the quantizer runs.
+    split = args.decode_path == "split"
+    xq_dev = torch.empty((x_elems,), dtype=torch.uint8, device=dev)
+    xs_dev = torch.empty((layers * len(DECODE_SHAPES),), device=dev)
+    y32_dev = torch.zeros((y_elems,), device=dev) if split else None
+    y_host32 = torch.empty((y_elems,), dtype=torch.float32).pin_memory() if split else None
+
     def enqueue_pass():
         xo = yo = 0
         n = 0
+        st = torch.cuda.current_stream()
         for mats in weights:
             for (wq, ws), (_, rows, k) in zip(mats, DECODE_SHAPES):
-                lib.gemb_fp8_gemv_bf16in(x_dev[xo:xo + k], wq, ws, y_dev[yo:yo + rows], 1, rows, k,
-                                         torch.cuda.current_stream())
+                if split:
+                    lib.gemb_fp8_quantize(x_dev[xo:xo + k], 1, xq_dev[xo:xo + k], xs_dev[n:n + 1], 1, k, st)
+                    lib.gemb_fp8_gemv(xq_dev[xo:xo + k], xs_dev[n:n + 1], wq, ws, y32_dev[yo:yo + rows], rows, k, st)
+                else:
+                    lib.gemb_fp8_gemv_bf16in(x_dev[xo:xo + k], wq, ws, y_dev[yo:yo + rows], 1, rows, k, st)
                 xo += k
                 yo += rows
                 n += 1
-        return n
+        return n * (2 if split else 1)
 
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
@@ -247,7 +260,7 @@ def run_decode_gemv(args):
         def step_e2e():
             x_dev.copy_(x_host, non_blocking=True)
             graph.replay()
-            y_host.copy_(y_dev, non_blocking=True)
+            (y_host32 if split else y_host).copy_(y32_dev if split else y_dev, non_blocking=True)
             stream.synchronize()
 
         for _ in range(max(args.warmup, 3)):
@@ -285,11 +298,11 @@ def run_decode_gemv(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": "decode_gemv", "layers": layers, "shapes": DECODE_SHAPES,
                    "l2": f"{layers} distinct weight sets, {bytes_step / 1e9:.2f} GB per pass >> 126 MB L2",
-                   "multi_gpu": "replicas only"},
-        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": x_elems * 2, "d2h_bytes_per_step": y_elems * 2},
+                   "multi_gpu": "replicas only", "decode_path": args.decode_path},
+        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": x_elems * 2, "d2h_bytes_per_step": y_elems * (4 if split else 2)},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "fp8_gemv_kernel (bf16-in fused quantisation)",
+        "roofline": {"bound": "hbm", "kernel": "fp8_gemv_kernel" + (" + fp8_quantize_decode_kernel" if split else " (bf16-in fused quantisation)"),
                      "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                      "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": None,
@@ -300,7 +313,7 @@ def run_decode_gemv(args):
     if world == 1 and not args.no_other_workloads:
         other = line["other_workloads"]
         for name, fn in (("nvfp4_linear", bench_nvfp4_linear), ("prefill_gemm", bench_prefill_gemm),
-                         ("moe_layer", bench_moe_layer)):
+                         ("prefill_stack", bench_prefill_stack), ("moe_layer", bench_moe_layer)):
             try:
                 other[name] = fn(lib, dev)
             except Exception as exc:  # a secondary workload must not take the headline line down
@@ -426,6 +439,71 @@ def bench_prefill_gemm(lib, dev):
     return out
 
 
+def bench_prefill_stack(lib, dev, layers=48, tokens=16384):
+    """Dense 12B-like prefill linear stack: per layer FP8 QKV and O projections and the NVFP4 gated
+    MLP, every activation quantiser inside the timed region (attention itself is replaced by a
+    seeded bf16 tensor: it is not part of this path)."""
+    import torch
+    h, qkv, ao, inter = 3840, 8192, 4096, 15360
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + 2500)
+    c = lib.cdll
+
+    def fp8_w(n, k):
+        w = torch.randn((n, k), device=dev, generator=gen) * 0.02
+        q = torch.empty((n, k), dtype=torch.uint8, device=dev)
+        s = torch.empty((n,), device=dev)
+        lib.gemb_fp8_quantize(w, 0, q, s, n, k, None)
+        return q, s.to(torch.bfloat16).view(torch.int16)
+
+    def fp4_w(n, k):
+        w = torch.randn((n, k), device=dev, generator=gen) * 0.02
+        g = float(2688.0 / w.abs().max().item())
+        q = torch.empty((n, k // 2), dtype=torch.uint8, device=dev)
+        s = torch.zeros((c.gemb_interleaved_scale_bytes(n, k),), dtype=torch.uint8, device=dev)
+        lib.gemb_nvfp4_quantize(w, 0, q, s, n, k, g, 1, 0, None)
+        return q, s, g
+
+    weights = [(fp8_w(qkv, h), fp8_w(h, ao), fp4_w(inter, h), fp4_w(inter, h), fp4_w(h, inter)) for _ in range(layers)]
+    x = torch.randn((tokens, h), device=dev, generator=gen).to(torch.bfloat16).view(torch.int16)
+    attn = torch.randn((tokens, ao), device=dev, generator=gen).to(torch.bfloat16).view(torch.int16)
+    u8 = dict(dtype=torch.uint8, device=dev)
+    xq, xs = torch.empty((tokens, h), **u8), torch.empty((tokens,), device=dev)
+    aq, as_ = torch.empty((tokens, ao), **u8), torch.empty((tokens,), device=dev)
+    y_qkv = torch.empty((tokens, qkv), dtype=torch.int16, device=dev)
+    y_o = torch.empty((tokens, h), dtype=torch.int16, device=dev)
+    oq = torch.empty((tokens, h // 2), **u8)
+    os_ = torch.zeros((c.gemb_interleaved_scale_bytes(tokens, h),), **u8)
+    gate = torch.empty((tokens, inter), dtype=torch.int16, device=dev)
+    up = torch.empty((tokens, inter), dtype=torch.int16, device=dev)
+    pq = torch.empty((tokens, inter // 2), **u8)
+    ps = torch.zeros((c.gemb_interleaved_scale_bytes(tokens, inter),), **u8)
+    out = torch.empty((tokens, h), dtype=torch.int16, device=dev)
+    ga_mlp, ga_dn = 2688.0 / 0.6, 2688.0 / 0.05   # static input divisors (checkpoint-style constants)
+
+    def run(st):
+        for (wq, wqs), (wo, wos), (wg, wgs, gg), (wu, wus, gu), (wd, wds, gd) in weights:
+            lib.gemb_fp8_quantize(x, 1, xq, xs, tokens, h, st)
+            lib.gemb_fp8_gemm_bf16(xq, xs, wq, wqs, y_qkv, tokens, qkv, h, st)
+            lib.gemb_fp8_quantize(attn, 1, aq, as_, tokens, ao, st)
+            lib.gemb_fp8_gemm_bf16(aq, as_, wo, wos, y_o, tokens, h, ao, st)
+            lib.gemb_nvfp4_quantize(y_o, 1, oq, os_, tokens, h, ga_mlp, 1, 0, st)
+            lib.gemb_nvfp4_gemm_bf16(oq, os_, wg, wgs, gate, tokens, inter, h, ga_mlp, gg, st)
+            lib.gemb_nvfp4_gemm_bf16(oq, os_, wu, wus, up, tokens, inter, h, ga_mlp, gu, st)
+            lib.gemb_nvfp4_gated_gelu_quantize(gate, up, 1, pq, ps, tokens, inter, ga_dn, 1, 0, st)
+            lib.gemb_nvfp4_gemm_bf16(pq, ps, wd, wds, out, tokens, h, inter, ga_dn, gd, st)
+
+    secs = graph_time(run, 9 * layers, reps=3)
+    lib.gemb_check_device_status()
+    fp8_flops = 2.0 * tokens * (qkv * h + h * ao)
+    fp4_flops = 2.0 * tokens * 3 * inter * h
+    return {"metric": "prefill linear stack TFLOP/s", "workload": f"{layers} layers x 16,384 tokens: FP8 QKV+O, NVFP4 gate/up/down, quantisers timed",
+            "ms_per_stack": secs * 1e3, "ms_per_layer": secs * 1e3 / layers, "tokens_per_s": tokens / secs,
+            "tflops_total": (fp8_flops + fp4_flops) * layers / secs / 1e12,
+            "flops_per_layer": {"fp8": fp8_flops, "nvfp4": fp4_flops},
+            "ideal_ms_per_layer_at_nominal_peaks": (fp8_flops / 4.5e15 + fp4_flops / 9e15) * 1e3}
+
+
 def bench_moe_layer(lib, dev, tokens=4096):
     import torch
     from gem16_b200.moe import MoeLayer, synthetic_weights
@@ -519,11 +597,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_gemv", choices=["decode_gemv"])
+    ap.add_argument("--decode-path", default="split", choices=["fused", "split"],
+                    help="decode GEMV set: activation quantisation fused into the GEMV, or quantizer + GEMV launches")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-workloads", action="store_true")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="decode layers held on the device (48 = the benchmark; fewer for a small profiler capture)")
-    ap.add_argument("--only", default=None, choices=["nvfp4_linear", "moe_layer", "prefill_gemm"],
+    ap.add_argument("--only", default=None, choices=["nvfp4_linear", "moe_layer", "prefill_gemm", "prefill_stack"],
                     help="run just one secondary workload on one GPU and print its JSON (profiling aid)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -534,7 +614,8 @@ def main():
         from gem16_b200 import load
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(dev)
-        fn = {"nvfp4_linear": bench_nvfp4_linear, "moe_layer": bench_moe_layer, "prefill_gemm": bench_prefill_gemm}[args.only]
+        fn = {"nvfp4_linear": bench_nvfp4_linear, "moe_layer": bench_moe_layer, "prefill_gemm": bench_prefill_gemm,
+              "prefill_stack": bench_prefill_stack}[args.only]
         print(json.dumps(fn(load(), dev)), flush=True)
         return
     run_decode_gemv(args)

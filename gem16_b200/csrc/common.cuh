@@ -25,6 +25,10 @@ int32_t require_sm100(const char* op);
 int sm_count();
 // Tuning knobs owned by the GEMM translation unit (see gemb_set_tuning).
 int32_t gemm_set_tuning(int32_t knob, int32_t value);
+// Decode-size FP8 token quantizer (bf16 input, K <= 16384, K % 8 == 0); bit-identical to the
+// general kernel, one global round trip, programmatic-dependent-launch aware.
+int32_t launch_fp8_quantize_decode(const char* op, const uint16_t* x, uint8_t* out, float* scales, uint64_t tokens,
+                                   uint64_t k, cudaStream_t stream);
 // Reads and clears the decode GEMV's bounded-wait flag (0 = clean, -1 = could not read).
 int gemv_take_device_error();
 

@@ -13,10 +13,11 @@
 //   warp 1   MMA issuer: owns the 512 TMEM columns; per stage issues one tcgen05.mma per 32
 //            bytes of K and commits the stage's empty barrier; after the last K step commits
 //            the accumulator barrier;
-//   warps 2-5 epilogue: each warp drains its 32 TMEM lanes 64 columns at a time (two
+//   warps 2-5 and the last four warps: epilogue, two sets of four; each warp drains its 32 TMEM
+//            lanes 64 columns at a time, the sets taking alternate 64-column sub-tiles (two
 //            tcgen05.ld in flight), scales, rounds to bf16, writes a 32 x 128-byte block into
 //            its own swizzled staging buffer and issues a TMA store (which also clips the
-//            token / row tails); staging is double buffered per warp.  With kAccStages = 2 the
+//            token / row tails).  With kAccStages = 2 the
 //            accumulators are double buffered in TMEM so the epilogue of tile i overlaps the
 //            main loop of tile i+1.
 //   warps 6-9 (NVFP4 only) scale movers: each copies the stage's block scales from shared
@@ -47,8 +48,8 @@ __device__ int g_gemm_error = 0;
 
 namespace {
 
-constexpr int kGemmThreadsFp8 = 192;   // producer, MMA, 4 epilogue warps
-constexpr int kGemmThreadsFp4 = 320;   // + 4 scale-mover warps
+constexpr int kGemmThreadsFp8 = 320;   // producer, MMA, 2 x 4 epilogue warps
+constexpr int kGemmThreadsFp4 = 448;   // producer, MMA, 4 epilogue, 4 scale movers, 4 more epilogue warps
 constexpr int BM = 128;
 
 struct GemmParams {
@@ -143,7 +144,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     for (int s = 0; s < kAccStages; ++s) {
       ptx::mbar_init(&acc_full[s], 1);
-      ptx::mbar_init(&acc_empty[s], 4);
+      ptx::mbar_init(&acc_empty[s], 8);
     }
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -268,7 +269,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
       }
     }
-  } else if (warp >= 6) {
+  } else if (kFp4 && warp >= 6 && warp < 10) {
     // ------------------------------- scale movers (NVFP4) ------------------------------------
     if constexpr (kFp4) {
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -321,9 +322,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
   } else {
     // ------------------------------- epilogue -------------------------------------------------
+    // Two sets of four warps; set s drains the 64-column sub-tiles s, s+2, ... of every tile.
     const uint32_t quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    uint8_t* my_stage = epi_stage + quarter * 8192;
-    uint32_t as = 0, aphase = 0, buf = 0;
+    const uint32_t set = warp >= 6 ? 1u : 0u;
+    uint8_t* my_stage = epi_stage + (set * 4 + quarter) * 4096;
+    uint32_t as = 0, aphase = 0;
     for (uint32_t tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
       uint32_t mt, nt;
       tile_coords(tile, mt, nt);
@@ -336,7 +339,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         row_scale = __fdiv_rn(1.0f, __fmul_rn(p.ga, __ldg(p.w_divisors + (tile_expert ? __ldg(tile_expert + mt) : 0))));
       const uint32_t tmem_acc = tmem_base + as * BN + ((quarter * 32) << 16);
 #pragma unroll 1
-      for (uint32_t c = 0; c < BN / 64; ++c) {
+      for (uint32_t c = set; c < BN / 64; c += 2) {
         const uint32_t col0 = nt * BN + c * 64;
         if (col0 >= p.n || row0 >= p.m || (p.debug & 4)) break;  // warp-uniform
         uint32_t v0[32], v1[32];
@@ -378,11 +381,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
           continue;
         }
-        // The staging buffer about to be overwritten was handed to a TMA store two sub-tiles ago.
-        if (lane == 0) ptx::bulk_wait_group_read<1>();
+        // The staging buffer about to be overwritten was handed to a TMA store one sub-tile ago.
+        if (lane == 0) ptx::bulk_wait_group_read<0>();
         __syncwarp();
         ptx::tc_wait_ld();
-        uint8_t* sbuf = my_stage + buf * 4096;
+        uint8_t* sbuf = my_stage;
         auto convert = [&](const uint32_t (&v)[32], int half) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -417,7 +420,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           ptx::tma_store_2d(&map_out, sbuf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
           ptx::bulk_commit_group();
         }
-        buf ^= 1;
       }
       ptx::tc_fence_before();
       __syncwarp();

@@ -820,7 +820,77 @@ int32_t validate_nvfp4_gemv(const char* op, uint64_t rows, uint64_t k, float ga,
   return GEMB_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode-time FP8 token quantizer: one 1024-thread CTA per token, the token held in registers
+// between the amax pass and the conversion (one global round trip), quotients through
+// quotient_for_e4m3 (bit-identical to the IEEE division of src/numeric/fp8.cpp:41-58).  It
+// triggers its dependents at once and waits for its predecessor before touching the
+// activation, so under programmatic dependent launch the GEMV that follows can prefetch its
+// weights while this kernel runs.  bf16 input, K <= 16384, K % 8 == 0.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+fp8_quantize_decode_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ out,
+                           float* __restrict__ scales, uint32_t k) {
+  __shared__ float red[32];
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint64_t t = blockIdx.x;
+  const uint4* xp = reinterpret_cast<const uint4*>(x + t * k);
+  const uint32_t chunks = k / 8;
+  uint4 v[2];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const uint32_t c = threadIdx.x + i * 1024;
+    v[i] = c < chunks ? __ldg(xp + c) : make_uint4(0, 0, 0, 0);
+    amax = fmaxf(amax, chunk_amax(v[i]));
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 32; ++i) amax = fmaxf(amax, red[i]);
+  const float scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 448.0f);
+  const float inv_scale = __frcp_rn(scale);
+  if (threadIdx.x == 0) scales[t] = scale;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const uint32_t c = threadIdx.x + i * 1024;
+    if (c >= chunks) continue;
+    const uint32_t ww[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+    uint32_t q[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = quotient_for_e4m3(__uint_as_float(ww[j] << 16), scale, inv_scale);
+      const float hi = quotient_for_e4m3(__uint_as_float(ww[j] & 0xFFFF0000u), scale, inv_scale);
+      const uint32_t pair = static_cast<uint16_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+      q[j >> 1] |= pair << (16 * (j & 1));
+    }
+    *reinterpret_cast<uint2*>(out + t * k + static_cast<uint64_t>(c) * 8) = make_uint2(q[0], q[1]);
+  }
+}
+
 }  // namespace
+
+int32_t launch_fp8_quantize_decode(const char* op, const uint16_t* x, uint8_t* out, float* scales, uint64_t tokens,
+                                   uint64_t k, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(tokens));
+  cfg.blockDim = dim3(1024);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, fp8_quantize_decode_kernel, x, out, scales, static_cast<uint32_t>(k));
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(le), cudaGetErrorString(le));
+  }
+  return check_launch(op);
+}
 
 // Reads and clears the GEMV ring's bounded-wait flag (0 = clean).
 int gemv_take_device_error() {

@@ -354,6 +354,8 @@ int32_t gemb_fp8_quantize(const void* input, int32_t input_dtype, uint8_t* out, 
   const char* op = "gemb_fp8_quantize";
   GEMB_TRY(validate_fp8_quantize(op, input, out, scales, input_dtype, tokens, k));
   const unsigned grid = static_cast<unsigned>(tokens);
+  if (input_dtype == GEMB_BF16 && tokens <= 16 && k <= 16384)   // decode batches: latency-optimised kernel
+    return launch_fp8_quantize_decode(op, static_cast<const uint16_t*>(input), out, scales, tokens, k, stream);
   if (input_dtype == GEMB_F32)
     fp8_quantize_kernel<float, false><<<grid, 256, 0, stream>>>(static_cast<const float*>(input), nullptr, out, scales, k, 0.0f);
   else
