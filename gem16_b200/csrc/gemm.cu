@@ -74,7 +74,6 @@ struct GemmParams {
   float g_product;               // input divisor of the down projection
   uint8_t* out_packed;           // [M, n/4] payload of the product (n/2 features)
   uint8_t* out_scales;           // interleaved scales of the product
-  uint32_t debug;                // bit 0: skip loads, bit 1: skip MMAs, bit 2: skip epilogue (experiments only)
 };
 
 template <bool kFp4, int BN, int kStages, int kAccStages>
@@ -196,11 +195,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const uint32_t k0 = ks * C::kKPerStage;
           const uint32_t n_mma = min(4u, (p.k - k0) / C::kKPerMma);
           uint32_t bytes = C::kABytes + C::kBBytes;
-          if (p.debug & 1) {
-            ptx::mbar_arrive(&full[stage]);
-            if (++stage == kStages) { stage = 0; phase ^= 1; }
-            continue;
-          }
           if constexpr (kFp4) {
             const uint32_t groups_per_matrix = (p.n + 127) / 128;
             const uint32_t g0 = expert * groups_per_matrix + (nt * BN) / 128;
@@ -248,8 +242,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const uint32_t n_mma = min(4u, (p.k - ks * C::kKPerStage) / C::kKPerMma);
         const uint64_t a_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_a + stage * C::kABytes));
         const uint64_t b_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_b + stage * C::kBBytes));
-        if (p.debug & 2) {
-        } else if constexpr (kFp4) {
+        if constexpr (kFp4) {
           const uint32_t region = step % C::kSfStages;
           const uint32_t tsfa = tmem_base + C::kAccCols + region * C::kSfColsPerStage;
           const uint32_t tsfb = tsfa + C::kSfaCols;
@@ -341,7 +334,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll 1
       for (uint32_t c = set; c < BN / 64; c += 2) {
         const uint32_t col0 = nt * BN + c * 64;
-        if (col0 >= p.n || row0 >= p.m || (p.debug & 4)) break;  // warp-uniform
+        if (col0 >= p.n || row0 >= p.m) break;  // warp-uniform
         uint32_t v0[32], v1[32];
         ptx::tc_ld_32x32b_x32(tmem_acc + c * 64, v0);
         ptx::tc_ld_32x32b_x32(tmem_acc + c * 64 + 32, v1);
@@ -497,7 +490,6 @@ int32_t make_out_map(const char* op, CUtensorMap* map, void* base, uint64_t rows
   return GEMB_OK;
 }
 
-int g_gemm_debug = 0;
 int g_gemm_bn = 0;  // 0 = automatic; gemb_set_tuning(GEMB_TUNE_GEMM_BN, 128 | 256)
 
 template <bool kFp4, int BN, int kStages, int kAccStages>
@@ -545,10 +537,6 @@ int32_t gemm_set_tuning(int32_t knob, int32_t value) {
     g_gemm_bn = value;
     return GEMB_OK;
   }
-  if (knob == 99) {
-    g_gemm_debug = value;
-    return GEMB_OK;
-  }
   return fail(GEMB_INVALID_ARGUMENT, "gemb_set_tuning: unknown knob %d", knob);
 }
 
@@ -579,7 +567,6 @@ int32_t gemb_nvfp4_gemm_bf16(const uint8_t* act, const uint8_t* act_scales_inter
   p.m = static_cast<uint32_t>(tokens);
   p.n = static_cast<uint32_t>(rows);
   p.k = static_cast<uint32_t>(k);
-  p.debug = g_gemm_debug;
   p.alpha = 1.0f / (ga * gw);  // one multiply in the epilogue, as src/cuda/nvfp4/cutlass_sm120.cu:551-552
   const int bn = g_gemm_bn ? g_gemm_bn : 256;  // 256 measured fastest; 192 and 128 stay selectable
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
@@ -616,7 +603,6 @@ int32_t gemb_moe_grouped_gemm_bf16(const uint8_t* act, const uint8_t* act_scales
   p.w_divisors = w_divisors;
   p.ga = ga;
   p.experts = static_cast<uint32_t>(experts);
-  p.debug = g_gemm_debug;
   p.alpha = 1.0f;
   const int bn = g_gemm_bn ? g_gemm_bn : 256;
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
@@ -712,7 +698,6 @@ int32_t gemb_nvfp4_gemm_gated_quant(const uint8_t* act, const uint8_t* act_scale
   p.g_product = product_divisor;
   p.out_packed = product_packed;
   p.out_scales = product_interleaved_scales;
-  p.debug = g_gemm_debug;
   return launch_gated(op, act, w_fused, p, stream);
 }
 
@@ -752,7 +737,6 @@ int32_t gemb_moe_grouped_gemm_gated_quant(const uint8_t* act, const uint8_t* act
   p.g_product = product_divisor;
   p.out_packed = product_packed;
   p.out_scales = product_interleaved_scales;
-  p.debug = g_gemm_debug;
   return launch_gated(op, act, w_fused, p, stream);
 }
 
@@ -774,7 +758,6 @@ int32_t gemb_fp8_gemm_bf16(const uint8_t* act, const float* act_scales, const ui
   p.n = static_cast<uint32_t>(rows);
   p.k = static_cast<uint32_t>(k);
   p.alpha = 1.0f;
-  p.debug = g_gemm_debug;
   const int bn = g_gemm_bn == 128 ? 128 : 256;
   if (bn == 128) return launch_gemm<false, 128, 6, 2>(op, act, w, p, stream);
   return launch_gemm<false, 256, 4, 2>(op, act, w, p, stream);
