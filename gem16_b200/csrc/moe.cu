@@ -438,18 +438,20 @@ expert_gelu_quantize_kernel(const uint16_t* __restrict__ gate_up, const int32_t*
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const int32_t* __restrict__ index,
-                   uint32_t divisor, uint64_t rows, uint32_t chunks_per_row) {
+                   uint32_t divisor, uint64_t rows, uint32_t chunks_per_row, uint32_t src_stride_chunks,
+                   uint32_t dst_stride_chunks) {
   const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= rows * chunks_per_row) return;
   const uint64_t r = idx / chunks_per_row, c = idx % chunks_per_row;
   const uint64_t s = static_cast<uint64_t>(__ldg(index + r)) / divisor;
-  dst[r * chunks_per_row + c] = __ldg(src + s * chunks_per_row + c);
+  dst[r * dst_stride_chunks + c] = __ldg(src + s * src_stride_chunks + c);
 }
 
 __global__ void __launch_bounds__(256)
 scatter_quantized_kernel(const uint8_t* __restrict__ payload, const uint8_t* __restrict__ compact_scales,
                          const int32_t* __restrict__ slot_rows, uint8_t* __restrict__ packed,
-                         uint8_t* __restrict__ scales, uint64_t rows, uint32_t hidden, uint32_t c_pad) {
+                         uint8_t* __restrict__ scales, uint64_t rows, uint32_t hidden, uint32_t c_pad,
+                         uint64_t src_row_stride) {
   const uint32_t blocks = hidden / 16;
   const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= rows * blocks) return;
@@ -457,8 +459,8 @@ scatter_quantized_kernel(const uint8_t* __restrict__ payload, const uint8_t* __r
   const uint32_t c = static_cast<uint32_t>(idx % blocks);
   const uint64_t d = static_cast<uint64_t>(__ldg(slot_rows + r));
   *reinterpret_cast<uint2*>(packed + d * (hidden / 2) + c * 8) =
-      __ldg(reinterpret_cast<const uint2*>(payload + r * (hidden / 2) + c * 8));
-  scales[interleaved_scale_offset(d, c, c_pad)] = __ldg(compact_scales + r * blocks + c);
+      __ldg(reinterpret_cast<const uint2*>(payload + r * src_row_stride + c * 8));
+  scales[interleaved_scale_offset(d, c, c_pad)] = __ldg(compact_scales + r * src_row_stride + c);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -692,34 +694,42 @@ int32_t gemb_moe_dispatch_quantize(const uint16_t* x_bf16, const int32_t* slot_r
 }
 
 int32_t gemb_moe_gather_rows(const void* src, void* dst, const int32_t* index, uint64_t index_divisor,
-                             uint64_t rows, uint64_t row_bytes, gemb_stream_t stream) {
+                             uint64_t rows, uint64_t row_bytes, uint64_t src_row_stride, uint64_t dst_row_stride,
+                             gemb_stream_t stream) {
   const char* op = "gemb_moe_gather_rows";
   GEMB_REQUIRE(src && dst && index, "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(rows > 0 && rows < (1ull << 31) && index_divisor >= 1 && index_divisor < (1ull << 31), "%s: bad geometry", op);
   GEMB_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0 && row_bytes < (1ull << 24), "%s: row size must be a nonzero multiple of 16 bytes", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0,
                "%s: buffers must be 16-byte aligned", op);
+  GEMB_REQUIRE(src_row_stride >= row_bytes && dst_row_stride >= row_bytes && src_row_stride % 16 == 0 &&
+                   dst_row_stride % 16 == 0 && src_row_stride < (1ull << 30) && dst_row_stride < (1ull << 30),
+               "%s: row strides must be multiples of 16 bytes no smaller than the row", op);
   GEMB_TRY(require_sm100(op));
   const uint32_t chunks = static_cast<uint32_t>(row_bytes / 16);
   gather_rows_kernel<<<static_cast<unsigned>((rows * chunks + 255) / 256), 256, 0, stream>>>(
-      static_cast<const uint4*>(src), static_cast<uint4*>(dst), index, static_cast<uint32_t>(index_divisor), rows, chunks);
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), index, static_cast<uint32_t>(index_divisor), rows, chunks,
+      static_cast<uint32_t>(src_row_stride / 16), static_cast<uint32_t>(dst_row_stride / 16));
   return check_launch(op);
 }
 
 int32_t gemb_moe_scatter_quantized(const uint8_t* packed_rows, const uint8_t* compact_scales, const int32_t* slot_rows,
                                    uint8_t* packed_e2m1, uint8_t* interleaved_scales, uint64_t rows, uint64_t hidden,
-                                   gemb_stream_t stream) {
+                                   uint64_t src_row_stride, gemb_stream_t stream) {
   const char* op = "gemb_moe_scatter_quantized";
   GEMB_REQUIRE(packed_rows && compact_scales && slot_rows && packed_e2m1 && interleaved_scales, "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(rows > 0 && rows < (1ull << 31), "%s: bad row count", op);
   GEMB_REQUIRE(hidden > 0 && hidden % 16 == 0 && hidden < (1ull << 31), "%s: hidden must be a nonzero multiple of 16", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(packed_rows) % 8 == 0 && reinterpret_cast<uintptr_t>(packed_e2m1) % 8 == 0,
                "%s: payload buffers must be 8-byte aligned", op);
+  GEMB_REQUIRE(src_row_stride >= hidden / 2 && src_row_stride % 8 == 0 && src_row_stride < (1ull << 30),
+               "%s: source row stride must be a multiple of 8 bytes no smaller than the payload row", op);
   GEMB_TRY(require_sm100(op));
   const uint32_t c_pad = static_cast<uint32_t>((hidden / 16 + 3) / 4 * 4);
   const uint64_t work = rows * (hidden / 16);
   scatter_quantized_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
-      packed_rows, compact_scales, slot_rows, packed_e2m1, interleaved_scales, rows, static_cast<uint32_t>(hidden), c_pad);
+      packed_rows, compact_scales, slot_rows, packed_e2m1, interleaved_scales, rows, static_cast<uint32_t>(hidden), c_pad,
+      src_row_stride);
   return check_launch(op);
 }
 

@@ -5,8 +5,8 @@ C-ABI launch).  gem16 has no multi-GPU code; the protocol below is this library'
 Per layer, on every rank (T local tokens, R ranks, E experts, E/R local experts [r*E/R, (r+1)*E/R)):
   1. route the local tokens over all E experts (router replicated): ids, weights, counts,
      offsets and the stable permutation -- which orders assignments by expert, hence by owner rank;
-  2. NVFP4-quantise the local tokens once and pack payload + scales + local expert id in
-     permutation order (1,584 B + 4 B per assignment instead of 5,632 B of bf16);
+  2. NVFP4-quantise the local tokens once and pack payload + scales + local expert id into one
+     message row per assignment, in permutation order (1,600 B instead of 5,632 B of bf16);
   3. all-gather the per-expert counts (the only host read-back: the split sizes), all-to-all the
      packed rows;
   4. the owner sorts what it received by local expert with the same stable permutation kernel --
@@ -55,10 +55,10 @@ class EpMoeLayer:
         i32 = dict(dtype=torch.int32, device=dev)
         self.xq = torch.empty((tokens, h // 2), **u8)
         self.xs = torch.empty((tokens, h // 16), **u8)
-        self.send_payload = torch.empty((n, h // 2), **u8)
-        self.send_scales = torch.empty((n, h // 16), **u8)
-        self.recv_payload = torch.empty((cap, h // 2), **u8)
-        self.recv_scales = torch.empty((cap, h // 16), **u8)
+        # One dispatch message row per assignment: payload | block scales | local expert id | pad.
+        self.msg_bytes = (h // 2 + h // 16 + 4 + 15) // 16 * 16
+        self.send_msg = torch.zeros((n, self.msg_bytes), **u8)
+        self.recv_msg = torch.empty((cap, self.msg_bytes), **u8)
         self.recv_eid = torch.empty((cap,), **i32)
         self.counts_all = torch.empty((self.world, self.e_total), **i32)
         self.rows_max = c.gemb_moe_padded_rows_max(cap, self.e_local, 1)
@@ -98,29 +98,30 @@ class EpMoeLayer:
                              loc.workspace.numel(), t, self.e_total, k, None)
         # 2. quantise once, pack in permutation order
         lib.gemb_nvfp4_quantize(x_bf16, 1, self.xq, self.xs, t, h, self.ga, 0, 0, None)
-        lib.gemb_moe_gather_rows(self.xq, self.send_payload, loc.perm, k, n, h // 2, None)
-        lib.gemb_moe_gather_rows(self.xs, self.send_scales, loc.perm, k, n, h // 16, None)
+        mb, sc_off, id_off = self.msg_bytes, h // 2, h // 2 + h // 16
+        lib.gemb_moe_gather_rows(self.xq, self.send_msg, loc.perm, k, n, h // 2, h // 2, mb, None)
+        lib.gemb_moe_gather_rows(self.xs, self.send_msg[:, sc_off:], loc.perm, k, n, h // 16, h // 16, mb, None)
         send_eid = (loc.ids.view(-1)[loc.perm.long()] % self.e_local).to(torch.int32)
+        self.send_msg[:, id_off:id_off + 4] = send_eid.view(torch.uint8).view(n, 4)
         # 3. split sizes (host read-back of E*R integers), then the dispatch all-to-all
         dist.all_gather_into_tensor(self.counts_all.view(-1), loc.counts, group=self.group)
         send_splits, recv_splits = ep_splits(self.counts_all.cpu().numpy(), self.rank, self.e_local)
         n_recv = sum(recv_splits)
-        dist.all_to_all_single(self.recv_payload[:n_recv], self.send_payload, recv_splits, send_splits, group=self.group)
-        dist.all_to_all_single(self.recv_scales[:n_recv], self.send_scales, recv_splits, send_splits, group=self.group)
-        dist.all_to_all_single(self.recv_eid[:n_recv], send_eid, recv_splits, send_splits, group=self.group)
+        dist.all_to_all_single(self.recv_msg[:n_recv], self.send_msg, recv_splits, send_splits, group=self.group)
         # 4. local experts
         if n_recv > 0:
+            self.recv_eid[:n_recv] = self.recv_msg[:n_recv, id_off:id_off + 4].contiguous().view(torch.int32).view(-1)
             lib.gemb_moe_permute(self.recv_eid, self.l_counts, self.l_offsets, self.l_perm, self.l_rows, self.l_plan,
                                  self.l_ws, self.l_ws.numel(), n_recv, self.e_local, 1, None)
-            lib.gemb_moe_scatter_quantized(self.recv_payload, self.recv_scales, self.l_rows, self.a_packed,
-                                           self.a_scales, n_recv, h, None)
+            lib.gemb_moe_scatter_quantized(self.recv_msg, self.recv_msg[:, sc_off:], self.l_rows, self.a_packed,
+                                           self.a_scales, n_recv, h, mb, None)
             lib.gemb_moe_grouped_gemm_bf16(self.a_packed, self.a_scales, w.gu_packed, w.gu_scales, self.gate_up,
                                            self.l_plan, self.rows_max, self.e_local, 2 * w.inter, h, self.ga, w.gu_div, None)
             lib.gemb_moe_expert_gelu_quantize(self.gate_up, self.l_plan, self.p_packed, self.p_scales, self.rows_max,
                                               w.inter, self.ga_dn, None)
             lib.gemb_moe_grouped_gemm_bf16(self.p_packed, self.p_scales, w.dn_packed, w.dn_scales, self.y, self.l_plan,
                                            self.rows_max, self.e_local, h, w.inter, self.ga_dn, w.dn_div, None)
-            lib.gemb_moe_gather_rows(self.y, self.y_send, self.l_rows, 1, n_recv, h * 2, None)
+            lib.gemb_moe_gather_rows(self.y, self.y_send, self.l_rows, 1, n_recv, h * 2, h * 2, h * 2, None)
         # 5. reverse all-to-all, shared branch, slot-ordered combine on the token's owner
         dist.all_to_all_single(self.y_sorted.view(torch.uint8), self.y_send[:n_recv].view(torch.uint8), send_splits,
                                recv_splits, group=self.group)   # byte rows: 16-bit integers are not a NCCL type

@@ -317,17 +317,21 @@ int32_t gemb_moe_dispatch_quantize(const uint16_t* x_bf16, const int32_t* slot_r
 
 /* Expert-parallel plumbing (gem16 has no multi-GPU code; docs/GEMMA4_26B.md:114-117 excludes it,
  * so these have no counterpart there).
- * gather_rows: dst[i] = src[index[i] / index_divisor], rows of row_bytes (multiple of 16) bytes --
- * packs quantised tokens in permutation order for the dispatch all-to-all (index = perm, divisor =
- * topk) and expert outputs back into arrival order for the combine all-to-all (index = slot rows).
- * scatter_quantized: places already quantised rows (payload + COMPACT scales, as received) at
- * slot_rows[i] of the padded row space and converts their scales to the INTERLEAVED layout. */
+ * gather_rows: dst row i = src row index[i] / index_divisor; row_bytes (multiple of 16) are copied,
+ * rows are src_row_stride / dst_row_stride bytes apart -- packs quantised tokens in permutation
+ * order into the dispatch message (index = perm, divisor = topk; payload and scales of one
+ * assignment share a message row) and expert outputs back into arrival order for the combine
+ * all-to-all (index = slot rows).
+ * scatter_quantized: places already quantised rows (payload and COMPACT scales, both with
+ * src_row_stride bytes between rows, as received) at slot_rows[i] of the padded row space and
+ * converts their scales to the INTERLEAVED layout. */
 int32_t gemb_moe_gather_rows(const void* src, void* dst, const int32_t* index, uint64_t index_divisor,
-                             uint64_t rows, uint64_t row_bytes, gemb_stream_t stream);
+                             uint64_t rows, uint64_t row_bytes, uint64_t src_row_stride,
+                             uint64_t dst_row_stride, gemb_stream_t stream);
 int32_t gemb_moe_scatter_quantized(const uint8_t* packed_rows, const uint8_t* compact_scales,
                                    const int32_t* slot_rows, uint8_t* packed_e2m1,
                                    uint8_t* interleaved_scales, uint64_t rows, uint64_t hidden,
-                                   gemb_stream_t stream);
+                                   uint64_t src_row_stride, gemb_stream_t stream);
 
 /* Grouped expert projection over the padded row space: for every 128-row tile t of the plan,
  * out[rows of t] = bf16( A[rows of t] . W[tile_expert[t]]^T / (ga * w_divisors[expert]) ).
