@@ -65,3 +65,21 @@ def test_missing_library_fails_loudly(tmp_path):
     from gem16_b200.lib import Lib
     with pytest.raises(RuntimeError):
         Lib(str(tmp_path / "libgemb200.so"))
+
+
+def test_shim_compiles_against_the_reference_headers():
+    # The drop-in shim must match the reference's own launcher declarations: compile it against
+    # the gem16 headers where the reference tree is present; -Wmissing-declarations turns a
+    # definition whose signature matches no reference declaration into an error.
+    import os
+    import subprocess
+    ref = os.environ.get("GEM16_REFERENCE", "/root/reference")
+    if not os.path.isfile(os.path.join(ref, "src", "cuda", "nvfp4", "sm120.h")):
+        pytest.skip("reference tree not present")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cuda_inc = "/usr/local/cuda/include"
+    cmd = ["g++", "-std=c++20", "-fsyntax-only", "-Wall", "-Wmissing-declarations", "-Werror", "-I", os.path.join(ref, "include"),
+           "-I", os.path.join(ref, "src"), "-I", os.path.join(root, "include"), "-I", cuda_inc,
+           os.path.join(root, "gem16_b200", "shim", "gem16_internal_shim.cpp")]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
