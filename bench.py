@@ -277,7 +277,7 @@ def run_decode_gemv(args):
     bytes_step = decode_bytes_per_layer() * layers
     value = world * bytes_step * args.steps / secs / 1e9
     e2e = world * bytes_step * args.steps / secs_e2e / 1e9
-    moe_ep = None
+    moe_ep = tp_mlp = None
     if not args.no_other_workloads:
         del weights, graph
         torch.cuda.empty_cache()
@@ -285,6 +285,11 @@ def run_decode_gemv(args):
             moe_ep = bench_moe_ep(lib, dev, world, rank)
         except Exception as exc:
             moe_ep = {"error": f"{type(exc).__name__}: {exc}"}
+        if world > 1:
+            try:
+                tp_mlp = bench_tp_mlp(lib, dev, world, rank)
+            except Exception as exc:
+                tp_mlp = {"error": f"{type(exc).__name__}: {exc}"}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -310,6 +315,8 @@ def run_decode_gemv(args):
     }
     if moe_ep is not None:
         line["other_workloads"] = {"moe_ep_stack": moe_ep}
+        if tp_mlp is not None:
+            line["other_workloads"]["tp_mlp"] = tp_mlp
     if world == 1 and not args.no_other_workloads:
         other = line["other_workloads"]
         for name, fn in (("nvfp4_linear", bench_nvfp4_linear), ("prefill_gemm", bench_prefill_gemm),
@@ -528,6 +535,54 @@ def bench_moe_layer(lib, dev, tokens=4096):
             "bounds_us": {"tensor_at_9PF": flops / 9e15 * 1e6, "hbm_weights_at_measured_peak": weight_bytes / (measured_peaks()["hbm_gbs"] * 1e9) * 1e6},
             "padded_rows": int(layer.plan[1].item()), "tiles": int(layer.plan[0].item()),
             "expert_count_max": int(layer.counts.max().item()), "expert_count_min": int(layer.counts.min().item())}
+
+
+def bench_tp_mlp(lib, dev, world, rank, tokens=16384):
+    """Tensor-parallel 12B-like gated MLP (hidden 3840, intermediate 15360) on 16,384 tokens: gate/up
+    column split, down row split with an fp32 all-reduce.  Collective; N = 1 runs it unsharded."""
+    import torch
+    import torch.distributed as dist
+    from gem16_b200.tp import TpMlp
+    hidden, inter = 3840, 15360
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + 5000)
+
+    def quant(rows, k):
+        w = torch.randn((rows, k), device=dev, generator=gen) * 0.02
+        div = float(2688.0 / w.abs().max().item())
+        p = torch.empty((rows, k // 2), dtype=torch.uint8, device=dev)
+        s = torch.empty((rows, k // 16), dtype=torch.uint8, device=dev)
+        lib.gemb_nvfp4_quantize(w, 0, p, s, rows, k, div, 0, 0, None)
+        return p, s, div
+
+    gate, up, down = quant(inter, hidden), quant(inter, hidden), quant(hidden, inter)
+    x = torch.randn((tokens, hidden), device=dev, generator=gen).to(torch.bfloat16).view(torch.int16)
+    if world == 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29577", rank=0, world_size=1, device_id=dev)
+    mlp = TpMlp(dev, gate, up, down, tokens, 700.0, 2688.0 / 0.05)
+    del gate, up, down
+    for _ in range(3):
+        mlp.forward(x)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 10
+    s.record()
+    for _ in range(reps):
+        mlp.forward(x)
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / reps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    lib.gemb_check_device_status()
+    flops = 2.0 * tokens * 3 * inter * hidden
+    return {"metric": "tensor-parallel MLP tokens/s", "ranks": world, "tokens": tokens, "ms": ms,
+            "tokens_per_s": tokens / ms * 1e3, "tflops_aggregate": flops / ms / 1e9,
+            "allreduce_bytes_per_rank": tokens * hidden * 4 if world > 1 else 0}
 
 
 def bench_moe_ep(lib, dev, world, rank, layers=30, phases=((16384, "prefill"), (64, "decode"))):

@@ -70,6 +70,7 @@ struct GemmParams {
   // (gemb_nvfp4_pack_gate_up), so every 64 accumulator columns hold 32 gate + 32 up values of
   // the same features; the epilogue writes the NVFP4-quantised GELU product instead of bf16.
   uint32_t gated;
+  uint32_t out_f32;              // NVFP4 only: store fp32 (acc * alpha) instead of bf16 (row-split partial sums)
   float alpha_up;                // 1 / (ga * gw_up); `alpha` is the gate's
   float g_product;               // input divisor of the down projection
   uint8_t* out_packed;           // [M, n/4] payload of the product (n/2 features)
@@ -374,6 +375,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
           continue;
         }
+        if (kFp4 && p.out_f32) {
+          // fp32 output: two 32-column boxes (128 bytes per row each) through the same staging buffer.
+          ptx::tc_wait_ld();
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            if (col0 + half * 32 >= p.n) break;
+            if (lane == 0) ptx::bulk_wait_group_read<0>();
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const uint32_t* v = half == 0 ? v0 : v1;
+              *reinterpret_cast<uint4*>(my_stage + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_uint4(
+                  __float_as_uint(__fmul_rn(__uint_as_float(v[4 * q]), row_scale)),
+                  __float_as_uint(__fmul_rn(__uint_as_float(v[4 * q + 1]), row_scale)),
+                  __float_as_uint(__fmul_rn(__uint_as_float(v[4 * q + 2]), row_scale)),
+                  __float_as_uint(__fmul_rn(__uint_as_float(v[4 * q + 3]), row_scale)));
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_2d(&map_out, my_stage, static_cast<int32_t>(col0 + half * 32), static_cast<int32_t>(row0));
+              ptx::bulk_commit_group();
+            }
+          }
+          continue;
+        }
         // The staging buffer about to be overwritten was handed to a TMA store one sub-tile ago.
         if (lane == 0) ptx::bulk_wait_group_read<0>();
         __syncwarp();
@@ -490,6 +517,21 @@ int32_t make_out_map(const char* op, CUtensorMap* map, void* base, uint64_t rows
   return GEMB_OK;
 }
 
+// fp32 matrix [rows, cols] row-major -> boxes of 32 columns (128 bytes) x 32 rows, 128-byte swizzle.
+int32_t make_out_map_f32(const char* op, CUtensorMap* map, void* base, uint64_t rows, uint64_t cols) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(GEMB_UNSUPPORTED, "%s: cuTensorMapEncodeTiled is not available from the driver", op);
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 4};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(GEMB_INTERNAL, "%s: cuTensorMapEncodeTiled failed with CUresult %d", op, int(r));
+  return GEMB_OK;
+}
+
 int g_gemm_bn = 0;  // 0 = automatic; gemb_set_tuning(GEMB_TUNE_GEMM_BN, 128 | 256)
 
 template <bool kFp4, int BN, int kStages, int kAccStages>
@@ -509,7 +551,9 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
   CUtensorMap map_a, map_b, map_out;
   GEMB_TRY(make_byte_map(op, &map_a, a, p.m, row_bytes, BM));
   GEMB_TRY(make_byte_map(op, &map_b, b, static_cast<uint64_t>(p.n) * (p.plan ? p.experts : 1u), row_bytes, BN));
-  if (p.gated)  // the tensor-map store path is unused; describe the payload buffer so the map is valid
+  if (p.out_f32)
+    GEMB_TRY(make_out_map_f32(op, &map_out, p.out, p.m, p.n));
+  else if (p.gated)  // the tensor-map store path is unused; describe the payload buffer so the map is valid
     GEMB_TRY(make_out_map(op, &map_out, p.out_packed, p.m, p.n / 8));
   else
     GEMB_TRY(make_out_map(op, &map_out, p.out, p.m, p.n));
@@ -569,6 +613,35 @@ int32_t gemb_nvfp4_gemm_bf16(const uint8_t* act, const uint8_t* act_scales_inter
   p.k = static_cast<uint32_t>(k);
   p.alpha = 1.0f / (ga * gw);  // one multiply in the epilogue, as src/cuda/nvfp4/cutlass_sm120.cu:551-552
   const int bn = g_gemm_bn ? g_gemm_bn : 256;  // 256 measured fastest; 192 and 128 stay selectable
+  if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
+  if (bn == 192) return launch_gemm<true, 192, 4, 2>(op, act, w, p, stream);
+  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
+}
+
+int32_t gemb_nvfp4_gemm_f32(const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* w,
+                            const uint8_t* w_scales_interleaved, float* out, uint64_t tokens, uint64_t rows,
+                            uint64_t k, float ga, float gw, gemb_stream_t stream) {
+  const char* op = "gemb_nvfp4_gemm_f32";
+  GEMB_REQUIRE(act && act_scales_interleaved && w && w_scales_interleaved && out, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_gemm(op, tokens, rows, k, 64));
+  GEMB_REQUIRE(positive_finite(ga) && positive_finite(gw) && std::isfinite(ga * gw) && ga * gw > 0.0f,
+               "%s: global divisors must be positive and finite", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(act_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(w_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % 16 == 0,
+               "%s: all buffers must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  GemmParams p{};
+  p.sfa = act_scales_interleaved;
+  p.sfb = w_scales_interleaved;
+  p.out = reinterpret_cast<uint16_t*>(out);
+  p.out_f32 = 1;
+  p.m = static_cast<uint32_t>(tokens);
+  p.n = static_cast<uint32_t>(rows);
+  p.k = static_cast<uint32_t>(k);
+  p.alpha = 1.0f / (ga * gw);
+  const int bn = g_gemm_bn ? g_gemm_bn : 256;
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
   if (bn == 192) return launch_gemm<true, 192, 4, 2>(op, act, w, p, stream);
   return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);

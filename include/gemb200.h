@@ -209,6 +209,17 @@ int32_t gemb_nvfp4_gemm_bf16(const uint8_t* packed_activation_e2m1,
                              float activation_global_divisor, float weight_global_divisor,
                              gemb_stream_t stream);
 
+/* Same contraction with fp32 output [tokens, rows] = acc * (1 / (ga * gw)), no bf16 rounding: the
+ * partial sums of a row-split (K-sharded) projection, to be all-reduced and rounded once.  The
+ * reference has no multi-GPU path; its nearest relative is the fp32-output batch projection
+ * LaunchNvfp4Sm120DirectProjectionBatch, src/cuda/nvfp4/sm120.h:26-37. */
+int32_t gemb_nvfp4_gemm_f32(const uint8_t* packed_activation_e2m1,
+                            const uint8_t* interleaved_activation_scales,
+                            const uint8_t* packed_weight_e2m1, const uint8_t* interleaved_weight_scales,
+                            float* output_f32, uint64_t tokens, uint64_t rows,
+                            uint64_t contracting_elements, float activation_global_divisor,
+                            float weight_global_divisor, gemb_stream_t stream);
+
 /* Gate and Up projections, GELU and requantisation in ONE kernel.  The fused weight holds the
  * gate and up rows interleaved in runs of 32 features (gemb_nvfp4_pack_gate_up), so each token's
  * accumulator row carries gate and up of the same features side by side and the epilogue emits

@@ -24,3 +24,15 @@ def test_expert_parallel_matches_single_gpu(tokens):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     for rank in range(world):
         assert f"rank {rank} ok" in r.stdout
+
+
+def test_tensor_parallel_mlp_matches_unsharded():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29642", os.path.join(ROOT, "tests", "tp_gpu_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout

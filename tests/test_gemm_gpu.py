@@ -142,3 +142,17 @@ def test_prefill_property_at_full_size(lib, dev):
                                         w["compact"], ref, sel.numel(), rows, k, a["div"], w["div"], None)
     st = error_stats(bf16_tensor_to_f32(out[sel]), ref.cpu().numpy().astype(np.float64))
     assert st["rel_fro"] <= REL_FRO, st
+
+
+def test_nvfp4_gemm_f32_output(lib, dev, orc):
+    # fp32 epilogue (row-split partial sums): against the binary64 oracle without bf16 rounding.
+    tokens, rows, k = 77, 328, 704
+    a = nvfp4_operand(lib, dev, tokens, k, 1.0, 5)
+    w = nvfp4_operand(lib, dev, rows, k, 0.02, 6)
+    out = torch.full((tokens, rows), float("nan"), device=dev)
+    lib.gemb_nvfp4_gemm_f32(a["packed"], a["inter"], w["packed"], w["inter"], out, tokens, rows, k, a["div"], w["div"], None)
+    lib.gemb_check_device_status()
+    want = orc.nvfp4_matmul(to_np(a["packed"]), to_np(a["compact"]), to_np(w["packed"]), to_np(w["compact"]), a["div"], w["div"])
+    got = out.cpu().numpy().astype(np.float64)
+    assert np.isfinite(got).all()
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) < 1e-6
