@@ -332,6 +332,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       if (kFp4 && p.w_divisors != nullptr)
         row_scale = __fdiv_rn(1.0f, __fmul_rn(p.ga, __ldg(p.w_divisors + (tile_expert ? __ldg(tile_expert + mt) : 0))));
       const uint32_t tmem_acc = tmem_base + as * BN + ((quarter * 32) << 16);
+      bool released = false;
 #pragma unroll 1
       for (uint32_t c = set; c < BN / 64; c += 2) {
         const uint32_t col0 = nt * BN + c * 64;
@@ -405,6 +406,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (lane == 0) ptx::bulk_wait_group_read<0>();
         __syncwarp();
         ptx::tc_wait_ld();
+        if (c + 2 >= BN / 64) {
+          // This warp's last sub-tile is in registers: the accumulator can be overwritten while
+          // the conversion and the store below are still running.
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
+          released = true;
+        }
         uint8_t* sbuf = my_stage;
         auto convert = [&](const uint32_t (&v)[32], int half) {
 #pragma unroll
@@ -441,9 +450,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           ptx::bulk_commit_group();
         }
       }
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
+      if (!released) {
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
+      }
       if (++as == kAccStages) { as = 0; aphase ^= 1; }
     }
     if (lane == 0) ptx::bulk_wait_group_all();
