@@ -37,6 +37,8 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -49,7 +51,7 @@ __device__ int g_gemm_error = 0;
 namespace {
 
 constexpr int kGemmThreadsFp8 = 320;   // producer, MMA, 2 x 4 epilogue warps
-constexpr int kGemmThreadsFp4 = 448;   // producer, MMA, 4 epilogue, 4 scale movers, 4 more epilogue warps
+constexpr int kGemmThreadsFp4 = 576;   // producer, MMA, 2 x (4 epilogue + 4 scale mover) warps
 constexpr int BM = 128;
 
 struct GemmParams {
@@ -77,32 +79,32 @@ struct GemmParams {
   uint8_t* out_scales;           // interleaved scales of the product
 };
 
-template <bool kFp4, int BN, int kStages, int kAccStages>
+template <bool kFp4, int BN, int kStages, int kAccStages, bool kPair = false>
 struct Cfg {
   static constexpr int kKPerStage = kFp4 ? 256 : 128;      // elements covered by 128 bytes
   static constexpr int kKPerMma = kFp4 ? 64 : 32;          // elements per tcgen05.mma
   static constexpr int kABytes = BM * 128;
-  static constexpr int kBBytes = BN * 128;
-  // Weight scales are stored in 128-row groups.  A 192-wide tile starts on a group boundary
-  // (even tiles) or 64 rows into a group (odd tiles): it always stages two whole groups in shared
-  // memory and the scale movers write just the six 32-row columns the tile covers into TMEM.
-  static constexpr int kSfbGroups = BN <= 128 ? 1 : 2;
+  static constexpr int kBRows = kPair ? BN / 2 : BN;       // weight rows this CTA stages
+  static constexpr int kBBytes = kBRows * 128;
+  // Weight scales are stored in 128-row groups: a 256-wide tile stages two of them.
+  static constexpr int kSfbGroups = BN / 128;
   static constexpr int kSfaBytes = kFp4 ? 2048 : 0;        // 4 chunks of 512 B
   static constexpr int kSfbBytes = kFp4 ? kSfbGroups * 2048 : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kEpiBytes = 4 * 2 * 4096;          // 4 warps x 2 buffers x (32 rows x 128 B)
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarrierBytes + 1024;  // + alignment slack
-  // TMEM columns: accumulators first, then a ring of scale regions (one per step in flight).
+  // TMEM columns: accumulators first, then one scale region per shared-memory stage.  A stage's
+  // "empty" barrier (its MMAs have completed) therefore also frees its scale region, and a stage
+  // that is full again proves it: the scale movers need no barrier of their own for the region.
   static constexpr int kAccCols = kAccStages * BN;
   static constexpr int kSfaCols = 16;                      // 4 MMAs x 4 columns
   static constexpr int kSfbColsPerMma = BN / 32;
   static constexpr int kSfbCols = 4 * kSfbColsPerMma;
   static constexpr int kSfColsPerStage = kFp4 ? kSfaCols + kSfbCols : 0;
-  static constexpr int kSfStages = !kFp4 ? 1 : ((512 - kAccCols) / kSfColsPerStage < kStages ? (512 - kAccCols) / kSfColsPerStage : kStages);
-  static_assert(!kFp4 || kSfStages >= 2, "TMEM budget exceeded");
-  static_assert(kAccCols + (kFp4 ? kSfStages * kSfColsPerStage : 0) <= 512, "TMEM budget exceeded");
-  static_assert(BN % 64 == 0 && BN <= 256, "BN must be 128, 192 or 256");
+  static_assert(kAccCols + kStages * kSfColsPerStage <= 512, "TMEM budget exceeded");
+  static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
+  static_assert(!kPair || BN == 256, "CTA pairs compute 256 x 256 tiles");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget exceeded");
 };
 
@@ -112,11 +114,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
-template <bool kFp4, int BN, int kStages, int kAccStages>
+template <bool kFp4, int BN, int kStages, int kAccStages, bool kPair>
 __global__ void __launch_bounds__(kFp4 ? kGemmThreadsFp4 : kGemmThreadsFp8, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
-  using C = Cfg<kFp4, BN, kStages, kAccStages>;
+  using C = Cfg<kFp4, BN, kStages, kAccStages, kPair>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_a = smem;
@@ -129,22 +131,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   uint64_t* empty = full + kStages;
   uint64_t* acc_full = empty + kStages;
   uint64_t* acc_empty = acc_full + kAccStages;
-  uint64_t* sf_ready = acc_empty + kAccStages;   // per smem stage: scales are in TMEM
-  uint64_t* sf_free = sf_ready + kStages;        // per TMEM scale region: its MMAs have completed
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_free + kStages);
+  uint64_t* sf_ready = acc_empty + kAccStages;   // per stage: its scales are in TMEM
+  uint64_t* peer_full = sf_ready + kStages;      // pairs, FP8: the odd CTA's operands have landed
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(peer_full + kStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // CTA pairs: the even CTA (rank 0) issues every MMA; the barriers that gate it (scales ready,
+  // accumulator drained, peer operands landed) live in its shared memory and collect arrivals
+  // from both CTAs.  The MMA's completion is committed to the same barrier in both CTAs.
+  const uint32_t rank = kPair ? ptx::cluster_ctarank() : 0u;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(&full[s], 1);
       ptx::mbar_init(&empty[s], 1);
-      ptx::mbar_init(&sf_ready[s], 4);
-      ptx::mbar_init(&sf_free[s], 1);
+      ptx::mbar_init(&sf_ready[s], kPair ? 8 : 4);
+      ptx::mbar_init(&peer_full[s], 1);
     }
     for (int s = 0; s < kAccStages; ++s) {
       ptx::mbar_init(&acc_full[s], 1);
-      ptx::mbar_init(&acc_empty[s], 8);
+      ptx::mbar_init(&acc_empty[s], kPair ? 16 : 8);
     }
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -152,16 +158,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     ptx::prefetch_tensormap(&map_b);
     ptx::prefetch_tensormap(&map_out);
   }
-  if (warp == 1) ptx::tmem_alloc(tmem_holder, 512);
+  if (warp == 1) {
+    if constexpr (kPair) ptx::tmem_alloc_pair(tmem_holder, 512);
+    else ptx::tmem_alloc(tmem_holder, 512);
+  }
   ptx::tc_fence_before();
-  __syncthreads();
+  if constexpr (kPair) ptx::cluster_sync();
+  else __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
   const uint32_t m_tiles = p.plan ? static_cast<uint32_t>(__ldg(p.plan)) : (p.m + BM - 1) / BM;
   const uint32_t n_tiles = (p.n + BN - 1) / BN;
   const int32_t* tile_expert = p.plan ? p.plan + 3 + p.experts : nullptr;
-  const uint32_t num_tiles = m_tiles * n_tiles;
+  // A work unit is one 128-row token tile, or for pairs two consecutive ones (rank picks which).
+  const uint32_t m_units = kPair ? (m_tiles + 1) / 2 : m_tiles;
+  const uint32_t num_tiles = m_units * n_tiles;
+  const uint32_t first_tile = kPair ? blockIdx.x >> 1 : blockIdx.x;
+  const uint32_t tile_stride = kPair ? gridDim.x >> 1 : gridDim.x;
+  const uint32_t my_tiles = first_tile < num_tiles ? (num_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
   const uint32_t k_stages = (p.k + C::kKPerStage - 1) / C::kKPerStage;
   const uint32_t k_groups_pad = (p.k / 16 + 3) / 4;  // 512-byte scale chunks per 128-row group
 
@@ -169,13 +184,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   // CTAs of a wave share a few weight tiles and the group's activations stay in L2 while every
   // weight tile passes over them.
   auto tile_coords = [&](uint32_t tile, uint32_t& mt, uint32_t& nt) {
-    constexpr uint32_t kGroupM = 16;
+    constexpr uint32_t kGroupM = kPair ? 8 : 16;
     const uint32_t per_group = kGroupM * n_tiles;
     const uint32_t first_m = (tile / per_group) * kGroupM;
-    const uint32_t gm = min(kGroupM, m_tiles - first_m);
+    const uint32_t gm = min(kGroupM, m_units - first_m);
     const uint32_t within = tile % per_group;
     mt = first_m + within % gm;
+    if constexpr (kPair) mt = mt * 2 + rank;
     nt = within / gm;
+  };
+  // Completion of the MMAs issued so far, signalled to the same barrier of both CTAs of a pair.
+  const uint32_t bars_rank0 = kPair ? ptx::cluster_map(bars, 0) : 0u;
+  const uint32_t bars_rank1 = kPair ? ptx::cluster_map(bars, 1) : 0u;
+  auto commit = [&](uint64_t* bar) {
+    if constexpr (kPair) {
+      const uint32_t off = static_cast<uint32_t>(reinterpret_cast<uint8_t*>(bar) - reinterpret_cast<uint8_t*>(bars));
+      ptx::tc_commit_pair(bars_rank0 + off);
+      ptx::tc_commit_pair(bars_rank1 + off);
+    } else {
+      ptx::tc_commit(bar);
+    }
+  };
+  // Arrival on a barrier that gates the MMA issuer.
+  auto arrive_issuer = [&](uint64_t* bar) {
+    if constexpr (kPair) ptx::mbar_arrive_cluster(ptx::cluster_map(bar, 0));
+    else ptx::mbar_arrive(bar);
+  };
+  auto wait_issuer = [&](uint64_t* bar, uint32_t parity) {
+    if constexpr (kPair) return ptx::mbar_wait_cluster(bar, parity);
+    else return ptx::mbar_wait(bar, parity);
   };
 
   auto fail_wait = [&](int code) {
@@ -187,7 +224,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // ------------------------------- producer -------------------------------------------------
     if (ptx::elect_one()) {
       uint32_t stage = 0, phase = 0;
-      for (uint32_t tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+      for (uint32_t tile = first_tile; tile < num_tiles && !*abort_flag; tile += tile_stride) {
         uint32_t mt, nt;
         tile_coords(tile, mt, nt);
         const uint32_t expert = tile_expert ? static_cast<uint32_t>(__ldg(tile_expert + mt)) : 0u;
@@ -203,9 +240,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const uint32_t n_groups = min(static_cast<uint32_t>(C::kSfbGroups), total_groups - g0);
             bytes += n_mma * 512 * (1 + n_groups);
             ptx::mbar_expect_tx(&full[stage], bytes);
+            // The odd CTA of a pair may sit past the last token tile: its rows are never stored,
+            // it just reads the last tile's scales again.
             ptx::bulk_load_1d(stage_sfa + stage * C::kSfaBytes,
-                              p.sfa + (static_cast<uint64_t>(mt) * k_groups_pad + ks * 4) * 512, n_mma * 512,
-                              &full[stage]);
+                              p.sfa + (static_cast<uint64_t>(min(mt, m_tiles - 1)) * k_groups_pad + ks * 4) * 512,
+                              n_mma * 512, &full[stage]);
             for (uint32_t g = 0; g < n_groups; ++g)
               ptx::bulk_load_1d(stage_sfb + stage * C::kSfbBytes + g * 2048,
                                 p.sfb + (static_cast<uint64_t>(g0 + g) * k_groups_pad + ks * 4) * 512,
@@ -216,114 +255,191 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           ptx::tma_load_2d(stage_a + stage * C::kABytes, &map_a, &full[stage], static_cast<int32_t>(ks * 128),
                            static_cast<int32_t>(mt * BM));
           ptx::tma_load_2d(stage_b + stage * C::kBBytes, &map_b, &full[stage], static_cast<int32_t>(ks * 128),
-                           static_cast<int32_t>(expert * p.n + nt * BN));
+                           static_cast<int32_t>(expert * p.n + nt * BN + rank * C::kBRows));
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------- MMA issuer -----------------------------------------------
-    // The CTA's work is a flat sequence of steps (tile, k stage).
-    if (ptx::elect_one()) {
-      constexpr uint32_t idesc = kFp4 ? ptx::idesc_nvfp4(BM, BN) : ptx::idesc_e4m3(BM, BN);
-      const uint32_t my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  } else if (warp == 1 && rank != 0) {
+    // ------------------------------- odd CTA of a pair: relay (FP8) ---------------------------
+    // Tells the issuer in the even CTA that this CTA's operands have landed.  NVFP4 needs no
+    // relay: the scale movers, who wait for the operands, arrive on the issuer's barrier.
+    if (!kFp4 && ptx::elect_one()) {
       const uint32_t total_steps = my_tiles * k_stages;
-      uint32_t as = 0, aphase = 0;
       uint32_t stage = 0, phase = 0;
       for (uint32_t step = 0; step < total_steps && !*abort_flag; ++step) {
-        const uint32_t ks = step % k_stages;
-        if (ks == 0) {
-          if (!ptx::mbar_wait(&acc_empty[as], aphase ^ 1)) { fail_wait(2); break; }
-          ptx::tc_fence_after();
-        }
-        // NVFP4 waits for the scale movers (who waited for the operands); FP8 for the operands.
-        if (!ptx::mbar_wait(kFp4 ? &sf_ready[stage] : &full[stage], phase)) { fail_wait(3); break; }
-        ptx::tc_fence_after();
-        const uint32_t tmem_acc = tmem_base + as * BN;
-        const uint32_t n_mma = min(4u, (p.k - ks * C::kKPerStage) / C::kKPerMma);
-        const uint64_t a_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_a + stage * C::kABytes));
-        const uint64_t b_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_b + stage * C::kBBytes));
-        if constexpr (kFp4) {
-          const uint32_t region = step % C::kSfStages;
-          const uint32_t tsfa = tmem_base + C::kAccCols + region * C::kSfColsPerStage;
-          const uint32_t tsfb = tsfa + C::kSfaCols;
-          for (uint32_t j = 0; j < n_mma; ++j)
-            ptx::tc_mma_nvfp4(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, tsfa + j * 4,
-                              tsfb + j * C::kSfbColsPerMma, (ks | j) != 0 ? 1u : 0u);
-        } else {
-          for (uint32_t j = 0; j < n_mma; ++j)
-            ptx::tc_mma_f8(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, (ks | j) != 0 ? 1u : 0u);
-        }
-        ptx::tc_commit(&empty[stage]);
-        if constexpr (kFp4) ptx::tc_commit(&sf_free[step % C::kSfStages]);
+        if (!ptx::mbar_wait(&full[stage], phase)) { fail_wait(7); break; }
+        arrive_issuer(&peer_full[stage]);
         if (++stage == kStages) { stage = 0; phase ^= 1; }
-        if (ks + 1 == k_stages) {
-          ptx::tc_commit(&acc_full[as]);
-          if (++as == kAccStages) { as = 0; aphase ^= 1; }
-        }
       }
     }
-  } else if (kFp4 && warp >= 6 && warp < 10) {
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -----------------------------------------------
+    // One thread issues everything.  Its instruction stream is on the critical path (an MMA
+    // takes about 50 clocks to issue and 128 to execute, a barrier poll about 160 to return),
+    // so the barrier of the NEXT step is polled before this step's MMAs are issued and the
+    // answer is only looked at one iteration later.
+    if (ptx::elect_one()) {
+      constexpr uint32_t kM = kPair ? 2 * BM : BM;
+      constexpr uint32_t idesc = kFp4 ? ptx::idesc_nvfp4(kM, BN) : ptx::idesc_e4m3(kM, BN);
+      uint32_t as = 0, aphase = 0;
+      uint32_t stage = 0, phase = 0;
+      bool ready = false;
+      for (uint32_t t = 0; t < my_tiles && !*abort_flag; ++t) {
+        if (!wait_issuer(&acc_empty[as], aphase ^ 1)) { fail_wait(2); break; }
+        const uint32_t tmem_acc = tmem_base + as * BN;
+        uint32_t k_left = p.k;
+        bool ok = true;
+        for (uint32_t ks = 0; ks < k_stages; ++ks, k_left -= C::kKPerStage) {
+          // NVFP4 waits for the scale movers (who waited for the operands); FP8 for the operands.
+          if (!ready) {
+            if constexpr (kFp4) {
+              ok = wait_issuer(&sf_ready[stage], phase);
+            } else {
+              ok = ptx::mbar_wait(&full[stage], phase);
+              if constexpr (kPair) ok = ok && wait_issuer(&peer_full[stage], phase);
+            }
+            if (!ok) { fail_wait(3); break; }
+          }
+          ptx::tc_fence_after();
+          const uint32_t next_stage = stage + 1 == kStages ? 0 : stage + 1;
+          const uint32_t next_phase = stage + 1 == kStages ? phase ^ 1 : phase;
+          const uint32_t n_mma = min(4u, k_left / C::kKPerMma);
+          const uint64_t a_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_a + stage * C::kABytes));
+          const uint64_t b_desc = ptx::smem_desc_k128_swizzled(ptx::smem_addr(stage_b + stage * C::kBBytes));
+          // What the next step will wait for: NVFP4 the scale movers (who waited for the operands),
+          // FP8 the operands of this CTA and, in a pair, of the odd CTA.
+          uint64_t* poll0 = kFp4 ? &sf_ready[next_stage] : &full[next_stage];
+          uint64_t* poll1 = (!kFp4 && kPair) ? &peer_full[next_stage] : poll0;
+          if constexpr (kFp4) {
+            const uint32_t tsfa = tmem_base + C::kAccCols + stage * C::kSfColsPerStage;
+            const uint32_t tsfb = tsfa + C::kSfaCols;
+            if (n_mma == 4) {
+              if constexpr (kPair)
+                ready = ptx::tc_mma4_nvfp4_pair_poll(tmem_acc, a_desc, b_desc, idesc, ks, tsfa, tsfb,
+                                                     C::kSfbColsPerMma, poll0, poll1, next_phase);
+              else
+                ready = ptx::tc_mma4_nvfp4_poll(tmem_acc, a_desc, b_desc, idesc, ks, tsfa, tsfb,
+                                                C::kSfbColsPerMma, poll0, poll1, next_phase);
+            } else {
+              ready = false;
+              for (uint32_t j = 0; j < n_mma; ++j) {
+                if constexpr (kPair)
+                  ptx::tc_mma_nvfp4_pair(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, tsfa + j * 4,
+                                         tsfb + j * C::kSfbColsPerMma, (ks | j) != 0 ? 1u : 0u);
+                else
+                  ptx::tc_mma_nvfp4(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, tsfa + j * 4,
+                                    tsfb + j * C::kSfbColsPerMma, (ks | j) != 0 ? 1u : 0u);
+              }
+            }
+          } else {
+            if (n_mma == 4) {
+              if constexpr (kPair)
+                ready = ptx::tc_mma4_f8_pair_poll(tmem_acc, a_desc, b_desc, idesc, ks, poll0, poll1, next_phase);
+              else
+                ready = ptx::tc_mma4_f8_poll(tmem_acc, a_desc, b_desc, idesc, ks, poll0, poll1, next_phase);
+            } else {
+              ready = false;
+              for (uint32_t j = 0; j < n_mma; ++j) {
+                if constexpr (kPair)
+                  ptx::tc_mma_f8_pair(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, (ks | j) != 0 ? 1u : 0u);
+                else
+                  ptx::tc_mma_f8(tmem_acc, a_desc + j * 2, b_desc + j * 2, idesc, (ks | j) != 0 ? 1u : 0u);
+              }
+            }
+          }
+          commit(&empty[stage]);   // frees the operand stage and, NVFP4, its scale region
+          stage = next_stage;
+          phase = next_phase;
+        }
+        if (!ok) break;
+        commit(&acc_full[as]);
+        if (++as == kAccStages) { as = 0; aphase ^= 1; }
+      }
+    }
+  } else if (kFp4 && ((warp >= 6 && warp < 10) || warp >= 14)) {
     // ------------------------------- scale movers (NVFP4) ------------------------------------
+    // Two sets of four warps (one warp per TMEM lane quarter), since one trip of this loop
+    // (barrier poll, shared loads, tcgen05.st, wait, arrive) takes longer than a step's four
+    // MMAs.  Set 0 owns the even stages and set 1 the odd ones: every use of a stage's barrier is
+    // then seen by the same warps in order, which the parity waits rely on (a waiter that skipped
+    // a phase would take the older phase's completion for the one it wants).  Per stage each
+    // lane reads its 16-byte rows of the staged scale chunks (one row = the four TMEM columns of
+    // one MMA) and writes them to the stage's TMEM region with two wide tcgen05.st.  The set's
+    // next barrier is polled while the loads are in flight.
     if constexpr (kFp4) {
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-      const uint32_t my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
       const uint32_t total_steps = my_tiles * k_stages;
-      uint32_t stage = 0, phase = 0;
-      for (uint32_t step = 0; step < total_steps && !*abort_flag; ++step) {
-        if (!ptx::mbar_wait(&full[stage], phase)) { fail_wait(5); break; }
-        // The TMEM region is reused every kSfStages steps: wait until the MMAs that read its
-        // previous contents have completed.
-        const uint32_t region = step % C::kSfStages;
-        if (!ptx::mbar_wait(&sf_free[region], ((step / C::kSfStages) & 1) ^ 1)) { fail_wait(6); break; }
+      static_assert(kStages % 2 == 1 && kStages >= 3, "the mover sets split an odd number of stages");
+      const uint32_t mset = warp >= 14 ? 1u : 0u;
+      uint32_t stage = mset, phase = 0, step = mset, ks = mset % k_stages;
+      bool ready = false;
+      while (step < total_steps && !*abort_flag) {
+        if (!ready && !ptx::mbar_wait(&full[stage], phase)) { fail_wait(5); break; }
+        // A full stage means its previous MMAs completed (the producer waited for that), so the
+        // stage's TMEM scale region is free as well.
         ptx::tc_fence_after();
-        const uint32_t ks = step % k_stages;
         const uint32_t n_mma = min(4u, (p.k - ks * C::kKPerStage) / C::kKPerMma);
-        const uint32_t tsfa = tmem_base + C::kAccCols + region * C::kSfColsPerStage + lane_base;
+        const uint32_t tsfa = tmem_base + C::kAccCols + stage * C::kSfColsPerStage + lane_base;
         const uint32_t tsfb = tsfa + C::kSfaCols;
         const uint8_t* sfa_s = stage_sfa + stage * C::kSfaBytes + lane * 16;
         const uint8_t* sfb_s = stage_sfb + stage * C::kSfbBytes + lane * 16;
-        // A 512-byte chunk holds, for row r of 32, sixteen bytes: four 32-row groups x four K
-        // blocks.  Lane r's 16 bytes are exactly its four TMEM columns for one MMA.
-        uint32_t mt, nt;
-        tile_coords(blockIdx.x + (step / k_stages) * gridDim.x, mt, nt);
-        const bool mid_group = ((nt * BN) % 128) != 0;  // only possible for 192-wide tiles
-        for (uint32_t j = 0; j < n_mma; ++j) {
-          ptx::tc_st_32x32b_x4(tsfa + j * 4, *reinterpret_cast<const uint4*>(sfa_s + j * 512));
-          const uint4 g0 = *reinterpret_cast<const uint4*>(sfb_s + j * 512);
-          if constexpr (BN == 128) {
-            ptx::tc_st_32x32b_x4(tsfb + j * 4, g0);
-          } else {
-            const uint4 g1 = *reinterpret_cast<const uint4*>(sfb_s + 2048 + j * 512);
-            if constexpr (BN == 256) {
-              ptx::tc_st_32x32b_x4(tsfb + j * 8, g0);
-              ptx::tc_st_32x32b_x4(tsfb + j * 8 + 4, g1);
-            } else if (mid_group) {   // rows 64..127 of the first group, then the whole second
-              ptx::tc_st_32x32b_x2(tsfb + j * 6, g0.z, g0.w);
-              ptx::tc_st_32x32b_x4(tsfb + j * 6 + 2, g1);
-            } else {                  // the whole first group, then rows 0..63 of the second
-              ptx::tc_st_32x32b_x4(tsfb + j * 6, g0);
-              ptx::tc_st_32x32b_x2(tsfb + j * 6 + 4, g1.x, g1.y);
-            }
+        // This set's next stage: two further, or back to its first one (set 0 wraps from the last
+        // stage to stage 0, one step later; set 1 from the last but one to stage 1, three later).
+        uint32_t next_stage = stage + 2, next_phase = phase, delta = 2;
+        if (next_stage >= kStages) {
+          next_stage = mset;
+          next_phase ^= 1;
+          delta = mset ? 3 : 1;
+        }
+        if (n_mma == 4) {
+          uint4 a4[4], b4[4 * C::kSfbGroups];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            a4[j] = *reinterpret_cast<const uint4*>(sfa_s + j * 512);
+#pragma unroll
+            for (int g = 0; g < C::kSfbGroups; ++g)
+              b4[j * C::kSfbGroups + g] = *reinterpret_cast<const uint4*>(sfb_s + g * 2048 + j * 512);
+          }
+          ready = ptx::mbar_test_wait(&full[next_stage], next_phase);
+          ptx::tc_st_32x32b_x16(tsfa, a4);
+          if constexpr (C::kSfbGroups == 2) ptx::tc_st_32x32b_x32(tsfb, b4);
+          else ptx::tc_st_32x32b_x16(tsfb, b4);
+        } else {
+          // Last stage of a K that is not a multiple of 256: fewer MMAs, fewer scale rows staged.
+          ready = false;
+          for (uint32_t j = 0; j < n_mma; ++j) {
+            ptx::tc_st_32x32b_x4(tsfa + j * 4, *reinterpret_cast<const uint4*>(sfa_s + j * 512));
+            for (int g = 0; g < C::kSfbGroups; ++g)
+              ptx::tc_st_32x32b_x4(tsfb + j * C::kSfbColsPerMma + g * 4,
+                                   *reinterpret_cast<const uint4*>(sfb_s + g * 2048 + j * 512));
           }
         }
         ptx::tc_wait_st();
         ptx::tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&sf_ready[stage]);
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        if (lane == 0) arrive_issuer(&sf_ready[stage]);
+        stage = next_stage;
+        phase = next_phase;
+        step += delta;
+        ks += delta;
+        while (ks >= k_stages) ks -= k_stages;
       }
     }
   } else {
     // ------------------------------- epilogue -------------------------------------------------
     // Two sets of four warps; set s drains the 64-column sub-tiles s, s+2, ... of every tile.
     const uint32_t quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    const uint32_t set = warp >= 6 ? 1u : 0u;
+    const uint32_t set = warp >= (kFp4 ? 10 : 6) ? 1u : 0u;
     uint8_t* my_stage = epi_stage + (set * 4 + quarter) * 4096;
     uint32_t as = 0, aphase = 0;
-    for (uint32_t tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+    for (uint32_t tile = first_tile; tile < num_tiles && !*abort_flag; tile += tile_stride) {
       uint32_t mt, nt;
       tile_coords(tile, mt, nt);
+      // The staging buffer must be free again (the previous tile's last store has read it); checked
+      // here, while the tile is still being computed, rather than after the accumulator is full.
+      if (lane == 0) ptx::bulk_wait_group_read<0>();
+      __syncwarp();
       if (!ptx::mbar_wait(&acc_full[as], aphase)) { fail_wait(4); break; }
       ptx::tc_fence_after();
       const uint32_t row0 = mt * BM + quarter * 32;
@@ -332,7 +448,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       if (kFp4 && p.w_divisors != nullptr)
         row_scale = __fdiv_rn(1.0f, __fmul_rn(p.ga, __ldg(p.w_divisors + (tile_expert ? __ldg(tile_expert + mt) : 0))));
       const uint32_t tmem_acc = tmem_base + as * BN + ((quarter * 32) << 16);
-      bool released = false;
+      bool released = false, deferred = false;
+      uint32_t deferred_col = 0;
+      // Hands the staged sub-tile to a TMA store.
+      auto store_staged = [&](uint32_t col) {
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::tma_store_2d(&map_out, my_stage, static_cast<int32_t>(col), static_cast<int32_t>(row0));
+          ptx::bulk_commit_group();
+        }
+      };
 #pragma unroll 1
       for (uint32_t c = set; c < BN / 64; c += 2) {
         const uint32_t col0 = nt * BN + c * 64;
@@ -402,27 +528,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
           continue;
         }
-        // The staging buffer about to be overwritten was handed to a TMA store one sub-tile ago.
-        if (lane == 0) ptx::bulk_wait_group_read<0>();
-        __syncwarp();
+        // Plain bf16 output.  Nothing slow may sit between the accumulator becoming full and its
+        // release (the MMA issuer is idle meanwhile): a warp's first sub-tile is converted and
+        // staged but its proxy fence and TMA store wait until the last sub-tile is in registers
+        // and the accumulator has been released.
         ptx::tc_wait_ld();
         if (c + 2 >= BN / 64) {
-          // This warp's last sub-tile is in registers: the accumulator can be overwritten while
-          // the conversion and the store below are still running.
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
+          if (lane == 0) arrive_issuer(&acc_empty[as]);
           released = true;
         }
-        uint8_t* sbuf = my_stage;
-        auto convert = [&](const uint32_t (&v)[32], int half) {
+        if (deferred) {
+          store_staged(deferred_col);
+          deferred = false;
+          if (lane == 0) ptx::bulk_wait_group_read<0>();  // the staging buffer is about to be rewritten
+          __syncwarp();
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint32_t packed[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const int e = q * 8 + i * 2;  // column within this 32-column half
-              float lo = __uint_as_float(v[e]), hi = __uint_as_float(v[e + 1]);
+              float lo = __uint_as_float(half == 0 ? v0[e] : v1[e]);
+              float hi = __uint_as_float(half == 0 ? v0[e + 1] : v1[e + 1]);
               if constexpr (kFp4) {
                 lo = __fmul_rn(lo, row_scale);
                 hi = __fmul_rn(hi, row_scale);
@@ -434,26 +566,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
               }
               packed[i] = pack_bf16x2(lo, hi);
             }
-            // 16-byte chunk j of row `lane`, stored at chunk j ^ (lane % 8): the 128-byte swizzle
-            // the output tensor map expects, and conflict free for the warp.
+            // 16-byte chunk j of row `lane` goes to chunk j ^ (lane % 8): the 128-byte swizzle the
+            // output tensor map expects, and conflict free for the warp.
             const int j = half * 4 + q;
-            *reinterpret_cast<uint4*>(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            *reinterpret_cast<uint4*>(my_stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
                 make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
-        };
-        convert(v0, 0);
-        convert(v1, 1);
-        ptx::fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          ptx::tma_store_2d(&map_out, sbuf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
-          ptx::bulk_commit_group();
+        }
+        if (c + 2 >= BN / 64) {
+          store_staged(col0);
+        } else {
+          deferred = true;
+          deferred_col = col0;
         }
       }
+      if (deferred) store_staged(deferred_col);
       if (!released) {
         ptx::tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
+        if (lane == 0) arrive_issuer(&acc_empty[as]);
       }
       if (++as == kAccStages) { as = 0; aphase ^= 1; }
     }
@@ -468,9 +599,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  // Neither CTA of a pair may leave while the other can still reach its shared memory or barriers.
+  if constexpr (kPair) ptx::cluster_sync();
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, 512);
+    if constexpr (kPair) ptx::tmem_dealloc_pair(tmem_base, 512);
+    else ptx::tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -543,34 +677,68 @@ int32_t make_out_map_f32(const char* op, CUtensorMap* map, void* base, uint64_t 
   return GEMB_OK;
 }
 
-int g_gemm_bn = 0;  // 0 = automatic; gemb_set_tuning(GEMB_TUNE_GEMM_BN, 128 | 256)
+int g_gemm_bn = 0;    // 0 = automatic; gemb_set_tuning(GEMB_TUNE_GEMM_BN, 128 | 256)
+int g_gemm_pair = 0;  // 0 = automatic (pairs for the dense 256-wide tile), 1 = never, 2 = always
 
-template <bool kFp4, int BN, int kStages, int kAccStages>
+bool use_pairs() { return g_gemm_pair != 1 && (g_gemm_bn == 0 || g_gemm_bn == 256); }
+
+template <bool kFp4, int BN, int kStages, int kAccStages, bool kPair = false>
 int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmParams& p, cudaStream_t stream) {
-  using C = Cfg<kFp4, BN, kStages, kAccStages>;
-  auto kern = gemm_kernel<kFp4, BN, kStages, kAccStages>;
+  using C = Cfg<kFp4, BN, kStages, kAccStages, kPair>;
+  auto kern = gemm_kernel<kFp4, BN, kStages, kAccStages, kPair>;
+  constexpr unsigned kThreads = kFp4 ? kGemmThreadsFp4 : kGemmThreadsFp8;
   static bool configured[64] = {false};
+  static int max_pairs[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
   dev &= 63;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = kPair ? 1 : 0;
   if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+    if constexpr (kPair) {
+      // How many CTA pairs the device can hold at once: the persistent grid is sized to it.
+      cfg.gridDim = dim3(static_cast<unsigned>(sm_count()) & ~1u);
+      int clusters = 0;
+      e = cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg);
+      if (e != cudaSuccess || clusters <= 0) {
+        cudaGetLastError();
+        return fail(GEMB_INTERNAL, "%s: CTA pairs cannot be scheduled on this device (%s)", op, cudaGetErrorName(e));
+      }
+      max_pairs[dev] = clusters;
+      if (std::getenv("GEMB_DEBUG")) std::fprintf(stderr, "max_pairs=%d\n", clusters);
+    }
     configured[dev] = true;
   }
   const uint64_t row_bytes = kFp4 ? p.k / 2 : p.k;
   CUtensorMap map_a, map_b, map_out;
   GEMB_TRY(make_byte_map(op, &map_a, a, p.m, row_bytes, BM));
-  GEMB_TRY(make_byte_map(op, &map_b, b, static_cast<uint64_t>(p.n) * (p.plan ? p.experts : 1u), row_bytes, BN));
+  GEMB_TRY(make_byte_map(op, &map_b, b, static_cast<uint64_t>(p.n) * (p.plan ? p.experts : 1u), row_bytes, C::kBRows));
   if (p.out_f32)
     GEMB_TRY(make_out_map_f32(op, &map_out, p.out, p.m, p.n));
   else if (p.gated)  // the tensor-map store path is unused; describe the payload buffer so the map is valid
     GEMB_TRY(make_out_map(op, &map_out, p.out_packed, p.m, p.n / 8));
   else
     GEMB_TRY(make_out_map(op, &map_out, p.out, p.m, p.n));
-  const uint32_t tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
-  const unsigned grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(sm_count()));
-  kern<<<grid, kFp4 ? kGemmThreadsFp4 : kGemmThreadsFp8, C::kSmemBytes, stream>>>(map_a, map_b, map_out, p);
+  const uint32_t m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
+  if constexpr (kPair) {
+    const uint32_t units = ((m_tiles + 1) / 2) * n_tiles;
+    cfg.gridDim = dim3(2 * std::min<uint32_t>(units, static_cast<uint32_t>(max_pairs[dev])));
+  } else {
+    cfg.gridDim = dim3(std::min<uint32_t>(m_tiles * n_tiles, static_cast<uint32_t>(sm_count())));
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_a, map_b, map_out, p);
+  if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
   return check_launch(op);
 }
 
@@ -587,9 +755,14 @@ int32_t validate_gemm(const char* op, uint64_t tokens, uint64_t rows, uint64_t k
 
 int32_t gemm_set_tuning(int32_t knob, int32_t value) {
   if (knob == GEMB_TUNE_GEMM_BN) {
-    GEMB_REQUIRE(value == 0 || value == 128 || value == 192 || value == 256,
-                 "gemb_set_tuning: GEMM tile width must be 0 (auto), 128, 192 or 256");
+    GEMB_REQUIRE(value == 0 || value == 128 || value == 256,
+                 "gemb_set_tuning: GEMM tile width must be 0 (auto), 128 or 256");
     g_gemm_bn = value;
+    return GEMB_OK;
+  }
+  if (knob == GEMB_TUNE_GEMM_PAIR) {
+    GEMB_REQUIRE(value >= 0 && value <= 2, "gemb_set_tuning: GEMM pairing must be 0 (auto), 1 (off) or 2 (on)");
+    g_gemm_pair = value;
     return GEMB_OK;
   }
   return fail(GEMB_INVALID_ARGUMENT, "gemb_set_tuning: unknown knob %d", knob);
@@ -623,9 +796,9 @@ int32_t gemb_nvfp4_gemm_bf16(const uint8_t* act, const uint8_t* act_scales_inter
   p.n = static_cast<uint32_t>(rows);
   p.k = static_cast<uint32_t>(k);
   p.alpha = 1.0f / (ga * gw);  // one multiply in the epilogue, as src/cuda/nvfp4/cutlass_sm120.cu:551-552
-  const int bn = g_gemm_bn ? g_gemm_bn : 256;  // 256 measured fastest; 192 and 128 stay selectable
+  const int bn = g_gemm_bn ? g_gemm_bn : 256;  // 256 measured fastest; 128 stays selectable
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
-  if (bn == 192) return launch_gemm<true, 192, 4, 2>(op, act, w, p, stream);
+  if (use_pairs()) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
   return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
 }
 
@@ -654,7 +827,7 @@ int32_t gemb_nvfp4_gemm_f32(const uint8_t* act, const uint8_t* act_scales_interl
   p.alpha = 1.0f / (ga * gw);
   const int bn = g_gemm_bn ? g_gemm_bn : 256;
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
-  if (bn == 192) return launch_gemm<true, 192, 4, 2>(op, act, w, p, stream);
+  if (use_pairs()) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
   return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
 }
 
@@ -690,7 +863,6 @@ int32_t gemb_moe_grouped_gemm_bf16(const uint8_t* act, const uint8_t* act_scales
   p.alpha = 1.0f;
   const int bn = g_gemm_bn ? g_gemm_bn : 256;
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
-  if (bn == 192) return launch_gemm<true, 192, 4, 2>(op, act, w, p, stream);
   return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
 }
 
@@ -747,7 +919,8 @@ extern "C" int32_t gemb_nvfp4_pack_gate_up(const uint8_t* gate_packed, const uin
 static int32_t launch_gated(const char* op, const uint8_t* act, const uint8_t* w, GemmParams& p, cudaStream_t stream) {
   const int bn = g_gemm_bn ? g_gemm_bn : 256;
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
-  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);   // 192 is not a multiple of 64 gate/up runs per tile pair
+  if (!p.plan && use_pairs()) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
+  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
 }
 
 int32_t gemb_nvfp4_gemm_gated_quant(const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* w_fused,
@@ -844,6 +1017,7 @@ int32_t gemb_fp8_gemm_bf16(const uint8_t* act, const float* act_scales, const ui
   p.alpha = 1.0f;
   const int bn = g_gemm_bn == 128 ? 128 : 256;
   if (bn == 128) return launch_gemm<false, 128, 6, 2>(op, act, w, p, stream);
+  if (use_pairs()) return launch_gemm<false, 256, 6, 2, true>(op, act, w, p, stream);
   return launch_gemm<false, 256, 4, 2>(op, act, w, p, stream);
 }
 

@@ -77,9 +77,17 @@ int32_t gemb_device_check(void);
  * GEMVs, value 0 (automatic), 1, 2 or 4; GEMB_TUNE_GEMV_PDL = launch the decode GEMVs with
  * programmatic stream serialization so a GEMV's weight prefetch overlaps the tail of the kernel
  * before it (1, default) or not (0); GEMB_TUNE_GEMM_BN = output-feature width of a prefill GEMM
- * tile, 0 (automatic), 128, 192 or 256; GEMB_TUNE_GEMV_IMPL = FP8 decode GEMV data path, 0 (automatic),
- * 1 (direct global loads) or 2 (bulk-copy ring through shared memory wherever it fits). */
-enum { GEMB_TUNE_GEMV_ROWS = 1, GEMB_TUNE_GEMV_PDL = 2, GEMB_TUNE_GEMM_BN = 3, GEMB_TUNE_GEMV_IMPL = 4 };
+ * tile, 0 (automatic), 128 or 256; GEMB_TUNE_GEMV_IMPL = FP8 decode GEMV data path, 0 (automatic),
+ * 1 (direct global loads) or 2 (bulk-copy ring through shared memory wherever it fits);
+ * GEMB_TUNE_GEMM_PAIR = dense prefill GEMMs on CTA pairs (two SMs share one 256 x 256 tile and
+ * each stages half of the weight tile), 0 (automatic), 1 (never) or 2 (always, when the tile is 256 wide). */
+enum {
+  GEMB_TUNE_GEMV_ROWS = 1,
+  GEMB_TUNE_GEMV_PDL = 2,
+  GEMB_TUNE_GEMM_BN = 3,
+  GEMB_TUNE_GEMV_IMPL = 4,
+  GEMB_TUNE_GEMM_PAIR = 5
+};
 int32_t gemb_set_tuning(int32_t knob, int32_t value);
 /* Bytes of an INTERLEAVED scale buffer for `rows` rows of K elements. */
 uint64_t gemb_interleaved_scale_bytes(uint64_t rows, uint64_t contracting_elements);
