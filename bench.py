@@ -42,6 +42,11 @@ LAYERS = 48
 SEED = 20261125
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the captured fp8_gemv_kernel launches divided by
+# their algorithmic bytes (profiles/fp8_gemv_kernel_decode.md).
+NCU_TRAFFIC_OVER_ALGORITHMIC = 1.00
+
+
 def decode_bytes_per_layer() -> int:
     """Algorithmic bytes of one layer: weights + fp32-equivalent scales + bf16 x + bf16 y."""
     total = 0
@@ -225,6 +230,19 @@ def run_decode_gemv(args):
                 n += 1
         return n * (2 if split else 1)
 
+    def enqueue_gemvs_only():
+        # The same projections on the already quantised activations: the dominant kernel alone,
+        # for the roofline object (its launches are 99.9 % of the bytes of a pass).
+        xo = yo = n = 0
+        st = torch.cuda.current_stream()
+        for mats in weights:
+            for (wq, ws), (_, rows, k) in zip(mats, DECODE_SHAPES):
+                lib.gemb_fp8_gemv(xq_dev[xo:xo + k], xs_dev[n:n + 1], wq, ws, y32_dev[yo:yo + rows], rows, k, st)
+                xo += k
+                yo += rows
+                n += 1
+        return n
+
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
         launches_per_step = enqueue_pass()  # also warms lazily initialised state before capture
@@ -232,6 +250,14 @@ def run_decode_gemv(args):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             enqueue_pass()
+        gemv_graph = None
+        gemv_launches = 0
+        if split:
+            gemv_launches = enqueue_gemvs_only()
+            stream.synchronize()
+            gemv_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gemv_graph, stream=stream):
+                enqueue_gemvs_only()
 
         def barrier():
             torch.cuda.synchronize(dev)
@@ -273,13 +299,18 @@ def run_decode_gemv(args):
         for _ in range(2):
             step_e2e()
         secs_e2e = timed(step_e2e, args.steps)
+        secs_gemv = None
+        if gemv_graph is not None:
+            for _ in range(3):
+                gemv_graph.replay()
+            secs_gemv = timed(gemv_graph.replay, args.steps)
 
     bytes_step = decode_bytes_per_layer() * layers
     value = world * bytes_step * args.steps / secs / 1e9
     e2e = world * bytes_step * args.steps / secs_e2e / 1e9
     moe_ep = tp_mlp = None
     if not args.no_other_workloads:
-        del weights, graph
+        del weights, graph, gemv_graph
         torch.cuda.empty_cache()
         try:   # collective: every rank takes part
             moe_ep = bench_moe_ep(lib, dev, world, rank)
@@ -295,8 +326,16 @@ def run_decode_gemv(args):
             dist.destroy_process_group()
         return
     peaks = measured_peaks()
-    launch_s = secs / (args.steps * launches_per_step)
-    achieved = bytes_step / launches_per_step / launch_s / 1e9
+    # Roofline of the dominant kernel: algorithmic bytes of one GEMV launch (its weight matrix, the
+    # bf16 row scales, the activation and the output; the pass total / launches) over that kernel's
+    # average launch duration, timed with CUDA events over a region that launches only it.
+    if secs_gemv is not None:
+        launch_s = secs_gemv / (args.steps * gemv_launches)
+        achieved = bytes_step / gemv_launches / launch_s / 1e9
+    else:
+        launch_s = secs / (args.steps * launches_per_step)
+        achieved = bytes_step / launches_per_step / launch_s / 1e9
+    whole_pass = bytes_step * args.steps / secs / 1e9 if world == 1 else value / world
     line = {
         "metric": "decode GEMV GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
@@ -307,11 +346,19 @@ def run_decode_gemv(args):
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": x_elems * 2, "d2h_bytes_per_step": y_elems * (4 if split else 2)},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "fp8_gemv_kernel" + (" + fp8_quantize_decode_kernel" if split else " (bf16-in fused quantisation)"),
+        "roofline": {"bound": "hbm", "kernel": "fp8_gemv_kernel" + ("" if split else " (bf16-in fused quantisation)"),
                      "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                     "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": None,
-                     "avg_launch_us": launch_s * 1e6},
+                     "frac_of_nominal_8TBs": achieved / 8000.0,
+                     # dram read + write bytes per launch from the committed ncu capture of this kernel
+                     # (profiles/fp8_gemv_kernel_decode.md), as a ratio to the algorithmic bytes
+                     "traffic": NCU_TRAFFIC_OVER_ALGORITHMIC * bytes_step / (gemv_launches if secs_gemv is not None else launches_per_step),
+                     "traffic_unit": "bytes per launch (average)",
+                     "algorithmic_bytes_per_launch": bytes_step / (gemv_launches if secs_gemv is not None else launches_per_step),
+                     "avg_launch_us": launch_s * 1e6,
+                     "whole_pass": {"kernels": "fp8_quantize_decode_kernel + fp8_gemv_kernel" if split else "fp8_gemv_kernel",
+                                    "achieved": whole_pass, "frac": whole_pass / peaks["hbm_gbs"],
+                                    "launches_per_pass": launches_per_step}},
     }
     if moe_ep is not None:
         line["other_workloads"] = {"moe_ep_stack": moe_ep}
@@ -401,7 +448,7 @@ def bench_nvfp4_linear(lib, dev):
     return {"metric": "NVFP4 GEMM TFLOP/s", "workload": "nvfp4_linear 512x15360x3840 (W4A4)",
             "value": flops / t_gemm / 1e12, "unit": "TFLOP/s", "us_per_linear": t_gemm * 1e6,
             "with_activation_quantizer": {"value": flops / t_both / 1e12, "us_per_linear": t_both * 1e6},
-            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<nvfp4, 128x256>", "achieved": flops / t_gemm / 1e12,
+            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<nvfp4, 256x256 on CTA pairs>", "achieved": flops / t_gemm / 1e12,
                          "peak": nominal, "unit": "TFLOP/s", "frac": flops / t_gemm / 1e12 / nominal,
                          "peak_source": "nominal dense FP4 (9 PFLOP/s); MEASURED_PEAKS.json has no FP4 figure",
                          "frac_of_4x_measured_bf16_sustained": flops / t_gemm / 1e12 / (4 * 1391.3)},
