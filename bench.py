@@ -634,11 +634,12 @@ def bench_tp_mlp(lib, dev, world, rank, tokens=16384):
 
 def bench_moe_ep(lib, dev, world, rank, layers=30, phases=((16384, "prefill"), (64, "decode"))):
     """Expert-parallel MoE stack: `layers` distinct 26B-A4B-like layers, experts split evenly over
-    the ranks, tokens data-sharded, NCCL all-to-all dispatch/combine.  Collective: every rank calls
-    it; returns the summary on every rank (times are the max over ranks)."""
+    the ranks, tokens data-sharded; dispatch and combine by the library's pull kernels over peer
+    memory (NCCL all-to-all if no peer mapping can be had).  Collective: every rank calls it;
+    returns the summary on every rank (times are the max over ranks)."""
     import torch
     import torch.distributed as dist
-    from gem16_b200.ep import EpMoeLayer
+    from gem16_b200.ep import EpMoeLayer, EpPullMoeLayer
     from gem16_b200.moe import MoeLayer, synthetic_weights
     experts = 128
     e_local = experts // world
@@ -654,8 +655,12 @@ def bench_moe_ep(lib, dev, world, rank, layers=30, phases=((16384, "prefill"), (
         ga = float(2688.0 / x_all.float().abs().max().item())
         x = x_all[rank * t_local:(rank + 1) * t_local].contiguous().view(torch.int16)
         if world > 1:
-            stack = [None] * layers
-            shared_bufs = EpMoeLayer(weights[0], t_local, 8, ga, 336.0, 336.0)
+            try:
+                shared_bufs = EpPullMoeLayer(weights[0], t_local, 8, ga, 336.0, 336.0)
+                out["exchange"] = "pull kernels over peer memory (" + shared_bufs.send.how + ")"
+            except Exception as exc:
+                shared_bufs = EpMoeLayer(weights[0], t_local, 8, ga, 336.0, 336.0)
+                out["exchange"] = f"NCCL all-to-all ({type(exc).__name__}: {exc})"[:300]
             def run():
                 for w in weights:
                     shared_bufs.w = w

@@ -1,0 +1,271 @@
+// Expert parallelism over peer memory (NVLink / NVSwitch): the dispatch and the combine of the
+// mixture-of-experts layer as kernels that PULL rows straight out of the other GPUs' buffers with
+// plain global loads, instead of an all-to-all followed by local gather / scatter passes.
+//
+// Setting: R ranks (one process per GPU), E experts, rank r owns experts [r*E/R, (r+1)*E/R).
+// Every rank routes its own tokens over all E experts and leaves, in a buffer its peers can map,
+// one quantised message row per assignment in (expert, token, slot) order -- i.e. already grouped
+// by owner.  The per-expert counts of all ranks, C[s][e], are all-gathered (R*E integers; the
+// collective doubles as the "send buffers are complete" barrier).  Everything else follows from
+// C by arithmetic, identically on every rank, so no indices travel and nothing is read back to
+// the host:
+//
+//   rows of expert e held by source s start at      src(s, e) = sum_{e' < e} C[s][e']
+//   on e's owner they land, source after source, at dst(s, e) = pad(e) + sum_{s' < s} C[s'][e]
+//   pad(e) = start of e in the owner's padded row space (every expert starts on a multiple of
+//            128 rows, as the grouped GEMM wants)
+//
+// which is the (expert, global token, slot) order of the single-GPU layer.  After the grouped
+// GEMMs a second tiny collective says "expert outputs are complete", and each token's owner
+// combines its top-k contributions in slot order by reading the rows at dst(me, e) + j from the
+// owners' output buffers.
+//
+// gem16 has no multi-GPU code; this protocol is the library's own.
+#include "common.cuh"
+
+namespace gemb {
+namespace {
+
+constexpr uint32_t kMaxRanks = 16;
+constexpr uint32_t kMaxExperts = 1024;
+
+struct PeerPtrs {
+  const uint8_t* p[kMaxRanks];
+};
+
+// One CTA.  counts_all: [ranks][experts].
+__global__ void __launch_bounds__(256)
+ep_plan_kernel(const int32_t* __restrict__ counts_all, uint32_t ranks, uint32_t experts, uint32_t me,
+               int32_t* __restrict__ plan, int32_t* __restrict__ recv_prefix, int32_t* __restrict__ recv_src,
+               int32_t* __restrict__ recv_dst, int32_t* __restrict__ out_base) {
+  extern __shared__ int sm[];
+  const uint32_t el = experts / ranks;
+  int* tot = sm;                    // [experts] rows of expert e over all sources
+  int* pad = tot + experts;         // [experts] start of e in its owner's padded row space
+  int* before_me = pad + experts;   // [experts] sum_{s' < me} C[s'][e]
+  int* my_pad = before_me + experts;  // [experts] start of e in MY local padded space (single-GPU plan of my tokens)
+  for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
+    int t = 0, b = 0;
+    for (uint32_t s = 0; s < ranks; ++s) {
+      const int c = counts_all[s * experts + e];
+      if (s < me) b += c;
+      t += c;
+    }
+    tot[e] = t;
+    before_me[e] = b;
+  }
+  __syncthreads();
+  // Padded offsets restart at every owner's first expert; one thread per owner, plus one for mine.
+  if (threadIdx.x < ranks) {
+    const uint32_t d = threadIdx.x;
+    int po = 0;
+    for (uint32_t e = d * el; e < (d + 1) * el; ++e) {
+      pad[e] = po;
+      po += (tot[e] + 127) / 128 * 128;
+    }
+    if (d == me) {
+      plan[0] = po / 128;
+      plan[1] = po;
+      plan[2 + el] = po;
+    }
+  } else if (threadIdx.x == ranks) {
+    int po = 0;
+    for (uint32_t e = 0; e < experts; ++e) {
+      my_pad[e] = po;
+      po += (counts_all[me * experts + e] + 127) / 128 * 128;
+    }
+  }
+  __syncthreads();
+  for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x)
+    out_base[e] = pad[e] + before_me[e] - my_pad[e];
+  int32_t* tile_expert = plan + 2 + el + 1;
+  for (uint32_t e = threadIdx.x; e < el; e += blockDim.x) {
+    const uint32_t ge = me * el + e;
+    plan[2 + e] = pad[ge];
+    const int end = pad[ge] + (tot[ge] + 127) / 128 * 128;
+    for (int tile = pad[ge] / 128; tile < end / 128; ++tile) tile_expert[tile] = static_cast<int32_t>(e);
+  }
+  // Segments (source s, local expert e) in source-major order.
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (uint32_t s = 0; s < ranks; ++s) {
+      int src = 0;
+      for (uint32_t e2 = 0; e2 < me * el; ++e2) src += counts_all[s * experts + e2];
+      for (uint32_t e = 0; e < el; ++e) {
+        const uint32_t ge = me * el + e;
+        const uint32_t g = s * el + e;
+        int b = 0;
+        for (uint32_t s2 = 0; s2 < s; ++s2) b += counts_all[s2 * experts + ge];
+        recv_prefix[g] = run;
+        recv_src[g] = src;
+        recv_dst[g] = pad[ge] + b;
+        const int c = counts_all[s * experts + ge];
+        run += c;
+        src += c;
+      }
+    }
+    recv_prefix[ranks * el] = run;
+  }
+}
+
+// Persistent grid, one warp per received row: copies the E2M1 payload into the padded row space and
+// the compact block scales into the interleaved layout.
+__global__ void __launch_bounds__(256)
+ep_pull_dispatch_kernel(PeerPtrs peers, const int32_t* __restrict__ recv_prefix, const int32_t* __restrict__ recv_src,
+                        const int32_t* __restrict__ recv_dst, uint32_t segments, uint32_t el, uint32_t hidden,
+                        uint32_t msg_bytes, uint32_t c_pad, uint8_t* __restrict__ packed,
+                        uint8_t* __restrict__ scales) {
+  extern __shared__ int sm[];
+  int* prefix = sm;  // [segments + 1]
+  for (uint32_t i = threadIdx.x; i <= segments; i += blockDim.x) prefix[i] = recv_prefix[i];
+  __syncthreads();
+  const uint32_t total = static_cast<uint32_t>(prefix[segments]);
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+  const uint32_t payload_vecs = hidden / 32;   // 16-byte vectors of payload per row
+  const uint32_t scale_words = hidden / 64;    // 4-byte words of scales per row (four K blocks each)
+  for (uint32_t r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < total; r += warps) {
+    uint32_t lo = 0, hi = segments;            // last segment whose prefix is <= r
+    while (hi - lo > 1) {
+      const uint32_t mid = (lo + hi) >> 1;
+      if (static_cast<uint32_t>(prefix[mid]) <= r) lo = mid; else hi = mid;
+    }
+    const uint32_t j = r - static_cast<uint32_t>(prefix[lo]);
+    const uint8_t* src = peers.p[lo / el] + static_cast<uint64_t>(__ldg(recv_src + lo) + j) * msg_bytes;
+    const uint64_t d = static_cast<uint64_t>(__ldg(recv_dst + lo)) + j;
+    for (uint32_t v = lane; v < payload_vecs; v += 32)
+      *reinterpret_cast<uint4*>(packed + d * (hidden / 2) + v * 16) = *reinterpret_cast<const uint4*>(src + v * 16);
+    for (uint32_t w = lane; w < scale_words; w += 32)
+      *reinterpret_cast<uint32_t*>(scales + interleaved_scale_offset(d, w * 4, c_pad)) =
+          *reinterpret_cast<const uint32_t*>(src + hidden / 2 + w * 4);
+  }
+}
+
+// Deterministic combine (slot order, one fma per slot) with the expert outputs read from their owners.
+__global__ void __launch_bounds__(256)
+ep_pull_combine_kernel(PeerPtrs peers, const int32_t* __restrict__ ids, const int32_t* __restrict__ slot_rows,
+                       const int32_t* __restrict__ out_base, const float* __restrict__ weights,
+                       const uint16_t* __restrict__ shared_out, uint16_t* __restrict__ out, uint32_t tokens,
+                       uint32_t hidden, uint32_t topk, uint32_t el) {
+  const uint32_t chunks = hidden / 8;
+  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<uint64_t>(tokens) * chunks) return;
+  const uint32_t t = static_cast<uint32_t>(idx / chunks), c = static_cast<uint32_t>(idx % chunks);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  for (uint32_t s = 0; s < topk; ++s) {
+    const uint64_t a = static_cast<uint64_t>(t) * topk + s;
+    const float wv = __ldg(weights + a);
+    const uint32_t e = static_cast<uint32_t>(__ldg(ids + a));
+    const int64_t r = static_cast<int64_t>(__ldg(out_base + e)) + __ldg(slot_rows + a);
+    const uint4 v = *(reinterpret_cast<const uint4*>(peers.p[e / el] + r * hidden * 2) + c);
+    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] = fmaf(wv, __uint_as_float(ww[i] << 16), acc[2 * i]);
+      acc[2 * i + 1] = fmaf(wv, __uint_as_float(ww[i] & 0xFFFF0000u), acc[2 * i + 1]);
+    }
+  }
+  if (shared_out != nullptr) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(shared_out + static_cast<uint64_t>(t) * hidden) + c);
+    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] = __fadd_rn(acc[2 * i], __uint_as_float(ww[i] << 16));
+      acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __uint_as_float(ww[i] & 0xFFFF0000u));
+    }
+  }
+  uint32_t packed[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    packed[i] = static_cast<uint32_t>(float_to_bf16_bits(acc[2 * i])) |
+                (static_cast<uint32_t>(float_to_bf16_bits(acc[2 * i + 1])) << 16);
+  *(reinterpret_cast<uint4*>(out + static_cast<uint64_t>(t) * hidden) + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+}
+
+int32_t load_peers(const char* op, const uint64_t* peer_ptrs, uint64_t ranks, PeerPtrs* out) {
+  GEMB_REQUIRE(peer_ptrs != nullptr, "%s: peer pointer table must be nonnull", op);
+  GEMB_REQUIRE(ranks >= 1 && ranks <= kMaxRanks, "%s: between 1 and %u ranks are supported", op, kMaxRanks);
+  for (uint64_t r = 0; r < kMaxRanks; ++r) {
+    out->p[r] = r < ranks ? reinterpret_cast<const uint8_t*>(peer_ptrs[r]) : nullptr;
+    GEMB_REQUIRE(r >= ranks || (out->p[r] != nullptr && peer_ptrs[r] % 16 == 0),
+                 "%s: every rank's buffer must be mapped and 16-byte aligned", op);
+  }
+  return GEMB_OK;
+}
+
+}  // namespace
+}  // namespace gemb
+
+using namespace gemb;
+
+extern "C" {
+
+uint64_t gemb_moe_ep_plan_ints(uint64_t capacity_rows, uint64_t local_experts) {
+  // tiles, padded rows, local_experts + 1 padded offsets, one expert id per possible tile
+  return 3 + local_experts + (capacity_rows + 127) / 128 + local_experts;
+}
+
+int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t experts, uint64_t rank,
+                         int32_t* plan, int32_t* recv_prefix, int32_t* recv_src_rows, int32_t* recv_dst_rows,
+                         int32_t* combine_row_base, gemb_stream_t stream) {
+  const char* op = "gemb_moe_ep_plan";
+  GEMB_REQUIRE(counts_all && plan && recv_prefix && recv_src_rows && recv_dst_rows && combine_row_base,
+               "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(ranks >= 1 && ranks <= kMaxRanks && rank < ranks, "%s: bad rank geometry", op);
+  GEMB_REQUIRE(experts >= ranks && experts <= kMaxExperts && experts % ranks == 0,
+               "%s: experts must be a multiple of ranks, at most %u", op, kMaxExperts);
+  GEMB_TRY(require_sm100(op));
+  ep_plan_kernel<<<1, 256, 4 * experts * sizeof(int), stream>>>(
+      counts_all, static_cast<uint32_t>(ranks), static_cast<uint32_t>(experts), static_cast<uint32_t>(rank), plan,
+      recv_prefix, recv_src_rows, recv_dst_rows, combine_row_base);
+  return check_launch(op);
+}
+
+int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers, uint64_t ranks, uint64_t local_experts,
+                                  const int32_t* recv_prefix, const int32_t* recv_src_rows,
+                                  const int32_t* recv_dst_rows, uint8_t* packed_e2m1, uint8_t* interleaved_scales,
+                                  uint64_t hidden, uint64_t message_row_bytes, gemb_stream_t stream) {
+  const char* op = "gemb_moe_ep_pull_dispatch";
+  PeerPtrs peers;
+  GEMB_TRY(load_peers(op, peer_send_buffers, ranks, &peers));
+  GEMB_REQUIRE(recv_prefix && recv_src_rows && recv_dst_rows && packed_e2m1 && interleaved_scales,
+               "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(local_experts >= 1 && ranks * local_experts <= kMaxExperts, "%s: bad expert geometry", op);
+  GEMB_REQUIRE(hidden > 0 && hidden % 64 == 0 && hidden < (1ull << 24), "%s: hidden must be a nonzero multiple of 64", op);
+  GEMB_REQUIRE(message_row_bytes % 16 == 0 && message_row_bytes >= hidden / 2 + hidden / 16,
+               "%s: a message row holds the payload and the block scales, padded to 16 bytes", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(packed_e2m1) % 16 == 0 && reinterpret_cast<uintptr_t>(interleaved_scales) % 4 == 0,
+               "%s: outputs must be 16-byte (payload) and 4-byte (scales) aligned", op);
+  GEMB_TRY(require_sm100(op));
+  const uint32_t segments = static_cast<uint32_t>(ranks * local_experts);
+  const uint32_t c_pad = static_cast<uint32_t>((hidden / 16 + 3) / 4 * 4);
+  ep_pull_dispatch_kernel<<<static_cast<unsigned>(sm_count()) * 4, 256, (segments + 1) * sizeof(int), stream>>>(
+      peers, recv_prefix, recv_src_rows, recv_dst_rows, segments, static_cast<uint32_t>(local_experts),
+      static_cast<uint32_t>(hidden), static_cast<uint32_t>(message_row_bytes), c_pad, packed_e2m1, interleaved_scales);
+  return check_launch(op);
+}
+
+int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs, uint64_t ranks, uint64_t local_experts,
+                                 const int32_t* top_ids, const int32_t* slot_rows, const int32_t* combine_row_base,
+                                 const float* top_weights, const uint16_t* shared_bf16, uint16_t* out_bf16,
+                                 uint64_t tokens, uint64_t hidden, uint64_t topk, gemb_stream_t stream) {
+  const char* op = "gemb_moe_ep_pull_combine";
+  PeerPtrs peers;
+  GEMB_TRY(load_peers(op, peer_expert_outputs, ranks, &peers));
+  GEMB_REQUIRE(top_ids && slot_rows && combine_row_base && top_weights && out_bf16, "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(tokens > 0 && tokens < (1ull << 31) && topk >= 1 && topk <= 32, "%s: bad geometry", op);
+  GEMB_REQUIRE(local_experts >= 1 && ranks * local_experts <= kMaxExperts, "%s: bad expert geometry", op);
+  GEMB_REQUIRE(hidden > 0 && hidden % 8 == 0 && hidden < (1ull << 31), "%s: hidden must be a nonzero multiple of 8", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(out_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(shared_bf16) % 16 == 0,
+               "%s: buffers must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  const uint64_t work = tokens * (hidden / 8);
+  ep_pull_combine_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+      peers, top_ids, slot_rows, combine_row_base, top_weights, shared_bf16, out_bf16, static_cast<uint32_t>(tokens),
+      static_cast<uint32_t>(hidden), static_cast<uint32_t>(topk), static_cast<uint32_t>(local_experts));
+  return check_launch(op);
+}
+
+}  // extern "C"

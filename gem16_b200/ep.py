@@ -132,3 +132,123 @@ class EpMoeLayer:
         lib.gemb_moe_combine(self.y_sorted, self.inv_perm, loc.weights, shared, loc.out, t, h, k, None)
         self.last = {"n_recv": n_recv, "send_splits": send_splits, "recv_splits": recv_splits}
         return loc.out
+
+
+class EpPullMoeLayer:
+    """The same layer with the exchange done by this library's own kernels over peer memory
+    (`csrc/ep.cu`): each rank leaves its quantised assignments in a buffer the others have mapped,
+    the owners pull them straight into the grouped GEMM's padded row space, and each token's owner
+    pulls its expert outputs back inside the combine.  All row positions are arithmetic on the
+    all-gathered counts, so nothing is read back to the host and the launch sequence is fixed.
+
+    Ordering between GPUs comes from two tiny NCCL collectives per layer: the all-gather of the
+    counts is issued after the send buffer is filled ("send buffers complete"), a one-element
+    all-reduce after the expert GEMMs ("expert outputs complete").  They also make buffer reuse
+    safe: a rank refills its send buffer only after the second collective of the previous layer
+    (every peer has pulled), and overwrites its expert outputs only after the first collective of
+    the next layer (every peer has combined)."""
+
+    def __init__(self, weights: MoeWeights, tokens: int, topk: int, ga: float, ga_dn: float, ga_sh_dn: float,
+                 group=None, how: str = "auto", emulate=None):
+        """emulate=(rank, world): no process group; the caller runs every rank's stages in turn on one
+        GPU and wires the buffer tables together with `connect` (single-GPU test of the protocol)."""
+        from .peer import PeerBuffer, LocalBuffer
+        self.lib = load()
+        self.group = group
+        self.emulated = emulate is not None
+        self.rank, self.world = emulate if self.emulated else (dist.get_rank(group), dist.get_world_size(group))
+        self.w, self.tokens, self.topk = weights, tokens, topk
+        self.ga, self.ga_dn = ga, ga_dn
+        lib, dev, w, c = self.lib, weights.dev, weights, self.lib.cdll
+        self.e_total, self.e_local = w.router_experts, w.experts
+        assert self.e_local * self.world == self.e_total
+        h, i, n = w.hidden, w.inter, tokens * topk
+        self.local = MoeLayer(weights, tokens, topk, ga, ga_dn, ga_sh_dn, allocate_experts=False)
+        cap = n * self.world                      # worst case: every assignment of every rank lands here
+        self.cap = cap
+        u8 = dict(dtype=torch.uint8, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.xq = torch.empty((tokens, h // 2), **u8)
+        self.xs = torch.empty((tokens, h // 16), **u8)
+        self.msg_bytes = (h // 2 + h // 16 + 15) // 16 * 16   # payload | block scales | pad
+        self.rows_max = c.gemb_moe_padded_rows_max(cap, self.e_local, 1)
+        if self.emulated:
+            self.send = LocalBuffer(n * self.msg_bytes, dev)
+            self.y_peer = LocalBuffer(self.rows_max * h * 2, dev)
+        else:
+            self.send = PeerBuffer(n * self.msg_bytes, dev, group, how)
+            self.y_peer = PeerBuffer(self.rows_max * h * 2, dev, group, how)
+        self.send_msg = self.send.local.view(n, self.msg_bytes)
+        self.y = self.y_peer.local.view(torch.int16).view(self.rows_max, h)
+        self.counts_all = torch.zeros((self.world, self.e_total), **i32)
+        segs = self.world * self.e_local
+        self.l_plan = torch.zeros((c.gemb_moe_ep_plan_ints(cap, self.e_local),), **i32)
+        self.recv_prefix = torch.zeros((segs + 1,), **i32)
+        self.recv_src = torch.zeros((segs,), **i32)
+        self.recv_dst = torch.zeros((segs,), **i32)
+        self.row_base = torch.zeros((self.e_total,), **i32)
+        self.a_packed = torch.zeros((self.rows_max, h // 2), **u8)
+        self.a_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, h),), **u8)
+        self.gate_up = torch.empty((self.rows_max, 2 * i), dtype=torch.int16, device=dev)
+        self.p_packed = torch.zeros((self.rows_max, i // 2), **u8)
+        self.p_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, i),), **u8)
+        self.flag = torch.zeros((1,), device=dev)
+        self.side = torch.cuda.Stream(device=dev)
+
+    @staticmethod
+    def connect(layers):
+        """Emulation only: give every layer the addresses of all layers' send and output buffers."""
+        for l in layers:
+            l.send.set_table([m.send.local.data_ptr() for m in layers])
+            l.y_peer.set_table([m.y_peer.local.data_ptr() for m in layers])
+
+    def stage_send(self, x_bf16):
+        """Steps 1-2: route the local tokens, quantise once, leave the message rows for the peers."""
+        lib, w, t, k, loc = self.lib, self.w, self.tokens, self.topk, self.local
+        h, n = w.hidden, self.tokens * self.topk
+        main = torch.cuda.current_stream()
+        if w.shared is not None:
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                loc.shared_branch(x_bf16, self.side)
+        lib.gemb_moe_router_logits(x_bf16, w.router_w, w.router_bias, loc.logits, t, h, self.e_total, None)
+        lib.gemb_moe_route(loc.logits, None, loc.ids, loc.weights, None, t, self.e_total, k, None)
+        lib.gemb_moe_permute(loc.ids, loc.counts, loc.offsets, loc.perm, loc.slot_rows, loc.plan, loc.workspace,
+                             loc.workspace.numel(), t, self.e_total, k, None)
+        lib.gemb_nvfp4_quantize(x_bf16, 1, self.xq, self.xs, t, h, self.ga, 0, 0, None)
+        mb = self.msg_bytes
+        lib.gemb_moe_gather_rows(self.xq, self.send_msg, loc.perm, k, n, h // 2, h // 2, mb, None)
+        lib.gemb_moe_gather_rows(self.xs, self.send_msg[:, h // 2:], loc.perm, k, n, h // 16, h // 16, mb, None)
+
+    def stage_experts(self):
+        """Steps 3-4 after the counts of all ranks are in `counts_all`: positions, pull, expert GEMMs."""
+        lib, w = self.lib, self.w
+        h, el, R = w.hidden, self.e_local, self.world
+        lib.gemb_moe_ep_plan(self.counts_all, R, self.e_total, self.rank, self.l_plan, self.recv_prefix, self.recv_src,
+                             self.recv_dst, self.row_base, None)
+        lib.gemb_moe_ep_pull_dispatch(self.send.table, R, el, self.recv_prefix, self.recv_src, self.recv_dst,
+                                      self.a_packed, self.a_scales, h, self.msg_bytes, None)
+        lib.gemb_moe_grouped_gemm_bf16(self.a_packed, self.a_scales, w.gu_packed, w.gu_scales, self.gate_up,
+                                       self.l_plan, self.rows_max, el, 2 * w.inter, h, self.ga, w.gu_div, None)
+        lib.gemb_moe_expert_gelu_quantize(self.gate_up, self.l_plan, self.p_packed, self.p_scales, self.rows_max,
+                                          w.inter, self.ga_dn, None)
+        lib.gemb_moe_grouped_gemm_bf16(self.p_packed, self.p_scales, w.dn_packed, w.dn_scales, self.y, self.l_plan,
+                                       self.rows_max, el, h, w.inter, self.ga_dn, w.dn_div, None)
+
+    def stage_combine(self):
+        """Step 5 after every rank's expert outputs are complete."""
+        lib, w, loc = self.lib, self.w, self.local
+        if w.shared is not None:
+            torch.cuda.current_stream().wait_stream(self.side)
+        shared = loc.s_out if w.shared is not None else None
+        lib.gemb_moe_ep_pull_combine(self.y_peer.table, self.world, self.e_local, loc.ids, loc.slot_rows, self.row_base,
+                                     loc.weights, shared, loc.out, self.tokens, w.hidden, self.topk, None)
+        return loc.out
+
+    def forward(self, x_bf16):
+        self.stage_send(x_bf16)
+        # counts of every rank -- and: every send buffer is complete
+        dist.all_gather_into_tensor(self.counts_all.view(-1), self.local.counts, group=self.group)
+        self.stage_experts()
+        dist.all_reduce(self.flag, group=self.group)   # every expert output is complete
+        return self.stage_combine()

@@ -396,6 +396,42 @@ int32_t gemb_moe_expert_gelu_quantize(const uint16_t* gate_up_bf16, const int32_
                                       uint64_t rows_max, uint64_t intermediate,
                                       float global_divisor, gemb_stream_t stream);
 
+/* ---- expert parallelism over peer memory (no counterpart in the reference, which is single-GPU) ----
+ * R ranks, E experts, rank r owns experts [r*E/R, (r+1)*E/R).  Every rank leaves its quantised
+ * assignments, one message row each (payload | compact block scales, padded to 16 bytes) in
+ * (expert, token, slot) order, in a buffer its peers have mapped; counts_all [R][E] holds every
+ * rank's per-expert counts (all-gathered by the caller, which also orders the kernels below after
+ * the peers' writes).  All row positions follow from counts_all; nothing is read back to the host.
+ *
+ * gemb_moe_ep_plan (one small launch) writes, for rank `rank`:
+ *   plan              the grouped-GEMM plan of its local experts over the rows of ALL ranks
+ *                     (layout of gemb_moe_permute's plan; gemb_moe_ep_plan_ints integers),
+ *   recv_prefix       [R*E/R + 1] exclusive prefix of the segments (source, local expert) it receives,
+ *   recv_src_rows     [R*E/R] first row of each segment in the source's send buffer,
+ *   recv_dst_rows     [R*E/R] first row of each segment in its padded row space,
+ *   combine_row_base  [E] for an assignment of ITS OWN tokens to expert e whose local slot row
+ *                     (gemb_moe_permute's slot_rows) is p: the row of the result in the owner's
+ *                     output buffer is combine_row_base[e] + p.
+ * gemb_moe_ep_pull_dispatch reads the segments out of the peers' send buffers (peer_send_buffers:
+ * R device addresses, host array) into payload [rows, hidden/2] + INTERLEAVED scales.
+ * gemb_moe_ep_pull_combine is gemb_moe_combine with every expert row read from its owner's output
+ * buffer (peer_expert_outputs: R device addresses of bf16 [rows, hidden]). */
+uint64_t gemb_moe_ep_plan_ints(uint64_t capacity_rows, uint64_t local_experts);
+int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t experts, uint64_t rank,
+                         int32_t* plan, int32_t* recv_prefix, int32_t* recv_src_rows,
+                         int32_t* recv_dst_rows, int32_t* combine_row_base, gemb_stream_t stream);
+int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers, uint64_t ranks,
+                                  uint64_t local_experts, const int32_t* recv_prefix,
+                                  const int32_t* recv_src_rows, const int32_t* recv_dst_rows,
+                                  uint8_t* packed_e2m1, uint8_t* interleaved_scales, uint64_t hidden,
+                                  uint64_t message_row_bytes, gemb_stream_t stream);
+int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs, uint64_t ranks,
+                                 uint64_t local_experts, const int32_t* top_ids,
+                                 const int32_t* slot_rows, const int32_t* combine_row_base,
+                                 const float* top_weights, const uint16_t* shared_bf16,
+                                 uint16_t* out_bf16, uint64_t tokens, uint64_t hidden, uint64_t topk,
+                                 gemb_stream_t stream);
+
 /* out[t] = bf16( sum over slots in slot order of fma(weight[t][slot], y[slot_rows[t*topk+slot]])
  *                + shared[t] ), fp32 accumulation, no atomics; shared may be null.
  * docs/plans/gemma4-26b/specs/MOE_SEMANTICS_SPEC.md:74-83. */

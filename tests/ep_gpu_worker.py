@@ -10,7 +10,7 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 from gem16_b200 import load  # noqa: E402
-from gem16_b200.ep import EpMoeLayer  # noqa: E402
+from gem16_b200.ep import EpMoeLayer, EpPullMoeLayer  # noqa: E402
 from gem16_b200.moe import MoeLayer, synthetic_weights  # noqa: E402
 
 
@@ -44,8 +44,17 @@ def main():
         assert torch.equal(ep.local.weights, ref.weights[sl]), "routing weights differ"
         assert torch.equal(ep.counts_all.sum(0).to(torch.int32), ref.counts), "global counts differ"
         assert torch.equal(out, ref_out[sl]), "expert-parallel output differs from the single-GPU layer"
+    # the same layer with the exchange done by the library's own kernels over peer memory
+    pull = EpPullMoeLayer(mine, tokens, topk, ga, ga_dn, ga_sh)
+    for _ in range(3):     # three times: send and output buffers are reused without a host sync in between
+        out = pull.forward(x_all[sl].contiguous().view(torch.int16))
+    torch.cuda.synchronize()
+    lib.gemb_check_device_status()
+    assert torch.equal(pull.counts_all.sum(0).to(torch.int32), ref.counts), "global counts differ (peer path)"
+    assert int(pull.recv_prefix[-1].item()) == ep.last["n_recv"], "received row count differs (peer path)"
+    assert torch.equal(out, ref_out[sl]), "peer-memory expert-parallel output differs from the single-GPU layer"
     dist.barrier()
-    print(f"rank {rank} ok n_recv={ep.last['n_recv']}", flush=True)
+    print(f"rank {rank} ok n_recv={ep.last['n_recv']} peer={pull.send.how}", flush=True)
     dist.destroy_process_group()
 
 

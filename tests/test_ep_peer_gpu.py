@@ -1,0 +1,93 @@
+"""The peer-memory expert-parallel protocol (csrc/ep.cu) on ONE GPU: the ranks are emulated by running
+every rank's stages in turn, their "peer" buffers being ordinary buffers of the same device.  The
+kernels, the position arithmetic and the launch sequence are the ones the multi-GPU layer uses; only
+the two NCCL collectives are replaced by a host-side copy of the counts.  Result: bit-identical to the
+single-GPU layer."""
+import numpy as np
+import pytest
+import torch
+
+from gem16_b200.ep import EpPullMoeLayer
+from gem16_b200.moe import MoeLayer, synthetic_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def ep_plan_reference(counts_all, me):
+    """Plain restatement of the position arithmetic (see the header comment of csrc/ep.cu)."""
+    ranks, experts = counts_all.shape
+    el = experts // ranks
+    tot = counts_all.sum(0)
+    pad = np.zeros(experts, np.int64)
+    for d in range(ranks):
+        po = 0
+        for e in range(d * el, (d + 1) * el):
+            pad[e] = po
+            po += (tot[e] + 127) // 128 * 128
+    my_pad = np.concatenate([[0], np.cumsum((counts_all[me] + 127) // 128 * 128)])[:-1]
+    before_me = counts_all[:me].sum(0)
+    row_base = pad + before_me - my_pad
+    prefix, src, dst = [0], [], []
+    for s in range(ranks):
+        sorted_off = np.concatenate([[0], np.cumsum(counts_all[s])])
+        for e in range(me * el, (me + 1) * el):
+            src.append(sorted_off[e])
+            dst.append(pad[e] + counts_all[:s, e].sum())
+            prefix.append(prefix[-1] + counts_all[s, e])
+    mine = slice(me * el, (me + 1) * el)
+    padded_rows = int(((tot[mine] + 127) // 128 * 128).sum())
+    return dict(row_base=row_base, prefix=np.array(prefix), src=np.array(src), dst=np.array(dst),
+                pad_local=pad[mine], padded_rows=padded_rows)
+
+
+@pytest.mark.parametrize("ranks,tokens", [(2, 96), (4, 33), (8, 5)])
+def test_emulated_ranks_match_single_gpu(lib, dev, ranks, tokens):
+    hidden, experts, inter, shared_inter, topk = 2816, 128, 704, 2112, 8
+    el = experts // ranks
+    full = synthetic_weights(dev, 7, hidden, experts, inter, shared_inter, placement_ranks=ranks)
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    x_all = torch.randn((tokens * ranks, hidden), device=dev, generator=g).to(torch.bfloat16)
+    ga = float(2688.0 / x_all.float().abs().max().item())
+    ga_dn = ga_sh = 2688.0 / 8.0
+    ref = MoeLayer(full, tokens * ranks, topk, ga, ga_dn, ga_sh)
+    ref_out = ref.forward(x_all.view(torch.int16)).clone()
+    layers = []
+    for r in range(ranks):
+        mine = synthetic_weights(dev, 7, hidden, experts, inter, shared_inter, expert_range=(r * el, (r + 1) * el),
+                                 placement_ranks=ranks)
+        layers.append(EpPullMoeLayer(mine, tokens, topk, ga, ga_dn, ga_sh, emulate=(r, ranks)))
+    EpPullMoeLayer.connect(layers)
+    for rep in range(2):    # twice: every buffer is reused
+        for r, l in enumerate(layers):
+            l.stage_send(x_all[r * tokens:(r + 1) * tokens].contiguous().view(torch.int16))
+        counts_all = torch.stack([l.local.counts for l in layers]).contiguous()
+        for l in layers:
+            l.counts_all.copy_(counts_all)
+            l.stage_experts()
+        outs = [l.stage_combine().clone() for l in layers]
+        torch.cuda.synchronize()
+        lib.gemb_check_device_status()
+        c = counts_all.cpu().numpy().astype(np.int64)
+        assert np.array_equal(c.sum(0), ref.counts.cpu().numpy())
+        for r, l in enumerate(layers):
+            want = ep_plan_reference(c, r)
+            assert np.array_equal(l.row_base.cpu().numpy(), want["row_base"])
+            assert np.array_equal(l.recv_prefix.cpu().numpy(), want["prefix"])
+            assert np.array_equal(l.recv_src.cpu().numpy(), want["src"])
+            assert np.array_equal(l.recv_dst.cpu().numpy(), want["dst"])
+            plan = l.l_plan.cpu().numpy()
+            assert plan[1] == want["padded_rows"] and plan[0] == want["padded_rows"] // 128
+            assert np.array_equal(plan[2:2 + el], want["pad_local"])
+            assert torch.equal(outs[r], ref_out[r * tokens:(r + 1) * tokens]), f"rank {r} output differs (pass {rep})"
+
+
+def test_ep_plan_rejects_bad_geometry(lib, dev):
+    from gem16_b200.lib import GembError
+    z = torch.zeros((64,), dtype=torch.int32, device=dev)
+    with pytest.raises(GembError):
+        lib.gemb_moe_ep_plan(z, 3, 128, 0, z, z, z, z, z, None)      # experts not a multiple of ranks
+    with pytest.raises(GembError):
+        lib.gemb_moe_ep_plan(z, 2, 128, 2, z, z, z, z, z, None)      # rank out of range
+    with pytest.raises(GembError):
+        lib.gemb_moe_ep_plan(None, 2, 128, 0, z, z, z, z, z, None)
