@@ -406,9 +406,12 @@ expert_gelu_quantize_kernel(const uint16_t* __restrict__ gate_up, const int32_t*
                             uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, uint32_t rows_max,
                             uint32_t inter, float g, uint32_t c_pad) {
   const uint32_t blocks_per_row = inter / 16;
-  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const uint32_t rows = plan ? min(rows_max, static_cast<uint32_t>(__ldg(plan + 1))) : rows_max;
-  if (idx >= static_cast<uint64_t>(rows) * blocks_per_row) return;
+  const uint64_t work = static_cast<uint64_t>(rows) * blocks_per_row;
+  // Grid-stride: the grid is sized for a bounded number of CTAs, not for rows_max, which with a
+  // device-side plan can be far larger than the rows in use.
+  for (uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < work;
+       idx += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
   const uint32_t r = static_cast<uint32_t>(idx / blocks_per_row), c = static_cast<uint32_t>(idx % blocks_per_row);
   const uint16_t* gp = gate_up + static_cast<uint64_t>(r) * 2 * inter + c * 16;
   const uint4 ga = __ldg(reinterpret_cast<const uint4*>(gp)), gb = __ldg(reinterpret_cast<const uint4*>(gp) + 1);
@@ -429,6 +432,7 @@ expert_gelu_quantize_kernel(const uint16_t* __restrict__ gate_up, const int32_t*
   quantize_block16<false>(v, g, lo, hi, sb);
   *reinterpret_cast<uint2*>(packed + static_cast<uint64_t>(r) * (inter / 2) + c * 8) = make_uint2(lo, hi);
   scales[interleaved_scale_offset(r, c, c_pad)] = sb;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -747,7 +751,8 @@ int32_t gemb_moe_expert_gelu_quantize(const uint16_t* gate_up_bf16, const int32_
   GEMB_TRY(require_sm100(op));
   const uint64_t work = rows_max * (intermediate / 16);
   const uint32_t c_pad = static_cast<uint32_t>((intermediate / 16 + 3) / 4 * 4);
-  expert_gelu_quantize_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+  const uint64_t ctas = std::min<uint64_t>((work + 255) / 256, static_cast<uint64_t>(sm_count()) * 32);
+  expert_gelu_quantize_kernel<<<static_cast<unsigned>(ctas), 256, 0, stream>>>(
       gate_up_bf16, plan, packed_e2m1, interleaved_scales, static_cast<uint32_t>(rows_max),
       static_cast<uint32_t>(intermediate), global_divisor, c_pad);
   return check_launch(op);
