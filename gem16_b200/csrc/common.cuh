@@ -31,6 +31,7 @@ int32_t launch_fp8_quantize_decode(const char* op, const uint16_t* x, uint8_t* o
                                    uint64_t k, cudaStream_t stream);
 // Reads and clears the decode GEMV's bounded-wait flag (0 = clean, -1 = could not read).
 int gemv_take_device_error();
+int ep_take_device_error();
 
 inline bool positive_finite(float v) { return std::isfinite(v) && v > 0.0f; }
 

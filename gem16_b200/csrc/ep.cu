@@ -24,6 +24,24 @@
 #include "common.cuh"
 
 namespace gemb {
+
+// Set when a position computed from the counts falls outside a buffer (the counts were not what
+// the protocol promises, e.g. read before the peers had written them): the access is skipped.
+__device__ int g_ep_error = 0;
+
+int ep_take_device_error() {
+  int code = 0;
+  if (cudaMemcpyFromSymbol(&code, g_ep_error, sizeof code) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  if (code != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_ep_error, &zero, sizeof zero);
+  }
+  return code;
+}
+
 namespace {
 
 constexpr uint32_t kMaxRanks = 16;
@@ -114,12 +132,16 @@ __global__ void __launch_bounds__(256)
 ep_pull_dispatch_kernel(PeerPtrs peers, const int32_t* __restrict__ recv_prefix, const int32_t* __restrict__ recv_src,
                         const int32_t* __restrict__ recv_dst, uint32_t segments, uint32_t el, uint32_t hidden,
                         uint32_t msg_bytes, uint32_t c_pad, uint8_t* __restrict__ packed,
-                        uint8_t* __restrict__ scales) {
+                        uint8_t* __restrict__ scales, uint32_t send_rows, uint32_t rows_max) {
   extern __shared__ int sm[];
   int* prefix = sm;  // [segments + 1]
   for (uint32_t i = threadIdx.x; i <= segments; i += blockDim.x) prefix[i] = recv_prefix[i];
   __syncthreads();
-  const uint32_t total = static_cast<uint32_t>(prefix[segments]);
+  uint32_t total = static_cast<uint32_t>(prefix[segments]);
+  if (total > rows_max) {  // cannot be: every received row has a place in the padded row space
+    if (threadIdx.x == 0) atomicCAS(&g_ep_error, 0, 1);
+    total = 0;
+  }
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t warps = gridDim.x * (blockDim.x >> 5);
   const uint32_t payload_vecs = hidden / 32;   // 16-byte vectors of payload per row
@@ -131,8 +153,13 @@ ep_pull_dispatch_kernel(PeerPtrs peers, const int32_t* __restrict__ recv_prefix,
       if (static_cast<uint32_t>(prefix[mid]) <= r) lo = mid; else hi = mid;
     }
     const uint32_t j = r - static_cast<uint32_t>(prefix[lo]);
-    const uint8_t* src = peers.p[lo / el] + static_cast<uint64_t>(__ldg(recv_src + lo) + j) * msg_bytes;
-    const uint64_t d = static_cast<uint64_t>(__ldg(recv_dst + lo)) + j;
+    const uint64_t srow = static_cast<uint64_t>(static_cast<uint32_t>(__ldg(recv_src + lo))) + j;
+    const uint64_t d = static_cast<uint64_t>(static_cast<uint32_t>(__ldg(recv_dst + lo))) + j;
+    if (srow >= send_rows || d >= rows_max) {
+      if (lane == 0) atomicCAS(&g_ep_error, 0, 2);
+      continue;
+    }
+    const uint8_t* src = peers.p[lo / el] + srow * msg_bytes;
     for (uint32_t v = lane; v < payload_vecs; v += 32)
       *reinterpret_cast<uint4*>(packed + d * (hidden / 2) + v * 16) = *reinterpret_cast<const uint4*>(src + v * 16);
     for (uint32_t w = lane; w < scale_words; w += 32)
@@ -146,7 +173,7 @@ __global__ void __launch_bounds__(256)
 ep_pull_combine_kernel(PeerPtrs peers, const int32_t* __restrict__ ids, const int32_t* __restrict__ slot_rows,
                        const int32_t* __restrict__ out_base, const float* __restrict__ weights,
                        const uint16_t* __restrict__ shared_out, uint16_t* __restrict__ out, uint32_t tokens,
-                       uint32_t hidden, uint32_t topk, uint32_t el) {
+                       uint32_t hidden, uint32_t topk, uint32_t el, uint32_t experts, uint32_t rows_max) {
   const uint32_t chunks = hidden / 8;
   const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<uint64_t>(tokens) * chunks) return;
@@ -158,7 +185,15 @@ ep_pull_combine_kernel(PeerPtrs peers, const int32_t* __restrict__ ids, const in
     const uint64_t a = static_cast<uint64_t>(t) * topk + s;
     const float wv = __ldg(weights + a);
     const uint32_t e = static_cast<uint32_t>(__ldg(ids + a));
+    if (e >= experts) {
+      atomicCAS(&g_ep_error, 0, 3);
+      continue;
+    }
     const int64_t r = static_cast<int64_t>(__ldg(out_base + e)) + __ldg(slot_rows + a);
+    if (r < 0 || r >= static_cast<int64_t>(rows_max)) {
+      atomicCAS(&g_ep_error, 0, 4);
+      continue;
+    }
     const uint4 v = *(reinterpret_cast<const uint4*>(peers.p[e / el] + r * hidden * 2) + c);
     const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -226,7 +261,8 @@ int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t exp
 int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers, uint64_t ranks, uint64_t local_experts,
                                   const int32_t* recv_prefix, const int32_t* recv_src_rows,
                                   const int32_t* recv_dst_rows, uint8_t* packed_e2m1, uint8_t* interleaved_scales,
-                                  uint64_t hidden, uint64_t message_row_bytes, gemb_stream_t stream) {
+                                  uint64_t hidden, uint64_t message_row_bytes, uint64_t send_rows_per_rank,
+                                  uint64_t padded_rows_max, gemb_stream_t stream) {
   const char* op = "gemb_moe_ep_pull_dispatch";
   PeerPtrs peers;
   GEMB_TRY(load_peers(op, peer_send_buffers, ranks, &peers));
@@ -238,19 +274,24 @@ int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers, uint64_t ra
                "%s: a message row holds the payload and the block scales, padded to 16 bytes", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(packed_e2m1) % 16 == 0 && reinterpret_cast<uintptr_t>(interleaved_scales) % 4 == 0,
                "%s: outputs must be 16-byte (payload) and 4-byte (scales) aligned", op);
+  GEMB_REQUIRE(send_rows_per_rank > 0 && send_rows_per_rank < (1ull << 31) && padded_rows_max > 0 &&
+                   padded_rows_max < (1ull << 31) && padded_rows_max % 128 == 0,
+               "%s: buffer capacities must be nonzero (padded rows a multiple of 128)", op);
   GEMB_TRY(require_sm100(op));
   const uint32_t segments = static_cast<uint32_t>(ranks * local_experts);
   const uint32_t c_pad = static_cast<uint32_t>((hidden / 16 + 3) / 4 * 4);
   ep_pull_dispatch_kernel<<<static_cast<unsigned>(sm_count()) * 4, 256, (segments + 1) * sizeof(int), stream>>>(
       peers, recv_prefix, recv_src_rows, recv_dst_rows, segments, static_cast<uint32_t>(local_experts),
-      static_cast<uint32_t>(hidden), static_cast<uint32_t>(message_row_bytes), c_pad, packed_e2m1, interleaved_scales);
+      static_cast<uint32_t>(hidden), static_cast<uint32_t>(message_row_bytes), c_pad, packed_e2m1, interleaved_scales,
+      static_cast<uint32_t>(send_rows_per_rank), static_cast<uint32_t>(padded_rows_max));
   return check_launch(op);
 }
 
 int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs, uint64_t ranks, uint64_t local_experts,
                                  const int32_t* top_ids, const int32_t* slot_rows, const int32_t* combine_row_base,
                                  const float* top_weights, const uint16_t* shared_bf16, uint16_t* out_bf16,
-                                 uint64_t tokens, uint64_t hidden, uint64_t topk, gemb_stream_t stream) {
+                                 uint64_t tokens, uint64_t hidden, uint64_t topk, uint64_t padded_rows_max,
+                                 gemb_stream_t stream) {
   const char* op = "gemb_moe_ep_pull_combine";
   PeerPtrs peers;
   GEMB_TRY(load_peers(op, peer_expert_outputs, ranks, &peers));
@@ -258,13 +299,15 @@ int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs, uint64_t r
   GEMB_REQUIRE(tokens > 0 && tokens < (1ull << 31) && topk >= 1 && topk <= 32, "%s: bad geometry", op);
   GEMB_REQUIRE(local_experts >= 1 && ranks * local_experts <= kMaxExperts, "%s: bad expert geometry", op);
   GEMB_REQUIRE(hidden > 0 && hidden % 8 == 0 && hidden < (1ull << 31), "%s: hidden must be a nonzero multiple of 8", op);
+  GEMB_REQUIRE(padded_rows_max > 0 && padded_rows_max < (1ull << 31), "%s: output capacity must be nonzero", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(out_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(shared_bf16) % 16 == 0,
                "%s: buffers must be 16-byte aligned", op);
   GEMB_TRY(require_sm100(op));
   const uint64_t work = tokens * (hidden / 8);
   ep_pull_combine_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
       peers, top_ids, slot_rows, combine_row_base, top_weights, shared_bf16, out_bf16, static_cast<uint32_t>(tokens),
-      static_cast<uint32_t>(hidden), static_cast<uint32_t>(topk), static_cast<uint32_t>(local_experts));
+      static_cast<uint32_t>(hidden), static_cast<uint32_t>(topk), static_cast<uint32_t>(local_experts),
+      static_cast<uint32_t>(ranks * local_experts), static_cast<uint32_t>(padded_rows_max));
   return check_launch(op);
 }
 

@@ -1034,6 +1034,9 @@ int32_t gemb_check_device_status(void) {
   const int gemv_code = gemv_take_device_error();
   if (gemv_code != 0)
     return fail(GEMB_INTERNAL, "%s: a GEMV kernel gave up waiting on a pipeline barrier (role %d)", op, gemv_code);
+  const int ep_code = ep_take_device_error();
+  if (ep_code != 0)
+    return fail(GEMB_INTERNAL, "%s: an expert-parallel pull kernel skipped a row outside its buffers (check %d)", op, ep_code);
   return GEMB_OK;
 }
 

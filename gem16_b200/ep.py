@@ -206,43 +206,46 @@ class EpPullMoeLayer:
         """Steps 1-2: route the local tokens, quantise once, leave the message rows for the peers."""
         lib, w, t, k, loc = self.lib, self.w, self.tokens, self.topk, self.local
         h, n = w.hidden, self.tokens * self.topk
-        main = torch.cuda.current_stream()
+        main = torch.cuda.current_stream()   # every launch names the stream: the collectives are ordered on it
         if w.shared is not None:
             self.side.wait_stream(main)
             with torch.cuda.stream(self.side):
                 loc.shared_branch(x_bf16, self.side)
-        lib.gemb_moe_router_logits(x_bf16, w.router_w, w.router_bias, loc.logits, t, h, self.e_total, None)
-        lib.gemb_moe_route(loc.logits, None, loc.ids, loc.weights, None, t, self.e_total, k, None)
+        lib.gemb_moe_router_logits(x_bf16, w.router_w, w.router_bias, loc.logits, t, h, self.e_total, main)
+        lib.gemb_moe_route(loc.logits, None, loc.ids, loc.weights, None, t, self.e_total, k, main)
         lib.gemb_moe_permute(loc.ids, loc.counts, loc.offsets, loc.perm, loc.slot_rows, loc.plan, loc.workspace,
-                             loc.workspace.numel(), t, self.e_total, k, None)
-        lib.gemb_nvfp4_quantize(x_bf16, 1, self.xq, self.xs, t, h, self.ga, 0, 0, None)
+                             loc.workspace.numel(), t, self.e_total, k, main)
+        lib.gemb_nvfp4_quantize(x_bf16, 1, self.xq, self.xs, t, h, self.ga, 0, 0, main)
         mb = self.msg_bytes
-        lib.gemb_moe_gather_rows(self.xq, self.send_msg, loc.perm, k, n, h // 2, h // 2, mb, None)
-        lib.gemb_moe_gather_rows(self.xs, self.send_msg[:, h // 2:], loc.perm, k, n, h // 16, h // 16, mb, None)
+        lib.gemb_moe_gather_rows(self.xq, self.send_msg, loc.perm, k, n, h // 2, h // 2, mb, main)
+        lib.gemb_moe_gather_rows(self.xs, self.send_msg[:, h // 2:], loc.perm, k, n, h // 16, h // 16, mb, main)
 
     def stage_experts(self):
         """Steps 3-4 after the counts of all ranks are in `counts_all`: positions, pull, expert GEMMs."""
         lib, w = self.lib, self.w
         h, el, R = w.hidden, self.e_local, self.world
+        main = torch.cuda.current_stream()
         lib.gemb_moe_ep_plan(self.counts_all, R, self.e_total, self.rank, self.l_plan, self.recv_prefix, self.recv_src,
-                             self.recv_dst, self.row_base, None)
+                             self.recv_dst, self.row_base, main)
         lib.gemb_moe_ep_pull_dispatch(self.send.table, R, el, self.recv_prefix, self.recv_src, self.recv_dst,
-                                      self.a_packed, self.a_scales, h, self.msg_bytes, None)
+                                      self.a_packed, self.a_scales, h, self.msg_bytes, self.tokens * self.topk,
+                                      self.rows_max, main)
         lib.gemb_moe_grouped_gemm_bf16(self.a_packed, self.a_scales, w.gu_packed, w.gu_scales, self.gate_up,
-                                       self.l_plan, self.rows_max, el, 2 * w.inter, h, self.ga, w.gu_div, None)
+                                       self.l_plan, self.rows_max, el, 2 * w.inter, h, self.ga, w.gu_div, main)
         lib.gemb_moe_expert_gelu_quantize(self.gate_up, self.l_plan, self.p_packed, self.p_scales, self.rows_max,
-                                          w.inter, self.ga_dn, None)
+                                          w.inter, self.ga_dn, main)
         lib.gemb_moe_grouped_gemm_bf16(self.p_packed, self.p_scales, w.dn_packed, w.dn_scales, self.y, self.l_plan,
-                                       self.rows_max, el, h, w.inter, self.ga_dn, w.dn_div, None)
+                                       self.rows_max, el, h, w.inter, self.ga_dn, w.dn_div, main)
 
     def stage_combine(self):
         """Step 5 after every rank's expert outputs are complete."""
         lib, w, loc = self.lib, self.w, self.local
+        main = torch.cuda.current_stream()
         if w.shared is not None:
-            torch.cuda.current_stream().wait_stream(self.side)
+            main.wait_stream(self.side)
         shared = loc.s_out if w.shared is not None else None
         lib.gemb_moe_ep_pull_combine(self.y_peer.table, self.world, self.e_local, loc.ids, loc.slot_rows, self.row_base,
-                                     loc.weights, shared, loc.out, self.tokens, w.hidden, self.topk, None)
+                                     loc.weights, shared, loc.out, self.tokens, w.hidden, self.topk, self.rows_max, main)
         return loc.out
 
     def forward(self, x_bf16):

@@ -415,7 +415,10 @@ int32_t gemb_moe_expert_gelu_quantize(const uint16_t* gate_up_bf16, const int32_
  * gemb_moe_ep_pull_dispatch reads the segments out of the peers' send buffers (peer_send_buffers:
  * R device addresses, host array) into payload [rows, hidden/2] + INTERLEAVED scales.
  * gemb_moe_ep_pull_combine is gemb_moe_combine with every expert row read from its owner's output
- * buffer (peer_expert_outputs: R device addresses of bf16 [rows, hidden]). */
+ * buffer (peer_expert_outputs: R device addresses of bf16 [rows, hidden]).
+ * send_rows_per_rank / padded_rows_max are the capacities of the send and of the padded buffers: a
+ * position outside them (counts that are not what the protocol promises) is skipped and recorded,
+ * and gemb_check_device_status() then reports it, instead of the access faulting. */
 uint64_t gemb_moe_ep_plan_ints(uint64_t capacity_rows, uint64_t local_experts);
 int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t experts, uint64_t rank,
                          int32_t* plan, int32_t* recv_prefix, int32_t* recv_src_rows,
@@ -424,13 +427,14 @@ int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers, uint64_t ra
                                   uint64_t local_experts, const int32_t* recv_prefix,
                                   const int32_t* recv_src_rows, const int32_t* recv_dst_rows,
                                   uint8_t* packed_e2m1, uint8_t* interleaved_scales, uint64_t hidden,
-                                  uint64_t message_row_bytes, gemb_stream_t stream);
+                                  uint64_t message_row_bytes, uint64_t send_rows_per_rank,
+                                  uint64_t padded_rows_max, gemb_stream_t stream);
 int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs, uint64_t ranks,
                                  uint64_t local_experts, const int32_t* top_ids,
                                  const int32_t* slot_rows, const int32_t* combine_row_base,
                                  const float* top_weights, const uint16_t* shared_bf16,
                                  uint16_t* out_bf16, uint64_t tokens, uint64_t hidden, uint64_t topk,
-                                 gemb_stream_t stream);
+                                 uint64_t padded_rows_max, gemb_stream_t stream);
 
 /* out[t] = bf16( sum over slots in slot order of fma(weight[t][slot], y[slot_rows[t*topk+slot]])
  *                + shared[t] ), fp32 accumulation, no atomics; shared may be null.

@@ -91,3 +91,30 @@ def test_ep_plan_rejects_bad_geometry(lib, dev):
         lib.gemb_moe_ep_plan(z, 2, 128, 2, z, z, z, z, z, None)      # rank out of range
     with pytest.raises(GembError):
         lib.gemb_moe_ep_plan(None, 2, 128, 0, z, z, z, z, z, None)
+
+
+def test_pull_dispatch_skips_rows_outside_the_buffers(lib, dev):
+    """Positions that do not fit the buffers (counts that are not what the protocol promises) are
+    skipped and reported through gemb_check_device_status(); nothing is read or written there."""
+    import ctypes as C
+    from gem16_b200.lib import GembError
+    hidden, msg, send_rows, rows_max = 128, 80, 4, 128
+    send = torch.full((send_rows, msg), 7, dtype=torch.uint8, device=dev)
+    table = (C.c_uint64 * 1)(send.data_ptr())
+    packed = torch.zeros((rows_max, hidden // 2), dtype=torch.uint8, device=dev)
+    scales = torch.zeros((lib.cdll.gemb_interleaved_scale_bytes(rows_max, hidden),), dtype=torch.uint8, device=dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    prefix = torch.tensor([0, 4], **i32)
+    ok_src, ok_dst = torch.tensor([0], **i32), torch.tensor([0], **i32)
+    lib.gemb_moe_ep_pull_dispatch(table, 1, 1, prefix, ok_src, ok_dst, packed, scales, hidden, msg, send_rows, rows_max, None)
+    torch.cuda.synchronize()
+    lib.gemb_check_device_status()
+    assert int(packed[:4].min().item()) == 7 and int(packed[4:].max().item()) == 0
+    packed.zero_()
+    bad_src = torch.tensor([2], **i32)          # rows 2..5 of a 4-row send buffer
+    lib.gemb_moe_ep_pull_dispatch(table, 1, 1, prefix, bad_src, ok_dst, packed, scales, hidden, msg, send_rows, rows_max, None)
+    torch.cuda.synchronize()
+    with pytest.raises(GembError):
+        lib.gemb_check_device_status()
+    assert int(packed[:2].min().item()) == 7 and int(packed[2:].max().item()) == 0   # in-range rows copied, the rest skipped
+    lib.gemb_check_device_status()              # the record is cleared once read
