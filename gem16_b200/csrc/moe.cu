@@ -137,6 +137,95 @@ router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w
   }
 }
 
+// Decode-size and small-batch form of the same contract.  With few tokens the tile above leaves
+// most SMs idle (one CTA per 8 or 32 tokens, each walking all of K).  Here a thread owns ONE
+// expert and kTpt tokens (kTpt independent fma chains), a warp 32 experts, a CTA of two warps
+// 2 * kTpt tokens of the same 32 experts.  K is walked in tiles of 128: the CTA's weight tile
+// (32 experts x 128 k, each warp fetching 16 rows with fully coalesced 512-byte loads) and the
+// tokens' activations go through registers into shared memory, the loads of the next tile being
+// issued before the current one is consumed -- the chain over k is serial, so a tile's worth of
+// arithmetic is all there is to hide the L2 latency behind.  Same chain, same order: bias, then
+// one fma per k ascending.
+constexpr int kRsK = 128, kRsThreads = 64, kRsPad = 4;
+
+template <int kTpt>
+__global__ void __launch_bounds__(kRsThreads)
+router_logits_small_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
+                           const float* __restrict__ bias, float* __restrict__ logits, uint32_t tokens,
+                           uint32_t hidden, uint32_t experts) {
+  constexpr int kTokCta = 2 * kTpt;
+  constexpr int kXPerThread = kTokCta * (kRsK / 4) / kRsThreads;   // 8-byte x pieces per thread and tile
+  __shared__ __align__(16) float ws[32][kRsK + kRsPad];  // row stride 132 words: float4 reads of one k by 32 rows are conflict free
+  __shared__ __align__(16) float xs[kTokCta][kRsK];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t tok0 = blockIdx.x * kTokCta, exp0 = blockIdx.y * 32;
+  const uint32_t e = exp0 + lane;
+  const bool live = e < experts;
+  float acc[kTpt];
+  const float b = (bias != nullptr && live) ? __ldg(bias + e) : 0.0f;
+#pragma unroll
+  for (int i = 0; i < kTpt; ++i) acc[i] = b;
+  float4 wreg[16];
+  uint2 xreg[kXPerThread];
+  // Warp `warp` fetches rows warp*16 .. warp*16+15 of the weight tile, lane = 16-byte piece of the row.
+  auto load_tile = [&](uint32_t k0) {
+    const uint32_t kmax = min(static_cast<uint32_t>(kRsK), hidden - k0);
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      const uint32_t row = exp0 + warp * 16 + r;
+      wreg[r] = (row < experts && static_cast<uint32_t>(lane) * 4 < kmax)
+                    ? __ldg(reinterpret_cast<const float4*>(w + static_cast<uint64_t>(row) * hidden + k0) + lane)
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int q = 0; q < kXPerThread; ++q) {
+      const uint32_t idx = threadIdx.x + q * kRsThreads;
+      const uint32_t t = idx / (kRsK / 4), c = (idx % (kRsK / 4)) * 4;
+      xreg[q] = (tok0 + t < tokens && c < kmax)
+                    ? __ldg(reinterpret_cast<const uint2*>(x + static_cast<uint64_t>(tok0 + t) * hidden + k0 + c))
+                    : make_uint2(0u, 0u);
+    }
+  };
+  auto store_tile = [&]() {
+#pragma unroll
+    for (int r = 0; r < 16; ++r) *reinterpret_cast<float4*>(&ws[warp * 16 + r][lane * 4]) = wreg[r];
+#pragma unroll
+    for (int q = 0; q < kXPerThread; ++q) {
+      const uint32_t idx = threadIdx.x + q * kRsThreads;
+      const uint32_t t = idx / (kRsK / 4), c = (idx % (kRsK / 4)) * 4;
+      *reinterpret_cast<float4*>(&xs[t][c]) =
+          make_float4(__uint_as_float(xreg[q].x << 16), __uint_as_float(xreg[q].x & 0xFFFF0000u),
+                      __uint_as_float(xreg[q].y << 16), __uint_as_float(xreg[q].y & 0xFFFF0000u));
+    }
+  };
+  load_tile(0);
+  for (uint32_t k0 = 0; k0 < hidden; k0 += kRsK) {
+    const uint32_t groups = min(static_cast<uint32_t>(kRsK), hidden - k0) / 4;
+    __syncthreads();   // the previous tile has been consumed
+    store_tile();
+    __syncthreads();
+    if (k0 + kRsK < hidden) load_tile(k0 + kRsK);
+#pragma unroll 8
+    for (uint32_t g = 0; g < groups; ++g) {
+      const float4 wv = *reinterpret_cast<const float4*>(&ws[lane][g * 4]);
+#pragma unroll
+      for (int i = 0; i < kTpt; ++i) {
+        const float4 xv = *reinterpret_cast<const float4*>(&xs[warp * kTpt + i][g * 4]);
+        acc[i] = fmaf(xv.x, wv.x, acc[i]);
+        acc[i] = fmaf(xv.y, wv.y, acc[i]);
+        acc[i] = fmaf(xv.z, wv.z, acc[i]);
+        acc[i] = fmaf(xv.w, wv.w, acc[i]);
+      }
+    }
+  }
+  if (!live) return;
+#pragma unroll
+  for (int i = 0; i < kTpt; ++i) {
+    const uint32_t t = tok0 + warp * kTpt + i;
+    if (t < tokens) logits[static_cast<uint64_t>(t) * experts + e] = acc[i];
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Softmax over all experts, top-k with the lower id winning ties, renormalise, optional
 // per-expert scale (MOE_ROUTER_SPEC.md:27-63).  One warp per token; lane l owns experts
@@ -549,8 +638,25 @@ int32_t gemb_moe_router_logits(const uint16_t* x_bf16, const float* router_weigh
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(x_bf16) % 8 == 0 && reinterpret_cast<uintptr_t>(router_weight) % 16 == 0,
                "%s: activations must be 8-byte and router weights 16-byte aligned", op);
   GEMB_TRY(require_sm100(op));
-  // 8-token CTAs only while they do not outnumber the SMs (decode-size batches); beyond that the
-  // 32-token tile does four times the arithmetic per shared-memory load.
+  // Up to a couple of thousand tokens: one expert per thread, weight rows streamed from L2 (the
+  // tiled kernel would occupy a fraction of the SMs).  Its L2 traffic grows with the token count
+  // (one pass over the router weight per 2 * kTpt tokens), so large batches use the tiled kernel.
+  if (tokens <= 2048) {
+    if (tokens <= 512) {
+      dim3 g(static_cast<unsigned>((tokens + 7) / 8), static_cast<unsigned>((experts + 31) / 32));
+      router_logits_small_kernel<4><<<g, kRsThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
+                                                                   static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
+                                                                   static_cast<uint32_t>(experts));
+    } else {
+      dim3 g(static_cast<unsigned>((tokens + 15) / 16), static_cast<unsigned>((experts + 31) / 32));
+      router_logits_small_kernel<8><<<g, kRsThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
+                                                                   static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
+                                                                   static_cast<uint32_t>(experts));
+    }
+    return check_launch(op);
+  }
+  // 8-token CTAs only while they do not outnumber the SMs; beyond that the 32-token tile does four
+  // times the arithmetic per shared-memory load.
   const bool small = (tokens + 7) / 8 * ((experts + kRtExp - 1) / kRtExp) <= static_cast<uint64_t>(sm_count());
   const unsigned tile = small ? 8 : 32;
   dim3 grid(static_cast<unsigned>((tokens + tile - 1) / tile), static_cast<unsigned>((experts + kRtExp - 1) / kRtExp));
