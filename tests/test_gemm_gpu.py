@@ -156,3 +156,35 @@ def test_nvfp4_gemm_f32_output(lib, dev, orc):
     got = out.cpu().numpy().astype(np.float64)
     assert np.isfinite(got).all()
     assert np.linalg.norm(got - want) / np.linalg.norm(want) < 1e-6
+
+
+@pytest.mark.parametrize("tokens,rows,k", [(128, 256, 64), (300, 1000, 704), (4096, 4096, 512), (1153, 2816, 2112)])
+def test_cta_pair_and_single_cta_tiles_agree_bit_for_bit(lib, dev, tokens, rows, k):
+    """The dense GEMMs run 256x256 tiles on CTA pairs by default; GEMB_TUNE_GEMM_PAIR = 1 runs the same
+    256-wide tile on one CTA.  Same MMAs, same accumulation order: the outputs must be identical.
+    Shapes cover an odd number of 128-row tiles (the odd CTA of the last pair has no rows), ragged
+    rows / columns, a K tail, and several tiles per cluster."""
+    a = nvfp4_operand(lib, dev, tokens, k, 1.0, 3)
+    w = nvfp4_operand(lib, dev, rows, k, 0.02, 4)
+    a8 = fp8_operand(lib, dev, tokens, k, 1.0, 5)
+    w8 = fp8_operand(lib, dev, rows, k, 0.02, 6)
+    outs = {}
+    try:
+        for mode in (1, 2):
+            lib.gemb_set_tuning(5, mode)
+            o4 = torch.full((tokens, rows), 0x7FC0, dtype=torch.int16, device=dev)
+            o8 = torch.full((tokens, rows), 0x7FC0, dtype=torch.int16, device=dev)
+            o32 = torch.full((tokens, rows), float("nan"), device=dev)
+            lib.gemb_nvfp4_gemm_bf16(a["packed"], a["inter"], w["packed"], w["inter"], o4, tokens, rows, k,
+                                     a["div"], w["div"], None)
+            lib.gemb_nvfp4_gemm_f32(a["packed"], a["inter"], w["packed"], w["inter"], o32, tokens, rows, k,
+                                    a["div"], w["div"], None)
+            lib.gemb_fp8_gemm_bf16(a8["q"], a8["scales"], w8["q"], w8["scales_bf16"], o8, tokens, rows, k, None)
+            torch.cuda.synchronize()
+            lib.gemb_check_device_status()
+            outs[mode] = (o4, o32, o8)
+    finally:
+        lib.gemb_set_tuning(5, 0)
+    for x, y, name in zip(outs[1], outs[2], ("nvfp4 bf16", "nvfp4 f32", "fp8 bf16")):
+        assert torch.equal(x, y), name
+        assert not torch.isnan(y.float() if y.dtype == torch.float32 else y.view(torch.bfloat16).float()).any(), name
