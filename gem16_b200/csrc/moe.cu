@@ -28,7 +28,7 @@ constexpr int kRtExp = 128, kRtK = 32, kRtThreads = 128;
 // (multiples of 4 / 8 keep each thread's float4 groups intact) so that both the transposing
 // stores and the float4 loads are bank-conflict free.
 template <int kTok>
-__global__ void __launch_bounds__(kRtThreads)
+__global__ void __launch_bounds__(kRtThreads, 4)
 router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
                      const float* __restrict__ bias, float* __restrict__ logits, uint32_t tokens,
                      uint32_t hidden, uint32_t experts) {
@@ -99,8 +99,9 @@ router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w
     __syncthreads();
     if (k0 + kRtK < hidden) load_tile(k0 + kRtK);
     const uint32_t kmax = min(static_cast<uint32_t>(kRtK), hidden - k0);
-#pragma unroll 4
-    for (uint32_t k = 0; k < kmax; ++k) {
+    if (kmax == kRtK) {
+#pragma unroll
+      for (uint32_t k = 0; k < kRtK; ++k) {
       const float4 wv4 = *reinterpret_cast<const float4*>(&ws[k][(tx * 4) ^ (4 * (k >> 2))]);
       const float wv[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
       float xv[kPerThread];
@@ -119,6 +120,29 @@ router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w
       for (int i = 0; i < kPerThread; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+    }
+    } else {
+#pragma unroll 4
+      for (uint32_t k = 0; k < kmax; ++k) {
+      const float4 wv4 = *reinterpret_cast<const float4*>(&ws[k][(tx * 4) ^ (4 * (k >> 2))]);
+      const float wv[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
+      float xv[kPerThread];
+      if constexpr (kPerThread == 8) {
+        const int col = (ty * 8) ^ (8 * ((k >> 3) & 3));
+        const float4 xa = *reinterpret_cast<const float4*>(&xs[k][col]);
+        const float4 xb = *reinterpret_cast<const float4*>(&xs[k][col + 4]);
+        xv[0] = xa.x; xv[1] = xa.y; xv[2] = xa.z; xv[3] = xa.w;
+        xv[4] = xb.x; xv[5] = xb.y; xv[6] = xb.z; xv[7] = xb.w;
+      } else {
+        const int col = (ty * 2) ^ (8 * ((k >> 3) & 3));
+        const float2 xa = *reinterpret_cast<const float2*>(&xs[k][col]);
+        xv[0] = xa.x; xv[1] = xa.y;
+      }
+#pragma unroll
+      for (int i = 0; i < kPerThread; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+    }
     }
     __syncthreads();
   }
