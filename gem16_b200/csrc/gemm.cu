@@ -6,25 +6,31 @@
 // A is the activation [M, K] (tokens), B the weight [N, K] (output rows), both K-major, so
 // D = A * B^T lands with one token per TMEM lane and one output feature per TMEM column.
 //
-// One persistent CTA per SM, six warps:
-//   warp 0   producer: one elected lane issues TMA tile loads (128-byte swizzle, no multicast)
+// One persistent CTA per SM.  Dense calls pair the CTAs (clusters of two, tcgen05 cta_group::2):
+// the pair owns a 256 x 256 tile, each CTA stages its own 128 activation rows and 128 of the 256
+// weight rows, the even CTA issues every MMA, each CTA accumulates and stores its own 128 rows.
+// Grouped (mixture-of-experts) calls keep one CTA per 128 x 256 tile.  Warp roles:
+//   producer (warp 0): one elected lane issues TMA tile loads (128-byte swizzle, no multicast)
 //            for A and B and 1-D bulk copies for the interleaved block scales into a ring of
 //            kStages shared-memory stages, each guarded by a full/empty mbarrier pair;
-//   warp 1   MMA issuer: owns the 512 TMEM columns; per stage issues one tcgen05.mma per 32
-//            bytes of K and commits the stage's empty barrier; after the last K step commits
-//            the accumulator barrier;
-//   warps 2-5 and the last four warps: epilogue, two sets of four; each warp drains its 32 TMEM
-//            lanes 64 columns at a time, the sets taking alternate 64-column sub-tiles (two
-//            tcgen05.ld in flight), scales, rounds to bf16, writes a 32 x 128-byte block into
-//            its own swizzled staging buffer and issues a TMA store (which also clips the
-//            token / row tails).  With kAccStages = 2 the
-//            accumulators are double buffered in TMEM so the epilogue of tile i overlaps the
-//            main loop of tile i+1.
-//   warps 6-9 (NVFP4 only) scale movers: each copies the stage's block scales from shared
-//            memory into its quarter of TMEM with tcgen05.st (one 128-bit shared load feeds four
-//            TMEM columns) and arrives on the stage's scales-ready barrier.  Doing this with
-//            tcgen05.cp from the MMA thread costs a third of the tensor-pipe time, because those
-//            copies queue in front of the MMAs.
+//   MMA issuer (warp 1): per stage one tcgen05.mma per 32 bytes of K, then a commit of the stage's
+//            empty barrier; after the last K step a commit of the accumulator barrier.  In the odd
+//            CTA of a pair this warp only relays "operands landed" to the issuer (FP8);
+//   epilogue, two sets of four warps: each warp drains its 32 TMEM lanes 64 columns at a time,
+//            the sets taking alternate 64-column sub-tiles; scales, rounds to bf16, stages a
+//            32 x 128-byte block in its own swizzled buffer and issues a TMA store (which also
+//            clips the token / row tails).  FP8 double-buffers the accumulator; NVFP4 has room
+//            for one (256 columns + the scale regions), so its epilogue releases the accumulator
+//            as early as it can: first sub-tile converted in registers, second loaded, release,
+//            and only then the staging and the stores;
+//   scale movers (NVFP4), two sets of four warps: copy a stage's block scales from shared memory
+//            into the stage's TMEM region with tcgen05.st and arrive on its scales-ready barrier.
+//            Doing this with tcgen05.cp from the MMA thread costs a third of the tensor-pipe
+//            time, because those copies queue in front of the MMAs.
+// NVFP4 lays the roles out on warpgroup boundaries (warps 0-3 producer / issuer / two idle, 4-7
+// and 12-15 epilogue, 8-11 and 16-19 movers) so that setmaxnreg can move registers from the
+// producer, issuer and movers to the epilogue, which holds 96 accumulator values per thread
+// between the accumulator becoming full and its release.
 // Tiles are walked with the token-tile index fastest so CTAs running at the same time share the
 // same weight tile through L2.
 //
@@ -51,7 +57,7 @@ __device__ int g_gemm_error = 0;
 namespace {
 
 constexpr int kGemmThreadsFp8 = 320;   // producer, MMA, 2 x 4 epilogue warps
-constexpr int kGemmThreadsFp4 = 576;   // producer, MMA, 2 x (4 epilogue + 4 scale mover) warps
+constexpr int kGemmThreadsFp4 = 640;   // warpgroups: control (producer, MMA, 2 idle), epilogue, movers, epilogue, movers
 constexpr int BM = 128;
 
 struct GemmParams {
@@ -220,6 +226,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     *abort_flag = 1;
   };
 
+  // NVFP4: 640 threads start with 96 registers each.  The control warpgroup (to 40) and the two
+  // mover warpgroups (to 72) hand back 128 * (56 + 2 * 24) = 13,312 registers; the two epilogue
+  // warpgroups (to 144) take 128 * 2 * 48 = 12,288 of them.  An inc can only be served from what
+  // the same CTA has released, so the decs must cover the incs (the inc waits for them).  Each
+  // setmaxnreg is the first thing its whole warpgroup executes inside the branch it governs.
+  const bool is_ctrl = kFp4 ? warp < 4 : warp < 2;
+  const bool is_mover = kFp4 && ((warp >= 8 && warp < 12) || warp >= 16);
+  if (is_ctrl) {
+  if constexpr (kFp4) ptx::reg_dec<40>();
   if (warp == 0) {
     // ------------------------------- producer -------------------------------------------------
     if (ptx::elect_one()) {
@@ -357,7 +372,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (++as == kAccStages) { as = 0; aphase ^= 1; }
       }
     }
-  } else if (kFp4 && ((warp >= 6 && warp < 10) || warp >= 14)) {
+  }  // warps 2 and 3 of the NVFP4 control warpgroup are idle
+  } else if (is_mover) {
     // ------------------------------- scale movers (NVFP4) ------------------------------------
     // Two sets of four warps (one warp per TMEM lane quarter), since one trip of this loop
     // (barrier poll, shared loads, tcgen05.st, wait, arrive) takes longer than a step's four
@@ -368,10 +384,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // one MMA) and writes them to the stage's TMEM region with two wide tcgen05.st.  The set's
     // next barrier is polled while the loads are in flight.
     if constexpr (kFp4) {
+      ptx::reg_dec<72>();
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
       const uint32_t total_steps = my_tiles * k_stages;
       static_assert(kStages % 2 == 1 && kStages >= 3, "the mover sets split an odd number of stages");
-      const uint32_t mset = warp >= 14 ? 1u : 0u;
+      const uint32_t mset = warp >= 16 ? 1u : 0u;
       uint32_t stage = mset, phase = 0, step = mset, ks = mset % k_stages;
       bool ready = false;
       while (step < total_steps && !*abort_flag) {
@@ -429,8 +446,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   } else {
     // ------------------------------- epilogue -------------------------------------------------
     // Two sets of four warps; set s drains the 64-column sub-tiles s, s+2, ... of every tile.
+    if constexpr (kFp4) ptx::reg_inc<144>();
     const uint32_t quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    const uint32_t set = warp >= (kFp4 ? 10 : 6) ? 1u : 0u;
+    const uint32_t set = warp >= (kFp4 ? 12 : 6) ? 1u : 0u;
     uint8_t* my_stage = epi_stage + (set * 4 + quarter) * 4096;
     uint32_t as = 0, aphase = 0;
     for (uint32_t tile = first_tile; tile < num_tiles && !*abort_flag; tile += tile_stride) {
@@ -448,16 +466,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       if (kFp4 && p.w_divisors != nullptr)
         row_scale = __fdiv_rn(1.0f, __fmul_rn(p.ga, __ldg(p.w_divisors + (tile_expert ? __ldg(tile_expert + mt) : 0))));
       const uint32_t tmem_acc = tmem_base + as * BN + ((quarter * 32) << 16);
-      bool released = false, deferred = false;
-      uint32_t deferred_col = 0;
-      // Hands the staged sub-tile to a TMA store.
-      auto store_staged = [&](uint32_t col) {
+      bool released = false, pending = false;
+      uint32_t pending_col = 0;
+      uint32_t packed[32];  // one converted sub-tile: 16-byte chunk j of this lane's row = packed[4j .. 4j+3]
+      // Stages `packed` in this warp's swizzled buffer and hands it to a TMA store.
+      auto stage_and_store = [&](uint32_t col) {
+        if (lane == 0) ptx::bulk_wait_group_read<0>();  // the previous store has read the buffer
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          // chunk j of row `lane` goes to chunk j ^ (lane % 8): the 128-byte swizzle the output
+          // tensor map expects, and conflict free for the warp.
+          *reinterpret_cast<uint4*>(my_stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+              make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
           ptx::tma_store_2d(&map_out, my_stage, static_cast<int32_t>(col), static_cast<int32_t>(row0));
           ptx::bulk_commit_group();
         }
+        pending = false;
       };
 #pragma unroll 1
       for (uint32_t c = set; c < BN / 64; c += 2) {
@@ -529,9 +557,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           continue;
         }
         // Plain bf16 output.  Nothing slow may sit between the accumulator becoming full and its
-        // release (the MMA issuer is idle meanwhile): a warp's first sub-tile is converted and
-        // staged but its proxy fence and TMA store wait until the last sub-tile is in registers
-        // and the accumulator has been released.
+        // release (the MMA issuer is idle meanwhile): a warp's first sub-tile is only converted,
+        // registers to registers; once its last one is in registers too the accumulator is
+        // released, and the staging and the TMA stores of both follow.
         ptx::tc_wait_ld();
         if (c + 2 >= BN / 64) {
           ptx::tc_fence_before();
@@ -539,17 +567,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           if (lane == 0) arrive_issuer(&acc_empty[as]);
           released = true;
         }
-        if (deferred) {
-          store_staged(deferred_col);
-          deferred = false;
-          if (lane == 0) ptx::bulk_wait_group_read<0>();  // the staging buffer is about to be rewritten
-          __syncwarp();
-        }
+        if (pending) stage_and_store(pending_col);
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            uint32_t packed[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const int e = q * 8 + i * 2;  // column within this 32-column half
@@ -564,23 +586,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 lo = __fmul_rn(__fmul_rn(lo, row_scale), __uint_as_float(wp << 16));
                 hi = __fmul_rn(__fmul_rn(hi, row_scale), __uint_as_float(wp & 0xFFFF0000u));
               }
-              packed[i] = pack_bf16x2(lo, hi);
+              packed[(half * 4 + q) * 4 + i] = pack_bf16x2(lo, hi);
             }
-            // 16-byte chunk j of row `lane` goes to chunk j ^ (lane % 8): the 128-byte swizzle the
-            // output tensor map expects, and conflict free for the warp.
-            const int j = half * 4 + q;
-            *reinterpret_cast<uint4*>(my_stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-                make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
         }
-        if (c + 2 >= BN / 64) {
-          store_staged(col0);
-        } else {
-          deferred = true;
-          deferred_col = col0;
-        }
+        pending = true;
+        pending_col = col0;
       }
-      if (deferred) store_staged(deferred_col);
+      if (pending) stage_and_store(pending_col);
       if (!released) {
         ptx::tc_fence_before();
         __syncwarp();

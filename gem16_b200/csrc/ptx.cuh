@@ -119,6 +119,18 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// ---- register re-allocation between warpgroups -------------------------------------------------
+// All four warps of a warpgroup (warps 4i .. 4i+3) must execute the same one.  `inc` blocks until
+// other warpgroups have released enough registers with `dec`.
+template <int kRegs>
+__device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
 // ---- TMA -------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const void* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
