@@ -164,13 +164,35 @@ router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w
 // Decode-size and small-batch form of the same contract.  With few tokens the tile above leaves
 // most SMs idle (one CTA per 8 or 32 tokens, each walking all of K).  Here a thread owns ONE
 // expert and kTpt tokens (kTpt independent fma chains), a warp 32 experts, a CTA of two warps
-// 2 * kTpt tokens of the same 32 experts.  K is walked in tiles of 128: the CTA's weight tile
-// (32 experts x 128 k, each warp fetching 16 rows with fully coalesced 512-byte loads) and the
-// tokens' activations go through registers into shared memory, the loads of the next tile being
-// issued before the current one is consumed -- the chain over k is serial, so a tile's worth of
-// arithmetic is all there is to hide the L2 latency behind.  Same chain, same order: bias, then
-// one fma per k ascending.
-constexpr int kRsK = 128, kRsThreads = 64, kRsPad = 4;
+// 2 * kTpt tokens of the same 32 experts.  K is walked in tiles of 128.  The chain over k is
+// serial, so a tile's arithmetic (about 600 clocks) is all there is to hide a load behind, and
+// an L2 round trip takes longer than that: the CTA's weight tiles (32 experts x 128 k, fetched
+// as coalesced 16-byte cp.async pieces) and the tokens' raw bf16 activations therefore run
+// through a ring of kRsDepth shared-memory buffers, three tiles ahead of the arithmetic.  Same
+// chain, same order: bias, then one fma per k ascending.
+constexpr int kRsK = 128, kRsThreads = 64, kRsPad = 4, kRsDepth = 4;
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, bool valid) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  const uint32_t n = valid ? 16u : 0u;   // 0 source bytes: the destination is zero filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_8(void* smem_dst, const void* src, bool valid) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  const uint32_t n = valid ? 8u : 0u;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory"); }
+
+template <int kTpt>
+struct RouterSmallSmem {
+  static constexpr int kTokCta = 2 * kTpt;
+  float ws[kRsDepth][32][kRsK + kRsPad];     // row stride 132 words: float4 reads of one k by 32 rows are conflict free
+  uint16_t xraw[kRsDepth][kTokCta][kRsK];    // bf16 as loaded
+  float xs[kTokCta][kRsK];                   // the current tile's activations as fp32
+};
 
 template <int kTpt>
 __global__ void __launch_bounds__(kRsThreads)
@@ -178,9 +200,8 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const float* __restri
                            const float* __restrict__ bias, float* __restrict__ logits, uint32_t tokens,
                            uint32_t hidden, uint32_t experts) {
   constexpr int kTokCta = 2 * kTpt;
-  constexpr int kXPerThread = kTokCta * (kRsK / 4) / kRsThreads;   // 8-byte x pieces per thread and tile
-  __shared__ __align__(16) float ws[32][kRsK + kRsPad];  // row stride 132 words: float4 reads of one k by 32 rows are conflict free
-  __shared__ __align__(16) float xs[kTokCta][kRsK];
+  extern __shared__ __align__(16) uint8_t router_small_smem[];
+  auto& sm = *reinterpret_cast<RouterSmallSmem<kTpt>*>(router_small_smem);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t tok0 = blockIdx.x * kTokCta, exp0 = blockIdx.y * 32;
   const uint32_t e = exp0 + lane;
@@ -189,59 +210,66 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const float* __restri
   const float b = (bias != nullptr && live) ? __ldg(bias + e) : 0.0f;
 #pragma unroll
   for (int i = 0; i < kTpt; ++i) acc[i] = b;
-  float4 wreg[16];
-  uint2 xreg[kXPerThread];
-  // Warp `warp` fetches rows warp*16 .. warp*16+15 of the weight tile, lane = 16-byte piece of the row.
-  auto load_tile = [&](uint32_t k0) {
-    const uint32_t kmax = min(static_cast<uint32_t>(kRsK), hidden - k0);
+  const uint32_t tiles = (hidden + kRsK - 1) / kRsK;
+  // Warp `warp` fetches rows warp*16 .. warp*16+15 of the weight tile (lane = 16-byte piece of the
+  // row); the activation tile is kTokCta rows of 32 eight-byte pieces shared out over the CTA.
+  auto issue_tile = [&](uint32_t t) {
+    if (t < tiles) {
+      const uint32_t k0 = t * kRsK, buf = t % kRsDepth;
+      const uint32_t kmax = min(static_cast<uint32_t>(kRsK), hidden - k0);   // a multiple of 4
 #pragma unroll
-    for (int r = 0; r < 16; ++r) {
-      const uint32_t row = exp0 + warp * 16 + r;
-      wreg[r] = (row < experts && static_cast<uint32_t>(lane) * 4 < kmax)
-                    ? __ldg(reinterpret_cast<const float4*>(w + static_cast<uint64_t>(row) * hidden + k0) + lane)
-                    : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
+      for (int r = 0; r < 16; ++r) {
+        const uint32_t row = exp0 + warp * 16 + r;
+        const bool ok = row < experts && static_cast<uint32_t>(lane) * 4 < kmax;
+        const float* src = w + static_cast<uint64_t>(ok ? row : 0) * hidden + (ok ? k0 + lane * 4 : 0);
+        cp_async_16(&sm.ws[buf][warp * 16 + r][lane * 4], src, ok);
+      }
 #pragma unroll
-    for (int q = 0; q < kXPerThread; ++q) {
-      const uint32_t idx = threadIdx.x + q * kRsThreads;
-      const uint32_t t = idx / (kRsK / 4), c = (idx % (kRsK / 4)) * 4;
-      xreg[q] = (tok0 + t < tokens && c < kmax)
-                    ? __ldg(reinterpret_cast<const uint2*>(x + static_cast<uint64_t>(tok0 + t) * hidden + k0 + c))
-                    : make_uint2(0u, 0u);
-    }
-  };
-  auto store_tile = [&]() {
-#pragma unroll
-    for (int r = 0; r < 16; ++r) *reinterpret_cast<float4*>(&ws[warp * 16 + r][lane * 4]) = wreg[r];
-#pragma unroll
-    for (int q = 0; q < kXPerThread; ++q) {
-      const uint32_t idx = threadIdx.x + q * kRsThreads;
-      const uint32_t t = idx / (kRsK / 4), c = (idx % (kRsK / 4)) * 4;
-      *reinterpret_cast<float4*>(&xs[t][c]) =
-          make_float4(__uint_as_float(xreg[q].x << 16), __uint_as_float(xreg[q].x & 0xFFFF0000u),
-                      __uint_as_float(xreg[q].y << 16), __uint_as_float(xreg[q].y & 0xFFFF0000u));
-    }
-  };
-  load_tile(0);
-  for (uint32_t k0 = 0; k0 < hidden; k0 += kRsK) {
-    const uint32_t groups = min(static_cast<uint32_t>(kRsK), hidden - k0) / 4;
-    __syncthreads();   // the previous tile has been consumed
-    store_tile();
-    __syncthreads();
-    if (k0 + kRsK < hidden) load_tile(k0 + kRsK);
-#pragma unroll 8
-    for (uint32_t g = 0; g < groups; ++g) {
-      const float4 wv = *reinterpret_cast<const float4*>(&ws[lane][g * 4]);
-#pragma unroll
-      for (int i = 0; i < kTpt; ++i) {
-        const float4 xv = *reinterpret_cast<const float4*>(&xs[warp * kTpt + i][g * 4]);
-        acc[i] = fmaf(xv.x, wv.x, acc[i]);
-        acc[i] = fmaf(xv.y, wv.y, acc[i]);
-        acc[i] = fmaf(xv.z, wv.z, acc[i]);
-        acc[i] = fmaf(xv.w, wv.w, acc[i]);
+      for (int q = 0; q < kTokCta * 32 / kRsThreads; ++q) {
+        const uint32_t idx = threadIdx.x + q * kRsThreads;
+        const uint32_t tk = idx / 32, c = (idx % 32) * 4;
+        const bool ok = tok0 + tk < tokens && c < kmax;
+        const uint16_t* src = x + static_cast<uint64_t>(ok ? tok0 + tk : 0) * hidden + (ok ? k0 + c : 0);
+        cp_async_8(&sm.xraw[buf][tk][c], src, ok);
       }
     }
+    cp_async_commit();   // one group per call, empty past the last tile, so the counting stays uniform
+  };
+#pragma unroll
+  for (int t = 0; t < kRsDepth - 1; ++t) issue_tile(t);
+  for (uint32_t t = 0; t < tiles; ++t) {
+    const uint32_t buf = t % kRsDepth;
+    const uint32_t groups = min(static_cast<uint32_t>(kRsK), hidden - t * kRsK) / 4;
+    cp_async_wait<kRsDepth - 2>();   // this thread's pieces of tile t have landed
+    __syncthreads();                 // everyone's have; and tile t-1 has been consumed
+    issue_tile(t + kRsDepth - 1);    // refills the buffer tile t-1 used
+    for (uint32_t idx = threadIdx.x; idx < kTokCta * (kRsK / 4); idx += kRsThreads) {
+      const uint32_t tk = idx / (kRsK / 4), c = (idx % (kRsK / 4)) * 4;
+      const uint2 raw = *reinterpret_cast<const uint2*>(&sm.xraw[buf][tk][c]);
+      *reinterpret_cast<float4*>(&sm.xs[tk][c]) =
+          make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
+                      __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u));
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (uint32_t g = 0; g < groups; ++g) {
+      const float4 wv = *reinterpret_cast<const float4*>(&sm.ws[buf][lane][g * 4]);
+      float4 xv[kTpt];
+#pragma unroll
+      for (int i = 0; i < kTpt; ++i) xv[i] = *reinterpret_cast<const float4*>(&sm.xs[warp * kTpt + i][g * 4]);
+      // k-major: the kTpt chains advance together, so consecutive instructions are independent
+      // (a chain's own steps are four clocks apart at best).
+#pragma unroll
+      for (int i = 0; i < kTpt; ++i) acc[i] = fmaf(xv[i].x, wv.x, acc[i]);
+#pragma unroll
+      for (int i = 0; i < kTpt; ++i) acc[i] = fmaf(xv[i].y, wv.y, acc[i]);
+#pragma unroll
+      for (int i = 0; i < kTpt; ++i) acc[i] = fmaf(xv[i].z, wv.z, acc[i]);
+#pragma unroll
+      for (int i = 0; i < kTpt; ++i) acc[i] = fmaf(xv[i].w, wv.w, acc[i]);
+    }
   }
+  cp_async_wait<0>();
   if (!live) return;
 #pragma unroll
   for (int i = 0; i < kTpt; ++i) {
@@ -642,6 +670,22 @@ int32_t validate_permute_geometry(const char* op, uint64_t tokens, uint64_t expe
   return GEMB_OK;
 }
 
+// The small-batch router kernel's ring needs more than the 48 KB a kernel gets without opting in.
+template <int kTpt>
+int32_t router_small_configure(const char* op) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(router_logits_small_kernel<kTpt>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(sizeof(RouterSmallSmem<kTpt>)));
+    if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  return GEMB_OK;
+}
+
 int32_t validate_moe_geometry(const char* op, uint64_t tokens, uint64_t experts, uint64_t topk) {
   GEMB_REQUIRE(tokens > 0 && tokens * topk < (1ull << 31), "%s: token count must be nonzero and fit 31 bits", op);
   GEMB_REQUIRE(experts >= 32 && experts % 32 == 0 && experts <= 256, "%s: experts must be a multiple of 32 in [32, 256]", op);
@@ -666,14 +710,22 @@ int32_t gemb_moe_router_logits(const uint16_t* x_bf16, const float* router_weigh
   // tiled kernel would occupy a fraction of the SMs).  Its L2 traffic grows with the token count
   // (one pass over the router weight per 2 * kTpt tokens), so large batches use the tiled kernel.
   if (tokens <= 2048) {
-    if (tokens <= 512) {
+    if (tokens <= 256) {
+      dim3 g(static_cast<unsigned>((tokens + 3) / 4), static_cast<unsigned>((experts + 31) / 32));
+      GEMB_TRY(router_small_configure<2>(op));
+      router_logits_small_kernel<2><<<g, kRsThreads, sizeof(RouterSmallSmem<2>), stream>>>(x_bf16, router_weight, bias, logits,
+                                                                   static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
+                                                                   static_cast<uint32_t>(experts));
+    } else if (tokens <= 512) {
       dim3 g(static_cast<unsigned>((tokens + 7) / 8), static_cast<unsigned>((experts + 31) / 32));
-      router_logits_small_kernel<4><<<g, kRsThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
+      GEMB_TRY(router_small_configure<4>(op));
+      router_logits_small_kernel<4><<<g, kRsThreads, sizeof(RouterSmallSmem<4>), stream>>>(x_bf16, router_weight, bias, logits,
                                                                    static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
                                                                    static_cast<uint32_t>(experts));
     } else {
       dim3 g(static_cast<unsigned>((tokens + 15) / 16), static_cast<unsigned>((experts + 31) / 32));
-      router_logits_small_kernel<8><<<g, kRsThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
+      GEMB_TRY(router_small_configure<8>(op));
+      router_logits_small_kernel<8><<<g, kRsThreads, sizeof(RouterSmallSmem<8>), stream>>>(x_bf16, router_weight, bias, logits,
                                                                    static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
                                                                    static_cast<uint32_t>(experts));
     }
