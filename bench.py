@@ -367,7 +367,8 @@ def run_decode_gemv(args):
     if world == 1 and not args.no_other_workloads:
         other = line["other_workloads"]
         for name, fn in (("nvfp4_linear", bench_nvfp4_linear), ("prefill_gemm", bench_prefill_gemm),
-                         ("prefill_stack", bench_prefill_stack), ("moe_layer", bench_moe_layer)):
+                         ("prefill_stack", bench_prefill_stack), ("moe_layer", bench_moe_layer),
+                         ("output_head", bench_output_head)):
             try:
                 other[name] = fn(lib, dev)
             except Exception as exc:  # a secondary workload must not take the headline line down
@@ -584,6 +585,33 @@ def bench_moe_layer(lib, dev, tokens=4096):
             "expert_count_max": int(layer.counts.max().item()), "expert_count_min": int(layer.counts.min().item())}
 
 
+def bench_output_head(lib, dev, vocab=262144, hidden=3840):
+    """Tied bf16 output head of one decode step: 262,144 x 3,840 bf16 = 2.0 GB read per launch (far
+    beyond L2), fused soft cap + suppression + arg-max; one hidden row (decode) and five (the
+    reference's speculative-decoding verifier)."""
+    import torch
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + 7000)
+    w = (torch.randn((vocab, hidden), device=dev, generator=gen) * 0.05).to(torch.bfloat16).view(torch.int16)
+    blocks = lib.cdll.gemb_output_head_candidate_blocks()
+    peaks = measured_peaks()
+    out = {"metric": "output head GB/s", "workload": f"output_head {vocab}x{hidden} bf16, soft cap 30, arg-max", "rows": {}}
+    for rows in (1, 5):
+        h = torch.randn((rows, hidden), device=dev, generator=gen)
+        cand = torch.zeros((rows, blocks, 2), dtype=torch.int32, device=dev)
+        sel = torch.zeros((rows,), dtype=torch.int32, device=dev)
+        sup = torch.tensor([0, 1, 2, 3], dtype=torch.int32, device=dev)
+
+        def step(st):
+            lib.gemb_output_head_candidates(w, h, rows, sup, 4, None, cand, None, vocab, hidden, st)
+            lib.gemb_output_head_argmax(cand, rows, sel, st)
+
+        t = graph_time(step, 2)
+        nbytes = vocab * hidden * 2 + rows * hidden * 4 + rows * blocks * 8
+        out["rows"][str(rows)] = {"us": t * 1e6, "gbs": nbytes / t / 1e9, "frac_of_measured_hbm_peak": nbytes / t / 1e9 / peaks["hbm_gbs"]}
+    return out
+
+
 def bench_tp_mlp(lib, dev, world, rank, tokens=16384):
     """Tensor-parallel 12B-like gated MLP (hidden 3840, intermediate 15360) on 16,384 tokens: gate/up
     column split, down row split with an fp32 all-reduce.  Collective; N = 1 runs it unsharded."""
@@ -745,7 +773,7 @@ def main():
     ap.add_argument("--no-other-workloads", action="store_true")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="decode layers held on the device (48 = the benchmark; fewer for a small profiler capture)")
-    ap.add_argument("--only", default=None, choices=["nvfp4_linear", "moe_layer", "prefill_gemm", "prefill_stack"],
+    ap.add_argument("--only", default=None, choices=["nvfp4_linear", "moe_layer", "prefill_gemm", "prefill_stack", "output_head"],
                     help="run just one secondary workload on one GPU and print its JSON (profiling aid)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -757,7 +785,7 @@ def main():
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(dev)
         fn = {"nvfp4_linear": bench_nvfp4_linear, "moe_layer": bench_moe_layer, "prefill_gemm": bench_prefill_gemm,
-              "prefill_stack": bench_prefill_stack}[args.only]
+              "prefill_stack": bench_prefill_stack, "output_head": bench_output_head}[args.only]
         print(json.dumps(fn(load(), dev)), flush=True)
         return
     run_decode_gemv(args)

@@ -17,6 +17,7 @@
 #include "cuda/nvfp4/gemv.h"
 #include "cuda/nvfp4/reference.h"
 #include "cuda/nvfp4/sm120.h"
+#include "cuda/output_head.h"
 #include "gemb200.h"
 
 namespace gem16::internal {
@@ -186,6 +187,39 @@ Status LaunchFp8CutlassProjectionBatch(const std::uint8_t* act, const float* act
                                        std::uint16_t* output, std::uint64_t tokens, std::uint64_t rows,
                                        std::uint64_t k, void*, std::size_t, cudaStream_t stream) {
   return ToStatus(gemb_fp8_gemm_bf16(act, act_scales, weight, weight_scales, output, tokens, rows, k, S(stream)));
+}
+
+// ---- src/cuda/output_head.h ------------------------------------------------------------------------
+// The reference's kernels are specialised to its vocabulary and width; the same constants go in here.
+// OutputHeadCandidate is {float value; uint32 token}, the record gemb_output_head_candidates writes,
+// 4,096 per hidden row (kOutputHeadCandidateBlocks == gemb_output_head_candidate_blocks()).
+namespace {
+constexpr std::uint64_t kShimVocabulary = 262144U, kShimHidden = 3840U;
+}  // namespace
+Status LaunchFusedOutputHeadCandidates(const std::uint16_t* weights, const float* hidden,
+                                       const std::uint32_t* suppressed, std::uint32_t suppressed_count,
+                                       const DecodeControl* control, OutputHeadCandidate* candidates,
+                                       float* diagnostic_logits, cudaStream_t stream) {
+  // the reference reads control->suppressed_token_count on the device when control is non-null
+  const std::uint32_t* dynamic_count = control == nullptr ? nullptr : &control->suppressed_token_count;
+  return ToStatus(gemb_output_head_candidates(weights, hidden, 1, suppressed, suppressed_count, dynamic_count, candidates,
+                                              diagnostic_logits, kShimVocabulary, kShimHidden, S(stream)));
+}
+Status LaunchFusedOutputHeadBatchCandidates(const std::uint16_t* weights, const float* hidden,
+                                            const std::uint32_t* suppressed, std::uint32_t suppressed_count,
+                                            std::uint64_t rows, OutputHeadCandidate* candidates,
+                                            float* diagnostic_logits, cudaStream_t stream) {
+  if (rows == 0U || rows > 5U) return Status(StatusCode::kInvalidArgument, "batched output-head row count is invalid");
+  return ToStatus(gemb_output_head_candidates(weights, hidden, rows, suppressed, suppressed_count, nullptr, candidates,
+                                              diagnostic_logits, kShimVocabulary, kShimHidden, S(stream)));
+}
+Status LaunchOutputHeadCandidateArgmax(const OutputHeadCandidate* candidates, std::uint32_t* selected,
+                                       cudaStream_t stream) {
+  return ToStatus(gemb_output_head_argmax(candidates, 1, selected, S(stream)));
+}
+Status LaunchOutputHeadBatchArgmax(const OutputHeadCandidate* candidates, std::uint64_t rows, std::uint32_t* selected,
+                                   cudaStream_t stream) {
+  return ToStatus(gemb_output_head_argmax(candidates, rows, selected, S(stream)));
 }
 
 }  // namespace gem16::internal

@@ -396,6 +396,28 @@ int32_t gemb_moe_expert_gelu_quantize(const uint16_t* gate_up_bf16, const int32_
                                       uint64_t rows_max, uint64_t intermediate,
                                       float global_divisor, gemb_stream_t stream);
 
+/* ---- output head (the first row of the path's "next" list: the tied bf16 head of the decode step) ----
+ * For each of `rows` (1..8) fp32 hidden vectors [rows, hidden] and every vocabulary row v:
+ *   logit[r][v] = tanhf(dot(bf16 W[v, :], hidden[r, :]) / 30) * 30        (fp32 accumulation)
+ * Tokens on the suppression list never win; ties go to the lower token id.  The launch writes, per
+ * hidden row, gemb_output_head_candidate_blocks() = 4,096 candidates {float value; uint32 token}
+ * (candidates[r * 4096 + block]) and, when diagnostic_logits is non-null, every capped logit
+ * [rows, vocabulary].  dynamic_suppressed_count, when non-null, is a device word that overrides
+ * suppressed_count at run time (the reference reads it from DecodeControl).
+ * Replaces LaunchFusedOutputHeadCandidates / LaunchFusedOutputHeadBatchCandidates
+ * (src/cuda/output_head.h:19-30, kernels src/cuda/output_head.cu:55-110,113-186) and, with
+ * diagnostic_logits, LaunchOutputHeadLogits (output_head.h:40-43).
+ * gemb_output_head_argmax reduces the candidates of each row to selected[r]
+ * (LaunchOutputHeadCandidateArgmax / LaunchOutputHeadBatchArgmax, output_head.h:32-38). */
+uint64_t gemb_output_head_candidate_blocks(void);
+int32_t gemb_output_head_candidates(const uint16_t* weights_bf16, const float* hidden_rows, uint64_t rows,
+                                    const uint32_t* suppressed, uint64_t suppressed_count,
+                                    const uint32_t* dynamic_suppressed_count, void* candidates,
+                                    float* diagnostic_logits, uint64_t vocabulary, uint64_t hidden,
+                                    gemb_stream_t stream);
+int32_t gemb_output_head_argmax(const void* candidates, uint64_t rows, uint32_t* selected,
+                                gemb_stream_t stream);
+
 /* ---- expert parallelism over peer memory (no counterpart in the reference, which is single-GPU) ----
  * R ranks, E experts, rank r owns experts [r*E/R, (r+1)*E/R).  Every rank leaves its quantised
  * assignments, one message row each (payload | compact block scales, padded to 16 bytes) in

@@ -74,6 +74,9 @@ class Oracle:
             L.orc_moe_permute.argtypes = [_i32p, C.c_uint64, C.c_uint64, C.c_uint64, _i32p, _i32p, _i32p]
             L.orc_moe_combine.argtypes = [_u16p, _f32p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64,
                                           _u16p]
+            L.orc_output_head.restype = C.c_int
+            L.orc_output_head.argtypes = [_u16p, _f32p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p, C.c_uint64,
+                                          _f32p, C.c_void_p, C.c_int]
 
     # ---- codecs ----
     def e2m1_decode(self, nib): return getattr(self.lib, self.p + "e2m1_decode")(nib)
@@ -207,6 +210,20 @@ class Oracle:
         if rc:
             raise ValueError("moe_permute: expert id out of range")
         return counts, offsets, perm
+
+    def output_head(self, weights_bf16, hidden_rows, suppressed=()):
+        """(capped logits [rows, vocabulary] fp32, selected [rows] uint32); weights as bf16 bits."""
+        w = np.ascontiguousarray(weights_bf16, np.uint16)
+        h = np.ascontiguousarray(hidden_rows, np.float32)
+        vocab, hidden = w.shape
+        rows = h.shape[0]
+        sup = np.ascontiguousarray(np.asarray(suppressed, np.uint32))
+        logits = np.zeros((rows, vocab), np.float32)
+        selected = np.zeros((rows,), np.uint32)
+        rc = self.lib.orc_output_head(w, h, rows, vocab, hidden, sup.ctypes.data if sup.size else None, sup.size, logits,
+                                      selected.ctypes.data, default_threads())
+        assert rc == 0
+        return logits, selected
 
     def moe_combine(self, y_slots_bf16, weights, shared_bf16):
         y = np.ascontiguousarray(y_slots_bf16, np.uint16)

@@ -17,6 +17,7 @@
 // Every function cites the reference file:line it follows.
 #include <algorithm>
 #include <atomic>
+#include <cfloat>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -493,6 +494,44 @@ void orc_moe_combine(const uint16_t* y_slots_bf16, const float* weights, const u
       if (shared_bf16) acc = acc + bf16_to_f32(shared_bf16[t * hidden + h]);
       out_bf16[t * hidden + h] = f32_to_bf16_rn(acc);
     }
+}
+
+// Output head.  src/cuda/output_head.cu:35-53 (logit: dot of bf16 weights with the fp32 hidden
+// vector, soft cap tanhf(sum / 30) * 30), :24-32 (suppression list), :88-96 and :337-376 (the
+// larger value wins, equal values go to the lower token id).  PARITY UNPINNED: the reference has
+// no test or golden vector for this operator and its only implementation is a CUDA kernel.  The
+// dot product is accumulated in binary64 (as the other projection oracles do) and rounded to
+// fp32 once; the reference's kernels accumulate in fp32 in kernel-specific orders.
+// logits: [rows][vocabulary] (may be null); selected: [rows].
+int orc_output_head(const uint16_t* weights_bf16, const float* hidden_rows, uint64_t rows, uint64_t vocabulary,
+                    uint64_t hidden, const uint32_t* suppressed, uint64_t suppressed_count, float* logits,
+                    uint32_t* selected, int threads) {
+  if (!weights_bf16 || !hidden_rows || !selected || rows == 0 || vocabulary == 0 || hidden == 0) return 1;
+  std::vector<float> capped(rows * vocabulary);
+  parallel_for(vocabulary, threads, [&](uint64_t v) {
+    for (uint64_t r = 0; r < rows; ++r) {
+      double acc = 0.0;
+      for (uint64_t k = 0; k < hidden; ++k)
+        acc += static_cast<double>(bf16_to_f32(weights_bf16[v * hidden + k])) * static_cast<double>(hidden_rows[r * hidden + k]);
+      capped[r * vocabulary + v] = std::tanh(static_cast<float>(acc) / 30.0f) * 30.0f;
+    }
+  });
+  for (uint64_t r = 0; r < rows; ++r) {
+    float best = -FLT_MAX;
+    uint32_t token = 0;
+    for (uint64_t v = 0; v < vocabulary; ++v) {
+      bool banned = false;
+      for (uint64_t i = 0; i < suppressed_count; ++i) banned |= suppressed[i] == v;
+      const float x = capped[r * vocabulary + v];
+      if (!banned && (x > best || (x == best && v < token))) {
+        best = x;
+        token = static_cast<uint32_t>(v);
+      }
+    }
+    selected[r] = token;
+  }
+  if (logits) std::copy(capped.begin(), capped.end(), logits);
+  return 0;
 }
 
 }  // extern "C"
