@@ -368,7 +368,7 @@ def run_decode_gemv(args):
         other = line["other_workloads"]
         for name, fn in (("nvfp4_linear", bench_nvfp4_linear), ("prefill_gemm", bench_prefill_gemm),
                          ("prefill_stack", bench_prefill_stack), ("moe_layer", bench_moe_layer),
-                         ("output_head", bench_output_head)):
+                         ("output_head", bench_output_head), ("verifier_gemv", bench_verifier_gemv)):
             try:
                 other[name] = fn(lib, dev)
             except Exception as exc:  # a secondary workload must not take the headline line down
@@ -612,6 +612,47 @@ def bench_output_head(lib, dev, vocab=262144, hidden=3840):
     return out
 
 
+def bench_verifier_gemv(lib, dev, sets=6):
+    """The decode projection set at the speculative-decoding verifier's batch sizes (3 and 5 tokens):
+    small-batch FP8 GEMV, fp32 out, weights streamed once per launch; `sets` distinct weight sets in
+    rotation (1.35 GB, far beyond L2)."""
+    import torch
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + 8000)
+    weights = []
+    for _ in range(sets):
+        mats = []
+        for _, rows, k in DECODE_SHAPES:
+            w = torch.randn((rows, k), device=dev, generator=gen) * 0.02
+            wq = torch.empty((rows, k), device=dev, dtype=torch.uint8)
+            wsc = torch.empty((rows,), device=dev)
+            lib.gemb_fp8_quantize(w, 0, wq, wsc, rows, k, None)
+            mats.append((wq, wsc.to(torch.bfloat16).view(torch.int16)))
+            del w
+        weights.append(mats)
+    peaks = measured_peaks()
+    out = {"metric": "verifier GEMV GB/s", "workload": "decode projection set at 3 and 5 tokens, FP8, fp32 out", "tokens": {}}
+    for tokens in (3, 5):
+        acts = []
+        for _, rows, k in DECODE_SHAPES:
+            x = torch.randn((tokens, k), device=dev, generator=gen)
+            xq = torch.empty((tokens, k), device=dev, dtype=torch.uint8)
+            xs = torch.empty((tokens,), device=dev)
+            lib.gemb_fp8_quantize(x, 0, xq, xs, tokens, k, None)
+            acts.append((xq, xs, torch.zeros((tokens, rows), device=dev)))
+
+        def step(st):
+            for mats in weights:
+                for (wq, ws), (xq, xs, y), (_, rows, k) in zip(mats, acts, DECODE_SHAPES):
+                    lib.gemb_fp8_gemv_batch(xq, xs, wq, ws, y, tokens, rows, k, st)
+
+        t = graph_time(step, sets * len(DECODE_SHAPES))
+        nbytes = sets * sum(r * k + 2 * r + tokens * (k + 4 * r) for _, r, k in DECODE_SHAPES)
+        out["tokens"][str(tokens)] = {"us_per_layer": t / sets * 1e6, "gbs": nbytes / t / 1e9,
+                                      "frac_of_measured_hbm_peak": nbytes / t / 1e9 / peaks["hbm_gbs"]}
+    return out
+
+
 def bench_tp_mlp(lib, dev, world, rank, tokens=16384):
     """Tensor-parallel 12B-like gated MLP (hidden 3840, intermediate 15360) on 16,384 tokens: gate/up
     column split, down row split with an fp32 all-reduce.  Collective; N = 1 runs it unsharded."""
@@ -773,7 +814,7 @@ def main():
     ap.add_argument("--no-other-workloads", action="store_true")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="decode layers held on the device (48 = the benchmark; fewer for a small profiler capture)")
-    ap.add_argument("--only", default=None, choices=["nvfp4_linear", "moe_layer", "prefill_gemm", "prefill_stack", "output_head"],
+    ap.add_argument("--only", default=None, choices=["nvfp4_linear", "moe_layer", "prefill_gemm", "prefill_stack", "output_head", "verifier_gemv"],
                     help="run just one secondary workload on one GPU and print its JSON (profiling aid)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -785,7 +826,8 @@ def main():
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(dev)
         fn = {"nvfp4_linear": bench_nvfp4_linear, "moe_layer": bench_moe_layer, "prefill_gemm": bench_prefill_gemm,
-              "prefill_stack": bench_prefill_stack, "output_head": bench_output_head}[args.only]
+              "prefill_stack": bench_prefill_stack, "output_head": bench_output_head,
+              "verifier_gemv": bench_verifier_gemv}[args.only]
         print(json.dumps(fn(load(), dev)), flush=True)
         return
     run_decode_gemv(args)

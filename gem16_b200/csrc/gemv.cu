@@ -356,6 +356,141 @@ int32_t launch_fp8_gemv_variant(const char* op, const void* act, const float* ac
 }
 
 // ---------------------------------------------------------------------------------------------
+// Small-batch FP8 GEMV (2..8 tokens): the speculative-decoding verifier's projections.  Same
+// stream over the weights as the single-token kernel -- the matrix is read once -- with kTok
+// staged activations and kTok accumulators per row; a tensor-core tile would be 97 % padding
+// at these sizes and the launch is bound by HBM either way.  Output fp32 [tokens, rows] per
+// problem, (acc * a_scale[t]) * w_scale in that order like the single-token kernel.
+// ---------------------------------------------------------------------------------------------
+template <int kTok>
+__global__ void __launch_bounds__(kWarps * 32)
+fp8_gemv_batch_kernel(const uint8_t* __restrict__ act, const float* __restrict__ act_scales,
+                      const __grid_constant__ Fp8Group grp, uint64_t k) {
+  constexpr int kUnroll = 8 / (kTok > 4 ? 2 : 1);   // 16-byte loads in flight per lane: 8, or 4 with many tokens (registers)
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __half* xs = reinterpret_cast<__half*>(smem_raw);   // [kTok][k padded to 512]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t k_pad = (k + 511) / 512 * 512;
+  const uint64_t total_rows = grp.row_start[grp.n];
+  const uint64_t task_stride = static_cast<uint64_t>(gridDim.x) * kWarps;
+  const uint64_t step = 512ull * kUnroll;
+  auto row_pointer = [&](uint64_t vrow) -> const uint8_t* {
+    if (vrow >= total_rows) vrow = total_rows - 1;
+    int pi = 0;
+    while (pi + 1 < grp.n && vrow >= grp.row_start[pi + 1]) ++pi;
+    return grp.p[pi].w + (vrow - grp.row_start[pi]) * k;
+  };
+  uint4 wv[kUnroll];
+  auto load_step = [&](uint64_t task, uint64_t kb) {
+    const uint8_t* wp = row_pointer(task) + kb + lane * 16;
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      wv[u] = kb + u * 512 + lane * 16 < k ? ldg_stream(wp + u * 512) : make_uint4(0, 0, 0, 0);
+  };
+  asm volatile("griddepcontrol.launch_dependents;");
+  uint64_t task = static_cast<uint64_t>(blockIdx.x) * kWarps + warp;
+  bool prefetched = false;
+  if (task < total_rows) {
+    load_step(task, 0);
+    prefetched = true;
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll 1
+  for (int t = 0; t < kTok; ++t) stage_fp8_activation<kWarps>(act + static_cast<uint64_t>(t) * k, k, xs + t * k_pad);
+  float a_scale[kTok];
+#pragma unroll
+  for (int t = 0; t < kTok; ++t) a_scale[t] = __ldg(act_scales + t);
+  __syncthreads();
+  for (; task < total_rows; task += task_stride) {
+    float acc[kTok];
+#pragma unroll
+    for (int t = 0; t < kTok; ++t) acc[t] = 0.0f;
+    for (uint64_t kb = 0; kb < k; kb += step) {
+      if (!prefetched) load_step(task, kb);
+      prefetched = false;
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (kb + u * 512 < k) {  // warp-uniform; lanes past K hold zero weights
+#pragma unroll
+          for (int t = 0; t < kTok; ++t) {
+            const __half* xp = xs + t * k_pad + kb + u * 512 + lane * 8;
+            const uint4 xa = *reinterpret_cast<const uint4*>(xp), xb = *reinterpret_cast<const uint4*>(xp + 256);
+            dot16_fp8(acc[t], wv[u], xa, xb);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < kTok; ++t) acc[t] = warp_sum(acc[t]);
+    if (lane == 0) {
+      int pi = 0;
+      while (pi + 1 < grp.n && task >= grp.row_start[pi + 1]) ++pi;
+      const uint64_t row = task - grp.row_start[pi];
+      const uint64_t rows = grp.p[pi].rows;
+      const float ws = bf16_bits_to_float(__ldg(grp.p[pi].w_scales + row));
+#pragma unroll
+      for (int t = 0; t < kTok; ++t)
+        static_cast<float*>(grp.p[pi].out)[static_cast<uint64_t>(t) * rows + row] = __fmul_rn(__fmul_rn(acc[t], a_scale[t]), ws);
+    }
+  }
+}
+
+template <int kTok>
+int32_t launch_fp8_gemv_batch_variant(const char* op, const uint8_t* act, const float* act_scales, const Fp8Group& grp,
+                                      uint64_t k, cudaStream_t stream) {
+  auto kern = fp8_gemv_batch_kernel<kTok>;
+  const size_t smem = static_cast<size_t>(kTok) * ((k + 511) / 512 * 512) * sizeof(__half);
+  static int resident[64] = {0};
+  static size_t resident_smem[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (resident[dev] == 0 || smem != resident_smem[dev]) {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+    }
+    int occ = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kWarps * 32, smem);
+    if (e != cudaSuccess || occ < 1) return fail(GEMB_INTERNAL, "%s: occupancy query failed: %s", op, cudaGetErrorName(e));
+    resident[dev] = occ;
+    resident_smem[dev] = smem;
+  }
+  const uint64_t tasks = grp.row_start[grp.n];
+  const uint64_t wave = static_cast<uint64_t>(sm_count()) * resident[dev];
+  const unsigned blocks = static_cast<unsigned>(std::min<uint64_t>((tasks + kWarps - 1) / kWarps, wave));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(kWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, kern, act, act_scales, grp, k);
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(le), cudaGetErrorString(le));
+  }
+  return check_launch(op);
+}
+
+int32_t launch_fp8_gemv_batch(const char* op, const uint8_t* act, const float* act_scales, const Fp8Group& grp,
+                              uint64_t tokens, uint64_t k, cudaStream_t stream) {
+  switch (tokens) {
+    case 2: return launch_fp8_gemv_batch_variant<2>(op, act, act_scales, grp, k, stream);
+    case 3: return launch_fp8_gemv_batch_variant<3>(op, act, act_scales, grp, k, stream);
+    case 4: return launch_fp8_gemv_batch_variant<4>(op, act, act_scales, grp, k, stream);
+    case 5: return launch_fp8_gemv_batch_variant<5>(op, act, act_scales, grp, k, stream);
+    case 6: return launch_fp8_gemv_batch_variant<6>(op, act, act_scales, grp, k, stream);
+    case 7: return launch_fp8_gemv_batch_variant<7>(op, act, act_scales, grp, k, stream);
+    default: return launch_fp8_gemv_batch_variant<8>(op, act, act_scales, grp, k, stream);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // FP8 GEMV with a bulk-copy ring.  One persistent CTA per SM: warp 0 is the producer, sixteen
 // consumer warps follow.  The weight matrix is cut into chunks of whole rows (about 16 KB); the
 // producer streams chunk after chunk into a ring of shared-memory stages with 1-D bulk copies
@@ -960,6 +1095,49 @@ int32_t gemb_fp8_gemv_qkv(const uint8_t* act, const float* act_scale, const uint
   grp.p[1] = {k_w, k_s, k_out, k_rows};
   if (has_v) grp.p[2] = {v_w, v_s, v_out, v_rows};
   return launch_fp8_gemv<false, false>(op, act, act_scale, grp, k, stream);
+}
+
+int32_t gemb_fp8_gemv_batch(const uint8_t* act, const float* act_scales, const uint8_t* w, const uint16_t* w_scales,
+                            float* out, uint64_t tokens, uint64_t rows, uint64_t k, gemb_stream_t stream) {
+  const char* op = "gemb_fp8_gemv_batch";
+  GEMB_REQUIRE(act_scales != nullptr, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_fp8_gemv(op, act, w, w_scales, out, rows, k));
+  GEMB_REQUIRE(tokens >= 1 && tokens <= 8, "%s: between 1 and 8 tokens (larger batches go through gemb_fp8_gemm_bf16)", op);
+  GEMB_REQUIRE(tokens * ((k + 511) / 512 * 512) * 2 <= 200 * 1024,
+               "%s: tokens * K exceeds the shared-memory staging limit (102400 elements)", op);
+  GEMB_TRY(require_sm100(op));
+  Fp8Group grp{};
+  grp.n = 1;
+  grp.p[0] = {w, w_scales, out, rows};
+  grp.row_start[1] = rows;
+  if (tokens == 1) return launch_fp8_gemv<false, false>(op, act, act_scales, grp, k, stream);
+  return launch_fp8_gemv_batch(op, act, act_scales, grp, tokens, k, stream);
+}
+
+int32_t gemb_fp8_gemv_qkv_batch(const uint8_t* act, const float* act_scales, const uint8_t* q_w, const uint16_t* q_s,
+                                float* q_out, uint64_t q_rows, const uint8_t* k_w, const uint16_t* k_s, float* k_out,
+                                uint64_t k_rows, const uint8_t* v_w, const uint16_t* v_s, float* v_out, uint64_t v_rows,
+                                uint64_t tokens, uint64_t k, gemb_stream_t stream) {
+  const char* op = "gemb_fp8_gemv_qkv_batch";
+  GEMB_REQUIRE(act_scales != nullptr, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_fp8_gemv(op, act, q_w, q_s, q_out, q_rows, k));
+  GEMB_TRY(validate_fp8_gemv(op, act, k_w, k_s, k_out, k_rows, k));
+  const bool has_v = v_w != nullptr || v_rows != 0;
+  if (has_v) GEMB_TRY(validate_fp8_gemv(op, act, v_w, v_s, v_out, v_rows, k));
+  GEMB_REQUIRE(tokens >= 1 && tokens <= 8, "%s: between 1 and 8 tokens", op);
+  GEMB_REQUIRE(tokens * ((k + 511) / 512 * 512) * 2 <= 200 * 1024,
+               "%s: tokens * K exceeds the shared-memory staging limit (102400 elements)", op);
+  GEMB_TRY(require_sm100(op));
+  Fp8Group grp{};
+  grp.n = has_v ? 3 : 2;
+  grp.p[0] = {q_w, q_s, q_out, q_rows};
+  grp.p[1] = {k_w, k_s, k_out, k_rows};
+  if (has_v) grp.p[2] = {v_w, v_s, v_out, v_rows};
+  grp.row_start[1] = q_rows;
+  grp.row_start[2] = q_rows + k_rows;
+  grp.row_start[3] = q_rows + k_rows + (has_v ? v_rows : 0);
+  if (tokens == 1) return launch_fp8_gemv<false, false>(op, act, act_scales, grp, k, stream);
+  return launch_fp8_gemv_batch(op, act, act_scales, grp, tokens, k, stream);
 }
 
 int32_t gemb_fp8_gemv_bf16in(const uint16_t* act_bf16, const uint8_t* w, const uint16_t* w_scales,

@@ -182,6 +182,25 @@ Status LaunchFp8Sm120GroupedQkvProjection(const std::uint8_t* act, const float* 
   return ToStatus(gemb_fp8_gemv_qkv(act, act_scale, q_weight, q_scales, q_output, q_rows, k_weight, k_scales,
                                     k_output, k_rows, v_weight, v_scales, v_output, v_rows, k, S(stream)));
 }
+// Small batches (the speculative-decoding verifier) stream the weights once like the T=1 kernel; the
+// reference's function also accepts prefill-sized batches, which belong to the GEMM (bf16 output).
+Status LaunchFp8Sm120DirectProjectionBatch(const std::uint8_t* act, const float* act_scales, const std::uint8_t* weight,
+                                           const std::uint16_t* weight_scales, float* output, std::uint64_t tokens,
+                                           std::uint64_t rows, std::uint64_t k, cudaStream_t stream) {
+  if (tokens > 8U) return Status(StatusCode::kUnsupported, "more than 8 tokens: use the prefill GEMM (bf16 output)");
+  return ToStatus(gemb_fp8_gemv_batch(act, act_scales, weight, weight_scales, output, tokens, rows, k, S(stream)));
+}
+Status LaunchFp8Sm120GroupedQkvProjectionBatch(const std::uint8_t* act, const float* act_scales,
+                                               const std::uint8_t* q_weight, const std::uint16_t* q_scales,
+                                               float* q_output, std::uint64_t q_rows, const std::uint8_t* k_weight,
+                                               const std::uint16_t* k_scales, float* k_output, std::uint64_t k_rows,
+                                               const std::uint8_t* v_weight, const std::uint16_t* v_scales,
+                                               float* v_output, std::uint64_t v_rows, std::uint64_t tokens,
+                                               std::uint64_t k, cudaStream_t stream) {
+  if (tokens > 8U) return Status(StatusCode::kUnsupported, "more than 8 tokens: use the prefill GEMM (bf16 output)");
+  return ToStatus(gemb_fp8_gemv_qkv_batch(act, act_scales, q_weight, q_scales, q_output, q_rows, k_weight, k_scales,
+                                          k_output, k_rows, v_weight, v_scales, v_output, v_rows, tokens, k, S(stream)));
+}
 Status LaunchFp8CutlassProjectionBatch(const std::uint8_t* act, const float* act_scales,
                                        const std::uint8_t* weight, const std::uint16_t* weight_scales,
                                        std::uint16_t* output, std::uint64_t tokens, std::uint64_t rows,

@@ -166,6 +166,24 @@ int32_t gemb_fp8_gemv_qkv(const uint8_t* activation_e4m3fn, const float* activat
                           const uint16_t* v_scales_bf16, float* v_output, uint64_t v_rows,
                           uint64_t contracting_elements, gemb_stream_t stream);
 
+/* Small-batch forms for the speculative-decoding verifier (second row of the path's "next" list):
+ * 1..8 tokens share one pass over the weights.  activation [tokens, K] E4M3, activation_scales
+ * [tokens], output fp32 [tokens, rows] (per projection for the grouped form).  Per token the result
+ * is bit-identical to gemb_fp8_gemv on that token.  tokens * K (K padded to 512) <= 102,400.
+ * Replace LaunchFp8Sm120DirectProjectionBatch and LaunchFp8Sm120GroupedQkvProjectionBatch
+ * (src/cuda/fp8/sm120.h:45-79) for tokens <= 8; larger batches are prefill and belong to
+ * gemb_fp8_gemm_bf16. */
+int32_t gemb_fp8_gemv_batch(const uint8_t* activation_e4m3fn, const float* activation_scales,
+                            const uint8_t* weight_e4m3fn, const uint16_t* weight_scales_bf16,
+                            float* output, uint64_t tokens, uint64_t rows,
+                            uint64_t contracting_elements, gemb_stream_t stream);
+int32_t gemb_fp8_gemv_qkv_batch(const uint8_t* activation_e4m3fn, const float* activation_scales,
+                                const uint8_t* q_weight, const uint16_t* q_scales_bf16, float* q_output,
+                                uint64_t q_rows, const uint8_t* k_weight, const uint16_t* k_scales_bf16,
+                                float* k_output, uint64_t k_rows, const uint8_t* v_weight,
+                                const uint16_t* v_scales_bf16, float* v_output, uint64_t v_rows,
+                                uint64_t tokens, uint64_t contracting_elements, gemb_stream_t stream);
+
 /* Per-token FP8 quantization of a bf16 vector fused into the GEMV (each CTA re-derives the
  * token scale and bytes; results are bit-identical to gemb_fp8_quantize + gemb_fp8_gemv).
  * Fuses the decode pair at src/cuda/engine/inference_engine_decode_graphs.cuh:287-290.

@@ -154,3 +154,50 @@ def test_fused_quantisation_at_rounding_boundaries(lib, dev, orc):
     lib.gemb_fp8_gemv(to_dev(xq2, dev), to_dev(xsc2, dev), to_dev(wq, dev), to_dev(wsb, dev), y_plain, rows, k, None)
     lib.gemb_fp8_gemv_bf16in(to_dev(bf16_bits(x2), dev), to_dev(wq, dev), to_dev(wsb, dev), y_fused, 0, rows, k, None)
     assert torch.equal(y_plain, y_fused)
+
+
+@pytest.mark.parametrize("tokens,rows,k", [(2, 40, 528), (3, 8192, 3840), (5, 3840, 15360), (8, 1000, 4096), (7, 13, 16)])
+def test_fp8_gemv_small_batch(lib, dev, orc, tokens, rows, k):
+    """The verifier-sized batch (src/cuda/fp8/sm120.h:45-55): one pass over the weights for all tokens,
+    every token bit-identical to the single-token GEMV on it, and within the GEMV budget of the
+    binary64 oracle."""
+    rng = np.random.default_rng(tokens * 1000 + rows)
+    x = bf16_round(rng.standard_normal((tokens, k)).astype(np.float32) * np.arange(1, tokens + 1, dtype=np.float32)[:, None])
+    w = (rng.standard_normal((rows, k)) * 0.02).astype(np.float32)
+    wq, wsc = orc.fp8_quantize(w)
+    wsb = bf16_bits(wsc)
+    xq, xsc = orc.fp8_quantize(x)
+    want = orc.fp8_matmul(xq, xsc, wq, wsb)
+    out = torch.full((tokens, rows), float("nan"), device=dev)
+    xd, sd, wd, wsd = to_dev(xq, dev), to_dev(xsc, dev), to_dev(wq, dev), to_dev(wsb, dev)
+    lib.gemb_fp8_gemv_batch(xd, sd, wd, wsd, out, tokens, rows, k, None)
+    got = to_np(out)
+    assert rel_fro(got, want) < 1e-6
+    for t in range(tokens):
+        one = torch.zeros((rows,), device=dev)
+        lib.gemb_fp8_gemv(xd[t], sd[t:t + 1], wd, wsd, one, rows, k, None)
+        assert np.array_equal(to_np(one), got[t]), t
+
+
+def test_fp8_gemv_small_batch_grouped_and_limits(lib, dev, orc):
+    from gem16_b200.lib import GembError
+    tokens, k = 3, 3840
+    rng = np.random.default_rng(5)
+    x = bf16_round(rng.standard_normal((tokens, k)).astype(np.float32))
+    xq, xsc = orc.fp8_quantize(x)
+    mats = [make_fp8_problem(orc, r, k, 200 + r)[3:] for r in (4096, 2048, 2048)]
+    outs = [torch.full((tokens, r), float("nan"), device=dev) for r in (4096, 2048, 2048)]
+    d = [(to_dev(w, dev), to_dev(s, dev)) for w, s in mats]
+    xd, sd = to_dev(xq, dev), to_dev(xsc, dev)
+    lib.gemb_fp8_gemv_qkv_batch(xd, sd, d[0][0], d[0][1], outs[0], 4096, d[1][0], d[1][1], outs[1], 2048, d[2][0], d[2][1],
+                                outs[2], 2048, tokens, k, None)
+    for (w, s), o in zip(mats, outs):
+        assert rel_fro(to_np(o), orc.fp8_matmul(xq, xsc, w, s)) < 1e-6
+    o0, o1 = torch.zeros((tokens, 4096), device=dev), torch.zeros((tokens, 2048), device=dev)
+    lib.gemb_fp8_gemv_qkv_batch(xd, sd, d[0][0], d[0][1], o0, 4096, d[1][0], d[1][1], o1, 2048, None, None, None, 0,
+                                tokens, k, None)
+    assert torch.equal(o0, outs[0]) and torch.equal(o1, outs[1])
+    with pytest.raises(GembError):
+        lib.gemb_fp8_gemv_batch(xd, sd, d[0][0], d[0][1], o0, 9, 4096, k, None)          # more than 8 tokens
+    with pytest.raises(GembError):
+        lib.gemb_fp8_gemv_batch(xd, sd, d[0][0], d[0][1], o0, 8, 4096, 15360, None)      # 8 x 15360 does not fit
