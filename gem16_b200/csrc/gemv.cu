@@ -916,6 +916,82 @@ nvfp4_gemv_kernel(const uint8_t* __restrict__ act, const uint8_t* __restrict__ a
   }
 }
 
+// Small-batch NVFP4 GEMV (2..8 tokens, the verifier's MLP projections): the weight chunk is
+// converted to fp16 once and meets kTok staged activations; per token the arithmetic and its
+// order are those of the single-token kernel, so each token's result is bit-identical to it.
+template <int kTok>
+__global__ void __launch_bounds__(kThreads)
+nvfp4_gemv_batch_kernel(const uint8_t* __restrict__ act, const uint8_t* __restrict__ act_scales,
+                        const uint8_t* __restrict__ w, const uint8_t* __restrict__ ws, float* __restrict__ out,
+                        uint64_t rows, uint64_t k, float div) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const uint64_t k_pad = (k + 1023) / 1024 * 1024;
+  const uint64_t tok_bytes = k_pad * 2 + (k / 16) * 4;   // staged fp16 values, then fp32 block scales
+  for (int t = 0; t < kTok; ++t) {
+    __half* xs = reinterpret_cast<__half*>(smem_raw + t * tok_bytes);
+    float* sa = reinterpret_cast<float*>(smem_raw + t * tok_bytes + k_pad * 2);
+    const uint8_t* a = act + static_cast<uint64_t>(t) * (k / 2);
+    for (uint64_t c = threadIdx.x; c < k / 32; c += kThreads) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(a) + c);  // 32 elements
+      const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+      __half* dst = xs + (c / 32) * 1024 + (c % 32) * 8;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t h[4];
+        e2m1x8_to_half2(ww[i], h);
+        *reinterpret_cast<uint4*>(dst + i * 256) = make_uint4(h[0], h[1], h[2], h[3]);
+      }
+    }
+    for (uint64_t c = threadIdx.x; c < k / 16; c += kThreads)
+      sa[c] = e4m3_decode(__ldg(act_scales + static_cast<uint64_t>(t) * (k / 16) + c));
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t row = static_cast<uint64_t>(blockIdx.x) * kWarps + warp;
+  if (row >= rows) return;
+  const uint64_t row_bytes = k / 2, srow_bytes = k / 16;
+  float acc[kTok];
+#pragma unroll
+  for (int t = 0; t < kTok; ++t) acc[t] = 0.0f;
+  for (uint64_t kb = lane * 16ull; kb < row_bytes; kb += 512) {
+    const uint4 wv = ldg_stream(w + row * row_bytes + kb);
+    const uint16_t sv = __ldg(reinterpret_cast<const uint16_t*>(ws + row * srow_bytes + kb / 8));
+    const float sw0 = e4m3_decode(static_cast<uint8_t>(sv & 0xFF)), sw1 = e4m3_decode(static_cast<uint8_t>(sv >> 8));
+#pragma unroll
+    for (int t = 0; t < kTok; ++t) {
+      const __half* xp = reinterpret_cast<const __half*>(smem_raw + t * tok_bytes) + (kb / 512) * 1024 + lane * 8;
+      const float* sa = reinterpret_cast<const float*>(smem_raw + t * tok_bytes + k_pad * 2);
+      const uint4 x0 = *reinterpret_cast<const uint4*>(xp), x1 = *reinterpret_cast<const uint4*>(xp + 256),
+                  x2 = *reinterpret_cast<const uint4*>(xp + 512), x3 = *reinterpret_cast<const uint4*>(xp + 768);
+      const float d0 = block_dot_fp4(wv.x, wv.y, x0, x1);
+      const float d1 = block_dot_fp4(wv.z, wv.w, x2, x3);
+      acc[t] = fmaf(d0, sa[kb / 8] * sw0, acc[t]);
+      acc[t] = fmaf(d1, sa[kb / 8 + 1] * sw1, acc[t]);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kTok; ++t) acc[t] = warp_sum(acc[t]);
+  if (lane == 0) {
+#pragma unroll
+    for (int t = 0; t < kTok; ++t) out[static_cast<uint64_t>(t) * rows + row] = __fdiv_rn(acc[t], div);
+  }
+}
+
+template <int kTok>
+int32_t launch_nvfp4_gemv_batch_variant(const char* op, const uint8_t* act, const uint8_t* act_scales, const uint8_t* w,
+                                        const uint8_t* ws, float* out, uint64_t rows, uint64_t k, float div,
+                                        cudaStream_t stream) {
+  auto kern = nvfp4_gemv_batch_kernel<kTok>;
+  const size_t smem = static_cast<size_t>(kTok) * ((k + 1023) / 1024 * 1024 * 2 + (k / 16) * 4);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+  }
+  const unsigned blocks = static_cast<unsigned>((rows + kWarps - 1) / kWarps);
+  kern<<<blocks, kThreads, smem, stream>>>(act, act_scales, w, ws, out, rows, k, div);
+  return check_launch(op);
+}
+
 template <bool kGateUp>
 int32_t launch_nvfp4_gemv(const char* op, const uint8_t* act, const uint8_t* act_scales,
                           const uint8_t* w0, const uint8_t* ws0, const uint8_t* w1,
@@ -1166,6 +1242,33 @@ int32_t gemb_nvfp4_gemv(const uint8_t* act, const uint8_t* act_scales, const uin
   GEMB_TRY(require_sm100(op));
   return launch_nvfp4_gemv<false>(op, act, act_scales, w, w_scales, nullptr, nullptr, out, nullptr,
                                   nullptr, rows, k, ga * gw, 1.0f, stream);
+}
+
+int32_t gemb_nvfp4_gemv_batch(const uint8_t* act, const uint8_t* act_scales, const uint8_t* w, const uint8_t* w_scales,
+                              float* out, uint64_t tokens, uint64_t rows, uint64_t k, float ga, float gw,
+                              gemb_stream_t stream) {
+  const char* op = "gemb_nvfp4_gemv_batch";
+  GEMB_REQUIRE(act && act_scales && w && w_scales && out, "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_nvfp4_gemv(op, rows, k, ga, gw));
+  GEMB_REQUIRE(tokens >= 1 && tokens <= 8, "%s: between 1 and 8 tokens (larger batches go through gemb_nvfp4_gemm_bf16)", op);
+  GEMB_REQUIRE(tokens * ((k + 1023) / 1024 * 1024 * 2 + (k / 16) * 4) <= 200 * 1024,
+               "%s: tokens * K exceeds the shared-memory staging limit", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(w_scales) % 2 == 0,
+               "%s: activation and weight must be 16-byte aligned, weight scales 2-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  const float div = ga * gw;
+  switch (tokens) {
+    case 1: return launch_nvfp4_gemv<false>(op, act, act_scales, w, w_scales, nullptr, nullptr, out, nullptr, nullptr, rows,
+                                            k, div, 1.0f, stream);
+    case 2: return launch_nvfp4_gemv_batch_variant<2>(op, act, act_scales, w, w_scales, out, rows, k, div, stream);
+    case 3: return launch_nvfp4_gemv_batch_variant<3>(op, act, act_scales, w, w_scales, out, rows, k, div, stream);
+    case 4: return launch_nvfp4_gemv_batch_variant<4>(op, act, act_scales, w, w_scales, out, rows, k, div, stream);
+    case 5: return launch_nvfp4_gemv_batch_variant<5>(op, act, act_scales, w, w_scales, out, rows, k, div, stream);
+    case 6: return launch_nvfp4_gemv_batch_variant<6>(op, act, act_scales, w, w_scales, out, rows, k, div, stream);
+    case 7: return launch_nvfp4_gemv_batch_variant<7>(op, act, act_scales, w, w_scales, out, rows, k, div, stream);
+    default: return launch_nvfp4_gemv_batch_variant<8>(op, act, act_scales, w, w_scales, out, rows, k, div, stream);
+  }
 }
 
 int32_t gemb_nvfp4_gemv_gate_up(const uint8_t* act, const uint8_t* act_scales, const uint8_t* gate_w,

@@ -104,6 +104,14 @@ Status LaunchNvfp4Sm120FusedGateUp(const std::uint8_t* act, const std::uint8_t* 
                                           gate_output, up_output, product_output, rows, k, gate_ga, gate_gw,
                                           up_ga, up_gw, S(stream)));
 }
+// fp32-output batch form: the verifier's 3 or 5 tokens stream the weights once like the T=1 kernel.
+Status LaunchNvfp4Sm120DirectProjectionBatch(const std::uint8_t* act, const std::uint8_t* act_scales,
+                                             const std::uint8_t* weight, const std::uint8_t* weight_scales, float* output,
+                                             std::uint64_t tokens, std::uint64_t rows, std::uint64_t k, float ga, float gw,
+                                             cudaStream_t stream) {
+  if (tokens > 8U) return Status(StatusCode::kUnsupported, "more than 8 tokens: use the prefill GEMM (bf16 output)");
+  return ToStatus(gemb_nvfp4_gemv_batch(act, act_scales, weight, weight_scales, output, tokens, rows, k, ga, gw, S(stream)));
+}
 Status LaunchNvfp4Sm120DirectProjectionBf16Batch(const std::uint8_t* act, const std::uint8_t* act_scales_interleaved,
                                                  const std::uint8_t* weight,
                                                  const std::uint8_t* weight_scales_interleaved,

@@ -202,6 +202,16 @@ int32_t gemb_nvfp4_gemv(const uint8_t* packed_activation_e2m1, const uint8_t* ac
                         float activation_global_divisor, float weight_global_divisor,
                         gemb_stream_t stream);
 
+/* Small-batch form (1..8 tokens, the verifier's MLP projections): activation [tokens, K/2] with
+ * COMPACT scales [tokens, K/16], output fp32 [tokens, rows]; per token bit-identical to
+ * gemb_nvfp4_gemv.  Replaces LaunchNvfp4Sm120DirectProjectionBatch (src/cuda/nvfp4/sm120.h:26-37)
+ * for tokens <= 8; larger batches are prefill and belong to gemb_nvfp4_gemm_bf16. */
+int32_t gemb_nvfp4_gemv_batch(const uint8_t* packed_activation_e2m1, const uint8_t* activation_scales,
+                              const uint8_t* packed_weight_e2m1, const uint8_t* weight_scales,
+                              float* output, uint64_t tokens, uint64_t rows,
+                              uint64_t contracting_elements, float activation_global_divisor,
+                              float weight_global_divisor, gemb_stream_t stream);
+
 /* Gate and Up in one launch with the bf16 boundaries and the GELU-tanh product in the epilogue;
  * gate_output / up_output may be null.
  * Replaces LaunchNvfp4Sm120FusedGateUp, src/cuda/nvfp4/sm120.h:58-74. */

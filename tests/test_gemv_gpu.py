@@ -201,3 +201,29 @@ def test_fp8_gemv_small_batch_grouped_and_limits(lib, dev, orc):
         lib.gemb_fp8_gemv_batch(xd, sd, d[0][0], d[0][1], o0, 9, 4096, k, None)          # more than 8 tokens
     with pytest.raises(GembError):
         lib.gemb_fp8_gemv_batch(xd, sd, d[0][0], d[0][1], o0, 8, 4096, 15360, None)      # 8 x 15360 does not fit
+
+
+@pytest.mark.parametrize("tokens,rows,k", [(2, 8, 64), (3, 3840, 15360), (5, 15360, 3840), (8, 1000, 4096)])
+def test_nvfp4_gemv_small_batch(lib, dev, orc, tokens, rows, k):
+    """src/cuda/nvfp4/sm120.h:26-37 at verifier batch sizes: one pass over the weights, every token
+    bit-identical to the single-token GEMV and within its budget of the binary64 oracle."""
+    rng = np.random.default_rng(tokens * 7 + rows)
+    x = bf16_round(rng.standard_normal((tokens, k)).astype(np.float32))
+    ga = nvfp4_divisor(x)
+    xp, xs = orc.nvfp4_quantize(x, ga)
+    w = (rng.standard_normal((rows, k)) * 0.02).astype(np.float32)
+    gw = nvfp4_divisor(w)
+    wp, ws = orc.nvfp4_quantize(w, gw)
+    want = orc.nvfp4_matmul(xp, xs, wp, ws, ga, gw)
+    d = [to_dev(a, dev) for a in (xp, xs, wp, ws)]
+    out = torch.full((tokens, rows), float("nan"), device=dev)
+    lib.gemb_nvfp4_gemv_batch(d[0], d[1], d[2], d[3], out, tokens, rows, k, ga, gw, None)
+    got = to_np(out)
+    assert rel_fro(got, want) < 1e-6
+    for t in range(tokens):
+        one = torch.zeros((rows,), device=dev)
+        lib.gemb_nvfp4_gemv(d[0][t], d[1][t], d[2], d[3], one, rows, k, ga, gw, None)
+        assert np.array_equal(to_np(one), got[t]), t
+    from gem16_b200.lib import GembError
+    with pytest.raises(GembError):
+        lib.gemb_nvfp4_gemv_batch(d[0], d[1], d[2], d[3], out, 9, rows, k, ga, gw, None)
