@@ -126,6 +126,48 @@ ep_plan_kernel(const int32_t* __restrict__ counts_all, uint32_t ranks, uint32_t 
   }
 }
 
+// Cross-GPU barrier on flags in peer-mapped memory: every rank bumps its own epoch for barrier
+// `which`, publishes it to slot [which][rank] of every rank's flag array (release, system scope)
+// and waits until all slots of its own array have reached that epoch (acquire).  The kernels
+// before it in the stream have completed, so their writes are in this GPU's memory before the flag
+// leaves; a peer that has seen the flag may read them over NVLink.  The epoch lives on the device,
+// so a captured launch stays valid when replayed.  The wait is bounded: on expiry the kernel
+// records the fact and returns (the launches that follow then work on stale data and the caller
+// sees the error at its next gemb_check_device_status()).
+// One warp; the ranks run on different GPUs (never several ranks of one barrier on the same GPU).
+__global__ void __launch_bounds__(32)
+ep_barrier_kernel(PeerPtrs flag_arrays, uint32_t ranks, uint32_t me, uint32_t which, uint32_t* __restrict__ epochs) {
+  const uint32_t lane = threadIdx.x;
+  uint32_t e = 0;
+  if (lane == 0) {
+    e = epochs[which] + 1;
+    epochs[which] = e;
+  }
+  e = __shfl_sync(0xFFFFFFFFu, e, 0);
+  if (lane < ranks) {
+    uint32_t* theirs = reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(flag_arrays.p[lane])) + which * kMaxRanks + me;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(e) : "memory");
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(flag_arrays.p[me]) + which * kMaxRanks + lane;
+    bool ok = false;
+    for (uint32_t i = 0; i < (1u << 22) && !ok; ++i) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      ok = static_cast<int32_t>(v - e) >= 0;   // epochs only grow; a peer may already be one barrier ahead
+      if (!ok && i > 64) __nanosleep(500);   // about three seconds in all
+    }
+    if (!ok) atomicCAS(&g_ep_error, 0, 5);
+  }
+}
+
+// counts_all[s][e] = the per-expert counts rank s left in its peer-mapped buffer.
+__global__ void __launch_bounds__(256)
+ep_gather_counts_kernel(PeerPtrs count_buffers, uint32_t ranks, uint32_t experts, int32_t* __restrict__ counts_all) {
+  for (uint32_t i = threadIdx.x; i < ranks * experts; i += blockDim.x) {
+    const uint32_t s = i / experts, e = i % experts;
+    counts_all[i] = *(reinterpret_cast<const volatile int32_t*>(count_buffers.p[s]) + e);
+  }
+}
+
 // Persistent grid, one warp per received row: copies the E2M1 payload into the padded row space and
 // the compact block scales into the interleaved layout.
 __global__ void __launch_bounds__(256)
@@ -255,6 +297,29 @@ int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t exp
   ep_plan_kernel<<<1, 256, 4 * experts * sizeof(int), stream>>>(
       counts_all, static_cast<uint32_t>(ranks), static_cast<uint32_t>(experts), static_cast<uint32_t>(rank), plan,
       recv_prefix, recv_src_rows, recv_dst_rows, combine_row_base);
+  return check_launch(op);
+}
+
+int32_t gemb_moe_ep_barrier(const uint64_t* peer_flag_arrays, uint64_t ranks, uint64_t rank, uint64_t which,
+                            uint32_t* local_epochs, gemb_stream_t stream) {
+  const char* op = "gemb_moe_ep_barrier";
+  PeerPtrs peers;
+  GEMB_TRY(load_peers(op, peer_flag_arrays, ranks, &peers));
+  GEMB_REQUIRE(rank < ranks && which < 2 && local_epochs != nullptr, "%s: bad rank, barrier index or epoch pointer", op);
+  GEMB_TRY(require_sm100(op));
+  ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, static_cast<uint32_t>(ranks), static_cast<uint32_t>(rank),
+                                          static_cast<uint32_t>(which), local_epochs);
+  return check_launch(op);
+}
+
+int32_t gemb_moe_ep_gather_counts(const uint64_t* peer_count_buffers, uint64_t ranks, uint64_t experts,
+                                  int32_t* counts_all, gemb_stream_t stream) {
+  const char* op = "gemb_moe_ep_gather_counts";
+  PeerPtrs peers;
+  GEMB_TRY(load_peers(op, peer_count_buffers, ranks, &peers));
+  GEMB_REQUIRE(counts_all != nullptr && experts >= 1 && experts <= kMaxExperts, "%s: bad arguments", op);
+  GEMB_TRY(require_sm100(op));
+  ep_gather_counts_kernel<<<1, 256, 0, stream>>>(peers, static_cast<uint32_t>(ranks), static_cast<uint32_t>(experts), counts_all);
   return check_launch(op);
 }
 

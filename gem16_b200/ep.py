@@ -141,15 +141,17 @@ class EpPullMoeLayer:
     pulls its expert outputs back inside the combine.  All row positions are arithmetic on the
     all-gathered counts, so nothing is read back to the host and the launch sequence is fixed.
 
-    Ordering between GPUs comes from two tiny NCCL collectives per layer: the all-gather of the
-    counts is issued after the send buffer is filled ("send buffers complete"), a one-element
-    all-reduce after the expert GEMMs ("expert outputs complete").  They also make buffer reuse
-    safe: a rank refills its send buffer only after the second collective of the previous layer
-    (every peer has pulled), and overwrites its expert outputs only after the first collective of
-    the next layer (every peer has combined)."""
+    Ordering between GPUs comes from two barriers per layer: one after the send buffer and the
+    counts are written ("send buffers complete"), one after the expert GEMMs ("expert outputs
+    complete").  With sync="flags" (default) they are the library's own flag barrier over peer memory
+    and the counts are read from the peers' buffers; with sync="nccl" the first is the all-gather of
+    the counts and the second a one-element all-reduce.  The barriers also make buffer reuse safe:
+    a rank refills its send buffer only after the second barrier of the previous layer (every peer
+    has pulled), and overwrites its expert outputs only after the first barrier of the next layer
+    (every peer has combined)."""
 
     def __init__(self, weights: MoeWeights, tokens: int, topk: int, ga: float, ga_dn: float, ga_sh_dn: float,
-                 group=None, how: str = "auto", emulate=None):
+                 group=None, how: str = "auto", emulate=None, sync: str = "flags"):
         """emulate=(rank, world): no process group; the caller runs every rank's stages in turn on one
         GPU and wires the buffer tables together with `connect` (single-GPU test of the protocol)."""
         from .peer import PeerBuffer, LocalBuffer
@@ -194,6 +196,14 @@ class EpPullMoeLayer:
         self.p_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, i),), **u8)
         self.flag = torch.zeros((1,), device=dev)
         self.side = torch.cuda.Stream(device=dev)
+        self.sync = "host" if self.emulated else sync
+        if self.sync == "flags":
+            # the per-expert counts where the peers can read them, and the barrier's flag words
+            self.counts_peer = PeerBuffer(self.e_total * 4, dev, group, how)
+            self.flags_peer = PeerBuffer(2 * 16 * 4, dev, group, how)
+            self.local.counts = self.counts_peer.local.view(torch.int32)
+            self.epochs = torch.zeros((2,), **i32)
+            dist.barrier(group)   # every rank's flag words are zero before the first barrier kernel runs
 
     @staticmethod
     def connect(layers):
@@ -250,6 +260,13 @@ class EpPullMoeLayer:
 
     def forward(self, x_bf16):
         self.stage_send(x_bf16)
+        if self.sync == "flags":
+            lib, main = self.lib, torch.cuda.current_stream()
+            lib.gemb_moe_ep_barrier(self.flags_peer.table, self.world, self.rank, 0, self.epochs, main)
+            lib.gemb_moe_ep_gather_counts(self.counts_peer.table, self.world, self.e_total, self.counts_all, main)
+            self.stage_experts()
+            lib.gemb_moe_ep_barrier(self.flags_peer.table, self.world, self.rank, 1, self.epochs, main)
+            return self.stage_combine()
         # counts of every rank -- and: every send buffer is complete
         dist.all_gather_into_tensor(self.counts_all.view(-1), self.local.counts, group=self.group)
         self.stage_experts()

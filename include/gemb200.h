@@ -469,6 +469,18 @@ int32_t gemb_output_head_argmax(const void* candidates, uint64_t rows, uint32_t*
  * send_rows_per_rank / padded_rows_max are the capacities of the send and of the padded buffers: a
  * position outside them (counts that are not what the protocol promises) is skipped and recorded,
  * and gemb_check_device_status() then reports it, instead of the access faulting. */
+/* Ordering between the GPUs without a collective library.  gemb_moe_ep_barrier: rank `rank` bumps
+ * its device-resident epoch for barrier `which` (0 or 1; local_epochs holds two words, zero at
+ * start), stores it to slot [which][rank] of every rank's flag array (peer_flag_arrays: R device
+ * addresses of 2 x 16 zero-initialised words) and waits, for a bounded time, until every slot of its
+ * own array has reached the epoch.  Everything earlier in the stream is then visible to peers that
+ * pass their own barrier.  Each rank must run on its own GPU.  gemb_moe_ep_gather_counts copies
+ * every rank's per-expert counts (peer_count_buffers: R device addresses of E int32) into
+ * counts_all [R][E] -- the input of gemb_moe_ep_plan -- after such a barrier. */
+int32_t gemb_moe_ep_barrier(const uint64_t* peer_flag_arrays, uint64_t ranks, uint64_t rank, uint64_t which,
+                            uint32_t* local_epochs, gemb_stream_t stream);
+int32_t gemb_moe_ep_gather_counts(const uint64_t* peer_count_buffers, uint64_t ranks, uint64_t experts,
+                                  int32_t* counts_all, gemb_stream_t stream);
 uint64_t gemb_moe_ep_plan_ints(uint64_t capacity_rows, uint64_t local_experts);
 int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t experts, uint64_t rank,
                          int32_t* plan, int32_t* recv_prefix, int32_t* recv_src_rows,

@@ -44,15 +44,17 @@ def main():
         assert torch.equal(ep.local.weights, ref.weights[sl]), "routing weights differ"
         assert torch.equal(ep.counts_all.sum(0).to(torch.int32), ref.counts), "global counts differ"
         assert torch.equal(out, ref_out[sl]), "expert-parallel output differs from the single-GPU layer"
-    # the same layer with the exchange done by the library's own kernels over peer memory
-    pull = EpPullMoeLayer(mine, tokens, topk, ga, ga_dn, ga_sh)
-    for _ in range(3):     # three times: send and output buffers are reused without a host sync in between
-        out = pull.forward(x_all[sl].contiguous().view(torch.int16))
-    torch.cuda.synchronize()
-    lib.gemb_check_device_status()
-    assert torch.equal(pull.counts_all.sum(0).to(torch.int32), ref.counts), "global counts differ (peer path)"
-    assert int(pull.recv_prefix[-1].item()) == ep.last["n_recv"], "received row count differs (peer path)"
-    assert torch.equal(out, ref_out[sl]), "peer-memory expert-parallel output differs from the single-GPU layer"
+    # the same layer with the exchange done by the library's own kernels over peer memory, ordered
+    # by the library's flag barrier and by NCCL collectives
+    for sync in ("flags", "nccl"):
+        pull = EpPullMoeLayer(mine, tokens, topk, ga, ga_dn, ga_sh, sync=sync)
+        for _ in range(3):     # three times: send and output buffers are reused without a host sync in between
+            out = pull.forward(x_all[sl].contiguous().view(torch.int16))
+        torch.cuda.synchronize()
+        lib.gemb_check_device_status()
+        assert torch.equal(pull.counts_all.sum(0).to(torch.int32), ref.counts), f"global counts differ (peer path, {sync})"
+        assert int(pull.recv_prefix[-1].item()) == ep.last["n_recv"], f"received row count differs (peer path, {sync})"
+        assert torch.equal(out, ref_out[sl]), f"peer-memory expert-parallel output differs from the single-GPU layer ({sync})"
     dist.barrier()
     print(f"rank {rank} ok n_recv={ep.last['n_recv']} peer={pull.send.how}", flush=True)
     dist.destroy_process_group()

@@ -118,3 +118,29 @@ def test_pull_dispatch_skips_rows_outside_the_buffers(lib, dev):
         lib.gemb_check_device_status()
     assert int(packed[:2].min().item()) == 7 and int(packed[2:].max().item()) == 0   # in-range rows copied, the rest skipped
     lib.gemb_check_device_status()              # the record is cleared once read
+
+
+def test_flag_barrier_and_count_gather_single_rank(lib, dev):
+    """One rank: the barrier publishes and observes its own epoch (several times: the epoch lives on the
+    device), and the count gather copies the rank's counts.  The multi-rank form runs in
+    tests/test_ep_gpu.py, one rank per GPU."""
+    import ctypes as C
+    flags = torch.zeros((32,), dtype=torch.int32, device=dev)
+    epochs = torch.zeros((2,), dtype=torch.int32, device=dev)
+    table = (C.c_uint64 * 1)(flags.data_ptr())
+    for _ in range(3):
+        lib.gemb_moe_ep_barrier(table, 1, 0, 0, epochs, None)
+    lib.gemb_moe_ep_barrier(table, 1, 0, 1, epochs, None)
+    torch.cuda.synchronize()
+    lib.gemb_check_device_status()
+    assert epochs.tolist() == [3, 1] and int(flags[0]) == 3 and int(flags[16]) == 1
+    counts = torch.arange(128, dtype=torch.int32, device=dev)
+    out = torch.zeros((1, 128), dtype=torch.int32, device=dev)
+    lib.gemb_moe_ep_gather_counts((C.c_uint64 * 1)(counts.data_ptr()), 1, 128, out, None)
+    torch.cuda.synchronize()
+    assert torch.equal(out[0], counts)
+    from gem16_b200.lib import GembError
+    with pytest.raises(GembError):
+        lib.gemb_moe_ep_barrier(table, 1, 0, 2, epochs, None)      # only barriers 0 and 1 exist
+    with pytest.raises(GembError):
+        lib.gemb_moe_ep_barrier(table, 1, 1, 0, epochs, None)      # rank out of range
