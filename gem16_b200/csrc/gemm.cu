@@ -97,7 +97,7 @@ struct Cfg {
   static constexpr int kSfaBytes = kFp4 ? 2048 : 0;        // 4 chunks of 512 B
   static constexpr int kSfbBytes = kFp4 ? kSfbGroups * 2048 : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kEpiBytes = 4 * 2 * 4096;          // 4 warps x 2 buffers x (32 rows x 128 B)
+  static constexpr int kEpiBytes = 8 * 4096;               // eight epilogue warps x one staging buffer (32 rows x 128 B)
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarrierBytes + 1024;  // + alignment slack
   // TMEM columns: accumulators first, then one scale region per shared-memory stage.  A stage's
