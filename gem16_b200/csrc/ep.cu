@@ -300,11 +300,11 @@ int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t exp
   return check_launch(op);
 }
 
-int32_t gemb_moe_ep_barrier(const uint64_t* peer_flag_arrays, uint64_t ranks, uint64_t rank, uint64_t which,
+int32_t gemb_moe_ep_barrier(const uint64_t* peer_flag_arrays_host, uint64_t ranks, uint64_t rank, uint64_t which,
                             uint32_t* local_epochs, gemb_stream_t stream) {
   const char* op = "gemb_moe_ep_barrier";
   PeerPtrs peers;
-  GEMB_TRY(load_peers(op, peer_flag_arrays, ranks, &peers));
+  GEMB_TRY(load_peers(op, peer_flag_arrays_host, ranks, &peers));
   GEMB_REQUIRE(rank < ranks && which < 2 && local_epochs != nullptr, "%s: bad rank, barrier index or epoch pointer", op);
   GEMB_TRY(require_sm100(op));
   ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, static_cast<uint32_t>(ranks), static_cast<uint32_t>(rank),
@@ -312,25 +312,25 @@ int32_t gemb_moe_ep_barrier(const uint64_t* peer_flag_arrays, uint64_t ranks, ui
   return check_launch(op);
 }
 
-int32_t gemb_moe_ep_gather_counts(const uint64_t* peer_count_buffers, uint64_t ranks, uint64_t experts,
+int32_t gemb_moe_ep_gather_counts(const uint64_t* peer_count_buffers_host, uint64_t ranks, uint64_t experts,
                                   int32_t* counts_all, gemb_stream_t stream) {
   const char* op = "gemb_moe_ep_gather_counts";
   PeerPtrs peers;
-  GEMB_TRY(load_peers(op, peer_count_buffers, ranks, &peers));
+  GEMB_TRY(load_peers(op, peer_count_buffers_host, ranks, &peers));
   GEMB_REQUIRE(counts_all != nullptr && experts >= 1 && experts <= kMaxExperts, "%s: bad arguments", op);
   GEMB_TRY(require_sm100(op));
   ep_gather_counts_kernel<<<1, 256, 0, stream>>>(peers, static_cast<uint32_t>(ranks), static_cast<uint32_t>(experts), counts_all);
   return check_launch(op);
 }
 
-int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers, uint64_t ranks, uint64_t local_experts,
+int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers_host, uint64_t ranks, uint64_t local_experts,
                                   const int32_t* recv_prefix, const int32_t* recv_src_rows,
                                   const int32_t* recv_dst_rows, uint8_t* packed_e2m1, uint8_t* interleaved_scales,
                                   uint64_t hidden, uint64_t message_row_bytes, uint64_t send_rows_per_rank,
                                   uint64_t padded_rows_max, gemb_stream_t stream) {
   const char* op = "gemb_moe_ep_pull_dispatch";
   PeerPtrs peers;
-  GEMB_TRY(load_peers(op, peer_send_buffers, ranks, &peers));
+  GEMB_TRY(load_peers(op, peer_send_buffers_host, ranks, &peers));
   GEMB_REQUIRE(recv_prefix && recv_src_rows && recv_dst_rows && packed_e2m1 && interleaved_scales,
                "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(local_experts >= 1 && ranks * local_experts <= kMaxExperts, "%s: bad expert geometry", op);
@@ -352,14 +352,14 @@ int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers, uint64_t ra
   return check_launch(op);
 }
 
-int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs, uint64_t ranks, uint64_t local_experts,
+int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs_host, uint64_t ranks, uint64_t local_experts,
                                  const int32_t* top_ids, const int32_t* slot_rows, const int32_t* combine_row_base,
                                  const float* top_weights, const uint16_t* shared_bf16, uint16_t* out_bf16,
                                  uint64_t tokens, uint64_t hidden, uint64_t topk, uint64_t padded_rows_max,
                                  gemb_stream_t stream) {
   const char* op = "gemb_moe_ep_pull_combine";
   PeerPtrs peers;
-  GEMB_TRY(load_peers(op, peer_expert_outputs, ranks, &peers));
+  GEMB_TRY(load_peers(op, peer_expert_outputs_host, ranks, &peers));
   GEMB_REQUIRE(top_ids && slot_rows && combine_row_base && top_weights && out_bf16, "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(tokens > 0 && tokens < (1ull << 31) && topk >= 1 && topk <= 32, "%s: bad geometry", op);
   GEMB_REQUIRE(local_experts >= 1 && ranks * local_experts <= kMaxExperts, "%s: bad expert geometry", op);

@@ -462,36 +462,36 @@ int32_t gemb_output_head_argmax(const void* candidates, uint64_t rows, uint32_t*
  *   combine_row_base  [E] for an assignment of ITS OWN tokens to expert e whose local slot row
  *                     (gemb_moe_permute's slot_rows) is p: the row of the result in the owner's
  *                     output buffer is combine_row_base[e] + p.
- * gemb_moe_ep_pull_dispatch reads the segments out of the peers' send buffers (peer_send_buffers:
+ * gemb_moe_ep_pull_dispatch reads the segments out of the peers' send buffers (peer_send_buffers_host:
  * R device addresses, host array) into payload [rows, hidden/2] + INTERLEAVED scales.
  * gemb_moe_ep_pull_combine is gemb_moe_combine with every expert row read from its owner's output
- * buffer (peer_expert_outputs: R device addresses of bf16 [rows, hidden]).
+ * buffer (peer_expert_outputs_host: R device addresses of bf16 [rows, hidden]).
  * send_rows_per_rank / padded_rows_max are the capacities of the send and of the padded buffers: a
  * position outside them (counts that are not what the protocol promises) is skipped and recorded,
  * and gemb_check_device_status() then reports it, instead of the access faulting. */
 /* Ordering between the GPUs without a collective library.  gemb_moe_ep_barrier: rank `rank` bumps
  * its device-resident epoch for barrier `which` (0 or 1; local_epochs holds two words, zero at
- * start), stores it to slot [which][rank] of every rank's flag array (peer_flag_arrays: R device
+ * start), stores it to slot [which][rank] of every rank's flag array (peer_flag_arrays_host: R device
  * addresses of 2 x 16 zero-initialised words) and waits, for a bounded time, until every slot of its
  * own array has reached the epoch.  Everything earlier in the stream is then visible to peers that
  * pass their own barrier.  Each rank must run on its own GPU.  gemb_moe_ep_gather_counts copies
- * every rank's per-expert counts (peer_count_buffers: R device addresses of E int32) into
+ * every rank's per-expert counts (peer_count_buffers_host: R device addresses of E int32) into
  * counts_all [R][E] -- the input of gemb_moe_ep_plan -- after such a barrier. */
-int32_t gemb_moe_ep_barrier(const uint64_t* peer_flag_arrays, uint64_t ranks, uint64_t rank, uint64_t which,
+int32_t gemb_moe_ep_barrier(const uint64_t* peer_flag_arrays_host, uint64_t ranks, uint64_t rank, uint64_t which,
                             uint32_t* local_epochs, gemb_stream_t stream);
-int32_t gemb_moe_ep_gather_counts(const uint64_t* peer_count_buffers, uint64_t ranks, uint64_t experts,
+int32_t gemb_moe_ep_gather_counts(const uint64_t* peer_count_buffers_host, uint64_t ranks, uint64_t experts,
                                   int32_t* counts_all, gemb_stream_t stream);
 uint64_t gemb_moe_ep_plan_ints(uint64_t capacity_rows, uint64_t local_experts);
 int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t experts, uint64_t rank,
                          int32_t* plan, int32_t* recv_prefix, int32_t* recv_src_rows,
                          int32_t* recv_dst_rows, int32_t* combine_row_base, gemb_stream_t stream);
-int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers, uint64_t ranks,
+int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers_host, uint64_t ranks,
                                   uint64_t local_experts, const int32_t* recv_prefix,
                                   const int32_t* recv_src_rows, const int32_t* recv_dst_rows,
                                   uint8_t* packed_e2m1, uint8_t* interleaved_scales, uint64_t hidden,
                                   uint64_t message_row_bytes, uint64_t send_rows_per_rank,
                                   uint64_t padded_rows_max, gemb_stream_t stream);
-int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs, uint64_t ranks,
+int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs_host, uint64_t ranks,
                                  uint64_t local_experts, const int32_t* top_ids,
                                  const int32_t* slot_rows, const int32_t* combine_row_base,
                                  const float* top_weights, const uint16_t* shared_bf16,
