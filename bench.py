@@ -698,7 +698,9 @@ def bench_tp_mlp(lib, dev, world, rank, tokens=16384):
     flops = 2.0 * tokens * 3 * inter * hidden
     return {"metric": "tensor-parallel MLP tokens/s", "ranks": world, "tokens": tokens, "ms": ms,
             "tokens_per_s": tokens / ms * 1e3, "tflops_aggregate": flops / ms / 1e9,
-            "allreduce_bytes_per_rank": tokens * hidden * 4 if world > 1 else 0}
+            "reduction": {"peer": "reduce-scatter + all-gather kernels over peer memory, flag barriers",
+                          "nccl": "NCCL all-reduce of the fp32 partials"}[mlp.reduce] if world > 1 else "none",
+            "partial_bytes_per_rank": tokens * hidden * 4 if world > 1 else 0}
 
 
 def bench_moe_ep(lib, dev, world, rank, layers=30, phases=((16384, "prefill"), (64, "decode"))):

@@ -21,6 +21,8 @@
 // owners' output buffers.
 //
 // gem16 has no multi-GPU code; this protocol is the library's own.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace gemb {
@@ -261,6 +263,55 @@ ep_pull_combine_kernel(PeerPtrs peers, const int32_t* __restrict__ ids, const in
   *(reinterpret_cast<uint4*>(out + static_cast<uint64_t>(t) * hidden) + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-parallel reduction over peer memory: the all-reduce behind a K-split projection as a
+// reduce-scatter and an all-gather made of plain peer loads.  Rank r owns token rows
+// [r*T/R, (r+1)*T/R): it sums every rank's fp32 partial of those rows in rank order (so all ranks
+// agree bit for bit and the result does not depend on timing), rounds once to bf16 and writes its
+// slice of its own peer-mapped output; after a barrier every rank copies the other slices from
+// their owners.  Per rank (R-1)/R of the fp32 matrix and (R-1)/R of the bf16 matrix cross NVLink,
+// against 2(R-1)/R of the fp32 matrix for a ring all-reduce.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+tp_reduce_rows_kernel(PeerPtrs partials, uint32_t ranks, uint64_t row_begin, uint64_t row_end, uint32_t hidden,
+                      uint16_t* __restrict__ out) {
+  const uint32_t vecs = hidden / 4;
+  const uint64_t work = (row_end - row_begin) * vecs;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < work;
+       i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+    const uint64_t off = (row_begin + i / vecs) * hidden + (i % vecs) * 4;   // element offset
+    float4 acc = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(partials.p[0]) + off);
+    for (uint32_t s = 1; s < ranks; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(partials.p[s]) + off);
+      acc.x = __fadd_rn(acc.x, v.x);
+      acc.y = __fadd_rn(acc.y, v.y);
+      acc.z = __fadd_rn(acc.z, v.z);
+      acc.w = __fadd_rn(acc.w, v.w);
+    }
+    const uint32_t lo = static_cast<uint32_t>(float_to_bf16_bits(acc.x)) | (static_cast<uint32_t>(float_to_bf16_bits(acc.y)) << 16);
+    const uint32_t hi = static_cast<uint32_t>(float_to_bf16_bits(acc.z)) | (static_cast<uint32_t>(float_to_bf16_bits(acc.w)) << 16);
+    *reinterpret_cast<uint2*>(out + off) = make_uint2(lo, hi);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+tp_gather_rows_kernel(PeerPtrs slices, uint32_t ranks, uint32_t me, uint64_t tokens, uint32_t hidden,
+                      uint16_t* __restrict__ out) {
+  const uint32_t vecs = hidden / 8;   // 16-byte pieces per row
+  const uint64_t work = tokens * vecs;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < work;
+       i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+    const uint64_t row = i / vecs;
+    // owner of the row: the rank whose slice [s*T/R, (s+1)*T/R) holds it
+    uint32_t owner = static_cast<uint32_t>((row * ranks + ranks - 1) / tokens);
+    while (owner > 0 && row < owner * tokens / ranks) --owner;
+    while (owner + 1 < ranks && row >= (owner + 1) * tokens / ranks) ++owner;
+    if (owner == me) continue;
+    const uint64_t off = row * hidden + (i % vecs) * 8;
+    *reinterpret_cast<uint4*>(out + off) = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(slices.p[owner]) + off);
+  }
+}
+
 int32_t load_peers(const char* op, const uint64_t* peer_ptrs, uint64_t ranks, PeerPtrs* out) {
   GEMB_REQUIRE(peer_ptrs != nullptr, "%s: peer pointer table must be nonnull", op);
   GEMB_REQUIRE(ranks >= 1 && ranks <= kMaxRanks, "%s: between 1 and %u ranks are supported", op, kMaxRanks);
@@ -320,6 +371,44 @@ int32_t gemb_moe_ep_gather_counts(const uint64_t* peer_count_buffers_host, uint6
   GEMB_REQUIRE(counts_all != nullptr && experts >= 1 && experts <= kMaxExperts, "%s: bad arguments", op);
   GEMB_TRY(require_sm100(op));
   ep_gather_counts_kernel<<<1, 256, 0, stream>>>(peers, static_cast<uint32_t>(ranks), static_cast<uint32_t>(experts), counts_all);
+  return check_launch(op);
+}
+
+int32_t gemb_tp_reduce_rows(const uint64_t* peer_partials_host, uint64_t ranks, uint64_t rank, uint64_t tokens,
+                            uint64_t hidden, uint16_t* out_bf16, gemb_stream_t stream) {
+  const char* op = "gemb_tp_reduce_rows";
+  PeerPtrs peers;
+  GEMB_TRY(load_peers(op, peer_partials_host, ranks, &peers));
+  GEMB_REQUIRE(out_bf16 != nullptr && rank < ranks, "%s: bad output pointer or rank", op);
+  GEMB_REQUIRE(tokens > 0 && tokens < (1ull << 31) && hidden > 0 && hidden % 8 == 0 && hidden < (1ull << 24),
+               "%s: hidden must be a nonzero multiple of 8", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(out_bf16) % 16 == 0, "%s: output must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  const uint64_t begin = rank * tokens / ranks, end = (rank + 1) * tokens / ranks;
+  if (end == begin) return GEMB_OK;
+  const uint64_t work = (end - begin) * (hidden / 4);
+  const uint64_t ctas = std::min<uint64_t>((work + 255) / 256, static_cast<uint64_t>(sm_count()) * 16);
+  tp_reduce_rows_kernel<<<static_cast<unsigned>(ctas), 256, 0, stream>>>(peers, static_cast<uint32_t>(ranks), begin, end,
+                                                                        static_cast<uint32_t>(hidden), out_bf16);
+  return check_launch(op);
+}
+
+int32_t gemb_tp_gather_rows(const uint64_t* peer_outputs_host, uint64_t ranks, uint64_t rank, uint64_t tokens,
+                            uint64_t hidden, uint16_t* out_bf16, gemb_stream_t stream) {
+  const char* op = "gemb_tp_gather_rows";
+  PeerPtrs peers;
+  GEMB_TRY(load_peers(op, peer_outputs_host, ranks, &peers));
+  GEMB_REQUIRE(out_bf16 != nullptr && rank < ranks, "%s: bad output pointer or rank", op);
+  GEMB_REQUIRE(tokens > 0 && tokens < (1ull << 31) && hidden > 0 && hidden % 8 == 0 && hidden < (1ull << 24),
+               "%s: hidden must be a nonzero multiple of 8", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(out_bf16) % 16 == 0, "%s: output must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  if (ranks == 1) return GEMB_OK;
+  const uint64_t work = tokens * (hidden / 8);
+  const uint64_t ctas = std::min<uint64_t>((work + 255) / 256, static_cast<uint64_t>(sm_count()) * 16);
+  tp_gather_rows_kernel<<<static_cast<unsigned>(ctas), 256, 0, stream>>>(peers, static_cast<uint32_t>(ranks),
+                                                                        static_cast<uint32_t>(rank), tokens,
+                                                                        static_cast<uint32_t>(hidden), out_bf16);
   return check_launch(op);
 }
 

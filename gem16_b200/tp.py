@@ -12,7 +12,7 @@ from .lib import load
 
 
 class TpMlp:
-    def __init__(self, dev, gate, up, down, tokens: int, ga: float, ga_dn: float, group=None):
+    def __init__(self, dev, gate, up, down, tokens: int, ga: float, ga_dn: float, group=None, reduce: str = "auto"):
         """gate / up / down: (packed [rows, K/2] uint8, compact scales [rows, K/16] uint8, divisor) of the
         FULL matrices (identical on every rank); each rank keeps its shard."""
         self.lib = lib = load()
@@ -46,7 +46,26 @@ class TpMlp:
         self.u = torch.empty((tokens, il), dtype=torch.int16, device=dev)
         self.pq = torch.empty((tokens, il // 2), **u8)
         self.ps = torch.zeros((c.gemb_interleaved_scale_bytes(tokens, il),), **u8)
-        self.partial = torch.empty((tokens, self.hidden), dtype=torch.float32, device=dev)
+        # reduce = "peer": the library's reduce-scatter / all-gather over peer memory with its own flag
+        # barrier; "nccl": all-reduce of the fp32 partials; "auto": peer when the buffers can be mapped.
+        self.reduce = "nccl"
+        self.partial = None
+        if self.world > 1 and reduce in ("auto", "peer"):
+            try:
+                from .peer import PeerBuffer
+                self.partial_peer = PeerBuffer(tokens * self.hidden * 4, dev, group)
+                self.out_peer = PeerBuffer(tokens * self.hidden * 2, dev, group)
+                self.flags_peer = PeerBuffer(2 * 16 * 4, dev, group)
+                self.epochs = torch.zeros((2,), dtype=torch.int32, device=dev)
+                self.partial = self.partial_peer.local.view(torch.float32).view(tokens, self.hidden)
+                self.out = self.out_peer.local.view(torch.int16).view(tokens, self.hidden)
+                self.reduce = "peer"
+                dist.barrier(group)
+            except Exception:
+                if reduce == "peer":
+                    raise
+        if self.partial is None:
+            self.partial = torch.empty((tokens, self.hidden), dtype=torch.float32, device=dev)
 
     def forward(self, x_bf16):
         lib, t, h, il = self.lib, self.tokens, self.hidden, self.i_local
@@ -56,6 +75,13 @@ class TpMlp:
         lib.gemb_nvfp4_gated_gelu_quantize(self.g, self.u, 1, self.pq, self.ps, t, il, self.ga_dn, 1, 0, None)
         lib.gemb_nvfp4_gemm_f32(self.pq, self.ps, self.down[0], self.down[1], self.partial, t, h, il, self.ga_dn,
                                 self.down[2], None)
+        if self.reduce == "peer":
+            st, R, r = torch.cuda.current_stream(), self.world, self.rank
+            lib.gemb_moe_ep_barrier(self.flags_peer.table, R, r, 0, self.epochs, st)     # every partial is complete
+            lib.gemb_tp_reduce_rows(self.partial_peer.table, R, r, t, h, self.out, st)
+            lib.gemb_moe_ep_barrier(self.flags_peer.table, R, r, 1, self.epochs, st)     # every slice is complete
+            lib.gemb_tp_gather_rows(self.out_peer.table, R, r, t, h, self.out, st)
+            return self.out.view(torch.bfloat16)
         if self.world > 1:
             dist.all_reduce(self.partial, group=self.group)
         return self.partial.to(torch.bfloat16)

@@ -498,6 +498,18 @@ int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs_host, uint6
                                  uint16_t* out_bf16, uint64_t tokens, uint64_t hidden, uint64_t topk,
                                  uint64_t padded_rows_max, gemb_stream_t stream);
 
+/* Tensor-parallel reduction of a K-split projection over peer memory (no counterpart in the
+ * reference).  peer_partials_host: R device addresses of fp32 partial results [tokens, hidden]
+ * (gemb_nvfp4_gemm_f32 on each rank's K slice).  gemb_tp_reduce_rows sums, for the token rows rank
+ * `rank` owns ([rank*T/R, (rank+1)*T/R)), the partials of all ranks in rank order, rounds once to
+ * bf16 and writes those rows of out_bf16 [tokens, hidden]; gemb_tp_gather_rows then copies every
+ * other rank's rows from its out buffer (peer_outputs_host).  The caller separates the GEMM, the
+ * reduce and the gather with gemb_moe_ep_barrier (or any other barrier between the GPUs). */
+int32_t gemb_tp_reduce_rows(const uint64_t* peer_partials_host, uint64_t ranks, uint64_t rank, uint64_t tokens,
+                            uint64_t hidden, uint16_t* out_bf16, gemb_stream_t stream);
+int32_t gemb_tp_gather_rows(const uint64_t* peer_outputs_host, uint64_t ranks, uint64_t rank, uint64_t tokens,
+                            uint64_t hidden, uint16_t* out_bf16, gemb_stream_t stream);
+
 /* out[t] = bf16( sum over slots in slot order of fma(weight[t][slot], y[slot_rows[t*topk+slot]])
  *                + shared[t] ), fp32 accumulation, no atomics; shared may be null.
  * docs/plans/gemma4-26b/specs/MOE_SEMANTICS_SPEC.md:74-83. */

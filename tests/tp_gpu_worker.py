@@ -35,17 +35,27 @@ def main():
     gate, up, down = quant(inter, hidden), quant(inter, hidden), quant(hidden, inter)
     x = torch.randn((tokens, hidden), device=dev, generator=g).to(torch.bfloat16).view(torch.int16)
     ga, ga_dn = 700.0, 2688.0 / 0.05
-    sharded = TpMlp(dev, gate, up, down, tokens, ga, ga_dn).forward(x)
+    mlp = TpMlp(dev, gate, up, down, tokens, ga, ga_dn, reduce="peer")
+    sharded = mlp.forward(x).clone()
+    again = mlp.forward(x)          # buffers and barrier epochs are reused
+    assert torch.equal(sharded, again), "peer reduction is not repeatable"
+    via_nccl = TpMlp(dev, gate, up, down, tokens, ga, ga_dn, reduce="nccl").forward(x)
     solo_group = dist.new_group([rank]) if False else None
     # unsharded reference on every rank: same class with a one-rank group
     groups = [dist.new_group([r]) for r in range(world)]
     full = TpMlp(dev, gate, up, down, tokens, ga, ga_dn, group=groups[rank]).forward(x)
     torch.cuda.synchronize()
     lib.gemb_check_device_status()
-    a, b = sharded.float(), full.float()
-    rel = float((a - b).norm() / b.norm())
-    mism = float((a != b).float().mean())
-    assert rel <= 1e-3 and mism < 0.05, (rel, mism)
+    for name, got in (("peer", sharded), ("nccl", via_nccl)):
+        a, b = got.float(), full.float()
+        rel = float((a - b).norm() / b.norm())
+        mism = float((a != b).float().mean())
+        assert rel <= 1e-3 and mism < 0.05, (name, rel, mism)
+    # every rank holds the same bits after the gather
+    mine = sharded.view(torch.int16).to(torch.int32).sum().reshape(1).double()
+    both = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(both, mine)
+    assert all(float(v) == float(both[0]) for v in both), "ranks disagree after the peer all-gather"
     dist.barrier()
     print(f"rank {rank} ok rel={rel:.2e} mismatch={mism:.4f}", flush=True)
     dist.destroy_process_group()
