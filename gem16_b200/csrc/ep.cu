@@ -204,11 +204,34 @@ ep_pull_dispatch_kernel(PeerPtrs peers, const int32_t* __restrict__ recv_prefix,
       continue;
     }
     const uint8_t* src = peers.p[lo / el] + srow * msg_bytes;
-    for (uint32_t v = lane; v < payload_vecs; v += 32)
-      *reinterpret_cast<uint4*>(packed + d * (hidden / 2) + v * 16) = *reinterpret_cast<const uint4*>(src + v * 16);
-    for (uint32_t w = lane; w < scale_words; w += 32)
-      *reinterpret_cast<uint32_t*>(scales + interleaved_scale_offset(d, w * 4, c_pad)) =
-          *reinterpret_cast<const uint32_t*>(src + hidden / 2 + w * 4);
+    // All of a lane's loads of the row (over NVLink for a remote source) are issued before its first
+    // store: a row is small, so the loads in flight per warp are what hides the link latency.
+    for (uint32_t v0 = 0; v0 < payload_vecs; v0 += 128) {
+      uint4 pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t v = v0 + i * 32 + lane;
+        pv[i] = v < payload_vecs ? *reinterpret_cast<const uint4*>(src + v * 16) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t v = v0 + i * 32 + lane;
+        if (v < payload_vecs) *reinterpret_cast<uint4*>(packed + d * (hidden / 2) + v * 16) = pv[i];
+      }
+    }
+    for (uint32_t w0 = 0; w0 < scale_words; w0 += 64) {
+      uint32_t sv[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t w = w0 + i * 32 + lane;
+        sv[i] = w < scale_words ? *reinterpret_cast<const uint32_t*>(src + hidden / 2 + w * 4) : 0u;
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t w = w0 + i * 32 + lane;
+        if (w < scale_words) *reinterpret_cast<uint32_t*>(scales + interleaved_scale_offset(d, w * 4, c_pad)) = sv[i];
+      }
+    }
   }
 }
 
@@ -434,7 +457,7 @@ int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers_host, uint64
   GEMB_TRY(require_sm100(op));
   const uint32_t segments = static_cast<uint32_t>(ranks * local_experts);
   const uint32_t c_pad = static_cast<uint32_t>((hidden / 16 + 3) / 4 * 4);
-  ep_pull_dispatch_kernel<<<static_cast<unsigned>(sm_count()) * 4, 256, (segments + 1) * sizeof(int), stream>>>(
+  ep_pull_dispatch_kernel<<<static_cast<unsigned>(sm_count()) * 8, 256, (segments + 1) * sizeof(int), stream>>>(
       peers, recv_prefix, recv_src_rows, recv_dst_rows, segments, static_cast<uint32_t>(local_experts),
       static_cast<uint32_t>(hidden), static_cast<uint32_t>(message_row_bytes), c_pad, packed_e2m1, interleaved_scales,
       static_cast<uint32_t>(send_rows_per_rank), static_cast<uint32_t>(padded_rows_max));
