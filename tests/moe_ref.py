@@ -74,3 +74,30 @@ def moe_layer_oracle(orc, p, x_bf16_bits, topk, ga, ga_dn, ga_sh_dn=None):
                           None if shared is None else bf16_bits(shared))
     return {"logits": logits, "ids": ids, "weights": weights, "counts": counts, "offsets": offsets, "perm": perm,
             "y_slots": y_slots, "shared": shared, "out": out}
+
+
+def ep_plan_reference(counts_all, me):
+    """Plain restatement of the position arithmetic (see the header comment of csrc/ep.cu)."""
+    ranks, experts = counts_all.shape
+    el = experts // ranks
+    tot = counts_all.sum(0)
+    pad = np.zeros(experts, np.int64)
+    for d in range(ranks):
+        po = 0
+        for e in range(d * el, (d + 1) * el):
+            pad[e] = po
+            po += (tot[e] + 127) // 128 * 128
+    my_pad = np.concatenate([[0], np.cumsum((counts_all[me] + 127) // 128 * 128)])[:-1]
+    before_me = counts_all[:me].sum(0)
+    row_base = pad + before_me - my_pad
+    prefix, src, dst = [0], [], []
+    for s in range(ranks):
+        sorted_off = np.concatenate([[0], np.cumsum(counts_all[s])])
+        for e in range(me * el, (me + 1) * el):
+            src.append(sorted_off[e])
+            dst.append(pad[e] + counts_all[:s, e].sum())
+            prefix.append(prefix[-1] + counts_all[s, e])
+    mine = slice(me * el, (me + 1) * el)
+    padded_rows = int(((tot[mine] + 127) // 128 * 128).sum())
+    return dict(row_base=row_base, prefix=np.array(prefix), src=np.array(src), dst=np.array(dst),
+                pad_local=pad[mine], padded_rows=padded_rows)

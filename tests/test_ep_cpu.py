@@ -35,3 +35,57 @@ def test_tensor_parallel_mlp_two_ranks():
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
+
+
+def test_peer_protocol_positions_reproduce_the_single_gpu_order():
+    """The position arithmetic of the peer-memory protocol (csrc/ep.cu, restated in
+    tests/moe_ref.ep_plan_reference) against a brute-force model: R ranks each sort their own
+    assignments by expert; the rows an owner pulls, placed at recv_dst + j, must come out in the
+    single-GPU order (expert, global token, slot), every expert starting on a multiple of 128 rows,
+    and combine_row_base + the sender's local padded row must name the same row."""
+    import numpy as np
+    from tests.moe_ref import ep_plan_reference
+    rng = np.random.default_rng(0)
+    for ranks, experts, tokens, topk in [(2, 8, 37, 2), (4, 16, 50, 4), (8, 128, 9, 8)]:
+        el = experts // ranks
+        ids = rng.integers(0, experts, (ranks, tokens * topk))          # expert of assignment (token*topk + slot)
+        ids[:, : experts // 2] = 0                                        # a hot expert and some empty ones
+        counts = np.stack([np.bincount(ids[r], minlength=experts) for r in range(ranks)])
+        order = [np.argsort(ids[r], kind="stable") for r in range(ranks)]  # each rank's send buffer
+        # single-GPU order over all ranks' tokens: stable sort of (rank, assignment) by expert
+        flat = [(int(ids[r, a]), r, int(a)) for r in range(ranks) for a in range(tokens * topk)]
+        flat.sort(key=lambda x: x[0])
+        for me in range(ranks):
+            plan = ep_plan_reference(counts, me)
+            mine = [x for x in flat if me * el <= x[0] < (me + 1) * el]
+            want_row = {}
+            pos_in_expert = {}
+            for e, r, a in mine:
+                k = pos_in_expert.get(e, 0)
+                want_row[(r, a)] = int(plan["pad_local"][e - me * el]) + k
+                pos_in_expert[e] = k + 1
+            assert all(v % 128 == 0 for v in plan["pad_local"])
+            got_row = {}
+            for s_rank in range(ranks):
+                for e_loc in range(el):
+                    g = s_rank * el + e_loc
+                    n = int(plan["prefix"][g + 1] - plan["prefix"][g])
+                    for j in range(n):
+                        a = int(order[s_rank][plan["src"][g] + j])
+                        assert ids[s_rank, a] == me * el + e_loc
+                        got_row[(s_rank, a)] = int(plan["dst"][g]) + j
+            assert got_row == want_row
+            assert plan["prefix"][-1] == len(mine) and plan["padded_rows"] >= len(mine)
+        # the token owner's view: local padded row of an assignment -> row in the expert owner's output
+        for me in range(ranks):
+            plan = ep_plan_reference(counts, me)
+            my_pad = np.concatenate([[0], np.cumsum((counts[me] + 127) // 128 * 128)])
+            my_off = np.concatenate([[0], np.cumsum(counts[me])])
+            for p, a in enumerate(order[me]):
+                e = int(ids[me, a])
+                slot_row = my_pad[e] + (p - my_off[e])                 # what gemb_moe_permute's slot_rows holds
+                owner = e // el
+                owner_plan = ep_plan_reference(counts, owner)
+                g = me * el + (e - owner * el)
+                want = int(owner_plan["dst"][g]) + (p - int(my_off[e]))
+                assert int(plan["row_base"][e]) + slot_row == want
