@@ -43,8 +43,6 @@
 #include <cuda.h>
 
 #include <algorithm>
-#include <cstdio>
-#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -729,7 +727,6 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
         return fail(GEMB_INTERNAL, "%s: CTA pairs cannot be scheduled on this device (%s)", op, cudaGetErrorName(e));
       }
       max_pairs[dev] = clusters;
-      if (std::getenv("GEMB_DEBUG")) std::fprintf(stderr, "max_pairs=%d\n", clusters);
     }
     configured[dev] = true;
   }
