@@ -113,7 +113,7 @@ class Nvfp4Linear:
     compact_scales: object    # uint8 [rows, K/16] (decode GEMV)
     interleaved_scales: object  # uint8, 128x4 interleave per matrix, experts back to back (prefill / grouped GEMM)
     weight_divisor: object    # float, or list of floats per expert
-    input_divisor: object     # float, list per expert, or None when the tensor is absent
+    input_divisor: object     # float, or list of floats per expert
     rows: int
     k: int
     experts: int              # 0 for a plain linear
@@ -127,10 +127,18 @@ class Fp8Linear:
     k: int
 
 
-def _scalar_or_list(arr, experts, what):
+def _global_divisor(st, name, experts):
+    """A per-tensor global divisor: present, stored as F32, shape [1] ([experts] for a stack), positive
+    and finite -- the reference returns kDataLoss otherwise (src/model/manifest.cpp:346-365)."""
+    what = name
+    if name not in st:
+        raise CheckpointError(f"{what}: NVFP4 module is missing this required scale tensor")
+    if st.dtype(name) != "F32":
+        raise CheckpointError(f"{what}: global scales must be stored as F32, found {st.dtype(name)}")
+    arr = st.tensor(name)
+    if tuple(arr.shape) != (max(experts, 1),):
+        raise CheckpointError(f"{what}: expected shape [{max(experts, 1)}], found {list(arr.shape)}")
     a = np.asarray(arr, dtype=np.float32).reshape(-1)
-    if a.size != max(experts, 1):
-        raise CheckpointError(f"{what}: expected {max(experts, 1)} value(s), found {a.size}")
     if not np.all(np.isfinite(a)) or np.any(a <= 0):
         raise CheckpointError(f"{what}: global divisors must be positive and finite")
     return [float(v) for v in a] if experts else float(a[0])
@@ -156,10 +164,8 @@ def load_nvfp4_linear(st: SafetensorsFile, prefix: str, dev, lib=None) -> Nvfp4L
         raise CheckpointError(f"{prefix}: weight_scale shape {tuple(scale.shape)} does not match weight_packed")
     if np.any((scale & 0x7F) == 0x7F):
         raise CheckpointError(f"{prefix}: weight_scale holds an E4M3FN NaN encoding")
-    gw = _scalar_or_list(st.tensor(prefix + ".weight_global_scale"), experts, prefix + ".weight_global_scale")
-    ga = None
-    if prefix + ".input_global_scale" in st:
-        ga = _scalar_or_list(st.tensor(prefix + ".input_global_scale"), experts, prefix + ".input_global_scale")
+    gw = _global_divisor(st, prefix + ".weight_global_scale", experts)
+    ga = _global_divisor(st, prefix + ".input_global_scale", experts)
     d_packed = torch.from_numpy(np.array(packed)).to(dev)   # a copy: the map is read-only
     d_compact = torch.from_numpy(np.array(scale)).to(dev)
     per = lib.cdll.gemb_interleaved_scale_bytes(rows, k)

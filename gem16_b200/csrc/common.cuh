@@ -25,6 +25,7 @@ int32_t require_sm100(const char* op);
 int sm_count();
 // Tuning knobs owned by the GEMM translation unit (see gemb_set_tuning).
 int32_t gemm_set_tuning(int32_t knob, int32_t value);
+int32_t ep_set_tuning(int32_t knob, int32_t value);
 // Decode-size FP8 token quantizer (bf16 input, K <= 16384, K % 8 == 0); bit-identical to the
 // general kernel, one global round trip, programmatic-dependent-launch aware.
 int32_t launch_fp8_quantize_decode(const char* op, const uint16_t* x, uint8_t* out, float* scales, uint64_t tokens,
@@ -32,6 +33,7 @@ int32_t launch_fp8_quantize_decode(const char* op, const uint16_t* x, uint8_t* o
 // Reads and clears the decode GEMV's bounded-wait flag (0 = clean, -1 = could not read).
 int gemv_take_device_error();
 int ep_take_device_error();
+int moe_take_device_error();
 
 inline bool positive_finite(float v) { return std::isfinite(v) && v > 0.0f; }
 

@@ -44,6 +44,19 @@ int ep_take_device_error() {
   return code;
 }
 
+// Polls a flag barrier makes before it gives up (about 500 ns each once past the first 64):
+// gemb_set_tuning(GEMB_TUNE_EP_BARRIER_SPINS, n); the default is about three seconds.
+int g_ep_barrier_spins = 1 << 22;
+
+int32_t ep_set_tuning(int32_t knob, int32_t value) {
+  if (knob == GEMB_TUNE_EP_BARRIER_SPINS) {
+    GEMB_REQUIRE(value >= 0 && value <= (1 << 24), "gemb_set_tuning: barrier polls must be in [0, 2^24] (0 = default)");
+    g_ep_barrier_spins = value == 0 ? 1 << 22 : value;
+    return GEMB_OK;
+  }
+  return fail(GEMB_INVALID_ARGUMENT, "gemb_set_tuning: unknown knob %d", knob);
+}
+
 namespace {
 
 constexpr uint32_t kMaxRanks = 16;
@@ -57,9 +70,48 @@ struct PeerPtrs {
 __global__ void __launch_bounds__(256)
 ep_plan_kernel(const int32_t* __restrict__ counts_all, uint32_t ranks, uint32_t experts, uint32_t me,
                int32_t* __restrict__ plan, int32_t* __restrict__ recv_prefix, int32_t* __restrict__ recv_src,
-               int32_t* __restrict__ recv_dst, int32_t* __restrict__ out_base) {
+               int32_t* __restrict__ recv_dst, int32_t* __restrict__ out_base, uint32_t capacity_rows,
+               uint32_t send_rows) {
   extern __shared__ int sm[];
   const uint32_t el = experts / ranks;
+  // Counts that cannot be (negative, more than a rank can send, or more padded rows than the
+  // buffers hold -- e.g. read after a barrier gave up, while a peer was still writing them) give
+  // an empty plan: no tile, no segment, every combine base out of range (the combine skips those).
+  __shared__ int bad;
+  if (threadIdx.x == 0) bad = 0;
+  __syncthreads();
+  for (uint32_t s = threadIdx.x; s < ranks; s += blockDim.x) {
+    int64_t sent = 0;
+    bool neg = false;
+    for (uint32_t e = 0; e < experts; ++e) {
+      const int c = counts_all[s * experts + e];
+      neg |= c < 0;
+      sent += c;
+    }
+    if (neg || sent > static_cast<int64_t>(send_rows)) bad = 1;
+  }
+  if (threadIdx.x == 0) {
+    int64_t po = 0;
+    for (uint32_t e = me * el; e < (me + 1) * el; ++e) {
+      int64_t t = 0;
+      for (uint32_t s = 0; s < ranks; ++s) t += max(counts_all[s * experts + e], 0);
+      po += (t + 127) / 128 * 128;
+    }
+    if (po > static_cast<int64_t>(capacity_rows)) bad = 1;
+  }
+  __syncthreads();
+  if (bad) {
+    if (threadIdx.x == 0) {
+      atomicCAS(&g_ep_error, 0, 6);
+      plan[0] = 0;
+      plan[1] = 0;
+    }
+    for (uint32_t e = threadIdx.x; e <= el; e += blockDim.x) plan[2 + e] = 0;
+    for (uint32_t g = threadIdx.x; g <= ranks * el; g += blockDim.x) recv_prefix[g] = 0;
+    for (uint32_t g = threadIdx.x; g < ranks * el; g += blockDim.x) recv_src[g] = recv_dst[g] = 0;
+    for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) out_base[e] = -(1 << 30);
+    return;
+  }
   int* tot = sm;                    // [experts] rows of expert e over all sources
   int* pad = tot + experts;         // [experts] start of e in its owner's padded row space
   int* before_me = pad + experts;   // [experts] sum_{s' < me} C[s'][e]
@@ -138,7 +190,8 @@ ep_plan_kernel(const int32_t* __restrict__ counts_all, uint32_t ranks, uint32_t 
 // sees the error at its next gemb_check_device_status()).
 // One warp; the ranks run on different GPUs (never several ranks of one barrier on the same GPU).
 __global__ void __launch_bounds__(32)
-ep_barrier_kernel(PeerPtrs flag_arrays, uint32_t ranks, uint32_t me, uint32_t which, uint32_t* __restrict__ epochs) {
+ep_barrier_kernel(PeerPtrs flag_arrays, uint32_t ranks, uint32_t me, uint32_t which, uint32_t* __restrict__ epochs,
+                  uint32_t spin_limit) {
   const uint32_t lane = threadIdx.x;
   uint32_t e = 0;
   if (lane == 0) {
@@ -151,11 +204,11 @@ ep_barrier_kernel(PeerPtrs flag_arrays, uint32_t ranks, uint32_t me, uint32_t wh
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(e) : "memory");
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(flag_arrays.p[me]) + which * kMaxRanks + lane;
     bool ok = false;
-    for (uint32_t i = 0; i < (1u << 22) && !ok; ++i) {
+    for (uint32_t i = 0; i < spin_limit && !ok; ++i) {
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
       ok = static_cast<int32_t>(v - e) >= 0;   // epochs only grow; a peer may already be one barrier ahead
-      if (!ok && i > 64) __nanosleep(500);   // about three seconds in all
+      if (!ok && i > 64) __nanosleep(500);   // about three seconds in all at the default limit
     }
     if (!ok) atomicCAS(&g_ep_error, 0, 5);
   }
@@ -360,17 +413,22 @@ uint64_t gemb_moe_ep_plan_ints(uint64_t capacity_rows, uint64_t local_experts) {
 
 int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t experts, uint64_t rank,
                          int32_t* plan, int32_t* recv_prefix, int32_t* recv_src_rows, int32_t* recv_dst_rows,
-                         int32_t* combine_row_base, gemb_stream_t stream) {
+                         int32_t* combine_row_base, uint64_t capacity_rows, uint64_t send_rows_per_rank,
+                         gemb_stream_t stream) {
   const char* op = "gemb_moe_ep_plan";
   GEMB_REQUIRE(counts_all && plan && recv_prefix && recv_src_rows && recv_dst_rows && combine_row_base,
                "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(ranks >= 1 && ranks <= kMaxRanks && rank < ranks, "%s: bad rank geometry", op);
   GEMB_REQUIRE(experts >= ranks && experts <= kMaxExperts && experts % ranks == 0,
                "%s: experts must be a multiple of ranks, at most %u", op, kMaxExperts);
+  GEMB_REQUIRE(capacity_rows > 0 && capacity_rows < (1ull << 31) && capacity_rows % 128 == 0 &&
+                   send_rows_per_rank > 0 && send_rows_per_rank < (1ull << 31),
+               "%s: buffer capacities must be nonzero (padded rows a multiple of 128)", op);
   GEMB_TRY(require_sm100(op));
   ep_plan_kernel<<<1, 256, 4 * experts * sizeof(int), stream>>>(
       counts_all, static_cast<uint32_t>(ranks), static_cast<uint32_t>(experts), static_cast<uint32_t>(rank), plan,
-      recv_prefix, recv_src_rows, recv_dst_rows, combine_row_base);
+      recv_prefix, recv_src_rows, recv_dst_rows, combine_row_base, static_cast<uint32_t>(capacity_rows),
+      static_cast<uint32_t>(send_rows_per_rank));
   return check_launch(op);
 }
 
@@ -382,7 +440,8 @@ int32_t gemb_moe_ep_barrier(const uint64_t* peer_flag_arrays_host, uint64_t rank
   GEMB_REQUIRE(rank < ranks && which < 2 && local_epochs != nullptr, "%s: bad rank, barrier index or epoch pointer", op);
   GEMB_TRY(require_sm100(op));
   ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, static_cast<uint32_t>(ranks), static_cast<uint32_t>(rank),
-                                          static_cast<uint32_t>(which), local_epochs);
+                                          static_cast<uint32_t>(which), local_epochs,
+                                          static_cast<uint32_t>(g_ep_barrier_spins));
   return check_launch(op);
 }
 

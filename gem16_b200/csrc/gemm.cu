@@ -172,7 +172,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  const uint32_t m_tiles = p.plan ? static_cast<uint32_t>(__ldg(p.plan)) : (p.m + BM - 1) / BM;
+  // A device-side plan is clamped to the buffers' capacity (p.m rows): whatever it holds, no tile
+  // beyond the activation, scale and output buffers is touched.
+  const uint32_t m_tiles = p.plan ? min(static_cast<uint32_t>(__ldg(p.plan)), p.m / BM) : (p.m + BM - 1) / BM;
   const uint32_t n_tiles = (p.n + BN - 1) / BN;
   const int32_t* tile_expert = p.plan ? p.plan + 3 + p.experts : nullptr;
   // A work unit is one 128-row token tile, or for pairs two consecutive ones (rank picks which).
@@ -240,7 +242,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       for (uint32_t tile = first_tile; tile < num_tiles && !*abort_flag; tile += tile_stride) {
         uint32_t mt, nt;
         tile_coords(tile, mt, nt);
-        const uint32_t expert = tile_expert ? static_cast<uint32_t>(__ldg(tile_expert + mt)) : 0u;
+        const uint32_t expert = tile_expert ? min(static_cast<uint32_t>(__ldg(tile_expert + mt)), p.experts - 1) : 0u;
         for (uint32_t ks = 0; ks < k_stages; ++ks) {
           if (!ptx::mbar_wait(&empty[stage], phase ^ 1)) { fail_wait(1); break; }
           const uint32_t k0 = ks * C::kKPerStage;
@@ -462,7 +464,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       float row_scale = p.alpha;
       if constexpr (!kFp4) row_scale = row0 + lane < p.m ? __ldg(p.a_scales + row0 + lane) : 0.0f;
       if (kFp4 && p.w_divisors != nullptr)
-        row_scale = __fdiv_rn(1.0f, __fmul_rn(p.ga, __ldg(p.w_divisors + (tile_expert ? __ldg(tile_expert + mt) : 0))));
+        row_scale = __fdiv_rn(1.0f, __fmul_rn(p.ga, __ldg(p.w_divisors + (tile_expert ? min(static_cast<uint32_t>(__ldg(tile_expert + mt)), p.experts - 1) : 0u))));
       const uint32_t tmem_acc = tmem_base + as * BN + ((quarter * 32) << 16);
       bool released = false, pending = false;
       uint32_t pending_col = 0;
@@ -698,11 +700,15 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
   using C = Cfg<kFp4, BN, kStages, kAccStages, kPair>;
   auto kern = gemm_kernel<kFp4, BN, kStages, kAccStages, kPair>;
   constexpr unsigned kThreads = kFp4 ? kGemmThreadsFp4 : kGemmThreadsFp8;
+  // First call per device and kernel variant: shared-memory opt-in and the pair occupancy,
+  // serialised so that two host threads cannot race on it.
   static bool configured[64] = {false};
   static int max_pairs[64] = {0};
+  static std::mutex configure_mutex;
   int dev = 0;
   cudaGetDevice(&dev);
   dev &= 63;
+  std::lock_guard<std::mutex> configure_lock(configure_mutex);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
@@ -775,7 +781,7 @@ int32_t gemm_set_tuning(int32_t knob, int32_t value) {
     g_gemm_pair = value;
     return GEMB_OK;
   }
-  return fail(GEMB_INVALID_ARGUMENT, "gemb_set_tuning: unknown knob %d", knob);
+  return ep_set_tuning(knob, value);
 }
 
 }  // namespace gemb
@@ -1045,8 +1051,15 @@ int32_t gemb_check_device_status(void) {
   if (gemv_code != 0)
     return fail(GEMB_INTERNAL, "%s: a GEMV kernel gave up waiting on a pipeline barrier (role %d)", op, gemv_code);
   const int ep_code = ep_take_device_error();
+  if (ep_code == 5)
+    return fail(GEMB_INTERNAL, "%s: an expert-parallel flag barrier gave up waiting for a peer (check 5)", op);
   if (ep_code != 0)
-    return fail(GEMB_INTERNAL, "%s: an expert-parallel pull kernel skipped a row outside its buffers (check %d)", op, ep_code);
+    return fail(GEMB_INTERNAL, "%s: an expert-parallel kernel met positions outside its buffers and skipped or clamped them (check %d)", op, ep_code);
+  const int moe_code = moe_take_device_error();
+  if (moe_code == 1)
+    return fail(GEMB_DATA_LOSS, "%s: the router met a non-finite logit; the token got zero routing weights", op);
+  if (moe_code != 0)
+    return fail(GEMB_DATA_LOSS, "%s: an expert id outside [0, experts) reached the permutation and was clamped", op);
   return GEMB_OK;
 }
 

@@ -8,10 +8,31 @@
 // that decides routing is computed with a fixed operation order out of IEEE add / mul / fma /
 // div only, so expert ids, weights, counts and the permutation are reproducible bit for bit.
 #include <algorithm>
+#include <atomic>
 
 #include "common.cuh"
 
 namespace gemb {
+
+// Set by the routing kernels when they meet a state the router specification calls impossible
+// (MOE_ROUTER_SPEC.md:117-130): 1 = a non-finite router logit, 2 = an expert id outside
+// [0, experts) reached the permutation.  The offending access is skipped or replaced by an
+// in-range value, never dereferenced; gemb_check_device_status() reports and clears the word.
+__device__ int g_moe_error = 0;
+
+int moe_take_device_error() {
+  int code = 0;
+  if (cudaMemcpyFromSymbol(&code, g_moe_error, sizeof code) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  if (code != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_moe_error, &zero, sizeof zero);
+  }
+  return code;
+}
+
 namespace {
 
 // ---------------------------------------------------------------------------------------------
@@ -317,12 +338,27 @@ route_kernel(const float* __restrict__ logits, const float* __restrict__ per_exp
   float p[kMaxPerLane];
   float m = __ldg(lg + lane);
   p[0] = m;
+  bool finite = isfinite(m);
 #pragma unroll
   for (int j = 1; j < kMaxPerLane; ++j) {
     if (j < per_lane) {
       p[j] = __ldg(lg + lane + 32 * j);
+      finite = finite && isfinite(p[j]);
       m = fmaxf(m, p[j]);
     }
+  }
+  if (!__all_sync(0xFFFFFFFFu, finite)) {
+    // A NaN or infinite logit makes every probability of the token meaningless.  The state is
+    // recorded, and the token still gets in-range ids (its slot numbers) with zero weights so
+    // that nothing downstream indexes with garbage.
+    if (lane == 0) atomicCAS(&g_moe_error, 0, 1);
+    if (static_cast<uint32_t>(lane) < topk) {
+      ids[static_cast<uint64_t>(t) * topk + lane] = lane;
+      weights[static_cast<uint64_t>(t) * topk + lane] = 0.0f;
+    }
+    if (probs)
+      for (int j = 0; j < per_lane; ++j) probs[static_cast<uint64_t>(t) * experts + lane + 32 * j] = 0.0f;
+    return;
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
@@ -402,8 +438,15 @@ permute_count_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ bloc
   for (uint32_t e = threadIdx.x; e < experts; e += 128) smem_counts[e] = 0;
   __syncthreads();
   const uint32_t base = blockIdx.x * kSegment;
-  for (uint32_t i = threadIdx.x; i < kSegment; i += 128)
-    if (base + i < total) atomicAdd(&smem_counts[__ldg(ids + base + i)], 1);
+  for (uint32_t i = threadIdx.x; i < kSegment; i += 128) {
+    if (base + i >= total) continue;
+    uint32_t e = static_cast<uint32_t>(__ldg(ids + base + i));
+    if (e >= experts) {   // recorded, and counted under the last expert so that every position stays in range
+      atomicCAS(&g_moe_error, 0, 2);
+      e = experts - 1;
+    }
+    atomicAdd(&smem_counts[e], 1);
+  }
   __syncthreads();
   for (uint32_t e = threadIdx.x; e < experts; e += 128)
     block_counts[static_cast<uint64_t>(blockIdx.x) * experts + e] = smem_counts[e];
@@ -469,6 +512,8 @@ permute_scatter_kernel(const int32_t* __restrict__ ids, const int32_t* __restric
   for (int c = 0; c < 8; ++c) {
     const uint32_t i = base + c * 32 + lane;
     my_ids[c] = i < total ? __ldg(ids + i) : -1;
+    if (i < total && static_cast<uint32_t>(my_ids[c]) >= experts)
+      my_ids[c] = static_cast<int>(experts) - 1;   // same clamp as the count kernel, which recorded it
     if (my_ids[c] >= 0) atomicAdd(&warp_counts[warp * experts + my_ids[c]], 1);
   }
   __syncthreads();
@@ -673,15 +718,15 @@ int32_t validate_permute_geometry(const char* op, uint64_t tokens, uint64_t expe
 // The small-batch router kernel's ring needs more than the 48 KB a kernel gets without opting in.
 template <int kTpt>
 int32_t router_small_configure(const char* op) {
-  static bool configured[64] = {false};
+  static std::atomic<bool> configured[64];   // racing first calls both set the (idempotent) attribute
   int dev = 0;
   cudaGetDevice(&dev);
   dev &= 63;
-  if (!configured[dev]) {
+  if (!configured[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(router_logits_small_kernel<kTpt>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(sizeof(RouterSmallSmem<kTpt>)));
     if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
-    configured[dev] = true;
+    configured[dev].store(true, std::memory_order_release);
   }
   return GEMB_OK;
 }
@@ -809,7 +854,8 @@ static __device__ __align__(256) int32_t g_permute_scratch[kStaticMaxSegments * 
 
 // The array's name is only a host-side handle; kernels need its device address.  It is looked
 // up once per device, with that device current, and cached.
-static int32_t* g_permute_scratch_ptr[64] = {nullptr};
+// (Two host threads racing on a device's first call both store the same address.)
+static std::atomic<int32_t*> g_permute_scratch_ptr[64];
 
 static int32_t permute_scratch_address(const char* op, int32_t** out) {
   int dev = 0;
@@ -818,16 +864,16 @@ static int32_t permute_scratch_address(const char* op, int32_t** out) {
     cudaGetLastError();
     return fail(GEMB_UNSUPPORTED, "%s: no usable CUDA device", op);
   }
-  if (g_permute_scratch_ptr[dev] == nullptr) {
+  if (g_permute_scratch_ptr[dev].load(std::memory_order_acquire) == nullptr) {
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_permute_scratch);
     if (e != cudaSuccess || ptr == nullptr) {
       cudaGetLastError();
       return fail(GEMB_INTERNAL, "%s: cudaGetSymbolAddress: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
     }
-    g_permute_scratch_ptr[dev] = static_cast<int32_t*>(ptr);
+    g_permute_scratch_ptr[dev].store(static_cast<int32_t*>(ptr), std::memory_order_release);
   }
-  *out = g_permute_scratch_ptr[dev];
+  *out = g_permute_scratch_ptr[dev].load(std::memory_order_acquire);
   return GEMB_OK;
 }
 
@@ -836,7 +882,7 @@ int32_t gemb_moe_permute_static(const int32_t* top_ids, int32_t* counts, int32_t
                                 uint64_t topk, gemb_stream_t stream) {
   const char* op = "gemb_moe_permute_static";
   GEMB_REQUIRE(top_ids && counts && offsets && perm && slot_rows && plan, "%s: pointers must be nonnull", op);
-  GEMB_TRY(validate_moe_geometry(op, tokens, experts, topk));
+  GEMB_TRY(validate_permute_geometry(op, tokens, experts, topk));   // the same rules as gemb_moe_permute
   const uint64_t segments64 = moe_segments(tokens, topk);
   GEMB_REQUIRE(segments64 <= kStaticMaxSegments && experts <= kStaticMaxExperts,
                "%s: %llu assignments over %llu experts exceed the built-in scratch (at most %llu assignments, %llu "

@@ -207,10 +207,6 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
                : "memory");
 }
-// Shared -> TMEM copy of a 32-row x 128-bit block, broadcast to the four 32-lane quarters.
-__device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
-}
 // D[tmem] (+)= A[smem] * B[smem]^T with E2M1 operands and one UE4M3 scale per 16 K elements.
 __device__ __forceinline__ void tc_mma_nvfp4(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc,
                                              uint32_t idesc, uint32_t tmem_sfa, uint32_t tmem_sfb,

@@ -236,7 +236,7 @@ class EpPullMoeLayer:
         h, el, R = w.hidden, self.e_local, self.world
         main = torch.cuda.current_stream()
         lib.gemb_moe_ep_plan(self.counts_all, R, self.e_total, self.rank, self.l_plan, self.recv_prefix, self.recv_src,
-                             self.recv_dst, self.row_base, main)
+                             self.recv_dst, self.row_base, self.rows_max, self.tokens * self.topk, main)
         lib.gemb_moe_ep_pull_dispatch(self.send.table, R, el, self.recv_prefix, self.recv_src, self.recv_dst,
                                       self.a_packed, self.a_scales, h, self.msg_bytes, self.tokens * self.topk,
                                       self.rows_max, main)

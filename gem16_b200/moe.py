@@ -16,8 +16,14 @@ class MoeWeights:
     """Device-resident NVFP4 expert weights in the layout the grouped GEMM consumes."""
 
     def __init__(self, lib, dev, router_w, router_bias, gu_packed, gu_scales, gu_div, dn_packed, dn_scales, dn_div,
-                 shared=None):
+                 shared=None, keep_compact=False):
+        """keep_compact also keeps the row-major [rows, K/16] block scales as given (checkers
+        that dequantise the weights themselves want them; the kernels use the interleaved copies)."""
         self.dev = dev
+        if keep_compact:
+            self.gu_compact, self.dn_compact = gu_scales, dn_scales
+            self.shared_compact = None if shared is None else tuple(
+                (p.cpu().numpy(), s.cpu().numpy(), float(d)) for p, s, d in shared)
         self.experts, self.two_inter, half_h = gu_packed.shape       # experts held on this device
         self.hidden, self.inter = half_h * 2, self.two_inter // 2
         self.router_w = torch.as_tensor(router_w, device=dev).contiguous()
@@ -175,7 +181,7 @@ class MoeLayer:
 
 
 def synthetic_weights(dev, seed, hidden=2816, experts=128, inter=704, shared_inter=2112, zipf=True,
-                      expert_range=None, placement_ranks=1):
+                      expert_range=None, placement_ranks=1, keep_compact=False):
     """Seeded synthetic 26B-A4B-like layer generated and quantised on the GPU: router fp32 ~ N(0, 0.02)
     with a Zipf(1.1) bias (-1.1 ln(rank) over a seeded permutation, zero mean), NVFP4 expert and
     shared weights ~ N(0, 0.02) with per-tensor divisor 6*448/amax.  expert_range=(lo, hi) keeps
@@ -225,4 +231,4 @@ def synthetic_weights(dev, seed, hidden=2816, experts=128, inter=704, shared_int
         shared = (quant(2 * shared_inter, hidden), quant(hidden, shared_inter))
     return MoeWeights(lib, dev, router_w, bias, torch.stack([x[0] for x in gu]), torch.stack([x[1] for x in gu]),
                       [x[2] for x in gu], torch.stack([x[0] for x in dn]), torch.stack([x[1] for x in dn]),
-                      [x[2] for x in dn], shared)
+                      [x[2] for x in dn], shared, keep_compact=keep_compact)

@@ -80,13 +80,17 @@ int32_t gemb_device_check(void);
  * tile, 0 (automatic), 128 or 256; GEMB_TUNE_GEMV_IMPL = FP8 decode GEMV data path, 0 (automatic),
  * 1 (direct global loads) or 2 (bulk-copy ring through shared memory wherever it fits);
  * GEMB_TUNE_GEMM_PAIR = dense prefill GEMMs on CTA pairs (two SMs share one 256 x 256 tile and
- * each stages half of the weight tile), 0 (automatic), 1 (never) or 2 (always, when the tile is 256 wide). */
+ * each stages half of the weight tile), 0 (automatic), 1 (never) or 2 (always, when the tile is 256 wide);
+ * GEMB_TUNE_EP_BARRIER_SPINS = how many times gemb_moe_ep_barrier polls its flags before it gives
+ * up and records the fact (about 500 ns per poll; 0 = the default of 2^22, about three seconds) --
+ * a deployment's failure-detection latency, and what lets a test see the give-up path quickly. */
 enum {
   GEMB_TUNE_GEMV_ROWS = 1,
   GEMB_TUNE_GEMV_PDL = 2,
   GEMB_TUNE_GEMM_BN = 3,
   GEMB_TUNE_GEMV_IMPL = 4,
-  GEMB_TUNE_GEMM_PAIR = 5
+  GEMB_TUNE_GEMM_PAIR = 5,
+  GEMB_TUNE_EP_BARRIER_SPINS = 6
 };
 int32_t gemb_set_tuning(int32_t knob, int32_t value);
 /* Bytes of an INTERLEAVED scale buffer for `rows` rows of K elements. */
@@ -466,9 +470,12 @@ int32_t gemb_output_head_argmax(const void* candidates, uint64_t rows, uint32_t*
  * R device addresses, host array) into payload [rows, hidden/2] + INTERLEAVED scales.
  * gemb_moe_ep_pull_combine is gemb_moe_combine with every expert row read from its owner's output
  * buffer (peer_expert_outputs_host: R device addresses of bf16 [rows, hidden]).
- * send_rows_per_rank / padded_rows_max are the capacities of the send and of the padded buffers: a
- * position outside them (counts that are not what the protocol promises) is skipped and recorded,
- * and gemb_check_device_status() then reports it, instead of the access faulting. */
+ * send_rows_per_rank / padded_rows_max (capacity_rows for the plan) are the capacities of the send
+ * and of the padded buffers.  Counts that are not what the protocol promises (negative, more rows
+ * than a rank can send, more padded rows than the capacity -- e.g. read after a barrier gave up)
+ * make gemb_moe_ep_plan write an EMPTY plan and record the fact; a single position outside a
+ * buffer is skipped and recorded by the pull kernels; gemb_check_device_status() then reports it,
+ * instead of an access faulting. */
 /* Ordering between the GPUs without a collective library.  gemb_moe_ep_barrier: rank `rank` bumps
  * its device-resident epoch for barrier `which` (0 or 1; local_epochs holds two words, zero at
  * start), stores it to slot [which][rank] of every rank's flag array (peer_flag_arrays_host: R device
@@ -484,7 +491,8 @@ int32_t gemb_moe_ep_gather_counts(const uint64_t* peer_count_buffers_host, uint6
 uint64_t gemb_moe_ep_plan_ints(uint64_t capacity_rows, uint64_t local_experts);
 int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t experts, uint64_t rank,
                          int32_t* plan, int32_t* recv_prefix, int32_t* recv_src_rows,
-                         int32_t* recv_dst_rows, int32_t* combine_row_base, gemb_stream_t stream);
+                         int32_t* recv_dst_rows, int32_t* combine_row_base, uint64_t capacity_rows,
+                         uint64_t send_rows_per_rank, gemb_stream_t stream);
 int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers_host, uint64_t ranks,
                                   uint64_t local_experts, const int32_t* recv_prefix,
                                   const int32_t* recv_src_rows, const int32_t* recv_dst_rows,
@@ -517,9 +525,12 @@ int32_t gemb_moe_combine(const uint16_t* y_bf16, const int32_t* slot_rows, const
                          const uint16_t* shared_bf16, uint16_t* out_bf16, uint64_t tokens,
                          uint64_t hidden, uint64_t topk, gemb_stream_t stream);
 
-/* Synchronises the device and reports whether a GEMM or GEMV kernel gave up on a bounded pipeline wait
- * since the last call (GEMB_INTERNAL, flag cleared) or not (GEMB_OK).  The reference has no
- * counterpart: its kernels have no device-side waits. */
+/* Synchronises the device and reports what the kernels recorded since the last call (the record is
+ * cleared): a GEMM, GEMV or flag-barrier wait that ran out, an expert-parallel position outside its
+ * buffers (GEMB_INTERNAL); a non-finite router logit or an out-of-range expert id, the states
+ * MOE_ROUTER_SPEC.md:117-130 wants visible rather than repaired (GEMB_DATA_LOSS); else GEMB_OK.
+ * The kernels themselves never fault on such input: they skip or clamp the access.  The reference
+ * has no counterpart: its kernels have no device-side waits. */
 int32_t gemb_check_device_status(void);
 
 /* ------------------------------------------------------------------------------------------

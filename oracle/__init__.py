@@ -55,6 +55,9 @@ class Oracle:
         ]:
             fn = getattr(L, p + name)
             fn.restype, fn.argtypes = res, args
+        if ref:
+            L.ref_rmsnorm.restype = C.c_int
+            L.ref_rmsnorm.argtypes = [_f32p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_float, _f32p]
         if not ref:
             L.orc_det_exp.restype, L.orc_det_exp.argtypes = C.c_float, [C.c_float]
             L.orc_f32_to_bf16_array.argtypes = [_f32p, _u16p, C.c_uint64]
@@ -147,6 +150,18 @@ class Oracle:
         return out
 
     def det_exp(self, x): return self.lib.orc_det_exp(x)
+
+    def ref_rmsnorm(self, x, weight, eps):
+        """gem16::layer::RmsNorm of the compiled reference (binary64 sums, fp32 out, no bf16 boundary)."""
+        assert self.ref
+        x = np.ascontiguousarray(x, np.float32)
+        t, k = x.shape
+        out = np.zeros_like(x)
+        wv = None if weight is None else np.ascontiguousarray(weight, np.float32)
+        rc = self.lib.ref_rmsnorm(x, None if wv is None else wv.ctypes.data, t, k, eps, out)
+        if rc:
+            raise ValueError(f"reference RmsNorm rejected its input (status {rc})")
+        return out
 
     def rmsnorm_bf16(self, x, w_bf16, eps):
         x = np.ascontiguousarray(x, np.float32)

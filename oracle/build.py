@@ -2,10 +2,11 @@
 
 Two shared objects:
   oracle/libgemb_oracle.so   -- gemb_oracle.cpp, our restatement of the reference contract.
-  oracle/_ref/libgem16_ref.so -- the UNMODIFIED gem16 sources src/numeric/{nvfp4,fp8}.cpp compiled
-                                 where they lie under $GEM16_REFERENCE (default /root/reference)
-                                 plus ref_wrap.cpp.  Only built when that tree is present; the
-                                 prebuilt file is used otherwise.
+  oracle/_ref/libgem16_ref.so -- the UNMODIFIED gem16 sources src/numeric/{nvfp4,fp8,layer}.cpp
+                                 compiled where they lie under $GEM16_REFERENCE (a checkout of
+                                 gem16; without the variable, a `reference` directory beside this
+                                 repository) plus ref_wrap.cpp.  Only built when that tree is
+                                 present; the prebuilt file is used otherwise.
 Nothing from the reference tree is copied into this repository.
 """
 from __future__ import annotations
@@ -15,7 +16,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("GEM16_REFERENCE", "/root/reference")
+REF_ROOT = os.environ.get("GEM16_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 ORACLE_SO = os.path.join(HERE, "libgemb_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libgem16_ref.so")
@@ -48,6 +49,7 @@ def build_ref(force: bool = False) -> str | None:
         return REF_SO if os.path.exists(REF_SO) else None
     srcs = [os.path.join(REF_ROOT, "src", "numeric", "nvfp4.cpp"),
             os.path.join(REF_ROOT, "src", "numeric", "fp8.cpp"),
+            os.path.join(REF_ROOT, "src", "numeric", "layer.cpp"),
             os.path.join(HERE, "ref_wrap.cpp")]
     if force or _stale(REF_SO, srcs):
         os.makedirs(REF_DIR, exist_ok=True)

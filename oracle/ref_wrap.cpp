@@ -1,5 +1,5 @@
 // C entry points around the UNMODIFIED gem16 CPU numeric sources (src/numeric/nvfp4.cpp,
-// src/numeric/fp8.cpp), which the build recipe compiles from the reference tree where it lies.
+// src/numeric/fp8.cpp, src/numeric/layer.cpp), which the build recipe compiles from the reference tree where it lies.
 // TEST INFRASTRUCTURE ONLY: used to pin gemb_oracle.cpp and as the timed CPU reference arm.
 // The reference functions are called as they are; this file only loops over rows with threads.
 #include <atomic>
@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "gem16/fp8.h"
+#include "gem16/layer.h"
 #include "gem16/nvfp4.h"
 
 namespace {
@@ -128,6 +129,15 @@ int ref_fp8_matmul(const uint8_t* a, const float* a_scales, const uint8_t* w,
     }
   });
   return status.load();
+}
+
+// gem16::layer::RmsNorm (binary64 accumulation, fp32 result, no bf16 boundary); weight may be null.
+int ref_rmsnorm(const float* x, const float* weight, uint64_t tokens, uint64_t k, float eps, float* out) {
+  auto r = gem16::layer::RmsNorm(std::span<const float>(x, tokens * k),
+                                 weight ? std::span<const float>(weight, k) : std::span<const float>(), tokens, k, eps);
+  if (!r.ok()) return static_cast<int>(r.status().code());
+  std::copy(r.value().begin(), r.value().end(), out);
+  return 0;
 }
 
 }  // extern "C"

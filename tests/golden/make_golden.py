@@ -1,12 +1,14 @@
 """Generates tests/golden/linear_path.npz from the gem16 reference itself.
 
-Run in a container that holds the reference tree (default /root/reference):
+Run where a checkout of gem16 is present ($GEM16_REFERENCE, or a `reference` directory beside this
+repository):
 
     python tests/golden/make_golden.py
 
 Inputs are seeded numpy arrays; outputs come from the UNMODIFIED reference functions
 gem16::nvfp4::QuantizeActivation / ReferenceDotProduct and gem16::fp8::QuantizeToken /
-ReferenceDotProduct (src/numeric/nvfp4.cpp, src/numeric/fp8.cpp) compiled by oracle/build.py.
+ReferenceDotProduct and gem16::layer::RmsNorm (src/numeric/nvfp4.cpp, src/numeric/fp8.cpp,
+src/numeric/layer.cpp) compiled by oracle/build.py.
 The GPU box has no reference tree; it only reads the committed .npz.
 """
 import os
@@ -79,6 +81,16 @@ def main():
     out["codec_probes"] = probes
     out["codec_e4m3"] = np.array([ref.e4m3_encode(float(v)) for v in probes], np.uint8)
     out["codec_e2m1"] = np.array([ref.e2m1_encode(float(v)) for v in probes], np.uint8)
+
+    # RMSNorm (gem16::layer::RmsNorm: binary64 sums, fp32 result) with and without a learned weight;
+    # the weight is bf16-representable because the device kernels take it as bf16.
+    xn = bf16_round(rng.standard_normal((9, 704)).astype(np.float32) * 3.0)
+    xn[1] *= 1e-3
+    xn[2] *= 200.0
+    xn[3, 1:] = 0.0
+    wn = bf16_round((1.0 + 0.2 * rng.standard_normal(704)).astype(np.float32))
+    out.update(rms_x=xn, rms_w=wn, rms_eps=np.float32(1e-6), rms_y=ref.ref_rmsnorm(xn, wn, 1e-6),
+               rms_y_noweight=ref.ref_rmsnorm(xn, None, 1e-6))
 
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "linear_path.npz")
     np.savez_compressed(path, **out)

@@ -73,7 +73,7 @@ def test_shim_compiles_against_the_reference_headers():
     # definition whose signature matches no reference declaration into an error.
     import os
     import subprocess
-    ref = os.environ.get("GEM16_REFERENCE", "/root/reference")
+    from oracle.build import REF_ROOT as ref      # $GEM16_REFERENCE, or `reference` beside this repository
     if not os.path.isfile(os.path.join(ref, "src", "cuda", "nvfp4", "sm120.h")):
         pytest.skip("reference tree not present")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

@@ -22,7 +22,7 @@ def fixture_module(rows=8, k=64, seed=0):
     scale[0, 0] = FIXTURE_SCALE
     return {"m.weight_packed": ("U8", packed), "m.weight_scale": ("F8_E4M3", scale),
             "m.weight_global_scale": ("F32", np.array([FIXTURE_DIVISOR], np.float32)),
-            "m.input_global_scale": ("F32", np.array(1.0, np.float32))}
+            "m.input_global_scale": ("F32", np.array([1.0], np.float32))}
 
 
 def test_container_round_trip_and_nibble_order(tmp_path):
@@ -70,6 +70,15 @@ def test_validation_rules(tmp_path, lib, dev):
                  lambda m: m.__setitem__("m.weight_scale", ("F8_E4M3", m["m.weight_scale"][1][:, :3])),   # wrong shape
                  lambda m: m["m.weight_scale"][1].__setitem__((2, 1), 0x7F),                              # NaN scale byte
                  lambda m: m.__setitem__("m.weight_global_scale", ("F32", np.array([0.0], np.float32))),  # bad divisor
+                 # global scales: both present, F32, shape [1] (src/model/manifest.cpp:346-365).  A BF16 divisor
+                 # read as its 16-bit pattern (0x4300 = 128.0 would become 17152.0) would pass a value check.
+                 lambda m: m.__setitem__("m.weight_global_scale", ("BF16", np.array([0x4300], np.uint16))),
+                 lambda m: m.__setitem__("m.input_global_scale", ("F16", np.array([0x3C00], np.uint16))),
+                 lambda m: m.pop("m.input_global_scale"),
+                 lambda m: m.pop("m.weight_global_scale"),
+                 lambda m: m.__setitem__("m.input_global_scale", ("F32", np.array(1.0, np.float32))),        # shape []
+                 lambda m: m.__setitem__("m.weight_global_scale", ("F32", np.array([[9600.0]], np.float32))),  # shape [1, 1]
+                 lambda m: m.__setitem__("m.input_global_scale", ("F32", np.array([1.0, 1.0], np.float32))),
                  lambda m: m.__setitem__("m.weight_packed", ("U8", m["m.weight_packed"][1][:, :24]))):    # K = 48
         with pytest.raises(CheckpointError):
             attempt(edit)
@@ -117,10 +126,11 @@ def test_expert_stack_and_fp8_module(tmp_path, lib, dev, orc):
     path = str(tmp_path / "e.safetensors")
     write_safetensors(path, {"x.weight_packed": ("U8", packed), "x.weight_scale": ("F8_E4M3", scale),
                              "x.weight_global_scale": ("F32", np.array([100.0, 200.0, 300.0], np.float32)),
+                             "x.input_global_scale": ("F32", np.array([7.0, 8.0, 9.0], np.float32)),
                              "q.weight": ("F8_E4M3", wq), "q.weight_scale": ("BF16", orc.to_bf16(wsc).reshape(-1, 1))})
     st = SafetensorsFile(path)
     w = load_nvfp4_linear(st, "x", dev, lib)
-    assert w.experts == 3 and w.weight_divisor == [100.0, 200.0, 300.0] and w.input_divisor is None
+    assert w.experts == 3 and w.weight_divisor == [100.0, 200.0, 300.0] and w.input_divisor == [7.0, 8.0, 9.0]
     per = lib.cdll.gemb_interleaved_scale_bytes(rows, k)
     got = w.interleaved_scales.cpu().numpy()
     for e in range(experts):

@@ -60,11 +60,11 @@ def test_ep_plan_rejects_bad_geometry(lib, dev):
     from gem16_b200.lib import GembError
     z = torch.zeros((64,), dtype=torch.int32, device=dev)
     with pytest.raises(GembError):
-        lib.gemb_moe_ep_plan(z, 3, 128, 0, z, z, z, z, z, None)      # experts not a multiple of ranks
+        lib.gemb_moe_ep_plan(z, 3, 128, 0, z, z, z, z, z, 128, 128, None)      # experts not a multiple of ranks
     with pytest.raises(GembError):
-        lib.gemb_moe_ep_plan(z, 2, 128, 2, z, z, z, z, z, None)      # rank out of range
+        lib.gemb_moe_ep_plan(z, 2, 128, 2, z, z, z, z, z, 128, 128, None)      # rank out of range
     with pytest.raises(GembError):
-        lib.gemb_moe_ep_plan(None, 2, 128, 0, z, z, z, z, z, None)
+        lib.gemb_moe_ep_plan(None, 2, 128, 0, z, z, z, z, z, 128, 128, None)
 
 
 def test_pull_dispatch_skips_rows_outside_the_buffers(lib, dev):
@@ -118,3 +118,67 @@ def test_flag_barrier_and_count_gather_single_rank(lib, dev):
         lib.gemb_moe_ep_barrier(table, 1, 0, 2, epochs, None)      # only barriers 0 and 1 exist
     with pytest.raises(GembError):
         lib.gemb_moe_ep_barrier(table, 1, 1, 0, epochs, None)      # rank out of range
+
+
+def test_flag_barrier_gives_up_and_reports(lib, dev):
+    """The failure-detection path of the expert-parallel layer: a rank whose peer never reaches the barrier.
+    Two ranks are declared, both flag arrays are buffers of this GPU, and only rank 0's barrier kernel
+    ever runs, so the second slot of its array stays behind.  With the poll limit turned down to about a
+    millisecond the kernel gives up, returns, and leaves code 5 for gemb_check_device_status (kInternal,
+    reported once); the context stays usable and the next launch works.  Nothing here waits on
+    another kernel: the flag is simply never written."""
+    import ctypes as C
+    from gem16_b200.lib import GembError
+    mine = torch.zeros((32,), dtype=torch.int32, device=dev)
+    theirs = torch.zeros((32,), dtype=torch.int32, device=dev)
+    epochs = torch.zeros((2,), dtype=torch.int32, device=dev)
+    table = (C.c_uint64 * 2)(mine.data_ptr(), theirs.data_ptr())
+    lib.gemb_set_tuning(6, 2000)          # GEMB_TUNE_EP_BARRIER_SPINS: 2,000 polls of about 500 ns
+    try:
+        lib.gemb_moe_ep_barrier(table, 2, 0, 0, epochs, None)
+        torch.cuda.synchronize()
+        with pytest.raises(GembError) as err:
+            lib.gemb_check_device_status()
+        assert err.value.status_name == "kInternal" and "barrier" in str(err.value)
+        lib.gemb_check_device_status()                       # the record is cleared once read
+        # rank 0 did publish its epoch to both arrays before it gave up
+        assert int(mine[0]) == 1 and int(theirs[0]) == 1 and int(mine[1]) == 0
+        # once the peer's flag arrives (written here by the host), the same barrier passes
+        mine[1] = 2
+        lib.gemb_moe_ep_barrier(table, 2, 0, 0, epochs, None)
+        torch.cuda.synchronize()
+        lib.gemb_check_device_status()
+        assert epochs.tolist() == [2, 0]
+    finally:
+        lib.gemb_set_tuning(6, 0)
+
+
+def test_plan_with_impossible_counts_is_empty_and_recorded(lib, dev):
+    """Counts that the protocol cannot produce (what a rank would read if it went on after a barrier gave
+    up): more padded rows than the buffers hold, a negative count, more rows than a rank can send.  The plan
+    kernel writes an empty plan and records code 6; the grouped GEMM then has no tile to run and the
+    combine skips every row."""
+    from gem16_b200.lib import GembError
+    ranks, experts, el, cap, send_rows = 2, 8, 4, 1024, 256
+    i32 = dict(dtype=torch.int32, device=dev)
+
+    def plan_for(counts):
+        plan = torch.full((lib.cdll.gemb_moe_ep_plan_ints(cap, el),), 77, **i32)
+        prefix, src, dst = torch.full((ranks * el + 1,), 77, **i32), torch.full((ranks * el,), 77, **i32), torch.full((ranks * el,), 77, **i32)
+        base = torch.full((experts,), 77, **i32)
+        lib.gemb_moe_ep_plan(torch.tensor(counts, **i32), ranks, experts, 0, plan, prefix, src, dst, base, cap, send_rows, None)
+        torch.cuda.synchronize()
+        return plan.cpu().numpy(), prefix.cpu().numpy(), base.cpu().numpy()
+
+    good = [[30, 30, 30, 30, 34, 34, 34, 34], [10, 20, 30, 40, 39, 39, 39, 39]]
+    plan, prefix, base = plan_for(good)
+    lib.gemb_check_device_status()
+    assert plan[0] == 4 and plan[1] == 512 and prefix[-1] == 220
+    for bad in ([[200, 200, 200, 200, 0, 0, 0, 0], [250, 250, 250, 250, 0, 0, 0, 0]],      # 4 x 512 padded rows > 1,024; 800 > 256 sent
+                [[30, -1, 30, 30, 34, 34, 34, 34], good[1]],                                # a negative count
+                [[64, 64, 64, 64, 1, 0, 0, 0], good[1]]):                                   # rank 0 would have sent 257 rows
+        plan, prefix, base = plan_for(bad)
+        with pytest.raises(GembError) as err:
+            lib.gemb_check_device_status()
+        assert err.value.status_name == "kInternal"
+        assert plan[0] == 0 and plan[1] == 0 and not prefix.any() and (base < -cap).all()

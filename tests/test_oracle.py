@@ -138,6 +138,25 @@ def test_against_compiled_reference(orc):
     assert np.array_equal(orc.fp8_matmul(q1[0], q1[1], wq, bf16_bits(wsc)), ref.fp8_matmul(q1[0], q1[1], wq, bf16_bits(wsc)))
 
 
+def test_rmsnorm_restatement_against_reference_vectors(orc, golden):
+    """orc.rmsnorm_bf16 restates the DEVICE contract (fp32 partial sums folded by a tree, fp32 1/sqrt,
+    bf16 result: src/cuda/nvfp4/reference.cu:92-135); the vectors are gem16::layer::RmsNorm
+    (src/numeric/layer.cpp:27-63: binary64 sums, fp32 result).  After the same bf16 rounding the two may
+    differ only where the fp32 arithmetic moved a value across a rounding boundary: at most one bf16
+    step, on well under 2 % of the elements."""
+    x, w, eps = golden["rms_x"], golden["rms_w"], float(golden["rms_eps"])
+    for weight, want in ((bf16_bits(w), golden["rms_y"]), (None, golden["rms_y_noweight"])):
+        got = bf16_bits(orc.rmsnorm_bf16(x, weight, eps)).astype(np.int64)
+        ref_bits = bf16_bits(want).astype(np.int64)
+        assert np.abs(got - ref_bits).max() <= 1
+        assert (got != ref_bits).mean() < 0.02, (got != ref_bits).mean()
+    from oracle import Oracle, ref_available
+    if ref_available():       # and the compiled reference still gives the committed vectors
+        ref = Oracle(ref=True)
+        assert np.array_equal(ref.ref_rmsnorm(x, w, eps), golden["rms_y"])
+        assert np.array_equal(ref.ref_rmsnorm(x, None, eps), golden["rms_y_noweight"])
+
+
 def test_interleave_layout(orc):
     # src/cuda/nvfp4/cutlass_sm120.cu:160-194
     rows, k = 130, 16 * 6

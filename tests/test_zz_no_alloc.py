@@ -40,7 +40,8 @@ def run(lib, dev, ids, experts, static):
 def test_static_scratch_matches_workspace_variant_twice_in_a_row(lib, dev):
     # two back-to-back calls: a large problem first, then a smaller one that reuses (and must not
     # be disturbed by) the cells the first call left behind, then the large one again
-    problems = [(4096, 128, 8, 1), (300, 64, 4, 2), (4096, 128, 8, 3), (16384, 128, 8, 4)]
+    # (16 experts with top-1 is the sort an expert-parallel receiver does over its local experts)
+    problems = [(4096, 128, 8, 1), (300, 64, 4, 2), (4096, 128, 8, 3), (16384, 128, 8, 4), (777, 16, 1, 5), (50, 3, 2, 6)]
     for tokens, experts, topk, seed in problems:
         ids = routed_ids(tokens, experts, topk, seed)
         got = run(lib, dev, ids, experts, static=True)
