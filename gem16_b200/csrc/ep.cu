@@ -24,6 +24,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "moe_layer.h"
 
 namespace gemb {
 
@@ -66,12 +67,12 @@ struct PeerPtrs {
   const uint8_t* p[kMaxRanks];
 };
 
-// One CTA.  counts_all: [ranks][experts].
-__global__ void __launch_bounds__(256)
-ep_plan_kernel(const int32_t* __restrict__ counts_all, uint32_t ranks, uint32_t experts, uint32_t me,
-               int32_t* __restrict__ plan, int32_t* __restrict__ recv_prefix, int32_t* __restrict__ recv_src,
-               int32_t* __restrict__ recv_dst, int32_t* __restrict__ out_base, uint32_t capacity_rows,
-               uint32_t send_rows) {
+// One CTA.  counts_all: [ranks][experts].  tile_rows (optional): real rows of every 128-row tile.
+__device__ __forceinline__ void
+ep_plan_body(const int32_t* counts_all, uint32_t ranks, uint32_t experts, uint32_t me,
+             int32_t* __restrict__ plan, int32_t* __restrict__ recv_prefix, int32_t* __restrict__ recv_src,
+             int32_t* __restrict__ recv_dst, int32_t* __restrict__ out_base, uint32_t capacity_rows,
+             uint32_t send_rows, int32_t* __restrict__ tile_rows) {
   extern __shared__ int sm[];
   const uint32_t el = experts / ranks;
   // Counts that cannot be (negative, more than a rank can send, or more padded rows than the
@@ -155,7 +156,10 @@ ep_plan_kernel(const int32_t* __restrict__ counts_all, uint32_t ranks, uint32_t 
     const uint32_t ge = me * el + e;
     plan[2 + e] = pad[ge];
     const int end = pad[ge] + (tot[ge] + 127) / 128 * 128;
-    for (int tile = pad[ge] / 128; tile < end / 128; ++tile) tile_expert[tile] = static_cast<int32_t>(e);
+    for (int tile = pad[ge] / 128; tile < end / 128; ++tile) {
+      tile_expert[tile] = static_cast<int32_t>(e);
+      if (tile_rows != nullptr) tile_rows[tile] = min(128, tot[ge] - (tile * 128 - pad[ge]));
+    }
   }
   // Segments (source s, local expert e) in source-major order.
   if (threadIdx.x == 0) {
@@ -180,6 +184,15 @@ ep_plan_kernel(const int32_t* __restrict__ counts_all, uint32_t ranks, uint32_t 
   }
 }
 
+__global__ void __launch_bounds__(256)
+ep_plan_kernel(const int32_t* __restrict__ counts_all, uint32_t ranks, uint32_t experts, uint32_t me,
+               int32_t* __restrict__ plan, int32_t* __restrict__ recv_prefix, int32_t* __restrict__ recv_src,
+               int32_t* __restrict__ recv_dst, int32_t* __restrict__ out_base, uint32_t capacity_rows,
+               uint32_t send_rows, int32_t* __restrict__ tile_rows) {
+  ep_plan_body(counts_all, ranks, experts, me, plan, recv_prefix, recv_src, recv_dst, out_base, capacity_rows, send_rows,
+               tile_rows);
+}
+
 // Cross-GPU barrier on flags in peer-mapped memory: every rank bumps its own epoch for barrier
 // `which`, publishes it to slot [which][rank] of every rank's flag array (release, system scope)
 // and waits until all slots of its own array have reached that epoch (acquire).  The kernels
@@ -189,10 +202,10 @@ ep_plan_kernel(const int32_t* __restrict__ counts_all, uint32_t ranks, uint32_t 
 // records the fact and returns (the launches that follow then work on stale data and the caller
 // sees the error at its next gemb_check_device_status()).
 // One warp; the ranks run on different GPUs (never several ranks of one barrier on the same GPU).
-__global__ void __launch_bounds__(32)
-ep_barrier_kernel(PeerPtrs flag_arrays, uint32_t ranks, uint32_t me, uint32_t which, uint32_t* __restrict__ epochs,
-                  uint32_t spin_limit) {
-  const uint32_t lane = threadIdx.x;
+__device__ __forceinline__ void
+ep_barrier_warp(const PeerPtrs& flag_arrays, uint32_t ranks, uint32_t me, uint32_t which, uint32_t* __restrict__ epochs,
+                uint32_t spin_limit) {
+  const uint32_t lane = threadIdx.x & 31;
   uint32_t e = 0;
   if (lane == 0) {
     e = epochs[which] + 1;
@@ -214,6 +227,94 @@ ep_barrier_kernel(PeerPtrs flag_arrays, uint32_t ranks, uint32_t me, uint32_t wh
   }
 }
 
+__global__ void __launch_bounds__(32)
+ep_barrier_kernel(PeerPtrs flag_arrays, uint32_t ranks, uint32_t me, uint32_t which, uint32_t* __restrict__ epochs,
+                  uint32_t spin_limit) {
+  ep_barrier_warp(flag_arrays, ranks, me, which, epochs, spin_limit);
+}
+
+// Barrier 0, the read of every rank's per-expert counts and the position arithmetic in ONE launch
+// of one CTA: warp 0 runs the flag barrier (when `barrier` is set; its acquire loads order the
+// reads below after the peers' writes), then all threads copy the peers' counts into counts_all
+// (when `gather` is set; otherwise counts_all is the caller's) and the CTA derives the plan.
+__global__ void __launch_bounds__(256)
+ep_sync_plan_kernel(PeerPtrs flag_arrays, PeerPtrs count_buffers, uint32_t ranks, uint32_t experts, uint32_t me,
+                    uint32_t* __restrict__ epochs, uint32_t spin_limit, int barrier, int gather,
+                    int32_t* __restrict__ counts_all, int32_t* __restrict__ plan, int32_t* __restrict__ recv_prefix,
+                    int32_t* __restrict__ recv_src, int32_t* __restrict__ recv_dst, int32_t* __restrict__ out_base,
+                    uint32_t capacity_rows, uint32_t send_rows, int32_t* __restrict__ tile_rows) {
+  if (barrier && threadIdx.x < 32) ep_barrier_warp(flag_arrays, ranks, me, 0, epochs, spin_limit);
+  __syncthreads();
+  if (gather) {
+    for (uint32_t i = threadIdx.x; i < ranks * experts; i += blockDim.x) {
+      const uint32_t s = i / experts, e = i % experts;
+      int32_t v;
+      asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(reinterpret_cast<const int32_t*>(count_buffers.p[s]) + e) : "memory");
+      counts_all[i] = v;
+    }
+    __syncthreads();
+  }
+  ep_plan_body(counts_all, ranks, experts, me, plan, recv_prefix, recv_src, recv_dst, out_base, capacity_rows, send_rows,
+               tile_rows);
+}
+
+// Quantises each local token once (EXACT NVFP4 contract, src/numeric/nvfp4.cpp:139-150) and writes one
+// message row per assignment -- payload | compact block scales | assignment index (token * topk +
+// slot) -- at the assignment's position in (expert, token, slot) order, which groups the rows by
+// owner.  The position follows from the permutation's outputs: offsets[e] + (slot_rows[i] -
+// padded_offset[e]).  One CTA per token, one thread per 16-element block.
+__global__ void __launch_bounds__(256)
+ep_pack_kernel(const uint16_t* __restrict__ x, const int32_t* __restrict__ ids, const int32_t* __restrict__ slot_rows,
+               const int32_t* __restrict__ offsets, const int32_t* __restrict__ plan, uint8_t* __restrict__ send,
+               uint32_t hidden, uint32_t topk, uint32_t experts, uint32_t msg_bytes, uint32_t send_rows, float g) {
+  const uint32_t t = blockIdx.x;
+  __shared__ int pos[32];
+  extern __shared__ __align__(16) uint8_t pack_sc[];   // the token's hidden/16 scale bytes
+  if (threadIdx.x < topk) {
+    const uint64_t i = static_cast<uint64_t>(t) * topk + threadIdx.x;
+    const uint32_t e = static_cast<uint32_t>(__ldg(ids + i));
+    int pp = -1;
+    if (e < experts) {
+      const int64_t q = static_cast<int64_t>(__ldg(offsets + e)) + __ldg(slot_rows + i) - __ldg(plan + 2 + e);
+      if (q >= 0 && q < static_cast<int64_t>(send_rows)) pp = static_cast<int>(q);
+    }
+    if (pp < 0) atomicCAS(&g_ep_error, 0, 7);   // cannot be; the row is not written
+    pos[threadIdx.x] = pp;
+  }
+  __syncthreads();
+  const uint32_t blocks = hidden / 16;
+  for (uint32_t c = threadIdx.x; c < blocks; c += blockDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<uint64_t>(t) * hidden + c * 16);
+    const uint4 a = __ldg(src), b = __ldg(src + 1);
+    const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[2 * i] = __uint_as_float(ww[i] << 16);
+      v[2 * i + 1] = __uint_as_float(ww[i] & 0xFFFF0000u);
+    }
+    uint32_t lo, hi;
+    uint8_t sb;
+    quantize_block16<false>(v, g, lo, hi, sb);
+    pack_sc[c] = sb;
+    for (uint32_t s = 0; s < topk; ++s)
+      if (pos[s] >= 0)
+        *reinterpret_cast<uint2*>(send + static_cast<uint64_t>(pos[s]) * msg_bytes + c * 8) = make_uint2(lo, hi);
+  }
+  __syncthreads();
+  // the scales as 16-byte pieces (hidden is a multiple of 256, so hidden / 16 bytes are whole pieces), then the index
+  const uint32_t pieces = blocks / 16;
+  for (uint32_t idx = threadIdx.x; idx < pieces * topk; idx += blockDim.x) {
+    const uint32_t s = idx / pieces, q = idx % pieces;
+    if (pos[s] >= 0)
+      *reinterpret_cast<uint4*>(send + static_cast<uint64_t>(pos[s]) * msg_bytes + hidden / 2 + q * 16) =
+          *reinterpret_cast<const uint4*>(pack_sc + q * 16);
+  }
+  if (threadIdx.x < topk && pos[threadIdx.x] >= 0)
+    *reinterpret_cast<int32_t*>(send + static_cast<uint64_t>(pos[threadIdx.x]) * msg_bytes + hidden / 2 + hidden / 16) =
+        static_cast<int32_t>(t * topk + threadIdx.x);
+}
+
 // counts_all[s][e] = the per-expert counts rank s left in its peer-mapped buffer.
 __global__ void __launch_bounds__(256)
 ep_gather_counts_kernel(PeerPtrs count_buffers, uint32_t ranks, uint32_t experts, int32_t* __restrict__ counts_all) {
@@ -229,7 +330,7 @@ __global__ void __launch_bounds__(256)
 ep_pull_dispatch_kernel(PeerPtrs peers, const int32_t* __restrict__ recv_prefix, const int32_t* __restrict__ recv_src,
                         const int32_t* __restrict__ recv_dst, uint32_t segments, uint32_t el, uint32_t hidden,
                         uint32_t msg_bytes, uint32_t c_pad, uint8_t* __restrict__ packed,
-                        uint8_t* __restrict__ scales, uint32_t send_rows, uint32_t rows_max) {
+                        uint8_t* __restrict__ scales, uint32_t send_rows, uint32_t rows_max, int2* __restrict__ row_meta) {
   extern __shared__ int sm[];
   int* prefix = sm;  // [segments + 1]
   for (uint32_t i = threadIdx.x; i <= segments; i += blockDim.x) prefix[i] = recv_prefix[i];
@@ -257,6 +358,9 @@ ep_pull_dispatch_kernel(PeerPtrs peers, const int32_t* __restrict__ recv_prefix,
       continue;
     }
     const uint8_t* src = peers.p[lo / el] + srow * msg_bytes;
+    // Where the row's result has to go: {source rank, the assignment index the source wrote behind the scales}.
+    if (row_meta != nullptr && lane == 0)
+      row_meta[d] = make_int2(static_cast<int>(lo / el), *reinterpret_cast<const int32_t*>(src + hidden / 2 + hidden / 16));
     // All of a lane's loads of the row (over NVLink for a remote source) are issued before its first
     // store: a row is small, so the loads in flight per warp are what hides the link latency.
     for (uint32_t v0 = 0; v0 < payload_vecs; v0 += 128) {
@@ -428,7 +532,7 @@ int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t exp
   ep_plan_kernel<<<1, 256, 4 * experts * sizeof(int), stream>>>(
       counts_all, static_cast<uint32_t>(ranks), static_cast<uint32_t>(experts), static_cast<uint32_t>(rank), plan,
       recv_prefix, recv_src_rows, recv_dst_rows, combine_row_base, static_cast<uint32_t>(capacity_rows),
-      static_cast<uint32_t>(send_rows_per_rank));
+      static_cast<uint32_t>(send_rows_per_rank), nullptr);
   return check_launch(op);
 }
 
@@ -519,7 +623,7 @@ int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers_host, uint64
   ep_pull_dispatch_kernel<<<static_cast<unsigned>(sm_count()) * 8, 256, (segments + 1) * sizeof(int), stream>>>(
       peers, recv_prefix, recv_src_rows, recv_dst_rows, segments, static_cast<uint32_t>(local_experts),
       static_cast<uint32_t>(hidden), static_cast<uint32_t>(message_row_bytes), c_pad, packed_e2m1, interleaved_scales,
-      static_cast<uint32_t>(send_rows_per_rank), static_cast<uint32_t>(padded_rows_max));
+      static_cast<uint32_t>(send_rows_per_rank), static_cast<uint32_t>(padded_rows_max), nullptr);
   return check_launch(op);
 }
 
@@ -545,6 +649,214 @@ int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs_host, uint6
       static_cast<uint32_t>(hidden), static_cast<uint32_t>(topk), static_cast<uint32_t>(local_experts),
       static_cast<uint32_t>(ranks * local_experts), static_cast<uint32_t>(padded_rows_max));
   return check_launch(op);
+}
+
+// ---------------------------------------------------------------------------------------------
+// One expert-parallel layer: workspace planning and the launch sequence.
+// ---------------------------------------------------------------------------------------------
+}  // extern "C"
+
+namespace gemb {
+namespace {
+
+struct EpBuffers {
+  MoeCommonBuffers c;
+  uint64_t cap;         // assignments this rank can receive: tokens * topk * ranks
+  uint64_t rows_max;    // padded rows of its local experts for that many
+  uint64_t el;
+  int32_t* counts_all;
+  int32_t* plan;
+  int32_t* recv_prefix;
+  int32_t* recv_src;
+  int32_t* recv_dst;
+  int32_t* row_base;
+  int32_t* tile_rows;
+  int32_t* row_meta;
+  uint8_t* a_packed;
+  uint8_t* a_scales;
+  uint16_t* gate_up;
+  uint8_t* p_packed;
+  uint8_t* p_scales;
+};
+
+uint64_t carve_ep(const gemb_moe_layer_weights* w, uint64_t tokens, uint64_t ranks, uint8_t* base, EpBuffers* b) {
+  uint64_t cursor = 0;
+  carve_common(w, tokens, base, &cursor, &b->c);
+  auto take = [&](uint64_t bytes) {
+    uint8_t* p = base ? base + cursor : nullptr;
+    cursor += (bytes + 255) / 256 * 256;
+    return p;
+  };
+  const uint64_t h = w->hidden, i = w->intermediate, e = w->experts;
+  b->el = e / ranks;
+  b->cap = tokens * w->topk * ranks;
+  b->rows_max = gemb_moe_padded_rows_max(b->cap, b->el, 1);
+  b->counts_all = reinterpret_cast<int32_t*>(take(ranks * e * 4));
+  b->plan = reinterpret_cast<int32_t*>(take(gemb_moe_ep_plan_ints(b->cap, b->el) * 4));
+  b->recv_prefix = reinterpret_cast<int32_t*>(take((ranks * b->el + 1) * 4));
+  b->recv_src = reinterpret_cast<int32_t*>(take(ranks * b->el * 4));
+  b->recv_dst = reinterpret_cast<int32_t*>(take(ranks * b->el * 4));
+  b->row_base = reinterpret_cast<int32_t*>(take(e * 4));
+  b->tile_rows = reinterpret_cast<int32_t*>(take(b->rows_max / 128 * 4));
+  b->row_meta = reinterpret_cast<int32_t*>(take(b->rows_max * 8));
+  b->a_packed = take(b->rows_max * h / 2);
+  b->a_scales = take(gemb_interleaved_scale_bytes(b->rows_max, h));
+  b->gate_up = w->gate_up_fused ? nullptr : reinterpret_cast<uint16_t*>(take(b->rows_max * 2 * i * 2));
+  b->p_packed = take(b->rows_max * i / 2);
+  b->p_scales = take(gemb_interleaved_scale_bytes(b->rows_max, i));
+  return cursor;
+}
+
+int32_t validate_ep(const char* op, const gemb_moe_layer_weights* w, uint64_t tokens, uint64_t ranks) {
+  GEMB_REQUIRE(w != nullptr, "%s: weights must be nonnull", op);
+  GEMB_REQUIRE(ranks >= 1 && ranks <= kMaxRanks && w->experts % ranks == 0, "%s: experts must be a multiple of the rank count (at most %u ranks)",
+               op, kMaxRanks);
+  GEMB_TRY(validate_moe_weights(op, w, tokens, w->experts / ranks));
+  GEMB_REQUIRE(w->hidden % 256 == 0, "%s: hidden must be a multiple of 256", op);
+  GEMB_REQUIRE(tokens * w->topk * ranks < (1ull << 31), "%s: tokens * topk * ranks must fit 31 bits", op);
+  return GEMB_OK;
+}
+
+struct EpCall {
+  EpBuffers b;
+  PeerPtrs send, recv, counts, flags;
+  uint64_t msg_bytes;
+};
+
+int32_t prepare_ep(const char* op, const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, uint64_t tokens,
+                   void* workspace, uint64_t workspace_bytes, EpCall* call) {
+  GEMB_REQUIRE(comm != nullptr, "%s: comm must be nonnull", op);
+  GEMB_TRY(validate_ep(op, w, tokens, comm->ranks));
+  GEMB_REQUIRE(comm->rank < comm->ranks && comm->local_epochs != nullptr, "%s: bad rank or epoch pointer", op);
+  GEMB_REQUIRE(workspace != nullptr && reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "%s: workspace must be 256-byte aligned", op);
+  const uint64_t need = carve_ep(w, tokens, comm->ranks, static_cast<uint8_t*>(workspace), &call->b);
+  GEMB_REQUIRE(workspace_bytes >= need, "%s: workspace too small (%llu bytes needed)", op, static_cast<unsigned long long>(need));
+  GEMB_TRY(load_peers(op, comm->send_buffers_host, comm->ranks, &call->send));
+  GEMB_TRY(load_peers(op, comm->recv_buffers_host, comm->ranks, &call->recv));
+  GEMB_TRY(load_peers(op, comm->count_buffers_host, comm->ranks, &call->counts));
+  GEMB_TRY(load_peers(op, comm->flag_arrays_host, comm->ranks, &call->flags));
+  call->msg_bytes = gemb_moe_ep_message_row_bytes(w->hidden);
+  return require_sm100(op);
+}
+
+int32_t ep_stage_send(const char* op, const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const EpCall& call,
+                      const uint16_t* x, uint64_t tokens, gemb_stream_t stream) {
+  const EpBuffers& b = call.b;
+  int32_t* my_counts = reinterpret_cast<int32_t*>(const_cast<uint8_t*>(call.counts.p[comm->rank]));
+  GEMB_TRY(moe_route_stage(w, x, tokens, b.c, my_counts, stream));
+  const uint32_t h = static_cast<uint32_t>(w->hidden);
+  const unsigned threads = static_cast<unsigned>(std::min<uint64_t>(256, (h / 16 + 31) / 32 * 32));
+  ep_pack_kernel<<<static_cast<unsigned>(tokens), threads, h / 16, stream>>>(
+      x, b.c.ids, b.c.slot_rows, b.c.offsets, b.c.plan, const_cast<uint8_t*>(call.send.p[comm->rank]), h,
+      static_cast<uint32_t>(w->topk), static_cast<uint32_t>(w->experts), static_cast<uint32_t>(call.msg_bytes),
+      static_cast<uint32_t>(tokens * w->topk), w->gate_up.input_divisor);
+  return check_launch(op);
+}
+
+int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const EpCall& call,
+                         uint64_t tokens, bool barriers, gemb_stream_t stream) {
+  const EpBuffers& b = call.b;
+  const uint32_t ranks = static_cast<uint32_t>(comm->ranks), me = static_cast<uint32_t>(comm->rank);
+  const uint32_t e = static_cast<uint32_t>(w->experts), el = static_cast<uint32_t>(b.el);
+  const uint64_t h = w->hidden, i = w->intermediate, n = tokens * w->topk;
+  ep_sync_plan_kernel<<<1, 256, 4 * e * sizeof(int), stream>>>(
+      call.flags, call.counts, ranks, e, me, comm->local_epochs, static_cast<uint32_t>(g_ep_barrier_spins), barriers ? 1 : 0,
+      barriers ? 1 : 0, b.counts_all, b.plan, b.recv_prefix, b.recv_src, b.recv_dst, b.row_base,
+      static_cast<uint32_t>(b.rows_max), static_cast<uint32_t>(n), b.tile_rows);
+  GEMB_TRY(check_launch(op));
+  const uint32_t segments = ranks * el;
+  const uint32_t c_pad = static_cast<uint32_t>((h / 16 + 3) / 4 * 4);
+  ep_pull_dispatch_kernel<<<static_cast<unsigned>(sm_count()) * 8, 256, (segments + 1) * sizeof(int), stream>>>(
+      call.send, b.recv_prefix, b.recv_src, b.recv_dst, segments, el, static_cast<uint32_t>(h),
+      static_cast<uint32_t>(call.msg_bytes), c_pad, b.a_packed, b.a_scales, static_cast<uint32_t>(n),
+      static_cast<uint32_t>(b.rows_max), reinterpret_cast<int2*>(b.row_meta));
+  GEMB_TRY(check_launch(op));
+  const gemb_nvfp4_binding& gu = w->gate_up;
+  const gemb_nvfp4_binding& dn = w->down;
+  if (w->gate_up_fused != nullptr) {
+    GEMB_TRY(gemb_moe_grouped_gemm_gated_quant(b.a_packed, b.a_scales, w->gate_up_fused, w->gate_up_fused_scales, b.p_packed,
+                                               b.p_scales, b.plan, b.rows_max, el, i, h, gu.input_divisor,
+                                               gu.weight_divisors_device, dn.input_divisor, stream));
+  } else {
+    GEMB_TRY(gemb_moe_grouped_gemm_bf16(b.a_packed, b.a_scales, gu.packed_weight, gu.scales_interleaved, b.gate_up, b.plan,
+                                        b.rows_max, el, 2 * i, h, gu.input_divisor, gu.weight_divisors_device, stream));
+    GEMB_TRY(gemb_moe_expert_gelu_quantize(b.gate_up, b.plan, b.p_packed, b.p_scales, b.rows_max, i, dn.input_divisor, stream));
+  }
+  return grouped_gemm_push(op, b.p_packed, b.p_scales, dn.packed_weight, dn.scales_interleaved, b.plan, b.rows_max, el, h, i,
+                           dn.input_divisor, dn.weight_divisors_device, b.row_meta, b.tile_rows, comm->recv_buffers_host,
+                           comm->ranks, comm->rank, n, stream);
+}
+
+int32_t ep_stage_combine(const char* op, const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const EpCall& call,
+                         uint16_t* out, uint64_t tokens, bool barriers, gemb_stream_t stream) {
+  if (barriers) {
+    ep_barrier_kernel<<<1, 32, 0, stream>>>(call.flags, static_cast<uint32_t>(comm->ranks), static_cast<uint32_t>(comm->rank), 1,
+                                            comm->local_epochs, static_cast<uint32_t>(g_ep_barrier_spins));
+    GEMB_TRY(check_launch(op));
+  }
+  const uint16_t* rows = reinterpret_cast<const uint16_t*>(call.recv.p[comm->rank]);
+  return gemb_moe_combine(rows, nullptr, call.b.c.weights, w->shared_intermediate ? call.b.c.s_out : nullptr, out, tokens,
+                          w->hidden, w->topk, stream);
+}
+
+}  // namespace
+}  // namespace gemb
+
+extern "C" {
+
+uint64_t gemb_moe_ep_message_row_bytes(uint64_t hidden) { return (hidden / 2 + hidden / 16 + 4 + 15) / 16 * 16; }
+
+uint64_t gemb_moe_ep_layer_workspace_bytes(const gemb_moe_layer_weights* weights, uint64_t tokens, uint64_t ranks) {
+  if (validate_ep("gemb_moe_ep_layer_workspace_bytes", weights, tokens, ranks) != GEMB_OK) return 0;
+  EpBuffers b;
+  return carve_ep(weights, tokens, ranks, nullptr, &b);
+}
+
+int32_t gemb_moe_ep_layer_records(const gemb_moe_layer_weights* weights, uint64_t tokens, uint64_t ranks, void* workspace,
+                                  gemb_moe_records* records) {
+  const char* op = "gemb_moe_ep_layer_records";
+  GEMB_TRY(validate_ep(op, weights, tokens, ranks));
+  GEMB_REQUIRE(workspace != nullptr && records != nullptr && reinterpret_cast<uintptr_t>(workspace) % 256 == 0,
+               "%s: workspace (256-byte aligned) and records must be nonnull", op);
+  EpBuffers b;
+  carve_ep(weights, tokens, ranks, static_cast<uint8_t*>(workspace), &b);
+  *records = gemb_moe_records{b.c.logits, b.c.ids, b.c.weights, b.c.counts, b.c.offsets, b.c.perm,
+                              b.c.slot_rows, b.plan, nullptr, b.rows_max, b.counts_all};
+  return GEMB_OK;
+}
+
+int32_t gemb_moe_ep_layer_stage(const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const uint16_t* x, uint16_t* out,
+                                uint64_t tokens, void* workspace, uint64_t workspace_bytes, int32_t stage, int32_t barriers,
+                                gemb_stream_t stream) {
+  const char* op = "gemb_moe_ep_layer_stage";
+  EpCall call;
+  GEMB_TRY(prepare_ep(op, w, comm, tokens, workspace, workspace_bytes, &call));
+  GEMB_REQUIRE(stage >= 0 && stage <= 2, "%s: stage must be 0, 1 or 2", op);
+  if (stage == 0) {
+    GEMB_REQUIRE(x != nullptr, "%s: input must be nonnull", op);
+    if (w->shared_intermediate != 0) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, stream));
+    return ep_stage_send(op, w, comm, call, x, tokens, stream);
+  }
+  if (stage == 1) return ep_stage_experts(op, w, comm, call, tokens, barriers != 0, stream);
+  GEMB_REQUIRE(out != nullptr, "%s: output must be nonnull", op);
+  return ep_stage_combine(op, w, comm, call, out, tokens, barriers != 0, stream);
+}
+
+int32_t gemb_moe_ep_layer_forward(const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const uint16_t* x, uint16_t* out,
+                                  uint64_t tokens, void* workspace, uint64_t workspace_bytes, gemb_stream_t stream,
+                                  gemb_stream_t side_stream, void* fork_event, void* join_event) {
+  const char* op = "gemb_moe_ep_layer_forward";
+  EpCall call;
+  GEMB_TRY(prepare_ep(op, w, comm, tokens, workspace, workspace_bytes, &call));
+  GEMB_REQUIRE(x != nullptr && out != nullptr, "%s: input and output must be nonnull", op);
+  const bool shared = w->shared_intermediate != 0;
+  const bool forked = shared && side_stream != nullptr && fork_event != nullptr && join_event != nullptr;
+  if (forked) GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));
+  if (shared) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, forked ? side_stream : stream));
+  GEMB_TRY(ep_stage_send(op, w, comm, call, x, tokens, stream));
+  GEMB_TRY(ep_stage_experts(op, w, comm, call, tokens, true, stream));
+  if (forked) GEMB_TRY(stream_join(op, stream, side_stream, join_event));
+  return ep_stage_combine(op, w, comm, call, out, tokens, true, stream);
 }
 
 }  // extern "C"

@@ -81,6 +81,17 @@ struct GemmParams {
   float g_product;               // input divisor of the down projection
   uint8_t* out_packed;           // [M, n/4] payload of the product (n/2 features)
   uint8_t* out_scales;           // interleaved scales of the product
+  // Pushing epilogue (push_meta != null; grouped bf16 output only): row r of the padded row space
+  // is not stored at out[r] but at row push_meta[r].y of the bf16 [push_rows, n] buffer
+  // push_dst[push_meta[r].x] -- for expert parallelism the buffer of the GPU that owns the token,
+  // written with plain 16-byte stores over NVLink while the next tile's MMAs run.  Only the first
+  // push_tile_rows[tile] rows of a tile are real assignments; the rest is padding and is dropped.
+  const int2* push_meta;
+  const int32_t* push_tile_rows;
+  uint8_t* push_dst[16];
+  uint32_t push_ranks;
+  uint32_t push_rows;
+  uint32_t m_out;                // rows of the buffer the output tensor map describes (0: m)
 };
 
 template <bool kFp4, int BN, int kStages, int kAccStages, bool kPair = false>
@@ -470,7 +481,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       uint32_t pending_col = 0;
       uint32_t packed[32];  // one converted sub-tile: 16-byte chunk j of this lane's row = packed[4j .. 4j+3]
       // Stages `packed` in this warp's swizzled buffer and hands it to a TMA store.
+      // Pushing epilogue: where this lane's row goes, and how many of the warp's 32 rows are real.
+      int2 push_to = make_int2(-1, 0);
+      uint32_t push_valid = 0;
+      if (kFp4 && p.push_meta != nullptr) {
+        const uint32_t tile_rows = min(static_cast<uint32_t>(__ldg(p.push_tile_rows + mt)), static_cast<uint32_t>(BM));
+        push_valid = tile_rows > quarter * 32 ? min(32u, tile_rows - quarter * 32) : 0u;
+        if (static_cast<uint32_t>(lane) < push_valid) {
+          push_to = __ldg(p.push_meta + row0 + lane);
+          if (static_cast<uint32_t>(push_to.x) >= p.push_ranks || static_cast<uint32_t>(push_to.y) >= p.push_rows) {
+            atomicCAS(&g_gemm_error, 0, 8);   // a destination outside the buffers: recorded, the row is dropped
+            push_to.x = -1;
+          }
+        }
+      }
       auto stage_and_store = [&](uint32_t col) {
+        if (kFp4 && p.push_meta != nullptr) {
+          __syncwarp();   // the previous sub-tile's pushes have read the buffer
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(my_stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          __syncwarp();
+          // Eight lanes take one row: 8 x 16 bytes = one full 128-byte line of the destination row.
+          const uint32_t chunk = lane & 7;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const uint32_t r = it * 4 + (lane >> 3);
+            const int dst_rank = __shfl_sync(0xFFFFFFFFu, push_to.x, r);
+            const int dst_row = __shfl_sync(0xFFFFFFFFu, push_to.y, r);
+            if (dst_rank < 0 || col + chunk * 8 >= p.n) continue;
+            const uint4 v = *reinterpret_cast<const uint4*>(my_stage + r * 128 + ((chunk ^ (r & 7)) << 4));
+            uint8_t* dst = p.push_dst[dst_rank] + (static_cast<uint64_t>(dst_row) * p.n + col + chunk * 8) * 2;
+            asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+          }
+          pending = false;
+          return;
+        }
         if (lane == 0) ptx::bulk_wait_group_read<0>();  // the previous store has read the buffer
         __syncwarp();
 #pragma unroll
@@ -514,9 +561,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
               // bf16 projection boundaries, bf16 GELU, bf16 product: src/cuda/nvfp4/reference.cu:177-190
               const float gv = bf16_round(__fmul_rn(__uint_as_float(v0[b * 16 + i]), alpha_g));
               const float uv = bf16_round(__fmul_rn(__uint_as_float(v1[b * 16 + i]), alpha_u));
-              const float inner = 0.7978845608028654f * (gv + 0.044715f * gv * gv * gv);
-              const float gelu = bf16_round(0.5f * gv * (1.0f + tanhf(inner)));
-              prod[i] = bf16_round(gelu * uv);
+              prod[i] = gelu_tanh_product(gv, uv);
             }
             quantize_block16<false>(prod, p.g_product, words[2 * b], words[2 * b + 1], sb[b]);
           }
@@ -745,7 +790,7 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
   else if (p.gated)  // the tensor-map store path is unused; describe the payload buffer so the map is valid
     GEMB_TRY(make_out_map(op, &map_out, p.out_packed, p.m, p.n / 8));
   else
-    GEMB_TRY(make_out_map(op, &map_out, p.out, p.m, p.n));
+    GEMB_TRY(make_out_map(op, &map_out, p.out, p.m_out ? p.m_out : p.m, p.n));
   const uint32_t m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
   if constexpr (kPair) {
     const uint32_t units = ((m_tiles + 1) / 2) * n_tiles;
@@ -881,6 +926,52 @@ int32_t gemb_moe_grouped_gemm_bf16(const uint8_t* act, const uint8_t* act_scales
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
   return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
 }
+
+// Grouped down projection whose epilogue stores every real row at its destination in one of
+// `ranks` bf16 [dst_rows, rows_per_expert] buffers (dst_host: their device addresses, a host array;
+// buffers of other GPUs are peer-mapped) instead of the padded row space: meta[r] = {destination
+// buffer, destination row} per padded row, tile_rows[t] = real rows of 128-row tile t.
+}  // extern "C"
+namespace gemb {
+int32_t grouped_gemm_push(const char* op, const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* w,
+                          const uint8_t* w_scales_interleaved, const int32_t* plan, uint64_t padded_rows_max,
+                          uint64_t experts, uint64_t rows_per_expert, uint64_t k, float ga, const float* w_divisors,
+                          const int32_t* meta, const int32_t* tile_rows, const uint64_t* dst_host, uint64_t ranks,
+                          uint64_t rank, uint64_t dst_rows, gemb_stream_t stream) {
+  GEMB_REQUIRE(act && act_scales_interleaved && w && w_scales_interleaved && plan && w_divisors && meta && tile_rows && dst_host,
+               "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_gemm(op, padded_rows_max, rows_per_expert, k, 64));
+  GEMB_REQUIRE(padded_rows_max % 128 == 0 && rows_per_expert % 128 == 0, "%s: rows must come in multiples of 128", op);
+  GEMB_REQUIRE(experts > 0 && experts <= 4096 && experts * rows_per_expert < (1ull << 31), "%s: bad expert count", op);
+  GEMB_REQUIRE(ranks >= 1 && ranks <= 16 && rank < ranks && dst_rows > 0 && dst_rows < (1ull << 31), "%s: bad destination geometry", op);
+  GEMB_REQUIRE(positive_finite(ga), "%s: activation global divisor must be positive and finite", op);
+  GemmParams p{};
+  p.sfa = act_scales_interleaved;
+  p.sfb = w_scales_interleaved;
+  p.m = static_cast<uint32_t>(padded_rows_max);
+  p.n = static_cast<uint32_t>(rows_per_expert);
+  p.k = static_cast<uint32_t>(k);
+  p.plan = plan;
+  p.w_divisors = w_divisors;
+  p.ga = ga;
+  p.experts = static_cast<uint32_t>(experts);
+  p.alpha = 1.0f;
+  p.push_meta = reinterpret_cast<const int2*>(meta);
+  p.push_tile_rows = tile_rows;
+  p.push_ranks = static_cast<uint32_t>(ranks);
+  p.push_rows = static_cast<uint32_t>(dst_rows);
+  for (uint64_t r = 0; r < ranks; ++r) {
+    GEMB_REQUIRE(dst_host[r] != 0 && dst_host[r] % 16 == 0, "%s: every destination buffer must be mapped and 16-byte aligned", op);
+    p.push_dst[r] = reinterpret_cast<uint8_t*>(dst_host[r]);
+  }
+  p.out = reinterpret_cast<uint16_t*>(dst_host[rank]);   // describes the (unused) tensor-map store target
+  p.m_out = static_cast<uint32_t>(dst_rows);
+  const int bn = g_gemm_bn ? g_gemm_bn : 256;
+  if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
+  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
+}
+}  // namespace gemb
+extern "C" {
 
 // ---------------------------------------------------------------------------------------------
 // Gate/up weight packing for the gated epilogue: output row (f / 32) * 64 + which * 32 + f % 32
@@ -1045,6 +1136,8 @@ int32_t gemb_check_device_status(void) {
   if (code != 0) {
     const int zero = 0;
     cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof zero);
+    if (code == 8)
+      return fail(GEMB_INTERNAL, "%s: a pushing GEMM epilogue met a destination outside the receive buffers and dropped the row", op);
     return fail(GEMB_INTERNAL, "%s: a GEMM kernel gave up waiting on a pipeline barrier (role %d)", op, code);
   }
   const int gemv_code = gemv_take_device_error();

@@ -906,9 +906,7 @@ nvfp4_gemv_kernel(const uint8_t* __restrict__ act, const uint8_t* __restrict__ a
         if (out1) out1[row0 + r] = y1;
         // bf16 boundaries and GELU-tanh product: src/cuda/nvfp4/sm120.cu:375-386.
         const float g = bf16_round(y0), u = bf16_round(y1);
-        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
-        const float gelu = bf16_round(0.5f * g * (1.0f + tanhf(inner)));
-        product[row0 + r] = bf16_round(gelu * u);
+        product[row0 + r] = gelu_tanh_product(g, u);
       } else {
         out0[row0 + r] = y0;
       }

@@ -609,9 +609,7 @@ expert_gelu_quantize_kernel(const uint16_t* __restrict__ gate_up, const int32_t*
   for (int i = 0; i < 16; ++i) {
     const float gv = __uint_as_float((i & 1) ? (gw[i >> 1] & 0xFFFF0000u) : (gw[i >> 1] << 16));
     const float uv = __uint_as_float((i & 1) ? (uw[i >> 1] & 0xFFFF0000u) : (uw[i >> 1] << 16));
-    const float inner = 0.7978845608028654f * (gv + 0.044715f * gv * gv * gv);
-    const float gelu = bf16_round(0.5f * gv * (1.0f + tanhf(inner)));
-    v[i] = bf16_round(gelu * uv);
+    v[i] = gelu_tanh_product(gv, uv);
   }
   uint32_t lo, hi;
   uint8_t sb;
@@ -671,7 +669,8 @@ combine_kernel(const uint16_t* __restrict__ y, const int32_t* __restrict__ slot_
   for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
   for (uint32_t s = 0; s < topk; ++s) {
     const float wv = __ldg(weights + static_cast<uint64_t>(t) * topk + s);
-    const int64_t r = __ldg(slot_rows + static_cast<uint64_t>(t) * topk + s);
+    const int64_t r = slot_rows ? static_cast<int64_t>(__ldg(slot_rows + static_cast<uint64_t>(t) * topk + s))
+                                : static_cast<int64_t>(t) * topk + s;
     const uint4 v = __ldg(reinterpret_cast<const uint4*>(y + r * hidden) + c);
     const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -990,7 +989,7 @@ int32_t gemb_moe_combine(const uint16_t* y_bf16, const int32_t* slot_rows, const
                          const uint16_t* shared_bf16, uint16_t* out_bf16, uint64_t tokens, uint64_t hidden,
                          uint64_t topk, gemb_stream_t stream) {
   const char* op = "gemb_moe_combine";
-  GEMB_REQUIRE(y_bf16 && slot_rows && top_weights && out_bf16, "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(y_bf16 && top_weights && out_bf16, "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(tokens > 0 && tokens < (1ull << 31) && topk >= 1 && topk <= 32, "%s: bad geometry", op);
   GEMB_REQUIRE(hidden > 0 && hidden % 8 == 0 && hidden < (1ull << 31), "%s: hidden must be a nonzero multiple of 8", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(y_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(out_bf16) % 16 == 0 &&

@@ -9,8 +9,6 @@
 namespace gemb {
 namespace {
 
-constexpr float kSqrtTwoOverPi = 0.7978845608028654f;
-constexpr float kGeluCubic = 0.044715f;
 
 __device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
   const float4* q = reinterpret_cast<const float4*>(p);
@@ -55,9 +53,7 @@ struct GatedGeluLoader {
     for (int i = 0; i < 16; ++i) {
       const float gv = sizeof(In) == 4 ? bf16_round(g[i]) : g[i];
       const float uv = sizeof(In) == 4 ? bf16_round(u[i]) : u[i];
-      const float inner = kSqrtTwoOverPi * (gv + kGeluCubic * gv * gv * gv);
-      const float gelu = bf16_round(0.5f * gv * (1.0f + tanhf(inner)));
-      v[i] = bf16_round(gelu * uv);
+      v[i] = gelu_tanh_product(gv, uv);
     }
   }
 };

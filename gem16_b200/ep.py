@@ -18,6 +18,8 @@ Per layer, on every rank (T local tokens, R ranks, E experts, E/R local experts 
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 import torch.distributed as dist
 
@@ -272,3 +274,102 @@ class EpPullMoeLayer:
         self.stage_experts()
         dist.all_reduce(self.flag, group=self.group)   # every expert output is complete
         return self.stage_combine()
+
+
+class EpLayer:
+    """One expert-parallel layer through gemb_moe_ep_layer_forward: the launch sequence, the flag
+    barriers and the workspace plan live in the library (csrc/ep.cu); this class only owns the
+    memory -- the four peer-mapped buffers (message rows out, expert rows back, counts, flags)
+    and the local workspace -- and builds the descriptors.
+
+    emulate=(rank, world): no process group; plain device buffers stand in for the peer-mapped
+    ones and the caller walks all ranks through `stage(0..2)` on one GPU, wiring the address tables
+    with `connect` and copying the counts on the host side (tests)."""
+
+    def __init__(self, weights: MoeWeights, tokens: int, topk: int, ga: float, ga_dn: float, ga_sh_dn: float,
+                 group=None, how: str = "auto", emulate=None, fused: bool = True):
+        from .lib import MoeEpComm, MoeRecords
+        from .peer import LocalBuffer, PeerBuffer
+        self.lib = load()
+        lib, dev, w, c = self.lib, weights.dev, weights, self.lib.cdll
+        self.emulated = emulate is not None
+        self.rank, self.world = emulate if self.emulated else (dist.get_rank(group), dist.get_world_size(group))
+        self.w, self.tokens, self.topk, self.fused = weights, tokens, topk, fused
+        self.ga, self.ga_dn, self.ga_sh_dn = ga, ga_dn, ga_sh_dn
+        self.e_total, self.e_local = w.router_experts, w.experts
+        assert self.e_local * self.world == self.e_total
+        h, n = w.hidden, tokens * topk
+        self.msg_bytes = c.gemb_moe_ep_message_row_bytes(h)
+        make = (lambda nbytes: LocalBuffer(nbytes, dev)) if self.emulated else (lambda nbytes: PeerBuffer(nbytes, dev, group, how))
+        self.send, self.recv = make(n * self.msg_bytes), make(n * h * 2)
+        self.counts_peer, self.flags_peer = make(self.e_total * 4), make(2 * 16 * 4)
+        self.epochs = torch.zeros((2,), dtype=torch.int32, device=dev)
+        self.out = torch.empty((tokens, h), dtype=torch.int16, device=dev)
+        self._desc = {}
+        desc = self.descriptor()
+        nbytes = c.gemb_moe_ep_layer_workspace_bytes(C.addressof(desc), tokens, self.world)
+        if nbytes == 0:
+            raise RuntimeError(lib.last_error())
+        self.workspace = torch.full((nbytes + 256,), 255, dtype=torch.uint8, device=dev)
+        self.base = (self.workspace.data_ptr() + 255) // 256 * 256
+        rec = MoeRecords()
+        lib.gemb_moe_ep_layer_records(desc, tokens, self.world, self.base, rec)
+        self.rows_max = rec.padded_rows_max
+        e, k = self.e_total, topk
+        self.ids = self._view(rec.top_ids, torch.int32, tokens, k)
+        self.weights = self._view(rec.top_weights, torch.float32, tokens, k)
+        self.perm = self._view(rec.perm, torch.int32, n)
+        self.offsets = self._view(rec.offsets, torch.int32, e + 1)
+        self.counts_all = self._view(rec.counts_all, torch.int32, self.world, e)
+        self.plan = self._view(rec.plan, torch.int32, c.gemb_moe_ep_plan_ints(n * self.world, self.e_local))
+        self.counts = self.counts_peer.local.view(torch.int32)
+        self.side = torch.cuda.Stream(device=dev)
+        self.fork_event, self.join_event = torch.cuda.Event(), torch.cuda.Event()
+        self.fork_event.record()
+        self.join_event.record()
+        self.comm = None
+        if not self.emulated:
+            self._make_comm()
+            dist.barrier(group)   # every rank's flag words are zero before the first barrier kernel runs
+
+    def _view(self, ptr, dtype, *shape):
+        nbytes = torch.empty((), dtype=dtype).element_size()
+        for d in shape:
+            nbytes *= d
+        off = ptr - self.workspace.data_ptr()
+        return self.workspace[off:off + nbytes].view(dtype).view(*shape)
+
+    def descriptor(self):
+        key = (id(self.w), self.fused)
+        if key not in self._desc:
+            self._desc[key] = self.w.c_struct(self.topk, self.ga, self.ga_dn, self.ga_sh_dn, fused=self.fused)
+        return self._desc[key]
+
+    def _make_comm(self):
+        from .lib import MoeEpComm
+        m = MoeEpComm()
+        m.ranks, m.rank = self.world, self.rank
+        m.send_buffers_host, m.recv_buffers_host = C.addressof(self.send.table), C.addressof(self.recv.table)
+        m.count_buffers_host, m.flag_arrays_host = C.addressof(self.counts_peer.table), C.addressof(self.flags_peer.table)
+        m.local_epochs = self.epochs.data_ptr()
+        self.comm = m
+
+    @staticmethod
+    def connect(layers):
+        """Emulation only: give every layer the addresses of all layers' buffers."""
+        for l in layers:
+            for name in ("send", "recv", "counts_peer", "flags_peer"):
+                getattr(l, name).set_table([getattr(m, name).local.data_ptr() for m in layers])
+            l._make_comm()
+
+    def stage(self, which, x_bf16=None, barriers=False):
+        self.lib.gemb_moe_ep_layer_stage(self.descriptor(), self.comm, x_bf16, self.out, self.tokens, self.base,
+                                         self.workspace.numel() - 256, which, 1 if barriers else 0,
+                                         torch.cuda.current_stream())
+        return self.out
+
+    def forward(self, x_bf16):
+        self.lib.gemb_moe_ep_layer_forward(self.descriptor(), self.comm, x_bf16, self.out, self.tokens, self.base,
+                                           self.workspace.numel() - 256, torch.cuda.current_stream(), self.side,
+                                           self.fork_event.cuda_event, self.join_event.cuda_event)
+        return self.out

@@ -30,6 +30,46 @@ _SCALARS = {"uint64_t": C.c_uint64, "int32_t": C.c_int32, "float": C.c_float, "s
             "int64_t": C.c_int64, "uint32_t": C.c_uint32}
 
 
+class Fp8Binding(C.Structure):
+    """gemb_fp8_binding of include/gemb200.h."""
+    _fields_ = [("weight", C.c_void_p), ("scales", C.c_void_p), ("rows", C.c_uint64), ("contracting", C.c_uint64)]
+
+
+class Nvfp4Binding(C.Structure):
+    """gemb_nvfp4_binding of include/gemb200.h."""
+    _fields_ = [("packed_weight", C.c_void_p), ("scales", C.c_void_p), ("input_divisor_device", C.c_void_p),
+                ("input_divisor", C.c_float), ("weight_divisor", C.c_float), ("rows", C.c_uint64),
+                ("contracting", C.c_uint64), ("scales_interleaved", C.c_void_p),
+                ("weight_divisors_device", C.c_void_p), ("experts", C.c_uint64)]
+
+
+class MoeLayerWeights(C.Structure):
+    """gemb_moe_layer_weights of include/gemb200.h."""
+    _fields_ = [("hidden", C.c_uint64), ("experts", C.c_uint64), ("topk", C.c_uint64), ("intermediate", C.c_uint64),
+                ("shared_intermediate", C.c_uint64), ("router_weight", C.c_void_p), ("router_bias", C.c_void_p),
+                ("per_expert_scale", C.c_void_p), ("router_input_scale", C.c_void_p), ("router_epsilon", C.c_float),
+                ("gate_up", Nvfp4Binding), ("down", Nvfp4Binding), ("shared_gate_up", Nvfp4Binding),
+                ("shared_down", Nvfp4Binding), ("gate_up_fused", C.c_void_p), ("gate_up_fused_scales", C.c_void_p),
+                ("shared_gate_up_fused", C.c_void_p), ("shared_gate_up_fused_scales", C.c_void_p)]
+
+
+class MoeRecords(C.Structure):
+    """gemb_moe_records of include/gemb200.h."""
+    _fields_ = [(n, C.c_void_p) for n in ("logits", "top_ids", "top_weights", "counts", "offsets", "perm", "slot_rows",
+                                           "plan", "expert_rows")] + [("padded_rows_max", C.c_uint64),
+                                                                      ("counts_all", C.c_void_p)]
+
+
+class MoeEpComm(C.Structure):
+    """gemb_moe_ep_comm of include/gemb200.h."""
+    _fields_ = [("ranks", C.c_uint64), ("rank", C.c_uint64), ("send_buffers_host", C.c_void_p),
+                ("recv_buffers_host", C.c_void_p), ("count_buffers_host", C.c_void_p), ("flag_arrays_host", C.c_void_p),
+                ("local_epochs", C.c_void_p)]
+
+
+STRUCTS = [Fp8Binding, Nvfp4Binding, MoeLayerWeights, MoeRecords, MoeEpComm]   # order of gemb_struct_bytes
+
+
 def parse_header(path: str = HEADER) -> dict[str, tuple[str, list[tuple[str, str]]]]:
     """name -> (return type, [(ctype, param name)]) for every function the header declares."""
     text = open(path).read()
@@ -62,6 +102,10 @@ def _as_arg(v):
         return v.data_ptr()
     if hasattr(v, "cuda_stream"):
         return v.cuda_stream
+    if isinstance(v, C.Structure):
+        return C.addressof(v)
+    if isinstance(v, C.Array):
+        return C.addressof(v)
     return v
 
 

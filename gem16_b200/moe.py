@@ -1,15 +1,19 @@
-"""Host-side sequencing of one MoE layer over the C ABI (torch only allocates device buffers).
+"""Test and benchmark harness around the MoE layer of the C ABI (torch only owns device memory).
 
-Mirrors the stage order of docs/plans/gemma4-26b/specs/MOE_PREFILL_KERNEL_SPEC.md:34-47:
-router -> assignments -> histogram -> prefix -> stable permutation -> grouped gate_up ->
-activation + requantisation -> grouped down -> deterministic weighted reduction (+ shared
-branch).  Every stage is a separate observable launch on one stream; nothing is read back.
+`MoeLayer.forward` is one call of gemb_moe_layer_forward: the launch sequence, the workspace plan
+and the fork / join of the shared branch live in the library (csrc/moe_layer.cu).  The stage
+methods (`route`, `experts`, `shared_branch`, `combine`, `forward_stages`) issue the same
+operator launches one by one from here, for stage timing and for tests that look at the
+intermediate buffers; both ways give identical bytes.  Stage order:
+docs/plans/gemma4-26b/specs/MOE_PREFILL_KERNEL_SPEC.md:34-47.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
-from .lib import load
+from .lib import MoeLayerWeights, MoeRecords, Nvfp4Binding, load
 
 
 class MoeWeights:
@@ -49,6 +53,32 @@ class MoeWeights:
             f, fs = self._fuse(lib, self.shared["gu_packed"][None], sg_s[None], sg_p.shape[0] // 2, self.hidden)
             self.shared["gu_fused"], self.shared["gu_fused_scales"] = f[0], fs[0]
 
+    def c_struct(self, topk, ga, ga_dn, ga_sh_dn, fused=True, router_scale=None, router_eps=1e-6, per_expert_scale=None):
+        """The gemb_moe_layer_weights descriptor of these weights (tensors stay owned by `self`)."""
+        def ptr(t):
+            return None if t is None else t.data_ptr()
+        w = MoeLayerWeights()
+        w.hidden, w.experts, w.topk, w.intermediate = self.hidden, self.router_experts, topk, self.inter
+        w.router_weight, w.router_bias = ptr(self.router_w), ptr(self.router_bias)
+        self._keep = (router_scale, per_expert_scale)
+        w.router_input_scale, w.router_epsilon, w.per_expert_scale = ptr(router_scale), router_eps, ptr(per_expert_scale)
+        w.gate_up = Nvfp4Binding(ptr(self.gu_packed), None, None, ga, 0.0, self.two_inter, self.hidden, ptr(self.gu_scales),
+                                 ptr(self.gu_div), self.experts)
+        w.down = Nvfp4Binding(ptr(self.dn_packed), None, None, ga_dn, 0.0, self.hidden, self.inter, ptr(self.dn_scales),
+                              ptr(self.dn_div), self.experts)
+        if fused:
+            w.gate_up_fused, w.gate_up_fused_scales = ptr(self.gu_fused), ptr(self.gu_fused_scales)
+        if self.shared is not None:
+            s = self.shared
+            w.shared_intermediate = s["inter"]
+            w.shared_gate_up = Nvfp4Binding(ptr(s["gu_packed"]), None, None, ga, s["gu_div"], 2 * s["inter"], self.hidden,
+                                            ptr(s["gu_scales"]), None, 0)
+            w.shared_down = Nvfp4Binding(ptr(s["dn_packed"]), None, None, ga_sh_dn, s["dn_div"], self.hidden, s["inter"],
+                                         ptr(s["dn_scales"]), None, 0)
+            if fused:
+                w.shared_gate_up_fused, w.shared_gate_up_fused_scales = ptr(s["gu_fused"]), ptr(s["gu_fused_scales"])
+        return w
+
     def _fuse(self, lib, packed, compact, inter, k):
         """Per expert: gate rows [0, inter) and up rows [inter, 2*inter) -> the 32-feature
         interleaved layout the gated-epilogue GEMM consumes."""
@@ -75,7 +105,8 @@ class MoeLayer:
     """Preallocated buffers + the launch sequence for `tokens` tokens."""
 
     def __init__(self, weights: MoeWeights, tokens: int, topk: int, ga: float, ga_dn: float, ga_sh_dn: float = 1.0,
-                 allocate_experts: bool = True):
+                 allocate_experts: bool = True, stages: bool = True):
+        """stages=False skips the buffers only the stage methods use (forward() needs none of them)."""
         self.lib = load()
         self.side = None
         # gate/up GEMM + GELU + requantisation in one kernel: byte-identical, but with four epilogue
@@ -98,7 +129,7 @@ class MoeLayer:
         self.slot_rows = torch.empty((tokens * topk,), **i32)
         self.plan = torch.zeros((c.gemb_moe_plan_ints(tokens, e, topk),), **i32)
         self.workspace = torch.empty((c.gemb_moe_permute_workspace_bytes(tokens, e, topk),), **u8)
-        if allocate_experts:   # the expert-parallel layer owns its own (differently sized) expert buffers
+        if allocate_experts and stages:   # the expert-parallel layer owns its own (differently sized) expert buffers
             self.a_packed = torch.zeros((self.rows_max, h // 2), **u8)
             self.a_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, h),), **u8)
             self.gate_up = torch.empty((self.rows_max, 2 * i), dtype=torch.int16, device=dev)
@@ -106,7 +137,34 @@ class MoeLayer:
             self.p_scales = torch.zeros((c.gemb_interleaved_scale_bytes(self.rows_max, i),), **u8)
             self.y = torch.empty((self.rows_max, h), dtype=torch.int16, device=dev)
         self.out = torch.empty((tokens, h), dtype=torch.int16, device=dev)
-        if w.shared is not None:
+        self.router_scale = self.per_expert_scale = None     # optional router tensors (bf16 [hidden], fp32 [experts])
+        self.c_workspace = None
+        if allocate_experts:
+            # the library's own layer call: one workspace, records viewed in place
+            desc = w.c_struct(topk, ga, ga_dn, ga_sh_dn, fused=False)
+            nbytes = c.gemb_moe_layer_workspace_bytes(C.addressof(desc), tokens)
+            if nbytes == 0:
+                raise RuntimeError(lib.last_error())
+            nbytes += tokens * h * 2 + 256        # room for the router's transformed input, should a test switch it on
+            # filled with 0xFF: the layer must not depend on what the workspace held before
+            self.c_workspace = torch.full((nbytes + 256,), 255, **u8)
+            self.c_base = (self.c_workspace.data_ptr() + 255) // 256 * 256
+            rec = MoeRecords()
+            lib.gemb_moe_layer_records(desc, tokens, self.c_base, rec)
+
+            view = self._ws_view
+            self.logits = view(rec.logits, torch.float32, tokens, e)
+            self.ids = view(rec.top_ids, torch.int32, tokens, topk)
+            self.weights = view(rec.top_weights, torch.float32, tokens, topk)
+            self.counts = view(rec.counts, torch.int32, e)
+            self.offsets = view(rec.offsets, torch.int32, e + 1)
+            self.perm = view(rec.perm, torch.int32, tokens * topk)
+            self.slot_rows = view(rec.slot_rows, torch.int32, tokens * topk)
+            self.plan = view(rec.plan, torch.int32, c.gemb_moe_plan_ints(tokens, e, topk))
+            self.y = view(rec.expert_rows, torch.int16, self.rows_max, h)
+            self.fork_event, self.join_event = torch.cuda.Event(), torch.cuda.Event()
+            self._desc, self._y = {}, {}
+        if w.shared is not None and stages:
             si = w.shared["inter"]
             self.s_packed = torch.empty((tokens, h // 2), **u8)
             self.s_scales = torch.zeros((c.gemb_interleaved_scale_bytes(tokens, h),), **u8)
@@ -163,6 +221,34 @@ class MoeLayer:
                                   self.topk, stream)
 
     def forward(self, x_bf16, stream=None):
+        """One gemb_moe_layer_forward call (shared branch forked onto a side stream)."""
+        main = stream if stream is not None else torch.cuda.current_stream()
+        if self.side is None:
+            self.side = torch.cuda.Stream(device=self.w.dev)
+            self.fork_event.record(main)     # creates the CUDA events behind the torch objects
+            self.join_event.record(main)
+        key = (id(self.w), self.fused, id(self.router_scale), id(self.per_expert_scale))
+        if key not in self._desc:
+            self._desc[key] = self.w.c_struct(self.topk, self.ga, self.ga_dn, self.ga_sh_dn, fused=self.fused,
+                                              router_scale=self.router_scale, per_expert_scale=self.per_expert_scale)
+            rec = MoeRecords()
+            self.lib.gemb_moe_layer_records(self._desc[key], self.tokens, self.c_base, rec)
+            self._y[key] = self._ws_view(rec.expert_rows, torch.int16, self.rows_max, self.w.hidden)
+        self.y = self._y[key]    # the expert rows sit behind the optional buffers of the workspace
+        self.lib.gemb_moe_layer_forward(self._desc[key], x_bf16, self.out, self.tokens, self.c_base,
+                                        self.c_workspace.numel() - 256, main, self.side, self.fork_event.cuda_event,
+                                        self.join_event.cuda_event)
+        return self.out
+
+    def _ws_view(self, ptr, dtype, *shape):
+        n = torch.empty((), dtype=dtype).element_size()
+        for d in shape:
+            n *= d
+        off = ptr - self.c_workspace.data_ptr()
+        return self.c_workspace[off:off + n].view(dtype).view(*shape)
+
+    def forward_stages(self, x_bf16, stream=None):
+        """The same layer as separate launches from Python (stage timing, intermediate buffers)."""
         main = stream if stream is not None else torch.cuda.current_stream()
         if self.w.shared is not None:
             # The shared dense branch depends only on x: it runs on a side stream beside routing and

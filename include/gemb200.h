@@ -519,11 +519,168 @@ int32_t gemb_tp_gather_rows(const uint64_t* peer_outputs_host, uint64_t ranks, u
                             uint64_t hidden, uint16_t* out_bf16, gemb_stream_t stream);
 
 /* out[t] = bf16( sum over slots in slot order of fma(weight[t][slot], y[slot_rows[t*topk+slot]])
- *                + shared[t] ), fp32 accumulation, no atomics; shared may be null.
+ *                + shared[t] ), fp32 accumulation, no atomics; shared may be null; slot_rows may be
+ * null when y already holds the rows in assignment order (row t*topk+slot).
  * docs/plans/gemma4-26b/specs/MOE_SEMANTICS_SPEC.md:74-83. */
 int32_t gemb_moe_combine(const uint16_t* y_bf16, const int32_t* slot_rows, const float* top_weights,
                          const uint16_t* shared_bf16, uint16_t* out_bf16, uint64_t tokens,
                          uint64_t hidden, uint64_t topk, gemb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Weight descriptors and whole-layer entry points.  The launch sequence, the buffer planning, the
+ * fork / join of the shared branch and the expert-parallel protocol live here, in the library, so
+ * that a C++ host only fills descriptors, hands over one workspace and makes one call per layer.
+ * ---------------------------------------------------------------------------------------- */
+
+/* Mirror gem16::internal::Fp8Binding and Nvfp4Binding (src/cuda/engine/target_model.h:15-30):
+ * device pointers into the caller's weight arena plus geometry and divisors.  The NVFP4
+ * descriptor keeps the reference's fields and adds what this library's layouts need. */
+typedef struct gemb_fp8_binding {
+  const uint8_t* weight;                /* [rows, contracting] E4M3FN */
+  const uint16_t* scales;               /* [rows] bf16 bits */
+  uint64_t rows;
+  uint64_t contracting;
+} gemb_fp8_binding;
+
+typedef struct gemb_nvfp4_binding {
+  const uint8_t* packed_weight;         /* [rows, K/2]; expert stack: [experts, rows, K/2] */
+  const uint8_t* scales;                /* COMPACT [rows, K/16] (decode GEMV); may be null where only GEMMs run */
+  const float* input_divisor_device;    /* optional device copy of input_divisor, as in the reference */
+  float input_divisor;
+  float weight_divisor;                 /* plain module; unused for a stack */
+  uint64_t rows;
+  uint64_t contracting;
+  /* beyond the reference's fields */
+  const uint8_t* scales_interleaved;    /* 128x4 interleave for the tcgen05 GEMMs; stack: experts back to back */
+  const float* weight_divisors_device;  /* expert stack: fp32 [experts] */
+  uint64_t experts;                     /* 0 = plain module, else the number of matrices in the stack */
+} gemb_nvfp4_binding;
+
+/* One mixture-of-experts layer (26B-A4B shape: router, `experts` gated FFNs of which each token
+ * uses `topk`, one shared dense FFN).  gate_up / shared_gate_up hold the fused projection of
+ * tools/capture_gemma4_26b_goldens.py:232-240: rows = 2 * intermediate, gate rows first.  When the
+ * *_fused pointers are set (weights re-ordered once by gemb_nvfp4_pack_gate_up) the gate/up GEMM,
+ * the GELU and the requantisation run as ONE kernel and gate_up.packed_weight / scales_interleaved
+ * may be null; otherwise they run as GEMM + gemb_moe_expert_gelu_quantize (byte-identical results).
+ * Under expert parallelism the stacks hold this rank's experts only (gate_up.experts = experts / ranks).
+ * Router: logits = x . router_weight^T + router_bias, or, when router_input_scale is set, the
+ * specification's form  r = bf16(rmsnorm_noweight(x) * router_input_scale * hidden^-1/2),
+ * logits = r . router_weight^T  (docs/plans/gemma4-26b/specs/MOE_ROUTER_SPEC.md:3-13); weights are
+ * multiplied by per_expert_scale[id] when it is set (:41-63). */
+typedef struct gemb_moe_layer_weights {
+  uint64_t hidden;
+  uint64_t experts;                     /* experts the router scores */
+  uint64_t topk;
+  uint64_t intermediate;
+  uint64_t shared_intermediate;         /* 0 = no shared branch */
+  const float* router_weight;           /* fp32 [experts, hidden] */
+  const float* router_bias;             /* fp32 [experts] or null */
+  const float* per_expert_scale;        /* fp32 [experts] or null */
+  const uint16_t* router_input_scale;   /* bf16 [hidden] or null */
+  float router_epsilon;                 /* of the router's RMSNorm (with router_input_scale) */
+  gemb_nvfp4_binding gate_up;
+  gemb_nvfp4_binding down;
+  gemb_nvfp4_binding shared_gate_up;
+  gemb_nvfp4_binding shared_down;
+  const uint8_t* gate_up_fused;
+  const uint8_t* gate_up_fused_scales;
+  const uint8_t* shared_gate_up_fused;
+  const uint8_t* shared_gate_up_fused_scales;
+} gemb_moe_layer_weights;
+
+/* Where a layer call leaves its routing records inside the workspace (device pointers), for
+ * callers that want to observe them: RoutedExperts and Assignment records of
+ * MOE_ROUTER_SPEC.md:65-73 and MOE_PREFILL_KERNEL_SPEC.md:19-32 as arrays. */
+typedef struct gemb_moe_records {
+  float* logits;            /* [tokens, experts] */
+  int32_t* top_ids;         /* [tokens, topk] */
+  float* top_weights;       /* [tokens, topk] */
+  int32_t* counts;          /* [experts] */
+  int32_t* offsets;         /* [experts + 1] */
+  int32_t* perm;            /* [tokens * topk] */
+  int32_t* slot_rows;       /* [tokens * topk] */
+  int32_t* plan;            /* gemb_moe_plan_ints entries */
+  uint16_t* expert_rows;    /* bf16 [padded_rows_max, hidden]: the experts' outputs (single-GPU layer only) */
+  uint64_t padded_rows_max;
+  int32_t* counts_all;      /* expert-parallel layer only: every rank's counts, [ranks, experts] */
+} gemb_moe_records;
+
+/* sizeof of the structs above as this build of the library sees them (0 = gemb_fp8_binding,
+ * 1 = gemb_nvfp4_binding, 2 = gemb_moe_layer_weights, 3 = gemb_moe_records, 4 = gemb_moe_ep_comm),
+ * so a binding in another language can check its own layout. */
+uint64_t gemb_struct_bytes(int32_t which);
+
+/* r = bf16( ((x * inv) * scale) * hidden^-1/2 ), inv = 1 / sqrt(sum_k x_k^2 / hidden + epsilon): the
+ * router's input transform (MOE_ROUTER_SPEC.md:3-13).  The sum is one fp32 fma per k in ascending
+ * k and every other step one IEEE operation, so r is reproducible bit for bit. */
+int32_t gemb_moe_router_input(const uint16_t* x_bf16, const uint16_t* scale_bf16, uint16_t* out_bf16,
+                              uint64_t tokens, uint64_t hidden, float epsilon, gemb_stream_t stream);
+
+/* One layer on one GPU: router -> top-k -> stable permutation -> quantise and dispatch -> grouped
+ * gate/up -> GELU + requantisation -> grouped down -> slot-ordered weighted combine + shared branch
+ * (stage order of docs/plans/gemma4-26b/specs/MOE_PREFILL_KERNEL_SPEC.md:34-47; the entry point the
+ * plan reserves as gem16::internal::LaunchMoe* under src/cuda/moe/, milestones M11 and M15).
+ * x and out are bf16 [tokens, hidden].  The workspace (gemb_moe_layer_workspace_bytes, 256-byte
+ * aligned) needs no initialisation and keeps the records of the last call.  Stream-ordered, no
+ * allocation, no host synchronisation, capturable.  When side_stream, fork_event and join_event
+ * (cudaEvent_t created by the caller, timing disabled) are all set, the shared branch runs on
+ * side_stream beside routing and the expert GEMMs and joins before the combine; otherwise
+ * everything runs on `stream`.  Same results either way. */
+uint64_t gemb_moe_layer_workspace_bytes(const gemb_moe_layer_weights* weights, uint64_t tokens);
+int32_t gemb_moe_layer_records(const gemb_moe_layer_weights* weights, uint64_t tokens, void* workspace,
+                               gemb_moe_records* records);
+int32_t gemb_moe_layer_forward(const gemb_moe_layer_weights* weights, const uint16_t* x_bf16,
+                               uint16_t* out_bf16, uint64_t tokens, void* workspace,
+                               uint64_t workspace_bytes, gemb_stream_t stream, gemb_stream_t side_stream,
+                               void* fork_event, void* join_event);
+
+/* ---- one expert-parallel layer (no counterpart in the reference, which is single-GPU) ----
+ * R ranks, one per GPU; rank r holds experts [r*E/R, (r+1)*E/R) (weights->gate_up.experts = E/R) and
+ * `tokens` tokens of its own; the router is replicated.  Four buffers per rank must be mapped by
+ * every rank (peer memory); `comm` carries, per buffer kind, the R device addresses as seen from
+ * THIS rank (host arrays), entry [rank] being the rank's own buffer:
+ *   send_buffers   tokens * topk message rows of gemb_moe_ep_message_row_bytes(hidden) bytes
+ *   recv_buffers   tokens * topk expert output rows, bf16 [tokens * topk, hidden]
+ *   count_buffers  int32 [experts]
+ *   flag_arrays    2 x 16 words, zero before the first call
+ * plus local_epochs: two device words of this rank, zero before the first call.
+ * Per layer and rank: route the local tokens; quantise each token once and leave one message row
+ * per assignment (payload | block scales | assignment index) in the send buffer, grouped by owner;
+ * flag barrier 0; read all ranks' counts and derive every row position from them; pull the rows
+ * of the local experts out of the peers' send buffers; grouped gate/up (+ GELU + requantisation)
+ * and grouped down GEMM, whose epilogue stores each finished bf16 row straight into the recv
+ * buffer of the token's owner (plain 16-byte stores to peer memory, overlapped with the MMAs);
+ * flag barrier 1; slot-ordered combine from the local recv buffer plus the shared branch.
+ * Output, ids, weights and counts equal the single-GPU layer's bit for bit.  Nothing is read back
+ * to the host; the call is capturable, replays included (barrier epochs live on the device).
+ * A barrier that gives up (a peer that never arrives) is recorded for gemb_check_device_status and
+ * the layer then runs on an empty plan: no access leaves the buffers.  Every rank must call with
+ * the same geometry, each on its own GPU. */
+typedef struct gemb_moe_ep_comm {
+  uint64_t ranks;
+  uint64_t rank;
+  const uint64_t* send_buffers_host;
+  const uint64_t* recv_buffers_host;
+  const uint64_t* count_buffers_host;
+  const uint64_t* flag_arrays_host;
+  uint32_t* local_epochs;
+} gemb_moe_ep_comm;
+uint64_t gemb_moe_ep_message_row_bytes(uint64_t hidden);
+uint64_t gemb_moe_ep_layer_workspace_bytes(const gemb_moe_layer_weights* weights, uint64_t tokens, uint64_t ranks);
+int32_t gemb_moe_ep_layer_records(const gemb_moe_layer_weights* weights, uint64_t tokens, uint64_t ranks,
+                                  void* workspace, gemb_moe_records* records);
+int32_t gemb_moe_ep_layer_forward(const gemb_moe_layer_weights* weights, const gemb_moe_ep_comm* comm,
+                                  const uint16_t* x_bf16, uint16_t* out_bf16, uint64_t tokens, void* workspace,
+                                  uint64_t workspace_bytes, gemb_stream_t stream, gemb_stream_t side_stream,
+                                  void* fork_event, void* join_event);
+/* The stages of gemb_moe_ep_layer_forward, separately callable so that several ranks can be walked
+ * through the protocol on ONE GPU (tests; a host-side copy of the counts stands in for barrier 0):
+ * stage 0 = route + pack (+ shared branch), 1 = positions + pull + expert GEMMs with the pushing
+ * epilogue, 2 = combine.  With barriers = 0 the stages skip the flag barriers and stage 1 reads the
+ * counts from the records' counts_all (gemb_moe_ep_layer_records), which the caller fills. */
+int32_t gemb_moe_ep_layer_stage(const gemb_moe_layer_weights* weights, const gemb_moe_ep_comm* comm,
+                                const uint16_t* x_bf16, uint16_t* out_bf16, uint64_t tokens, void* workspace,
+                                uint64_t workspace_bytes, int32_t stage, int32_t barriers, gemb_stream_t stream);
 
 /* Synchronises the device and reports what the kernels recorded since the last call (the record is
  * cleared): a GEMM, GEMV or flag-barrier wait that ran out, an expert-parallel position outside its

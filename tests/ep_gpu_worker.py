@@ -10,7 +10,7 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 from gem16_b200 import load  # noqa: E402
-from gem16_b200.ep import EpMoeLayer, EpPullMoeLayer  # noqa: E402
+from gem16_b200.ep import EpLayer, EpMoeLayer, EpPullMoeLayer  # noqa: E402
 from gem16_b200.moe import MoeLayer, synthetic_weights  # noqa: E402
 
 
@@ -55,6 +55,19 @@ def main():
         assert torch.equal(pull.counts_all.sum(0).to(torch.int32), ref.counts), f"global counts differ (peer path, {sync})"
         assert int(pull.recv_prefix[-1].item()) == ep.last["n_recv"], f"received row count differs (peer path, {sync})"
         assert torch.equal(out, ref_out[sl]), f"peer-memory expert-parallel output differs from the single-GPU layer ({sync})"
+    # the library's own layer call (gemb_moe_ep_layer_forward): pack, fused barrier + positions, pull, grouped GEMMs
+    # whose epilogue pushes every row to the token's owner, combine from the local receive buffer
+    for fused in (True, False):
+        layer = EpLayer(mine, tokens, topk, ga, ga_dn, ga_sh, fused=fused)
+        ref.fused = fused
+        want = ref.forward(x_all.view(torch.int16)).clone()
+        for _ in range(4):     # every buffer is reused without a host sync in between
+            out = layer.forward(x_all[sl].contiguous().view(torch.int16))
+        torch.cuda.synchronize()
+        lib.gemb_check_device_status()
+        assert torch.equal(layer.ids, ref.ids[sl]) and torch.equal(layer.weights, ref.weights[sl]), "routing differs (library layer)"
+        assert torch.equal(layer.counts_all.sum(0).to(torch.int32), ref.counts), "global counts differ (library layer)"
+        assert torch.equal(out, want[sl]), f"library expert-parallel layer differs from the single-GPU layer (fused={fused})"
     dist.barrier()
     print(f"rank {rank} ok n_recv={ep.last['n_recv']} peer={pull.send.how}", flush=True)
     dist.destroy_process_group()

@@ -56,6 +56,46 @@ def test_emulated_ranks_match_single_gpu(lib, dev, ranks, tokens):
             assert torch.equal(outs[r], ref_out[r * tokens:(r + 1) * tokens]), f"rank {r} output differs (pass {rep})"
 
 
+@pytest.mark.parametrize("ranks,tokens,fused", [(2, 96, True), (2, 96, False), (4, 33, True), (8, 5, True), (8, 300, True)])
+def test_library_ep_layer_emulated_ranks_match_single_gpu(lib, dev, ranks, tokens, fused):
+    """gemb_moe_ep_layer_stage walked over all emulated ranks of one GPU (message rows with the
+    assignment index, positions from the counts, pull, grouped GEMMs whose epilogue stores each row
+    into the token owner's receive buffer, combine from that buffer): output, ids, weights and
+    counts bit-identical to the single-GPU layer, three passes over reused buffers."""
+    from gem16_b200.ep import EpLayer
+    hidden, experts, inter, shared_inter, topk = 2816, 128, 704, 2112, 8
+    el = experts // ranks
+    full = synthetic_weights(dev, 7, hidden, experts, inter, shared_inter, placement_ranks=ranks)
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    ga_dn = ga_sh = 2688.0 / 8.0
+    layers = []
+    for r in range(ranks):
+        mine = synthetic_weights(dev, 7, hidden, experts, inter, shared_inter, expert_range=(r * el, (r + 1) * el),
+                                 placement_ranks=ranks)
+        layers.append(EpLayer(mine, tokens, topk, 600.0, ga_dn, ga_sh, emulate=(r, ranks), fused=fused))
+    EpLayer.connect(layers)
+    ref = MoeLayer(full, tokens * ranks, topk, 600.0, ga_dn, ga_sh, stages=False)
+    ref.fused = fused
+    for rep in range(3):
+        x_all = torch.randn((tokens * ranks, hidden), device=dev, generator=g).to(torch.bfloat16)
+        ref_out = ref.forward(x_all.view(torch.int16)).clone()
+        for r, l in enumerate(layers):
+            l.stage(0, x_all[r * tokens:(r + 1) * tokens].contiguous().view(torch.int16))
+        counts_all = torch.stack([l.counts for l in layers]).contiguous()
+        for l in layers:
+            l.counts_all.copy_(counts_all)
+            l.stage(1)
+        outs = [l.stage(2).clone() for l in layers]
+        torch.cuda.synchronize()
+        lib.gemb_check_device_status()
+        assert torch.equal(counts_all.sum(0).to(torch.int32), ref.counts)
+        for r, l in enumerate(layers):
+            sl = slice(r * tokens, (r + 1) * tokens)
+            assert torch.equal(l.ids, ref.ids[sl]) and torch.equal(l.weights, ref.weights[sl])
+            assert torch.equal(outs[r], ref_out[sl]), f"rank {r} output differs (pass {rep})"
+
+
 def test_ep_plan_rejects_bad_geometry(lib, dev):
     from gem16_b200.lib import GembError
     z = torch.zeros((64,), dtype=torch.int32, device=dev)

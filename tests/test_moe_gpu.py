@@ -11,11 +11,12 @@ from tests.util import bf16_bits, from_bf16_bits, to_dev, to_np
 
 pytestmark = pytest.mark.gpu
 
-# Relative Frobenius gate of expert and layer outputs (bf16) against the bf16-rounded oracle.  An
-# output differs from the oracle's only where fp32 accumulation order moved a value across a bf16
-# rounding boundary, here or at the bf16 gate/up and product boundaries in the middle of the FFN,
-# where one flipped bf16 can also flip an E2M1 code of the down projection's input.
-MOE_GATE = 2e-3
+# Relative Frobenius gate of expert and layer outputs (bf16) against the bf16-rounded oracle: the
+# path's acceptance rule.  An output differs from the oracle's only where fp32 accumulation order moved
+# a value across a bf16 rounding boundary, here or at the bf16 gate/up and product boundaries in the
+# middle of the FFN (where one flipped bf16 can also flip an E2M1 code of the down projection's input);
+# observed 1.3e-5 on the 4,096-token layer at the model's dimensions.
+MOE_GATE = 1e-3
 
 
 def gpu_route(lib, dev, logits, topk, scale=None, want_probs=False):
@@ -274,7 +275,7 @@ def test_fused_gated_epilogue_is_byte_identical(lib, dev, orc):
         layer.fused = fused
         for t in (layer.p_packed, layer.p_scales, layer.s_p_packed, layer.s_p_scales):
             t.zero_()
-        out = layer.forward(x).clone()
+        out = layer.forward_stages(x).clone()
         torch.cuda.synchronize()
         lib.gemb_check_device_status()
         rows = layer.slot_rows.long()
@@ -287,3 +288,68 @@ def test_fused_gated_epilogue_is_byte_identical(lib, dev, orc):
                         layer.s_p_scales.clone(), layer.y[rows].clone(), out))
     for a, b in zip(*results):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_library_layer_call_equals_the_stage_launches(lib, dev, fused):
+    """gemb_moe_layer_forward (the launch sequence inside the library, workspace filled with 0xFF
+    beforehand, shared branch forked onto a second stream) against the same operators launched one
+    by one: identical records and identical output bytes, with and without the fused GELU epilogue,
+    and the same again without a second stream."""
+    from gem16_b200.moe import synthetic_weights
+    tokens, topk = 333, 8
+    w = synthetic_weights(dev, 9)
+    g = torch.Generator(device=dev)
+    g.manual_seed(10)
+    x = torch.randn((tokens, 2816), device=dev, generator=g).to(torch.bfloat16).view(torch.int16)
+    a, b = MoeLayer(w, tokens, topk, 650.0, 336.0, 336.0), MoeLayer(w, tokens, topk, 650.0, 336.0, 336.0)
+    a.fused = b.fused = fused
+    want = a.forward_stages(x).clone()
+    got = b.forward(x).clone()
+    torch.cuda.synchronize()
+    lib.gemb_check_device_status()
+    for name in ("logits", "ids", "weights", "counts", "offsets", "perm", "slot_rows"):
+        assert torch.equal(getattr(a, name), getattr(b, name)), name
+    rows = a.slot_rows.long()
+    assert torch.equal(a.y[rows], b.y[rows]) and torch.equal(want, got)
+    # everything on one stream
+    desc = w.c_struct(topk, 650.0, 336.0, 336.0, fused=fused)
+    out = torch.zeros_like(got)
+    lib.gemb_moe_layer_forward(desc, x, out, tokens, b.c_base, b.c_workspace.numel() - 256, None, None, None, None)
+    torch.cuda.synchronize()
+    assert torch.equal(out, got)
+    # too small a workspace, a missing weight: rejected before anything runs
+    from gem16_b200.lib import GembError
+    with pytest.raises(GembError):
+        lib.gemb_moe_layer_forward(desc, x, out, tokens, b.c_base, 1024, None, None, None, None)
+    desc.down.packed_weight = None
+    with pytest.raises(GembError):
+        lib.gemb_moe_layer_forward(desc, x, out, tokens, b.c_base, b.c_workspace.numel() - 256, None, None, None, None)
+
+
+def test_router_specification_mode(lib, dev, orc):
+    """The router as docs/plans/gemma4-26b/specs/MOE_ROUTER_SPEC.md:3-13,41-63 writes it: r =
+    rmsnorm_noweight(x) * scale * hidden^-1/2, logits = W r (no bias), softmax, top-8, renormalise,
+    times per_expert_scale -- the transformed input, ids and weights bit for bit against the oracle,
+    alone and through the layer call."""
+    from gem16_b200.moe import synthetic_weights
+    rng = np.random.default_rng(12)
+    tokens, hidden, experts, topk = 200, 2816, 128, 8
+    x = bf16_bits((rng.standard_normal((tokens, hidden)) * 3).astype(np.float32))
+    scale = bf16_bits((1.0 + 0.3 * rng.standard_normal(hidden)).astype(np.float32))
+    pes = rng.uniform(0.5, 2.0, experts).astype(np.float32)
+    want_r = orc.moe_router_input(x, scale, 1e-6)
+    got_r = torch.zeros((tokens, hidden), dtype=torch.int16, device=dev)
+    lib.gemb_moe_router_input(to_dev(x, dev), to_dev(scale, dev), got_r, tokens, hidden, 1e-6, None)
+    assert np.array_equal(to_np(got_r, np.uint16), want_r)
+    w = synthetic_weights(dev, 13, zipf=False)
+    layer = MoeLayer(w, tokens, topk, 650.0, 336.0, 336.0, stages=False)
+    layer.router_scale, layer.per_expert_scale = to_dev(scale, dev), to_dev(pes, dev)
+    layer.forward(to_dev(x, dev))
+    torch.cuda.synchronize()
+    lib.gemb_check_device_status()
+    logits = orc.moe_router_logits(want_r, to_np(w.router_w), None)
+    ids, weights = orc.moe_route(logits, topk, per_expert_scale=pes)
+    assert np.array_equal(to_np(layer.logits).view(np.uint32), logits.view(np.uint32))
+    assert np.array_equal(to_np(layer.ids), ids)
+    assert np.array_equal(to_np(layer.weights).view(np.uint32), weights.view(np.uint32))
