@@ -1,34 +1,36 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-contraction hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode_gemv] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    torchrun --nproc-per-node N bench.py --gpus N ...        (one rank per GPU)
 
-One JSON line on stdout (rank 0).  Workloads (synthetic, seeded; shapes from the decode /
-prefill configurations of the Gemma-4 12B-like model):
+One JSON line on stdout (rank 0).  The headline workload is the expert-parallel MoE stack, the one
+of the path's three metrics that is defined at 1, 2, 4 and 8 GPUs:
 
-  decode_gemv   48 "layers" x {gate/up 3840->30720, down 15360->3840, QKV 3840->8192,
-                O 4096->3840}: FP8 E4M3 weights with bf16 per-row scales, bf16 activations
-                quantised per token to E4M3 inside each GEMV launch; 48 distinct weight sets
-                (10.76 GB, far larger than L2).  Metric: GB/s of algorithmic bytes.
+  moe_ep_stack_prefill   30 distinct 26B-A4B-like MoE layers (hidden 2816, 128 experts x 704, top-8,
+                shared FFN 2112, NVFP4 W4A4) over a 16,384-token batch.  Experts are split evenly over
+                the ranks, tokens are data-sharded (16,384 / N per rank), the router is replicated;
+                dispatch and combine run over NVLink peer memory inside the library's layer call.
+                A step is one pass of the batch through all 30 layers, replayed as one CUDA graph.
+                The total work is fixed as N grows (strong scaling).  Metric: tokens/s.
 
-  nvfp4_linear  (reported under "other_workloads") X bf16 [512, 3840] -> NVFP4 quantiser -> tcgen05 GEMM
-                against W NVFP4 [15360, 3840]; eight distinct weight sets (266 MB > L2) in rotation.
-                Metric: TFLOP/s counting the GEMM's 2*M*N*K flops, for the GEMM alone and with the
-                activation quantiser in the timed region.
-  moe_layer     (reported under "other_workloads") one 26B-A4B-like MoE layer on 4096 tokens: router,
-                top-8, stable permutation, dispatch, grouped NVFP4 expert GEMMs, GELU requantisation,
-                shared FFN, slot-ordered combine.  Metric: tokens/s.
+`value` is measured with the tokens resident in HBM; `e2e` copies each rank's tokens from pinned
+host memory and the bf16 result back inside the timed region.  The 64-token decode batch through
+the same stack is reported beside it, and the other workloads of the path (decode GEMV set, the
+single NVFP4 linear, the 4,096-token MoE layer, the dense prefill projections, output head,
+verifier GEMV, tensor-parallel MLP) under "other_workloads", each with its own roofline and, for
+the three named metrics, CPU baseline and end-to-end figures.
 
-A step is one pass over all 48 layers, replayed as one CUDA graph.  `value` is measured with
-inputs resident in HBM; `e2e` copies the step's activations from pinned host memory and the
-results back inside the timed region.  With N > 1 every rank runs an independent replica
-(the path does not shard at batch 1) and `value` is the sum over ranks.
+Every rank feeds every layer the same seeded N(0,1) tokens (the layers differ in their weights):
+chaining the layers without the norms and residuals that sit between them in the model would let the
+activations drift off the quantisers' static scales and the routing collapse.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -38,21 +40,30 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 DECODE_SHAPES = [("gate_up", 30720, 3840), ("down", 3840, 15360), ("qkv", 8192, 3840), ("o", 3840, 4096)]
-LAYERS = 48
+LAYERS = 48            # decode GEMV set
+MOE_LAYERS = 30
+MOE = dict(hidden=2816, experts=128, inter=704, shared_inter=2112, topk=8)
 SEED = 20261125
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum of the captured fp8_gemv_kernel launches divided by
-# their algorithmic bytes (profiles/fp8_gemv_kernel_decode.md).
-NCU_TRAFFIC_OVER_ALGORITHMIC = 1.00
+FP4_NOMINAL_TFLOPS = 9000.0      # dense NVFP4, vendor figure; no measured FP4 peak exists on this pool
+FP8_NOMINAL_TFLOPS = 4500.0
 
 
 def decode_bytes_per_layer() -> int:
-    """Algorithmic bytes of one layer: weights + fp32-equivalent scales + bf16 x + bf16 y."""
+    """Algorithmic bytes of one decode layer: weights + fp32-equivalent scales + bf16 x + bf16 y."""
     total = 0
     for _, rows, k in DECODE_SHAPES:
         total += rows * k + rows * 4 + k * 2 + rows * 2
     return total
+
+
+def moe_layer_flops(tokens: int) -> dict:
+    h, e, i, s, k = MOE["hidden"], MOE["experts"], MOE["inter"], MOE["shared_inter"], MOE["topk"]
+    return {"router": 2.0 * tokens * e * h, "experts": tokens * k * 2.0 * 3 * i * h, "shared": tokens * 2.0 * 3 * s * h}
+
+
+def moe_layer_weight_bytes() -> float:
+    h, e, i, s = MOE["hidden"], MOE["experts"], MOE["inter"], MOE["shared_inter"]
+    return e * 3 * i * h * 0.5625 + 3 * s * h * 0.5625 + e * h * 4
 
 
 def measured_peaks() -> dict:
@@ -60,12 +71,30 @@ def measured_peaks() -> dict:
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
-        return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "source": "fallback"}
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops", 1590.0)),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", 1400.0)), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def profile_traffic(name: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of a kernel, as recorded in the kept ncu
+    summary of that kernel (a line `traffic_bytes_per_launch: <n>` together with the algorithmic bytes
+    or flops of the captured launch).  None when no summary holds the figure."""
+    path = os.path.join(ROOT, "profiles", name)
+    out = {}
+    try:
+        with open(path) as f:
+            for line in f:
+                for key in ("traffic_bytes_per_launch", "captured_units_per_launch"):
+                    if line.strip().startswith(key + ":"):
+                        out[key] = float(line.split(":", 1)[1].split()[0].replace(",", ""))
+    except OSError:
+        return None
+    return out or None
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -84,6 +113,7 @@ class ClockSampler:
             self.thread.start()
         except OSError:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
@@ -112,18 +142,19 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------------
-# reference arm / CPU baseline: the reference's own CPU numeric path on a bounded sample
+# CPU baselines / reference arm: the reference's own CPU numeric functions on bounded samples
 # --------------------------------------------------------------------------------------------
-def cpu_decode_sample(steps: int, warmup: int, use_ref: bool):
-    """Times one decode layer (all four GEMVs incl. the per-token FP8 quantisation) on the host
-    cores with the reference's src/numeric/fp8.cpp functions (or the oracle port when the
-    compiled reference is absent).  Returns (GB/s, seconds per sample, cores, kind)."""
-    import numpy as np
+def cpu_oracles(use_ref: bool):
     from oracle import Oracle, default_threads, ref_available
     kind = "reference" if use_ref and ref_available() else "port"
-    o = Oracle(ref=(kind == "reference"))
-    port = Oracle()
-    threads = default_threads()
+    return Oracle(ref=(kind == "reference")), Oracle(), default_threads(), kind
+
+
+def cpu_decode_sample(steps: int, warmup: int, use_ref: bool):
+    """One decode layer (four FP8 GEMVs incl. the per-token quantisation) on the host cores with gem16's
+    src/numeric/fp8.cpp functions.  Returns (GB/s, seconds per layer, cores, kind)."""
+    import numpy as np
+    o, port, threads, kind = cpu_oracles(use_ref)
     rng = np.random.default_rng(SEED)
     layer = []
     for _, rows, k in DECODE_SHAPES:
@@ -147,239 +178,407 @@ def cpu_decode_sample(steps: int, warmup: int, use_ref: bool):
     return decode_bytes_per_layer() / dt / 1e9, dt, threads, kind
 
 
+def cpu_linear_sample(use_ref: bool, tokens: int = 8):
+    """`tokens` rows of the single NVFP4 linear (K = 3840, 15,360 output rows): gem16's QuantizeActivation
+    and ReferenceDotProduct (src/numeric/nvfp4.cpp:113-201).  Returns (TFLOP/s, seconds, cores, kind)."""
+    import numpy as np
+    o, port, threads, kind = cpu_oracles(use_ref)
+    rng = np.random.default_rng(SEED + 1)
+    n, k = 15360, 3840
+    wp = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    ws = rng.integers(0x30, 0x48, size=(n, k // 16), dtype=np.uint8)
+    x = port.from_bf16(port.to_bf16(rng.standard_normal((tokens, k)).astype(np.float32)))
+    t0 = time.perf_counter()
+    xp, xs = o.nvfp4_quantize(x, 600.0, threads=threads)
+    o.nvfp4_matmul(xp, xs, wp, ws, 600.0, 9000.0, threads=threads)
+    dt = time.perf_counter() - t0
+    return 2.0 * tokens * n * k / dt / 1e12, dt, threads, kind
+
+
+_CPU_MOE_CACHE = {}
+
+
+def cpu_moe_layer_sample(use_ref: bool, tokens: int = 64, fresh: bool = False):
+    """Cached wrapper (the own arm reports the same sample under two workloads)."""
+    key = (use_ref, tokens)
+    if fresh or key not in _CPU_MOE_CACHE:
+        _CPU_MOE_CACHE[key] = _cpu_moe_layer_sample(use_ref, tokens)
+    return _CPU_MOE_CACHE[key]
+
+
+def _cpu_moe_layer_sample(use_ref: bool, tokens: int = 64):
+    """One MoE layer on `tokens` tokens on the host cores: router, top-8, stable permutation and combine
+    through the CPU restatement of the specifications (gem16 has no MoE code), every expert and shared
+    projection through gem16's own QuantizeActivation / ReferenceDotProduct.  One random expert matrix
+    stands in for all 128 (only the time is wanted).  Returns (seconds per layer, cores, kind)."""
+    import numpy as np
+    o, port, threads, kind = cpu_oracles(use_ref)
+    rng = np.random.default_rng(SEED + 3)
+    h, e, i, s, k = MOE["hidden"], MOE["experts"], MOE["inter"], MOE["shared_inter"], MOE["topk"]
+
+    def rand_w(rows, kk):
+        return (rng.integers(0, 256, size=(rows, kk // 2), dtype=np.uint8),
+                rng.integers(0x30, 0x48, size=(rows, kk // 16), dtype=np.uint8))
+
+    gu, dn, sgu, sdn = rand_w(2 * i, h), rand_w(h, i), rand_w(2 * s, h), rand_w(h, s)
+    router_w = (rng.standard_normal((e, h)) * 0.02).astype(np.float32)
+    rank = rng.permutation(e) + 1
+    bias = (-1.1 * np.log(rank)).astype(np.float32)
+    xb = port.to_bf16(rng.standard_normal((tokens, h)).astype(np.float32))
+    x = port.from_bf16(xb)
+
+    def ffn(xq, xs, wgu, wdn, inter):
+        gate_up = port.from_bf16(port.to_bf16(o.nvfp4_matmul(xq, xs, wgu[0], wgu[1], 600.0, 9000.0, threads=threads).astype(np.float32)))
+        prod = port.gated_gelu(gate_up[:, :inter], gate_up[:, inter:])
+        pq, ps = o.nvfp4_quantize(prod, 336.0, threads=threads)
+        return port.to_bf16(o.nvfp4_matmul(pq, ps, wdn[0], wdn[1], 336.0, 9000.0, threads=threads).astype(np.float32))
+
+    t0 = time.perf_counter()
+    logits = port.moe_router_logits(xb, router_w, bias, threads=threads)
+    ids, weights = port.moe_route(logits, k)
+    counts, offsets, perm = port.moe_permute(ids, e)
+    xq, xs = o.nvfp4_quantize(x, 600.0, threads=threads)
+    y = np.zeros((tokens * k, h), np.uint16)
+    for ex in range(e):
+        sel = perm[offsets[ex]:offsets[ex + 1]]
+        if sel.size:
+            y[sel] = ffn(xq[sel // k], xs[sel // k], gu, dn, i)
+    shared = ffn(xq, xs, sgu, sdn, s)
+    port.moe_combine(y.reshape(tokens, k, h), weights, shared)
+    return time.perf_counter() - t0, threads, kind
+
+
 def run_reference_arm(args):
+    """The reference's CPU numeric path on this box's host cores, for the headline workload: each step
+    is one MoE layer on a 64-token sample; tokens/s of the whole 30-layer stack is that rate / 30."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    gbs, dt, cores, kind = cpu_decode_sample(args.steps, min(args.warmup, 1), use_ref=True)
-    sample = "one decode layer (4 FP8 GEMVs + per-token quantisation, 224 MB) per step, all host cores"
+    tokens = 64
+    steps = max(1, min(args.steps, 5))
+    times = []
+    for _ in range(min(args.warmup, 1) + steps):
+        dt, cores, kind = cpu_moe_layer_sample(use_ref=True, tokens=tokens, fresh=True)
+        times.append(dt)
+    dt = statistics.median(times[-steps:])
+    value = tokens / (dt * MOE_LAYERS)
+    sample = (f"{tokens}-token sample of ONE of the {MOE_LAYERS} layers per step ({dt:.2f} s on {cores} host threads); "
+              f"tokens/s of the stack = sample rate / {MOE_LAYERS} (extrapolated: CPU time is linear in tokens and layers)")
     line = {
-        "impl": "reference", "metric": "decode GEMV GB/s", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-        "config": {"workload": "decode_gemv", "layers": LAYERS, "shapes": DECODE_SHAPES},
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
-        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": "MoE stack tokens/s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (binary64 accumulate on the CPU)", "data": "synthetic",
+        "config": moe_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample,
+                         "note": "expert and shared projections: gem16 src/numeric/nvfp4.cpp; router / permutation / combine: "
+                                 "CPU restatement of gem16's MoE specifications (gem16 has no MoE code)"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-# --------------------------------------------------------------------------------------------
-# our arm
-# --------------------------------------------------------------------------------------------
-def run_decode_gemv(args):
-    import torch
-    import torch.distributed as dist
-    from gem16_b200 import load
+def moe_config(world: int) -> dict:
+    return {"workload": "moe_ep_stack_prefill", "layers": MOE_LAYERS, "tokens": 16384, **MOE,
+            "format": "NVFP4 W4A4, E4M3 block scales per 16, fp32 global divisors",
+            "parallelism": f"ep{world}" if world > 1 else "single GPU",
+            "l2": "30 distinct layers of expert weights, 12.8 GB per pass >> 126 MB L2",
+            "inputs": "every layer reads the same seeded N(0,1) bf16 tokens; router bias Zipf(1.1)"}
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+
+# --------------------------------------------------------------------------------------------
+# headline: the expert-parallel MoE stack
+# --------------------------------------------------------------------------------------------
+STAGE_BITS = {"route": 1, "pack": 2, "gate_up": 4, "gelu": 8, "down": 16, "combine": 32, "shared": 64, "exchange": 128}
+
+
+class Dist:
+    """Rank plumbing: NCCL process group when launched with torchrun, trivial otherwise."""
+
+    def __init__(self):
+        import torch
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+
+    def barrier(self):
+        import torch
+        torch.cuda.synchronize(self.dev)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize(self.dev)
+
+    def max(self, value: float) -> float:
+        if self.world == 1:
+            return value
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([value], device=self.dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def all_true(self, flag: bool) -> bool:
+        if self.world == 1:
+            return flag
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([1 if flag else 0], device=self.dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    def close(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+def timed_region(d: Dist, stream, fn, steps: int) -> float:
+    """Seconds for exactly `steps` calls of fn: CUDA events on the launching stream, a barrier and a
+    device synchronise on both sides, the maximum over ranks."""
+    import torch
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    d.barrier()
+    start.record(stream)
+    for _ in range(steps):
+        fn()
+    end.record(stream)
+    d.barrier()
+    return d.max(start.elapsed_time(end) / 1e3)
+
+
+def repeated_regions(d: Dist, stream, fn, steps: int, min_seconds: float = 0.5, max_regions: int = 9):
+    """Runs the K-step region until at least min_seconds of device time have been measured (at most
+    max_regions times) and returns (median seconds per region, all samples)."""
+    samples = []
+    while len(samples) < 1 or (sum(samples) < min_seconds and len(samples) < max_regions):
+        samples.append(timed_region(d, stream, fn, steps))
+    return statistics.median(samples), samples
+
+
+def capture(stream, enqueue):
+    """enqueue() once eagerly, then captured (twice: a graph with a forked side stream instantiated right
+    after the eager pass has replayed measurably slower here than the same capture taken once more)."""
+    import torch
+    with torch.cuda.stream(stream):
+        enqueue()
+        stream.synchronize()
+        for _ in range(2):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                enqueue()
+            g.replay()
+            stream.synchronize()
+    return g
+
+
+def run_moe_stack(args):
+    import torch
+    from gem16_b200 import load
+    from gem16_b200.ep import EpLayer
+    from gem16_b200.moe import MoeLayer, synthetic_weights
+
+    d = Dist()
+    dev, world, rank = d.dev, d.world, d.rank
     lib = load()
     lib.gemb_device_check()
-
-    # ---- synthetic model state: 48 distinct FP8 weight sets quantised with our own quantizer --
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(SEED + 1000 * 1 + rank)
-    weights = []
-    layers = args.layers
-    for layer in range(layers):
-        mats = []
-        for _, rows, k in DECODE_SHAPES:
-            w = torch.randn((rows, k), device=dev, dtype=torch.float32, generator=gen) * 0.02
-            wq = torch.empty((rows, k), device=dev, dtype=torch.uint8)
-            wsc = torch.empty((rows,), device=dev, dtype=torch.float32)
-            lib.gemb_fp8_quantize(w, 0, wq, wsc, rows, k, None)
-            mats.append((wq, wsc.to(torch.bfloat16).view(torch.int16)))
-            del w
-        weights.append(mats)
-    # activations: one bf16 vector per op, in one contiguous buffer (device + pinned host copy)
-    x_elems = sum(k for _, _, k in DECODE_SHAPES) * layers
-    y_elems = sum(r for _, r, _ in DECODE_SHAPES) * layers
-    x_host = torch.randn((x_elems,), dtype=torch.float32).to(torch.bfloat16).pin_memory()
-    y_host = torch.empty((y_elems,), dtype=torch.bfloat16).pin_memory()
-    x_dev = x_host.to(dev)
-    y_dev = torch.zeros((y_elems,), device=dev, dtype=torch.bfloat16)
-
-    # "fused": one launch per projection, the bf16 activation is quantised inside the GEMV.
-    # "split": the decode-size token quantizer, then the GEMV on E4M3 bytes (fp32 out); with
-    # programmatic dependent launch the GEMV prefetches weights while the quantizer runs.
-    split = args.decode_path == "split"
-    xq_dev = torch.empty((x_elems,), dtype=torch.uint8, device=dev)
-    xs_dev = torch.empty((layers * len(DECODE_SHAPES),), device=dev)
-    y32_dev = torch.zeros((y_elems,), device=dev) if split else None
-    y_host32 = torch.empty((y_elems,), dtype=torch.float32).pin_memory() if split else None
-
-    def enqueue_pass():
-        xo = yo = 0
-        n = 0
-        st = torch.cuda.current_stream()
-        for mats in weights:
-            for (wq, ws), (_, rows, k) in zip(mats, DECODE_SHAPES):
-                if split:
-                    lib.gemb_fp8_quantize(x_dev[xo:xo + k], 1, xq_dev[xo:xo + k], xs_dev[n:n + 1], 1, k, st)
-                    lib.gemb_fp8_gemv(xq_dev[xo:xo + k], xs_dev[n:n + 1], wq, ws, y32_dev[yo:yo + rows], rows, k, st)
-                else:
-                    lib.gemb_fp8_gemv_bf16in(x_dev[xo:xo + k], wq, ws, y_dev[yo:yo + rows], 1, rows, k, st)
-                xo += k
-                yo += rows
-                n += 1
-        return n * (2 if split else 1)
-
-    def enqueue_gemvs_only():
-        # The same projections on the already quantised activations: the dominant kernel alone,
-        # for the roofline object (its launches are 99.9 % of the bytes of a pass).
-        xo = yo = n = 0
-        st = torch.cuda.current_stream()
-        for mats in weights:
-            for (wq, ws), (_, rows, k) in zip(mats, DECODE_SHAPES):
-                lib.gemb_fp8_gemv(xq_dev[xo:xo + k], xs_dev[n:n + 1], wq, ws, y32_dev[yo:yo + rows], rows, k, st)
-                xo += k
-                yo += rows
-                n += 1
-        return n
-
+    layers = args.moe_layers
+    e_local = MOE["experts"] // world
+    own = (rank * e_local, (rank + 1) * e_local)
+    weights = [synthetic_weights(dev, SEED + 4000 + l, expert_range=own if world > 1 else None, placement_ranks=world)
+               for l in range(layers)]
+    topk, h = MOE["topk"], MOE["hidden"]
+    phases = {}
     stream = torch.cuda.Stream(device=dev)
-    with torch.cuda.stream(stream):
-        launches_per_step = enqueue_pass()  # also warms lazily initialised state before capture
-        stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            enqueue_pass()
-        gemv_graph = None
-        gemv_launches = 0
-        if split:
-            gemv_launches = enqueue_gemvs_only()
-            stream.synchronize()
-            gemv_graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gemv_graph, stream=stream):
-                enqueue_gemvs_only()
+    for name, tokens in (("prefill", 16384), ("decode", 64)):
+        t_local = tokens // world
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(SEED + 4100)
+        x_all = torch.randn((tokens, h), device=dev, generator=gen).to(torch.bfloat16)
+        ga = float(2688.0 / x_all.float().abs().max().item())
+        x_dev = x_all[rank * t_local:(rank + 1) * t_local].contiguous().view(torch.int16)
+        x_host = x_dev.cpu().pin_memory()
+        out_host = torch.empty((t_local, h), dtype=torch.int16).pin_memory()
+        if world > 1:
+            obj = EpLayer(weights[0], t_local, topk, ga, 336.0, 336.0, fused=args.fused)
+        else:
+            obj = MoeLayer(weights[0], tokens, topk, ga, 336.0, 336.0, stages=False)
+            obj.fused = args.fused
 
-        def barrier():
-            torch.cuda.synchronize(dev)
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize(dev)
+        def enqueue():
+            for w in weights:
+                obj.w = w
+                if world > 1:
+                    obj.forward(x_dev)
+                else:
+                    obj.forward(x_dev, torch.cuda.current_stream())
 
-        def timed(fn, steps):
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            barrier()
-            start.record(stream)
-            for _ in range(steps):
-                fn()
-            end.record(stream)
-            barrier()
-            ms = start.elapsed_time(end)
-            if world > 1:
-                t = torch.tensor([ms], device=dev)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                ms = float(t.item())
-            return ms / 1e3
-
-        def step_resident():
-            graph.replay()
+        graph = capture(stream, enqueue)
 
         def step_e2e():
             x_dev.copy_(x_host, non_blocking=True)
             graph.replay()
-            (y_host32 if split else y_host).copy_(y32_dev if split else y_dev, non_blocking=True)
+            out_host.copy_(obj.out, non_blocking=True)
             stream.synchronize()
 
-        for _ in range(max(args.warmup, 3)):
-            step_resident()
-        sampler = ClockSampler(local)
-        if rank == 0:
-            sampler.start()
-        secs = timed(step_resident, args.steps)
-        clocks = sampler.stop() if rank == 0 else None
-        for _ in range(2):
-            step_e2e()
-        secs_e2e = timed(step_e2e, args.steps)
-        secs_gemv = None
-        if gemv_graph is not None:
-            for _ in range(3):
-                gemv_graph.replay()
-            secs_gemv = timed(gemv_graph.replay, args.steps)
-
-    bytes_step = decode_bytes_per_layer() * layers
-    value = world * bytes_step * args.steps / secs / 1e9
-    e2e = world * bytes_step * args.steps / secs_e2e / 1e9
-    moe_ep = tp_mlp = None
-    if not args.no_other_workloads:
-        del weights, graph, gemv_graph
+        with torch.cuda.stream(stream):
+            for _ in range(max(args.warmup, 3)):
+                graph.replay()
+            sampler = ClockSampler(d.local).start() if rank == 0 else None
+            secs, samples = repeated_regions(d, stream, graph.replay, args.steps)
+            clocks = sampler.stop() if sampler else None
+            for _ in range(2):
+                step_e2e()
+            secs_e2e, _ = repeated_regions(d, stream, step_e2e, args.steps)
+            lib.gemb_check_device_status()
+            # Stage by stage: the same graph with one stage of the layer call enabled at a time, on the
+            # workspace the full pass left behind (each layer's own weights, the last layer's plan).
+            stage_us = {}
+            counts_total = int(obj.counts.sum().item()) if world == 1 else int(obj.counts_all[:, own[0]:own[1]].sum().item())
+            if not args.no_stage_times:
+                for sname, bit in STAGE_BITS.items():
+                    if sname == "gelu" and args.fused:
+                        continue
+                    if sname == "exchange" and world == 1:
+                        continue
+                    lib.gemb_set_tuning(7, bit)
+                    try:
+                        g = capture(stream, enqueue)
+                        for _ in range(2):
+                            g.replay()
+                        t = timed_region(d, stream, g.replay, 5) / 5 / layers
+                        stage_us[sname] = t * 1e6
+                    finally:
+                        lib.gemb_set_tuning(7, 0)
+                    del g
+                lib.gemb_check_device_status()
+        phases[name] = {"tokens": tokens, "tokens_per_rank": t_local, "secs_per_step": secs / args.steps,
+                        "region_samples_s": samples, "secs_per_step_e2e": secs_e2e / args.steps, "clocks": clocks,
+                        "stage_us_per_layer": stage_us, "assignments_on_rank0_last_layer": counts_total,
+                        "h2d_bytes": x_host.numel() * 2 * world, "d2h_bytes": out_host.numel() * 2 * world,
+                        "exchange": ("peer memory, " + obj.send.how) if world > 1 else "none"}
+        del graph, obj, x_all
         torch.cuda.empty_cache()
-        try:   # collective: every rank takes part
-            moe_ep = bench_moe_ep(lib, dev, world, rank)
-        except Exception as exc:
-            moe_ep = {"error": f"{type(exc).__name__}: {exc}"}
-        if world > 1:
-            try:
-                tp_mlp = bench_tp_mlp(lib, dev, world, rank)
-            except Exception as exc:
-                tp_mlp = {"error": f"{type(exc).__name__}: {exc}"}
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    peaks = measured_peaks()
-    # Roofline of the dominant kernel: algorithmic bytes of one GEMV launch (its weight matrix, the
-    # bf16 row scales, the activation and the output; the pass total / launches) over that kernel's
-    # average launch duration, timed with CUDA events over a region that launches only it.
-    if secs_gemv is not None:
-        launch_s = secs_gemv / (args.steps * gemv_launches)
-        achieved = bytes_step / gemv_launches / launch_s / 1e9
-    else:
-        launch_s = secs / (args.steps * launches_per_step)
-        achieved = bytes_step / launches_per_step / launch_s / 1e9
-    whole_pass = bytes_step * args.steps / secs / 1e9 if world == 1 else value / world
-    line = {
-        "metric": "decode GEMV GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": "decode_gemv", "layers": layers, "shapes": DECODE_SHAPES,
-                   "l2": f"{layers} distinct weight sets, {bytes_step / 1e9:.2f} GB per pass >> 126 MB L2",
-                   "multi_gpu": "replicas only", "decode_path": args.decode_path},
-        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": x_elems * 2, "d2h_bytes_per_step": y_elems * (4 if split else 2)},
-        "gpu_launches": launches_per_step * args.steps,
-        "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "fp8_gemv_kernel" + ("" if split else " (bf16-in fused quantisation)"),
-                     "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                     "frac_of_nominal_8TBs": achieved / 8000.0,
-                     # dram read + write bytes per launch from the committed ncu capture of this kernel
-                     # (profiles/fp8_gemv_kernel_decode.md), as a ratio to the algorithmic bytes
-                     "traffic": NCU_TRAFFIC_OVER_ALGORITHMIC * bytes_step / (gemv_launches if secs_gemv is not None else launches_per_step),
-                     "traffic_unit": "bytes per launch (average)",
-                     "algorithmic_bytes_per_launch": bytes_step / (gemv_launches if secs_gemv is not None else launches_per_step),
-                     "avg_launch_us": launch_s * 1e6,
-                     "whole_pass": {"kernels": "fp8_quantize_decode_kernel + fp8_gemv_kernel" if split else "fp8_gemv_kernel",
-                                    "achieved": whole_pass, "frac": whole_pass / peaks["hbm_gbs"],
-                                    "launches_per_pass": launches_per_step}},
-    }
-    if moe_ep is not None:
-        line["other_workloads"] = {"moe_ep_stack": moe_ep}
-        if tp_mlp is not None:
-            line["other_workloads"]["tp_mlp"] = tp_mlp
-    if world == 1 and not args.no_other_workloads:
-        other = line["other_workloads"]
-        for name, fn in (("nvfp4_linear", bench_nvfp4_linear), ("prefill_gemm", bench_prefill_gemm),
-                         ("prefill_stack", bench_prefill_stack), ("moe_layer", bench_moe_layer),
-                         ("output_head", bench_output_head), ("verifier_gemv", bench_verifier_gemv)):
-            try:
-                other[name] = fn(lib, dev)
-            except Exception as exc:  # a secondary workload must not take the headline line down
-                other[name] = {"error": f"{type(exc).__name__}: {exc}"}
-    if world == 1 and not args.no_cpu_baseline:
-        gbs, dt, cores, kind = cpu_decode_sample(1, 0, use_ref=True)
-        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
-                                "sample": f"one decode layer of 48 (224 MB), {dt:.2f} s on {cores} host threads"}
-    print(json.dumps(line), flush=True)
+
+    # Bit-exactness of the expert-parallel layer against the single-GPU layer, on every rank, outside
+    # the timed regions: 96 tokens per rank through both.
+    parity = None
     if world > 1:
-        dist.destroy_process_group()
+        t_local = 96
+        full = synthetic_weights(dev, SEED + 4000, placement_ranks=world)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(SEED + 4200)
+        x_all = torch.randn((t_local * world, h), device=dev, generator=gen).to(torch.bfloat16).view(torch.int16)
+        sl = slice(rank * t_local, (rank + 1) * t_local)
+        ref = MoeLayer(full, t_local * world, topk, 600.0, 336.0, 336.0, stages=False)
+        ref.fused = args.fused
+        want = ref.forward(x_all).clone()
+        ref_local = MoeLayer(full, t_local, topk, 600.0, 336.0, 336.0, stages=False)
+        ref_local.fused = args.fused
+        ref_local.forward(x_all[sl].contiguous())
+        ep = EpLayer(weights[0], t_local, topk, 600.0, 336.0, 336.0, fused=args.fused)
+        for _ in range(2):
+            got = ep.forward(x_all[sl].contiguous())
+        torch.cuda.synchronize()
+        lib.gemb_check_device_status()
+        routing = (torch.equal(ep.ids, ref.ids[sl]) and torch.equal(ep.weights, ref.weights[sl])
+                   and torch.equal(ep.counts_all.sum(0).to(torch.int32), ref.counts)
+                   and torch.equal(ep.counts, ref_local.counts) and torch.equal(ep.perm, ref_local.perm))
+        parity = {"ranks": world, "tokens_per_rank": t_local,
+                  "ids_counts_perm_bit_exact": d.all_true(bool(routing)),
+                  "output_bit_exact": d.all_true(bool(torch.equal(got, want[sl])))}
+        del full, ref, ref_local, ep
+        torch.cuda.empty_cache()
+    del weights
+    torch.cuda.empty_cache()
+    return d, lib, phases, parity
+
+
+def moe_headline(args):
+    d, lib, phases, parity = run_moe_stack(args)
+    import torch
+    world, rank, dev = d.world, d.rank, d.dev
+    layers = args.moe_layers
+    others = {}
+    if not args.no_other_workloads:
+        if world > 1:
+            try:
+                others["tp_mlp"] = bench_tp_mlp(lib, dev, world, rank)
+            except Exception as exc:
+                others["tp_mlp"] = {"error": f"{type(exc).__name__}: {exc}"}
+        elif rank == 0:
+            for name, fn in (("decode_gemv", bench_decode_gemv), ("nvfp4_linear", bench_nvfp4_linear), ("moe_layer", bench_moe_layer),
+                             ("prefill_gemm", bench_prefill_gemm), ("prefill_stack", bench_prefill_stack),
+                             ("output_head", bench_output_head), ("verifier_gemv", bench_verifier_gemv)):
+                try:
+                    others[name] = fn(lib, dev, args)
+                except Exception as exc:  # a secondary workload must not take the headline line down
+                    others[name] = {"error": f"{type(exc).__name__}: {exc}"}
+    if rank != 0:
+        d.close()
+        return
+    pre, dec = phases["prefill"], phases["decode"]
+    tokens = pre["tokens"]
+    value = tokens / pre["secs_per_step"]
+    flops = moe_layer_flops(tokens)
+    peaks = measured_peaks()
+    # Roofline of the dominant kernel, the grouped gate/up GEMM of rank 0: algorithmic flops of one launch
+    # (the rank's real assignments x 2 x 1408 x 2816) over its average duration in a graph that launches
+    # only that kernel for every layer.
+    gate_us = pre["stage_us_per_layer"].get("gate_up")
+    roof = None
+    if gate_us:
+        launch_flops = pre["assignments_on_rank0_last_layer"] * 2.0 * 2 * MOE["inter"] * MOE["hidden"]
+        achieved = launch_flops / (gate_us * 1e-6) / 1e12
+        prof = profile_traffic("gemm_kernel_grouped_gate_up.md")
+        traffic = None
+        if prof and prof.get("captured_units_per_launch"):
+            traffic = prof["traffic_bytes_per_launch"] * pre["assignments_on_rank0_last_layer"] / prof["captured_units_per_launch"]
+        roof = {"bound": "tensor", "kernel": "gemm_kernel<nvfp4, grouped 128x256> gate/up" + (" + GELU requantising epilogue" if args.fused else ""),
+                "achieved": achieved, "peak": FP4_NOMINAL_TFLOPS, "unit": "TFLOP/s", "frac": achieved / FP4_NOMINAL_TFLOPS,
+                "peak_source": "nominal dense NVFP4 (9 PFLOP/s): no measured FP4 peak exists for this pool",
+                "frac_of_4x_measured_bf16": achieved / (4 * peaks["bf16_tflops"]),
+                "avg_launch_us": gate_us, "flops_per_launch": launch_flops,
+                "time_x_sm_mhz": gate_us * (pre["clocks"]["sm_mhz"] or 0) if pre["clocks"] else None,
+                "traffic": traffic, "traffic_unit": "dram bytes per launch, scaled from the kept ncu capture by assignments",
+                "per_rank_bound_us_per_layer": {
+                    "tensor_at_nominal": sum(flops.values()) / world / (FP4_NOMINAL_TFLOPS * 1e12) * 1e6,
+                    "weights_over_hbm": moe_layer_weight_bytes() / world / (peaks["hbm_gbs"] * 1e9) * 1e6,
+                    "nvlink_combine": (tokens / world) * MOE["topk"] * (world - 1) / world * MOE["hidden"] * 2 / 770e9 * 1e6}}
+    launches_per_layer = (11 if args.fused else 12) + (3 if world > 1 else 0)
+    line = {
+        "metric": "MoE stack tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": pre["secs_per_step"] * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (W4A4, fp32 accumulate)", "data": "synthetic",
+        "config": dict(moe_config(world), layers=layers, exchange=pre["exchange"], fused_gelu_epilogue=bool(args.fused),
+                       timing=f"median of {len(pre['region_samples_s'])} regions of {args.steps} steps"),
+        "e2e": {"value": tokens / pre["secs_per_step_e2e"], "unit": "tokens/s", "h2d_bytes_per_step": pre["h2d_bytes"],
+                "d2h_bytes_per_step": pre["d2h_bytes"]},
+        "gpu_launches": launches_per_layer * layers * args.steps,
+        "clocks": pre["clocks"],
+        "roofline": roof,
+        "us_per_layer": pre["secs_per_step"] / layers * 1e6,
+        "stage_us_per_layer": pre["stage_us_per_layer"],
+        "decode_phase": {"tokens": 64, "value": 64 / dec["secs_per_step"], "unit": "tokens/s",
+                         "us_per_layer": dec["secs_per_step"] / layers * 1e6,
+                         "e2e": 64 / dec["secs_per_step_e2e"], "stage_us_per_layer": dec["stage_us_per_layer"],
+                         "clocks": dec["clocks"]},
+    }
+    if parity is not None:
+        line["ep_parity"] = parity
+    if others:
+        line["other_workloads"] = others
+    if world == 1 and not args.no_cpu_baseline:
+        dt, cores, kind = cpu_moe_layer_sample(use_ref=True, tokens=64)
+        line["cpu_baseline"] = {"value": 64 / (dt * layers), "unit": "tokens/s", "cores": cores, "kind": kind,
+                                "sample": f"64 tokens through one of the {layers} layers: {dt:.2f} s on {cores} host threads; "
+                                          f"stack rate extrapolated as sample rate / {layers}"}
+    print(json.dumps(line), flush=True)
+    d.close()
 
 
 # --------------------------------------------------------------------------------------------
@@ -411,7 +610,7 @@ def graph_time(enqueue, launches_per_graph, reps=20):
     return s.elapsed_time(e) / reps / 1e3
 
 
-def bench_nvfp4_linear(lib, dev):
+def bench_nvfp4_linear(lib, dev, args=None):
     import torch
     m, n, k, copies = 512, 15360, 3840, 8
     gen = torch.Generator(device=dev)
@@ -441,22 +640,51 @@ def bench_nvfp4_linear(lib, dev):
             lib.gemb_nvfp4_quantize(x.view(torch.int16), 1, xq, xs, m, k, ga, 1, 0, st)
             lib.gemb_nvfp4_gemm_bf16(xq, xs, wq, wsc, out, m, n, k, ga, gw, st)
 
-    t_gemm = graph_time(gemm_only, copies) / copies
-    t_both = graph_time(quant_and_gemm, 2 * copies) / copies
+    reps = 3000      # 8 linears per replay: about half a second of device time
+    t_gemm, clocks = sampled(lambda: graph_time(gemm_only, copies, reps=reps) / copies, dev.index or 0)
+    t_both = graph_time(quant_and_gemm, 2 * copies, reps=reps // 2) / copies
+    # end to end: bf16 activations from pinned host memory, quantiser + GEMM, bf16 result back
+    x_host = x.view(torch.int16).cpu().pin_memory()
+    y_host = torch.empty((m, n), dtype=torch.int16).pin_memory()
+    st = torch.cuda.Stream(device=dev)
+    xi = x.view(torch.int16)
+    with torch.cuda.stream(st):
+        def e2e_step(i):
+            wq, wsc, gw = ws[i % copies]
+            xi.copy_(x_host, non_blocking=True)
+            lib.gemb_nvfp4_quantize(xi, 1, xq, xs, m, k, ga, 1, 0, st)
+            lib.gemb_nvfp4_gemm_bf16(xq, xs, wq, wsc, out, m, n, k, ga, gw, st)
+            y_host.copy_(out, non_blocking=True)
+            st.synchronize()
+        for i in range(3):
+            e2e_step(i)
+        t0 = time.perf_counter()
+        for i in range(40):
+            e2e_step(i)
+        t_e2e = (time.perf_counter() - t0) / 40
     lib.gemb_check_device_status()
     flops = 2.0 * m * n * k
-    nominal = 9000.0
-    return {"metric": "NVFP4 GEMM TFLOP/s", "workload": "nvfp4_linear 512x15360x3840 (W4A4)",
-            "value": flops / t_gemm / 1e12, "unit": "TFLOP/s", "us_per_linear": t_gemm * 1e6,
-            "with_activation_quantizer": {"value": flops / t_both / 1e12, "us_per_linear": t_both * 1e6},
-            "roofline": {"bound": "tensor", "kernel": "gemm_kernel<nvfp4, 256x256 on CTA pairs>", "achieved": flops / t_gemm / 1e12,
-                         "peak": nominal, "unit": "TFLOP/s", "frac": flops / t_gemm / 1e12 / nominal,
-                         "peak_source": "nominal dense FP4 (9 PFLOP/s); MEASURED_PEAKS.json has no FP4 figure",
-                         "frac_of_4x_measured_bf16_sustained": flops / t_gemm / 1e12 / (4 * 1391.3)},
-            "l2": f"{copies} distinct weight sets in rotation, {copies * (n * k // 2 + n * k // 16) / 1e6:.0f} MB > 126 MB L2"}
+    peaks = measured_peaks()
+    res = {"metric": "NVFP4 GEMM TFLOP/s", "workload": "nvfp4_linear 512x15360x3840 (W4A4)",
+           "value": flops / t_gemm / 1e12, "unit": "TFLOP/s", "us_per_linear": t_gemm * 1e6, "dtype": "nvfp4 (W4A4, fp32 accumulate)",
+           "with_activation_quantizer": {"value": flops / t_both / 1e12, "us_per_linear": t_both * 1e6},
+           "e2e": {"value": flops / t_e2e / 1e12, "unit": "TFLOP/s", "us_per_linear": t_e2e * 1e6,
+                   "h2d_bytes_per_step": m * k * 2, "d2h_bytes_per_step": m * n * 2},
+           "clocks": clocks, "timed_region_s": t_gemm * copies * reps,
+           "roofline": {"bound": "tensor", "kernel": "gemm_kernel<nvfp4, 256x256 on CTA pairs>", "achieved": flops / t_gemm / 1e12,
+                        "peak": FP4_NOMINAL_TFLOPS, "unit": "TFLOP/s", "frac": flops / t_gemm / 1e12 / FP4_NOMINAL_TFLOPS,
+                        "peak_source": "nominal dense NVFP4 (9 PFLOP/s): no measured FP4 peak exists for this pool",
+                        "frac_of_4x_measured_bf16": flops / t_gemm / 1e12 / (4 * peaks["bf16_tflops"]),
+                        "time_x_sm_mhz": t_gemm * 1e6 * (clocks["sm_mhz"] or 0)},
+           "l2": f"{copies} distinct weight sets in rotation, {copies * (n * k // 2 + n * k // 16) / 1e6:.0f} MB > 126 MB L2"}
+    if args is None or not args.no_cpu_baseline:
+        tf, dt, cores, kind = cpu_linear_sample(use_ref=True, tokens=8)
+        res["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": kind,
+                               "sample": f"8 of the 512 tokens x all 15,360 rows (gem16 QuantizeActivation + ReferenceDotProduct): {dt:.2f} s on {cores} host threads"}
+    return res
 
 
-def bench_prefill_gemm(lib, dev):
+def bench_prefill_gemm(lib, dev, args=None):
     """The 16,384-token prefill projections of one 12B-like layer (shapes of the prefill stack):
     NVFP4 gate/up/down and FP8 QKV/O GEMMs on pre-quantised operands, each timed alone."""
     import torch
@@ -498,7 +726,7 @@ def bench_prefill_gemm(lib, dev):
     return out
 
 
-def bench_prefill_stack(lib, dev, layers=48, tokens=16384):
+def bench_prefill_stack(lib, dev, args=None, layers=48, tokens=16384):
     """Dense 12B-like prefill linear stack: per layer FP8 QKV and O projections and the NVFP4 gated
     MLP, every activation quantiser inside the timed region (attention itself is replaced by a
     seeded bf16 tensor: it is not part of this path)."""
@@ -563,29 +791,82 @@ def bench_prefill_stack(lib, dev, layers=48, tokens=16384):
             "ideal_ms_per_layer_at_nominal_peaks": (fp8_flops / 4.5e15 + fp4_flops / 9e15) * 1e3}
 
 
-def bench_moe_layer(lib, dev, tokens=4096):
+def bench_moe_layer(lib, dev, args=None, tokens=4096):
+    """One 26B-A4B-like MoE layer on 4,096 tokens through gemb_moe_layer_forward (one CUDA graph)."""
     import torch
     from gem16_b200.moe import MoeLayer, synthetic_weights
+    fused = True if args is None else args.fused
     w = synthetic_weights(dev, SEED + 3000)
     gen = torch.Generator(device=dev)
     gen.manual_seed(SEED + 3001)
     x = torch.randn((tokens, 2816), device=dev, generator=gen).to(torch.bfloat16)
     ga = float(2688.0 / x.float().abs().max().item())
-    layer = MoeLayer(w, tokens, 8, ga, 2688.0 / 8.0, 2688.0 / 8.0)
+    layer = MoeLayer(w, tokens, 8, ga, 2688.0 / 8.0, 2688.0 / 8.0, stages=False)
+    layer.fused = fused
     xi = x.view(torch.int16)
-    secs = graph_time(lambda st: layer.forward(xi, st), 14)
+    x_host = xi.cpu().pin_memory()
+    out_host = torch.empty((tokens, 2816), dtype=torch.int16).pin_memory()
+    st = torch.cuda.Stream(device=dev)
+    graph = capture(st, lambda: layer.forward(xi, st))
+
+    def region(fn, reps):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            fn()
+        st.synchronize()
+        s.record(st)
+        for _ in range(reps):
+            fn()
+        e.record(st)
+        st.synchronize()
+        return s.elapsed_time(e) / reps / 1e3
+
+    def step_e2e():
+        xi.copy_(x_host, non_blocking=True)
+        graph.replay()
+        out_host.copy_(layer.out, non_blocking=True)
+        st.synchronize()
+
+    with torch.cuda.stream(st):
+        secs, clocks = sampled(lambda: region(graph.replay, 1200), dev.index or 0)
+        secs_e2e = region(step_e2e, 100)
+        stage_us = {}
+        for sname, bit in STAGE_BITS.items():
+            if (sname == "gelu" and fused) or sname == "exchange":
+                continue
+            lib.gemb_set_tuning(7, bit)
+            try:
+                g = capture(st, lambda: layer.forward(xi, st))
+                stage_us[sname] = region(g.replay, 50) * 1e6
+            finally:
+                lib.gemb_set_tuning(7, 0)
     lib.gemb_check_device_status()
-    flops = 2.0 * tokens * 128 * 2816 + tokens * 8 * 2.0 * 3 * 704 * 2816 + tokens * 2.0 * 3 * 2112 * 2816
-    weight_bytes = 128 * 3 * 704 * 2816 * 0.5625 + 3 * 2112 * 2816 * 0.5625 + 128 * 2816 * 4
-    return {"metric": "MoE layer tokens/s", "workload": f"moe_layer {tokens} tokens, 128 experts top-8, hidden 2816, expert 704, shared 2112",
-            "value": tokens / secs, "unit": "tokens/s", "us_per_layer": secs * 1e6,
-            "flops": flops, "achieved_tflops": flops / secs / 1e12, "weight_bytes": weight_bytes,
-            "bounds_us": {"tensor_at_9PF": flops / 9e15 * 1e6, "hbm_weights_at_measured_peak": weight_bytes / (measured_peaks()["hbm_gbs"] * 1e9) * 1e6},
-            "padded_rows": int(layer.plan[1].item()), "tiles": int(layer.plan[0].item()),
-            "expert_count_max": int(layer.counts.max().item()), "expert_count_min": int(layer.counts.min().item())}
+    fl = moe_layer_flops(tokens)
+    flops = sum(fl.values())
+    weight_bytes = moe_layer_weight_bytes()
+    peaks = measured_peaks()
+    gate_flops = tokens * 8 * 2.0 * 2 * 704 * 2816
+    res = {"metric": "MoE layer tokens/s", "workload": f"moe_layer {tokens} tokens, 128 experts top-8, hidden 2816, expert 704, shared 2112",
+           "value": tokens / secs, "unit": "tokens/s", "us_per_layer": secs * 1e6, "dtype": "nvfp4 (W4A4, fp32 accumulate)",
+           "fused_gelu_epilogue": bool(fused), "timed_region_s": secs * 1200, "clocks": clocks,
+           "e2e": {"value": tokens / secs_e2e, "unit": "tokens/s", "h2d_bytes_per_step": tokens * 2816 * 2, "d2h_bytes_per_step": tokens * 2816 * 2},
+           "stage_us": stage_us, "flops": flops, "achieved_tflops": flops / secs / 1e12, "weight_bytes": weight_bytes,
+           "bounds_us": {"tensor_at_9PF": flops / 9e15 * 1e6, "hbm_weights_at_measured_peak": weight_bytes / (peaks["hbm_gbs"] * 1e9) * 1e6},
+           "roofline": {"bound": "tensor", "kernel": "gemm_kernel<nvfp4, grouped 128x256> gate/up" + (" + GELU requantising epilogue" if fused else ""),
+                        "achieved": gate_flops / (stage_us["gate_up"] * 1e-6) / 1e12, "peak": FP4_NOMINAL_TFLOPS, "unit": "TFLOP/s",
+                        "frac": gate_flops / (stage_us["gate_up"] * 1e-6) / 1e12 / FP4_NOMINAL_TFLOPS,
+                        "peak_source": "nominal dense NVFP4 (9 PFLOP/s): no measured FP4 peak exists for this pool",
+                        "avg_launch_us": stage_us["gate_up"], "time_x_sm_mhz": stage_us["gate_up"] * (clocks["sm_mhz"] or 0)},
+           "padded_rows": int(layer.plan[1].item()), "tiles": int(layer.plan[0].item()),
+           "expert_count_max": int(layer.counts.max().item()), "expert_count_min": int(layer.counts.min().item())}
+    if args is None or not args.no_cpu_baseline:
+        dt, cores, kind = cpu_moe_layer_sample(use_ref=True, tokens=64)
+        res["cpu_baseline"] = {"value": 64 / dt, "unit": "tokens/s", "cores": cores, "kind": kind,
+                               "sample": f"64 of the {tokens} tokens through the layer: {dt:.2f} s on {cores} host threads"}
+    return res
 
 
-def bench_output_head(lib, dev, vocab=262144, hidden=3840):
+def bench_output_head(lib, dev, args=None, vocab=262144, hidden=3840):
     """Tied bf16 output head of one decode step: 262,144 x 3,840 bf16 = 2.0 GB read per launch (far
     beyond L2), fused soft cap + suppression + arg-max; one hidden row (decode) and five (the
     reference's speculative-decoding verifier)."""
@@ -612,7 +893,7 @@ def bench_output_head(lib, dev, vocab=262144, hidden=3840):
     return out
 
 
-def bench_verifier_gemv(lib, dev, sets=6):
+def bench_verifier_gemv(lib, dev, args=None, sets=6):
     """The decode projection set at the speculative-decoding verifier's batch sizes (3 and 5 tokens):
     small-batch FP8 GEMV, fp32 out, weights streamed once per launch; `sets` distinct weight sets in
     rotation (1.35 GB, far beyond L2)."""
@@ -703,103 +984,105 @@ def bench_tp_mlp(lib, dev, world, rank, tokens=16384):
             "partial_bytes_per_rank": tokens * hidden * 4 if world > 1 else 0}
 
 
-def bench_moe_ep(lib, dev, world, rank, layers=30, phases=((16384, "prefill"), (64, "decode"))):
-    """Expert-parallel MoE stack: `layers` distinct 26B-A4B-like layers, experts split evenly over
-    the ranks, tokens data-sharded; dispatch and combine by the library's pull kernels over peer
-    memory (NCCL all-to-all if no peer mapping can be had).  Collective: every rank calls it;
-    returns the summary on every rank (times are the max over ranks)."""
+def sampled(fn, index=0):
+    """fn() with the SM clock sampled beside it: (result, clocks)."""
+    s = ClockSampler(index).start()
+    r = fn()
+    return r, s.stop()
+
+
+def bench_decode_gemv(lib, dev, args):
+    """The decode GEMV set: 48 layers x four FP8 projections (gate/up, down, QKV, O), bf16 activations
+    quantised per token, 48 distinct weight sets (10.8 GB >> L2), one CUDA graph per pass."""
     import torch
-    import torch.distributed as dist
-    from gem16_b200.ep import EpMoeLayer, EpPullMoeLayer
-    from gem16_b200.moe import MoeLayer, synthetic_weights
-    experts = 128
-    e_local = experts // world
-    rng = (rank * e_local, (rank + 1) * e_local)
-    weights = [synthetic_weights(dev, SEED + 4000 + l, expert_range=rng if world > 1 else None, placement_ranks=world)
-               for l in range(layers)]
-    out = {"metric": "MoE stack tokens/s", "layers": layers, "ranks": world, "experts_per_rank": e_local, "phases": {}}
-    for tokens, name in phases:
-        t_local = tokens // world
-        gen = torch.Generator(device=dev)
-        gen.manual_seed(SEED + 4100)
-        x_all = torch.randn((tokens, 2816), device=dev, generator=gen).to(torch.bfloat16)
-        ga = float(2688.0 / x_all.float().abs().max().item())
-        x = x_all[rank * t_local:(rank + 1) * t_local].contiguous().view(torch.int16)
-        if world > 1:
-            try:
-                shared_bufs = EpPullMoeLayer(weights[0], t_local, 8, ga, 336.0, 336.0)
-                out["exchange"] = "pull kernels over peer memory (" + shared_bufs.send.how + ")"
-            except Exception as exc:
-                shared_bufs = EpMoeLayer(weights[0], t_local, 8, ga, 336.0, 336.0)
-                out["exchange"] = f"NCCL all-to-all ({type(exc).__name__}: {exc})"[:300]
-            def run():
-                for w in weights:
-                    shared_bufs.w = w
-                    shared_bufs.local.w = w
-                    shared_bufs.forward(x)
-        else:
-            buf = MoeLayer(weights[0], tokens, 8, ga, 336.0, 336.0)
-            def run():
-                st = torch.cuda.current_stream()
-                for w in weights:
-                    buf.w = w
-                    buf.forward(x, st)
-        for _ in range(2):
-            run()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        # The launch sequence is fixed (nothing is read back to the host), so the whole stack --
-        # the two NCCL collectives per layer included -- replays as one CUDA graph.  All ranks
-        # agree on whether the capture worked; otherwise the stack runs eagerly.
-        step, mode, graph = run, "eager", None
-        if "NCCL all-to-all" not in out.get("exchange", ""):
-            st = torch.cuda.Stream(device=dev)
-            ok = 1
-            try:
-                with torch.cuda.stream(st):
-                    run()
-                    st.synchronize()
-                    graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(graph, stream=st):
-                        run()
-                    graph.replay()
-                    st.synchronize()
-            except Exception:
-                ok = 0
-            if world > 1:
-                okt = torch.tensor([ok], device=dev)
-                dist.all_reduce(okt, op=dist.ReduceOp.MIN)
-                ok = int(okt.item())
-            if ok:
-                step, mode = graph.replay, "cuda graph"
-        out.setdefault("launch", {})[name] = mode
-        for _ in range(2):
-            step()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
+    layers = args.layers
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(SEED + 1000)
+    weights = []
+    for _ in range(layers):
+        mats = []
+        for _, rows, k in DECODE_SHAPES:
+            w = torch.randn((rows, k), device=dev, dtype=torch.float32, generator=gen) * 0.02
+            wq = torch.empty((rows, k), device=dev, dtype=torch.uint8)
+            wsc = torch.empty((rows,), device=dev, dtype=torch.float32)
+            lib.gemb_fp8_quantize(w, 0, wq, wsc, rows, k, None)
+            mats.append((wq, wsc.to(torch.bfloat16).view(torch.int16)))
+            del w
+        weights.append(mats)
+    x_elems = sum(k for _, _, k in DECODE_SHAPES) * layers
+    y_elems = sum(r for _, r, _ in DECODE_SHAPES) * layers
+    x_host = torch.randn((x_elems,), dtype=torch.float32).to(torch.bfloat16).pin_memory()
+    x_dev = x_host.to(dev)
+    xq_dev = torch.empty((x_elems,), dtype=torch.uint8, device=dev)
+    xs_dev = torch.empty((layers * len(DECODE_SHAPES),), device=dev)
+    y_dev = torch.zeros((y_elems,), device=dev)
+    y_host = torch.empty((y_elems,), dtype=torch.float32).pin_memory()
+
+    def enqueue(st, quantize=True):
+        xo = yo = n = 0
+        for mats in weights:
+            for (wq, ws), (_, rows, k) in zip(mats, DECODE_SHAPES):
+                if quantize:
+                    lib.gemb_fp8_quantize(x_dev[xo:xo + k], 1, xq_dev[xo:xo + k], xs_dev[n:n + 1], 1, k, st)
+                lib.gemb_fp8_gemv(xq_dev[xo:xo + k], xs_dev[n:n + 1], wq, ws, y_dev[yo:yo + rows], rows, k, st)
+                xo += k
+                yo += rows
+                n += 1
+        return n
+
+    st = torch.cuda.Stream(device=dev)
+    launches = 2 * layers * len(DECODE_SHAPES)
+    full = capture(st, lambda: enqueue(st))
+    only = capture(st, lambda: enqueue(st, quantize=False))
+
+    def region(g, reps):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 3
-        s.record()
+        for _ in range(3):
+            g()
+        st.synchronize()
+        s.record(st)
         for _ in range(reps):
-            step()
-        e.record()
-        torch.cuda.synchronize()
-        ms = s.elapsed_time(e) / reps
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        lib.gemb_check_device_status()
-        out["phases"][name] = {"tokens": tokens, "ms_per_stack": ms, "tokens_per_s": tokens / ms * 1e3,
-                               "us_per_layer": ms * 1e3 / layers}
-        del x_all, step, graph
-        if world > 1:
-            del shared_bufs
-        else:
-            del buf
-        torch.cuda.empty_cache()
+            g()
+        e.record(st)
+        st.synchronize()
+        return s.elapsed_time(e) / reps / 1e3
+
+    def step_e2e():
+        x_dev.copy_(x_host, non_blocking=True)
+        full.replay()
+        y_host.copy_(y_dev, non_blocking=True)
+        st.synchronize()
+
+    with torch.cuda.stream(st):
+        reps = max(20, int(0.6 / 2.6e-3))
+        secs, clocks = sampled(lambda: region(full.replay, reps), dev.index or 0)
+        secs_gemv = region(only.replay, reps)
+        secs_e2e = region(step_e2e, 20)
+    lib.gemb_check_device_status()
+    bytes_pass = decode_bytes_per_layer() * layers
+    peaks = measured_peaks()
+    per_launch = bytes_pass / (launches // 2)
+    achieved = bytes_pass / secs_gemv / 1e9
+    prof = profile_traffic("fp8_gemv_kernel_decode.md")
+    out = {"metric": "decode GEMV GB/s", "workload": "decode_gemv: 48 layers x (gate/up 3840->30720, down 15360->3840, QKV 3840->8192, O 4096->3840), FP8 W8A8",
+           "value": bytes_pass / secs / 1e9, "unit": "GB/s", "ms_per_pass": secs * 1e3, "dtype": "fp8_e4m3 (fp32 accumulate)",
+           "timed_region_s": secs * reps, "clocks": clocks, "launches_per_pass": launches,
+           "e2e": {"value": bytes_pass / secs_e2e / 1e9, "unit": "GB/s", "h2d_bytes_per_step": x_elems * 2, "d2h_bytes_per_step": y_elems * 4},
+           "roofline": {"bound": "hbm", "kernel": "fp8_gemv_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "frac_of_nominal_8TBs": achieved / 8000.0,
+                        "avg_launch_us": secs_gemv / (launches // 2) * 1e6, "algorithmic_bytes_per_launch": per_launch,
+                        "traffic": (prof["traffic_bytes_per_launch"] * per_launch / prof["captured_units_per_launch"])
+                        if prof and prof.get("captured_units_per_launch") else None,
+                        "traffic_unit": "dram bytes per launch, scaled from the kept ncu capture by algorithmic bytes",
+                        "whole_pass": {"kernels": "fp8_quantize_decode_kernel + fp8_gemv_kernel", "achieved": bytes_pass / secs / 1e9,
+                                       "frac": bytes_pass / secs / 1e9 / peaks["hbm_gbs"]}},
+           "l2": f"{layers} distinct weight sets, {bytes_pass / 1e9:.2f} GB per pass >> 126 MB L2", "multi_gpu": "replicas only"}
+    if not args.no_cpu_baseline:
+        gbs, dt, cores, kind = cpu_decode_sample(1, 0, use_ref=True)
+        out["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
+                               "sample": f"one decode layer of 48 (224 MB), {dt:.2f} s on {cores} host threads"}
+    del weights, full, only
+    torch.cuda.empty_cache()
     return out
 
 
@@ -809,14 +1092,17 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_gemv", choices=["decode_gemv"])
-    ap.add_argument("--decode-path", default="split", choices=["fused", "split"],
-                    help="decode GEMV set: activation quantisation fused into the GEMV, or quantizer + GEMV launches")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-workloads", action="store_true")
+    ap.add_argument("--no-stage-times", action="store_true")
+    ap.add_argument("--unfused", dest="fused", action="store_false",
+                    help="gate/up GEMM, GELU requantisation as separate launches instead of the fused epilogue")
+    ap.add_argument("--moe-layers", type=int, default=MOE_LAYERS,
+                    help="MoE layers held on the device (30 = the benchmark; fewer for a small profiler capture)")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="decode layers held on the device (48 = the benchmark; fewer for a small profiler capture)")
-    ap.add_argument("--only", default=None, choices=["nvfp4_linear", "moe_layer", "prefill_gemm", "prefill_stack", "output_head", "verifier_gemv"],
+    ap.add_argument("--only", default=None, choices=["decode_gemv", "nvfp4_linear", "moe_layer", "prefill_gemm", "prefill_stack",
+                                                     "output_head", "verifier_gemv"],
                     help="run just one secondary workload on one GPU and print its JSON (profiling aid)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -827,12 +1113,12 @@ def main():
         from gem16_b200 import load
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(dev)
-        fn = {"nvfp4_linear": bench_nvfp4_linear, "moe_layer": bench_moe_layer, "prefill_gemm": bench_prefill_gemm,
-              "prefill_stack": bench_prefill_stack, "output_head": bench_output_head,
+        fn = {"decode_gemv": bench_decode_gemv, "nvfp4_linear": bench_nvfp4_linear, "moe_layer": bench_moe_layer,
+              "prefill_gemm": bench_prefill_gemm, "prefill_stack": bench_prefill_stack, "output_head": bench_output_head,
               "verifier_gemv": bench_verifier_gemv}[args.only]
-        print(json.dumps(fn(load(), dev)), flush=True)
+        print(json.dumps(fn(load(), dev, args)), flush=True)
         return
-    run_decode_gemv(args)
+    moe_headline(args)
 
 
 if __name__ == "__main__":

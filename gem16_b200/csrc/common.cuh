@@ -26,6 +26,7 @@ int sm_count();
 // Tuning knobs owned by the GEMM translation unit (see gemb_set_tuning).
 int32_t gemm_set_tuning(int32_t knob, int32_t value);
 int32_t ep_set_tuning(int32_t knob, int32_t value);
+int32_t moe_set_tuning(int32_t knob, int32_t value);
 // Decode-size FP8 token quantizer (bf16 input, K <= 16384, K % 8 == 0); bit-identical to the
 // general kernel, one global round trip, programmatic-dependent-launch aware.
 int32_t launch_fp8_quantize_decode(const char* op, const uint16_t* x, uint8_t* out, float* scales, uint64_t tokens,

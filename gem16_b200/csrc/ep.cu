@@ -55,7 +55,7 @@ int32_t ep_set_tuning(int32_t knob, int32_t value) {
     g_ep_barrier_spins = value == 0 ? 1 << 22 : value;
     return GEMB_OK;
   }
-  return fail(GEMB_INVALID_ARGUMENT, "gemb_set_tuning: unknown knob %d", knob);
+  return moe_set_tuning(knob, value);
 }
 
 namespace {
@@ -743,7 +743,8 @@ int32_t ep_stage_send(const char* op, const gemb_moe_layer_weights* w, const gem
                       const uint16_t* x, uint64_t tokens, gemb_stream_t stream) {
   const EpBuffers& b = call.b;
   int32_t* my_counts = reinterpret_cast<int32_t*>(const_cast<uint8_t*>(call.counts.p[comm->rank]));
-  GEMB_TRY(moe_route_stage(w, x, tokens, b.c, my_counts, stream));
+  if (moe_stage_on(kStageRoute)) GEMB_TRY(moe_route_stage(w, x, tokens, b.c, my_counts, stream));
+  if (!moe_stage_on(kStagePack)) return GEMB_OK;
   const uint32_t h = static_cast<uint32_t>(w->hidden);
   const unsigned threads = static_cast<unsigned>(std::min<uint64_t>(256, (h / 16 + 31) / 32 * 32));
   ep_pack_kernel<<<static_cast<unsigned>(tokens), threads, h / 16, stream>>>(
@@ -759,6 +760,7 @@ int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const 
   const uint32_t ranks = static_cast<uint32_t>(comm->ranks), me = static_cast<uint32_t>(comm->rank);
   const uint32_t e = static_cast<uint32_t>(w->experts), el = static_cast<uint32_t>(b.el);
   const uint64_t h = w->hidden, i = w->intermediate, n = tokens * w->topk;
+  if (moe_stage_on(kStageExchange)) {
   ep_sync_plan_kernel<<<1, 256, 4 * e * sizeof(int), stream>>>(
       call.flags, call.counts, ranks, e, me, comm->local_epochs, static_cast<uint32_t>(g_ep_barrier_spins), barriers ? 1 : 0,
       barriers ? 1 : 0, b.counts_all, b.plan, b.recv_prefix, b.recv_src, b.recv_dst, b.row_base,
@@ -771,17 +773,22 @@ int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const 
       static_cast<uint32_t>(call.msg_bytes), c_pad, b.a_packed, b.a_scales, static_cast<uint32_t>(n),
       static_cast<uint32_t>(b.rows_max), reinterpret_cast<int2*>(b.row_meta));
   GEMB_TRY(check_launch(op));
+  }
   const gemb_nvfp4_binding& gu = w->gate_up;
   const gemb_nvfp4_binding& dn = w->down;
   if (w->gate_up_fused != nullptr) {
+    if (moe_stage_on(kStageGateUp))
     GEMB_TRY(gemb_moe_grouped_gemm_gated_quant(b.a_packed, b.a_scales, w->gate_up_fused, w->gate_up_fused_scales, b.p_packed,
                                                b.p_scales, b.plan, b.rows_max, el, i, h, gu.input_divisor,
                                                gu.weight_divisors_device, dn.input_divisor, stream));
   } else {
+    if (moe_stage_on(kStageGateUp))
     GEMB_TRY(gemb_moe_grouped_gemm_bf16(b.a_packed, b.a_scales, gu.packed_weight, gu.scales_interleaved, b.gate_up, b.plan,
                                         b.rows_max, el, 2 * i, h, gu.input_divisor, gu.weight_divisors_device, stream));
+    if (moe_stage_on(kStageGelu))
     GEMB_TRY(gemb_moe_expert_gelu_quantize(b.gate_up, b.plan, b.p_packed, b.p_scales, b.rows_max, i, dn.input_divisor, stream));
   }
+  if (!moe_stage_on(kStageDown)) return GEMB_OK;
   return grouped_gemm_push(op, b.p_packed, b.p_scales, dn.packed_weight, dn.scales_interleaved, b.plan, b.rows_max, el, h, i,
                            dn.input_divisor, dn.weight_divisors_device, b.row_meta, b.tile_rows, comm->recv_buffers_host,
                            comm->ranks, comm->rank, n, stream);
@@ -789,11 +796,12 @@ int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const 
 
 int32_t ep_stage_combine(const char* op, const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const EpCall& call,
                          uint16_t* out, uint64_t tokens, bool barriers, gemb_stream_t stream) {
-  if (barriers) {
+  if (barriers && moe_stage_on(kStageExchange)) {
     ep_barrier_kernel<<<1, 32, 0, stream>>>(call.flags, static_cast<uint32_t>(comm->ranks), static_cast<uint32_t>(comm->rank), 1,
                                             comm->local_epochs, static_cast<uint32_t>(g_ep_barrier_spins));
     GEMB_TRY(check_launch(op));
   }
+  if (!moe_stage_on(kStageCombine)) return GEMB_OK;
   const uint16_t* rows = reinterpret_cast<const uint16_t*>(call.recv.p[comm->rank]);
   return gemb_moe_combine(rows, nullptr, call.b.c.weights, w->shared_intermediate ? call.b.c.s_out : nullptr, out, tokens,
                           w->hidden, w->topk, stream);
@@ -852,7 +860,7 @@ int32_t gemb_moe_ep_layer_forward(const gemb_moe_layer_weights* w, const gemb_mo
   const bool shared = w->shared_intermediate != 0;
   const bool forked = shared && side_stream != nullptr && fork_event != nullptr && join_event != nullptr;
   if (forked) GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));
-  if (shared) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, forked ? side_stream : stream));
+  if (shared && moe_stage_on(kStageShared)) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, forked ? side_stream : stream));
   GEMB_TRY(ep_stage_send(op, w, comm, call, x, tokens, stream));
   GEMB_TRY(ep_stage_experts(op, w, comm, call, tokens, true, stream));
   if (forked) GEMB_TRY(stream_join(op, stream, side_stream, join_event));

@@ -56,6 +56,18 @@ uint64_t align256(uint64_t v) { return (v + 255) / 256 * 256; }
 
 }  // namespace
 
+int g_moe_stage_mask = 0;   // 0 = every stage
+bool moe_stage_on(int bit) { return g_moe_stage_mask == 0 || (g_moe_stage_mask & bit) != 0; }
+
+int32_t moe_set_tuning(int32_t knob, int32_t value) {
+  if (knob == GEMB_TUNE_MOE_STAGE_MASK) {
+    GEMB_REQUIRE(value >= 0 && value < 256, "gemb_set_tuning: the stage mask has eight bits");
+    g_moe_stage_mask = value;
+    return GEMB_OK;
+  }
+  return fail(GEMB_INVALID_ARGUMENT, "gemb_set_tuning: unknown knob %d", knob);
+}
+
 int32_t validate_moe_weights(const char* op, const gemb_moe_layer_weights* w, uint64_t tokens, uint64_t local_experts) {
   GEMB_REQUIRE(w != nullptr, "%s: weights must be nonnull", op);
   GEMB_REQUIRE(tokens > 0 && tokens * w->topk < (1ull << 31), "%s: token count must be nonzero and fit 31 bits", op);
@@ -281,24 +293,30 @@ int32_t gemb_moe_layer_forward(const gemb_moe_layer_weights* w, const uint16_t* 
   // The shared dense branch depends only on x: beside routing and the expert GEMMs when the caller
   // gave a second stream, first otherwise.
   if (forked) GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));
-  if (shared) GEMB_TRY(moe_shared_stage(w, x, tokens, b.c, forked ? side_stream : stream));
-  GEMB_TRY(moe_route_stage(w, x, tokens, b.c, nullptr, stream));
+  if (shared && moe_stage_on(kStageShared)) GEMB_TRY(moe_shared_stage(w, x, tokens, b.c, forked ? side_stream : stream));
+  if (moe_stage_on(kStageRoute)) GEMB_TRY(moe_route_stage(w, x, tokens, b.c, nullptr, stream));
   const gemb_nvfp4_binding& gu = w->gate_up;
   const gemb_nvfp4_binding& dn = w->down;
   const uint64_t h = w->hidden, i = w->intermediate, e = w->experts;
-  GEMB_TRY(gemb_moe_dispatch_quantize(x, b.c.slot_rows, b.a_packed, b.a_scales, tokens, h, w->topk, gu.input_divisor, stream));
+  if (moe_stage_on(kStagePack))
+    GEMB_TRY(gemb_moe_dispatch_quantize(x, b.c.slot_rows, b.a_packed, b.a_scales, tokens, h, w->topk, gu.input_divisor, stream));
   if (w->gate_up_fused != nullptr) {
+    if (moe_stage_on(kStageGateUp))
     GEMB_TRY(gemb_moe_grouped_gemm_gated_quant(b.a_packed, b.a_scales, w->gate_up_fused, w->gate_up_fused_scales, b.p_packed,
                                                b.p_scales, b.c.plan, b.rows_max, e, i, h, gu.input_divisor,
                                                gu.weight_divisors_device, dn.input_divisor, stream));
   } else {
+    if (moe_stage_on(kStageGateUp))
     GEMB_TRY(gemb_moe_grouped_gemm_bf16(b.a_packed, b.a_scales, gu.packed_weight, gu.scales_interleaved, b.gate_up, b.c.plan,
                                         b.rows_max, e, 2 * i, h, gu.input_divisor, gu.weight_divisors_device, stream));
+    if (moe_stage_on(kStageGelu))
     GEMB_TRY(gemb_moe_expert_gelu_quantize(b.gate_up, b.c.plan, b.p_packed, b.p_scales, b.rows_max, i, dn.input_divisor, stream));
   }
+  if (moe_stage_on(kStageDown))
   GEMB_TRY(gemb_moe_grouped_gemm_bf16(b.p_packed, b.p_scales, dn.packed_weight, dn.scales_interleaved, b.y, b.c.plan,
                                       b.rows_max, e, h, i, dn.input_divisor, dn.weight_divisors_device, stream));
   if (forked) GEMB_TRY(stream_join(op, stream, side_stream, join_event));
+  if (!moe_stage_on(kStageCombine)) return GEMB_OK;
   return gemb_moe_combine(b.y, b.c.slot_rows, b.c.weights, shared ? b.c.s_out : nullptr, out, tokens, h, w->topk, stream);
 }
 

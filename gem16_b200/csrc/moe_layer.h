@@ -45,6 +45,10 @@ int32_t grouped_gemm_push(const char* op, const uint8_t* act, const uint8_t* act
                           uint64_t experts, uint64_t rows_per_expert, uint64_t k, float ga, const float* w_divisors,
                           const int32_t* meta, const int32_t* tile_rows, const uint64_t* dst_host, uint64_t ranks,
                           uint64_t rank, uint64_t dst_rows, gemb_stream_t stream);
+// Stage selection of the layer calls (gemb_set_tuning(GEMB_TUNE_MOE_STAGE_MASK, ...)).
+enum : int { kStageRoute = 1, kStagePack = 2, kStageGateUp = 4, kStageGelu = 8, kStageDown = 16, kStageCombine = 32,
+             kStageShared = 64, kStageExchange = 128 };
+bool moe_stage_on(int bit);
 // Fork: side_stream waits for what `stream` holds so far.  Join: `stream` waits for side_stream.
 int32_t stream_fork(const char* op, gemb_stream_t stream, gemb_stream_t side_stream, void* event);
 int32_t stream_join(const char* op, gemb_stream_t stream, gemb_stream_t side_stream, void* event);

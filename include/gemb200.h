@@ -83,14 +83,20 @@ int32_t gemb_device_check(void);
  * each stages half of the weight tile), 0 (automatic), 1 (never) or 2 (always, when the tile is 256 wide);
  * GEMB_TUNE_EP_BARRIER_SPINS = how many times gemb_moe_ep_barrier polls its flags before it gives
  * up and records the fact (about 500 ns per poll; 0 = the default of 2^22, about three seconds) --
- * a deployment's failure-detection latency, and what lets a test see the give-up path quickly. */
+ * a deployment's failure-detection latency, and what lets a test see the give-up path quickly;
+ * GEMB_TUNE_MOE_STAGE_MASK = which stages the two layer calls launch (bit 0 router + permutation, 1
+ * dispatch / pack, 2 grouped gate/up GEMM, 3 separate GELU requantisation, 4 grouped down GEMM, 5
+ * combine, 6 shared branch, 7 flag barriers + position arithmetic + pull; 0 = all): with a subset
+ * the call re-runs just those launches on what the previous full call left in the workspace, so a
+ * benchmark can time one kernel of the sequence in place.  Results of a partial call are not a layer. */
 enum {
   GEMB_TUNE_GEMV_ROWS = 1,
   GEMB_TUNE_GEMV_PDL = 2,
   GEMB_TUNE_GEMM_BN = 3,
   GEMB_TUNE_GEMV_IMPL = 4,
   GEMB_TUNE_GEMM_PAIR = 5,
-  GEMB_TUNE_EP_BARRIER_SPINS = 6
+  GEMB_TUNE_EP_BARRIER_SPINS = 6,
+  GEMB_TUNE_MOE_STAGE_MASK = 7
 };
 int32_t gemb_set_tuning(int32_t knob, int32_t value);
 /* Bytes of an INTERLEAVED scale buffer for `rows` rows of K elements. */
