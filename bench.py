@@ -39,6 +39,16 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# Exactly one line goes to stdout, the result.  Libraries that print to file descriptor 1 (NCCL's
+# version banner, for one) are sent to stderr instead: descriptor 1 is pointed at descriptor 2 and
+# the result is written to a saved copy of the original.
+_RESULT_FD = os.dup(1)
+os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    os.write(_RESULT_FD, (json.dumps(line) + "\n").encode())
+
 DECODE_SHAPES = [("gate_up", 30720, 3840), ("down", 3840, 15360), ("qkv", 8192, 3840), ("o", 3840, 4096)]
 LAYERS = 48            # decode GEMV set
 MOE_LAYERS = 30
@@ -274,7 +284,7 @@ def run_reference_arm(args):
                                  "CPU restatement of gem16's MoE specifications (gem16 has no MoE code)"},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def moe_config(world: int) -> dict:
@@ -577,7 +587,7 @@ def moe_headline(args):
         line["cpu_baseline"] = {"value": 64 / (dt * layers), "unit": "tokens/s", "cores": cores, "kind": kind,
                                 "sample": f"64 tokens through one of the {layers} layers: {dt:.2f} s on {cores} host threads; "
                                           f"stack rate extrapolated as sample rate / {layers}"}
-    print(json.dumps(line), flush=True)
+    emit(line)
     d.close()
 
 
@@ -1116,7 +1126,7 @@ def main():
         fn = {"decode_gemv": bench_decode_gemv, "nvfp4_linear": bench_nvfp4_linear, "moe_layer": bench_moe_layer,
               "prefill_gemm": bench_prefill_gemm, "prefill_stack": bench_prefill_stack, "output_head": bench_output_head,
               "verifier_gemv": bench_verifier_gemv}[args.only]
-        print(json.dumps(fn(load(), dev, args)), flush=True)
+        emit(fn(load(), dev, args))
         return
     moe_headline(args)
 

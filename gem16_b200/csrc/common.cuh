@@ -148,8 +148,21 @@ __device__ __forceinline__ void quantize_block16(const float (&v)[16], float g, 
   } else {
     scale_bits = e4m3_encode(__fmul_rn(__fmul_rn(amax, kInvSix), g));
     const float ds = e4m3_decode(scale_bits);
+    // (x * g) / ds, correctly rounded, with ONE division per block: r = RN(1 / ds), then per element
+    // q0 = RN(t * r), e = t - ds * q0 (exact in one fma), q = RN(q0 + e * r).  With a correctly rounded
+    // reciprocal this residual correction yields the correctly rounded quotient (Markstein); for the
+    // 126 values an E4M3 scale can take it is also checked exhaustively around every E2M1 rounding
+    // boundary in tests/test_oracle.py.  Sixteen IEEE divisions per block kept the conversion pipe of
+    // the fused GEMM epilogue busier than the tensor pipe.
+    const float r = ds == 0.0f ? 0.0f : __fdiv_rn(1.0f, ds);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) n[i] = ds == 0.0f ? 0.0f : __fdiv_rn(__fmul_rn(v[i], g), ds);
+    for (int i = 0; i < 16; ++i) {
+      const float t = __fmul_rn(v[i], g);
+      const float q0 = __fmul_rn(t, r);
+      // (the quotient has the sign of t, also when it is zero: -0 keeps its sign bit in E2M1, and the
+      // residual correction alone would turn -0 into +0)
+      n[i] = ds == 0.0f ? 0.0f : copysignf(__fmaf_rn(__fmaf_rn(-ds, q0, t), r, q0), t);
+    }
   }
   lo = hi = 0;
 #pragma unroll

@@ -96,7 +96,7 @@ ep_plan_body(const int32_t* counts_all, uint32_t ranks, uint32_t experts, uint32
     for (uint32_t e = me * el; e < (me + 1) * el; ++e) {
       int64_t t = 0;
       for (uint32_t s = 0; s < ranks; ++s) t += max(counts_all[s * experts + e], 0);
-      po += (t + 127) / 128 * 128;
+      po += (t + 255) / 256 * 256;
     }
     if (po > static_cast<int64_t>(capacity_rows)) bad = 1;
   }
@@ -106,6 +106,7 @@ ep_plan_body(const int32_t* counts_all, uint32_t ranks, uint32_t experts, uint32
       atomicCAS(&g_ep_error, 0, 6);
       plan[0] = 0;
       plan[1] = 0;
+      plan[3 + el + capacity_rows / 128] = 0;
     }
     for (uint32_t e = threadIdx.x; e <= el; e += blockDim.x) plan[2 + e] = 0;
     for (uint32_t g = threadIdx.x; g <= ranks * el; g += blockDim.x) recv_prefix[g] = 0;
@@ -117,6 +118,7 @@ ep_plan_body(const int32_t* counts_all, uint32_t ranks, uint32_t experts, uint32
   int* pad = tot + experts;         // [experts] start of e in its owner's padded row space
   int* before_me = pad + experts;   // [experts] sum_{s' < me} C[s'][e]
   int* my_pad = before_me + experts;  // [experts] start of e in MY local padded space (single-GPU plan of my tokens)
+  int* live_off = my_pad + experts;   // [local experts] first entry of the expert in the list of real tiles
   for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
     int t = 0, b = 0;
     for (uint32_t s = 0; s < ranks; ++s) {
@@ -134,31 +136,41 @@ ep_plan_body(const int32_t* counts_all, uint32_t ranks, uint32_t experts, uint32
     int po = 0;
     for (uint32_t e = d * el; e < (d + 1) * el; ++e) {
       pad[e] = po;
-      po += (tot[e] + 127) / 128 * 128;
+      po += (tot[e] + 255) / 256 * 256;
     }
     if (d == me) {
       plan[0] = po / 128;
       plan[1] = po;
       plan[2 + el] = po;
+      // first entry of every local expert in the list of tiles that hold real rows
+      int lo = 0;
+      for (uint32_t e = d * el; e < (d + 1) * el; ++e) {
+        live_off[e - d * el] = lo;
+        lo += (tot[e] + 127) / 128;
+      }
+      plan[3 + el + capacity_rows / 128] = lo;
     }
   } else if (threadIdx.x == ranks) {
     int po = 0;
     for (uint32_t e = 0; e < experts; ++e) {
       my_pad[e] = po;
-      po += (counts_all[me * experts + e] + 127) / 128 * 128;
+      po += (counts_all[me * experts + e] + 255) / 256 * 256;
     }
   }
   __syncthreads();
   for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x)
     out_base[e] = pad[e] + before_me[e] - my_pad[e];
   int32_t* tile_expert = plan + 2 + el + 1;
+  int32_t* live = plan + 3 + el + capacity_rows / 128 + 1;
   for (uint32_t e = threadIdx.x; e < el; e += blockDim.x) {
     const uint32_t ge = me * el + e;
     plan[2 + e] = pad[ge];
-    const int end = pad[ge] + (tot[ge] + 127) / 128 * 128;
-    for (int tile = pad[ge] / 128; tile < end / 128; ++tile) {
-      tile_expert[tile] = static_cast<int32_t>(e);
-      if (tile_rows != nullptr) tile_rows[tile] = min(128, tot[ge] - (tile * 128 - pad[ge]));
+    const int end = pad[ge] + (tot[ge] + 255) / 256 * 256;
+    for (int tile = pad[ge] / 128, j = 0; tile < end / 128; ++tile, ++j) {
+      const int real = max(0, min(128, tot[ge] - (tile * 128 - pad[ge])));
+      tile_expert[tile] = real > 0 ? static_cast<int32_t>(e) : -1;   // -1: padding only
+      if (real > 0) live[live_off[e] + j] = tile;
+      if (tile_rows != nullptr) tile_rows[tile] = real;
     }
   }
   // Segments (source s, local expert e) in source-major order.
@@ -511,8 +523,10 @@ using namespace gemb;
 extern "C" {
 
 uint64_t gemb_moe_ep_plan_ints(uint64_t capacity_rows, uint64_t local_experts) {
-  // tiles, padded rows, local_experts + 1 padded offsets, one expert id per possible tile
-  return 3 + local_experts + (capacity_rows + 127) / 128 + local_experts;
+  // tiles, padded rows, local_experts + 1 padded offsets, one expert id per possible tile (every
+  // expert's rows are padded to a multiple of 256: at most capacity / 128 + 2 per expert tiles)
+  // the same again for the list of tiles that hold real rows, plus its length
+  return 3 + local_experts + 2 * ((capacity_rows + 127) / 128 + 2 * local_experts) + 1;
 }
 
 int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t experts, uint64_t rank,
@@ -529,7 +543,7 @@ int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t exp
                    send_rows_per_rank > 0 && send_rows_per_rank < (1ull << 31),
                "%s: buffer capacities must be nonzero (padded rows a multiple of 128)", op);
   GEMB_TRY(require_sm100(op));
-  ep_plan_kernel<<<1, 256, 4 * experts * sizeof(int), stream>>>(
+  ep_plan_kernel<<<1, 256, 5 * experts * sizeof(int), stream>>>(
       counts_all, static_cast<uint32_t>(ranks), static_cast<uint32_t>(experts), static_cast<uint32_t>(rank), plan,
       recv_prefix, recv_src_rows, recv_dst_rows, combine_row_base, static_cast<uint32_t>(capacity_rows),
       static_cast<uint32_t>(send_rows_per_rank), nullptr);
@@ -761,7 +775,7 @@ int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const 
   const uint32_t e = static_cast<uint32_t>(w->experts), el = static_cast<uint32_t>(b.el);
   const uint64_t h = w->hidden, i = w->intermediate, n = tokens * w->topk;
   if (moe_stage_on(kStageExchange)) {
-  ep_sync_plan_kernel<<<1, 256, 4 * e * sizeof(int), stream>>>(
+  ep_sync_plan_kernel<<<1, 256, 5 * e * sizeof(int), stream>>>(
       call.flags, call.counts, ranks, e, me, comm->local_epochs, static_cast<uint32_t>(g_ep_barrier_spins), barriers ? 1 : 0,
       barriers ? 1 : 0, b.counts_all, b.plan, b.recv_prefix, b.recv_src, b.recv_dst, b.row_base,
       static_cast<uint32_t>(b.rows_max), static_cast<uint32_t>(n), b.tile_rows);
@@ -776,6 +790,11 @@ int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const 
   }
   const gemb_nvfp4_binding& gu = w->gate_up;
   const gemb_nvfp4_binding& dn = w->down;
+  // with balanced routing this rank's experts receive about as many rows as the rank routes itself
+  struct Hint {
+    explicit Hint(uint64_t rows) { set_grouped_rows_hint(rows); }
+    ~Hint() { set_grouped_rows_hint(0); }
+  } hint(n);
   if (w->gate_up_fused != nullptr) {
     if (moe_stage_on(kStageGateUp))
     GEMB_TRY(gemb_moe_grouped_gemm_gated_quant(b.a_packed, b.a_scales, w->gate_up_fused, w->gate_up_fused_scales, b.p_packed,

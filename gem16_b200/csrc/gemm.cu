@@ -185,7 +185,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
   // A device-side plan is clamped to the buffers' capacity (p.m rows): whatever it holds, no tile
   // beyond the activation, scale and output buffers is touched.
-  const uint32_t m_tiles = p.plan ? min(static_cast<uint32_t>(__ldg(p.plan)), p.m / BM) : (p.m + BM - 1) / BM;
+  // Grouped mode: experts are padded to 256 rows, so a 128-row tile may hold padding only.  A single
+  // CTA walks the plan's list of tiles that hold real rows; a pair walks all 256-row units (the even
+  // tile of a unit is always real) and takes the expert from the even tile.
+  const int32_t* live_tiles = (p.plan && !kPair) ? p.plan + 3 + p.experts + p.m / BM + 1 : nullptr;
+  const uint32_t m_tiles = p.plan ? min(static_cast<uint32_t>(__ldg(kPair ? p.plan : p.plan + 3 + p.experts + p.m / BM)), p.m / BM)
+                                  : (p.m + BM - 1) / BM;
   const uint32_t n_tiles = (p.n + BN - 1) / BN;
   const int32_t* tile_expert = p.plan ? p.plan + 3 + p.experts : nullptr;
   // A work unit is one 128-row token tile, or for pairs two consecutive ones (rank picks which).
@@ -196,6 +201,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t my_tiles = first_tile < num_tiles ? (num_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
   const uint32_t k_stages = (p.k + C::kKPerStage - 1) / C::kKPerStage;
   const uint32_t k_groups_pad = (p.k / 16 + 3) / 4;  // 512-byte scale chunks per 128-row group
+  auto tile_expert_of = [&](uint32_t mt) -> int32_t {
+    return __ldg(tile_expert + (kPair ? (mt & ~1u) : mt));
+  };
 
   // Tile order: groups of 16 token tiles; inside a group the token tile runs fastest, so the
   // CTAs of a wave share a few weight tiles and the group's activations stay in L2 while every
@@ -208,6 +216,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const uint32_t within = tile % per_group;
     mt = first_m + within % gm;
     if constexpr (kPair) mt = mt * 2 + rank;
+    else if (live_tiles != nullptr) mt = min(static_cast<uint32_t>(__ldg(live_tiles + mt)), p.m / BM - 1);
     nt = within / gm;
   };
   // Completion of the MMAs issued so far, signalled to the same barrier of both CTAs of a pair.
@@ -253,7 +262,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       for (uint32_t tile = first_tile; tile < num_tiles && !*abort_flag; tile += tile_stride) {
         uint32_t mt, nt;
         tile_coords(tile, mt, nt);
-        const uint32_t expert = tile_expert ? min(static_cast<uint32_t>(__ldg(tile_expert + mt)), p.experts - 1) : 0u;
+        const uint32_t expert = tile_expert ? min(static_cast<uint32_t>(tile_expert_of(mt)), p.experts - 1) : 0u;
         for (uint32_t ks = 0; ks < k_stages; ++ks) {
           if (!ptx::mbar_wait(&empty[stage], phase ^ 1)) { fail_wait(1); break; }
           const uint32_t k0 = ks * C::kKPerStage;
@@ -269,7 +278,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             // The odd CTA of a pair may sit past the last token tile: its rows are never stored,
             // it just reads the last tile's scales again.
             ptx::bulk_load_1d(stage_sfa + stage * C::kSfaBytes,
-                              p.sfa + (static_cast<uint64_t>(min(mt, m_tiles - 1)) * k_groups_pad + ks * 4) * 512,
+                              p.sfa + (static_cast<uint64_t>(min(mt, (p.plan ? p.m / BM : m_tiles) - 1)) * k_groups_pad + ks * 4) * 512,
                               n_mma * 512, &full[stage]);
             for (uint32_t g = 0; g < n_groups; ++g)
               ptx::bulk_load_1d(stage_sfb + stage * C::kSfbBytes + g * 2048,
@@ -465,6 +474,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     for (uint32_t tile = first_tile; tile < num_tiles && !*abort_flag; tile += tile_stride) {
       uint32_t mt, nt;
       tile_coords(tile, mt, nt);
+      // In a pair the odd CTA may own a padding-only tile: it takes part in the barriers, nothing else.
+      const bool dead = kPair && tile_expert != nullptr && (mt >= p.m / BM || __ldg(tile_expert + mt) < 0);
       // The staging buffer must be free again (the previous tile's last store has read it); checked
       // here, while the tile is still being computed, rather than after the accumulator is full.
       if (lane == 0) ptx::bulk_wait_group_read<0>();
@@ -475,7 +486,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       float row_scale = p.alpha;
       if constexpr (!kFp4) row_scale = row0 + lane < p.m ? __ldg(p.a_scales + row0 + lane) : 0.0f;
       if (kFp4 && p.w_divisors != nullptr)
-        row_scale = __fdiv_rn(1.0f, __fmul_rn(p.ga, __ldg(p.w_divisors + (tile_expert ? min(static_cast<uint32_t>(__ldg(tile_expert + mt)), p.experts - 1) : 0u))));
+        row_scale = __fdiv_rn(1.0f, __fmul_rn(p.ga, __ldg(p.w_divisors + (tile_expert ? min(static_cast<uint32_t>(tile_expert_of(mt)), p.experts - 1) : 0u))));
       const uint32_t tmem_acc = tmem_base + as * BN + ((quarter * 32) << 16);
       bool released = false, pending = false;
       uint32_t pending_col = 0;
@@ -484,7 +495,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       // Pushing epilogue: where this lane's row goes, and how many of the warp's 32 rows are real.
       int2 push_to = make_int2(-1, 0);
       uint32_t push_valid = 0;
-      if (kFp4 && p.push_meta != nullptr) {
+      if (kFp4 && p.push_meta != nullptr && !dead) {
         const uint32_t tile_rows = min(static_cast<uint32_t>(__ldg(p.push_tile_rows + mt)), static_cast<uint32_t>(BM));
         push_valid = tile_rows > quarter * 32 ? min(32u, tile_rows - quarter * 32) : 0u;
         if (static_cast<uint32_t>(lane) < push_valid) {
@@ -534,10 +545,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         pending = false;
       };
+      // Gated epilogue, second half: packed[i] = {bf16 gate, bf16 up} of feature f0 + i -> GELU, product,
+      // NVFP4 quantisation (two 16-blocks), 16 payload bytes and two scale bytes per row.
+      auto emit_gated = [&](uint32_t col) {
+        const uint32_t f0 = col / 2, inter = p.n / 2;
+        uint32_t words[4];
+        uint8_t sb[2];
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          float prod[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)   // bf16 boundaries of src/cuda/nvfp4/reference.cu:177-190
+            prod[i] = gelu_tanh_product(__uint_as_float(packed[b * 16 + i] << 16), __uint_as_float(packed[b * 16 + i] & 0xFFFF0000u));
+          quantize_block16<false>(prod, p.g_product, words[2 * b], words[2 * b + 1], sb[b]);
+        }
+        const uint32_t row = row0 + lane;
+        if (row < p.m) {
+          *reinterpret_cast<uint4*>(p.out_packed + static_cast<uint64_t>(row) * (inter / 2) + f0 / 2) =
+              make_uint4(words[0], words[1], words[2], words[3]);
+          const uint32_t c_pad = (inter / 16 + 3) / 4 * 4;
+          *reinterpret_cast<uint16_t*>(p.out_scales + interleaved_scale_offset(row, f0 / 16, c_pad)) =
+              static_cast<uint16_t>(sb[0]) | (static_cast<uint16_t>(sb[1]) << 8);
+        }
+        pending = false;
+      };
 #pragma unroll 1
       for (uint32_t c = set; c < BN / 64; c += 2) {
         const uint32_t col0 = nt * BN + c * 64;
-        if (col0 >= p.n || row0 >= p.m) break;  // warp-uniform
+        if (col0 >= p.n || row0 >= p.m || dead) break;  // warp-uniform
         uint32_t v0[32], v1[32];
         ptx::tc_ld_32x32b_x32(tmem_acc + c * 64, v0);
         ptx::tc_ld_32x32b_x32(tmem_acc + c * 64 + 32, v1);
@@ -548,31 +583,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         if (kFp4 && p.gated) {
           // v0 = 32 gate values, v1 = 32 up values of features f0 .. f0+31 for this thread's token.
+          // Like the plain path, nothing slow sits between "accumulator full" and its release: a
+          // sub-tile is only scaled and rounded to bf16 pairs (the first step of the boundary
+          // arithmetic anyway) and kept in `packed`; the GELU, the product and the quantiser run
+          // after the warp's last sub-tile is in registers and the accumulator has been released.
           ptx::tc_wait_ld();
-          const uint32_t f0 = col0 / 2, inter = p.n / 2;
-          float alpha_g = row_scale, alpha_u = p.w_divisors != nullptr ? row_scale : p.alpha_up;
-          uint32_t words[4];
-          uint8_t sb[2];
-#pragma unroll
-          for (int b = 0; b < 2; ++b) {
-            float prod[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              // bf16 projection boundaries, bf16 GELU, bf16 product: src/cuda/nvfp4/reference.cu:177-190
-              const float gv = bf16_round(__fmul_rn(__uint_as_float(v0[b * 16 + i]), alpha_g));
-              const float uv = bf16_round(__fmul_rn(__uint_as_float(v1[b * 16 + i]), alpha_u));
-              prod[i] = gelu_tanh_product(gv, uv);
-            }
-            quantize_block16<false>(prod, p.g_product, words[2 * b], words[2 * b + 1], sb[b]);
+          if (c + 2 >= BN / 64 || col0 + 128 >= p.n) {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) arrive_issuer(&acc_empty[as]);
+            released = true;
           }
-          const uint32_t row = row0 + lane;
-          if (row < p.m) {
-            *reinterpret_cast<uint4*>(p.out_packed + static_cast<uint64_t>(row) * (inter / 2) + f0 / 2) =
-                make_uint4(words[0], words[1], words[2], words[3]);
-            const uint32_t c_pad = (inter / 16 + 3) / 4 * 4;
-            *reinterpret_cast<uint16_t*>(p.out_scales + interleaved_scale_offset(row, f0 / 16, c_pad)) =
-                static_cast<uint16_t>(sb[0]) | (static_cast<uint16_t>(sb[1]) << 8);
-          }
+          if (pending) emit_gated(pending_col);
+          const float alpha_g = row_scale, alpha_u = p.w_divisors != nullptr ? row_scale : p.alpha_up;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            packed[i] = pack_bf16x2(__fmul_rn(__uint_as_float(v0[i]), alpha_g), __fmul_rn(__uint_as_float(v1[i]), alpha_u));
+          pending = true;
+          pending_col = col0;
           continue;
         }
         if (kFp4 && p.out_f32) {
@@ -638,7 +666,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         pending = true;
         pending_col = col0;
       }
-      if (pending) stage_and_store(pending_col);
+      if (pending) {
+        if (kFp4 && p.gated) emit_gated(pending_col);
+        else stage_and_store(pending_col);
+      }
       if (!released) {
         ptx::tc_fence_before();
         __syncwarp();
@@ -740,6 +771,19 @@ int g_gemm_pair = 0;  // 0 = automatic (pairs for the dense 256-wide tile), 1 = 
 
 bool use_pairs() { return g_gemm_pair != 1 && (g_gemm_bn == 0 || g_gemm_bn == 256); }
 
+// Grouped calls run on CTA pairs when the experts are expected to hold a couple of 128-row tiles
+// each (a pair shares one weight tile between two SMs, which is what the grouped GEMM is short of:
+// operand bandwidth out of L2); with a handful of rows per expert a pair would only tie up a
+// second SM per tile.  The expectation is the rows the caller announced (the layer calls know how
+// many assignments they route) or else what the capacity of the padded row space implies.
+thread_local uint64_t g_grouped_rows_hint = 0;
+bool grouped_pairs(uint64_t padded_rows_max, uint64_t experts) {
+  if (!use_pairs()) return false;
+  uint64_t rows = g_grouped_rows_hint;
+  if (rows == 0) rows = padded_rows_max / 128 > 2 * experts ? (padded_rows_max / 128 - 2 * experts) * 128 : 0;
+  return g_gemm_pair == 2 || rows >= 192 * experts;
+}
+
 template <bool kFp4, int BN, int kStages, int kAccStages, bool kPair = false>
 int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmParams& p, cudaStream_t stream) {
   using C = Cfg<kFp4, BN, kStages, kAccStages, kPair>;
@@ -813,6 +857,8 @@ int32_t validate_gemm(const char* op, uint64_t tokens, uint64_t rows, uint64_t k
 }
 
 }  // namespace
+
+void set_grouped_rows_hint(uint64_t rows) { g_grouped_rows_hint = rows; }
 
 int32_t gemm_set_tuning(int32_t knob, int32_t value) {
   if (knob == GEMB_TUNE_GEMM_BN) {
@@ -924,6 +970,7 @@ int32_t gemb_moe_grouped_gemm_bf16(const uint8_t* act, const uint8_t* act_scales
   p.alpha = 1.0f;
   const int bn = g_gemm_bn ? g_gemm_bn : 256;
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
+  if (grouped_pairs(padded_rows_max, experts)) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
   return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
 }
 
@@ -968,6 +1015,7 @@ int32_t grouped_gemm_push(const char* op, const uint8_t* act, const uint8_t* act
   p.m_out = static_cast<uint32_t>(dst_rows);
   const int bn = g_gemm_bn ? g_gemm_bn : 256;
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
+  if (grouped_pairs(padded_rows_max, experts)) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
   return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
 }
 }  // namespace gemb
@@ -1026,7 +1074,7 @@ extern "C" int32_t gemb_nvfp4_pack_gate_up(const uint8_t* gate_packed, const uin
 static int32_t launch_gated(const char* op, const uint8_t* act, const uint8_t* w, GemmParams& p, cudaStream_t stream) {
   const int bn = g_gemm_bn ? g_gemm_bn : 256;
   if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
-  if (!p.plan && use_pairs()) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
+  if (p.plan ? grouped_pairs(p.m, p.experts) : use_pairs()) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
   return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
 }
 

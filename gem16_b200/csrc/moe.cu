@@ -127,11 +127,23 @@ router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w
       const float wv[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
       float xv[kPerThread];
       if constexpr (kPerThread == 8) {
+        // Two tokens per instruction: the packed fp32 fma (one IEEE fma per half, so every chain
+        // keeps its order and rounding) halves the instructions the issue slots have to carry.
         const int col = (ty * 8) ^ (8 * ((k >> 3) & 3));
         const float4 xa = *reinterpret_cast<const float4*>(&xs[k][col]);
         const float4 xb = *reinterpret_cast<const float4*>(&xs[k][col + 4]);
-        xv[0] = xa.x; xv[1] = xa.y; xv[2] = xa.z; xv[3] = xa.w;
-        xv[4] = xb.x; xv[5] = xb.y; xv[6] = xb.z; xv[7] = xb.w;
+        const float2 xp[4] = {make_float2(xa.x, xa.y), make_float2(xa.z, xa.w), make_float2(xb.x, xb.y), make_float2(xb.z, xb.w)};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 wp = make_float2(wv[j], wv[j]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 r = __ffma2_rn(xp[i], wp, make_float2(acc[2 * i][j], acc[2 * i + 1][j]));
+            acc[2 * i][j] = r.x;
+            acc[2 * i + 1][j] = r.y;
+          }
+        }
+        continue;
       } else {
         const int col = (ty * 2) ^ (8 * ((k >> 3) & 3));
         const float2 xa = *reinterpret_cast<const float2*>(&xs[k][col]);
@@ -426,10 +438,13 @@ route_kernel(const float* __restrict__ logits, const float* __restrict__ per_exp
 // slot).  Three launches, no atomics on global memory, no host readback:
 //   1. per segment of 1024 assignments: per-expert counts (block_counts[segment][expert]);
 //   2. one CTA: exclusive scan over segments per expert, counts, offsets, and the padded plan
-//      (every expert's rows start on a multiple of 128 so a GEMM tile never mixes experts);
+//      (every expert's rows start on a multiple of 256, so neither a 128-row GEMM tile nor the
+//      256-row tile of a CTA pair ever mixes experts; a 128-row tile that holds padding only is
+//      marked -1 and costs the GEMM nothing);
 //   3. per segment: stable ranks from warp match masks, scatter perm[] and slot_rows[].
 // ---------------------------------------------------------------------------------------------
 constexpr int kSegment = 1024;  // assignments per CTA: 4 warps x 8 chunks x 32
+constexpr int kRowAlign = 256;  // every expert's padded rows start on a multiple of this
 
 __global__ void __launch_bounds__(128)
 permute_count_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ block_counts,
@@ -452,16 +467,19 @@ permute_count_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ bloc
     block_counts[static_cast<uint64_t>(blockIdx.x) * experts + e] = smem_counts[e];
 }
 
-// plan layout (int32): [0] number of 128-row tiles, [1] padded rows in total,
-// [2 .. 2+E] padded offset of every expert (+ the end), then tile_expert[tile].
+// plan layout (int32), T = the most 128-row tiles the padded row space can hold:
+// [0] number of 128-row tiles, [1] padded rows in total, [2 .. 2+E] padded offset of every expert
+// (+ the end), [3+E .. 3+E+T) tile_expert[tile] (-1: padding only), [3+E+T] number of tiles that hold
+// real rows, then their tile indices in ascending order (what a single-CTA grouped GEMM walks).
 __global__ void __launch_bounds__(256)
 permute_scan_kernel(int32_t* __restrict__ block_counts, int32_t* __restrict__ counts,
                     int32_t* __restrict__ offsets, int32_t* __restrict__ plan, uint32_t segments,
-                    uint32_t experts) {
+                    uint32_t experts, uint32_t max_tiles) {
   extern __shared__ int sm[];
   int* cnt = sm;                 // [experts]
   int* off = sm + experts;       // [experts + 1]
   int* poff = off + experts + 1; // [experts + 1]
+  int* loff = poff + experts + 1; // [experts + 1] first entry of the expert in the list of real tiles
   for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
     int run = 0;
     for (uint32_t b = 0; b < segments; ++b) {
@@ -474,17 +492,20 @@ permute_scan_kernel(int32_t* __restrict__ block_counts, int32_t* __restrict__ co
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int o = 0, po = 0;
+    int o = 0, po = 0, lo = 0;
     for (uint32_t e = 0; e < experts; ++e) {
       off[e] = o;
       poff[e] = po;
+      loff[e] = lo;
       o += cnt[e];
-      po += (cnt[e] + 127) / 128 * 128;
+      po += (cnt[e] + kRowAlign - 1) / kRowAlign * kRowAlign;
+      lo += (cnt[e] + 127) / 128;
     }
     off[experts] = o;
     poff[experts] = po;
     plan[0] = po / 128;
     plan[1] = po;
+    plan[3 + experts + max_tiles] = lo;
   }
   __syncthreads();
   for (uint32_t e = threadIdx.x; e <= experts; e += blockDim.x) {
@@ -492,8 +513,13 @@ permute_scan_kernel(int32_t* __restrict__ block_counts, int32_t* __restrict__ co
     plan[2 + e] = poff[e];
   }
   int32_t* tile_expert = plan + 2 + experts + 1;
+  int32_t* live = plan + 3 + experts + max_tiles + 1;
   for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x)
-    for (int tile = poff[e] / 128; tile < poff[e + 1] / 128; ++tile) tile_expert[tile] = static_cast<int32_t>(e);
+    for (int tile = poff[e] / 128, j = 0; tile < poff[e + 1] / 128; ++tile, ++j) {
+      const bool real = tile * 128 - poff[e] < cnt[e];
+      tile_expert[tile] = real ? static_cast<int32_t>(e) : -1;
+      if (real) live[loff[e] + j] = tile;
+    }
 }
 
 __global__ void __launch_bounds__(128)
@@ -703,7 +729,8 @@ using namespace gemb;
 
 namespace {
 uint64_t moe_segments(uint64_t tokens, uint64_t topk) { return (tokens * topk + kSegment - 1) / kSegment; }
-uint64_t moe_max_tiles(uint64_t tokens, uint64_t experts, uint64_t topk) { return tokens * topk / 128 + experts; }
+// sum over experts of ceil(c_e / 256) * 2 tiles of 128 rows <= assignments / 128 + 2 * experts
+uint64_t moe_max_tiles(uint64_t tokens, uint64_t experts, uint64_t topk) { return tokens * topk / 128 + 2 * experts; }
 
 // The permutation itself has no warp-shape constraint on the expert count (the expert-parallel
 // receiver sorts by a handful of local experts).
@@ -808,7 +835,7 @@ uint64_t gemb_moe_permute_workspace_bytes(uint64_t tokens, uint64_t experts, uin
   return moe_segments(tokens, topk) * experts * sizeof(int32_t);
 }
 uint64_t gemb_moe_plan_ints(uint64_t tokens, uint64_t experts, uint64_t topk) {
-  return 2 + experts + 1 + moe_max_tiles(tokens, experts, topk);
+  return 2 + experts + 1 + 2 * moe_max_tiles(tokens, experts, topk) + 1;
 }
 uint64_t gemb_moe_padded_rows_max(uint64_t tokens, uint64_t experts, uint64_t topk) {
   return moe_max_tiles(tokens, experts, topk) * 128;
@@ -829,7 +856,8 @@ int32_t gemb_moe_permute(const int32_t* top_ids, int32_t* counts, int32_t* offse
   int32_t* block_counts = static_cast<int32_t*>(workspace);
   permute_count_kernel<<<segments, 128, e * sizeof(int), stream>>>(top_ids, block_counts, total, e);
   GEMB_TRY(check_launch(op));
-  permute_scan_kernel<<<1, 256, (3 * e + 2) * sizeof(int), stream>>>(block_counts, counts, offsets, plan, segments, e);
+  permute_scan_kernel<<<1, 256, (4 * e + 3) * sizeof(int), stream>>>(block_counts, counts, offsets, plan, segments, e,
+                                                                     static_cast<uint32_t>(moe_max_tiles(tokens, experts, topk)));
   GEMB_TRY(check_launch(op));
   permute_scatter_kernel<<<segments, 128, 4 * e * sizeof(int), stream>>>(top_ids, block_counts, offsets, plan, perm,
                                                                         slot_rows, total, e);
@@ -898,7 +926,8 @@ int32_t gemb_moe_permute_static(const int32_t* top_ids, int32_t* counts, int32_t
   // be cleared even though the array still holds the previous call's values.
   permute_count_kernel<<<segments, 128, e * sizeof(int), stream>>>(top_ids, block_counts, total, e);
   GEMB_TRY(check_launch(op));
-  permute_scan_kernel<<<1, 256, (3 * e + 2) * sizeof(int), stream>>>(block_counts, counts, offsets, plan, segments, e);
+  permute_scan_kernel<<<1, 256, (4 * e + 3) * sizeof(int), stream>>>(block_counts, counts, offsets, plan, segments, e,
+                                                                     static_cast<uint32_t>(moe_max_tiles(tokens, experts, topk)));
   GEMB_TRY(check_launch(op));
   permute_scatter_kernel<<<segments, 128, 4 * e * sizeof(int), stream>>>(top_ids, block_counts, offsets, plan, perm,
                                                                         slot_rows, total, e);

@@ -290,6 +290,10 @@ int32_t gemb_moe_layer_forward(const gemb_moe_layer_weights* w, const uint16_t* 
   GEMB_TRY(require_sm100(op));
   const bool shared = w->shared_intermediate != 0;
   const bool forked = shared && side_stream != nullptr && fork_event != nullptr && join_event != nullptr;
+  struct Hint {
+    explicit Hint(uint64_t rows) { set_grouped_rows_hint(rows); }
+    ~Hint() { set_grouped_rows_hint(0); }
+  } hint(tokens * w->topk);
   // The shared dense branch depends only on x: beside routing and the expert GEMMs when the caller
   // gave a second stream, first otherwise.
   if (forked) GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));

@@ -45,6 +45,9 @@ int32_t grouped_gemm_push(const char* op, const uint8_t* act, const uint8_t* act
                           uint64_t experts, uint64_t rows_per_expert, uint64_t k, float ga, const float* w_divisors,
                           const int32_t* meta, const int32_t* tile_rows, const uint64_t* dst_host, uint64_t ranks,
                           uint64_t rank, uint64_t dst_rows, gemb_stream_t stream);
+// Announces how many rows the calling thread's next grouped GEMMs will really hold (0: unknown),
+// for their choice between single CTAs and CTA pairs (csrc/gemm.cu).
+void set_grouped_rows_hint(uint64_t rows);
 // Stage selection of the layer calls (gemb_set_tuning(GEMB_TUNE_MOE_STAGE_MASK, ...)).
 enum : int { kStageRoute = 1, kStagePack = 2, kStageGateUp = 4, kStageGelu = 8, kStageDown = 16, kStageCombine = 32,
              kStageShared = 64, kStageExchange = 128 };

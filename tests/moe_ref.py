@@ -86,8 +86,8 @@ def ep_plan_reference(counts_all, me):
         po = 0
         for e in range(d * el, (d + 1) * el):
             pad[e] = po
-            po += (tot[e] + 127) // 128 * 128
-    my_pad = np.concatenate([[0], np.cumsum((counts_all[me] + 127) // 128 * 128)])[:-1]
+            po += (tot[e] + 255) // 256 * 256
+    my_pad = np.concatenate([[0], np.cumsum((counts_all[me] + 255) // 256 * 256)])[:-1]
     before_me = counts_all[:me].sum(0)
     row_base = pad + before_me - my_pad
     prefix, src, dst = [0], [], []
@@ -98,6 +98,6 @@ def ep_plan_reference(counts_all, me):
             dst.append(pad[e] + counts_all[:s, e].sum())
             prefix.append(prefix[-1] + counts_all[s, e])
     mine = slice(me * el, (me + 1) * el)
-    padded_rows = int(((tot[mine] + 127) // 128 * 128).sum())
+    padded_rows = int(((tot[mine] + 255) // 256 * 256).sum())
     return dict(row_base=row_base, prefix=np.array(prefix), src=np.array(src), dst=np.array(dst),
                 pad_local=pad[mine], padded_rows=padded_rows)

@@ -64,7 +64,7 @@ def test_peer_protocol_positions_reproduce_the_single_gpu_order():
                 k = pos_in_expert.get(e, 0)
                 want_row[(r, a)] = int(plan["pad_local"][e - me * el]) + k
                 pos_in_expert[e] = k + 1
-            assert all(v % 128 == 0 for v in plan["pad_local"])
+            assert all(v % 256 == 0 for v in plan["pad_local"])
             got_row = {}
             for s_rank in range(ranks):
                 for e_loc in range(el):
@@ -79,7 +79,7 @@ def test_peer_protocol_positions_reproduce_the_single_gpu_order():
         # the token owner's view: local padded row of an assignment -> row in the expert owner's output
         for me in range(ranks):
             plan = ep_plan_reference(counts, me)
-            my_pad = np.concatenate([[0], np.cumsum((counts[me] + 127) // 128 * 128)])
+            my_pad = np.concatenate([[0], np.cumsum((counts[me] + 255) // 256 * 256)])
             my_off = np.concatenate([[0], np.cumsum(counts[me])])
             for p, a in enumerate(order[me]):
                 e = int(ids[me, a])

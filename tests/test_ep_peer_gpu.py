@@ -213,7 +213,7 @@ def test_plan_with_impossible_counts_is_empty_and_recorded(lib, dev):
     good = [[30, 30, 30, 30, 34, 34, 34, 34], [10, 20, 30, 40, 39, 39, 39, 39]]
     plan, prefix, base = plan_for(good)
     lib.gemb_check_device_status()
-    assert plan[0] == 4 and plan[1] == 512 and prefix[-1] == 220
+    assert plan[0] == 8 and plan[1] == 1024 and prefix[-1] == 220      # four experts, each padded to 256 rows
     for bad in ([[200, 200, 200, 200, 0, 0, 0, 0], [250, 250, 250, 250, 0, 0, 0, 0]],      # 4 x 512 padded rows > 1,024; 800 > 256 sent
                 [[30, -1, 30, 30, 34, 34, 34, 34], good[1]],                                # a negative count
                 [[64, 64, 64, 64, 1, 0, 0, 0], good[1]]):                                   # rank 0 would have sent 257 rows

@@ -98,11 +98,21 @@ def check_permute(lib, dev, orc, ids, experts):
     oc, oo, op = orc.moe_permute(ids, experts)
     assert np.array_equal(to_np(counts), oc) and np.array_equal(to_np(offsets), oo) and np.array_equal(to_np(perm), op)
     plan, rows = to_np(plan), to_np(rows)
-    padded = np.concatenate([[0], np.cumsum((oc + 127) // 128 * 128)])
+    # every expert's rows are padded to a multiple of 256; a 128-row tile of padding only is marked -1
+    padded = np.concatenate([[0], np.cumsum((oc + 255) // 256 * 256)])
     assert plan[0] == padded[-1] // 128 and plan[1] == padded[-1]
     assert np.array_equal(plan[2:2 + experts + 1], padded)
     tile_expert = plan[3 + experts:3 + experts + plan[0]]
-    assert np.array_equal(tile_expert, np.repeat(np.arange(experts), (oc + 127) // 128))
+    want_tiles = []
+    for e in range(experts):
+        real = (oc[e] + 127) // 128
+        want_tiles += [e] * real + [-1] * ((oc[e] + 255) // 256 * 2 - real)
+    assert np.array_equal(tile_expert, np.array(want_tiles, np.int32))
+    # the list of tiles that hold real rows, behind the tile_expert array of full capacity
+    cap_tiles = c.gemb_moe_padded_rows_max(t, experts, k) // 128
+    live_n = plan[3 + experts + cap_tiles]
+    assert live_n == ((oc + 127) // 128).sum()
+    assert np.array_equal(plan[4 + experts + cap_tiles:4 + experts + cap_tiles + live_n], np.nonzero(np.array(want_tiles) >= 0)[0])
     # slot_rows: assignment perm[offsets[e] + j] sits at padded row padded[e] + j
     want_rows = np.empty(t * k, np.int32)
     for e in range(experts):
@@ -167,7 +177,7 @@ def test_layer_benchmark_size_routing_in_full(lib, dev, orc):
     assert np.array_equal(to_np(layer.weights).view(np.uint32), weights.view(np.uint32))
     assert np.array_equal(to_np(layer.counts), counts) and np.array_equal(to_np(layer.offsets), offsets)
     assert np.array_equal(to_np(layer.perm), perm)
-    padded = np.concatenate([[0], np.cumsum((counts + 127) // 128 * 128)])
+    padded = np.concatenate([[0], np.cumsum((counts + 255) // 256 * 256)])
     want_rows = np.empty(tokens * topk, np.int32)
     for e in range(experts):
         want_rows[perm[offsets[e]:offsets[e + 1]]] = padded[e] + np.arange(counts[e])

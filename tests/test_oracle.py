@@ -174,3 +174,54 @@ def test_bf16_helpers(orc):
     x = rng.standard_normal(4096).astype(np.float32)
     assert np.array_equal(orc.to_bf16(x), bf16_bits(x))
     assert np.array_equal(orc.from_bf16(bf16_bits(x)), bf16_round(x))
+
+
+def test_division_by_reciprocal_and_residual_is_correctly_rounded():
+    """The device quantisers compute (x * g) / scale as q0 = RN(t * r), q = RN(q0 + (t - scale * q0) * r)
+    with r = RN(1 / scale) -- one division per 16-block instead of sixteen.  Exact rational arithmetic
+    shows that for every value an E4M3 scale can take this equals the correctly rounded quotient, in
+    particular on and next to every E2M1 rounding boundary, so the bytes stay those of
+    src/numeric/nvfp4.cpp:145-150."""
+    from fractions import Fraction
+    import random
+
+    def rn32(fr):
+        if fr == 0:
+            return Fraction(0)
+        a = abs(fr)
+        e = a.numerator.bit_length() - a.denominator.bit_length()
+        if Fraction(2) ** e > a:
+            e -= 1
+        if Fraction(2) ** (e + 1) <= a:
+            e += 1
+        ulp = Fraction(2) ** (e - 23)
+        q = a / ulp
+        n = q.numerator // q.denominator
+        rem = q - n
+        if rem > Fraction(1, 2) or (rem == Fraction(1, 2) and n % 2 == 1):
+            n += 1
+        return (n if fr > 0 else -n) * ulp
+
+    def step(x, k):
+        a = np.float32(float(x))
+        for _ in range(abs(k)):
+            a = np.nextafter(a, np.float32(np.inf if k > 0 else -np.inf))
+        return Fraction(float(a))
+
+    random.seed(1)
+    mids = [Fraction(1, 4), Fraction(3, 4), Fraction(5, 4), Fraction(7, 4), Fraction(5, 2), Fraction(7, 2), Fraction(5)]
+    checked = 0
+    for bits in range(1, 127):
+        ex, m = (bits >> 3) & 15, bits & 7
+        ds = Fraction(m, 8) * Fraction(2) ** -6 if ex == 0 else (1 + Fraction(m, 8)) * Fraction(2) ** (ex - 7)
+        r = rn32(1 / ds)
+        cands = [step(rn32(mid * ds), k) for mid in mids for k in range(-2, 3)]
+        cands += [Fraction(float(np.float32(random.uniform(0, 7) * float(ds)))) for _ in range(10)]
+        for t in cands:
+            if t <= 0:
+                continue
+            q0 = rn32(t * r)
+            q = rn32(q0 + rn32(t - ds * q0) * r)
+            assert q == rn32(t / ds), (bits, float(t))
+            checked += 1
+    assert checked > 5000
