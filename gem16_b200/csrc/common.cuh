@@ -107,15 +107,18 @@ __host__ __device__ __forceinline__ uint64_t interleaved_scale_offset(uint64_t r
   return ((r / 128) * (c_pad / 4) + c / 4) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + c % 4;
 }
 
-// tanh for the GELU boundary: 1 - 2 / (exp(2x) + 1) with ex2.approx and rcp.approx (two MUFU
-// operations and three arithmetic ones, against the two dozen of tanhf).  Absolute error about
-// 2e-7, i.e. two or three ulps of the "1 + tanh" the GELU formula adds it to -- the same class as
-// tanhf's own deviation from a correctly rounded tanh.  Every kernel that applies the GELU uses
-// this one function, so their results agree byte for byte with one another.
+// tanh for the GELU boundary: 1 - 2 / (exp(2x) + 1) with ex2.approx, rcp.approx and one Newton step
+// on the reciprocal (two MUFU operations and five arithmetic ones, against the two dozen of tanhf).
+// Absolute error about 1e-7, i.e. one or two ulps of the "1 + tanh" the GELU formula adds it to --
+// the same class as tanhf's own deviation from a correctly rounded tanh.  Every kernel that
+// applies the GELU uses this one function, so their results agree byte for byte with one another.
 __device__ __forceinline__ float tanh_gelu(float x) {
   float e;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(x, 2.8853900817779268f)));   // exp(2x)
-  return fmaf(-2.0f, rcp_approx_ftz(__fadd_rn(e, 1.0f)), 1.0f);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(fminf(__fmul_rn(x, 2.8853900817779268f), 126.0f)));   // exp(2x), finite
+  const float d = __fadd_rn(e, 1.0f);
+  const float y0 = rcp_approx_ftz(d);
+  const float y = fmaf(fmaf(-d, y0, 1.0f), y0, y0);
+  return fmaf(-2.0f, y, 1.0f);
 }
 // bf16(gelu_tanh(g)) * u with the bf16 boundaries of src/cuda/nvfp4/reference.cu:177-190
 // (g and u already bf16 values): gelu = bf16(0.5 g (1 + tanh(0.79788456 (g + 0.044715 g^3)))),

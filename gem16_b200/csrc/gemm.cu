@@ -92,6 +92,9 @@ struct GemmParams {
   uint32_t push_ranks;
   uint32_t push_rows;
   uint32_t m_out;                // rows of the buffer the output tensor map describes (0: m)
+  // Up projection with a materialised gate (gate_in != null): the accumulator holds Up [M, n], the
+  // bf16 Gate [M, n] is read in the epilogue, which writes the quantised GELU product like `gated`.
+  const uint16_t* gate_in;
 };
 
 template <bool kFp4, int BN, int kStages, int kAccStages, bool kPair = false>
@@ -603,6 +606,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           pending_col = col0;
           continue;
         }
+        if (kFp4 && p.gate_in != nullptr) {
+          // 64 up values of features col0 .. col0+63 for this thread's token; the gate of the same
+          // features comes from memory (bf16, 128 bytes of the token's row).
+          ptx::tc_wait_ld();
+          if (c + 2 >= BN / 64 || col0 + 128 >= p.n) {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) arrive_issuer(&acc_empty[as]);
+            released = true;
+          }
+          const uint32_t row = row0 + lane;
+          if (row < p.m) {
+            const uint4* gp = reinterpret_cast<const uint4*>(p.gate_in + static_cast<uint64_t>(row) * p.n + col0);
+            const uint32_t c_pad = (p.n / 16 + 3) / 4 * 4;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              if (col0 + b * 16 >= p.n) break;
+              const uint4 ga4 = __ldg(gp + 2 * b), gb4 = __ldg(gp + 2 * b + 1);
+              const uint32_t gw[8] = {ga4.x, ga4.y, ga4.z, ga4.w, gb4.x, gb4.y, gb4.z, gb4.w};
+              float prod[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const uint32_t acc = b < 2 ? v0[b * 16 + i] : v1[(b - 2) * 16 + i];
+                const float uv = bf16_round(__fmul_rn(__uint_as_float(acc), row_scale));
+                const float gv = __uint_as_float((i & 1) ? (gw[i >> 1] & 0xFFFF0000u) : (gw[i >> 1] << 16));
+                prod[i] = gelu_tanh_product(gv, uv);
+              }
+              uint32_t lo, hi;
+              uint8_t sb;
+              quantize_block16<false>(prod, p.g_product, lo, hi, sb);
+              *reinterpret_cast<uint2*>(p.out_packed + static_cast<uint64_t>(row) * (p.n / 2) + (col0 + b * 16) / 2) = make_uint2(lo, hi);
+              p.out_scales[interleaved_scale_offset(row, (col0 + b * 16) / 16, c_pad)] = sb;
+            }
+          }
+          continue;
+        }
         if (kFp4 && p.out_f32) {
           // fp32 output: two 32-column boxes (128 bytes per row each) through the same staging buffer.
           ptx::tc_wait_ld();
@@ -833,6 +872,8 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
     GEMB_TRY(make_out_map_f32(op, &map_out, p.out, p.m, p.n));
   else if (p.gated)  // the tensor-map store path is unused; describe the payload buffer so the map is valid
     GEMB_TRY(make_out_map(op, &map_out, p.out_packed, p.m, p.n / 8));
+  else if (p.gate_in != nullptr)
+    GEMB_TRY(make_out_map(op, &map_out, p.out_packed, p.m, p.n / 4));
   else
     GEMB_TRY(make_out_map(op, &map_out, p.out, p.m_out ? p.m_out : p.m, p.n));
   const uint32_t m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
@@ -1111,6 +1152,39 @@ int32_t gemb_nvfp4_gemm_gated_quant(const uint8_t* act, const uint8_t* act_scale
   p.out_packed = product_packed;
   p.out_scales = product_interleaved_scales;
   return launch_gated(op, act, w_fused, p, stream);
+}
+
+int32_t gemb_nvfp4_gemm_up_gated_quant(const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* up_w,
+                                       const uint8_t* up_scales_interleaved, const uint16_t* gate_bf16,
+                                       uint8_t* product_packed, uint8_t* product_interleaved_scales, uint64_t tokens,
+                                       uint64_t rows, uint64_t k, float ga, float gw_up, float product_divisor,
+                                       gemb_stream_t stream) {
+  const char* op = "gemb_nvfp4_gemm_up_gated_quant";
+  GEMB_REQUIRE(act && act_scales_interleaved && up_w && up_scales_interleaved && gate_bf16 && product_packed &&
+                   product_interleaved_scales,
+               "%s: pointers must be nonnull", op);
+  GEMB_TRY(validate_gemm(op, tokens, rows, k, 64));
+  GEMB_REQUIRE(rows % 64 == 0, "%s: rows must be a multiple of 64", op);
+  GEMB_REQUIRE(positive_finite(ga) && positive_finite(gw_up) && positive_finite(product_divisor) && std::isfinite(ga * gw_up),
+               "%s: global divisors must be positive and finite", op);
+  GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(up_w) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(act_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(up_scales_interleaved) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(gate_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(product_packed) % 16 == 0,
+               "%s: all buffers must be 16-byte aligned", op);
+  GEMB_TRY(require_sm100(op));
+  GemmParams p{};
+  p.sfa = act_scales_interleaved;
+  p.sfb = up_scales_interleaved;
+  p.m = static_cast<uint32_t>(tokens);
+  p.n = static_cast<uint32_t>(rows);
+  p.k = static_cast<uint32_t>(k);
+  p.alpha = 1.0f / (ga * gw_up);
+  p.gate_in = gate_bf16;
+  p.g_product = product_divisor;
+  p.out_packed = product_packed;
+  p.out_scales = product_interleaved_scales;
+  return launch_gated(op, act, up_w, p, stream);
 }
 
 int32_t gemb_moe_grouped_gemm_gated_quant(const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* w_fused,

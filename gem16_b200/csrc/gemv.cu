@@ -1290,4 +1290,19 @@ int32_t gemb_nvfp4_gemv_gate_up(const uint8_t* act, const uint8_t* act_scales, c
                                  product, rows, k, gate_ga * gate_gw, up_ga * up_gw, stream);
 }
 
+int32_t gemb_nvfp4_gemv_gate_up_batch(const uint8_t* act, const uint8_t* act_scales, const uint8_t* gate_w,
+                                      const uint8_t* gate_s, const uint8_t* up_w, const uint8_t* up_s, float* gate_out,
+                                      float* up_out, float* product, uint64_t tokens, uint64_t rows, uint64_t k,
+                                      float gate_ga, float gate_gw, float up_ga, float up_gw, gemb_stream_t stream) {
+  const char* op = "gemb_nvfp4_gemv_gate_up_batch";
+  GEMB_REQUIRE(tokens >= 1 && tokens <= 65535, "%s: between 1 and 65,535 tokens", op);
+  // One fused gate/up launch per token (the verifier's batches are a handful of tokens): every
+  // token's result is bit-identical to the single-token operator.
+  for (uint64_t t = 0; t < tokens; ++t)
+    GEMB_TRY(gemb_nvfp4_gemv_gate_up(act + t * (k / 2), act_scales + t * (k / 16), gate_w, gate_s, up_w, up_s,
+                                     gate_out ? gate_out + t * rows : nullptr, up_out ? up_out + t * rows : nullptr,
+                                     product + t * rows, rows, k, gate_ga, gate_gw, up_ga, up_gw, stream));
+  return GEMB_OK;
+}
+
 }  // extern "C"

@@ -152,7 +152,7 @@ output_head_kernel(const uint16_t* __restrict__ weights, const float* __restrict
         const uint32_t ot = __shfl_down_sync(0xFFFFFFFFu, c.token, off);
         if (better(ov, ot, c)) c = {ov, ot};
       }
-      if (lane == 0) candidates[static_cast<uint64_t>(r) * kOhBlocks + blockIdx.x] = c;
+      if (lane == 0 && candidates != nullptr) candidates[static_cast<uint64_t>(r) * kOhBlocks + blockIdx.x] = c;
     }
   }
 }
@@ -222,7 +222,8 @@ int32_t gemb_output_head_candidates(const uint16_t* weights_bf16, const float* h
                                     float* diagnostic_logits, uint64_t vocabulary, uint64_t hidden,
                                     gemb_stream_t stream) {
   const char* op = "gemb_output_head_candidates";
-  GEMB_REQUIRE(weights_bf16 && hidden_rows && candidates, "%s: pointers must be nonnull", op);
+  GEMB_REQUIRE(weights_bf16 && hidden_rows && (candidates || diagnostic_logits),
+               "%s: weights, hidden rows and at least one of candidates / logits must be nonnull", op);
   GEMB_REQUIRE(rows >= 1 && rows <= kOhMaxRows, "%s: between 1 and %d hidden rows", op, kOhMaxRows);
   GEMB_REQUIRE(suppressed_count == 0 || suppressed != nullptr, "%s: a nonempty suppression list needs a pointer", op);
   GEMB_REQUIRE(suppressed_count < (1ull << 20), "%s: suppression list too long", op);

@@ -160,6 +160,30 @@ __device__ __forceinline__ float rmsnorm_inverse(const In* row, uint64_t k, floa
   return rsqrtf(red[0] / static_cast<float>(k) + eps);
 }
 
+// RMSNorm + residual (+ layer scalar) with the bf16 boundaries of src/cuda/norm/reference.cu:66-160:
+// n = bf16(x * inv * w), v = bf16(n + residual), v = bf16(v * scalar) when a scalar is given.
+__device__ __forceinline__ void store_scalar(float* p, uint64_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void store_scalar(uint16_t* p, uint64_t i, float v) { p[i] = float_to_bf16_bits(v); }
+
+template <typename In, typename Res, typename Out>
+__global__ void __launch_bounds__(256)
+rmsnorm_residual_kernel(const In* __restrict__ x, const uint16_t* __restrict__ w, const Res* __restrict__ residual,
+                        float* __restrict__ normalized, Out* __restrict__ out, uint64_t k, float eps,
+                        const uint16_t* __restrict__ scalar) {
+  __shared__ float red[256];
+  const uint64_t base = static_cast<uint64_t>(blockIdx.x) * k;
+  const float inv = rmsnorm_inverse(x + base, k, eps, red);
+  const float layer_scale = scalar ? bf16_bits_to_float(__ldg(scalar)) : 1.0f;
+  for (uint64_t i = threadIdx.x; i < k; i += 256) {
+    const float ws = w ? bf16_bits_to_float(__ldg(w + i)) : 1.0f;
+    const float n = bf16_round(__fmul_rn(__fmul_rn(load_scalar(x + base, i), inv), ws));
+    if (normalized) normalized[base + i] = n;
+    float v = bf16_round(__fadd_rn(n, load_scalar(residual + base, i)));
+    if (scalar) v = bf16_round(__fmul_rn(v, layer_scale));
+    store_scalar(out, base + i, v);
+  }
+}
+
 template <typename In, bool kRcp, bool kInterleaved>
 __global__ void __launch_bounds__(256)
 rmsnorm_nvfp4_quantize_kernel(const In* __restrict__ x, const uint16_t* __restrict__ w,
@@ -370,6 +394,34 @@ int32_t gemb_fp8_rmsnorm_quantize(const void* input, int32_t input_dtype, const 
     fp8_quantize_kernel<float, true><<<grid, 256, 0, stream>>>(static_cast<const float*>(input), weight, out, scales, k, eps);
   else
     fp8_quantize_kernel<uint16_t, true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(input), weight, out, scales, k, eps);
+  return check_launch(op);
+}
+
+int32_t gemb_rmsnorm_residual(const void* input, int32_t input_dtype, const uint16_t* weight_bf16, const void* residual,
+                              float* normalized_output, void* output, int32_t residual_output_dtype, uint64_t vectors,
+                              uint64_t width, float epsilon, const uint16_t* scalar_bf16, gemb_stream_t stream) {
+  const char* op = "gemb_rmsnorm_residual";
+  GEMB_REQUIRE(input && residual && output, "%s: input, residual and output must be nonnull", op);
+  GEMB_REQUIRE((input_dtype == GEMB_F32 || input_dtype == GEMB_BF16) &&
+                   (residual_output_dtype == GEMB_F32 || residual_output_dtype == GEMB_BF16), "%s: unknown dtype", op);
+  GEMB_REQUIRE(vectors > 0 && vectors < (1ull << 31) && width > 0 && width < (1ull << 31), "%s: bad geometry", op);
+  GEMB_REQUIRE(positive_finite(epsilon), "%s: epsilon must be positive and finite", op);
+  GEMB_REQUIRE(residual_output_dtype == GEMB_F32 || (input_dtype == GEMB_BF16 && normalized_output == nullptr),
+               "%s: bf16 residual and output go with a bf16 input and no separate normalised output", op);
+  GEMB_TRY(require_sm100(op));
+  const unsigned grid = static_cast<unsigned>(vectors);
+  if (residual_output_dtype == GEMB_BF16)
+    rmsnorm_residual_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(input), weight_bf16,
+                                                      static_cast<const uint16_t*>(residual), normalized_output,
+                                                      static_cast<uint16_t*>(output), width, epsilon, scalar_bf16);
+  else if (input_dtype == GEMB_BF16)
+    rmsnorm_residual_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(input), weight_bf16,
+                                                      static_cast<const float*>(residual), normalized_output,
+                                                      static_cast<float*>(output), width, epsilon, scalar_bf16);
+  else
+    rmsnorm_residual_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(input), weight_bf16,
+                                                      static_cast<const float*>(residual), normalized_output,
+                                                      static_cast<float*>(output), width, epsilon, scalar_bf16);
   return check_launch(op);
 }
 

@@ -15,6 +15,7 @@
 #include "cuda/fp8/sm120.h"
 #include "cuda/nvfp4/cutlass_sm120.h"
 #include "cuda/nvfp4/gemv.h"
+#include "cuda/nvfp4/mlp.h"
 #include "cuda/nvfp4/reference.h"
 #include "cuda/nvfp4/sm120.h"
 #include "cuda/output_head.h"
@@ -247,6 +248,66 @@ Status LaunchOutputHeadCandidateArgmax(const OutputHeadCandidate* candidates, st
 Status LaunchOutputHeadBatchArgmax(const OutputHeadCandidate* candidates, std::uint64_t rows, std::uint32_t* selected,
                                    cudaStream_t stream) {
   return ToStatus(gemb_output_head_argmax(candidates, rows, selected, S(stream)));
+}
+
+// ---- launchers beside the projections that the engine calls on the same path ------------------
+Status LaunchNvfp4CutlassUpGatedGeluQuantizedBatch(
+    const std::uint8_t* act, const std::uint8_t* act_scales_interleaved, const std::uint8_t* up_weight,
+    const std::uint8_t* up_weight_scales, std::uint8_t*, std::uint8_t*, void*, std::size_t,
+    const std::uint16_t* gate_bf16, std::uint8_t* product_packed, std::uint8_t* product_scales,
+    std::uint64_t tokens, std::uint64_t rows, std::uint64_t k, float ga, float gw, float product_divisor,
+    const float*, cudaStream_t stream) {
+  return ToStatus(gemb_nvfp4_gemm_up_gated_quant(act, act_scales_interleaved, up_weight, up_weight_scales, gate_bf16,
+                                                 product_packed, product_scales, tokens, rows, k, ga, gw,
+                                                 product_divisor, S(stream)));
+}
+Status LaunchNvfp4Sm120FusedGateUpBatch(const std::uint8_t* act, const std::uint8_t* act_scales,
+                                        const std::uint8_t* gate_weight, const std::uint8_t* gate_scales,
+                                        const std::uint8_t* up_weight, const std::uint8_t* up_scales,
+                                        float* gate_output, float* up_output, float* product_output,
+                                        std::uint64_t tokens, std::uint64_t rows, std::uint64_t k, float gate_ga,
+                                        float gate_gw, float up_ga, float up_gw, cudaStream_t stream) {
+  return ToStatus(gemb_nvfp4_gemv_gate_up_batch(act, act_scales, gate_weight, gate_scales, up_weight, up_scales,
+                                                gate_output, up_output, product_output, tokens, rows, k, gate_ga,
+                                                gate_gw, up_ga, up_gw, S(stream)));
+}
+Status LaunchGeluTanhProduct(const float* gate, const float* up, float* output, std::uint64_t elements,
+                             cudaStream_t stream) {
+  return ToStatus(gemb_gelu_tanh_product_f32(gate, up, output, elements, S(stream)));
+}
+Status LaunchAddResidual(const float* mlp_output, const float* residual, float* output, std::uint64_t elements,
+                         cudaStream_t stream) {
+  return ToStatus(gemb_add_residual_f32(mlp_output, residual, output, elements, S(stream)));
+}
+Status LaunchOutputHeadLogits(const std::uint16_t* weights, const float* hidden, float* logits, cudaStream_t stream) {
+  return ToStatus(gemb_output_head_candidates(weights, hidden, 1, nullptr, 0, nullptr, nullptr, logits, 262144, 3840,
+                                              S(stream)));
+}
+Status LaunchLogitArgmax(const float* logits, const std::uint32_t* suppressed, std::uint32_t suppressed_count,
+                         std::uint32_t* selected, cudaStream_t stream) {
+  return ToStatus(gemb_logit_argmax(logits, suppressed, suppressed_count, selected, 262144, S(stream)));
+}
+
+// ---- src/cuda/layer/reference.h: the RMSNorm + residual forms on both sides of every linear ------
+Status LaunchRmsNormResidualBf16(const float* input, const std::uint16_t* weight_bf16, const float* residual,
+                                 float* normalized_output, float* output, std::uint64_t vectors, std::uint64_t width,
+                                 float epsilon, const std::uint16_t* scalar_bf16, cudaStream_t stream) {
+  return ToStatus(gemb_rmsnorm_residual(input, GEMB_F32, weight_bf16, residual, normalized_output, output, GEMB_F32,
+                                        vectors, width, epsilon, scalar_bf16, S(stream)));
+}
+Status LaunchRmsNormResidualBf16Input(const std::uint16_t* input_bf16, const std::uint16_t* weight_bf16,
+                                      const float* residual, float* normalized_output, float* output,
+                                      std::uint64_t vectors, std::uint64_t width, float epsilon,
+                                      const std::uint16_t* scalar_bf16, cudaStream_t stream) {
+  return ToStatus(gemb_rmsnorm_residual(input_bf16, GEMB_BF16, weight_bf16, residual, normalized_output, output, GEMB_F32,
+                                        vectors, width, epsilon, scalar_bf16, S(stream)));
+}
+Status LaunchRmsNormResidualPhysicalBf16(const std::uint16_t* input_bf16, const std::uint16_t* weight_bf16,
+                                         const std::uint16_t* residual_bf16, std::uint16_t* output_bf16,
+                                         std::uint64_t vectors, std::uint64_t width, float epsilon,
+                                         const std::uint16_t* scalar_bf16, cudaStream_t stream) {
+  return ToStatus(gemb_rmsnorm_residual(input_bf16, GEMB_BF16, weight_bf16, residual_bf16, nullptr, output_bf16, GEMB_BF16,
+                                        vectors, width, epsilon, scalar_bf16, S(stream)));
 }
 
 }  // namespace gem16::internal

@@ -155,6 +155,24 @@ int32_t gemb_fp8_rmsnorm_quantize(const void* input, int32_t input_dtype,
                                   uint64_t elements_per_token, float epsilon,
                                   gemb_stream_t stream);
 
+/* RMSNorm + residual (+ layer scalar) with bf16 boundaries: n = bf16(x * inv * w), v = bf16(n +
+ * residual), v = bf16(v * scalar) when scalar_bf16 is non-null; weight_bf16 may be null.  input is fp32
+ * or bf16 (input_dtype); residual and output are both fp32 or both bf16 (residual_output_dtype; bf16
+ * needs a bf16 input); normalized_output (fp32, optional) receives n.
+ * Replaces LaunchRmsNormResidualBf16, ...Bf16Input and ...PhysicalBf16, src/cuda/layer/reference.h:45-71
+ * (kernels src/cuda/norm/reference.cu:66-160). */
+int32_t gemb_rmsnorm_residual(const void* input, int32_t input_dtype, const uint16_t* weight_bf16,
+                              const void* residual, float* normalized_output, void* output,
+                              int32_t residual_output_dtype, uint64_t vectors, uint64_t width, float epsilon,
+                              const uint16_t* scalar_bf16, gemb_stream_t stream);
+
+/* out = bf16(gelu_tanh(gate)) * up in fp32, and out = a + b: the MLP's elementwise bridges.
+ * Replace LaunchGeluTanhProduct and LaunchAddResidual, src/cuda/nvfp4/mlp.h:13-23. */
+int32_t gemb_gelu_tanh_product_f32(const float* gate, const float* up, float* output, uint64_t elements,
+                                   gemb_stream_t stream);
+int32_t gemb_add_residual_f32(const float* values, const float* residual, float* output, uint64_t elements,
+                              gemb_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Batch-1 decode projections (HBM-streaming GEMV).  Weights are row-major [rows, K] in the
  * checkpoint's source layout; NVFP4 block scales are COMPACT [rows, K/16].
@@ -236,6 +254,25 @@ int32_t gemb_nvfp4_gemv_gate_up(const uint8_t* packed_activation_e2m1,
                                 float up_activation_global_divisor,
                                 float up_weight_global_divisor, gemb_stream_t stream);
 
+/* The same for 1..65,535 tokens (the verifier's batches are a handful): activation [tokens, K/2]
+ * with COMPACT scales [tokens, K/16], outputs [tokens, rows]; per token bit-identical to
+ * gemb_nvfp4_gemv_gate_up, which it launches once per token.
+ * Replaces LaunchNvfp4Sm120FusedGateUpBatch, src/cuda/nvfp4/sm120.h:75-92. */
+int32_t gemb_nvfp4_gemv_gate_up_batch(const uint8_t* packed_activation_e2m1, const uint8_t* activation_scales,
+                                      const uint8_t* packed_gate_weight, const uint8_t* gate_weight_scales,
+                                      const uint8_t* packed_up_weight, const uint8_t* up_weight_scales,
+                                      float* gate_output, float* up_output, float* product_output,
+                                      uint64_t tokens, uint64_t rows, uint64_t contracting_elements,
+                                      float gate_activation_global_divisor, float gate_weight_global_divisor,
+                                      float up_activation_global_divisor, float up_weight_global_divisor,
+                                      gemb_stream_t stream);
+
+/* y[row] = bf16( sum_k x[k] * W[row][k] ) kept as fp32: fp32 activation, bf16 weights [rows, K],
+ * fp32 accumulation, one bf16 rounding of the result.  K % 8 == 0, K <= 12,288.  The assistant
+ * model's projections; replaces the Bf16GemvKernel launches of src/cuda/mtp/assistant.cu:99-122. */
+int32_t gemb_bf16_gemv(const float* input, const uint16_t* weight_bf16, float* output, uint64_t rows,
+                       uint64_t contracting_elements, gemb_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Prefill projections (tcgen05 GEMM, TMEM accumulators, TMA-staged tiles), bf16 output [tokens,
  * rows].  Operands are row-major and K-major: activation [tokens, K], weight [rows, K].
@@ -285,6 +322,21 @@ int32_t gemb_nvfp4_gemm_gated_quant(const uint8_t* packed_activation_e2m1,
                                     uint64_t contracting_elements, float activation_global_divisor,
                                     float gate_weight_global_divisor, float up_weight_global_divisor,
                                     float product_global_divisor, gemb_stream_t stream);
+
+/* The reference's own split of the same step: the Gate projection is already materialised as bf16
+ * [tokens, rows]; this call runs the Up projection and its epilogue reads the gate, applies the
+ * bf16 boundaries, the GELU-tanh product and the NVFP4 quantiser (EXACT contract) with the down
+ * projection's input divisor.  Output as gemb_nvfp4_gemm_gated_quant; byte-identical to
+ * gemb_nvfp4_gemm_bf16 (up) + gemb_nvfp4_gated_gelu_quantize.  rows % 64 == 0, K % 64 == 0.
+ * Replaces LaunchNvfp4CutlassUpGatedGeluQuantizedBatch, src/cuda/nvfp4/cutlass_sm120.h:47-67. */
+int32_t gemb_nvfp4_gemm_up_gated_quant(const uint8_t* packed_activation_e2m1,
+                                       const uint8_t* interleaved_activation_scales,
+                                       const uint8_t* packed_up_weight_e2m1,
+                                       const uint8_t* interleaved_up_weight_scales, const uint16_t* gate_bf16,
+                                       uint8_t* product_packed_e2m1, uint8_t* product_interleaved_scales,
+                                       uint64_t tokens, uint64_t rows, uint64_t contracting_elements,
+                                       float activation_global_divisor, float up_weight_global_divisor,
+                                       float product_global_divisor, gemb_stream_t stream);
 
 /* Builds the fused gate/up weight of gemb_nvfp4_gemm_gated_quant from the two row-major NVFP4
  * matrices [intermediate, K/2] with COMPACT scales: output row (f/32)*64 + which*32 + f%32 holds
@@ -447,7 +499,12 @@ int32_t gemb_moe_expert_gelu_quantize(const uint16_t* gate_up_bf16, const int32_
  * diagnostic_logits, LaunchOutputHeadLogits (output_head.h:40-43).
  * gemb_output_head_argmax reduces the candidates of each row to selected[r]
  * (LaunchOutputHeadCandidateArgmax / LaunchOutputHeadBatchArgmax, output_head.h:32-38). */
+/* candidates may be null when only the diagnostic logits are wanted (LaunchOutputHeadLogits).
+ * gemb_logit_argmax picks the largest of `vocabulary` materialised logits that is not on the
+ * suppression list, the lower token id on ties (LaunchLogitArgmax, output_head.h:44-48). */
 uint64_t gemb_output_head_candidate_blocks(void);
+int32_t gemb_logit_argmax(const float* logits, const uint32_t* suppressed, uint64_t suppressed_count,
+                          uint32_t* selected, uint64_t vocabulary, gemb_stream_t stream);
 int32_t gemb_output_head_candidates(const uint16_t* weights_bf16, const float* hidden_rows, uint64_t rows,
                                     const uint32_t* suppressed, uint64_t suppressed_count,
                                     const uint32_t* dynamic_suppressed_count, void* candidates,

@@ -83,3 +83,22 @@ def test_shim_compiles_against_the_reference_headers():
            os.path.join(root, "gem16_b200", "shim", "gem16_internal_shim.cpp")]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-3000:]
+
+
+def test_shim_defines_every_launcher_of_the_operator_headers():
+    # The shim replaces gem16's operator sources at link time only if it defines every launcher the
+    # operator headers of this path declare (and the RMSNorm + residual forms of layer/reference.h).
+    import os
+    import re
+    from oracle.build import REF_ROOT as ref
+    if not os.path.isfile(os.path.join(ref, "src", "cuda", "nvfp4", "sm120.h")):
+        pytest.skip("reference tree not present")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    shim = open(os.path.join(root, "gem16_b200", "shim", "gem16_internal_shim.cpp")).read()
+    defined = set(re.findall(r"^Status (Launch\w+)\(", shim, flags=re.M))
+    declared = set()
+    for h in ("nvfp4/reference", "nvfp4/sm120", "nvfp4/cutlass_sm120", "nvfp4/gemv", "nvfp4/mlp", "fp8/reference", "fp8/sm120",
+              "fp8/cutlass_sm120", "output_head"):
+        declared |= set(re.findall(r"Status (Launch\w+)\(", open(os.path.join(ref, "src", "cuda", h + ".h")).read()))
+    assert declared and not (declared - defined), sorted(declared - defined)
+    assert {"LaunchRmsNormResidualBf16", "LaunchRmsNormResidualBf16Input", "LaunchRmsNormResidualPhysicalBf16"} <= defined
