@@ -1,6 +1,7 @@
 """In-tree build of libgemb200.so (sm_100a only) with plain nvcc.
 
     python -m gem16_b200.build [--force] [--verbose]
+    GEMB_NVTX=1 python -m gem16_b200.build --force      (NVTX range around every entry point)
 
 The shared object lands next to this file so it travels with the source tree.  It links the
 CUDA runtime statically and has no Python or torch dependency.
@@ -32,13 +33,14 @@ def headers() -> list[str]:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
+    flags = FLAGS + (["-DGEMB_NVTX"] if os.environ.get("GEMB_NVTX") == "1" else [])
     hdr_time = max(os.path.getmtime(h) for h in headers())
     objs, procs = [], []
     for src in sources():
         obj = os.path.join(OBJ, os.path.basename(src) + ".o")
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_time):
-            cmd = [NVCC, *FLAGS, "-c", src, "-o", obj] + (["-Xptxas", "-v"] if verbose else [])
+            cmd = [NVCC, *flags, "-c", src, "-o", obj] + (["-Xptxas", "-v"] if verbose else [])
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for src, p in procs:

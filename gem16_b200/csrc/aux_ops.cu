@@ -120,7 +120,7 @@ int32_t gemb_gelu_tanh_product_f32(const float* gate, const float* up, float* ou
   const char* op = "gemb_gelu_tanh_product_f32";
   GEMB_REQUIRE(gate && up && output, "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(elements > 0 && elements < (1ull << 40), "%s: extent must be nonzero", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   gelu_tanh_product_kernel<<<static_cast<unsigned>((elements + 255) / 256), 256, 0, stream>>>(gate, up, output, elements);
   return check_launch(op);
 }
@@ -129,7 +129,7 @@ int32_t gemb_add_residual_f32(const float* values, const float* residual, float*
   const char* op = "gemb_add_residual_f32";
   GEMB_REQUIRE(values && residual && output, "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(elements > 0 && elements < (1ull << 40), "%s: extent must be nonzero", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   add_residual_kernel<<<static_cast<unsigned>((elements + 255) / 256), 256, 0, stream>>>(values, residual, output, elements);
   return check_launch(op);
 }
@@ -140,7 +140,7 @@ int32_t gemb_logit_argmax(const float* logits, const uint32_t* suppressed, uint6
   GEMB_REQUIRE(logits && selected, "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(suppressed_count == 0 || suppressed != nullptr, "%s: a nonempty suppression list needs a pointer", op);
   GEMB_REQUIRE(suppressed_count < 4096 && vocabulary > 0 && vocabulary < (1ull << 31), "%s: bad geometry", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   logit_argmax_kernel<<<1, 1024, 0, stream>>>(logits, suppressed, static_cast<uint32_t>(suppressed_count),
                                              static_cast<uint32_t>(vocabulary), selected);
   return check_launch(op);
@@ -154,7 +154,7 @@ int32_t gemb_bf16_gemv(const float* input, const uint16_t* weight_bf16, float* o
   GEMB_REQUIRE(contracting_elements > 0 && contracting_elements % 8 == 0 && contracting_elements <= 48 * 1024 / 4,
                "%s: the contracting extent must be a nonzero multiple of 8, at most 12,288", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(weight_bf16) % 16 == 0, "%s: weights must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const uint64_t ctas = std::min<uint64_t>((rows + 7) / 8, static_cast<uint64_t>(sm_count()) * 8);
   bf16_gemv_kernel<<<static_cast<unsigned>(ctas), kBgThreads, contracting_elements * 4, stream>>>(
       input, weight_bf16, output, static_cast<uint32_t>(rows), static_cast<uint32_t>(contracting_elements));

@@ -12,6 +12,16 @@
 
 #include "gemb200.h"
 
+#ifdef GEMB_NVTX
+#include <nvtx3/nvToolsExt.h>
+namespace gemb {
+struct OpRange {
+  explicit OpRange(const char* name) { nvtxRangePushA(name); }
+  ~OpRange() { nvtxRangePop(); }
+};
+}  // namespace gemb
+#endif
+
 namespace gemb {
 
 // Records `message` (printf style) as the calling thread's last error and returns `code`.
@@ -42,6 +52,18 @@ inline bool positive_finite(float v) { return std::isfinite(v) && v > 0.0f; }
   do {                                                                    \
     if (!(cond)) return ::gemb::fail(GEMB_INVALID_ARGUMENT, __VA_ARGS__); \
   } while (0)
+
+// Device gate plus, when the library is built with -DGEMB_NVTX, an NVTX range named after the entry
+// point for the rest of the call (gem16 brackets its operators the same way,
+// src/cuda/engine/inference_engine.cu:81-87).  Off by default: a range costs a few hundred
+// nanoseconds per launch.
+#ifdef GEMB_NVTX
+#define GEMB_ENTER(op)                     \
+  GEMB_TRY(::gemb::require_sm100(op));     \
+  ::gemb::OpRange gemb_op_range_(op)
+#else
+#define GEMB_ENTER(op) GEMB_TRY(::gemb::require_sm100(op))
+#endif
 
 #define GEMB_TRY(expr)                   \
   do {                                   \

@@ -542,7 +542,7 @@ int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t exp
   GEMB_REQUIRE(capacity_rows > 0 && capacity_rows < (1ull << 31) && capacity_rows % 128 == 0 &&
                    send_rows_per_rank > 0 && send_rows_per_rank < (1ull << 31),
                "%s: buffer capacities must be nonzero (padded rows a multiple of 128)", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   ep_plan_kernel<<<1, 256, 5 * experts * sizeof(int), stream>>>(
       counts_all, static_cast<uint32_t>(ranks), static_cast<uint32_t>(experts), static_cast<uint32_t>(rank), plan,
       recv_prefix, recv_src_rows, recv_dst_rows, combine_row_base, static_cast<uint32_t>(capacity_rows),
@@ -556,7 +556,7 @@ int32_t gemb_moe_ep_barrier(const uint64_t* peer_flag_arrays_host, uint64_t rank
   PeerPtrs peers;
   GEMB_TRY(load_peers(op, peer_flag_arrays_host, ranks, &peers));
   GEMB_REQUIRE(rank < ranks && which < 2 && local_epochs != nullptr, "%s: bad rank, barrier index or epoch pointer", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   ep_barrier_kernel<<<1, 32, 0, stream>>>(peers, static_cast<uint32_t>(ranks), static_cast<uint32_t>(rank),
                                           static_cast<uint32_t>(which), local_epochs,
                                           static_cast<uint32_t>(g_ep_barrier_spins));
@@ -569,7 +569,7 @@ int32_t gemb_moe_ep_gather_counts(const uint64_t* peer_count_buffers_host, uint6
   PeerPtrs peers;
   GEMB_TRY(load_peers(op, peer_count_buffers_host, ranks, &peers));
   GEMB_REQUIRE(counts_all != nullptr && experts >= 1 && experts <= kMaxExperts, "%s: bad arguments", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   ep_gather_counts_kernel<<<1, 256, 0, stream>>>(peers, static_cast<uint32_t>(ranks), static_cast<uint32_t>(experts), counts_all);
   return check_launch(op);
 }
@@ -583,7 +583,7 @@ int32_t gemb_tp_reduce_rows(const uint64_t* peer_partials_host, uint64_t ranks, 
   GEMB_REQUIRE(tokens > 0 && tokens < (1ull << 31) && hidden > 0 && hidden % 8 == 0 && hidden < (1ull << 24),
                "%s: hidden must be a nonzero multiple of 8", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(out_bf16) % 16 == 0, "%s: output must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const uint64_t begin = rank * tokens / ranks, end = (rank + 1) * tokens / ranks;
   if (end == begin) return GEMB_OK;
   const uint64_t work = (end - begin) * (hidden / 4);
@@ -602,7 +602,7 @@ int32_t gemb_tp_gather_rows(const uint64_t* peer_outputs_host, uint64_t ranks, u
   GEMB_REQUIRE(tokens > 0 && tokens < (1ull << 31) && hidden > 0 && hidden % 8 == 0 && hidden < (1ull << 24),
                "%s: hidden must be a nonzero multiple of 8", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(out_bf16) % 16 == 0, "%s: output must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   if (ranks == 1) return GEMB_OK;
   const uint64_t work = tokens * (hidden / 8);
   const uint64_t ctas = std::min<uint64_t>((work + 255) / 256, static_cast<uint64_t>(sm_count()) * 16);
@@ -631,7 +631,7 @@ int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers_host, uint64
   GEMB_REQUIRE(send_rows_per_rank > 0 && send_rows_per_rank < (1ull << 31) && padded_rows_max > 0 &&
                    padded_rows_max < (1ull << 31) && padded_rows_max % 128 == 0,
                "%s: buffer capacities must be nonzero (padded rows a multiple of 128)", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const uint32_t segments = static_cast<uint32_t>(ranks * local_experts);
   const uint32_t c_pad = static_cast<uint32_t>((hidden / 16 + 3) / 4 * 4);
   ep_pull_dispatch_kernel<<<static_cast<unsigned>(sm_count()) * 8, 256, (segments + 1) * sizeof(int), stream>>>(
@@ -656,7 +656,7 @@ int32_t gemb_moe_ep_pull_combine(const uint64_t* peer_expert_outputs_host, uint6
   GEMB_REQUIRE(padded_rows_max > 0 && padded_rows_max < (1ull << 31), "%s: output capacity must be nonzero", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(out_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(shared_bf16) % 16 == 0,
                "%s: buffers must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const uint64_t work = tokens * (hidden / 8);
   ep_pull_combine_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
       peers, top_ids, slot_rows, combine_row_base, top_weights, shared_bf16, out_bf16, static_cast<uint32_t>(tokens),

@@ -935,7 +935,7 @@ int32_t gemb_nvfp4_gemm_bf16(const uint8_t* act, const uint8_t* act_scales_inter
                    reinterpret_cast<uintptr_t>(w_scales_interleaved) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(out) % 16 == 0,
                "%s: all buffers must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   GemmParams p{};
   p.sfa = act_scales_interleaved;
   p.sfb = w_scales_interleaved;
@@ -963,7 +963,7 @@ int32_t gemb_nvfp4_gemm_f32(const uint8_t* act, const uint8_t* act_scales_interl
                    reinterpret_cast<uintptr_t>(w_scales_interleaved) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(out) % 16 == 0,
                "%s: all buffers must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   GemmParams p{};
   p.sfa = act_scales_interleaved;
   p.sfb = w_scales_interleaved;
@@ -996,7 +996,7 @@ int32_t gemb_moe_grouped_gemm_bf16(const uint8_t* act, const uint8_t* act_scales
                    reinterpret_cast<uintptr_t>(w_scales_interleaved) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(out) % 16 == 0,
                "%s: all buffers must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   GemmParams p{};
   p.sfa = act_scales_interleaved;
   p.sfb = w_scales_interleaved;
@@ -1102,7 +1102,7 @@ extern "C" int32_t gemb_nvfp4_pack_gate_up(const uint8_t* gate_packed, const uin
                    reinterpret_cast<uintptr_t>(fused_packed) % 16 == 0 && reinterpret_cast<uintptr_t>(gate_scales) % 2 == 0 &&
                    reinterpret_cast<uintptr_t>(up_scales) % 2 == 0 && reinterpret_cast<uintptr_t>(fused_interleaved_scales) % 4 == 0,
                "%s: payloads must be 16-byte, scales 2-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   cudaError_t e = cudaMemsetAsync(fused_interleaved_scales, 0, gemb_interleaved_scale_bytes(2 * intermediate, k), stream);
   if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
   const uint64_t work = 2 * intermediate * (k / 32);
@@ -1138,7 +1138,7 @@ int32_t gemb_nvfp4_gemm_gated_quant(const uint8_t* act, const uint8_t* act_scale
                    reinterpret_cast<uintptr_t>(product_packed) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(product_interleaved_scales) % 4 == 0,
                "%s: all buffers must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   GemmParams p{};
   p.sfa = act_scales_interleaved;
   p.sfb = w_scales_interleaved;
@@ -1172,7 +1172,7 @@ int32_t gemb_nvfp4_gemm_up_gated_quant(const uint8_t* act, const uint8_t* act_sc
                    reinterpret_cast<uintptr_t>(up_scales_interleaved) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(gate_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(product_packed) % 16 == 0,
                "%s: all buffers must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   GemmParams p{};
   p.sfa = act_scales_interleaved;
   p.sfb = up_scales_interleaved;
@@ -1207,7 +1207,7 @@ int32_t gemb_moe_grouped_gemm_gated_quant(const uint8_t* act, const uint8_t* act
                    reinterpret_cast<uintptr_t>(product_packed) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(product_interleaved_scales) % 4 == 0,
                "%s: all buffers must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   GemmParams p{};
   p.sfa = act_scales_interleaved;
   p.sfb = w_scales_interleaved;
@@ -1235,7 +1235,7 @@ int32_t gemb_fp8_gemm_bf16(const uint8_t* act, const float* act_scales, const ui
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(out) % 16 == 0,
                "%s: activation, weight and output must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   GemmParams p{};
   p.a_scales = act_scales;
   p.w_scales = w_scales_bf16;

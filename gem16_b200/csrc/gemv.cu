@@ -1144,7 +1144,7 @@ int32_t gemb_fp8_gemv(const uint8_t* act, const float* act_scale, const uint8_t*
   const char* op = "gemb_fp8_gemv";
   GEMB_REQUIRE(act_scale != nullptr, "%s: pointers must be nonnull", op);
   GEMB_TRY(validate_fp8_gemv(op, act, w, w_scales, out, rows, k));
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   Fp8Group grp{};
   grp.n = 1;
   grp.p[0] = {w, w_scales, out, rows};
@@ -1162,7 +1162,7 @@ int32_t gemb_fp8_gemv_qkv(const uint8_t* act, const float* act_scale, const uint
   GEMB_TRY(validate_fp8_gemv(op, act, k_w, k_s, k_out, k_rows, k));
   const bool has_v = v_w != nullptr || v_rows != 0;
   if (has_v) GEMB_TRY(validate_fp8_gemv(op, act, v_w, v_s, v_out, v_rows, k));
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   Fp8Group grp{};
   grp.n = has_v ? 3 : 2;
   grp.p[0] = {q_w, q_s, q_out, q_rows};
@@ -1179,7 +1179,7 @@ int32_t gemb_fp8_gemv_batch(const uint8_t* act, const float* act_scales, const u
   GEMB_REQUIRE(tokens >= 1 && tokens <= 8, "%s: between 1 and 8 tokens (larger batches go through gemb_fp8_gemm_bf16)", op);
   GEMB_REQUIRE(tokens * ((k + 511) / 512 * 512) * 2 <= 200 * 1024,
                "%s: tokens * K exceeds the shared-memory staging limit (102400 elements)", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   Fp8Group grp{};
   grp.n = 1;
   grp.p[0] = {w, w_scales, out, rows};
@@ -1201,7 +1201,7 @@ int32_t gemb_fp8_gemv_qkv_batch(const uint8_t* act, const float* act_scales, con
   GEMB_REQUIRE(tokens >= 1 && tokens <= 8, "%s: between 1 and 8 tokens", op);
   GEMB_REQUIRE(tokens * ((k + 511) / 512 * 512) * 2 <= 200 * 1024,
                "%s: tokens * K exceeds the shared-memory staging limit (102400 elements)", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   Fp8Group grp{};
   grp.n = has_v ? 3 : 2;
   grp.p[0] = {q_w, q_s, q_out, q_rows};
@@ -1220,7 +1220,7 @@ int32_t gemb_fp8_gemv_bf16in(const uint16_t* act_bf16, const uint8_t* w, const u
   const char* op = "gemb_fp8_gemv_bf16in";
   GEMB_TRY(validate_fp8_gemv(op, act_bf16, w, w_scales, out, rows, k));
   GEMB_REQUIRE(out_dtype == GEMB_F32 || out_dtype == GEMB_BF16, "%s: output dtype must be GEMB_F32 or GEMB_BF16", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   Fp8Group grp{};
   grp.n = 1;
   grp.p[0] = {w, w_scales, out, rows};
@@ -1237,7 +1237,7 @@ int32_t gemb_nvfp4_gemv(const uint8_t* act, const uint8_t* act_scales, const uin
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(w_scales) % 2 == 0,
                "%s: activation and weight must be 16-byte aligned, weight scales 2-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   return launch_nvfp4_gemv<false>(op, act, act_scales, w, w_scales, nullptr, nullptr, out, nullptr,
                                   nullptr, rows, k, ga * gw, 1.0f, stream);
 }
@@ -1254,7 +1254,7 @@ int32_t gemb_nvfp4_gemv_batch(const uint8_t* act, const uint8_t* act_scales, con
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(act) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(w_scales) % 2 == 0,
                "%s: activation and weight must be 16-byte aligned, weight scales 2-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const float div = ga * gw;
   switch (tokens) {
     case 1: return launch_nvfp4_gemv<false>(op, act, act_scales, w, w_scales, nullptr, nullptr, out, nullptr, nullptr, rows,
@@ -1285,7 +1285,7 @@ int32_t gemb_nvfp4_gemv_gate_up(const uint8_t* act, const uint8_t* act_scales, c
                    reinterpret_cast<uintptr_t>(up_w) % 16 == 0 && reinterpret_cast<uintptr_t>(gate_s) % 2 == 0 &&
                    reinterpret_cast<uintptr_t>(up_s) % 2 == 0,
                "%s: activation and weights must be 16-byte aligned, weight scales 2-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   return launch_nvfp4_gemv<true>(op, act, act_scales, gate_w, gate_s, up_w, up_s, gate_out, up_out,
                                  product, rows, k, gate_ga * gate_gw, up_ga * up_gw, stream);
 }

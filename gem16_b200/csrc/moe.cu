@@ -20,6 +20,10 @@ namespace gemb {
 // in-range value, never dereferenced; gemb_check_device_status() reports and clears the word.
 __device__ int g_moe_error = 0;
 
+// Benchmark hook (GEMB_TUNE_ROUTER_TILE): 0 = automatic, 1 = expert-per-thread kernels wherever they
+// apply, 8 / 16 / 32 = the tiled kernel with that many tokens per CTA.  All give the same bits.
+int g_router_tile = 0;
+
 int moe_take_device_error() {
   int code = 0;
   if (cudaMemcpyFromSymbol(&code, g_moe_error, sizeof code) != cudaSuccess) {
@@ -53,7 +57,7 @@ __global__ void __launch_bounds__(kRtThreads, 4)
 router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
                      const float* __restrict__ bias, float* __restrict__ logits, uint32_t tokens,
                      uint32_t hidden, uint32_t experts) {
-  constexpr int kPerThread = kTok / 4;  // tokens per thread: 8 or 2
+  constexpr int kPerThread = kTok / 4;  // tokens per thread: 8, 4 or 2
   __shared__ __align__(16) float xs[kRtK][32];
   __shared__ __align__(16) float ws[kRtK][kRtExp];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // experts tx*4.., tokens ty*kPerThread..
@@ -120,62 +124,48 @@ router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w
     __syncthreads();
     if (k0 + kRtK < hidden) load_tile(k0 + kRtK);
     const uint32_t kmax = min(static_cast<uint32_t>(kRtK), hidden - k0);
-    if (kmax == kRtK) {
-#pragma unroll
-      for (uint32_t k = 0; k < kRtK; ++k) {
+    // One k: four weights, kPerThread activations, kPerThread x 4 fma.  With four or eight tokens per
+    // thread two tokens share an instruction: the packed fp32 fma is one IEEE fma per half, so every
+    // chain keeps its order and rounding while the issue slots carry half the instructions.
+    auto step = [&](uint32_t k) {
       const float4 wv4 = *reinterpret_cast<const float4*>(&ws[k][(tx * 4) ^ (4 * (k >> 2))]);
       const float wv[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
-      float xv[kPerThread];
-      if constexpr (kPerThread == 8) {
-        // Two tokens per instruction: the packed fp32 fma (one IEEE fma per half, so every chain
-        // keeps its order and rounding) halves the instructions the issue slots have to carry.
-        const int col = (ty * 8) ^ (8 * ((k >> 3) & 3));
+      const int col = (ty * kPerThread) ^ (8 * ((k >> 3) & 3));
+      if constexpr (kPerThread >= 4) {
+        float2 xp[kPerThread / 2];
         const float4 xa = *reinterpret_cast<const float4*>(&xs[k][col]);
-        const float4 xb = *reinterpret_cast<const float4*>(&xs[k][col + 4]);
-        const float2 xp[4] = {make_float2(xa.x, xa.y), make_float2(xa.z, xa.w), make_float2(xb.x, xb.y), make_float2(xb.z, xb.w)};
+        xp[0] = make_float2(xa.x, xa.y);
+        xp[1] = make_float2(xa.z, xa.w);
+        if constexpr (kPerThread == 8) {
+          const float4 xb = *reinterpret_cast<const float4*>(&xs[k][col + 4]);
+          xp[2] = make_float2(xb.x, xb.y);
+          xp[3] = make_float2(xb.z, xb.w);
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 wp = make_float2(wv[j], wv[j]);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < kPerThread / 2; ++i) {
             const float2 r = __ffma2_rn(xp[i], wp, make_float2(acc[2 * i][j], acc[2 * i + 1][j]));
             acc[2 * i][j] = r.x;
             acc[2 * i + 1][j] = r.y;
           }
         }
-        continue;
       } else {
-        const int col = (ty * 2) ^ (8 * ((k >> 3) & 3));
         const float2 xa = *reinterpret_cast<const float2*>(&xs[k][col]);
-        xv[0] = xa.x; xv[1] = xa.y;
+        const float xv[2] = {xa.x, xa.y};
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
       }
+    };
+    if (kmax == kRtK) {
 #pragma unroll
-      for (int i = 0; i < kPerThread; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
-    }
+      for (uint32_t k = 0; k < kRtK; ++k) step(k);
     } else {
 #pragma unroll 4
-      for (uint32_t k = 0; k < kmax; ++k) {
-      const float4 wv4 = *reinterpret_cast<const float4*>(&ws[k][(tx * 4) ^ (4 * (k >> 2))]);
-      const float wv[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
-      float xv[kPerThread];
-      if constexpr (kPerThread == 8) {
-        const int col = (ty * 8) ^ (8 * ((k >> 3) & 3));
-        const float4 xa = *reinterpret_cast<const float4*>(&xs[k][col]);
-        const float4 xb = *reinterpret_cast<const float4*>(&xs[k][col + 4]);
-        xv[0] = xa.x; xv[1] = xa.y; xv[2] = xa.z; xv[3] = xa.w;
-        xv[4] = xb.x; xv[5] = xb.y; xv[6] = xb.z; xv[7] = xb.w;
-      } else {
-        const int col = (ty * 2) ^ (8 * ((k >> 3) & 3));
-        const float2 xa = *reinterpret_cast<const float2*>(&xs[k][col]);
-        xv[0] = xa.x; xv[1] = xa.y;
-      }
-#pragma unroll
-      for (int i = 0; i < kPerThread; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
-    }
+      for (uint32_t k = 0; k < kmax; ++k) step(k);
     }
     __syncthreads();
   }
@@ -776,11 +766,13 @@ int32_t gemb_moe_router_logits(const uint16_t* x_bf16, const float* router_weigh
   GEMB_REQUIRE(hidden > 0 && hidden % 4 == 0 && hidden < (1ull << 31), "%s: hidden must be a nonzero multiple of 4", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(x_bf16) % 8 == 0 && reinterpret_cast<uintptr_t>(router_weight) % 16 == 0,
                "%s: activations must be 8-byte and router weights 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
-  // Up to a couple of thousand tokens: one expert per thread, weight rows streamed from L2 (the
-  // tiled kernel would occupy a fraction of the SMs).  Its L2 traffic grows with the token count
-  // (one pass over the router weight per 2 * kTpt tokens), so large batches use the tiled kernel.
-  if (tokens <= 2048) {
+  GEMB_ENTER(op);
+  // Up to a thousand tokens: one expert per thread, weight rows streamed from L2 (the tiled kernel
+  // would occupy a fraction of the SMs).  Its L2 traffic grows with the token count (one pass over
+  // the router weight per 2 * kTpt tokens), so larger batches use the tiled kernel.  Measured on
+  // 2,816 x 128: 25 / 31 / 43 / 56 us at 64 / 256 / 512 / 1,024 tokens here, against 64 us for the
+  // tiled kernel; at 2,048 tokens 105 us against 72 us for the 16-token tile.
+  if ((tokens <= 1024 && g_router_tile == 0) || (tokens <= 2048 && g_router_tile == 1)) {
     if (tokens <= 256) {
       dim3 g(static_cast<unsigned>((tokens + 3) / 4), static_cast<unsigned>((experts + 31) / 32));
       GEMB_TRY(router_small_configure<2>(op));
@@ -802,15 +794,22 @@ int32_t gemb_moe_router_logits(const uint16_t* x_bf16, const float* router_weigh
     }
     return check_launch(op);
   }
-  // 8-token CTAs only while they do not outnumber the SMs; beyond that the 32-token tile does four
-  // times the arithmetic per shared-memory load.
-  const bool small = (tokens + 7) / 8 * ((experts + kRtExp - 1) / kRtExp) <= static_cast<uint64_t>(sm_count());
-  const unsigned tile = small ? 8 : 32;
+  // 8- and 16-token CTAs only while they do not outnumber the SMs; beyond that the 32-token tile does
+  // the most arithmetic per shared-memory load.
+  const uint64_t expert_tiles = (experts + kRtExp - 1) / kRtExp;
+  unsigned tile = 32;
+  if ((tokens + 7) / 8 * expert_tiles <= static_cast<uint64_t>(sm_count())) tile = 8;
+  else if ((tokens + 15) / 16 * expert_tiles <= static_cast<uint64_t>(sm_count())) tile = 16;
+  if (g_router_tile == 8 || g_router_tile == 16 || g_router_tile == 32) tile = static_cast<unsigned>(g_router_tile);
   dim3 grid(static_cast<unsigned>((tokens + tile - 1) / tile), static_cast<unsigned>((experts + kRtExp - 1) / kRtExp));
-  if (small)
+  if (tile == 8)
     router_logits_kernel<8><<<grid, kRtThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
                                                             static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
                                                             static_cast<uint32_t>(experts));
+  else if (tile == 16)
+    router_logits_kernel<16><<<grid, kRtThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
+                                                             static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
+                                                             static_cast<uint32_t>(experts));
   else
     router_logits_kernel<32><<<grid, kRtThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
                                                              static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
@@ -824,7 +823,7 @@ int32_t gemb_moe_route(const float* logits, const float* per_expert_scale, int32
   const char* op = "gemb_moe_route";
   GEMB_REQUIRE(logits && top_ids && top_weights, "%s: pointers must be nonnull", op);
   GEMB_TRY(validate_moe_geometry(op, tokens, experts, topk));
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   route_kernel<<<static_cast<unsigned>((tokens + 3) / 4), 128, 0, stream>>>(
       logits, per_expert_scale, top_ids, top_weights, probabilities, static_cast<uint32_t>(tokens),
       static_cast<uint32_t>(experts), static_cast<uint32_t>(topk));
@@ -850,7 +849,7 @@ int32_t gemb_moe_permute(const int32_t* top_ids, int32_t* counts, int32_t* offse
   GEMB_REQUIRE(workspace_bytes >= gemb_moe_permute_workspace_bytes(tokens, experts, topk),
                "%s: workspace too small (%llu bytes needed)", op,
                static_cast<unsigned long long>(gemb_moe_permute_workspace_bytes(tokens, experts, topk)));
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const uint32_t total = static_cast<uint32_t>(tokens * topk), e = static_cast<uint32_t>(experts);
   const uint32_t segments = static_cast<uint32_t>(moe_segments(tokens, topk));
   int32_t* block_counts = static_cast<int32_t*>(workspace);
@@ -917,7 +916,7 @@ int32_t gemb_moe_permute_static(const int32_t* top_ids, int32_t* counts, int32_t
                op, static_cast<unsigned long long>(tokens * topk), static_cast<unsigned long long>(experts),
                static_cast<unsigned long long>(kStaticMaxSegments * kSegment),
                static_cast<unsigned long long>(kStaticMaxExperts));
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   int32_t* block_counts = nullptr;
   GEMB_TRY(permute_scratch_address(op, &block_counts));
   const uint32_t total = static_cast<uint32_t>(tokens * topk), e = static_cast<uint32_t>(experts);
@@ -944,7 +943,7 @@ int32_t gemb_moe_dispatch_quantize(const uint16_t* x_bf16, const int32_t* slot_r
   GEMB_REQUIRE(positive_finite(global_divisor), "%s: global divisor must be positive and finite", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(x_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(packed_e2m1) % 8 == 0,
                "%s: input must be 16-byte and payload 8-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const uint32_t c_pad = static_cast<uint32_t>((hidden / 16 + 3) / 4 * 4);
   const unsigned threads = static_cast<unsigned>(std::min<uint64_t>(256, (hidden / 16 + 31) / 32 * 32));
   dispatch_quantize_kernel<<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
@@ -965,7 +964,7 @@ int32_t gemb_moe_gather_rows(const void* src, void* dst, const int32_t* index, u
   GEMB_REQUIRE(src_row_stride >= row_bytes && dst_row_stride >= row_bytes && src_row_stride % 16 == 0 &&
                    dst_row_stride % 16 == 0 && src_row_stride < (1ull << 30) && dst_row_stride < (1ull << 30),
                "%s: row strides must be multiples of 16 bytes no smaller than the row", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const uint32_t chunks = static_cast<uint32_t>(row_bytes / 16);
   gather_rows_kernel<<<static_cast<unsigned>((rows * chunks + 255) / 256), 256, 0, stream>>>(
       static_cast<const uint4*>(src), static_cast<uint4*>(dst), index, static_cast<uint32_t>(index_divisor), rows, chunks,
@@ -984,7 +983,7 @@ int32_t gemb_moe_scatter_quantized(const uint8_t* packed_rows, const uint8_t* co
                "%s: payload buffers must be 8-byte aligned", op);
   GEMB_REQUIRE(src_row_stride >= hidden / 2 && src_row_stride % 8 == 0 && src_row_stride < (1ull << 30),
                "%s: source row stride must be a multiple of 8 bytes no smaller than the payload row", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const uint32_t c_pad = static_cast<uint32_t>((hidden / 16 + 3) / 4 * 4);
   const uint64_t work = rows * (hidden / 16);
   scatter_quantized_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
@@ -1004,7 +1003,7 @@ int32_t gemb_moe_expert_gelu_quantize(const uint16_t* gate_up_bf16, const int32_
   GEMB_REQUIRE(positive_finite(global_divisor), "%s: global divisor must be positive and finite", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(gate_up_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(packed_e2m1) % 8 == 0,
                "%s: input must be 16-byte and payload 8-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const uint64_t work = rows_max * (intermediate / 16);
   const uint32_t c_pad = static_cast<uint32_t>((intermediate / 16 + 3) / 4 * 4);
   const uint64_t ctas = std::min<uint64_t>((work + 255) / 256, static_cast<uint64_t>(sm_count()) * 32);
@@ -1024,7 +1023,7 @@ int32_t gemb_moe_combine(const uint16_t* y_bf16, const int32_t* slot_rows, const
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(y_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(out_bf16) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(shared_bf16) % 16 == 0,
                "%s: buffers must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const uint64_t work = tokens * (hidden / 8);
   combine_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
       y_bf16, slot_rows, top_weights, shared_bf16, out_bf16, static_cast<uint32_t>(tokens),

@@ -56,6 +56,7 @@ uint64_t align256(uint64_t v) { return (v + 255) / 256 * 256; }
 
 }  // namespace
 
+extern int g_router_tile;
 int g_moe_stage_mask = 0;   // 0 = every stage
 bool moe_stage_on(int bit) { return g_moe_stage_mask == 0 || (g_moe_stage_mask & bit) != 0; }
 
@@ -63,6 +64,12 @@ int32_t moe_set_tuning(int32_t knob, int32_t value) {
   if (knob == GEMB_TUNE_MOE_STAGE_MASK) {
     GEMB_REQUIRE(value >= 0 && value < 256, "gemb_set_tuning: the stage mask has eight bits");
     g_moe_stage_mask = value;
+    return GEMB_OK;
+  }
+  if (knob == GEMB_TUNE_ROUTER_TILE) {
+    GEMB_REQUIRE(value == 0 || value == 1 || value == 8 || value == 16 || value == 32,
+                 "gemb_set_tuning: router tile must be 0 (auto), 1 (expert-per-thread kernels), 8, 16 or 32");
+    g_router_tile = value;
     return GEMB_OK;
   }
   return fail(GEMB_INVALID_ARGUMENT, "gemb_set_tuning: unknown knob %d", knob);
@@ -250,7 +257,7 @@ int32_t gemb_moe_router_input(const uint16_t* x_bf16, const uint16_t* scale_bf16
                "%s: hidden must be a nonzero multiple of 8", op);
   GEMB_REQUIRE(positive_finite(epsilon), "%s: epsilon must be positive and finite", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(x_bf16) % 16 == 0, "%s: input must be 16-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const float root = 1.0f / std::sqrt(static_cast<float>(hidden));
   router_input_kernel<<<static_cast<unsigned>((tokens + 127) / 128), 128, 0, stream>>>(
       x_bf16, scale_bf16, out_bf16, static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden), epsilon, root);
@@ -287,7 +294,7 @@ int32_t gemb_moe_layer_forward(const gemb_moe_layer_weights* w, const uint16_t* 
   LayerBuffers b;
   const uint64_t need = carve_layer(w, tokens, static_cast<uint8_t*>(workspace), &b);
   GEMB_REQUIRE(workspace_bytes >= need, "%s: workspace too small (%llu bytes needed)", op, static_cast<unsigned long long>(need));
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const bool shared = w->shared_intermediate != 0;
   const bool forked = shared && side_stream != nullptr && fork_event != nullptr && join_event != nullptr;
   struct Hint {

@@ -233,7 +233,7 @@ int32_t gemb_output_head_candidates(const uint16_t* weights_bf16, const float* h
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(weights_bf16) % 16 == 0 && reinterpret_cast<uintptr_t>(hidden_rows) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(candidates) % 8 == 0,
                "%s: weights and hidden must be 16-byte, candidates 8-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   Candidate* c = static_cast<Candidate*>(candidates);
   const uint32_t sc = static_cast<uint32_t>(suppressed_count), v = static_cast<uint32_t>(vocabulary),
                  h = static_cast<uint32_t>(hidden);
@@ -253,7 +253,7 @@ int32_t gemb_output_head_argmax(const void* candidates, uint64_t rows, uint32_t*
   const char* op = "gemb_output_head_argmax";
   GEMB_REQUIRE(candidates && selected, "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(rows >= 1 && rows <= kOhMaxRows, "%s: between 1 and %d rows", op, kOhMaxRows);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   output_head_argmax_kernel<<<static_cast<unsigned>(rows), kOhThreads, 0, stream>>>(static_cast<const Candidate*>(candidates), selected);
   return check_launch(op);
 }

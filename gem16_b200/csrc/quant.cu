@@ -350,7 +350,7 @@ int32_t gemb_nvfp4_interleave_scales(const uint8_t* compact, uint8_t* interleave
   GEMB_REQUIRE(compact && interleaved, "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(rows > 0 && k > 0 && k % 16 == 0, "%s: geometry must be nonzero with K a multiple of 16", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(interleaved) % 4 == 0, "%s: output must be 4-byte aligned", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const uint64_t rows_pad = (rows + 127) / 128 * 128, quads = (k / 16 + 3) / 4;
   const unsigned grid = static_cast<unsigned>((rows_pad * quads + 255) / 256);
   interleave_scales_kernel<<<grid, 256, 0, stream>>>(compact, interleaved, rows, k / 16, rows_pad, quads);
@@ -408,7 +408,7 @@ int32_t gemb_rmsnorm_residual(const void* input, int32_t input_dtype, const uint
   GEMB_REQUIRE(positive_finite(epsilon), "%s: epsilon must be positive and finite", op);
   GEMB_REQUIRE(residual_output_dtype == GEMB_F32 || (input_dtype == GEMB_BF16 && normalized_output == nullptr),
                "%s: bf16 residual and output go with a bf16 input and no separate normalised output", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   const unsigned grid = static_cast<unsigned>(vectors);
   if (residual_output_dtype == GEMB_BF16)
     rmsnorm_residual_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(input), weight_bf16,

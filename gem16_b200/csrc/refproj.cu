@@ -63,7 +63,7 @@ int32_t gemb_nvfp4_reference_projection(const uint8_t* a, const uint8_t* as, con
   GEMB_REQUIRE(tokens <= 65535, "%s: at most 65535 tokens per launch", op);
   GEMB_REQUIRE(positive_finite(ga) && positive_finite(gw) && std::isfinite(ga * gw),
                "%s: global divisors must be positive and finite", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   dim3 grid(static_cast<unsigned>((rows + 127) / 128), static_cast<unsigned>(tokens));
   nvfp4_reference_projection_kernel<<<grid, 128, 0, stream>>>(a, as, w, ws, out, tokens, rows, k, ga * gw);
   return check_launch(op);
@@ -76,7 +76,7 @@ int32_t gemb_fp8_reference_projection(const uint8_t* a, const float* as, const u
   GEMB_REQUIRE(a && as && w && ws && out, "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(tokens > 0 && rows > 0 && k > 0, "%s: geometry must be nonzero", op);
   GEMB_REQUIRE(tokens <= 65535, "%s: at most 65535 tokens per launch", op);
-  GEMB_TRY(require_sm100(op));
+  GEMB_ENTER(op);
   dim3 grid(static_cast<unsigned>((rows + 127) / 128), static_cast<unsigned>(tokens));
   fp8_reference_projection_kernel<<<grid, 128, 0, stream>>>(a, as, w, ws, out, tokens, rows, k);
   return check_launch(op);

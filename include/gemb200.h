@@ -88,7 +88,9 @@ int32_t gemb_device_check(void);
  * dispatch / pack, 2 grouped gate/up GEMM, 3 separate GELU requantisation, 4 grouped down GEMM, 5
  * combine, 6 shared branch, 7 flag barriers + position arithmetic + pull; 0 = all): with a subset
  * the call re-runs just those launches on what the previous full call left in the workspace, so a
- * benchmark can time one kernel of the sequence in place.  Results of a partial call are not a layer. */
+ * benchmark can time one kernel of the sequence in place.  Results of a partial call are not a layer;
+ * GEMB_TUNE_ROUTER_TILE = which router-logits kernel runs: 0 automatic, 1 the expert-per-thread kernels
+ * wherever they apply, 8 / 16 / 32 the tiled kernel with that many tokens per CTA (same bits from all). */
 enum {
   GEMB_TUNE_GEMV_ROWS = 1,
   GEMB_TUNE_GEMV_PDL = 2,
@@ -96,7 +98,8 @@ enum {
   GEMB_TUNE_GEMV_IMPL = 4,
   GEMB_TUNE_GEMM_PAIR = 5,
   GEMB_TUNE_EP_BARRIER_SPINS = 6,
-  GEMB_TUNE_MOE_STAGE_MASK = 7
+  GEMB_TUNE_MOE_STAGE_MASK = 7,
+  GEMB_TUNE_ROUTER_TILE = 8
 };
 int32_t gemb_set_tuning(int32_t knob, int32_t value);
 /* Bytes of an INTERLEAVED scale buffer for `rows` rows of K elements. */
@@ -618,6 +621,32 @@ typedef struct gemb_nvfp4_binding {
   const float* weight_divisors_device;  /* expert stack: fp32 [experts] */
   uint64_t experts;                     /* 0 = plain module, else the number of matrices in the stack */
 } gemb_nvfp4_binding;
+
+/* Checkpoint loader (load time, host side): opens a safetensors file, validates a module the way
+ * gem16's loader does and binds it into the caller's device arena in this library's layouts.
+ *   NVFP4 module `m`:  m.weight_packed U8 [rows, K/2] (or [experts, rows, K/2]), m.weight_scale F8_E4M3
+ *     [.., rows, K/16], m.weight_global_scale and m.input_global_scale F32 [1] (or [experts]): all four
+ *     required, exact dtypes and shapes, no NaN scale byte, positive finite divisors, K % 64 == 0,
+ *     rows % 8 == 0  (src/model/manifest.cpp:344-365, src/cuda/engine/target_model.cu:361-388).
+ *   FP8 module `m`:  m.weight F8_E4M3 [rows, K], m.weight_scale BF16 [rows, 1]  (manifest.cpp:366-372,
+ *     target_model.cu:345-358).
+ * rows / contracting_elements, when nonzero, must match the stored geometry (the reference binds with
+ * the geometry the model expects).  Failures: GEMB_NOT_FOUND (no such weight tensor), GEMB_DATA_LOSS
+ * (schema violations, as the reference reports them), GEMB_IO_ERROR, GEMB_UNSUPPORTED (unknown dtype).
+ * The arena piece (gemb_checkpoint_*_bytes, 256-byte aligned) receives, for NVFP4: payload, COMPACT
+ * scales, INTERLEAVED scales (per expert, back to back), the weight divisors and the input divisor as
+ * device floats; binding->weight_divisor / input_divisor hold the first (or only) values. */
+typedef struct gemb_checkpoint gemb_checkpoint;
+int32_t gemb_checkpoint_open(const char* path, gemb_checkpoint** checkpoint);
+void gemb_checkpoint_close(gemb_checkpoint* checkpoint);
+uint64_t gemb_checkpoint_nvfp4_bytes(const gemb_checkpoint* checkpoint, const char* module);
+int32_t gemb_checkpoint_bind_nvfp4(const gemb_checkpoint* checkpoint, const char* module, uint64_t rows,
+                                   uint64_t contracting_elements, void* device_arena, uint64_t arena_bytes,
+                                   gemb_nvfp4_binding* binding, gemb_stream_t stream);
+uint64_t gemb_checkpoint_fp8_bytes(const gemb_checkpoint* checkpoint, const char* module);
+int32_t gemb_checkpoint_bind_fp8(const gemb_checkpoint* checkpoint, const char* module, uint64_t rows,
+                                 uint64_t contracting_elements, void* device_arena, uint64_t arena_bytes,
+                                 gemb_fp8_binding* binding, gemb_stream_t stream);
 
 /* One mixture-of-experts layer (26B-A4B shape: router, `experts` gated FFNs of which each token
  * uses `topk`, one shared dense FFN).  gate_up / shared_gate_up hold the fused projection of

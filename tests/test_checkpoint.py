@@ -142,3 +142,118 @@ def test_expert_stack_and_fp8_module(tmp_path, lib, dev, orc):
     lib.gemb_fp8_gemv(torch.from_numpy(xq).to(dev), torch.from_numpy(xsc).to(dev), f.weight, f.scales_bf16, y, 40, 528, None)
     want = orc.fp8_matmul(xq, xsc, wq, orc.to_bf16(wsc))[0]
     assert np.linalg.norm(y.cpu().numpy() - want) <= 1e-6 * np.linalg.norm(want)
+
+
+# ---- the library's own loader (csrc/checkpoint.cu) against the same fixtures ---------------------
+def c_open(lib, path):
+    import ctypes as C
+    handle = C.c_void_p()
+    rc = lib.raw("gemb_checkpoint_open", path.encode(), C.addressof(handle))
+    return rc, handle
+
+
+def test_library_loader_rejects_what_the_reference_rejects(tmp_path, lib):
+    """No GPU needed: validation runs before anything touches the device.  Same edits as the Python
+    harness's test, and the status codes gem16 reports (kDataLoss for schema violations)."""
+    import ctypes as C
+    from gem16_b200.lib import STATUS_NAMES
+
+    def nvfp4_bytes(edit):
+        mod = fixture_module()
+        edit(mod)
+        path = str(tmp_path / "c.safetensors")
+        write_safetensors(path, mod)
+        rc, h = c_open(lib, path)
+        assert rc == 0, lib.last_error()
+        n = lib.cdll.gemb_checkpoint_nvfp4_bytes(h, b"m")
+        rc = lib.raw("gemb_checkpoint_bind_nvfp4", h, b"m", 0, 0, None, 0, None, None) if n == 0 else 0
+        lib.gemb_checkpoint_close(h)
+        return n, rc
+
+    n, _ = nvfp4_bytes(lambda m: None)
+    per = lib.cdll.gemb_interleaved_scale_bytes(8, 64)
+    assert n == 256 + 256 + (per + 255) // 256 * 256 + 256 + 256
+    for edit, want in ((lambda m: m.pop("m.weight_packed"), "kNotFound"),
+                       (lambda m: m.pop("m.weight_scale"), "kDataLoss"),
+                       (lambda m: m.pop("m.input_global_scale"), "kDataLoss"),
+                       (lambda m: m.__setitem__("m.weight_scale", ("U8", m["m.weight_scale"][1])), "kDataLoss"),
+                       (lambda m: m.__setitem__("m.weight_scale", ("F8_E4M3", m["m.weight_scale"][1][:, :3])), "kDataLoss"),
+                       (lambda m: m["m.weight_scale"][1].__setitem__((2, 1), 0xFF), "kDataLoss"),
+                       (lambda m: m.__setitem__("m.weight_global_scale", ("F32", np.array([0.0], np.float32))), "kDataLoss"),
+                       (lambda m: m.__setitem__("m.weight_global_scale", ("BF16", np.array([0x4300], np.uint16))), "kDataLoss"),
+                       (lambda m: m.__setitem__("m.input_global_scale", ("F32", np.array(1.0, np.float32))), "kDataLoss"),
+                       (lambda m: m.__setitem__("m.weight_packed", ("U8", m["m.weight_packed"][1][:, :24])), "kDataLoss")):
+        n, rc = nvfp4_bytes(edit)
+        assert n == 0 and STATUS_NAMES[rc] == want, (STATUS_NAMES[rc], lib.last_error())
+    # container errors
+    bad = str(tmp_path / "bad.safetensors")
+    open(bad, "wb").write(b"\x05\x00\x00")
+    assert STATUS_NAMES[c_open(lib, bad)[0]] == "kDataLoss"
+    assert STATUS_NAMES[c_open(lib, str(tmp_path / "absent.safetensors"))[0]] == "kIoError"
+    import json, struct
+    hdr = json.dumps({"t": {"dtype": "F32", "shape": [4], "data_offsets": [0, 8]}}).encode()
+    open(bad, "wb").write(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 8)
+    assert STATUS_NAMES[c_open(lib, bad)[0]] == "kDataLoss"
+
+
+@pytest.mark.gpu
+def test_library_loader_binds_like_the_harness(tmp_path, lib, dev, orc):
+    """gemb_checkpoint_bind_nvfp4 / _fp8: the bytes in the arena equal what the Python harness uploads
+    (payload, compact and interleaved scales, divisors), for a plain module, an expert stack and an
+    FP8 module; the binding then drives the decode GEMV on the pinned checkpoint-byte fixture."""
+    import ctypes as C
+    from gem16_b200.lib import Fp8Binding, Nvfp4Binding
+    rng = np.random.default_rng(5)
+    experts, rows, k = 3, 128, 128
+    packed = rng.integers(0, 256, (experts, rows, k // 2), dtype=np.uint8)
+    scale = rng.integers(0x30, 0x50, (experts, rows, k // 16), dtype=np.uint8)
+    wq, wsc = orc.fp8_quantize((rng.standard_normal((40, 528)) * 0.02).astype(np.float32))
+    mod = fixture_module()
+    mod.update({"x.weight_packed": ("U8", packed), "x.weight_scale": ("F8_E4M3", scale),
+                "x.weight_global_scale": ("F32", np.array([100.0, 200.0, 300.0], np.float32)),
+                "x.input_global_scale": ("F32", np.array([7.0, 8.0, 9.0], np.float32)),
+                "q.weight": ("F8_E4M3", wq), "q.weight_scale": ("BF16", orc.to_bf16(wsc).reshape(-1, 1))})
+    path = str(tmp_path / "l.safetensors")
+    write_safetensors(path, mod)
+    rc, h = c_open(lib, path)
+    assert rc == 0
+    st = SafetensorsFile(path)
+    for name in ("m", "x"):
+        want = load_nvfp4_linear(st, name, dev, lib)
+        n = lib.cdll.gemb_checkpoint_nvfp4_bytes(h, name.encode())
+        arena = torch.zeros((n,), dtype=torch.uint8, device=dev)
+        b = Nvfp4Binding()
+        lib.gemb_checkpoint_bind_nvfp4(h, name.encode(), want.rows, want.k, arena, n, b, None)
+        torch.cuda.synchronize()
+
+        def at(ptr, nbytes):
+            off = ptr - arena.data_ptr()
+            return arena[off:off + nbytes]
+
+        ne = max(want.experts, 1)
+        assert (b.rows, b.contracting, b.experts) == (want.rows, want.k, want.experts)
+        assert torch.equal(at(b.packed_weight, want.packed.numel()), want.packed.view(-1))
+        assert torch.equal(at(b.scales, want.compact_scales.numel()), want.compact_scales.view(-1))
+        assert torch.equal(at(b.scales_interleaved, want.interleaved_scales.numel()), want.interleaved_scales)
+        gw = at(b.weight_divisors_device, 4 * ne).view(torch.float32).tolist()
+        assert gw == (want.weight_divisor if want.experts else [want.weight_divisor])
+        assert b.weight_divisor == gw[0] and at(b.input_divisor_device, 4).view(torch.float32).item() == b.input_divisor
+        with pytest.raises(Exception):     # the geometry the model expects must match
+            lib.gemb_checkpoint_bind_nvfp4(h, name.encode(), want.rows + 8, want.k, arena, n, b, None)
+        if name == "m":                    # pinned bytes of the reference's fixture through the decode GEMV
+            act = np.zeros((1, 32), np.uint8)
+            act[0, 0] = 2                  # element 0 = 1.0
+            y = torch.zeros((8,), device=dev)
+            lib.gemb_nvfp4_gemv(torch.from_numpy(act[0]).to(dev), torch.full((4,), 0x38, dtype=torch.uint8, device=dev),
+                                b.packed_weight, b.scales, y, 8, 64, 1.0, b.weight_divisor, None)
+            assert abs(float(y[0]) - E2M1[FIXTURE_NIBBLES[0]] * FIXTURE_SCALE_VALUE / FIXTURE_DIVISOR) < 1e-9
+    n = lib.cdll.gemb_checkpoint_fp8_bytes(h, b"q")
+    arena = torch.zeros((n,), dtype=torch.uint8, device=dev)
+    f = Fp8Binding()
+    lib.gemb_checkpoint_bind_fp8(h, b"q", 40, 528, arena, n, f, None)
+    want = load_fp8_linear(st, "q", dev)
+    torch.cuda.synchronize()
+    assert torch.equal(arena[:40 * 528], want.weight.view(-1)) and (f.rows, f.contracting) == (40, 528)
+    off = f.scales - arena.data_ptr()
+    assert torch.equal(arena[off:off + 80].view(torch.int16), want.scales_bf16)
+    lib.gemb_checkpoint_close(h)
