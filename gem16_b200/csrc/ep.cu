@@ -173,26 +173,32 @@ ep_plan_body(const int32_t* counts_all, uint32_t ranks, uint32_t experts, uint32
       if (tile_rows != nullptr) tile_rows[tile] = real;
     }
   }
-  // Segments (source s, local expert e) in source-major order.
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (uint32_t s = 0; s < ranks; ++s) {
-      int src = 0;
-      for (uint32_t e2 = 0; e2 < me * el; ++e2) src += counts_all[s * experts + e2];
-      for (uint32_t e = 0; e < el; ++e) {
-        const uint32_t ge = me * el + e;
-        const uint32_t g = s * el + e;
-        int b = 0;
-        for (uint32_t s2 = 0; s2 < s; ++s2) b += counts_all[s2 * experts + ge];
-        recv_prefix[g] = run;
-        recv_src[g] = src;
-        recv_dst[g] = pad[ge] + b;
-        const int c = counts_all[s * experts + ge];
-        run += c;
-        src += c;
-      }
+  // Segments (source s, local expert e) in source-major order: one thread per source.
+  __shared__ int rows_from[kMaxRanks];
+  if (threadIdx.x < ranks) {
+    int n = 0;
+    for (uint32_t e = 0; e < el; ++e) n += counts_all[threadIdx.x * experts + me * el + e];
+    rows_from[threadIdx.x] = n;
+  }
+  __syncthreads();
+  if (threadIdx.x < ranks) {
+    const uint32_t s = threadIdx.x;
+    int run = 0, src = 0;
+    for (uint32_t s2 = 0; s2 < s; ++s2) run += rows_from[s2];
+    for (uint32_t e2 = 0; e2 < me * el; ++e2) src += counts_all[s * experts + e2];
+    for (uint32_t e = 0; e < el; ++e) {
+      const uint32_t ge = me * el + e;
+      const uint32_t g = s * el + e;
+      int b = 0;
+      for (uint32_t s2 = 0; s2 < s; ++s2) b += counts_all[s2 * experts + ge];
+      recv_prefix[g] = run;
+      recv_src[g] = src;
+      recv_dst[g] = pad[ge] + b;
+      const int c = counts_all[s * experts + ge];
+      run += c;
+      src += c;
     }
-    recv_prefix[ranks * el] = run;
+    if (s == ranks - 1) recv_prefix[ranks * el] = run;
   }
 }
 

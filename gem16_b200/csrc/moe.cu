@@ -562,6 +562,92 @@ permute_scatter_kernel(const int32_t* __restrict__ ids, const int32_t* __restric
   }
 }
 
+// The three steps above in ONE launch of one CTA, for batches of at most kSegment assignments (the
+// decode-size layer, where three launches cost more than the work): same records, same order.
+__global__ void __launch_bounds__(128)
+permute_small_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                     int32_t* __restrict__ plan, int32_t* __restrict__ perm, int32_t* __restrict__ slot_rows,
+                     uint32_t total, uint32_t experts, uint32_t max_tiles) {
+  extern __shared__ int sm[];
+  int* cnt = sm;                        // [experts]
+  int* off = cnt + experts;             // [experts + 1]
+  int* poff = off + experts + 1;        // [experts + 1]
+  int* loff = poff + experts + 1;       // [experts + 1]
+  int* warp_counts = loff + experts + 1;  // [4][experts]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (uint32_t i = threadIdx.x; i < 5 * experts; i += 128) (i < experts ? cnt[i] : warp_counts[i - experts]) = 0;
+  __syncthreads();
+  int my_ids[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint32_t i = warp * 256 + c * 32 + lane;
+    my_ids[c] = i < total ? __ldg(ids + i) : -1;
+    if (i < total && static_cast<uint32_t>(my_ids[c]) >= experts) {
+      atomicCAS(&g_moe_error, 0, 2);
+      my_ids[c] = static_cast<int>(experts) - 1;
+    }
+    if (my_ids[c] >= 0) {
+      atomicAdd(&cnt[my_ids[c]], 1);
+      atomicAdd(&warp_counts[warp * experts + my_ids[c]], 1);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, po = 0, lo = 0;
+    for (uint32_t e = 0; e < experts; ++e) {
+      off[e] = o;
+      poff[e] = po;
+      loff[e] = lo;
+      o += cnt[e];
+      po += (cnt[e] + kRowAlign - 1) / kRowAlign * kRowAlign;
+      lo += (cnt[e] + 127) / 128;
+    }
+    off[experts] = o;
+    poff[experts] = po;
+    plan[0] = po / 128;
+    plan[1] = po;
+    plan[3 + experts + max_tiles] = lo;
+  }
+  __syncthreads();
+  int32_t* tile_expert = plan + 3 + experts;
+  int32_t* live = plan + 3 + experts + max_tiles + 1;
+  for (uint32_t e = threadIdx.x; e <= experts; e += 128) {
+    offsets[e] = off[e];
+    plan[2 + e] = poff[e];
+    if (e == experts) break;
+    counts[e] = cnt[e];
+    for (int tile = poff[e] / 128, j = 0; tile < poff[e + 1] / 128; ++tile, ++j) {
+      const bool real = tile * 128 - poff[e] < cnt[e];
+      tile_expert[tile] = real ? static_cast<int32_t>(e) : -1;
+      if (real) live[loff[e] + j] = tile;
+    }
+    int run = 0;   // exclusive prefix of the expert over the four warps
+    for (int wq = 0; wq < 4; ++wq) {
+      const int c = warp_counts[wq * experts + e];
+      warp_counts[wq * experts + e] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  int* running = warp_counts + warp * experts;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int e = my_ids[c];
+    const unsigned active = __ballot_sync(0xFFFFFFFFu, e >= 0);
+    if (e >= 0) {
+      const unsigned peers = __match_any_sync(active, e);
+      const int rank = __popc(peers & ((1u << lane) - 1));
+      const int within = running[e] + rank;
+      const uint32_t i = warp * 256 + c * 32 + lane;
+      perm[off[e] + within] = static_cast<int32_t>(i);
+      slot_rows[i] = poff[e] + within;
+      __syncwarp(active);
+      if (rank == 0) running[e] += __popc(peers);
+    }
+    __syncwarp();
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Quantise each token's expert input to NVFP4 once and write it to the padded row of every one
 // of its topk assignments, block scales in the interleaved layout of the padded row space.
@@ -852,6 +938,11 @@ int32_t gemb_moe_permute(const int32_t* top_ids, int32_t* counts, int32_t* offse
   GEMB_ENTER(op);
   const uint32_t total = static_cast<uint32_t>(tokens * topk), e = static_cast<uint32_t>(experts);
   const uint32_t segments = static_cast<uint32_t>(moe_segments(tokens, topk));
+  if (segments == 1) {   // decode-size batch: count, scan and scatter in one launch
+    permute_small_kernel<<<1, 128, (8 * e + 3) * sizeof(int), stream>>>(
+        top_ids, counts, offsets, plan, perm, slot_rows, total, e, static_cast<uint32_t>(moe_max_tiles(tokens, experts, topk)));
+    return check_launch(op);
+  }
   int32_t* block_counts = static_cast<int32_t*>(workspace);
   permute_count_kernel<<<segments, 128, e * sizeof(int), stream>>>(top_ids, block_counts, total, e);
   GEMB_TRY(check_launch(op));
