@@ -106,7 +106,7 @@ ep_plan_body(const int32_t* counts_all, uint32_t ranks, uint32_t experts, uint32
       atomicCAS(&g_ep_error, 0, 6);
       plan[0] = 0;
       plan[1] = 0;
-      plan[3 + el + capacity_rows / 128] = 0;
+      plan[3 + el] = 0;
     }
     for (uint32_t e = threadIdx.x; e <= el; e += blockDim.x) plan[2 + e] = 0;
     for (uint32_t g = threadIdx.x; g <= ranks * el; g += blockDim.x) recv_prefix[g] = 0;
@@ -148,7 +148,7 @@ ep_plan_body(const int32_t* counts_all, uint32_t ranks, uint32_t experts, uint32
         live_off[e - d * el] = lo;
         lo += (tot[e] + 127) / 128;
       }
-      plan[3 + el + capacity_rows / 128] = lo;
+      plan[3 + el + 2 * (po / 128)] = lo;
     }
   } else if (threadIdx.x == ranks) {
     int po = 0;
@@ -160,16 +160,15 @@ ep_plan_body(const int32_t* counts_all, uint32_t ranks, uint32_t experts, uint32
   __syncthreads();
   for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x)
     out_base[e] = pad[e] + before_me[e] - my_pad[e];
-  int32_t* tile_expert = plan + 2 + el + 1;
-  int32_t* live = plan + 3 + el + capacity_rows / 128 + 1;
+  int32_t* info = plan + 3 + el;   // pairs {expert of tile i, i-th tile with real rows}, then the number of those
   for (uint32_t e = threadIdx.x; e < el; e += blockDim.x) {
     const uint32_t ge = me * el + e;
     plan[2 + e] = pad[ge];
     const int end = pad[ge] + (tot[ge] + 255) / 256 * 256;
     for (int tile = pad[ge] / 128, j = 0; tile < end / 128; ++tile, ++j) {
       const int real = max(0, min(128, tot[ge] - (tile * 128 - pad[ge])));
-      tile_expert[tile] = real > 0 ? static_cast<int32_t>(e) : -1;   // -1: padding only
-      if (real > 0) live[live_off[e] + j] = tile;
+      info[2 * tile] = real > 0 ? static_cast<int32_t>(e) : -1;   // -1: padding only
+      if (real > 0) info[2 * (live_off[e] + j) + 1] = tile;
       if (tile_rows != nullptr) tile_rows[tile] = real;
     }
   }

@@ -191,11 +191,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   // Grouped mode: experts are padded to 256 rows, so a 128-row tile may hold padding only.  A single
   // CTA walks the plan's list of tiles that hold real rows; a pair walks all 256-row units (the even
   // tile of a unit is always real) and takes the expert from the even tile.
-  const int32_t* live_tiles = (p.plan && !kPair) ? p.plan + 3 + p.experts + p.m / BM + 1 : nullptr;
-  const uint32_t m_tiles = p.plan ? min(static_cast<uint32_t>(__ldg(kPair ? p.plan : p.plan + 3 + p.experts + p.m / BM)), p.m / BM)
+  // plan entries behind the expert offsets: {expert of tile i (-1: padding only), i-th tile that holds real rows},
+  // then, behind the last tile's pair, the number of tiles that hold real rows.
+  const int32_t* tile_info = p.plan ? p.plan + 3 + p.experts : nullptr;
+  const uint32_t plan_tiles = p.plan ? min(static_cast<uint32_t>(__ldg(p.plan)), p.m / BM) : 0u;
+  const uint32_t m_tiles = p.plan ? (kPair ? plan_tiles : min(static_cast<uint32_t>(__ldg(tile_info + 2 * plan_tiles)), plan_tiles))
                                   : (p.m + BM - 1) / BM;
   const uint32_t n_tiles = (p.n + BN - 1) / BN;
-  const int32_t* tile_expert = p.plan ? p.plan + 3 + p.experts : nullptr;
+  const int32_t* tile_expert = tile_info;   // stride 2
   // A work unit is one 128-row token tile, or for pairs two consecutive ones (rank picks which).
   const uint32_t m_units = kPair ? (m_tiles + 1) / 2 : m_tiles;
   const uint32_t num_tiles = m_units * n_tiles;
@@ -205,7 +208,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t k_stages = (p.k + C::kKPerStage - 1) / C::kKPerStage;
   const uint32_t k_groups_pad = (p.k / 16 + 3) / 4;  // 512-byte scale chunks per 128-row group
   auto tile_expert_of = [&](uint32_t mt) -> int32_t {
-    return __ldg(tile_expert + (kPair ? (mt & ~1u) : mt));
+    return __ldg(tile_expert + 2 * (kPair ? (mt & ~1u) : mt));
   };
 
   // Tile order: groups of 16 token tiles; inside a group the token tile runs fastest, so the
@@ -219,7 +222,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const uint32_t within = tile % per_group;
     mt = first_m + within % gm;
     if constexpr (kPair) mt = mt * 2 + rank;
-    else if (live_tiles != nullptr) mt = min(static_cast<uint32_t>(__ldg(live_tiles + mt)), p.m / BM - 1);
+    else if (tile_info != nullptr) mt = min(static_cast<uint32_t>(__ldg(tile_info + 2 * mt + 1)), p.m / BM - 1);
     nt = within / gm;
   };
   // Completion of the MMAs issued so far, signalled to the same barrier of both CTAs of a pair.
@@ -478,7 +481,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       uint32_t mt, nt;
       tile_coords(tile, mt, nt);
       // In a pair the odd CTA may own a padding-only tile: it takes part in the barriers, nothing else.
-      const bool dead = kPair && tile_expert != nullptr && (mt >= p.m / BM || __ldg(tile_expert + mt) < 0);
+      const bool dead = kPair && tile_expert != nullptr && (mt >= p.m / BM || __ldg(tile_expert + 2 * mt) < 0);
       // The staging buffer must be free again (the previous tile's last store has read it); checked
       // here, while the tile is still being computed, rather than after the accumulator is full.
       if (lane == 0) ptx::bulk_wait_group_read<0>();

@@ -457,10 +457,9 @@ permute_count_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ bloc
     block_counts[static_cast<uint64_t>(blockIdx.x) * experts + e] = smem_counts[e];
 }
 
-// plan layout (int32), T = the most 128-row tiles the padded row space can hold:
-// [0] number of 128-row tiles, [1] padded rows in total, [2 .. 2+E] padded offset of every expert
-// (+ the end), [3+E .. 3+E+T) tile_expert[tile] (-1: padding only), [3+E+T] number of tiles that hold
-// real rows, then their tile indices in ascending order (what a single-CTA grouped GEMM walks).
+// plan layout (int32): [0] number T of 128-row tiles, [1] padded rows in total, [2 .. 2+E] padded
+// offset of every expert (+ the end), then T pairs {expert of tile i (-1: padding only), i-th tile
+// that holds real rows (what a single-CTA grouped GEMM walks)}, then the number of such tiles.
 __global__ void __launch_bounds__(256)
 permute_scan_kernel(int32_t* __restrict__ block_counts, int32_t* __restrict__ counts,
                     int32_t* __restrict__ offsets, int32_t* __restrict__ plan, uint32_t segments,
@@ -495,20 +494,19 @@ permute_scan_kernel(int32_t* __restrict__ block_counts, int32_t* __restrict__ co
     poff[experts] = po;
     plan[0] = po / 128;
     plan[1] = po;
-    plan[3 + experts + max_tiles] = lo;
+    plan[3 + experts + 2 * (po / 128)] = lo;
   }
   __syncthreads();
   for (uint32_t e = threadIdx.x; e <= experts; e += blockDim.x) {
     offsets[e] = off[e];
     plan[2 + e] = poff[e];
   }
-  int32_t* tile_expert = plan + 2 + experts + 1;
-  int32_t* live = plan + 3 + experts + max_tiles + 1;
+  int32_t* info = plan + 3 + experts;
   for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x)
     for (int tile = poff[e] / 128, j = 0; tile < poff[e + 1] / 128; ++tile, ++j) {
       const bool real = tile * 128 - poff[e] < cnt[e];
-      tile_expert[tile] = real ? static_cast<int32_t>(e) : -1;
-      if (real) live[loff[e] + j] = tile;
+      info[2 * tile] = real ? static_cast<int32_t>(e) : -1;
+      if (real) info[2 * (loff[e] + j) + 1] = tile;
     }
 }
 
@@ -606,11 +604,10 @@ permute_small_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ coun
     poff[experts] = po;
     plan[0] = po / 128;
     plan[1] = po;
-    plan[3 + experts + max_tiles] = lo;
+    plan[3 + experts + 2 * (po / 128)] = lo;
   }
   __syncthreads();
-  int32_t* tile_expert = plan + 3 + experts;
-  int32_t* live = plan + 3 + experts + max_tiles + 1;
+  int32_t* info = plan + 3 + experts;
   for (uint32_t e = threadIdx.x; e <= experts; e += 128) {
     offsets[e] = off[e];
     plan[2 + e] = poff[e];
@@ -618,8 +615,8 @@ permute_small_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ coun
     counts[e] = cnt[e];
     for (int tile = poff[e] / 128, j = 0; tile < poff[e + 1] / 128; ++tile, ++j) {
       const bool real = tile * 128 - poff[e] < cnt[e];
-      tile_expert[tile] = real ? static_cast<int32_t>(e) : -1;
-      if (real) live[loff[e] + j] = tile;
+      info[2 * tile] = real ? static_cast<int32_t>(e) : -1;
+      if (real) info[2 * (loff[e] + j) + 1] = tile;
     }
     int run = 0;   // exclusive prefix of the expert over the four warps
     for (int wq = 0; wq < 4; ++wq) {

@@ -385,7 +385,7 @@ int32_t gemb_moe_route(const float* logits, const float* per_expert_scale, int32
                        uint64_t topk, gemb_stream_t stream);
 
 /* Sizes for gemb_moe_permute: scratch bytes, int32 entries of `plan`, and the upper bound of
- * padded rows (every expert's rows start on a multiple of 128) that dispatch / grouped GEMM /
+ * padded rows (every expert's rows start on a multiple of 256) that dispatch / grouped GEMM /
  * combine buffers must hold. */
 uint64_t gemb_moe_permute_workspace_bytes(uint64_t tokens, uint64_t experts, uint64_t topk);
 uint64_t gemb_moe_plan_ints(uint64_t tokens, uint64_t experts, uint64_t topk);
@@ -395,8 +395,11 @@ uint64_t gemb_moe_padded_rows_max(uint64_t tokens, uint64_t experts, uint64_t to
  * assignments (assignment i = token * topk + slot; inside an expert i ascends).
  *   counts[experts], offsets[experts + 1], perm[tokens * topk] (perm[pos] = i)   -- the spec's
  *   records;  slot_rows[i] = row of assignment i in the padded per-expert row space;
- *   plan = {tiles, padded rows, padded_offsets[experts + 1], tile_expert[tiles]} consumed on
- *   the device by the grouped GEMM (no host readback).  1 <= experts <= 1024, topk <= 32.
+ *   plan = {tiles, padded rows, padded_offsets[experts + 1], tiles x {expert of the tile or -1 for a
+ *   tile of padding only, i-th tile that holds real rows}, number of tiles that hold real rows},
+ *   consumed on the device by the grouped GEMM (no host readback).  Every expert's rows start on a
+ *   multiple of 256, so a 128-row tile and the 256-row tile of a CTA pair never mix experts.
+ *   1 <= experts <= 1024, topk <= 32.
  * docs/plans/gemma4-26b/specs/MOE_PREFILL_KERNEL_SPEC.md:19-58. */
 int32_t gemb_moe_permute(const int32_t* top_ids, int32_t* counts, int32_t* offsets, int32_t* perm,
                          int32_t* slot_rows, int32_t* plan, void* workspace, uint64_t workspace_bytes,

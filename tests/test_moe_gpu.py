@@ -102,17 +102,16 @@ def check_permute(lib, dev, orc, ids, experts):
     padded = np.concatenate([[0], np.cumsum((oc + 255) // 256 * 256)])
     assert plan[0] == padded[-1] // 128 and plan[1] == padded[-1]
     assert np.array_equal(plan[2:2 + experts + 1], padded)
-    tile_expert = plan[3 + experts:3 + experts + plan[0]]
+    info = plan[3 + experts:3 + experts + 2 * plan[0] + 1]       # pairs {expert of tile i, i-th real tile}, then their number
+    tile_expert = info[0:2 * plan[0]:2]
     want_tiles = []
     for e in range(experts):
         real = (oc[e] + 127) // 128
         want_tiles += [e] * real + [-1] * ((oc[e] + 255) // 256 * 2 - real)
     assert np.array_equal(tile_expert, np.array(want_tiles, np.int32))
-    # the list of tiles that hold real rows, behind the tile_expert array of full capacity
-    cap_tiles = c.gemb_moe_padded_rows_max(t, experts, k) // 128
-    live_n = plan[3 + experts + cap_tiles]
+    live_n = info[2 * plan[0]]
     assert live_n == ((oc + 127) // 128).sum()
-    assert np.array_equal(plan[4 + experts + cap_tiles:4 + experts + cap_tiles + live_n], np.nonzero(np.array(want_tiles) >= 0)[0])
+    assert np.array_equal(info[1:2 * live_n:2], np.nonzero(np.array(want_tiles) >= 0)[0])
     # slot_rows: assignment perm[offsets[e] + j] sits at padded row padded[e] + j
     want_rows = np.empty(t * k, np.int32)
     for e in range(experts):

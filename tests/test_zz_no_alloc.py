@@ -34,7 +34,7 @@ def run(lib, dev, ids, experts, static):
         lib.gemb_moe_permute(d_ids, counts, offsets, perm, rows, plan, ws, ws.numel(), t, experts, k, None)
     torch.cuda.synchronize()
     tiles = int(plan[0].item())
-    return [counts.cpu(), offsets.cpu(), perm.cpu(), rows.cpu(), plan[: 3 + experts + tiles].cpu()]
+    return [counts.cpu(), offsets.cpu(), perm.cpu(), rows.cpu(), plan[: 3 + experts + 2 * tiles + 1].cpu()]
 
 
 def test_static_scratch_matches_workspace_variant_twice_in_a_row(lib, dev):
