@@ -68,13 +68,24 @@ struct PeerPtrs {
 };
 
 // One CTA.  counts_all: [ranks][experts].  tile_rows (optional): real rows of every 128-row tile.
+constexpr uint32_t kPlanSmemCounts = 4096;
 __device__ __forceinline__ void
-ep_plan_body(const int32_t* counts_all, uint32_t ranks, uint32_t experts, uint32_t me,
+ep_plan_body(const int32_t* counts_all_global, uint32_t ranks, uint32_t experts, uint32_t me,
              int32_t* __restrict__ plan, int32_t* __restrict__ recv_prefix, int32_t* __restrict__ recv_src,
              int32_t* __restrict__ recv_dst, int32_t* __restrict__ out_base, uint32_t capacity_rows,
              uint32_t send_rows, int32_t* __restrict__ tile_rows) {
+  const int32_t* counts_all = counts_all_global;
   extern __shared__ int sm[];
   const uint32_t el = experts / ranks;
+  // A single thread walking global memory waits for every load in turn (about a quarter of a
+  // microsecond each); the serial prefix sums below therefore work on a shared-memory copy of the
+  // counts whenever it fits (ranks * experts <= 4,096, which covers 16 ranks x 256 experts).
+  if (ranks * experts <= kPlanSmemCounts) {
+    int* copy = sm + 5 * experts;
+    for (uint32_t i = threadIdx.x; i < ranks * experts; i += blockDim.x) copy[i] = counts_all_global[i];
+    __syncthreads();
+    counts_all = copy;
+  }
   // Counts that cannot be (negative, more than a rank can send, or more padded rows than the
   // buffers hold -- e.g. read after a barrier gave up, while a peer was still writing them) give
   // an empty plan: no tile, no segment, every combine base out of range (the combine skips those).
@@ -548,7 +559,7 @@ int32_t gemb_moe_ep_plan(const int32_t* counts_all, uint64_t ranks, uint64_t exp
                    send_rows_per_rank > 0 && send_rows_per_rank < (1ull << 31),
                "%s: buffer capacities must be nonzero (padded rows a multiple of 128)", op);
   GEMB_ENTER(op);
-  ep_plan_kernel<<<1, 256, 5 * experts * sizeof(int), stream>>>(
+  ep_plan_kernel<<<1, 256, (5 * experts + (ranks * experts <= kPlanSmemCounts ? ranks * experts : 0)) * sizeof(int), stream>>>(
       counts_all, static_cast<uint32_t>(ranks), static_cast<uint32_t>(experts), static_cast<uint32_t>(rank), plan,
       recv_prefix, recv_src_rows, recv_dst_rows, combine_row_base, static_cast<uint32_t>(capacity_rows),
       static_cast<uint32_t>(send_rows_per_rank), nullptr);
@@ -780,7 +791,7 @@ int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const 
   const uint32_t e = static_cast<uint32_t>(w->experts), el = static_cast<uint32_t>(b.el);
   const uint64_t h = w->hidden, i = w->intermediate, n = tokens * w->topk;
   if (moe_stage_on(kStageExchange)) {
-  ep_sync_plan_kernel<<<1, 256, 5 * e * sizeof(int), stream>>>(
+  ep_sync_plan_kernel<<<1, 256, (5 * e + (ranks * e <= kPlanSmemCounts ? ranks * e : 0)) * sizeof(int), stream>>>(
       call.flags, call.counts, ranks, e, me, comm->local_epochs, static_cast<uint32_t>(g_ep_barrier_spins), barriers ? 1 : 0,
       barriers ? 1 : 0, b.counts_all, b.plan, b.recv_prefix, b.recv_src, b.recv_dst, b.row_base,
       static_cast<uint32_t>(b.rows_max), static_cast<uint32_t>(n), b.tile_rows);

@@ -471,10 +471,18 @@ permute_scan_kernel(int32_t* __restrict__ block_counts, int32_t* __restrict__ co
   int* loff = poff + experts + 1; // [experts + 1] first entry of the expert in the list of real tiles
   for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
     int run = 0;
-    for (uint32_t b = 0; b < segments; ++b) {
-      const int c = block_counts[static_cast<uint64_t>(b) * experts + e];
-      block_counts[static_cast<uint64_t>(b) * experts + e] = run;  // exclusive prefix over segments
-      run += c;
+    // eight loads in flight at a time: a thread that consumes each count before it asks for the
+    // next one waits a full memory round trip per segment
+    for (uint32_t b0 = 0; b0 < segments; b0 += 8) {
+      int c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        c[j] = b0 + j < segments ? block_counts[static_cast<uint64_t>(b0 + j) * experts + e] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (b0 + j < segments) block_counts[static_cast<uint64_t>(b0 + j) * experts + e] = run;  // exclusive prefix over segments
+        run += c[j];
+      }
     }
     cnt[e] = run;
     counts[e] = run;
