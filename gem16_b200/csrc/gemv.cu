@@ -9,6 +9,7 @@
 // once: algorithmic bytes per output row are K (FP8) or K/2 + K/16 (NVFP4) plus the scale and
 // the 4-byte result; the activation (K bytes or less) is re-read per CTA from L2.
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -23,6 +24,7 @@ constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 
 int g_rows_override = 0;  // 0 = automatic; set through gemb_set_tuning(GEMB_TUNE_GEMV_ROWS, n)
+int g_gemv_impl = 0;  // single token: 0 = bulk-copy ring when it fits, 1 = direct global loads; batch: 1 = SIMT form
 int g_pdl = 1;            // programmatic dependent launch; gemb_set_tuning(GEMB_TUNE_GEMV_PDL, 0/1)
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
@@ -477,8 +479,167 @@ int32_t launch_fp8_gemv_batch_variant(const char* op, const uint8_t* act, const 
   return check_launch(op);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Small-batch FP8 GEMV on the warp-level tensor-core path (mma.sync m16n8k32, E4M3 x E4M3 -> fp32):
+// 2..8 tokens share one pass over the weights at the streaming rate of the single-token kernel.
+// With more than two or three tokens the SIMT form above is bound by its dot-product arithmetic
+// (one mixed fma per token and weight); here a warp takes 16 weight rows as the M side of the MMA
+// (row-major weights are the "row" A operand as they lie in memory) and the tokens as its N = 8
+// columns, so the arithmetic is one MMA per 16 rows x 32 k whatever the token count.
+//
+// Fragment mapping (lane = 4 g + t): the lane loads 16 contiguous bytes of rows g and g + 8 at k
+// offset 16 t of a 64-byte span -- four lanes cover 64 contiguous bytes of a row, eight rows per
+// load instruction.  Those 2 x 16 bytes feed two MMAs: MMA j takes bytes [8 j, 8 j + 4) of each
+// load as a0 / a1 and bytes [8 j + 4, 8 j + 8) as a2 / a3.  That permutes k inside the span
+// relative to the instruction's canonical order, which is harmless as long as the B operand uses
+// the same permutation: b0 / b1 of the lane are the 8 activation bytes of token g at the same k
+// offset (16 t + 8 j), one 8-byte shared-memory load.  Accumulators c0 / c1 belong to row g and
+// tokens 2 t, 2 t + 1, c2 / c3 to row g + 8.  The result differs from the single-token kernel's
+// only in the order of the fp32 additions.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_e4m3_m16n8k32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                   uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int kMmaSpans = 4;   // 64-byte spans per step: eight 16-byte loads in flight per lane
+
+__global__ void __launch_bounds__(kWarps * 32, 3)
+fp8_gemv_mma_kernel(const uint8_t* __restrict__ act, const float* __restrict__ act_scales,
+                    const __grid_constant__ Fp8Group grp, uint64_t k, uint32_t tokens) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  const uint64_t xs_stride = (k + 63) / 64 * 64 + 16;   // bytes per token row in shared memory (+16: spreads the banks)
+  const uint64_t total_rows = grp.row_start[grp.n];
+  const uint64_t num_tasks = (total_rows + 15) / 16;
+  const uint64_t task_stride = static_cast<uint64_t>(gridDim.x) * kWarps;
+  auto row_pointer = [&](uint64_t vrow) -> const uint8_t* {
+    if (vrow >= total_rows) vrow = total_rows - 1;
+    int pi = 0;
+    while (pi + 1 < grp.n && vrow >= grp.row_start[pi + 1]) ++pi;
+    return grp.p[pi].w + (vrow - grp.row_start[pi]) * k;
+  };
+  uint4 wa[kMmaSpans], wb[kMmaSpans];
+  auto load_step = [&](const uint8_t* ra, const uint8_t* rb, uint64_t kb) {
+#pragma unroll
+    for (int u = 0; u < kMmaSpans; ++u) {
+      const uint64_t off = kb + u * 64 + t4 * 16;
+      const bool in = off < k;
+      wa[u] = in ? ldg_stream(ra + off) : make_uint4(0, 0, 0, 0);
+      wb[u] = in ? ldg_stream(rb + off) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  asm volatile("griddepcontrol.launch_dependents;");
+  uint64_t task = static_cast<uint64_t>(blockIdx.x) * kWarps + warp;
+  const uint8_t* ra = nullptr;
+  const uint8_t* rb = nullptr;
+  bool prefetched = false;
+  if (task < num_tasks) {
+    ra = row_pointer(task * 16 + g);
+    rb = row_pointer(task * 16 + g + 8);
+    load_step(ra, rb, 0);
+    prefetched = true;
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // the activations as raw E4M3 bytes, one padded row per token, zero rows up to eight tokens
+  for (uint64_t i = threadIdx.x; i < 8 * (xs_stride / 16); i += kWarps * 32) {
+    const uint64_t tok = i / (xs_stride / 16), c = (i % (xs_stride / 16)) * 16;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tok < tokens && c < k) v = __ldg(reinterpret_cast<const uint4*>(act + tok * k + c));
+    *reinterpret_cast<uint4*>(smem_raw + tok * xs_stride + c) = v;
+  }
+  __syncthreads();
+  const unsigned char* xg = smem_raw + g * xs_stride + t4 * 16;
+  const float s0 = 2 * t4 < static_cast<int>(tokens) ? __ldg(act_scales + 2 * t4) : 0.0f;
+  const float s1 = 2 * t4 + 1 < static_cast<int>(tokens) ? __ldg(act_scales + 2 * t4 + 1) : 0.0f;
+  for (; task < num_tasks; task += task_stride) {
+    if (!prefetched) {
+      ra = row_pointer(task * 16 + g);
+      rb = row_pointer(task * 16 + g + 8);
+    }
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (uint64_t kb = 0; kb < k; kb += kMmaSpans * 64) {
+      if (!prefetched) load_step(ra, rb, kb);
+      prefetched = false;
+#pragma unroll
+      for (int u = 0; u < kMmaSpans; ++u) {
+        if (kb + u * 64 < k) {   // warp-uniform; lanes past K hold zero weights
+          const uint4 xv = *reinterpret_cast<const uint4*>(xg + kb + u * 64);
+          mma_e4m3_m16n8k32(acc, wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);
+          mma_e4m3_m16n8k32(acc, wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);
+        }
+      }
+    }
+    // (acc * a_scale) * w_scale, in that order: src/cuda/fp8/sm120.cu:234-239.
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const uint64_t vrow = task * 16 + g + 8 * half;
+      if (vrow >= total_rows) continue;
+      int pi = 0;
+      while (pi + 1 < grp.n && vrow >= grp.row_start[pi + 1]) ++pi;
+      const uint64_t row = vrow - grp.row_start[pi];
+      const float ws = bf16_bits_to_float(__ldg(grp.p[pi].w_scales + row));
+      float* out = static_cast<float*>(grp.p[pi].out);
+      if (2 * t4 < static_cast<int>(tokens)) out[static_cast<uint64_t>(2 * t4) * grp.p[pi].rows + row] = __fmul_rn(__fmul_rn(acc[2 * half], s0), ws);
+      if (2 * t4 + 1 < static_cast<int>(tokens))
+        out[static_cast<uint64_t>(2 * t4 + 1) * grp.p[pi].rows + row] = __fmul_rn(__fmul_rn(acc[2 * half + 1], s1), ws);
+    }
+  }
+}
+
+int32_t launch_fp8_gemv_mma(const char* op, const uint8_t* act, const float* act_scales, const Fp8Group& grp,
+                            uint64_t tokens, uint64_t k, cudaStream_t stream) {
+  const size_t smem = 8 * ((k + 63) / 64 * 64 + 16);
+  static std::mutex configure_mutex;
+  static int resident[64] = {0};
+  static size_t resident_smem[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  int occ;
+  {
+    std::lock_guard<std::mutex> lock(configure_mutex);
+    if (resident[dev] == 0 || smem != resident_smem[dev]) {
+      if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(fp8_gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
+      }
+      int o = 0;
+      cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, fp8_gemv_mma_kernel, kWarps * 32, smem);
+      if (e != cudaSuccess || o < 1) return fail(GEMB_INTERNAL, "%s: occupancy query failed: %s", op, cudaGetErrorName(e));
+      resident[dev] = o;
+      resident_smem[dev] = smem;
+    }
+    occ = resident[dev];
+  }
+  const uint64_t tasks = (grp.row_start[grp.n] + 15) / 16;
+  const uint64_t wave = static_cast<uint64_t>(sm_count()) * occ;
+  const unsigned blocks = static_cast<unsigned>(std::min<uint64_t>((tasks + kWarps - 1) / kWarps, wave));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(kWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, fp8_gemv_mma_kernel, act, act_scales, grp, k, static_cast<uint32_t>(tokens));
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(le), cudaGetErrorString(le));
+  }
+  return check_launch(op);
+}
+
 int32_t launch_fp8_gemv_batch(const char* op, const uint8_t* act, const float* act_scales, const Fp8Group& grp,
                               uint64_t tokens, uint64_t k, cudaStream_t stream) {
+  // Tensor-core form by default; GEMB_TUNE_GEMV_IMPL = 1 keeps the SIMT form, whose per-token results
+  // are bit-identical to the single-token kernel.
+  if (g_gemv_impl != 1) return launch_fp8_gemv_mma(op, act, act_scales, grp, tokens, k, stream);
   switch (tokens) {
     case 2: return launch_fp8_gemv_batch_variant<2>(op, act, act_scales, grp, k, stream);
     case 3: return launch_fp8_gemv_batch_variant<3>(op, act, act_scales, grp, k, stream);
@@ -695,8 +856,6 @@ fp8_gemv_ring_kernel(const void* __restrict__ act, const float* __restrict__ act
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
   }
 }
-
-int g_gemv_impl = 0;  // 0 = bulk-copy ring when it fits, 1 = direct global loads
 
 template <bool kFusedQuant, bool kBf16Out>
 int32_t launch_fp8_gemv_ring(const char* op, const void* act, const float* act_scale, const Fp8Group& grp,

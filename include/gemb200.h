@@ -78,7 +78,8 @@ int32_t gemb_device_check(void);
  * programmatic stream serialization so a GEMV's weight prefetch overlaps the tail of the kernel
  * before it (1, default) or not (0); GEMB_TUNE_GEMM_BN = output-feature width of a prefill GEMM
  * tile, 0 (automatic), 128 or 256; GEMB_TUNE_GEMV_IMPL = FP8 decode GEMV data path, 0 (automatic),
- * 1 (direct global loads) or 2 (bulk-copy ring through shared memory wherever it fits);
+ * 1 (direct global loads; also selects the SIMT form of the FP8 small-batch GEMVs, whose per-token
+ * results are bit-identical to gemb_fp8_gemv) or 2 (bulk-copy ring through shared memory wherever it fits);
  * GEMB_TUNE_GEMM_PAIR = dense prefill GEMMs on CTA pairs (two SMs share one 256 x 256 tile and
  * each stages half of the weight tile), 0 (automatic), 1 (never) or 2 (always, when the tile is 256 wide);
  * GEMB_TUNE_EP_BARRIER_SPINS = how many times gemb_moe_ep_barrier polls its flags before it gives
@@ -199,8 +200,12 @@ int32_t gemb_fp8_gemv_qkv(const uint8_t* activation_e4m3fn, const float* activat
 
 /* Small-batch forms for the speculative-decoding verifier (second row of the path's "next" list):
  * 1..8 tokens share one pass over the weights.  activation [tokens, K] E4M3, activation_scales
- * [tokens], output fp32 [tokens, rows] (per projection for the grouped form).  Per token the result
- * is bit-identical to gemb_fp8_gemv on that token.  tokens * K (K padded to 512) <= 102,400.
+ * [tokens], output fp32 [tokens, rows] (per projection for the grouped form).  With two or more
+ * tokens the dot products run on the warp-level tensor-core path (mma.sync m16n8k32, E4M3 x E4M3 ->
+ * fp32, the instruction the reference's batch kernel issues, src/cuda/fp8/sm120.cu:101): exact where
+ * every partial sum is representable (the reference's fixture, tests/cuda/nvfp4_reference_test.cu:1131),
+ * else within the single-token budget of the binary64 value but not bit-identical to gemb_fp8_gemv,
+ * since the order of the fp32 additions differs.  tokens * K (K padded to 512) <= 102,400.
  * Replace LaunchFp8Sm120DirectProjectionBatch and LaunchFp8Sm120GroupedQkvProjectionBatch
  * (src/cuda/fp8/sm120.h:45-79) for tokens <= 8; larger batches are prefill and belong to
  * gemb_fp8_gemm_bf16. */

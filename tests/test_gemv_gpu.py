@@ -156,11 +156,12 @@ def test_fused_quantisation_at_rounding_boundaries(lib, dev, orc):
     assert torch.equal(y_plain, y_fused)
 
 
-@pytest.mark.parametrize("tokens,rows,k", [(2, 40, 528), (3, 8192, 3840), (5, 3840, 15360), (8, 1000, 4096), (7, 13, 16)])
+@pytest.mark.parametrize("tokens,rows,k", [(2, 40, 528), (3, 8192, 3840), (5, 3840, 15360), (8, 1000, 4096), (7, 13, 16),
+                                           (4, 3841, 2816), (6, 30720, 3840)])
 def test_fp8_gemv_small_batch(lib, dev, orc, tokens, rows, k):
-    """The verifier-sized batch (src/cuda/fp8/sm120.h:45-55): one pass over the weights for all tokens,
-    every token bit-identical to the single-token GEMV on it, and within the GEMV budget of the
-    binary64 oracle."""
+    """The verifier-sized batch (src/cuda/fp8/sm120.h:45-55): one pass over the weights for all tokens on
+    the warp-level tensor-core path, within the GEMV budget of the binary64 oracle; the SIMT form behind
+    the tuning knob stays bit-identical per token to the single-token GEMV."""
     rng = np.random.default_rng(tokens * 1000 + rows)
     x = bf16_round(rng.standard_normal((tokens, k)).astype(np.float32) * np.arange(1, tokens + 1, dtype=np.float32)[:, None])
     w = (rng.standard_normal((rows, k)) * 0.02).astype(np.float32)
@@ -172,11 +173,42 @@ def test_fp8_gemv_small_batch(lib, dev, orc, tokens, rows, k):
     xd, sd, wd, wsd = to_dev(xq, dev), to_dev(xsc, dev), to_dev(wq, dev), to_dev(wsb, dev)
     lib.gemb_fp8_gemv_batch(xd, sd, wd, wsd, out, tokens, rows, k, None)
     got = to_np(out)
-    assert rel_fro(got, want) < 1e-6
+    assert rel_fro(got, want) < 1e-6, rel_fro(got, want)
+    assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+    lib.gemb_set_tuning(4, 1)           # GEMB_TUNE_GEMV_IMPL: the SIMT form
+    try:
+        simt = torch.full((tokens, rows), float("nan"), device=dev)
+        lib.gemb_fp8_gemv_batch(xd, sd, wd, wsd, simt, tokens, rows, k, None)
+        for t in range(tokens):
+            one = torch.zeros((rows,), device=dev)
+            lib.gemb_fp8_gemv(xd[t], sd[t:t + 1], wd, wsd, one, rows, k, None)
+            assert np.array_equal(to_np(one), to_np(simt[t])), t
+    finally:
+        lib.gemb_set_tuning(4, 0)
+    assert rel_fro(to_np(simt), want) < 1e-6
+
+
+def test_fp8_gemv_small_batch_is_exact_on_representable_sums(lib, dev):
+    """The reference holds its tensor-core batch kernel to equality with its scalar one on values whose
+    partial sums are all representable (tests/cuda/nvfp4_reference_test.cu:1131-1140; seven E4M3 codes of
+    magnitude 0.5 .. 2 and power-of-two scales).  The same here: both forms and the single-token kernel
+    return the same bits."""
+    codes = np.array([0x00, 0x30, 0x38, 0x40, 0xB0, 0xB8, 0xC0], np.uint8)
+    tokens, rows, k = 8, 1030, 3840
+    idx = np.arange(tokens * k, dtype=np.int64)
+    x = codes[(idx * 5 + idx // k) % 7].reshape(tokens, k)
+    idx = np.arange(rows * k, dtype=np.int64)
+    w = codes[(idx * 3 + idx // k) % 7].reshape(rows, k)
+    xs = np.array([0.125, 0.25, 0.5, 1.0], np.float32)[np.arange(tokens) % 4]
+    ws = np.array([0x3E00, 0x3E80, 0x3F00, 0x3F80], np.uint16)[np.arange(rows) % 4]
+    xd, sd, wd, wsd = (to_dev(a, dev) for a in (x, xs, w, ws))
+    mma = torch.zeros((tokens, rows), device=dev)
+    lib.gemb_fp8_gemv_batch(xd, sd, wd, wsd, mma, tokens, rows, k, None)
     for t in range(tokens):
         one = torch.zeros((rows,), device=dev)
         lib.gemb_fp8_gemv(xd[t], sd[t:t + 1], wd, wsd, one, rows, k, None)
-        assert np.array_equal(to_np(one), got[t]), t
+        assert torch.equal(one, mma[t]), t
+    assert float(mma.abs().max()) > 0
 
 
 def test_fp8_gemv_small_batch_grouped_and_limits(lib, dev, orc):
