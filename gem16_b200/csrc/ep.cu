@@ -893,11 +893,17 @@ int32_t gemb_moe_ep_layer_forward(const gemb_moe_layer_weights* w, const gemb_mo
   GEMB_TRY(prepare_ep(op, w, comm, tokens, workspace, workspace_bytes, &call));
   GEMB_REQUIRE(x != nullptr && out != nullptr, "%s: input and output must be nonnull", op);
   const bool shared = w->shared_intermediate != 0;
-  const bool forked = shared && side_stream != nullptr && fork_event != nullptr && join_event != nullptr;
-  if (forked) GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));
-  if (shared && moe_stage_on(kStageShared)) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, forked ? side_stream : stream));
+  // Small batches: the shared branch on the side stream from the start.  Large ones: in line, behind the
+  // pushing down GEMM, so that it runs while the slower ranks' rows are still arriving and only then
+  // does this rank wait at the second barrier.
+  const bool forked = shared && side_stream != nullptr && fork_event != nullptr && join_event != nullptr && fork_pays(tokens);
+  if (forked) {
+    GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));
+    if (moe_stage_on(kStageShared)) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, side_stream));
+  }
   GEMB_TRY(ep_stage_send(op, w, comm, call, x, tokens, stream));
   GEMB_TRY(ep_stage_experts(op, w, comm, call, tokens, true, stream));
+  if (shared && !forked && moe_stage_on(kStageShared)) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, stream));
   if (forked) GEMB_TRY(stream_join(op, stream, side_stream, join_event));
   return ep_stage_combine(op, w, comm, call, out, tokens, true, stream);
 }

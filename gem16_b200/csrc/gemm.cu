@@ -122,8 +122,7 @@ struct Cfg {
   static constexpr int kSfColsPerStage = kFp4 ? kSfaCols + kSfbCols : 0;
   static_assert(kAccCols + kStages * kSfColsPerStage <= 512, "TMEM budget exceeded");
   static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
-  static_assert(!kPair || BN == 256, "CTA pairs compute 256 x 256 tiles");
-  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget exceeded");
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget exceeded");
 };
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -811,7 +810,7 @@ int32_t make_out_map_f32(const char* op, CUtensorMap* map, void* base, uint64_t 
 int g_gemm_bn = 0;    // 0 = automatic; gemb_set_tuning(GEMB_TUNE_GEMM_BN, 128 | 256)
 int g_gemm_pair = 0;  // 0 = automatic (pairs for the dense 256-wide tile), 1 = never, 2 = always
 
-bool use_pairs() { return g_gemm_pair != 1 && (g_gemm_bn == 0 || g_gemm_bn == 256); }
+bool use_pairs() { return g_gemm_pair != 1 && (g_gemm_bn == 0 || g_gemm_bn == 256 || g_gemm_pair == 2); }
 
 // Grouped calls run on CTA pairs when the experts are expected to hold a couple of 128-row tiles
 // each (a pair shares one weight tile between two SMs, which is what the grouped GEMM is short of:
@@ -891,6 +890,34 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
   return check_launch(op);
 }
 
+// NVFP4 tile variants.  256 x 256 pair tiles hold one accumulator (256 TMEM columns plus the scale regions
+// fill the 512); 256 x 128 pair tiles hold two, so a tile's epilogue runs under the next tile's MMAs, at
+// the operand traffic per flop of the single-CTA 128 x 256 tile.
+//
+// Automatic choice: 256 wide, except where that leaves SMs without a tile or the tiles are too coarse to
+// balance -- a dense call with fewer 256-wide tiles than SMs (decode-size batches of the shared branch: 23 us
+// instead of 29), and the grouped gate/up GEMM with the GELU epilogue up to 16,384 announced assignments
+// (its 1,408 interleaved columns are 5.5 tiles of 256 but 11 of 128: 37 us instead of 41 at 64 tokens,
+// 89 instead of 92 at 2,048; from 4,096 tokens on the wide tile wins).
+int32_t launch_fp4(const char* op, const void* act, const void* w, const GemmParams& p, bool pairs, cudaStream_t stream) {
+  int bn = g_gemm_bn;
+  if (bn == 0) {
+    bool narrow;
+    if (p.plan != nullptr)
+      narrow = p.gated && g_grouped_rows_hint != 0 && g_grouped_rows_hint <= 16384;
+    else
+      narrow = static_cast<uint64_t>((p.m + BM - 1) / BM) * ((p.n + 255) / 256) < static_cast<uint64_t>(sm_count());
+    bn = narrow ? 128 : 256;
+    if (narrow) pairs = false;
+  }
+  if (bn == 128) {
+    if (pairs) return launch_gemm<true, 128, 5, 2, true>(op, act, w, p, stream);
+    return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
+  }
+  if (pairs) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
+  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
+}
+
 int32_t validate_gemm(const char* op, uint64_t tokens, uint64_t rows, uint64_t k, uint64_t k_multiple) {
   GEMB_REQUIRE(tokens > 0 && rows > 0 && k > 0, "%s: geometry must be nonzero", op);
   GEMB_REQUIRE(k % k_multiple == 0, "%s: contracting extent must be a multiple of %llu", op,
@@ -947,10 +974,7 @@ int32_t gemb_nvfp4_gemm_bf16(const uint8_t* act, const uint8_t* act_scales_inter
   p.n = static_cast<uint32_t>(rows);
   p.k = static_cast<uint32_t>(k);
   p.alpha = 1.0f / (ga * gw);  // one multiply in the epilogue, as src/cuda/nvfp4/cutlass_sm120.cu:551-552
-  const int bn = g_gemm_bn ? g_gemm_bn : 256;  // 256 measured fastest; 128 stays selectable
-  if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
-  if (use_pairs()) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
-  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
+  return launch_fp4(op, act, w, p, use_pairs(), stream);
 }
 
 int32_t gemb_nvfp4_gemm_f32(const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* w,
@@ -976,10 +1000,7 @@ int32_t gemb_nvfp4_gemm_f32(const uint8_t* act, const uint8_t* act_scales_interl
   p.n = static_cast<uint32_t>(rows);
   p.k = static_cast<uint32_t>(k);
   p.alpha = 1.0f / (ga * gw);
-  const int bn = g_gemm_bn ? g_gemm_bn : 256;
-  if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
-  if (use_pairs()) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
-  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
+  return launch_fp4(op, act, w, p, use_pairs(), stream);
 }
 
 int32_t gemb_moe_grouped_gemm_bf16(const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* w,
@@ -1012,10 +1033,7 @@ int32_t gemb_moe_grouped_gemm_bf16(const uint8_t* act, const uint8_t* act_scales
   p.ga = ga;
   p.experts = static_cast<uint32_t>(experts);
   p.alpha = 1.0f;
-  const int bn = g_gemm_bn ? g_gemm_bn : 256;
-  if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
-  if (grouped_pairs(padded_rows_max, experts)) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
-  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
+  return launch_fp4(op, act, w, p, grouped_pairs(padded_rows_max, experts), stream);
 }
 
 // Grouped down projection whose epilogue stores every real row at its destination in one of
@@ -1057,10 +1075,7 @@ int32_t grouped_gemm_push(const char* op, const uint8_t* act, const uint8_t* act
   }
   p.out = reinterpret_cast<uint16_t*>(dst_host[rank]);   // describes the (unused) tensor-map store target
   p.m_out = static_cast<uint32_t>(dst_rows);
-  const int bn = g_gemm_bn ? g_gemm_bn : 256;
-  if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
-  if (grouped_pairs(padded_rows_max, experts)) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
-  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
+  return launch_fp4(op, act, w, p, grouped_pairs(padded_rows_max, experts), stream);
 }
 }  // namespace gemb
 extern "C" {
@@ -1116,10 +1131,7 @@ extern "C" int32_t gemb_nvfp4_pack_gate_up(const uint8_t* gate_packed, const uin
 }
 
 static int32_t launch_gated(const char* op, const uint8_t* act, const uint8_t* w, GemmParams& p, cudaStream_t stream) {
-  const int bn = g_gemm_bn ? g_gemm_bn : 256;
-  if (bn == 128) return launch_gemm<true, 128, 5, 2>(op, act, w, p, stream);
-  if (p.plan ? grouped_pairs(p.m, p.experts) : use_pairs()) return launch_gemm<true, 256, 5, 1, true>(op, act, w, p, stream);
-  return launch_gemm<true, 256, 3, 1>(op, act, w, p, stream);
+  return launch_fp4(op, act, w, p, p.plan ? grouped_pairs(p.m, p.experts) : use_pairs(), stream);
 }
 
 int32_t gemb_nvfp4_gemm_gated_quant(const uint8_t* act, const uint8_t* act_scales_interleaved, const uint8_t* w_fused,

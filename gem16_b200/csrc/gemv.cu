@@ -483,19 +483,24 @@ int32_t launch_fp8_gemv_batch_variant(const char* op, const uint8_t* act, const 
 // Small-batch FP8 GEMV on the warp-level tensor-core path (mma.sync m16n8k32, E4M3 x E4M3 -> fp32):
 // 2..8 tokens share one pass over the weights at the streaming rate of the single-token kernel.
 // With more than two or three tokens the SIMT form above is bound by its dot-product arithmetic
-// (one mixed fma per token and weight); here a warp takes 16 weight rows as the M side of the MMA
-// (row-major weights are the "row" A operand as they lie in memory) and the tokens as its N = 8
-// columns, so the arithmetic is one MMA per 16 rows x 32 k whatever the token count.
+// (one mixed fma per token and weight); here the weights are the M side of the MMA (row-major
+// weights are the "row" A operand as they lie in memory) and the tokens its N = 8 columns, so the
+// arithmetic is one MMA per 16 rows x 32 k whatever the token count.
+//
+// A CTA takes 16 weight rows; its eight warps split K in 256-byte spans, round robin, and their
+// partial sums meet in shared memory in warp order.  That keeps every warp of the GPU loading even
+// when a projection has few rows (3,840 rows are 240 CTAs), which a warp-per-16-rows split does not.
 //
 // Fragment mapping (lane = 4 g + t): the lane loads 16 contiguous bytes of rows g and g + 8 at k
-// offset 16 t of a 64-byte span -- four lanes cover 64 contiguous bytes of a row, eight rows per
+// offset 16 t of a 64-byte piece -- four lanes cover 64 contiguous bytes of a row, eight rows per
 // load instruction.  Those 2 x 16 bytes feed two MMAs: MMA j takes bytes [8 j, 8 j + 4) of each
-// load as a0 / a1 and bytes [8 j + 4, 8 j + 8) as a2 / a3.  That permutes k inside the span
+// load as a0 / a1 and bytes [8 j + 4, 8 j + 8) as a2 / a3.  That permutes k inside the piece
 // relative to the instruction's canonical order, which is harmless as long as the B operand uses
 // the same permutation: b0 / b1 of the lane are the 8 activation bytes of token g at the same k
-// offset (16 t + 8 j), one 8-byte shared-memory load.  Accumulators c0 / c1 belong to row g and
-// tokens 2 t, 2 t + 1, c2 / c3 to row g + 8.  The result differs from the single-token kernel's
-// only in the order of the fp32 additions.
+// offset (16 t + 8 j), half of one 16-byte load of the token's row (the activations, at most 8 x K
+// bytes, stay in L1; the weights stream past it).  Accumulators c0 / c1 belong to row g and tokens
+// 2 t, 2 t + 1, c2 / c3 to row g + 8.  The result differs from the single-token kernel's only in the
+// order of the fp32 additions.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mma_e4m3_m16n8k32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                    uint32_t b0, uint32_t b1) {
@@ -504,27 +509,26 @@ __device__ __forceinline__ void mma_e4m3_m16n8k32(float (&c)[4], uint32_t a0, ui
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-constexpr int kMmaSpans = 4;   // 64-byte spans per step: eight 16-byte loads in flight per lane
+constexpr int kMmaPieces = 4;                  // 64-byte pieces per span: eight 16-byte weight loads in flight per lane
+constexpr int kMmaSpan = kMmaPieces * 64;      // bytes of K one warp takes per step
 
 __global__ void __launch_bounds__(kWarps * 32, 3)
 fp8_gemv_mma_kernel(const uint8_t* __restrict__ act, const float* __restrict__ act_scales,
                     const __grid_constant__ Fp8Group grp, uint64_t k, uint32_t tokens) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float4 partial[kWarps][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
-  const uint64_t xs_stride = (k + 63) / 64 * 64 + 16;   // bytes per token row in shared memory (+16: spreads the banks)
   const uint64_t total_rows = grp.row_start[grp.n];
   const uint64_t num_tasks = (total_rows + 15) / 16;
-  const uint64_t task_stride = static_cast<uint64_t>(gridDim.x) * kWarps;
   auto row_pointer = [&](uint64_t vrow) -> const uint8_t* {
     if (vrow >= total_rows) vrow = total_rows - 1;
     int pi = 0;
     while (pi + 1 < grp.n && vrow >= grp.row_start[pi + 1]) ++pi;
     return grp.p[pi].w + (vrow - grp.row_start[pi]) * k;
   };
-  uint4 wa[kMmaSpans], wb[kMmaSpans];
-  auto load_step = [&](const uint8_t* ra, const uint8_t* rb, uint64_t kb) {
+  uint4 wa[kMmaPieces], wb[kMmaPieces];
+  auto load_span = [&](const uint8_t* ra, const uint8_t* rb, uint64_t kb) {
 #pragma unroll
-    for (int u = 0; u < kMmaSpans; ++u) {
+    for (int u = 0; u < kMmaPieces; ++u) {
       const uint64_t off = kb + u * 64 + t4 * 16;
       const bool in = off < k;
       wa[u] = in ? ldg_stream(ra + off) : make_uint4(0, 0, 0, 0);
@@ -532,95 +536,81 @@ fp8_gemv_mma_kernel(const uint8_t* __restrict__ act, const float* __restrict__ a
     }
   };
   asm volatile("griddepcontrol.launch_dependents;");
-  uint64_t task = static_cast<uint64_t>(blockIdx.x) * kWarps + warp;
+  uint64_t task = blockIdx.x;
+  const uint64_t first_kb = static_cast<uint64_t>(warp) * kMmaSpan;
   const uint8_t* ra = nullptr;
   const uint8_t* rb = nullptr;
   bool prefetched = false;
-  if (task < num_tasks) {
+  if (task < num_tasks && first_kb < k) {   // the weights do not depend on the kernel before this one
     ra = row_pointer(task * 16 + g);
     rb = row_pointer(task * 16 + g + 8);
-    load_step(ra, rb, 0);
+    load_span(ra, rb, first_kb);
     prefetched = true;
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  // the activations as raw E4M3 bytes, one padded row per token, zero rows up to eight tokens
-  for (uint64_t i = threadIdx.x; i < 8 * (xs_stride / 16); i += kWarps * 32) {
-    const uint64_t tok = i / (xs_stride / 16), c = (i % (xs_stride / 16)) * 16;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (tok < tokens && c < k) v = __ldg(reinterpret_cast<const uint4*>(act + tok * k + c));
-    *reinterpret_cast<uint4*>(smem_raw + tok * xs_stride + c) = v;
-  }
-  __syncthreads();
-  const unsigned char* xg = smem_raw + g * xs_stride + t4 * 16;
+  const bool token_live = static_cast<uint32_t>(g) < tokens;   // B column g = token g; columns past the batch are zero
+  const uint8_t* xrow = act + static_cast<uint64_t>(token_live ? g : 0) * k + t4 * 16;
   const float s0 = 2 * t4 < static_cast<int>(tokens) ? __ldg(act_scales + 2 * t4) : 0.0f;
   const float s1 = 2 * t4 + 1 < static_cast<int>(tokens) ? __ldg(act_scales + 2 * t4 + 1) : 0.0f;
-  for (; task < num_tasks; task += task_stride) {
+  for (; task < num_tasks; task += gridDim.x) {
     if (!prefetched) {
       ra = row_pointer(task * 16 + g);
       rb = row_pointer(task * 16 + g + 8);
     }
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (uint64_t kb = 0; kb < k; kb += kMmaSpans * 64) {
-      if (!prefetched) load_step(ra, rb, kb);
+    for (uint64_t kb = first_kb; kb < k; kb += static_cast<uint64_t>(kWarps) * kMmaSpan) {
+      if (!prefetched) load_span(ra, rb, kb);
       prefetched = false;
 #pragma unroll
-      for (int u = 0; u < kMmaSpans; ++u) {
-        if (kb + u * 64 < k) {   // warp-uniform; lanes past K hold zero weights
-          const uint4 xv = *reinterpret_cast<const uint4*>(xg + kb + u * 64);
+      for (int u = 0; u < kMmaPieces; ++u) {
+        if (kb + u * 64 < k) {   // warp-uniform; K is a multiple of 16, lanes past it hold zero weights
+          uint4 xv = make_uint4(0, 0, 0, 0);
+          if (token_live && kb + u * 64 + t4 * 16 < k) xv = __ldg(reinterpret_cast<const uint4*>(xrow + kb + u * 64));
           mma_e4m3_m16n8k32(acc, wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);
           mma_e4m3_m16n8k32(acc, wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);
         }
       }
     }
-    // (acc * a_scale) * w_scale, in that order: src/cuda/fp8/sm120.cu:234-239.
+    __syncthreads();   // the previous task's sums have been read
+    partial[warp][lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncthreads();
+    if (warp == 0) {
+      float4 sum = partial[0][lane];
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const uint64_t vrow = task * 16 + g + 8 * half;
-      if (vrow >= total_rows) continue;
-      int pi = 0;
-      while (pi + 1 < grp.n && vrow >= grp.row_start[pi + 1]) ++pi;
-      const uint64_t row = vrow - grp.row_start[pi];
-      const float ws = bf16_bits_to_float(__ldg(grp.p[pi].w_scales + row));
-      float* out = static_cast<float*>(grp.p[pi].out);
-      if (2 * t4 < static_cast<int>(tokens)) out[static_cast<uint64_t>(2 * t4) * grp.p[pi].rows + row] = __fmul_rn(__fmul_rn(acc[2 * half], s0), ws);
-      if (2 * t4 + 1 < static_cast<int>(tokens))
-        out[static_cast<uint64_t>(2 * t4 + 1) * grp.p[pi].rows + row] = __fmul_rn(__fmul_rn(acc[2 * half + 1], s1), ws);
+      for (int w = 1; w < kWarps; ++w) {   // warp order: the same sum on every launch
+        const float4 v = partial[w][lane];
+        sum.x = __fadd_rn(sum.x, v.x);
+        sum.y = __fadd_rn(sum.y, v.y);
+        sum.z = __fadd_rn(sum.z, v.z);
+        sum.w = __fadd_rn(sum.w, v.w);
+      }
+      // (acc * a_scale) * w_scale, in that order: src/cuda/fp8/sm120.cu:234-239.
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const uint64_t vrow = task * 16 + g + 8 * half;
+        if (vrow >= total_rows) continue;
+        int pi = 0;
+        while (pi + 1 < grp.n && vrow >= grp.row_start[pi + 1]) ++pi;
+        const uint64_t row = vrow - grp.row_start[pi];
+        const float ws = bf16_bits_to_float(__ldg(grp.p[pi].w_scales + row));
+        float* out = static_cast<float*>(grp.p[pi].out);
+        const float c0 = half ? sum.z : sum.x, c1 = half ? sum.w : sum.y;
+        if (2 * t4 < static_cast<int>(tokens)) out[static_cast<uint64_t>(2 * t4) * grp.p[pi].rows + row] = __fmul_rn(__fmul_rn(c0, s0), ws);
+        if (2 * t4 + 1 < static_cast<int>(tokens))
+          out[static_cast<uint64_t>(2 * t4 + 1) * grp.p[pi].rows + row] = __fmul_rn(__fmul_rn(c1, s1), ws);
+      }
     }
   }
 }
 
 int32_t launch_fp8_gemv_mma(const char* op, const uint8_t* act, const float* act_scales, const Fp8Group& grp,
                             uint64_t tokens, uint64_t k, cudaStream_t stream) {
-  const size_t smem = 8 * ((k + 63) / 64 * 64 + 16);
-  static std::mutex configure_mutex;
-  static int resident[64] = {0};
-  static size_t resident_smem[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  dev &= 63;
-  int occ;
-  {
-    std::lock_guard<std::mutex> lock(configure_mutex);
-    if (resident[dev] == 0 || smem != resident_smem[dev]) {
-      if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(fp8_gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
-      }
-      int o = 0;
-      cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, fp8_gemv_mma_kernel, kWarps * 32, smem);
-      if (e != cudaSuccess || o < 1) return fail(GEMB_INTERNAL, "%s: occupancy query failed: %s", op, cudaGetErrorName(e));
-      resident[dev] = o;
-      resident_smem[dev] = smem;
-    }
-    occ = resident[dev];
-  }
   const uint64_t tasks = (grp.row_start[grp.n] + 15) / 16;
-  const uint64_t wave = static_cast<uint64_t>(sm_count()) * occ;
-  const unsigned blocks = static_cast<unsigned>(std::min<uint64_t>((tasks + kWarps - 1) / kWarps, wave));
+  const unsigned blocks = static_cast<unsigned>(std::min<uint64_t>(tasks, static_cast<uint64_t>(sm_count()) * 3));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(blocks);
   cfg.blockDim = dim3(kWarps * 32);
-  cfg.dynamicSmemBytes = smem;
+  cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -189,6 +189,14 @@ int32_t moe_shared_stage(const gemb_moe_layer_weights* w, const uint16_t* x, uin
                               sd.input_divisor, sd.weight_divisor, stream);
 }
 
+// Whether the shared branch goes to the side stream.  Up to about a thousand tokens the layer's kernels
+// leave SMs idle and a second stream fills them (15 % at 64 tokens).  Beyond that every kernel fills the
+// GPU, so two streams cannot beat the sum of the kernels -- and the persistent GEMMs of the two streams,
+// one CTA per SM with a fixed share of tiles each, can only take turns on an SM: whichever CTAs start
+// late finish late, and the same captured graph was measured at either 477 or 637 us (4,096 tokens)
+// depending on how the CTAs happened to interleave.  In line the layer is the sum of its kernels, every time.
+bool fork_pays(uint64_t tokens) { return tokens <= 1024; }
+
 int32_t stream_fork(const char* op, gemb_stream_t stream, gemb_stream_t side_stream, void* event) {
   cudaError_t e = cudaEventRecord(static_cast<cudaEvent_t>(event), stream);
   if (e == cudaSuccess) e = cudaStreamWaitEvent(side_stream, static_cast<cudaEvent_t>(event), 0);
@@ -296,13 +304,13 @@ int32_t gemb_moe_layer_forward(const gemb_moe_layer_weights* w, const uint16_t* 
   GEMB_REQUIRE(workspace_bytes >= need, "%s: workspace too small (%llu bytes needed)", op, static_cast<unsigned long long>(need));
   GEMB_ENTER(op);
   const bool shared = w->shared_intermediate != 0;
-  const bool forked = shared && side_stream != nullptr && fork_event != nullptr && join_event != nullptr;
+  const bool forked = shared && side_stream != nullptr && fork_event != nullptr && join_event != nullptr && fork_pays(tokens);
   struct Hint {
     explicit Hint(uint64_t rows) { set_grouped_rows_hint(rows); }
     ~Hint() { set_grouped_rows_hint(0); }
   } hint(tokens * w->topk);
   // The shared dense branch depends only on x: beside routing and the expert GEMMs when the caller
-  // gave a second stream, first otherwise.
+  // gave a second stream and the batch is small enough for that to pay, first otherwise.
   if (forked) GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));
   if (shared && moe_stage_on(kStageShared)) GEMB_TRY(moe_shared_stage(w, x, tokens, b.c, forked ? side_stream : stream));
   if (moe_stage_on(kStageRoute)) GEMB_TRY(moe_route_stage(w, x, tokens, b.c, nullptr, stream));

@@ -52,6 +52,8 @@ void set_grouped_rows_hint(uint64_t rows);
 enum : int { kStageRoute = 1, kStagePack = 2, kStageGateUp = 4, kStageGelu = 8, kStageDown = 16, kStageCombine = 32,
              kStageShared = 64, kStageExchange = 128 };
 bool moe_stage_on(int bit);
+// Whether a batch of this many tokens is small enough for the shared branch to gain from a second stream.
+bool fork_pays(uint64_t tokens);
 // Fork: side_stream waits for what `stream` holds so far.  Join: `stream` waits for side_stream.
 int32_t stream_fork(const char* op, gemb_stream_t stream, gemb_stream_t side_stream, void* event);
 int32_t stream_join(const char* op, gemb_stream_t stream, gemb_stream_t side_stream, void* event);

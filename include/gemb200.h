@@ -723,9 +723,10 @@ int32_t gemb_moe_router_input(const uint16_t* x_bf16, const uint16_t* scale_bf16
  * x and out are bf16 [tokens, hidden].  The workspace (gemb_moe_layer_workspace_bytes, 256-byte
  * aligned) needs no initialisation and keeps the records of the last call.  Stream-ordered, no
  * allocation, no host synchronisation, capturable.  When side_stream, fork_event and join_event
- * (cudaEvent_t created by the caller, timing disabled) are all set, the shared branch runs on
- * side_stream beside routing and the expert GEMMs and joins before the combine; otherwise
- * everything runs on `stream`.  Same results either way. */
+ * (cudaEvent_t created by the caller, timing disabled) are all set and the batch holds at most 1,024
+ * tokens, the shared branch runs on side_stream beside routing and the expert GEMMs and joins before
+ * the combine; otherwise everything runs on `stream` (from about a thousand tokens on every kernel of
+ * the layer fills the GPU, and two streams of persistent GEMMs only take turns).  Same results either way. */
 uint64_t gemb_moe_layer_workspace_bytes(const gemb_moe_layer_weights* weights, uint64_t tokens);
 int32_t gemb_moe_layer_records(const gemb_moe_layer_weights* weights, uint64_t tokens, void* workspace,
                                gemb_moe_records* records);

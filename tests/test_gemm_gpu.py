@@ -160,8 +160,9 @@ def test_nvfp4_gemm_f32_output(lib, dev, orc):
 
 @pytest.mark.parametrize("tokens,rows,k", [(128, 256, 64), (300, 1000, 704), (4096, 4096, 512), (1153, 2816, 2112)])
 def test_cta_pair_and_single_cta_tiles_agree_bit_for_bit(lib, dev, tokens, rows, k):
-    """The dense GEMMs run 256x256 tiles on CTA pairs by default; GEMB_TUNE_GEMM_PAIR = 1 runs the same
-    256-wide tile on one CTA.  Same MMAs, same accumulation order: the outputs must be identical.
+    """The dense GEMMs run on CTA pairs by default; GEMB_TUNE_GEMM_PAIR = 1 runs the 256-wide tile on one
+    CTA, GEMB_TUNE_GEMM_BN = 128 with pairs forced the 256 x 128 pair tile.  Same accumulation order along
+    K in all of them: the outputs must be identical.
     Shapes cover an odd number of 128-row tiles (the odd CTA of the last pair has no rows), ragged
     rows / columns, a K tail, and several tiles per cluster."""
     a = nvfp4_operand(lib, dev, tokens, k, 1.0, 3)
@@ -170,8 +171,9 @@ def test_cta_pair_and_single_cta_tiles_agree_bit_for_bit(lib, dev, tokens, rows,
     w8 = fp8_operand(lib, dev, rows, k, 0.02, 6)
     outs = {}
     try:
-        for mode in (1, 2):
-            lib.gemb_set_tuning(5, mode)
+        for mode in (1, 2, 3):          # 3: pairs on 256 x 128 tiles with two accumulators (NVFP4)
+            lib.gemb_set_tuning(5, min(mode, 2))
+            lib.gemb_set_tuning(3, 128 if mode == 3 else 0)
             o4 = torch.full((tokens, rows), 0x7FC0, dtype=torch.int16, device=dev)
             o8 = torch.full((tokens, rows), 0x7FC0, dtype=torch.int16, device=dev)
             o32 = torch.full((tokens, rows), float("nan"), device=dev)
@@ -185,6 +187,8 @@ def test_cta_pair_and_single_cta_tiles_agree_bit_for_bit(lib, dev, tokens, rows,
             outs[mode] = (o4, o32, o8)
     finally:
         lib.gemb_set_tuning(5, 0)
-    for x, y, name in zip(outs[1], outs[2], ("nvfp4 bf16", "nvfp4 f32", "fp8 bf16")):
+        lib.gemb_set_tuning(3, 0)
+    for x, y, z, name in zip(outs[1], outs[2], outs[3], ("nvfp4 bf16", "nvfp4 f32", "fp8 bf16")):
         assert torch.equal(x, y), name
+        assert torch.equal(x, z), name + " (256 x 128 pair tiles)"
         assert not torch.isnan(y.float() if y.dtype == torch.float32 else y.view(torch.bfloat16).float()).any(), name
