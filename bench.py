@@ -396,6 +396,8 @@ def run_moe_stack(args):
     dev, world, rank = d.dev, d.world, d.rank
     lib = load()
     lib.gemb_device_check()
+    if args.ep_shared_sms is not None:
+        lib.gemb_set_tuning(9, args.ep_shared_sms)
     layers = args.moe_layers
     e_local = MOE["experts"] // world
     own = (rank * e_local, (rank + 1) * e_local)
@@ -1112,6 +1114,8 @@ def main():
     ap.add_argument("--no-stage-times", action="store_true")
     ap.add_argument("--unfused", dest="fused", action="store_false",
                     help="gate/up GEMM, GELU requantisation as separate launches instead of the fused epilogue")
+    ap.add_argument("--ep-shared-sms", type=int, default=None,
+                    help="N > 1: SMs the shared branch gets beside the pushing down GEMM (GEMB_TUNE_EP_SHARED_SMS; default: the library's)")
     ap.add_argument("--moe-layers", type=int, default=MOE_LAYERS,
                     help="MoE layers held on the device (30 = the benchmark; fewer for a small profiler capture)")
     ap.add_argument("--layers", type=int, default=LAYERS,

@@ -48,11 +48,17 @@ int ep_take_device_error() {
 // Polls a flag barrier makes before it gives up (about 500 ns each once past the first 64):
 // gemb_set_tuning(GEMB_TUNE_EP_BARRIER_SPINS, n); the default is about three seconds.
 int g_ep_barrier_spins = 1 << 22;
+int g_ep_shared_sms = 40;  // large batches: SMs given to the shared branch beside the pushing down GEMM (0: in line)
 
 int32_t ep_set_tuning(int32_t knob, int32_t value) {
   if (knob == GEMB_TUNE_EP_BARRIER_SPINS) {
     GEMB_REQUIRE(value >= 0 && value <= (1 << 24), "gemb_set_tuning: barrier polls must be in [0, 2^24] (0 = default)");
     g_ep_barrier_spins = value == 0 ? 1 << 22 : value;
+    return GEMB_OK;
+  }
+  if (knob == GEMB_TUNE_EP_SHARED_SMS) {
+    GEMB_REQUIRE(value >= 0 && value <= 128 && value % 2 == 0, "gemb_set_tuning: SMs for the shared branch must be even, in [0, 128]");
+    g_ep_shared_sms = value;
     return GEMB_OK;
   }
   return moe_set_tuning(knob, value);
@@ -95,22 +101,29 @@ ep_plan_body(const int32_t* counts_all_global, uint32_t ranks, uint32_t experts,
   for (uint32_t s = threadIdx.x; s < ranks; s += blockDim.x) {
     int64_t sent = 0;
     bool neg = false;
-    for (uint32_t e = 0; e < experts; ++e) {
-      const int c = counts_all[s * experts + e];
-      neg |= c < 0;
-      sent += c;
+    for (uint32_t e0 = 0; e0 < experts; e0 += 8) {
+      int c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = e0 + j < experts ? counts_all[s * experts + e0 + j] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        neg |= c[j] < 0;
+        sent += c[j];
+      }
     }
     if (neg || sent > static_cast<int64_t>(send_rows)) bad = 1;
   }
-  if (threadIdx.x == 0) {
-    int64_t po = 0;
-    for (uint32_t e = me * el; e < (me + 1) * el; ++e) {
-      int64_t t = 0;
-      for (uint32_t s = 0; s < ranks; ++s) t += max(counts_all[s * experts + e], 0);
-      po += (t + 255) / 256 * 256;
-    }
-    if (po > static_cast<int64_t>(capacity_rows)) bad = 1;
+  // padded rows of my experts: one thread per expert, combined with a shared-memory atomic
+  __shared__ unsigned long long padded_total;
+  if (threadIdx.x == 0) padded_total = 0ull;
+  __syncthreads();
+  for (uint32_t e = me * el + threadIdx.x; e < (me + 1) * el; e += blockDim.x) {
+    int64_t t = 0;
+    for (uint32_t s = 0; s < ranks; ++s) t += max(counts_all[s * experts + e], 0);
+    atomicAdd(&padded_total, static_cast<unsigned long long>((t + 255) / 256 * 256));
   }
+  __syncthreads();
+  if (threadIdx.x == 0 && padded_total > static_cast<unsigned long long>(capacity_rows)) bad = 1;
   __syncthreads();
   if (bad) {
     if (threadIdx.x == 0) {
@@ -144,28 +157,43 @@ ep_plan_body(const int32_t* counts_all_global, uint32_t ranks, uint32_t experts,
   // Padded offsets restart at every owner's first expert; one thread per owner, plus one for mine.
   if (threadIdx.x < ranks) {
     const uint32_t d = threadIdx.x;
-    int po = 0;
-    for (uint32_t e = d * el; e < (d + 1) * el; ++e) {
-      pad[e] = po;
-      po += (tot[e] + 255) / 256 * 256;
+    // A serial prefix sum in one thread: the loads of eight values are issued together, so an iteration
+    // costs one add instead of one shared-memory round trip.  live_off (the first entry of every local
+    // expert in the list of tiles that hold real rows) rides along for this rank's own experts.
+    int po = 0, lo = 0;
+    for (uint32_t e0 = d * el; e0 < (d + 1) * el; e0 += 8) {
+      int t[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) t[j] = e0 + j < (d + 1) * el ? tot[e0 + j] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (e0 + j >= (d + 1) * el) break;
+        pad[e0 + j] = po;
+        po += (t[j] + 255) / 256 * 256;
+        if (d == me) {
+          live_off[e0 + j - d * el] = lo;
+          lo += (t[j] + 127) / 128;
+        }
+      }
     }
     if (d == me) {
       plan[0] = po / 128;
       plan[1] = po;
       plan[2 + el] = po;
-      // first entry of every local expert in the list of tiles that hold real rows
-      int lo = 0;
-      for (uint32_t e = d * el; e < (d + 1) * el; ++e) {
-        live_off[e - d * el] = lo;
-        lo += (tot[e] + 127) / 128;
-      }
       plan[3 + el + 2 * (po / 128)] = lo;
     }
-  } else if (threadIdx.x == ranks) {
+  } else if (threadIdx.x == 32) {   // another warp, so that it runs beside the owners' threads
     int po = 0;
-    for (uint32_t e = 0; e < experts; ++e) {
-      my_pad[e] = po;
-      po += (counts_all[me * experts + e] + 255) / 256 * 256;
+    for (uint32_t e0 = 0; e0 < experts; e0 += 8) {
+      int t[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) t[j] = e0 + j < experts ? counts_all[me * experts + e0 + j] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (e0 + j >= experts) break;
+        my_pad[e0 + j] = po;
+        po += (t[j] + 255) / 256 * 256;
+      }
     }
   }
   __syncthreads();
@@ -187,26 +215,46 @@ ep_plan_body(const int32_t* counts_all_global, uint32_t ranks, uint32_t experts,
   __shared__ int rows_from[kMaxRanks];
   if (threadIdx.x < ranks) {
     int n = 0;
-    for (uint32_t e = 0; e < el; ++e) n += counts_all[threadIdx.x * experts + me * el + e];
+    for (uint32_t e0 = 0; e0 < el; e0 += 8) {
+      int c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = e0 + j < el ? counts_all[threadIdx.x * experts + me * el + e0 + j] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) n += c[j];
+    }
     rows_from[threadIdx.x] = n;
   }
   __syncthreads();
+  for (uint32_t g = threadIdx.x; g < ranks * el; g += blockDim.x) {   // destination: rows of the sources before s
+    const uint32_t s = g / el, ge = me * el + g % el;
+    int b = 0;
+    for (uint32_t s2 = 0; s2 < s; ++s2) b += counts_all[s2 * experts + ge];
+    recv_dst[g] = pad[ge] + b;
+  }
   if (threadIdx.x < ranks) {
     const uint32_t s = threadIdx.x;
     int run = 0, src = 0;
     for (uint32_t s2 = 0; s2 < s; ++s2) run += rows_from[s2];
-    for (uint32_t e2 = 0; e2 < me * el; ++e2) src += counts_all[s * experts + e2];
-    for (uint32_t e = 0; e < el; ++e) {
-      const uint32_t ge = me * el + e;
-      const uint32_t g = s * el + e;
-      int b = 0;
-      for (uint32_t s2 = 0; s2 < s; ++s2) b += counts_all[s2 * experts + ge];
-      recv_prefix[g] = run;
-      recv_src[g] = src;
-      recv_dst[g] = pad[ge] + b;
-      const int c = counts_all[s * experts + ge];
-      run += c;
-      src += c;
+    for (uint32_t e0 = 0; e0 < me * el; e0 += 8) {
+      int c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = e0 + j < me * el ? counts_all[s * experts + e0 + j] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) src += c[j];
+    }
+    for (uint32_t e0 = 0; e0 < el; e0 += 8) {
+      int c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = e0 + j < el ? counts_all[s * experts + me * el + e0 + j] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (e0 + j >= el) break;
+        const uint32_t g = s * el + e0 + j;
+        recv_prefix[g] = run;
+        recv_src[g] = src;
+        run += c[j];
+        src += c[j];
+      }
     }
     if (s == ranks - 1) recv_prefix[ranks * el] = run;
   }
@@ -286,28 +334,32 @@ ep_sync_plan_kernel(PeerPtrs flag_arrays, PeerPtrs count_buffers, uint32_t ranks
                tile_rows);
 }
 
-// Quantises each local token once (EXACT NVFP4 contract, src/numeric/nvfp4.cpp:139-150) and writes one
+// Quantises each local token once (EXACT NVFP4 contract, src/numeric/nvfp4.cpp:139-150) and PUSHES one
 // message row per assignment -- payload | compact block scales | assignment index (token * topk +
-// slot) -- at the assignment's position in (expert, token, slot) order, which groups the rows by
-// owner.  The position follows from the permutation's outputs: offsets[e] + (slot_rows[i] -
-// padded_offset[e]).  One CTA per token, one thread per 16-element block.
+// slot) -- into the message buffer of the rank that owns the expert (plain stores, peer memory for
+// another rank).  A rank's message buffer holds one region of send_rows rows per source rank; inside its
+// region a row sits at the assignment's position in the source's (expert, token, slot) order, which
+// follows from the permutation's outputs alone: offsets[e] + (slot_rows[i] - padded_offset[e]).  So the
+// source needs nobody else's counts to place a row, and the owner finds it where the position
+// arithmetic over all counts says (recv_src).  One CTA per token, one thread per 16-element block.
 __global__ void __launch_bounds__(256)
 ep_pack_kernel(const uint16_t* __restrict__ x, const int32_t* __restrict__ ids, const int32_t* __restrict__ slot_rows,
-               const int32_t* __restrict__ offsets, const int32_t* __restrict__ plan, uint8_t* __restrict__ send,
+               const int32_t* __restrict__ offsets, const int32_t* __restrict__ plan, PeerPtrs msg, uint32_t me, uint32_t el,
                uint32_t hidden, uint32_t topk, uint32_t experts, uint32_t msg_bytes, uint32_t send_rows, float g) {
   const uint32_t t = blockIdx.x;
-  __shared__ int pos[32];
+  __shared__ uint8_t* dst[32];
   extern __shared__ __align__(16) uint8_t pack_sc[];   // the token's hidden/16 scale bytes
   if (threadIdx.x < topk) {
     const uint64_t i = static_cast<uint64_t>(t) * topk + threadIdx.x;
     const uint32_t e = static_cast<uint32_t>(__ldg(ids + i));
-    int pp = -1;
+    uint8_t* d = nullptr;
     if (e < experts) {
       const int64_t q = static_cast<int64_t>(__ldg(offsets + e)) + __ldg(slot_rows + i) - __ldg(plan + 2 + e);
-      if (q >= 0 && q < static_cast<int64_t>(send_rows)) pp = static_cast<int>(q);
+      if (q >= 0 && q < static_cast<int64_t>(send_rows))
+        d = const_cast<uint8_t*>(msg.p[e / el]) + (static_cast<uint64_t>(me) * send_rows + static_cast<uint64_t>(q)) * msg_bytes;
     }
-    if (pp < 0) atomicCAS(&g_ep_error, 0, 7);   // cannot be; the row is not written
-    pos[threadIdx.x] = pp;
+    if (d == nullptr) atomicCAS(&g_ep_error, 0, 7);   // cannot be; the row is not written
+    dst[threadIdx.x] = d;
   }
   __syncthreads();
   const uint32_t blocks = hidden / 16;
@@ -326,21 +378,18 @@ ep_pack_kernel(const uint16_t* __restrict__ x, const int32_t* __restrict__ ids, 
     quantize_block16<false>(v, g, lo, hi, sb);
     pack_sc[c] = sb;
     for (uint32_t s = 0; s < topk; ++s)
-      if (pos[s] >= 0)
-        *reinterpret_cast<uint2*>(send + static_cast<uint64_t>(pos[s]) * msg_bytes + c * 8) = make_uint2(lo, hi);
+      if (dst[s] != nullptr) *reinterpret_cast<uint2*>(dst[s] + c * 8) = make_uint2(lo, hi);
   }
   __syncthreads();
   // the scales as 16-byte pieces (hidden is a multiple of 256, so hidden / 16 bytes are whole pieces), then the index
   const uint32_t pieces = blocks / 16;
   for (uint32_t idx = threadIdx.x; idx < pieces * topk; idx += blockDim.x) {
     const uint32_t s = idx / pieces, q = idx % pieces;
-    if (pos[s] >= 0)
-      *reinterpret_cast<uint4*>(send + static_cast<uint64_t>(pos[s]) * msg_bytes + hidden / 2 + q * 16) =
-          *reinterpret_cast<const uint4*>(pack_sc + q * 16);
+    if (dst[s] != nullptr)
+      *reinterpret_cast<uint4*>(dst[s] + hidden / 2 + q * 16) = *reinterpret_cast<const uint4*>(pack_sc + q * 16);
   }
-  if (threadIdx.x < topk && pos[threadIdx.x] >= 0)
-    *reinterpret_cast<int32_t*>(send + static_cast<uint64_t>(pos[threadIdx.x]) * msg_bytes + hidden / 2 + hidden / 16) =
-        static_cast<int32_t>(t * topk + threadIdx.x);
+  if (threadIdx.x < topk && dst[threadIdx.x] != nullptr)
+    *reinterpret_cast<int32_t*>(dst[threadIdx.x] + hidden / 2 + hidden / 16) = static_cast<int32_t>(t * topk + threadIdx.x);
 }
 
 // counts_all[s][e] = the per-expert counts rank s left in its peer-mapped buffer.
@@ -352,13 +401,16 @@ ep_gather_counts_kernel(PeerPtrs count_buffers, uint32_t ranks, uint32_t experts
   }
 }
 
+// kPullPayloadVecs: 16-byte payload vectors per lane and row (4: hidden <= 4,096; 8: hidden <= 8,192).
 // Persistent grid, one warp per received row: copies the E2M1 payload into the padded row space and
 // the compact block scales into the interleaved layout.
+template <int kPullPayloadVecs>
 __global__ void __launch_bounds__(256)
 ep_pull_dispatch_kernel(PeerPtrs peers, const int32_t* __restrict__ recv_prefix, const int32_t* __restrict__ recv_src,
                         const int32_t* __restrict__ recv_dst, uint32_t segments, uint32_t el, uint32_t hidden,
                         uint32_t msg_bytes, uint32_t c_pad, uint8_t* __restrict__ packed,
                         uint8_t* __restrict__ scales, uint32_t send_rows, uint32_t rows_max, int2* __restrict__ row_meta) {
+  constexpr int kPullScaleWords = kPullPayloadVecs / 2;   // 4-byte scale words per lane and row
   extern __shared__ int sm[];
   int* prefix = sm;  // [segments + 1]
   for (uint32_t i = threadIdx.x; i <= segments; i += blockDim.x) prefix[i] = recv_prefix[i];
@@ -386,37 +438,35 @@ ep_pull_dispatch_kernel(PeerPtrs peers, const int32_t* __restrict__ recv_prefix,
       continue;
     }
     const uint8_t* src = peers.p[lo / el] + srow * msg_bytes;
+    // Every load of the row (over NVLink for a remote source) is issued before the first store: a row is
+    // small, so what hides the latency is the loads in flight per warp, and a store that waited for its
+    // own load in program order would hold back the loads behind it.
+    uint4 pv[kPullPayloadVecs];
+#pragma unroll
+    for (int i = 0; i < kPullPayloadVecs; ++i) {
+      const uint32_t v = i * 32 + lane;
+      pv[i] = v < payload_vecs ? *reinterpret_cast<const uint4*>(src + v * 16) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    uint32_t sv[kPullScaleWords];
+#pragma unroll
+    for (int i = 0; i < kPullScaleWords; ++i) {
+      const uint32_t w = i * 32 + lane;
+      sv[i] = w < scale_words ? *reinterpret_cast<const uint32_t*>(src + hidden / 2 + w * 4) : 0u;
+    }
     // Where the row's result has to go: {source rank, the assignment index the source wrote behind the scales}.
-    if (row_meta != nullptr && lane == 0)
-      row_meta[d] = make_int2(static_cast<int>(lo / el), *reinterpret_cast<const int32_t*>(src + hidden / 2 + hidden / 16));
-    // All of a lane's loads of the row (over NVLink for a remote source) are issued before its first
-    // store: a row is small, so the loads in flight per warp are what hides the link latency.
-    for (uint32_t v0 = 0; v0 < payload_vecs; v0 += 128) {
-      uint4 pv[4];
+    int assignment = 0;
+    if (row_meta != nullptr && lane == 0) assignment = *reinterpret_cast<const int32_t*>(src + hidden / 2 + hidden / 16);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t v = v0 + i * 32 + lane;
-        pv[i] = v < payload_vecs ? *reinterpret_cast<const uint4*>(src + v * 16) : make_uint4(0u, 0u, 0u, 0u);
-      }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t v = v0 + i * 32 + lane;
-        if (v < payload_vecs) *reinterpret_cast<uint4*>(packed + d * (hidden / 2) + v * 16) = pv[i];
-      }
+    for (int i = 0; i < kPullPayloadVecs; ++i) {
+      const uint32_t v = i * 32 + lane;
+      if (v < payload_vecs) *reinterpret_cast<uint4*>(packed + d * (hidden / 2) + v * 16) = pv[i];
     }
-    for (uint32_t w0 = 0; w0 < scale_words; w0 += 64) {
-      uint32_t sv[2];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const uint32_t w = w0 + i * 32 + lane;
-        sv[i] = w < scale_words ? *reinterpret_cast<const uint32_t*>(src + hidden / 2 + w * 4) : 0u;
-      }
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const uint32_t w = w0 + i * 32 + lane;
-        if (w < scale_words) *reinterpret_cast<uint32_t*>(scales + interleaved_scale_offset(d, w * 4, c_pad)) = sv[i];
-      }
+    for (int i = 0; i < kPullScaleWords; ++i) {
+      const uint32_t w = i * 32 + lane;
+      if (w < scale_words) *reinterpret_cast<uint32_t*>(scales + interleaved_scale_offset(d, w * 4, c_pad)) = sv[i];
     }
+    if (row_meta != nullptr && lane == 0) row_meta[d] = make_int2(static_cast<int>(lo / el), assignment);
   }
 }
 
@@ -639,7 +689,7 @@ int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers_host, uint64
   GEMB_REQUIRE(recv_prefix && recv_src_rows && recv_dst_rows && packed_e2m1 && interleaved_scales,
                "%s: pointers must be nonnull", op);
   GEMB_REQUIRE(local_experts >= 1 && ranks * local_experts <= kMaxExperts, "%s: bad expert geometry", op);
-  GEMB_REQUIRE(hidden > 0 && hidden % 64 == 0 && hidden < (1ull << 24), "%s: hidden must be a nonzero multiple of 64", op);
+  GEMB_REQUIRE(hidden > 0 && hidden % 64 == 0 && hidden <= 8192, "%s: hidden must be a nonzero multiple of 64, at most 8,192", op);
   GEMB_REQUIRE(message_row_bytes % 16 == 0 && message_row_bytes >= hidden / 2 + hidden / 16,
                "%s: a message row holds the payload and the block scales, padded to 16 bytes", op);
   GEMB_REQUIRE(reinterpret_cast<uintptr_t>(packed_e2m1) % 16 == 0 && reinterpret_cast<uintptr_t>(interleaved_scales) % 4 == 0,
@@ -650,7 +700,13 @@ int32_t gemb_moe_ep_pull_dispatch(const uint64_t* peer_send_buffers_host, uint64
   GEMB_ENTER(op);
   const uint32_t segments = static_cast<uint32_t>(ranks * local_experts);
   const uint32_t c_pad = static_cast<uint32_t>((hidden / 16 + 3) / 4 * 4);
-  ep_pull_dispatch_kernel<<<static_cast<unsigned>(sm_count()) * 8, 256, (segments + 1) * sizeof(int), stream>>>(
+  if (hidden <= 4096)
+    ep_pull_dispatch_kernel<4><<<static_cast<unsigned>(sm_count()) * 8, 256, (segments + 1) * sizeof(int), stream>>>(
+      peers, recv_prefix, recv_src_rows, recv_dst_rows, segments, static_cast<uint32_t>(local_experts),
+      static_cast<uint32_t>(hidden), static_cast<uint32_t>(message_row_bytes), c_pad, packed_e2m1, interleaved_scales,
+      static_cast<uint32_t>(send_rows_per_rank), static_cast<uint32_t>(padded_rows_max), nullptr);
+  else
+    ep_pull_dispatch_kernel<8><<<static_cast<unsigned>(sm_count()) * 8, 256, (segments + 1) * sizeof(int), stream>>>(
       peers, recv_prefix, recv_src_rows, recv_dst_rows, segments, static_cast<uint32_t>(local_experts),
       static_cast<uint32_t>(hidden), static_cast<uint32_t>(message_row_bytes), c_pad, packed_e2m1, interleaved_scales,
       static_cast<uint32_t>(send_rows_per_rank), static_cast<uint32_t>(padded_rows_max), nullptr);
@@ -742,7 +798,7 @@ int32_t validate_ep(const char* op, const gemb_moe_layer_weights* w, uint64_t to
   GEMB_REQUIRE(ranks >= 1 && ranks <= kMaxRanks && w->experts % ranks == 0, "%s: experts must be a multiple of the rank count (at most %u ranks)",
                op, kMaxRanks);
   GEMB_TRY(validate_moe_weights(op, w, tokens, w->experts / ranks));
-  GEMB_REQUIRE(w->hidden % 256 == 0, "%s: hidden must be a multiple of 256", op);
+  GEMB_REQUIRE(w->hidden % 256 == 0 && w->hidden <= 8192, "%s: hidden must be a multiple of 256, at most 8,192", op);
   GEMB_REQUIRE(tokens * w->topk * ranks < (1ull << 31), "%s: tokens * topk * ranks must fit 31 bits", op);
   return GEMB_OK;
 }
@@ -778,8 +834,8 @@ int32_t ep_stage_send(const char* op, const gemb_moe_layer_weights* w, const gem
   const uint32_t h = static_cast<uint32_t>(w->hidden);
   const unsigned threads = static_cast<unsigned>(std::min<uint64_t>(256, (h / 16 + 31) / 32 * 32));
   ep_pack_kernel<<<static_cast<unsigned>(tokens), threads, h / 16, stream>>>(
-      x, b.c.ids, b.c.slot_rows, b.c.offsets, b.c.plan, const_cast<uint8_t*>(call.send.p[comm->rank]), h,
-      static_cast<uint32_t>(w->topk), static_cast<uint32_t>(w->experts), static_cast<uint32_t>(call.msg_bytes),
+      x, b.c.ids, b.c.slot_rows, b.c.offsets, b.c.plan, call.send, static_cast<uint32_t>(comm->rank),
+      static_cast<uint32_t>(b.el), h, static_cast<uint32_t>(w->topk), static_cast<uint32_t>(w->experts), static_cast<uint32_t>(call.msg_bytes),
       static_cast<uint32_t>(tokens * w->topk), w->gate_up.input_divisor);
   return check_launch(op);
 }
@@ -798,8 +854,17 @@ int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const 
   GEMB_TRY(check_launch(op));
   const uint32_t segments = ranks * el;
   const uint32_t c_pad = static_cast<uint32_t>((h / 16 + 3) / 4 * 4);
-  ep_pull_dispatch_kernel<<<static_cast<unsigned>(sm_count()) * 8, 256, (segments + 1) * sizeof(int), stream>>>(
-      call.send, b.recv_prefix, b.recv_src, b.recv_dst, segments, el, static_cast<uint32_t>(h),
+  // The rows were pushed: source s's rows lie in region s of this rank's own message buffer.
+  PeerPtrs regions{};
+  for (uint32_t s = 0; s < ranks; ++s) regions.p[s] = call.send.p[me] + static_cast<uint64_t>(s) * n * call.msg_bytes;
+  if (h <= 4096)
+    ep_pull_dispatch_kernel<4><<<static_cast<unsigned>(sm_count()) * 8, 256, (segments + 1) * sizeof(int), stream>>>(
+      regions, b.recv_prefix, b.recv_src, b.recv_dst, segments, el, static_cast<uint32_t>(h),
+      static_cast<uint32_t>(call.msg_bytes), c_pad, b.a_packed, b.a_scales, static_cast<uint32_t>(n),
+      static_cast<uint32_t>(b.rows_max), reinterpret_cast<int2*>(b.row_meta));
+  else
+    ep_pull_dispatch_kernel<8><<<static_cast<unsigned>(sm_count()) * 8, 256, (segments + 1) * sizeof(int), stream>>>(
+      regions, b.recv_prefix, b.recv_src, b.recv_dst, segments, el, static_cast<uint32_t>(h),
       static_cast<uint32_t>(call.msg_bytes), c_pad, b.a_packed, b.a_scales, static_cast<uint32_t>(n),
       static_cast<uint32_t>(b.rows_max), reinterpret_cast<int2*>(b.row_meta));
   GEMB_TRY(check_launch(op));
@@ -823,7 +888,20 @@ int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const 
     if (moe_stage_on(kStageGelu))
     GEMB_TRY(gemb_moe_expert_gelu_quantize(b.gate_up, b.plan, b.p_packed, b.p_scales, b.rows_max, i, dn.input_divisor, stream));
   }
+  return GEMB_OK;
+}
+
+int32_t ep_stage_down(const char* op, const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const EpCall& call,
+                      uint64_t tokens, gemb_stream_t stream) {
+  const EpBuffers& b = call.b;
+  const gemb_nvfp4_binding& dn = w->down;
+  const uint32_t el = static_cast<uint32_t>(b.el);
+  const uint64_t h = w->hidden, i = w->intermediate, n = tokens * w->topk;
   if (!moe_stage_on(kStageDown)) return GEMB_OK;
+  struct Hint {
+    explicit Hint(uint64_t rows) { set_grouped_rows_hint(rows); }
+    ~Hint() { set_grouped_rows_hint(0); }
+  } hint(n);
   return grouped_gemm_push(op, b.p_packed, b.p_scales, dn.packed_weight, dn.scales_interleaved, b.plan, b.rows_max, el, h, i,
                            dn.input_divisor, dn.weight_divisors_device, b.row_meta, b.tile_rows, comm->recv_buffers_host,
                            comm->ranks, comm->rank, n, stream);
@@ -880,7 +958,10 @@ int32_t gemb_moe_ep_layer_stage(const gemb_moe_layer_weights* w, const gemb_moe_
     if (w->shared_intermediate != 0) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, stream));
     return ep_stage_send(op, w, comm, call, x, tokens, stream);
   }
-  if (stage == 1) return ep_stage_experts(op, w, comm, call, tokens, barriers != 0, stream);
+  if (stage == 1) {
+    GEMB_TRY(ep_stage_experts(op, w, comm, call, tokens, barriers != 0, stream));
+    return ep_stage_down(op, w, comm, call, tokens, stream);
+  }
   GEMB_REQUIRE(out != nullptr, "%s: output must be nonnull", op);
   return ep_stage_combine(op, w, comm, call, out, tokens, barriers != 0, stream);
 }
@@ -903,7 +984,30 @@ int32_t gemb_moe_ep_layer_forward(const gemb_moe_layer_weights* w, const gemb_mo
   }
   GEMB_TRY(ep_stage_send(op, w, comm, call, x, tokens, stream));
   GEMB_TRY(ep_stage_experts(op, w, comm, call, tokens, true, stream));
-  if (shared && !forked && moe_stage_on(kStageShared)) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, stream));
+  // The pushing down GEMM is bound by NVLink, not by the SMs: with GEMB_TUNE_EP_SHARED_SMS = S the shared
+  // branch's GEMMs run beside it on S SMs of their own (both grids capped, so all CTAs are resident at
+  // once and none waits for another kernel's CTA to leave an SM).
+  const bool beside = shared && !forked && g_ep_shared_sms > 0 && comm->ranks > 1 && side_stream != nullptr &&
+                      fork_event != nullptr && join_event != nullptr && moe_stage_on(kStageShared) && moe_stage_on(kStageDown);
+  struct Cap {
+    explicit Cap(uint32_t ctas) { set_gemm_cta_cap(ctas); }
+    ~Cap() { set_gemm_cta_cap(0); }
+  };
+  if (beside) {
+    GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));
+    {
+      Cap cap(static_cast<uint32_t>(g_ep_shared_sms));
+      GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, side_stream));
+    }
+    {
+      Cap cap(static_cast<uint32_t>(sm_count() - g_ep_shared_sms) & ~1u);
+      GEMB_TRY(ep_stage_down(op, w, comm, call, tokens, stream));
+    }
+    GEMB_TRY(stream_join(op, stream, side_stream, join_event));
+  } else {
+    GEMB_TRY(ep_stage_down(op, w, comm, call, tokens, stream));
+    if (shared && !forked && moe_stage_on(kStageShared)) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, stream));
+  }
   if (forked) GEMB_TRY(stream_join(op, stream, side_stream, join_event));
   return ep_stage_combine(op, w, comm, call, out, tokens, true, stream);
 }

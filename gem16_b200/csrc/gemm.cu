@@ -818,6 +818,9 @@ bool use_pairs() { return g_gemm_pair != 1 && (g_gemm_bn == 0 || g_gemm_bn == 25
 // second SM per tile.  The expectation is the rows the caller announced (the layer calls know how
 // many assignments they route) or else what the capacity of the padded row space implies.
 thread_local uint64_t g_grouped_rows_hint = 0;
+// Upper bound on the persistent grid of the GEMMs this thread launches (0 = none): lets a caller run two
+// GEMMs side by side on disjoint sets of SMs instead of having their CTAs take turns.
+thread_local uint32_t g_gemm_cta_cap = 0;
 bool grouped_pairs(uint64_t padded_rows_max, uint64_t experts) {
   if (!use_pairs()) return false;
   uint64_t rows = g_grouped_rows_hint;
@@ -881,9 +884,13 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
   const uint32_t m_tiles = (p.m + BM - 1) / BM, n_tiles = (p.n + BN - 1) / BN;
   if constexpr (kPair) {
     const uint32_t units = ((m_tiles + 1) / 2) * n_tiles;
-    cfg.gridDim = dim3(2 * std::min<uint32_t>(units, static_cast<uint32_t>(max_pairs[dev])));
+    uint32_t pairs_max = static_cast<uint32_t>(max_pairs[dev]);
+    if (g_gemm_cta_cap != 0) pairs_max = std::max(1u, std::min(pairs_max, g_gemm_cta_cap / 2));
+    cfg.gridDim = dim3(2 * std::min<uint32_t>(units, pairs_max));
   } else {
-    cfg.gridDim = dim3(std::min<uint32_t>(m_tiles * n_tiles, static_cast<uint32_t>(sm_count())));
+    uint32_t ctas_max = static_cast<uint32_t>(sm_count());
+    if (g_gemm_cta_cap != 0) ctas_max = std::max(1u, std::min(ctas_max, g_gemm_cta_cap));
+    cfg.gridDim = dim3(std::min<uint32_t>(m_tiles * n_tiles, ctas_max));
   }
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_a, map_b, map_out, p);
   if (e != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(e), cudaGetErrorString(e));
@@ -930,6 +937,7 @@ int32_t validate_gemm(const char* op, uint64_t tokens, uint64_t rows, uint64_t k
 }  // namespace
 
 void set_grouped_rows_hint(uint64_t rows) { g_grouped_rows_hint = rows; }
+void set_gemm_cta_cap(uint32_t ctas) { g_gemm_cta_cap = ctas; }
 
 int32_t gemm_set_tuning(int32_t knob, int32_t value) {
   if (knob == GEMB_TUNE_GEMM_BN) {

@@ -48,6 +48,9 @@ int32_t grouped_gemm_push(const char* op, const uint8_t* act, const uint8_t* act
 // Announces how many rows the calling thread's next grouped GEMMs will really hold (0: unknown),
 // for their choice between single CTAs and CTA pairs (csrc/gemm.cu).
 void set_grouped_rows_hint(uint64_t rows);
+// Upper bound on the persistent grid of the GEMMs the calling thread launches next (0: none), so that two
+// GEMMs on two streams can each keep a set of SMs to themselves.
+void set_gemm_cta_cap(uint32_t ctas);
 // Stage selection of the layer calls (gemb_set_tuning(GEMB_TUNE_MOE_STAGE_MASK, ...)).
 enum : int { kStageRoute = 1, kStagePack = 2, kStageGateUp = 4, kStageGelu = 8, kStageDown = 16, kStageCombine = 32,
              kStageShared = 64, kStageExchange = 128 };

@@ -301,7 +301,8 @@ class EpLayer:
         h, n = w.hidden, tokens * topk
         self.msg_bytes = c.gemb_moe_ep_message_row_bytes(h)
         make = (lambda nbytes: LocalBuffer(nbytes, dev)) if self.emulated else (lambda nbytes: PeerBuffer(nbytes, dev, group, how))
-        self.send, self.recv = make(n * self.msg_bytes), make(n * h * 2)
+        # message rows in (one region of n rows per source rank), expert rows back
+        self.send, self.recv = make(self.world * n * self.msg_bytes), make(n * h * 2)
         self.counts_peer, self.flags_peer = make(self.e_total * 4), make(2 * 16 * 4)
         self.epochs = torch.zeros((2,), dtype=torch.int32, device=dev)
         self.out = torch.empty((tokens, h), dtype=torch.int16, device=dev)

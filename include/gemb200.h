@@ -90,6 +90,9 @@ int32_t gemb_device_check(void);
  * combine, 6 shared branch, 7 flag barriers + position arithmetic + pull; 0 = all): with a subset
  * the call re-runs just those launches on what the previous full call left in the workspace, so a
  * benchmark can time one kernel of the sequence in place.  Results of a partial call are not a layer;
+ * GEMB_TUNE_EP_SHARED_SMS = for batches above 1,024 tokens per rank, how many SMs (even) the shared branch's
+ * GEMMs get beside the NVLink-bound pushing down GEMM of gemb_moe_ep_layer_forward when a side stream is
+ * given (default 40, measured best of 0 / 40 / 56 / 72 on two GPUs; 0: the shared branch runs in line behind it);
  * GEMB_TUNE_ROUTER_TILE = which router-logits kernel runs: 0 automatic, 1 the expert-per-thread kernels
  * wherever they apply, 8 / 16 / 32 the tiled kernel with that many tokens per CTA (same bits from all). */
 enum {
@@ -100,7 +103,8 @@ enum {
   GEMB_TUNE_GEMM_PAIR = 5,
   GEMB_TUNE_EP_BARRIER_SPINS = 6,
   GEMB_TUNE_MOE_STAGE_MASK = 7,
-  GEMB_TUNE_ROUTER_TILE = 8
+  GEMB_TUNE_ROUTER_TILE = 8,
+  GEMB_TUNE_EP_SHARED_SMS = 9
 };
 int32_t gemb_set_tuning(int32_t knob, int32_t value);
 /* Bytes of an INTERLEAVED scale buffer for `rows` rows of K elements. */
@@ -740,15 +744,18 @@ int32_t gemb_moe_layer_forward(const gemb_moe_layer_weights* weights, const uint
  * `tokens` tokens of its own; the router is replicated.  Four buffers per rank must be mapped by
  * every rank (peer memory); `comm` carries, per buffer kind, the R device addresses as seen from
  * THIS rank (host arrays), entry [rank] being the rank's own buffer:
- *   send_buffers   tokens * topk message rows of gemb_moe_ep_message_row_bytes(hidden) bytes
+ *   send_buffers   message rows IN: R regions (one per source rank) of tokens * topk rows of
+ *                  gemb_moe_ep_message_row_bytes(hidden) bytes each
  *   recv_buffers   tokens * topk expert output rows, bf16 [tokens * topk, hidden]
  *   count_buffers  int32 [experts]
  *   flag_arrays    2 x 16 words, zero before the first call
  * plus local_epochs: two device words of this rank, zero before the first call.
- * Per layer and rank: route the local tokens; quantise each token once and leave one message row
- * per assignment (payload | block scales | assignment index) in the send buffer, grouped by owner;
- * flag barrier 0; read all ranks' counts and derive every row position from them; pull the rows
- * of the local experts out of the peers' send buffers; grouped gate/up (+ GELU + requantisation)
+ * Per layer and rank: route the local tokens; quantise each token once and push one message row
+ * per assignment (payload | block scales | assignment index) into the owner's message buffer, at
+ * the row's position in this rank's (expert, token, slot) order inside this rank's region there;
+ * flag barrier 0; read all ranks' counts and derive every row position from them; gather the rows
+ * of the local experts out of the regions of the own message buffer into the grouped GEMM's padded
+ * row space; grouped gate/up (+ GELU + requantisation)
  * and grouped down GEMM, whose epilogue stores each finished bf16 row straight into the recv
  * buffer of the token's owner (plain 16-byte stores to peer memory, overlapped with the MMAs);
  * flag barrier 1; slot-ordered combine from the local recv buffer plus the shared branch.

@@ -59,7 +59,7 @@ def test_emulated_ranks_match_single_gpu(lib, dev, ranks, tokens):
 @pytest.mark.parametrize("ranks,tokens,fused", [(2, 96, True), (2, 96, False), (4, 33, True), (8, 5, True), (8, 300, True)])
 def test_library_ep_layer_emulated_ranks_match_single_gpu(lib, dev, ranks, tokens, fused):
     """gemb_moe_ep_layer_stage walked over all emulated ranks of one GPU (message rows with the
-    assignment index, positions from the counts, pull, grouped GEMMs whose epilogue stores each row
+    assignment index pushed into the owner's buffer, positions from the counts, gather, grouped GEMMs whose epilogue stores each row
     into the token owner's receive buffer, combine from that buffer): output, ids, weights and
     counts bit-identical to the single-GPU layer, three passes over reused buffers."""
     from gem16_b200.ep import EpLayer
