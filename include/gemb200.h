@@ -94,7 +94,7 @@ int32_t gemb_device_check(void);
  * GEMMs get beside the NVLink-bound pushing down GEMM of gemb_moe_ep_layer_forward when a side stream is
  * given (default 40, measured best of 0 / 40 / 56 / 72 on two GPUs; 0: the shared branch runs in line behind it);
  * GEMB_TUNE_ROUTER_TILE = which router-logits kernel runs: 0 automatic, 1 the expert-per-thread kernels
- * wherever they apply, 8 / 16 / 32 the tiled kernel with that many tokens per CTA (same bits from all). */
+ * wherever they apply, 8 / 16 / 32 / 64 the tiled kernel with that many tokens per CTA (same bits from all). */
 enum {
   GEMB_TUNE_GEMV_ROWS = 1,
   GEMB_TUNE_GEMV_PDL = 2,

@@ -54,7 +54,7 @@ def test_router_kats(lib, dev, orc):
 
 
 # 1-256 / 257-512 / 513-2,048 tokens run the three expert-per-thread kernels, 2,049 and up the tiled
-# kernel (8-token CTAs while those fit the SMs, 32-token CTAs beyond): every one of them, and the
+# kernel (8- and 16-token CTAs while those fit the SMs, 32-token CTAs beyond, 64-token CTAs from about 7,000 tokens): every one of them, and the
 # sizes the benchmarks run (4,096 and 16,384 tokens x 2,816 x 128), against the oracle bit for bit.
 @pytest.mark.parametrize("tokens,hidden,experts", [(1, 64, 32), (77, 2816, 128), (300, 260, 160), (513, 2816, 128),
                                                     (2048, 2816, 128), (2049, 2816, 128), (2051, 260, 160),
@@ -70,6 +70,26 @@ def test_router_logits_bit_exact(lib, dev, orc, tokens, hidden, experts):
                                    tokens, hidden, experts, None)
         want = orc.moe_router_logits(x, w, bias)
         assert np.array_equal(to_np(out).view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("tokens,hidden,experts", [(2100, 2816, 128), (333, 264, 160), (70, 2816, 128)])
+def test_every_router_kernel_variant_gives_the_same_bits(lib, dev, orc, tokens, hidden, experts):
+    """GEMB_TUNE_ROUTER_TILE forces each logits kernel in turn (expert-per-thread, 8 / 16 / 32 / 64-token tiles):
+    all of them against the oracle bit for bit, on a batch with token, expert and K tails."""
+    rng = np.random.default_rng(tokens + hidden)
+    x = bf16_bits(rng.standard_normal((tokens, hidden)).astype(np.float32))
+    w = (rng.standard_normal((experts, hidden)) * 0.02).astype(np.float32)
+    b = rng.standard_normal(experts).astype(np.float32)
+    want = orc.moe_router_logits(x, w, b)
+    xd, wd, bd = to_dev(x, dev), to_dev(w, dev), to_dev(b, dev)
+    try:
+        for tile in (1, 8, 16, 32, 64):
+            lib.gemb_set_tuning(8, tile)
+            out = torch.full((tokens, experts), float("nan"), device=dev)
+            lib.gemb_moe_router_logits(xd, wd, bd, out, tokens, hidden, experts, None)
+            assert np.array_equal(to_np(out).view(np.uint32), want.view(np.uint32)), tile
+    finally:
+        lib.gemb_set_tuning(8, 0)
 
 
 @pytest.mark.parametrize("tokens", [1, 17, 511, 512, 1023, 4096])
