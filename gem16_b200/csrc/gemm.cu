@@ -812,10 +812,11 @@ int g_gemm_pair = 0;  // 0 = automatic (pairs for the dense 256-wide tile), 1 = 
 
 bool use_pairs() { return g_gemm_pair != 1 && (g_gemm_bn == 0 || g_gemm_bn == 256 || g_gemm_pair == 2); }
 
-// Grouped calls run on CTA pairs when the experts are expected to hold a couple of 128-row tiles
-// each (a pair shares one weight tile between two SMs, which is what the grouped GEMM is short of:
-// operand bandwidth out of L2); with a handful of rows per expert a pair would only tie up a
-// second SM per tile.  The expectation is the rows the caller announced (the layer calls know how
+// Grouped calls run on CTA pairs when the experts are expected to hold many 128-row tiles each.  A pair
+// works in units of 256 rows, so it also multiplies the padding rows behind every expert (on average
+// 128 per expert against 64 for single CTAs that walk the list of real tiles): measured on 128 experts,
+// pairs win from about 768 rows per expert (16,384 tokens top-8: gate/up 328 against 350 us) and lose
+// below (4,096 tokens: 132 against 123 us, down 103 against 90 us).  The expectation is the rows the caller announced (the layer calls know how
 // many assignments they route) or else what the capacity of the padded row space implies.
 thread_local uint64_t g_grouped_rows_hint = 0;
 // Upper bound on the persistent grid of the GEMMs this thread launches (0 = none): lets a caller run two
@@ -825,7 +826,7 @@ bool grouped_pairs(uint64_t padded_rows_max, uint64_t experts) {
   if (!use_pairs()) return false;
   uint64_t rows = g_grouped_rows_hint;
   if (rows == 0) rows = padded_rows_max / 128 > 2 * experts ? (padded_rows_max / 128 - 2 * experts) * 128 : 0;
-  return g_gemm_pair == 2 || rows >= 192 * experts;
+  return g_gemm_pair == 2 || rows >= 768 * experts;
 }
 
 template <bool kFp4, int BN, int kStages, int kAccStages, bool kPair = false>

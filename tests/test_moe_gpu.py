@@ -347,6 +347,18 @@ def test_library_layer_call_equals_the_stage_launches(lib, dev, fused):
     lib.gemb_moe_layer_forward(desc, x, out, tokens, b.c_base, b.c_workspace.numel() - 256, None, None, None, None)
     torch.cuda.synchronize()
     assert torch.equal(out, got)
+    # grouped GEMMs forced onto CTA pairs (256-row units, the odd CTA of a unit often on padding only) and onto
+    # single CTAs (the automatic choice at this size): the same bytes
+    try:
+        for mode in (2, 1):
+            lib.gemb_set_tuning(5, mode)
+            out.zero_()
+            lib.gemb_moe_layer_forward(desc, x, out, tokens, b.c_base, b.c_workspace.numel() - 256, None, None, None, None)
+            torch.cuda.synchronize()
+            lib.gemb_check_device_status()
+            assert torch.equal(out, got), mode
+    finally:
+        lib.gemb_set_tuning(5, 0)
     # too small a workspace, a missing weight: rejected before anything runs
     from gem16_b200.lib import GembError
     with pytest.raises(GembError):
