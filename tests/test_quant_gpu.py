@@ -88,8 +88,8 @@ def test_interleaved_scales(lib, dev, orc, tokens, k):
 
 
 def test_rcp_mode_close_to_exact(lib, dev, orc):
-    # The two contracts differ by at most a few nibbles per thousand (one nibble on
-    # the 16-value vLLM fixture); scales are identical except at rounding boundaries.
+    # The two contracts differ by at most a few nibbles per thousand (one nibble on the 16-value vLLM
+    # fixture of tests/cuda/nvfp4_reference_test.cu:208-255); scales are identical except at rounding boundaries.
     rng = np.random.default_rng(5)
     x = bf16_round(rng.standard_normal((64, 3840)).astype(np.float32))
     g = nvfp4_divisor(x)
