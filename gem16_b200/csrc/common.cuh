@@ -164,6 +164,7 @@ __device__ __forceinline__ void quantize_block16(const float (&v)[16], float g, 
 #pragma unroll
   for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
   float n[16];
+  bool zero_scale = false;
   if constexpr (kRcp) {
     scale_bits = e4m3_encode(__fmul_rn(__fmul_rn(amax, rcp_approx_ftz(6.0f)), g));
     const float ds = e4m3_decode(scale_bits);
@@ -179,15 +180,22 @@ __device__ __forceinline__ void quantize_block16(const float (&v)[16], float g, 
     // 126 values an E4M3 scale can take it is also checked exhaustively around every E2M1 rounding
     // boundary in tests/test_oracle.py.  Sixteen IEEE divisions per block kept the conversion pipe of
     // the fused GEMM epilogue busier than the tensor pipe.
+    // Two elements per instruction (packed fp32 multiply and fma: one IEEE operation per half, so the
+    // rounding of every step is that of the scalar form).  A zero scale gives sixteen +0 codes, set after
+    // the packing below.
     const float r = ds == 0.0f ? 0.0f : __fdiv_rn(1.0f, ds);
+    const float2 g2 = make_float2(g, g), r2 = make_float2(r, r), nds2 = make_float2(-ds, -ds);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float t = __fmul_rn(v[i], g);
-      const float q0 = __fmul_rn(t, r);
+    for (int i = 0; i < 16; i += 2) {
+      const float2 t = __fmul2_rn(make_float2(v[i], v[i + 1]), g2);
+      const float2 q0 = __fmul2_rn(t, r2);
+      const float2 q = __ffma2_rn(__ffma2_rn(nds2, q0, t), r2, q0);
       // (the quotient has the sign of t, also when it is zero: -0 keeps its sign bit in E2M1, and the
       // residual correction alone would turn -0 into +0)
-      n[i] = ds == 0.0f ? 0.0f : copysignf(__fmaf_rn(__fmaf_rn(-ds, q0, t), r, q0), t);
+      n[i] = copysignf(q.x, t.x);
+      n[i + 1] = copysignf(q.y, t.y);
     }
+    zero_scale = ds == 0.0f;
   }
   lo = hi = 0;
 #pragma unroll
@@ -195,6 +203,7 @@ __device__ __forceinline__ void quantize_block16(const float (&v)[16], float g, 
     lo |= static_cast<uint32_t>(e2m1x2_encode(n[2 * i], n[2 * i + 1])) << (8 * i);
     hi |= static_cast<uint32_t>(e2m1x2_encode(n[8 + 2 * i], n[8 + 2 * i + 1])) << (8 * i);
   }
+  if (zero_scale) lo = hi = 0;
 }
 
 #endif  // __CUDACC__
