@@ -398,6 +398,8 @@ def run_moe_stack(args):
     lib.gemb_device_check()
     if args.ep_shared_sms is not None:
         lib.gemb_set_tuning(9, args.ep_shared_sms)
+    if args.ep_split_sms is not None:
+        lib.gemb_set_tuning(10, args.ep_split_sms)
     layers = args.moe_layers
     e_local = MOE["experts"] // world
     own = (rank * e_local, (rank + 1) * e_local)
@@ -477,33 +479,39 @@ def run_moe_stack(args):
         torch.cuda.empty_cache()
 
     # Bit-exactness of the expert-parallel layer against the single-GPU layer, on every rank, outside
-    # the timed regions: 96 tokens per rank through both.
+    # the timed regions: at 96 tokens per rank (the small-batch launch sequence) and at the benchmark's
+    # prefill size (the large-batch sequence that was timed above).
     parity = None
     if world > 1:
-        t_local = 96
         full = synthetic_weights(dev, SEED + 4000, placement_ranks=world)
-        gen = torch.Generator(device=dev)
-        gen.manual_seed(SEED + 4200)
-        x_all = torch.randn((t_local * world, h), device=dev, generator=gen).to(torch.bfloat16).view(torch.int16)
-        sl = slice(rank * t_local, (rank + 1) * t_local)
-        ref = MoeLayer(full, t_local * world, topk, 600.0, 336.0, 336.0, stages=False)
-        ref.fused = args.fused
-        want = ref.forward(x_all).clone()
-        ref_local = MoeLayer(full, t_local, topk, 600.0, 336.0, 336.0, stages=False)
-        ref_local.fused = args.fused
-        ref_local.forward(x_all[sl].contiguous())
-        ep = EpLayer(weights[0], t_local, topk, 600.0, 336.0, 336.0, fused=args.fused)
-        for _ in range(2):
-            got = ep.forward(x_all[sl].contiguous())
-        torch.cuda.synchronize()
-        lib.gemb_check_device_status()
-        routing = (torch.equal(ep.ids, ref.ids[sl]) and torch.equal(ep.weights, ref.weights[sl])
-                   and torch.equal(ep.counts_all.sum(0).to(torch.int32), ref.counts)
-                   and torch.equal(ep.counts, ref_local.counts) and torch.equal(ep.perm, ref_local.perm))
-        parity = {"ranks": world, "tokens_per_rank": t_local,
-                  "ids_counts_perm_bit_exact": d.all_true(bool(routing)),
-                  "output_bit_exact": d.all_true(bool(torch.equal(got, want[sl])))}
-        del full, ref, ref_local, ep
+        checks = []
+        for t_local in (96, 16384 // world):
+            gen = torch.Generator(device=dev)
+            gen.manual_seed(SEED + 4200 + t_local)
+            x_all = torch.randn((t_local * world, h), device=dev, generator=gen).to(torch.bfloat16).view(torch.int16)
+            sl = slice(rank * t_local, (rank + 1) * t_local)
+            ref = MoeLayer(full, t_local * world, topk, 600.0, 336.0, 336.0, stages=False)
+            ref.fused = args.fused
+            want = ref.forward(x_all).clone()
+            ref_local = MoeLayer(full, t_local, topk, 600.0, 336.0, 336.0, stages=False)
+            ref_local.fused = args.fused
+            ref_local.forward(x_all[sl].contiguous())
+            ep = EpLayer(weights[0], t_local, topk, 600.0, 336.0, 336.0, fused=args.fused)
+            for _ in range(2):
+                got = ep.forward(x_all[sl].contiguous())
+            torch.cuda.synchronize()
+            lib.gemb_check_device_status()
+            routing = (torch.equal(ep.ids, ref.ids[sl]) and torch.equal(ep.weights, ref.weights[sl])
+                       and torch.equal(ep.counts_all.sum(0).to(torch.int32), ref.counts)
+                       and torch.equal(ep.counts, ref_local.counts) and torch.equal(ep.perm, ref_local.perm))
+            checks.append({"tokens_per_rank": t_local, "ids_counts_perm_bit_exact": d.all_true(bool(routing)),
+                           "output_bit_exact": d.all_true(bool(torch.equal(got, want[sl])))})
+            del ref, ref_local, ep, x_all, want, got
+            torch.cuda.empty_cache()
+        parity = {"ranks": world, "tokens_per_rank": checks[0]["tokens_per_rank"],
+                  "ids_counts_perm_bit_exact": checks[0]["ids_counts_perm_bit_exact"],
+                  "output_bit_exact": checks[0]["output_bit_exact"], "prefill_size": checks[1]}
+        del full
         torch.cuda.empty_cache()
     del weights
     torch.cuda.empty_cache()
@@ -1130,6 +1138,8 @@ def main():
                     help="gate/up GEMM, GELU requantisation as separate launches instead of the fused epilogue")
     ap.add_argument("--ep-shared-sms", type=int, default=None,
                     help="N > 1: SMs the shared branch gets beside the pushing down GEMM (GEMB_TUNE_EP_SHARED_SMS; default: the library's)")
+    ap.add_argument("--ep-split-sms", type=int, default=None,
+                    help="N > 1: two-half schedule with the first half's push on this many SMs (GEMB_TUNE_EP_SPLIT_SMS)")
     ap.add_argument("--moe-layers", type=int, default=MOE_LAYERS,
                     help="MoE layers held on the device (30 = the benchmark; fewer for a small profiler capture)")
     ap.add_argument("--layers", type=int, default=LAYERS,

@@ -48,12 +48,18 @@ int ep_take_device_error() {
 // Polls a flag barrier makes before it gives up (about 500 ns each once past the first 64):
 // gemb_set_tuning(GEMB_TUNE_EP_BARRIER_SPINS, n); the default is about three seconds.
 int g_ep_barrier_spins = 1 << 22;
+int g_ep_split_sms = 0;    // large batches: experts in two halves, the first half's push on this many SMs (0: one pass)
 int g_ep_shared_sms = 40;  // large batches: SMs given to the shared branch beside the pushing down GEMM (0: in line)
 
 int32_t ep_set_tuning(int32_t knob, int32_t value) {
   if (knob == GEMB_TUNE_EP_BARRIER_SPINS) {
     GEMB_REQUIRE(value >= 0 && value <= (1 << 24), "gemb_set_tuning: barrier polls must be in [0, 2^24] (0 = default)");
     g_ep_barrier_spins = value == 0 ? 1 << 22 : value;
+    return GEMB_OK;
+  }
+  if (knob == GEMB_TUNE_EP_SPLIT_SMS) {
+    GEMB_REQUIRE(value >= 0 && value <= 128 && value % 2 == 0, "gemb_set_tuning: SMs for the first half's push must be even, in [0, 128]");
+    g_ep_split_sms = value;
     return GEMB_OK;
   }
   if (knob == GEMB_TUNE_EP_SHARED_SMS) {
@@ -840,13 +846,14 @@ int32_t ep_stage_send(const char* op, const gemb_moe_layer_weights* w, const gem
   return check_launch(op);
 }
 
-int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const EpCall& call,
-                         uint64_t tokens, bool barriers, gemb_stream_t stream) {
+// Flag barrier 0 + counts + position arithmetic, then the gather of the pushed rows into the padded row space.
+int32_t ep_stage_exchange(const char* op, const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const EpCall& call,
+                          uint64_t tokens, bool barriers, gemb_stream_t stream) {
   const EpBuffers& b = call.b;
   const uint32_t ranks = static_cast<uint32_t>(comm->ranks), me = static_cast<uint32_t>(comm->rank);
   const uint32_t e = static_cast<uint32_t>(w->experts), el = static_cast<uint32_t>(b.el);
-  const uint64_t h = w->hidden, i = w->intermediate, n = tokens * w->topk;
-  if (moe_stage_on(kStageExchange)) {
+  const uint64_t h = w->hidden, n = tokens * w->topk;
+  if (!moe_stage_on(kStageExchange)) return GEMB_OK;
   ep_sync_plan_kernel<<<1, 256, (5 * e + (ranks * e <= kPlanSmemCounts ? ranks * e : 0)) * sizeof(int), stream>>>(
       call.flags, call.counts, ranks, e, me, comm->local_epochs, static_cast<uint32_t>(g_ep_barrier_spins), barriers ? 1 : 0,
       barriers ? 1 : 0, b.counts_all, b.plan, b.recv_prefix, b.recv_src, b.recv_dst, b.row_base,
@@ -867,8 +874,16 @@ int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const 
       regions, b.recv_prefix, b.recv_src, b.recv_dst, segments, el, static_cast<uint32_t>(h),
       static_cast<uint32_t>(call.msg_bytes), c_pad, b.a_packed, b.a_scales, static_cast<uint32_t>(n),
       static_cast<uint32_t>(b.rows_max), reinterpret_cast<int2*>(b.row_meta));
-  GEMB_TRY(check_launch(op));
-  }
+  return check_launch(op);
+}
+
+// Grouped gate/up GEMM (+ GELU + requantisation) of the local experts, or of the range the caller set.
+int32_t ep_stage_gate_up(const char* op, const gemb_moe_layer_weights* w, const EpCall& call, uint64_t tokens,
+                         gemb_stream_t stream) {
+  (void)op;
+  const EpBuffers& b = call.b;
+  const uint32_t el = static_cast<uint32_t>(b.el);
+  const uint64_t h = w->hidden, i = w->intermediate, n = tokens * w->topk;
   const gemb_nvfp4_binding& gu = w->gate_up;
   const gemb_nvfp4_binding& dn = w->down;
   // with balanced routing this rank's experts receive about as many rows as the rank routes itself
@@ -889,6 +904,12 @@ int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const 
     GEMB_TRY(gemb_moe_expert_gelu_quantize(b.gate_up, b.plan, b.p_packed, b.p_scales, b.rows_max, i, dn.input_divisor, stream));
   }
   return GEMB_OK;
+}
+
+int32_t ep_stage_experts(const char* op, const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const EpCall& call,
+                         uint64_t tokens, bool barriers, gemb_stream_t stream) {
+  GEMB_TRY(ep_stage_exchange(op, w, comm, call, tokens, barriers, stream));
+  return ep_stage_gate_up(op, w, call, tokens, stream);
 }
 
 int32_t ep_stage_down(const char* op, const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const EpCall& call,
@@ -983,16 +1004,65 @@ int32_t gemb_moe_ep_layer_forward(const gemb_moe_layer_weights* w, const gemb_mo
     if (moe_stage_on(kStageShared)) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, side_stream));
   }
   GEMB_TRY(ep_stage_send(op, w, comm, call, x, tokens, stream));
+  struct Cap {
+    explicit Cap(uint32_t ctas) { set_gemm_cta_cap(ctas); }
+    ~Cap() { set_gemm_cta_cap(0); }
+  };
+  struct Range {
+    Range(uint32_t lo, uint32_t hi) { set_grouped_expert_range(lo, hi); }
+    ~Range() { set_grouped_expert_range(0, 0); }
+  };
+  // Large batches, GEMB_TUNE_EP_SPLIT_SMS = C > 0: the local experts in two halves, so that the NVLink-bound
+  // pushing down GEMM of the first half (side stream, C SMs) runs beside the gate/up GEMM of the second (the
+  // other SMs), and the second half's pushing down GEMM beside the shared branch.  Needs the grouped GEMMs on
+  // CTA pairs (an expert range is a range of 256-row units) and the fused gate/up epilogue.
+  const uint32_t el = static_cast<uint32_t>(call.b.el);
+  bool split = !forked && g_ep_split_sms > 0 && comm->ranks > 1 && el >= 2 && side_stream != nullptr && fork_event != nullptr &&
+               join_event != nullptr && w->gate_up_fused != nullptr && moe_stage_on(kStageGateUp) && moe_stage_on(kStageDown) &&
+               moe_stage_on(kStageShared) && moe_stage_on(kStageExchange);
+  if (split) {
+    set_grouped_rows_hint(tokens * w->topk);
+    split = grouped_uses_pairs(call.b.rows_max, el);
+    set_grouped_rows_hint(0);
+  }
+  if (split) {
+    const uint32_t sms = static_cast<uint32_t>(sm_count()), c1 = std::min(static_cast<uint32_t>(g_ep_split_sms), sms - 2) & ~1u;
+    const uint32_t s_sms = shared ? std::min(static_cast<uint32_t>(std::max(g_ep_shared_sms, 2)), sms - 2) & ~1u : 0u;
+    GEMB_TRY(ep_stage_exchange(op, w, comm, call, tokens, true, stream));
+    {
+      Range first(0, el / 2);
+      GEMB_TRY(ep_stage_gate_up(op, w, call, tokens, stream));
+      GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));
+      Cap cap(c1);
+      GEMB_TRY(ep_stage_down(op, w, comm, call, tokens, side_stream));
+    }
+    // "first half pushed", recorded on the side stream here and waited for by the main stream only before its own push
+    cudaError_t ce = cudaEventRecord(static_cast<cudaEvent_t>(join_event), side_stream);
+    if (ce != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(ce), cudaGetErrorString(ce));
+    {
+      Range second(el / 2, el);
+      {
+        Cap cap((sms - c1) & ~1u);
+        GEMB_TRY(ep_stage_gate_up(op, w, call, tokens, stream));
+      }
+      ce = cudaStreamWaitEvent(stream, static_cast<cudaEvent_t>(join_event), 0);
+      if (ce != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(ce), cudaGetErrorString(ce));
+      if (shared) {
+        Cap cap(s_sms);
+        GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, side_stream));
+      }
+      Cap cap(shared ? (sms - s_sms) & ~1u : 0u);
+      GEMB_TRY(ep_stage_down(op, w, comm, call, tokens, stream));
+    }
+    GEMB_TRY(stream_join(op, stream, side_stream, fork_event));
+    return ep_stage_combine(op, w, comm, call, out, tokens, true, stream);
+  }
   GEMB_TRY(ep_stage_experts(op, w, comm, call, tokens, true, stream));
   // The pushing down GEMM is bound by NVLink, not by the SMs: with GEMB_TUNE_EP_SHARED_SMS = S the shared
   // branch's GEMMs run beside it on S SMs of their own (both grids capped, so all CTAs are resident at
   // once and none waits for another kernel's CTA to leave an SM).
   const bool beside = shared && !forked && g_ep_shared_sms > 0 && comm->ranks > 1 && side_stream != nullptr &&
                       fork_event != nullptr && join_event != nullptr && moe_stage_on(kStageShared) && moe_stage_on(kStageDown);
-  struct Cap {
-    explicit Cap(uint32_t ctas) { set_gemm_cta_cap(ctas); }
-    ~Cap() { set_gemm_cta_cap(0); }
-  };
   if (beside) {
     GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));
     {

@@ -95,6 +95,8 @@ struct GemmParams {
   // Up projection with a materialised gate (gate_in != null): the accumulator holds Up [M, n], the
   // bf16 Gate [M, n] is read in the epilogue, which writes the quantised GELU product like `gated`.
   const uint16_t* gate_in;
+  // Grouped calls on CTA pairs: only the tiles of experts [expert_lo, expert_hi) (expert_hi = 0: all of them).
+  uint32_t expert_lo, expert_hi;
 };
 
 template <bool kFp4, int BN, int kStages, int kAccStages, bool kPair = false>
@@ -199,7 +201,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const uint32_t n_tiles = (p.n + BN - 1) / BN;
   const int32_t* tile_expert = tile_info;   // stride 2
   // A work unit is one 128-row token tile, or for pairs two consecutive ones (rank picks which).
-  const uint32_t m_units = kPair ? (m_tiles + 1) / 2 : m_tiles;
+  uint32_t m_units = kPair ? (m_tiles + 1) / 2 : m_tiles;
+  uint32_t unit0 = 0;   // first 256-row unit of the call's expert range
+  if constexpr (kPair) {
+    if (p.plan != nullptr && p.expert_hi != 0) {   // padded offsets are multiples of 256 rows: whole units
+      const uint32_t lo_t = min(static_cast<uint32_t>(__ldg(p.plan + 2 + min(p.expert_lo, p.experts))) / BM, plan_tiles);
+      const uint32_t hi_t = min(static_cast<uint32_t>(__ldg(p.plan + 2 + min(p.expert_hi, p.experts))) / BM, plan_tiles);
+      unit0 = lo_t / 2;
+      m_units = hi_t > lo_t ? (hi_t - lo_t + 1) / 2 : 0u;
+    }
+  }
   const uint32_t num_tiles = m_units * n_tiles;
   const uint32_t first_tile = kPair ? blockIdx.x >> 1 : blockIdx.x;
   const uint32_t tile_stride = kPair ? gridDim.x >> 1 : gridDim.x;
@@ -220,7 +231,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const uint32_t gm = min(kGroupM, m_units - first_m);
     const uint32_t within = tile % per_group;
     mt = first_m + within % gm;
-    if constexpr (kPair) mt = mt * 2 + rank;
+    if constexpr (kPair) mt = (mt + unit0) * 2 + rank;
     else if (tile_info != nullptr) mt = min(static_cast<uint32_t>(__ldg(tile_info + 2 * mt + 1)), p.m / BM - 1);
     nt = within / gm;
   };
@@ -822,6 +833,8 @@ thread_local uint64_t g_grouped_rows_hint = 0;
 // Upper bound on the persistent grid of the GEMMs this thread launches (0 = none): lets a caller run two
 // GEMMs side by side on disjoint sets of SMs instead of having their CTAs take turns.
 thread_local uint32_t g_gemm_cta_cap = 0;
+// Expert range of the grouped GEMMs this thread launches next on CTA pairs ({0, 0}: all experts).
+thread_local uint32_t g_expert_lo = 0, g_expert_hi = 0;
 bool grouped_pairs(uint64_t padded_rows_max, uint64_t experts) {
   if (!use_pairs()) return false;
   uint64_t rows = g_grouped_rows_hint;
@@ -904,15 +917,20 @@ int32_t launch_gemm(const char* op, const void* a, const void* b, const GemmPara
 //
 // Automatic choice: 256 wide, except where that leaves SMs without a tile or the tiles are too coarse to
 // balance -- a dense call with fewer 256-wide tiles than SMs (decode-size batches of the shared branch: 23 us
-// instead of 29), and the grouped gate/up GEMM with the GELU epilogue up to 16,384 announced assignments
-// (its 1,408 interleaved columns are 5.5 tiles of 256 but 11 of 128: 37 us instead of 41 at 64 tokens,
-// 89 instead of 92 at 2,048; from 4,096 tokens on the wide tile wins).
-int32_t launch_fp4(const char* op, const void* act, const void* w, const GemmParams& p, bool pairs, cudaStream_t stream) {
+// instead of 29), and the grouped gate/up GEMM with the GELU epilogue up to 128 announced assignments per
+// expert (its 1,408 interleaved columns are 5.5 tiles of 256 but 11 of 128; on 128 experts 37 us instead
+// of 41 at 64 tokens, 89 instead of 92 at 2,048; from 4,096 tokens, 256 rows per expert, the wide tile wins).
+int32_t launch_fp4(const char* op, const void* act, const void* w, const GemmParams& params, bool pairs, cudaStream_t stream) {
+  GemmParams p = params;
+  if (p.plan != nullptr) {
+    p.expert_lo = g_expert_lo;
+    p.expert_hi = g_expert_hi;
+  }
   int bn = g_gemm_bn;
   if (bn == 0) {
     bool narrow;
     if (p.plan != nullptr)
-      narrow = p.gated && g_grouped_rows_hint != 0 && g_grouped_rows_hint <= 16384;
+      narrow = p.gated && g_grouped_rows_hint != 0 && g_grouped_rows_hint <= 128ull * p.experts;
     else
       narrow = static_cast<uint64_t>((p.m + BM - 1) / BM) * ((p.n + 255) / 256) < static_cast<uint64_t>(sm_count());
     bn = narrow ? 128 : 256;
@@ -939,6 +957,13 @@ int32_t validate_gemm(const char* op, uint64_t tokens, uint64_t rows, uint64_t k
 
 void set_grouped_rows_hint(uint64_t rows) { g_grouped_rows_hint = rows; }
 void set_gemm_cta_cap(uint32_t ctas) { g_gemm_cta_cap = ctas; }
+void set_grouped_expert_range(uint32_t lo, uint32_t hi) {
+  g_expert_lo = lo;
+  g_expert_hi = hi;
+}
+bool grouped_uses_pairs(uint64_t padded_rows_max, uint64_t experts) {
+  return g_gemm_bn != 128 && grouped_pairs(padded_rows_max, experts);
+}
 
 int32_t gemm_set_tuning(int32_t knob, int32_t value) {
   if (knob == GEMB_TUNE_GEMM_BN) {

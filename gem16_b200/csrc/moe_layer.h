@@ -51,6 +51,10 @@ void set_grouped_rows_hint(uint64_t rows);
 // Upper bound on the persistent grid of the GEMMs the calling thread launches next (0: none), so that two
 // GEMMs on two streams can each keep a set of SMs to themselves.
 void set_gemm_cta_cap(uint32_t ctas);
+// Restricts the calling thread's next grouped GEMMs to the experts [lo, hi) ({0, 0}: all).  Takes effect on
+// CTA pairs only, which grouped_uses_pairs predicts for the rows announced with set_grouped_rows_hint.
+void set_grouped_expert_range(uint32_t lo, uint32_t hi);
+bool grouped_uses_pairs(uint64_t padded_rows_max, uint64_t experts);
 // Stage selection of the layer calls (gemb_set_tuning(GEMB_TUNE_MOE_STAGE_MASK, ...)).
 enum : int { kStageRoute = 1, kStagePack = 2, kStageGateUp = 4, kStageGelu = 8, kStageDown = 16, kStageCombine = 32,
              kStageShared = 64, kStageExchange = 128 };

@@ -93,6 +93,10 @@ int32_t gemb_device_check(void);
  * GEMB_TUNE_EP_SHARED_SMS = for batches above 1,024 tokens per rank, how many SMs (even) the shared branch's
  * GEMMs get beside the NVLink-bound pushing down GEMM of gemb_moe_ep_layer_forward when a side stream is
  * given (default 40, measured best of 0 / 40 / 56 / 72 on two GPUs; 0: the shared branch runs in line behind it);
+ * GEMB_TUNE_EP_SPLIT_SMS = for the same batches, C > 0 runs the local experts in two halves: the pushing down
+ * GEMM of the first half on C SMs beside the gate/up GEMM of the second half, the second half's pushing down GEMM
+ * beside the shared branch (0, the default: one pass over all local experts; at two GPUs the two-half schedule
+ * measured 1.23-1.35 ms per layer against 1.00 ms, because neither push is light enough on the SMs);
  * GEMB_TUNE_ROUTER_TILE = which router-logits kernel runs: 0 automatic, 1 the expert-per-thread kernels
  * wherever they apply, 8 / 16 / 32 / 64 the tiled kernel with that many tokens per CTA (same bits from all). */
 enum {
@@ -104,7 +108,8 @@ enum {
   GEMB_TUNE_EP_BARRIER_SPINS = 6,
   GEMB_TUNE_MOE_STAGE_MASK = 7,
   GEMB_TUNE_ROUTER_TILE = 8,
-  GEMB_TUNE_EP_SHARED_SMS = 9
+  GEMB_TUNE_EP_SHARED_SMS = 9,
+  GEMB_TUNE_EP_SPLIT_SMS = 10
 };
 int32_t gemb_set_tuning(int32_t knob, int32_t value);
 /* Bytes of an INTERLEAVED scale buffer for `rows` rows of K elements. */

@@ -68,6 +68,20 @@ def main():
         assert torch.equal(layer.ids, ref.ids[sl]) and torch.equal(layer.weights, ref.weights[sl]), "routing differs (library layer)"
         assert torch.equal(layer.counts_all.sum(0).to(torch.int32), ref.counts), "global counts differ (library layer)"
         assert torch.equal(out, want[sl]), f"library expert-parallel layer differs from the single-GPU layer (fused={fused})"
+        if fused and tokens > 1024:
+            # the two-half schedule of large batches (first half's push beside the second half's gate/up GEMM on
+            # disjoint SMs), with the grouped GEMMs forced onto CTA pairs as a full-size batch would have them
+            lib.gemb_set_tuning(5, 2)
+            lib.gemb_set_tuning(10, 74)
+            try:
+                for _ in range(3):
+                    out = layer.forward(x_all[sl].contiguous().view(torch.int16))
+                torch.cuda.synchronize()
+                lib.gemb_check_device_status()
+                assert torch.equal(out, want[sl]), "two-half schedule differs from the single-GPU layer"
+            finally:
+                lib.gemb_set_tuning(10, 0)
+                lib.gemb_set_tuning(5, 0)
     dist.barrier()
     print(f"rank {rank} ok n_recv={ep.last['n_recv']} peer={pull.send.how}", flush=True)
     dist.destroy_process_group()

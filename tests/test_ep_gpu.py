@@ -10,7 +10,9 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("tokens", [96, 5])
+# 96 and 5 tokens per rank take the small-batch launch sequence (shared branch on the side stream from the
+# start), 2,048 the large-batch one (shared branch beside the pushing down GEMM on its own SMs).
+@pytest.mark.parametrize("tokens", [96, 5, 2048])
 def test_expert_parallel_matches_single_gpu(tokens):
     n = torch.cuda.device_count()
     if n < 2:
