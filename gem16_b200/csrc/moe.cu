@@ -48,19 +48,23 @@ namespace {
 // ---------------------------------------------------------------------------------------------
 constexpr int kRtExp = 128, kRtK = 32, kRtThreads = 128;
 
-// kTok = tokens per CTA (64 or 32 for prefill batches -- 64 halves the weight reads from shared memory per
-// fma, at 64 accumulators per thread -- 8 for decode batches so that a few dozen tokens
+// kTok = tokens per CTA (64, 56 or 32 for prefill batches -- 64 halves the weight reads from shared memory per
+// fma, at 64 accumulators per thread; 56 is the same with 14 tokens per thread, for batches that 64-token
+// CTAs would spread unevenly over the SMs -- 8 for decode batches so that a few dozen tokens
 // still spread over many SMs).  Shared tiles are stored k-major with an xor swizzle of the column
 // (multiples of 4 / 8 keep each thread's float4 groups intact) so that both the transposing
 // stores and the float4 loads are bank-conflict free.
 template <int kTok>
-__global__ void __launch_bounds__(kRtThreads, kTok == 64 ? 3 : 4)
+__global__ void __launch_bounds__(kRtThreads, kTok >= 56 ? 3 : 4)
 router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w,
                      const float* __restrict__ bias, float* __restrict__ logits, uint32_t tokens,
                      uint32_t hidden, uint32_t experts) {
-  constexpr int kPerThread = kTok / 4;  // tokens per thread: 16, 8, 4 or 2
-  constexpr int kXCols = kTok > 32 ? kTok : 32;
-  constexpr int kXLoads = kTok > 32 ? kTok / 32 : 1;   // staged 16-byte pieces of the token tile per thread
+  constexpr int kPerThread = kTok / 4;  // tokens per thread: 16, 14, 8, 4 or 2
+  // A warp's tokens occupy a slot of kSlot columns of the shared tile (kSlot = kPerThread rounded up to a
+  // multiple of four, so that the float4 reads stay aligned: 16 columns for the 14 tokens of the 56-token tile).
+  constexpr int kSlot = kPerThread >= 4 ? (kPerThread + 3) / 4 * 4 : kPerThread;
+  constexpr int kXCols = 4 * kSlot > 32 ? 4 * kSlot : 32;
+  constexpr int kXLoads = kTok > 32 ? (kTok + 31) / 32 : 1;   // staged 16-byte pieces of the token tile per thread
   __shared__ __align__(16) float xs[kRtK][kXCols];
   __shared__ __align__(16) float ws[kRtK][kRtExp];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // experts tx*4.., tokens ty*kPerThread..
@@ -112,7 +116,9 @@ router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w
 #pragma unroll
     for (int l = 0; l < kXLoads; ++l) {
       const uint32_t xw[4] = {xr[l].x, xr[l].y, xr[l].z, xr[l].w};
-      const int xcol = (xt + 32 * l) ^ (8 * xq);  // rows xk..xk+7 all have (k / 8) & 3 == xq
+      const int tk = xt + 32 * l;
+      if (tk >= kTok) continue;
+      const int xcol = ((tk / kPerThread) * kSlot + tk % kPerThread) ^ (8 * xq);  // rows xk..xk+7 all have (k / 8) & 3 == xq
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         xs[xk + 2 * i][xcol] = __uint_as_float(xw[i] << 16);
@@ -144,10 +150,10 @@ router_logits_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w
       if constexpr (kPerThread >= 4) {
         float2 xp[kPerThread / 2];
 #pragma unroll
-        for (int q = 0; q < kPerThread / 4; ++q) {   // the swizzle moves groups of eight columns: a group of four stays whole
-          const float4 xa = *reinterpret_cast<const float4*>(&xs[k][(ty * kPerThread + 4 * q) ^ (8 * ((k >> 3) & 3))]);
+        for (int q = 0; q < kSlot / 4; ++q) {   // the swizzle moves groups of eight columns: a group of four stays whole
+          const float4 xa = *reinterpret_cast<const float4*>(&xs[k][(ty * kSlot + 4 * q) ^ (8 * ((k >> 3) & 3))]);
           xp[2 * q] = make_float2(xa.x, xa.y);
-          xp[2 * q + 1] = make_float2(xa.z, xa.w);
+          if (2 * q + 1 < kPerThread / 2) xp[2 * q + 1] = make_float2(xa.z, xa.w);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -915,7 +921,16 @@ int32_t gemb_moe_router_logits(const uint16_t* x_bf16, const float* router_weigh
   if ((tokens + 7) / 8 * expert_tiles <= static_cast<uint64_t>(sm_count())) tile = 8;
   else if ((tokens + 15) / 16 * expert_tiles <= static_cast<uint64_t>(sm_count())) tile = 16;
   else if ((tokens + 63) / 64 * expert_tiles * 8 >= static_cast<uint64_t>(sm_count()) * 6) tile = 64;
-  if (g_router_tile == 8 || g_router_tile == 16 || g_router_tile == 32 || g_router_tile == 64) tile = static_cast<unsigned>(g_router_tile);
+  // 56-token CTAs where they even out the load: with up to two of the large CTAs per SM, an SM's time goes with
+  // the tokens it holds (16,384 tokens: 256 CTAs of 64 leave 40 SMs with one CTA and 108 with two, 293 CTAs
+  // of 56 give every SM two).
+  if (tile == 64) {
+    const uint64_t sms = static_cast<uint64_t>(sm_count());
+    const uint64_t c64 = (tokens + 63) / 64 * expert_tiles, c56 = (tokens + 55) / 56 * expert_tiles;
+    if ((c56 + sms - 1) / sms * 56 < (c64 + sms - 1) / sms * 64) tile = 56;
+  }
+  if (g_router_tile == 8 || g_router_tile == 16 || g_router_tile == 32 || g_router_tile == 56 || g_router_tile == 64)
+    tile = static_cast<unsigned>(g_router_tile);
   dim3 grid(static_cast<unsigned>((tokens + tile - 1) / tile), static_cast<unsigned>((experts + kRtExp - 1) / kRtExp));
   if (tile == 8)
     router_logits_kernel<8><<<grid, kRtThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
@@ -923,6 +938,10 @@ int32_t gemb_moe_router_logits(const uint16_t* x_bf16, const float* router_weigh
                                                             static_cast<uint32_t>(experts));
   else if (tile == 16)
     router_logits_kernel<16><<<grid, kRtThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
+                                                             static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
+                                                             static_cast<uint32_t>(experts));
+  else if (tile == 56)
+    router_logits_kernel<56><<<grid, kRtThreads, 0, stream>>>(x_bf16, router_weight, bias, logits,
                                                              static_cast<uint32_t>(tokens), static_cast<uint32_t>(hidden),
                                                              static_cast<uint32_t>(experts));
   else if (tile == 64)

@@ -67,8 +67,8 @@ int32_t moe_set_tuning(int32_t knob, int32_t value) {
     return GEMB_OK;
   }
   if (knob == GEMB_TUNE_ROUTER_TILE) {
-    GEMB_REQUIRE(value == 0 || value == 1 || value == 8 || value == 16 || value == 32 || value == 64,
-                 "gemb_set_tuning: router tile must be 0 (auto), 1 (expert-per-thread kernels), 8, 16, 32 or 64");
+    GEMB_REQUIRE(value == 0 || value == 1 || value == 8 || value == 16 || value == 32 || value == 56 || value == 64,
+                 "gemb_set_tuning: router tile must be 0 (auto), 1 (expert-per-thread kernels), 8, 16, 32, 56 or 64");
     g_router_tile = value;
     return GEMB_OK;
   }

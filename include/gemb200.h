@@ -98,7 +98,7 @@ int32_t gemb_device_check(void);
  * beside the shared branch (0, the default: one pass over all local experts; at two GPUs the two-half schedule
  * measured 1.23-1.35 ms per layer against 1.00 ms, because neither push is light enough on the SMs);
  * GEMB_TUNE_ROUTER_TILE = which router-logits kernel runs: 0 automatic, 1 the expert-per-thread kernels
- * wherever they apply, 8 / 16 / 32 / 64 the tiled kernel with that many tokens per CTA (same bits from all). */
+ * wherever they apply, 8 / 16 / 32 / 56 / 64 the tiled kernel with that many tokens per CTA (same bits from all). */
 enum {
   GEMB_TUNE_GEMV_ROWS = 1,
   GEMB_TUNE_GEMV_PDL = 2,

@@ -74,7 +74,7 @@ def test_router_logits_bit_exact(lib, dev, orc, tokens, hidden, experts):
 
 @pytest.mark.parametrize("tokens,hidden,experts", [(2100, 2816, 128), (333, 264, 160), (70, 2816, 128)])
 def test_every_router_kernel_variant_gives_the_same_bits(lib, dev, orc, tokens, hidden, experts):
-    """GEMB_TUNE_ROUTER_TILE forces each logits kernel in turn (expert-per-thread, 8 / 16 / 32 / 64-token tiles):
+    """GEMB_TUNE_ROUTER_TILE forces each logits kernel in turn (expert-per-thread, 8 / 16 / 32 / 56 / 64-token tiles):
     all of them against the oracle bit for bit, on a batch with token, expert and K tails."""
     rng = np.random.default_rng(tokens + hidden)
     x = bf16_bits(rng.standard_normal((tokens, hidden)).astype(np.float32))
@@ -83,7 +83,7 @@ def test_every_router_kernel_variant_gives_the_same_bits(lib, dev, orc, tokens, 
     want = orc.moe_router_logits(x, w, b)
     xd, wd, bd = to_dev(x, dev), to_dev(w, dev), to_dev(b, dev)
     try:
-        for tile in (1, 8, 16, 32, 64):
+        for tile in (1, 8, 16, 32, 56, 64):
             lib.gemb_set_tuning(8, tile)
             out = torch.full((tokens, experts), float("nan"), device=dev)
             lib.gemb_moe_router_logits(xd, wd, bd, out, tokens, hidden, experts, None)
