@@ -15,7 +15,9 @@ of the path's three metrics that is defined at 1, 2, 4 and 8 GPUs:
                 The total work is fixed as N grows (strong scaling).  Metric: tokens/s.
 
 `value` is measured with the tokens resident in HBM; `e2e` copies each rank's tokens from pinned
-host memory and the bf16 result back inside the timed region.  The 64-token decode batch through
+host memory and the bf16 result back inside the timed region, every step, on a copy stream: the next
+step's upload and the previous step's download run under the current step's layers, as a serving loop
+would overlap them, and the region closes only when the last result is in host memory.  The 64-token decode batch through
 the same stack is reported beside it, and the other workloads of the path (decode GEMV set, the
 single NVFP4 linear, the 4,096-token MoE layer, the dense prefill projections, output head,
 verifier GEMV, tensor-parallel MLP) under "other_workloads", each with its own roofline and, for
@@ -347,26 +349,29 @@ class Dist:
             dist.destroy_process_group()
 
 
-def timed_region(d: Dist, stream, fn, steps: int) -> float:
+def timed_region(d: Dist, stream, fn, steps: int, tail=None) -> float:
     """Seconds for exactly `steps` calls of fn: CUDA events on the launching stream, a barrier and a
-    device synchronise on both sides, the maximum over ranks."""
+    device synchronise on both sides, the maximum over ranks.  `tail` (optional) is enqueued behind the
+    last step and before the closing event: it makes the stream wait for work the steps left on other streams."""
     import torch
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     d.barrier()
     start.record(stream)
     for _ in range(steps):
         fn()
+    if tail is not None:
+        tail()
     end.record(stream)
     d.barrier()
     return d.max(start.elapsed_time(end) / 1e3)
 
 
-def repeated_regions(d: Dist, stream, fn, steps: int, min_seconds: float = 0.5, max_regions: int = 9):
+def repeated_regions(d: Dist, stream, fn, steps: int, min_seconds: float = 0.5, max_regions: int = 9, tail=None):
     """Runs the K-step region until at least min_seconds of device time have been measured (at most
     max_regions times) and returns (median seconds per region, all samples)."""
     samples = []
     while len(samples) < 1 or (sum(samples) < min_seconds and len(samples) < max_regions):
-        samples.append(timed_region(d, stream, fn, steps))
+        samples.append(timed_region(d, stream, fn, steps, tail))
     return statistics.median(samples), samples
 
 
@@ -433,11 +438,45 @@ def run_moe_stack(args):
 
         graph = capture(stream, enqueue)
 
+        # End to end, as a serving loop would run it: every step's tokens come from pinned host memory and every
+        # step's result goes back to it, on a copy stream, so that step i + 1's upload and step i - 1's download
+        # run under step i's layers.  Staging buffers on the device decouple the copies from the graph's fixed
+        # input and output: the compute stream takes the staged tokens (device-to-device) before its layers and
+        # leaves the result in a staging buffer behind them.
+        copy_stream = torch.cuda.Stream(device=dev)
+        x_stage, out_stage = torch.empty_like(x_dev), torch.empty_like(obj.out)
+        ev_h2d, ev_taken, ev_out, ev_d2h = (torch.cuda.Event() for _ in range(4))
+
+        def upload():
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(ev_taken)          # the previous tokens have left the staging buffer
+                x_stage.copy_(x_host, non_blocking=True)
+                ev_h2d.record(copy_stream)
+
         def step_e2e():
+            stream.wait_event(ev_h2d)                     # this step's tokens have arrived
+            x_dev.copy_(x_stage, non_blocking=True)
+            ev_taken.record(stream)
+            upload()                                      # the next step's tokens, under this step's layers
+            graph.replay()
+            stream.wait_event(ev_d2h)                     # the previous result has left its staging buffer
+            out_stage.copy_(obj.out, non_blocking=True)
+            ev_out.record(stream)
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(ev_out)
+                out_host.copy_(out_stage, non_blocking=True)
+                ev_d2h.record(copy_stream)
+
+        def step_e2e_serial():
+            """The same step with nothing overlapped: upload, layers, download, host synchronise."""
             x_dev.copy_(x_host, non_blocking=True)
             graph.replay()
             out_host.copy_(obj.out, non_blocking=True)
             stream.synchronize()
+
+        def e2e_tail():
+            stream.wait_event(ev_d2h)                     # the last result is in host memory
+            stream.wait_event(ev_h2d)                     # and the look-ahead upload has ended
 
         with torch.cuda.stream(stream):
             for _ in range(max(args.warmup, 3)):
@@ -445,9 +484,15 @@ def run_moe_stack(args):
             sampler = ClockSampler(d.local).start() if rank == 0 else None
             secs, samples = repeated_regions(d, stream, graph.replay, args.steps)
             clocks = sampler.stop() if sampler else None
+            ev_taken.record(stream)
+            ev_d2h.record(stream)
+            upload()
             for _ in range(2):
                 step_e2e()
-            secs_e2e, _ = repeated_regions(d, stream, step_e2e, args.steps)
+            secs_e2e, _ = repeated_regions(d, stream, step_e2e, args.steps, tail=e2e_tail)
+            stream.synchronize()
+            copy_stream.synchronize()
+            secs_e2e_serial = timed_region(d, stream, step_e2e_serial, args.steps)
             lib.gemb_check_device_status()
             # Stage by stage: the same graph with one stage of the layer call enabled at a time, on the
             # workspace the full pass left behind (each layer's own weights, the last layer's plan).
@@ -471,7 +516,7 @@ def run_moe_stack(args):
                     del g
                 lib.gemb_check_device_status()
         phases[name] = {"tokens": tokens, "tokens_per_rank": t_local, "secs_per_step": secs / args.steps,
-                        "region_samples_s": samples, "secs_per_step_e2e": secs_e2e / args.steps, "clocks": clocks,
+                        "region_samples_s": samples, "secs_per_step_e2e": secs_e2e / args.steps, "secs_per_step_e2e_serial": secs_e2e_serial / args.steps, "clocks": clocks,
                         "stage_us_per_layer": stage_us, "assignments_on_rank0_last_layer": counts_total,
                         "h2d_bytes": x_host.numel() * 2 * world, "d2h_bytes": out_host.numel() * 2 * world,
                         "exchange": ("peer memory, " + obj.send.how) if world > 1 else "none"}
@@ -577,7 +622,10 @@ def moe_headline(args):
         "config": dict(moe_config(world), layers=layers, exchange=pre["exchange"], fused_gelu_epilogue=bool(args.fused),
                        timing=f"median of {len(pre['region_samples_s'])} regions of {args.steps} steps"),
         "e2e": {"value": tokens / pre["secs_per_step_e2e"], "unit": "tokens/s", "h2d_bytes_per_step": pre["h2d_bytes"],
-                "d2h_bytes_per_step": pre["d2h_bytes"]},
+                "d2h_bytes_per_step": pre["d2h_bytes"],
+                "how": "every step uploads its tokens from pinned host memory and downloads its result; the copies run on a "
+                       "second stream under the neighbouring steps' layers; the region ends when the last result is in host memory",
+                "not_overlapped": tokens / pre["secs_per_step_e2e_serial"]},
         "gpu_launches": launches_per_layer * layers * args.steps,
         "clocks": pre["clocks"],
         "roofline": roof,
