@@ -941,6 +941,56 @@ int32_t ep_stage_combine(const char* op, const gemb_moe_layer_weights* w, const 
                           w->hidden, w->topk, stream);
 }
 
+// Grid caps and expert ranges of the GEMM launches of the calling thread, for the duration of a scope.
+struct Cap {
+  explicit Cap(uint32_t ctas) { set_gemm_cta_cap(ctas); }
+  ~Cap() { set_gemm_cta_cap(0); }
+};
+struct Range {
+  Range(uint32_t lo, uint32_t hi) { set_grouped_expert_range(lo, hi); }
+  ~Range() { set_grouped_expert_range(0, 0); }
+};
+
+// The layer behind the pack kernel with the local experts in two halves: exchange; gate/up of the first half;
+// then the first half's pushing down GEMM on C SMs of the side stream beside the second half's gate/up GEMM
+// on the others; then the second half's push beside the shared branch; join; barrier 1 and combine.
+int32_t ep_forward_two_halves(const char* op, const gemb_moe_layer_weights* w, const gemb_moe_ep_comm* comm, const EpCall& call,
+                              const uint16_t* x, uint16_t* out, uint64_t tokens, gemb_stream_t stream, gemb_stream_t side_stream,
+                              void* fork_event, void* join_event) {
+  const bool shared = w->shared_intermediate != 0;
+  const uint32_t el = static_cast<uint32_t>(call.b.el);
+  const uint32_t sms = static_cast<uint32_t>(sm_count()), c1 = std::min(static_cast<uint32_t>(g_ep_split_sms), sms - 2) & ~1u;
+  const uint32_t s_sms = shared ? std::min(static_cast<uint32_t>(std::max(g_ep_shared_sms, 2)), sms - 2) & ~1u : 0u;
+  GEMB_TRY(ep_stage_exchange(op, w, comm, call, tokens, true, stream));
+  {
+    Range first(0, el / 2);
+    GEMB_TRY(ep_stage_gate_up(op, w, call, tokens, stream));
+    GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));
+    Cap cap(c1);
+    GEMB_TRY(ep_stage_down(op, w, comm, call, tokens, side_stream));
+  }
+  // "first half pushed", recorded on the side stream here and waited for by the main stream only before its own push
+  cudaError_t ce = cudaEventRecord(static_cast<cudaEvent_t>(join_event), side_stream);
+  if (ce != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(ce), cudaGetErrorString(ce));
+  {
+    Range second(el / 2, el);
+    {
+      Cap cap((sms - c1) & ~1u);
+      GEMB_TRY(ep_stage_gate_up(op, w, call, tokens, stream));
+    }
+    ce = cudaStreamWaitEvent(stream, static_cast<cudaEvent_t>(join_event), 0);
+    if (ce != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(ce), cudaGetErrorString(ce));
+    if (shared) {
+      Cap cap(s_sms);
+      GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, side_stream));
+    }
+    Cap cap(shared ? (sms - s_sms) & ~1u : 0u);
+    GEMB_TRY(ep_stage_down(op, w, comm, call, tokens, stream));
+  }
+  GEMB_TRY(stream_join(op, stream, side_stream, fork_event));
+  return ep_stage_combine(op, w, comm, call, out, tokens, true, stream);
+}
+
 }  // namespace
 }  // namespace gemb
 
@@ -1004,14 +1054,6 @@ int32_t gemb_moe_ep_layer_forward(const gemb_moe_layer_weights* w, const gemb_mo
     if (moe_stage_on(kStageShared)) GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, side_stream));
   }
   GEMB_TRY(ep_stage_send(op, w, comm, call, x, tokens, stream));
-  struct Cap {
-    explicit Cap(uint32_t ctas) { set_gemm_cta_cap(ctas); }
-    ~Cap() { set_gemm_cta_cap(0); }
-  };
-  struct Range {
-    Range(uint32_t lo, uint32_t hi) { set_grouped_expert_range(lo, hi); }
-    ~Range() { set_grouped_expert_range(0, 0); }
-  };
   // Large batches, GEMB_TUNE_EP_SPLIT_SMS = C > 0: the local experts in two halves, so that the NVLink-bound
   // pushing down GEMM of the first half (side stream, C SMs) runs beside the gate/up GEMM of the second (the
   // other SMs), and the second half's pushing down GEMM beside the shared branch.  Needs the grouped GEMMs on
@@ -1025,38 +1067,7 @@ int32_t gemb_moe_ep_layer_forward(const gemb_moe_layer_weights* w, const gemb_mo
     split = grouped_uses_pairs(call.b.rows_max, el);
     set_grouped_rows_hint(0);
   }
-  if (split) {
-    const uint32_t sms = static_cast<uint32_t>(sm_count()), c1 = std::min(static_cast<uint32_t>(g_ep_split_sms), sms - 2) & ~1u;
-    const uint32_t s_sms = shared ? std::min(static_cast<uint32_t>(std::max(g_ep_shared_sms, 2)), sms - 2) & ~1u : 0u;
-    GEMB_TRY(ep_stage_exchange(op, w, comm, call, tokens, true, stream));
-    {
-      Range first(0, el / 2);
-      GEMB_TRY(ep_stage_gate_up(op, w, call, tokens, stream));
-      GEMB_TRY(stream_fork(op, stream, side_stream, fork_event));
-      Cap cap(c1);
-      GEMB_TRY(ep_stage_down(op, w, comm, call, tokens, side_stream));
-    }
-    // "first half pushed", recorded on the side stream here and waited for by the main stream only before its own push
-    cudaError_t ce = cudaEventRecord(static_cast<cudaEvent_t>(join_event), side_stream);
-    if (ce != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(ce), cudaGetErrorString(ce));
-    {
-      Range second(el / 2, el);
-      {
-        Cap cap((sms - c1) & ~1u);
-        GEMB_TRY(ep_stage_gate_up(op, w, call, tokens, stream));
-      }
-      ce = cudaStreamWaitEvent(stream, static_cast<cudaEvent_t>(join_event), 0);
-      if (ce != cudaSuccess) return fail(GEMB_INTERNAL, "%s: %s: %s", op, cudaGetErrorName(ce), cudaGetErrorString(ce));
-      if (shared) {
-        Cap cap(s_sms);
-        GEMB_TRY(moe_shared_stage(w, x, tokens, call.b.c, side_stream));
-      }
-      Cap cap(shared ? (sms - s_sms) & ~1u : 0u);
-      GEMB_TRY(ep_stage_down(op, w, comm, call, tokens, stream));
-    }
-    GEMB_TRY(stream_join(op, stream, side_stream, fork_event));
-    return ep_stage_combine(op, w, comm, call, out, tokens, true, stream);
-  }
+  if (split) return ep_forward_two_halves(op, w, comm, call, x, out, tokens, stream, side_stream, fork_event, join_event);
   GEMB_TRY(ep_stage_experts(op, w, comm, call, tokens, true, stream));
   // The pushing down GEMM is bound by NVLink, not by the SMs: with GEMB_TUNE_EP_SHARED_SMS = S the shared
   // branch's GEMMs run beside it on S SMs of their own (both grids capped, so all CTAs are resident at
