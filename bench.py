@@ -266,7 +266,7 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    tokens = 64
+    tokens = int(os.environ.get("GEMB_BENCH_REFERENCE_TOKENS", "64"))   # the CPU test suite shrinks the sample
     steps = max(1, min(args.steps, 5))
     times = []
     for _ in range(min(args.warmup, 1) + steps):
