@@ -291,18 +291,27 @@ def synthetic_weights(dev, seed, hidden=2816, experts=128, inter=704, shared_int
         b = -1.1 * torch.log(rank)
         bias = (b - b.mean()).float()
         if placement_ranks > 1:
-            # Load-time expert placement: expert ids are labels, so hand the popularity prior out
-            # in serpentine order over the ranks (hot experts spread evenly); rank r owns ids
-            # [r*E/R, (r+1)*E/R).  The prior is all that is known before any token is routed.
-            order = torch.argsort(bias, descending=True)
+            # Load-time expert placement: expert ids are labels; rank r owns ids [r*E/R, (r+1)*E/R).  What is
+            # known before any token is routed is the popularity prior, and with top-8 routing a hot expert
+            # saturates (it is picked by nearly every token and then holds as many rows as a whole rank's fair
+            # share at 8 ranks), so the expected load is estimated by routing a seeded calibration batch of
+            # random logits (the router weight's contribution is N(0, sigma^2) per expert) through the same
+            # top-k, and the experts go to the ranks greedily, heaviest first, each to the least loaded rank
+            # that still has a free slot.  Serpentine dealing by prior left the fullest rank 31 % above the mean
+            # at 8 ranks.
+            sigma = 0.02 * float(hidden) ** 0.5
+            z = torch.randn((8192, experts), device=dev, generator=g) * sigma + bias
+            picked = torch.topk(z, 8, dim=1).indices.reshape(-1)
+            load_est = torch.bincount(picked, minlength=experts).double().cpu()
+            order = sorted(range(experts), key=lambda e: (-float(load_est[e]), e))
             per = experts // placement_ranks
             new_bias = torch.empty_like(bias)
-            fill = [0] * placement_ranks
-            for p, src in enumerate(order.tolist()):
-                rnd, pos = divmod(p, placement_ranks)
-                r = pos if rnd % 2 == 0 else placement_ranks - 1 - pos
+            fill, rank_load = [0] * placement_ranks, [0.0] * placement_ranks
+            for src in order:
+                r = min((r for r in range(placement_ranks) if fill[r] < per), key=lambda r: (rank_load[r], r))
                 new_bias[r * per + fill[r]] = bias[src]
                 fill[r] += 1
+                rank_load[r] += float(load_est[src])
             bias = new_bias
     # Every rank draws every expert (identical streams) and keeps its own range.
     lo, hi = expert_range if expert_range is not None else (0, experts)
