@@ -686,12 +686,17 @@ permute_small_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ coun
 // of its topk assignments, block scales in the interleaved layout of the padded row space.
 // One CTA per token, one thread per 16-element block.
 // ---------------------------------------------------------------------------------------------
+constexpr uint32_t kDispatchMaxBlocks = 1024;   // 16-element blocks of a token whose scales are staged in shared memory
 __global__ void __launch_bounds__(256)
 dispatch_quantize_kernel(const uint16_t* __restrict__ x, const int32_t* __restrict__ slot_rows,
                          uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, uint32_t hidden,
                          uint32_t topk, float g, uint32_t c_pad) {
   const uint32_t t = blockIdx.x;
   __shared__ int rows[32];
+  // The token's scale bytes meet here, so that they leave as 4-byte words (four consecutive K blocks are
+  // contiguous in the interleaved layout) instead of one byte store per block and assignment.
+  __shared__ __align__(4) uint8_t token_scales[kDispatchMaxBlocks];
+  const bool words = hidden / 16 <= kDispatchMaxBlocks && (hidden / 16) % 4 == 0;
   if (threadIdx.x < topk) rows[threadIdx.x] = __ldg(slot_rows + static_cast<uint64_t>(t) * topk + threadIdx.x);
   __syncthreads();
   for (uint32_t c = threadIdx.x; c < hidden / 16; c += blockDim.x) {
@@ -708,11 +713,20 @@ dispatch_quantize_kernel(const uint16_t* __restrict__ x, const int32_t* __restri
     uint32_t lo, hi;
     uint8_t sb;
     quantize_block16<false>(v, g, lo, hi, sb);
+    if (words) token_scales[c] = sb;
     for (uint32_t s = 0; s < topk; ++s) {
       const uint64_t r = static_cast<uint64_t>(rows[s]);
       *reinterpret_cast<uint2*>(packed + r * (hidden / 2) + c * 8) = make_uint2(lo, hi);
-      scales[interleaved_scale_offset(r, c, c_pad)] = sb;
+      if (!words) scales[interleaved_scale_offset(r, c, c_pad)] = sb;
     }
+  }
+  if (!words) return;
+  __syncthreads();
+  const uint32_t quads = hidden / 64;
+  for (uint32_t idx = threadIdx.x; idx < quads * topk; idx += blockDim.x) {
+    const uint32_t s = idx / quads, q = idx % quads;
+    *reinterpret_cast<uint32_t*>(scales + interleaved_scale_offset(static_cast<uint64_t>(rows[s]), 4 * q, c_pad)) =
+        *reinterpret_cast<const uint32_t*>(token_scales + 4 * q);
   }
 }
 
