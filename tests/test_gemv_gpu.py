@@ -157,7 +157,7 @@ def test_fused_quantisation_at_rounding_boundaries(lib, dev, orc):
 
 
 @pytest.mark.parametrize("tokens,rows,k", [(2, 40, 528), (3, 8192, 3840), (5, 3840, 15360), (8, 1000, 4096), (7, 13, 16),
-                                           (4, 3841, 2816), (6, 30720, 3840)])
+                                           (4, 3841, 2816), (6, 30720, 3840), (3, 64, 8192), (6, 200, 12288)])
 def test_fp8_gemv_small_batch(lib, dev, orc, tokens, rows, k):
     """The verifier-sized batch (src/cuda/fp8/sm120.h:45-55): one pass over the weights for all tokens on
     the warp-level tensor-core path, within the GEMV budget of the binary64 oracle; the SIMT form behind
@@ -194,7 +194,7 @@ def test_fp8_gemv_small_batch_is_exact_on_representable_sums(lib, dev):
     magnitude 0.5 .. 2 and power-of-two scales).  The same here: both forms and the single-token kernel
     return the same bits."""
     codes = np.array([0x00, 0x30, 0x38, 0x40, 0xB0, 0xB8, 0xC0], np.uint8)
-    tokens, rows, k = 8, 1030, 3840
+    tokens, rows, k = 8, 1030, 4096
     idx = np.arange(tokens * k, dtype=np.int64)
     x = codes[(idx * 5 + idx // k) % 7].reshape(tokens, k)
     idx = np.arange(rows * k, dtype=np.int64)
