@@ -266,6 +266,32 @@ class MoeLayer:
         return self.out
 
 
+def place_experts(bias, hidden, ranks, generator, topk=8, samples=8192, weight_std=0.02):
+    """Load-time expert placement for expert parallelism: returns the router bias re-labelled so that rank r owns
+    ids [r*E/R, (r+1)*E/R) (expert ids are labels; the router rows are exchangeable).  What is known before any
+    token is routed is the popularity prior, and with top-k routing a hot expert saturates (it is picked by nearly
+    every token and then holds as many rows as a whole rank's fair share at 8 ranks), so the expected load is
+    estimated by routing a seeded calibration batch of random logits (the router weight's contribution is
+    N(0, sigma^2) per expert) through the same top-k, and the experts go to the ranks greedily, heaviest first,
+    each to the least loaded rank that still has a free slot.  Dealing the prior out in serpentine order left the
+    fullest rank 31 % above the mean at 8 ranks; this leaves it 1-2 % above."""
+    experts = bias.numel()
+    sigma = weight_std * float(hidden) ** 0.5
+    z = torch.randn((samples, experts), device=bias.device, generator=generator) * sigma + bias
+    picked = torch.topk(z, topk, dim=1).indices.reshape(-1)
+    load_est = torch.bincount(picked, minlength=experts).double().cpu()
+    order = sorted(range(experts), key=lambda e: (-float(load_est[e]), e))
+    per = experts // ranks
+    new_bias = torch.empty_like(bias)
+    fill, rank_load = [0] * ranks, [0.0] * ranks
+    for src in order:
+        r = min((r for r in range(ranks) if fill[r] < per), key=lambda r: (rank_load[r], r))
+        new_bias[r * per + fill[r]] = bias[src]
+        fill[r] += 1
+        rank_load[r] += float(load_est[src])
+    return new_bias
+
+
 def synthetic_weights(dev, seed, hidden=2816, experts=128, inter=704, shared_inter=2112, zipf=True,
                       expert_range=None, placement_ranks=1, keep_compact=False):
     """Seeded synthetic 26B-A4B-like layer generated and quantised on the GPU: router fp32 ~ N(0, 0.02)
@@ -291,28 +317,7 @@ def synthetic_weights(dev, seed, hidden=2816, experts=128, inter=704, shared_int
         b = -1.1 * torch.log(rank)
         bias = (b - b.mean()).float()
         if placement_ranks > 1:
-            # Load-time expert placement: expert ids are labels; rank r owns ids [r*E/R, (r+1)*E/R).  What is
-            # known before any token is routed is the popularity prior, and with top-8 routing a hot expert
-            # saturates (it is picked by nearly every token and then holds as many rows as a whole rank's fair
-            # share at 8 ranks), so the expected load is estimated by routing a seeded calibration batch of
-            # random logits (the router weight's contribution is N(0, sigma^2) per expert) through the same
-            # top-k, and the experts go to the ranks greedily, heaviest first, each to the least loaded rank
-            # that still has a free slot.  Serpentine dealing by prior left the fullest rank 31 % above the mean
-            # at 8 ranks.
-            sigma = 0.02 * float(hidden) ** 0.5
-            z = torch.randn((8192, experts), device=dev, generator=g) * sigma + bias
-            picked = torch.topk(z, 8, dim=1).indices.reshape(-1)
-            load_est = torch.bincount(picked, minlength=experts).double().cpu()
-            order = sorted(range(experts), key=lambda e: (-float(load_est[e]), e))
-            per = experts // placement_ranks
-            new_bias = torch.empty_like(bias)
-            fill, rank_load = [0] * placement_ranks, [0.0] * placement_ranks
-            for src in order:
-                r = min((r for r in range(placement_ranks) if fill[r] < per), key=lambda r: (rank_load[r], r))
-                new_bias[r * per + fill[r]] = bias[src]
-                fill[r] += 1
-                rank_load[r] += float(load_est[src])
-            bias = new_bias
+            bias = place_experts(bias, hidden, placement_ranks, g)
     # Every rank draws every expert (identical streams) and keeps its own range.
     lo, hi = expert_range if expert_range is not None else (0, experts)
     gu, dn = [], []
